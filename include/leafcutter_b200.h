@@ -1,0 +1,233 @@
+/* leafcutter_b200 -- C ABI of the B200 (sm_100a) token-generation path.
+ *
+ * A drop-in for the decode hot path of the LeafcutterLLM Rust crate: the
+ * operator level mirrors `trait Backend` and the quantised-matmul free
+ * functions, the model level mirrors `Engine` / `ShardEngine` / `KVCache`.
+ * Citations are file:line inside the reference project.
+ *
+ * Conventions
+ *   - every entry point returns an int32 status: 0 = ok, negative = lc_status;
+ *     no exception or panic crosses this boundary;
+ *   - the text of the last error of the calling thread: lc_last_error();
+ *   - pointers are HOST pointers unless the name ends in `_dev`;
+ *   - outputs are caller-allocated; matrices are row-major f32;
+ *   - there is no CPU fallback: without a usable CUDA device every compute
+ *     entry point returns LC_ERR_CUDA;
+ *   - one lc_model = one engine; calls on one handle must be serialised by the
+ *     caller (the reference wraps its Engine in a Mutex, rust/src/api/mod.rs:42,50);
+ *     distinct handles may be used from distinct threads.
+ */
+#ifndef LEAFCUTTER_B200_H
+#define LEAFCUTTER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum lc_status {
+    LC_OK = 0,
+    LC_ERR_INVALID = -1,     /* bad argument / shape mismatch (the reference asserts, rust/src/model/tensor.rs:108-113,139) */
+    LC_ERR_UNSUPPORTED = -2, /* quant type or feature not implemented */
+    LC_ERR_CUDA = -3,        /* CUDA runtime error or no device; see lc_last_error() */
+    LC_ERR_OOM = -4,         /* device allocation failed */
+    LC_ERR_KV_FULL = -5,     /* no free KV page / sequence slot */
+    LC_ERR_MISSING = -6,     /* a required tensor was never set (the reference panics, rust/src/inference/engine.rs:84,97,101) */
+    LC_ERR_STATE = -7        /* call order (e.g. forward before finalize) */
+} lc_status;
+
+/* ggml tensor type codes: rust/src/model/quant.rs:45-76 */
+enum {
+    LC_TYPE_F32 = 0, LC_TYPE_F16 = 1, LC_TYPE_Q4_0 = 2, LC_TYPE_Q8_0 = 8,
+    LC_TYPE_Q4_K = 12, LC_TYPE_Q5_K = 13, LC_TYPE_Q6_K = 14, LC_TYPE_IQ4_NL = 20
+};
+
+const char* lc_last_error(void);
+/* Library version string and the number of CUDA devices visible (0 when none). */
+const char* lc_version(void);
+int32_t lc_device_count(void);
+int32_t lc_set_device(int32_t device);
+
+/* Bytes of a tensor of `count` elements of ggml type `typ`:
+ * rust/src/model/quant.rs:254-261 (tensor_size), rust/src/model/gguf.rs:307-313. */
+size_t lc_tensor_bytes(uint32_t typ, size_t count);
+
+/* ------------------------------------------------------------------------
+ * L1 -- operator level.  One entry per method of `trait Backend`
+ * (rust/src/backend/mod.rs:18-46, CPU behaviour rust/src/backend/cpu.rs:13-83).
+ * Host slices in, host slice out, as the trait has it.
+ * ---------------------------------------------------------------------- */
+/* Backend::matmul  (backend/mod.rs:21; cpu.rs:13-23): c[m,n] = a[m,k] . b[k,n] */
+int32_t lc_matmul_f32(const float* a, const float* b, size_t m, size_t k, size_t n, float* c);
+/* Backend::vec_add (mod.rs:24) */
+int32_t lc_vec_add(const float* a, const float* b, size_t n, float* out);
+/* Backend::vec_mul (mod.rs:27) */
+int32_t lc_vec_mul(const float* a, const float* b, size_t n, float* out);
+/* Backend::vec_scale (mod.rs:30) */
+int32_t lc_vec_scale(const float* a, float scale, size_t n, float* out);
+/* Backend::vec_scale_mul (mod.rs:33): out = (a * scale) * b */
+int32_t lc_vec_scale_mul(const float* a, float scale, const float* b, size_t n, float* out);
+/* Backend::rms_norm (mod.rs:36; cpu.rs:49-60): x is [rows, hidden] with rows = n / hidden */
+int32_t lc_rms_norm(const float* x, const float* weight, float eps, size_t hidden, size_t rows, float* out);
+/* Backend::silu (mod.rs:39; cpu.rs:62-64) */
+int32_t lc_silu(const float* x, size_t n, float* out);
+/* Backend::softmax (mod.rs:42; cpu.rs:66-79) */
+int32_t lc_softmax(const float* x, size_t hidden, size_t rows, float* out);
+/* Backend::sum_sq (mod.rs:45) */
+int32_t lc_sum_sq(const float* x, size_t n, float* out);
+
+/* kernels::dequantize_{q4_0,q8_0,q4_k,q5_k,q6_k,iq4_nl} and the F32/F16 arms of
+ * GGUFModel::dequantize (rust/src/kernels/mod.rs:16-216, rust/src/model/loader.rs:205-235).
+ * Bit-exact with the reference. */
+int32_t lc_dequantize(uint32_t typ, const void* bytes, size_t n_elems, float* out);
+
+/* Tensor::matmul against a quantised weight (rust/src/model/tensor.rs:107-135 after
+ * loader.rs:145-168): c[m,n] = a[m,k] . dequant(W)^T, W = raw GGUF blocks, n rows of k/block
+ * blocks (quant blocks run along k).  The weight is never expanded to f32 in memory. */
+int32_t lc_qmatmul(uint32_t typ, const float* a, const void* w_blocks, size_t m, size_t k, size_t n, float* c);
+
+/* int8_gemm::q8_0_matmul / q4_0_matmul (rust/src/kernels/int8_gemm.rs:172-194, 336-358) over the
+ * shard-order matrices of q8_0.rs:56-86 / q4_0.rs:66-94: blocks laid [k rows][n/32], one f32
+ * scale per block; Q8_0 qs int8[k*n]; Q4_0 qs uint8[k*n/2] with byte i = elements 2i, 2i+1. */
+int32_t lc_q8_0_matmul_shard(const float* a, const float* scales, const int8_t* qs, size_t m, size_t k, size_t n, float* c);
+int32_t lc_q4_0_matmul_shard(const float* a, const float* scales, const uint8_t* qs, size_t m, size_t k, size_t n, float* c);
+
+/* attention::apply_rotary_emb (rust/src/inference/attention.rs:13-34), in place on x[seq, heads, head_dim];
+ * pos0 = 0 reproduces the reference (position = index inside the call). */
+int32_t lc_rope(float* x, size_t seq, size_t heads, size_t head_dim, float theta, size_t pos0);
+/* sampler::sample_top_p greedy branch (rust/src/inference/sampler.rs:6-10): LAST index among equal maxima. */
+int32_t lc_argmax(const float* v, size_t n, int64_t* out_index);
+
+/* Device-resident variants used to time kernels without host copies.  All pointers are device
+ * pointers obtained from lc_dev_alloc; work is queued on the library's stream of the current device. */
+int32_t lc_dev_alloc(size_t bytes, void** out_dev);
+int32_t lc_dev_free(void* dev);
+int32_t lc_dev_upload(void* dst_dev, const void* src_host, size_t bytes);
+int32_t lc_dev_download(void* dst_host, const void* src_dev, size_t bytes);
+int32_t lc_dev_sync(void);
+int32_t lc_qmatmul_dev(uint32_t typ, const float* a_dev, const void* w_dev, size_t m, size_t k, size_t n, float* c_dev);
+int32_t lc_dequantize_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, float* out_dev);
+/* CUDA-event stopwatch on the library's stream: begin, queue work, end -> milliseconds. */
+int32_t lc_timer_begin(void);
+int32_t lc_timer_end(float* out_ms);
+/* Writes `bytes` bytes to a scratch buffer larger than L2 so the next kernel starts from a cold cache. */
+int32_t lc_flush_l2(void);
+
+/* Deterministic synthetic tensors (test and benchmark input; no counterpart in the reference).
+ * Element i of tensor (seed, name) is N(0, sigma) from a counter-based generator, quantised to
+ * `typ` in GGUF block order.  The host and the device generator produce identical bytes. */
+int32_t lc_synth_tensor_host(uint32_t typ, uint64_t seed, const char* name, float sigma, size_t n_elems, void* out_bytes);
+int32_t lc_synth_tensor_dev(uint32_t typ, uint64_t seed, const char* name, float sigma, size_t n_elems, void* out_dev);
+int32_t lc_synth_tokens(uint64_t seed, size_t n, int64_t vocab, int64_t* out);
+
+/* ------------------------------------------------------------------------
+ * L2 -- model level.
+ * ---------------------------------------------------------------------- */
+typedef struct lc_model lc_model;
+
+/* ModelConfig (rust/src/model/loader.rs:13-22) plus the switches the reference hard-codes. */
+typedef struct lc_model_config {
+    int32_t hidden_size;
+    int32_t num_layers;
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t intermediate_size;
+    int32_t max_seq_len;      /* per-sequence KV capacity in tokens */
+    int32_t vocab_size;
+    float rope_theta;
+    float rms_eps;            /* 0 -> 1e-5, the constant at rust/src/inference/engine.rs:102,111,121 */
+    int32_t kv_dtype;         /* 0 = f16 storage as rust/src/cache/mod.rs:33-61; 1 = f32 */
+    int32_t rope_mode;        /* 0 = position inside the call, as attention.rs:13-21; 1 = absolute position */
+    int32_t n_experts;        /* 0 = dense FFN (mixture-of-experts has no counterpart in the reference) */
+    int32_t top_k;
+    int32_t max_seqs;         /* concurrent sequences; 0 -> 1 */
+    int32_t kv_page_tokens;   /* tokens per KV page; 0 -> 16 */
+    int64_t kv_pool_tokens;   /* KV pool size in tokens over all sequences; 0 -> max_seqs * max_seq_len */
+    int32_t device;           /* CUDA device ordinal */
+    int32_t reserved[7];
+} lc_model_config;
+
+/* Engine::load without the file: create, then hand over each tensor, then finalize.
+ * rust/src/inference/engine.rs:18-49, rust/src/model/loader.rs:145-203. */
+int32_t lc_model_create(const lc_model_config* cfg, lc_model** out);
+/* `name` is the GGUF tensor name ("blk.3.attn_q.weight", "token_embd.weight", "output_norm.weight",
+ * "output.weight") or the engine name it maps to (rust/src/model/arch.rs:83-96, loader.rs:173-177).
+ * `dims` in GGUF order (fastest first).  `bytes` are the raw GGUF blocks on the host. */
+int32_t lc_model_set_tensor(lc_model* m, const char* name, uint32_t typ, const uint64_t* dims, int32_t ndims,
+                            const void* bytes, size_t nbytes);
+/* Same, but the library synthesises the tensor on the device (lc_synth_tensor_dev) -- no host copy. */
+int32_t lc_model_synth_tensor(lc_model* m, const char* name, uint32_t typ, const uint64_t* dims, int32_t ndims,
+                              uint64_t seed, float sigma);
+/* Copies the raw blocks of a tensor back to the host (to hand the same bytes to a checker). */
+int32_t lc_model_get_tensor(lc_model* m, const char* name, void* out_bytes, size_t nbytes);
+/* Checks completeness (the 9 per-layer tensors + embedding + final norm; tied head when
+ * output.weight is absent, loader.rs:192-199), runs the weight sanity scan (loader.rs:241-249:
+ * counts elements that dequantise to NaN/Inf/|v|>100), builds the execution plan. */
+int32_t lc_model_finalize(lc_model* m);
+int32_t lc_model_destroy(lc_model* m);
+/* Engine::load(path) (engine.rs:18-49): parse a GGUF v3 file (rust/src/model/gguf.rs:76-119),
+ * read the config keys (loader.rs:106-133), upload every tensor, finalize. */
+int32_t lc_model_load_gguf(const char* path, const lc_model_config* overrides, lc_model** out);
+int32_t lc_model_get_config(const lc_model* m, lc_model_config* out);
+
+/* KVCache::clear (rust/src/cache/mod.rs:26-30) for one sequence slot (seq_id < max_seqs); -1 = all. */
+int32_t lc_kv_clear(lc_model* m, int32_t seq_id);
+/* KVCache::memory_bytes (cache/mod.rs:80-84): bytes of K and V held for the live tokens. */
+int32_t lc_kv_memory_bytes(const lc_model* m, uint64_t* out);
+/* Tokens currently cached for a sequence. */
+int32_t lc_kv_length(const lc_model* m, int32_t seq_id, int32_t* out);
+
+/* Engine::forward (engine.rs:78-132) on sequence slot 0: append n tokens, return the logits of the
+ * last one ([vocab]). */
+int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_out);
+/* The same for several sequences in one step (what a server.ModelRunner.RunBatch implementation,
+ * pkg/server/scheduler.go:55-60, would call per step).  tokens is ragged: n_tokens[i] ids for
+ * seq_ids[i], concatenated.  logits_out is [n_seqs, vocab] (may be NULL); next_out receives the
+ * greedy token of each sequence (may be NULL). */
+int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* tokens,
+                         const int32_t* n_tokens, float* logits_out, int64_t* next_out);
+
+typedef void (*lc_token_cb)(int64_t token, void* user);
+/* Engine::generate (engine.rs:51-76) / Go inference.Model.Generate (pkg/inference/speculative.go:18-20):
+ * clears the cache of slot 0, prefills, emits the first token from the prefill logits, then up to
+ * max_tokens-1 decode steps.  temperature <= 0 selects greedy (sampler.rs:7-10); the stochastic
+ * branch draws from an unseeded RNG in the reference and returns LC_ERR_UNSUPPORTED here.
+ * stop_on_eos != 0 keeps the reference's stop on token id 2 (engine.rs:60-63,70-72). */
+int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature,
+                    float top_p, int32_t stop_on_eos, int64_t* out_tokens, int32_t* n_out, lc_token_cb cb,
+                    void* user);
+
+/* Device-resident decode loop for measurement: `steps` greedy decode steps for every live sequence
+ * listed, each step feeding the previous step's token; nothing crosses PCIe inside the loop.
+ * out_tokens is [steps, n_seqs] (may be NULL).  *out_ms = CUDA-event time of the loop. */
+int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* first_tokens,
+                       int32_t steps, int64_t* out_tokens, float* out_ms);
+
+/* Counters since creation or the last reset. */
+typedef struct lc_counters {
+    uint64_t tokens_prefilled;
+    uint64_t tokens_decoded;
+    uint64_t forward_calls;
+    uint64_t kernel_launches;     /* kernels of this library queued (graph replays count their nodes) */
+    uint64_t weight_bytes;        /* quantised weight bytes resident */
+    uint64_t kv_pages_in_use;
+    uint64_t kv_pages_total;
+    uint64_t sanitize_hits;       /* elements the weight sanity scan would zero (loader.rs:241-249) */
+    uint64_t algo_bytes_last_step;/* algorithmic HBM bytes of the last decode step */
+    uint64_t reserved[7];
+} lc_counters;
+int32_t lc_get_counters(const lc_model* m, lc_counters* out);
+int32_t lc_reset_counters(lc_model* m);
+
+/* Layer-level probes for parity tests: run one sub-block of layer `layer` on host activations
+ * through the same kernels lc_forward uses.  attention_forward (attention.rs:37-118) appends to
+ * the KV cache of slot 0; ffn_forward (engine.rs:146-164). */
+int32_t lc_probe_attention(lc_model* m, int32_t layer, const float* normed, int32_t seq, float* out);
+int32_t lc_probe_ffn(lc_model* m, int32_t layer, const float* x, int32_t seq, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEAFCUTTER_B200_H */

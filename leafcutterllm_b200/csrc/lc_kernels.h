@@ -1,0 +1,96 @@
+// Internal launch interface: every function queues kernels on `s` and takes
+// DEVICE pointers.  The C ABI (host pointers) and the engine both sit on these.
+#pragma once
+#include "lc_common.cuh"
+
+namespace lc {
+
+// ---- dequant.cu ----
+int32_t launch_dequant(uint32_t typ, const void* w, size_t n_elems, float* out, cudaStream_t s);
+// Adds to *count the number of elements that dequantise to NaN / Inf / |v| > 100
+// (the condition of rust/src/model/loader.rs:241-249).
+int32_t launch_sanity_scan(uint32_t typ, const void* w, size_t n_elems, unsigned long long* count, cudaStream_t s);
+// One f32 row of a quantised [rows, cols] tensor per token id (embedding gather,
+// rust/src/inference/engine.rs:134-144; id outside [0, rows) -> zero row).
+int32_t launch_embed(uint32_t typ, const void* w, size_t rows, size_t cols, const int64_t* ids, int n, float* out,
+                     cudaStream_t s);
+
+// ---- ops.cu ----
+int32_t launch_vec_add(const float* a, const float* b, size_t n, float* o, cudaStream_t s);
+int32_t launch_vec_mul(const float* a, const float* b, size_t n, float* o, cudaStream_t s);
+int32_t launch_vec_scale(const float* a, float sc, size_t n, float* o, cudaStream_t s);
+int32_t launch_vec_scale_mul(const float* a, float sc, const float* b, size_t n, float* o, cudaStream_t s);
+int32_t launch_silu(const float* x, size_t n, float* o, cudaStream_t s);
+int32_t launch_silu_mul(const float* gate, const float* up, size_t n, float* o, cudaStream_t s);
+int32_t launch_rms_norm(const float* x, const float* w, float eps, size_t hidden, size_t rows, float* o, cudaStream_t s);
+int32_t launch_softmax(const float* x, size_t hidden, size_t rows, float* o, cudaStream_t s);
+int32_t launch_sum_sq(const float* x, size_t n, float* out1, cudaStream_t s);
+int32_t launch_matmul_f32(const float* a, const float* b, size_t m, size_t k, size_t n, float* c, cudaStream_t s);
+int32_t launch_q8_0_shard(const float* a, const float* scales, const int8_t* qs, size_t m, size_t k, size_t n, float* c,
+                          cudaStream_t s);
+int32_t launch_q4_0_shard(const float* a, const float* scales, const uint8_t* qs, size_t m, size_t k, size_t n, float* c,
+                          cudaStream_t s);
+int32_t launch_rope(float* x, size_t seq, size_t heads, size_t hd, float theta, const int32_t* pos0_dev, int32_t pos0,
+                    cudaStream_t s);
+// Greedy pick per row of v[rows, n]: last index among equal maxima under the total order of
+// f32 (rust/src/inference/sampler.rs:6-10).
+int32_t launch_argmax(const float* v, size_t n, size_t rows, int64_t* out, cudaStream_t s);
+
+// ---- qgemv.cu ----
+// A quantised weight matrix resident on the device: `n` output rows of `k`
+// inputs, raw GGUF blocks, rows contiguous.
+struct QWeight {
+    const void* data = nullptr;
+    uint32_t typ = 0;
+    int n = 0, k = 0;
+    size_t row_bytes = 0;
+    alignas(64) unsigned char tmap[128];  // CUtensorMap for the TMA-staged kernels
+    bool has_tmap = false;
+};
+int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int k);
+
+enum GemvEpilogue { EPI_STORE = 0, EPI_ADD_RESIDUAL = 1, EPI_SILU_MUL = 2 };
+struct GemvArgs {
+    const QWeight* w = nullptr;   // first matrix
+    const QWeight* w2 = nullptr;  // EPI_SILU_MUL: the `up` matrix (w is `gate`)
+    const float* x = nullptr;     // [m, k]
+    int m = 1;
+    float* out = nullptr;         // [m, n]
+    const float* residual = nullptr;  // EPI_ADD_RESIDUAL: out = residual + y
+    const float* norm_w = nullptr;    // when set: x is RMS-normalised with this gain before the product
+    float eps = 1e-5f;
+    GemvEpilogue epi = EPI_STORE;
+};
+// y[m,n] = x[m,k] . dequant(W)^T, fp32 activations and accumulation.
+int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s);
+// Number of kernels launch_qgemv queues for these arguments (for launch accounting).
+int qgemv_launch_count(const GemvArgs& a);
+
+// ---- attention.cu ----
+struct KvLayout {
+    void* k_pool = nullptr;  // [pages][n_kv][page_tokens][hd]  (f16 or f32)
+    void* v_pool = nullptr;
+    int n_kv = 0, hd = 0, page_tokens = 16;
+    int kv_f32 = 0;
+};
+// For each of the `n_tok` new tokens (token i belongs to sequence row tok_seq[i], at cache
+// position tok_pos[i], with rotary position tok_rope[i]): rotate q and k in place
+// (rust/src/inference/attention.rs:13-34; q, k, v rows are row_stride floats apart) and store k, v into the paged cache
+// (rust/src/cache/mod.rs:33-61: f32 -> f16 round to nearest even).
+int32_t launch_rope_kv_append(float* q, float* k, const float* v, int row_stride, int n_tok, int n_heads, const KvLayout& kv,
+                              const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* tok_rope,
+                              const int32_t* page_table, int pages_per_seq, float theta, cudaStream_t s);
+// Causal GQA attention of every new token over its sequence's cache (attention.rs:69-113).
+// tok_pos[i] is the cache position of token i (it attends to positions 0..tok_pos[i]).
+// scratch: split-KV partials, sized by attention_scratch_bytes().
+size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx);
+int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
+                         const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
+                         void* scratch, cudaStream_t s);
+int attention_launch_count(int n_tok, int n_heads, int max_ctx);
+
+// ---- synth.cu ----
+int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_elems, void* out_dev,
+                     cudaStream_t s);
+
+}  // namespace lc

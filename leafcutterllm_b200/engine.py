@@ -1,0 +1,141 @@
+"""Host-side mirror of the reference's `Engine` (rust/src/inference/engine.rs) over the C ABI.
+
+Same surface as the Rust type: `forward(tokens) -> logits of the last position`,
+`generate(tokens, max_tokens, temperature, top_p) -> tokens`, a KV cache that can be cleared
+and sized (rust/src/cache/mod.rs).  Weights arrive as raw GGUF blocks and stay on the device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Iterable, Optional, Sequence
+
+import numpy as np
+
+from . import _capi
+from ._capi import Counters, ModelConfig, check, load
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class Engine:
+    def __init__(self, hidden_size: int, num_layers: int, num_heads: int, num_kv_heads: int, intermediate_size: int,
+                 vocab_size: int, max_seq_len: int = 4096, rope_theta: float = 10000.0, rms_eps: float = 1e-5,
+                 kv_dtype: str = "f16", rope_mode: str = "call_relative", max_seqs: int = 1, kv_page_tokens: int = 16,
+                 kv_pool_tokens: int = 0, device: int = 0):
+        cfg = ModelConfig()
+        cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads = hidden_size, num_layers, num_heads, num_kv_heads
+        cfg.intermediate_size, cfg.max_seq_len, cfg.vocab_size = intermediate_size, max_seq_len, vocab_size
+        cfg.rope_theta, cfg.rms_eps = rope_theta, rms_eps
+        cfg.kv_dtype = {"f16": 0, "f32": 1}[kv_dtype]
+        cfg.rope_mode = {"call_relative": 0, "absolute": 1}[rope_mode]
+        cfg.max_seqs, cfg.kv_page_tokens, cfg.kv_pool_tokens, cfg.device = max_seqs, kv_page_tokens, kv_pool_tokens, device
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        check(load().lc_model_create(C.byref(cfg), C.byref(self._h)))
+        self.vocab_size = vocab_size
+        self.max_seqs = max_seqs
+
+    # ---- weights -------------------------------------------------------
+    def set_tensor(self, name: str, typ: int, dims: Sequence[int], data) -> None:
+        """`dims` in GGUF order (fastest first); `data` = raw block bytes."""
+        buf = np.ascontiguousarray(data).view(np.uint8).ravel()
+        d = (C.c_uint64 * len(dims))(*dims)
+        check(load().lc_model_set_tensor(self._h, name.encode(), typ, d, len(dims), _p(buf), buf.size))
+
+    def synth_tensor(self, name: str, typ: int, dims: Sequence[int], seed: int, sigma: float) -> None:
+        d = (C.c_uint64 * len(dims))(*dims)
+        check(load().lc_model_synth_tensor(self._h, name.encode(), typ, d, len(dims), seed, sigma))
+
+    def get_tensor(self, name: str, typ: int, dims: Sequence[int]) -> np.ndarray:
+        count = int(np.prod(dims))
+        out = np.empty(load().lc_tensor_bytes(typ, count), np.uint8)
+        check(load().lc_model_get_tensor(self._h, name.encode(), _p(out), out.size))
+        return out
+
+    def finalize(self) -> None:
+        check(load().lc_model_finalize(self._h))
+
+    # ---- KV cache (rust/src/cache/mod.rs) --------------------------------
+    def kv_clear(self, seq_id: int = -1) -> None:
+        check(load().lc_kv_clear(self._h, seq_id))
+
+    def kv_memory_bytes(self) -> int:
+        out = C.c_uint64()
+        check(load().lc_kv_memory_bytes(self._h, C.byref(out)))
+        return out.value
+
+    def kv_length(self, seq_id: int = 0) -> int:
+        out = C.c_int32()
+        check(load().lc_kv_length(self._h, seq_id, C.byref(out)))
+        return out.value
+
+    # ---- Engine::forward / generate ---------------------------------------
+    def forward(self, tokens: Iterable[int]) -> np.ndarray:
+        t = np.ascontiguousarray(list(tokens), dtype=np.int64)
+        out = np.empty(self.vocab_size, np.float32)
+        check(load().lc_forward(self._h, _p(t), t.size, _p(out)))
+        return out
+
+    def forward_batch(self, seq_ids: Sequence[int], token_lists: Sequence[Sequence[int]], want_logits: bool = True):
+        n = len(seq_ids)
+        ids = np.ascontiguousarray(seq_ids, dtype=np.int32)
+        counts = np.ascontiguousarray([len(t) for t in token_lists], dtype=np.int32)
+        flat = np.ascontiguousarray([x for t in token_lists for x in t], dtype=np.int64)
+        logits = np.empty((n, self.vocab_size), np.float32) if want_logits else None
+        nxt = np.empty(n, np.int64)
+        check(load().lc_forward_batch(self._h, n, _p(ids), _p(flat), _p(counts), _p(logits) if want_logits else None, _p(nxt)))
+        return logits, nxt
+
+    def generate(self, tokens: Iterable[int], max_tokens: int, temperature: float = 0.0, top_p: float = 1.0,
+                 stop_on_eos: bool = True, on_token: Optional[Callable[[int], None]] = None) -> list:
+        t = np.ascontiguousarray(list(tokens), dtype=np.int64)
+        out = np.empty(max_tokens, np.int64)
+        n_out = C.c_int32()
+        cb = _capi.TOKEN_CB((lambda tok, _u: on_token(int(tok))) if on_token else 0)
+        check(load().lc_generate(self._h, _p(t), t.size, max_tokens, temperature, top_p, int(stop_on_eos), _p(out),
+                                 C.byref(n_out), cb, None))
+        return out[: n_out.value].tolist()
+
+    def decode_loop(self, seq_ids: Sequence[int], first_tokens: Sequence[int], steps: int):
+        """`steps` greedy steps per sequence without leaving the device; returns (tokens[steps, n], milliseconds)."""
+        n = len(seq_ids)
+        ids = np.ascontiguousarray(seq_ids, dtype=np.int32)
+        first = np.ascontiguousarray(first_tokens, dtype=np.int64)
+        out = np.empty((steps, n), np.int64)
+        ms = C.c_float()
+        check(load().lc_decode_loop(self._h, n, _p(ids), _p(first), steps, _p(out), C.byref(ms)))
+        return out, ms.value
+
+    # ---- probes / counters -------------------------------------------------
+    def probe_attention(self, layer: int, normed: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(normed, np.float32)
+        out = np.empty_like(x)
+        check(load().lc_probe_attention(self._h, layer, _p(x), x.shape[0], _p(out)))
+        return out
+
+    def probe_ffn(self, layer: int, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        check(load().lc_probe_ffn(self._h, layer, _p(x), x.shape[0], _p(out)))
+        return out
+
+    def counters(self) -> dict:
+        c = Counters()
+        check(load().lc_get_counters(self._h, C.byref(c)))
+        return {f: getattr(c, f) for f, _ in Counters._fields_ if f != "reserved"}
+
+    def reset_counters(self) -> None:
+        check(load().lc_reset_counters(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            load().lc_model_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,128 @@
+"""Model-level parity on the GPU: Engine::forward / generate through the C ABI against the CPU oracle,
+on identical synthetic weights."""
+import numpy as np
+import pytest
+
+from conftest import assert_close, make_pair
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_ABS, LOGIT_REL = 1e-2, 1e-3  # the stated bar for logits
+
+
+def small_spec(layer_type, embed_type, head_type, layers=2, hidden=256, heads=8, kv=2, ffn=512, vocab=1000):
+    from leafcutterllm_b200.synth import ModelSpec
+    return ModelSpec("small", layers, hidden, heads, kv, ffn, vocab, 10000.0, layer_type, embed_type, head_type)
+
+
+@pytest.mark.parametrize("types", [(12, 12, 12), (2, 8, 8), (8, 8, 8)])
+def test_forward_and_generate_small(gpu, oracle, types):
+    from leafcutterllm_b200 import synth
+    spec = small_spec(*types)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=128)
+    prompt = synth.prompt_tokens(17, spec.vocab_size)
+    got = eng.forward(prompt)
+    want = om.forward(prompt)
+    assert_close(got, want, LOGIT_ABS, LOGIT_REL, "prefill logits")
+    assert eng.kv_length() == 17
+    assert eng.kv_memory_bytes() == om.kv_memory_bytes()  # rust/src/cache/mod.rs:80-84
+    nxt = int(np.argmax(want))
+    assert_close(eng.forward([nxt]), om.forward([nxt]), LOGIT_ABS, LOGIT_REL, "decode logits")
+    toks = eng.generate(prompt, 24, stop_on_eos=False)
+    ref, margins = om.generate(prompt, 24, stop_on_eos=False, want_margins=True)
+    assert toks == ref, f"greedy tokens differ; oracle top-2 margins {margins}"
+    # per-token callback path and the device-resident loop give the same tokens
+    seen = []
+    assert eng.generate(prompt, 24, stop_on_eos=False, on_token=seen.append) == ref and seen == ref
+    eng.close()
+
+
+def test_layer_probes(gpu, oracle):
+    spec = small_spec(12, 12, 12, layers=1, hidden=512, heads=8, kv=4, ffn=768)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=64)
+    r = np.random.default_rng(0)
+    x = r.standard_normal((5, 512)).astype(np.float32)
+    assert_close(eng.probe_ffn(0, x), om.ffn(0, x), 1e-5, 1e-4, "ffn")
+    assert_close(eng.probe_attention(0, x), om.attention(0, x), 1e-5, 2e-4, "attention (5 tokens)")
+    x1 = r.standard_normal((1, 512)).astype(np.float32)
+    assert_close(eng.probe_attention(0, x1), om.attention(0, x1), 1e-5, 2e-4, "attention (next token over the cache)")
+    eng.close()
+
+
+@pytest.mark.parametrize("kw", [dict(kv_dtype="f32"), dict(rope_mode="absolute"), dict(kv_page_tokens=4)])
+def test_switches(gpu, oracle, kw):
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=96, **kw)
+    prompt = synth.prompt_tokens(33, spec.vocab_size, 3)
+    assert_close(eng.forward(prompt), om.forward(prompt), LOGIT_ABS, LOGIT_REL, f"prefill {kw}")
+    assert eng.generate(prompt, 12, stop_on_eos=False) == om.generate(prompt, 12, stop_on_eos=False)
+    eng.close()
+
+
+def test_chunked_prefill_matches(gpu, oracle):
+    """A prompt longer than the engine's prefill chunk (512 tokens) keeps call-relative RoPE indices."""
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=1, hidden=256, heads=4, kv=4, ffn=256, vocab=500)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=800)
+    prompt = synth.prompt_tokens(700, spec.vocab_size, 1)
+    assert_close(eng.forward(prompt), om.forward(prompt), LOGIT_ABS, LOGIT_REL, "700-token prefill")
+    eng.close()
+
+
+def test_batched_sequences_match_single(gpu, oracle):
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=64, max_seqs=5)
+    prompts = [synth.prompt_tokens(n, spec.vocab_size, i).tolist() for i, n in enumerate([3, 20, 1, 9, 16])]
+    logits, nxt = eng.forward_batch([0, 1, 2, 3, 4], prompts)
+    for i, p in enumerate(prompts):
+        om.kv_clear()
+        want = om.forward(p)
+        assert_close(logits[i], want, LOGIT_ABS, LOGIT_REL, f"sequence {i}")
+        assert nxt[i] == oracle.argmax(want)
+    # four decode steps for all five sequences on the device == four oracle steps each
+    toks, _ms = eng.decode_loop([0, 1, 2, 3, 4], nxt, 4)
+    for i, p in enumerate(prompts):
+        ref = om.generate(p, 5, stop_on_eos=False)
+        assert [int(nxt[i])] + toks[:, i].tolist() == ref
+    assert eng.counters()["kv_pages_in_use"] == sum((len(p) + 4 + 15) // 16 for p in prompts)
+    eng.kv_clear(1)
+    assert eng.kv_length(1) == 0 and eng.kv_length(0) == 3 + 4
+    eng.close()
+
+
+def test_error_paths(gpu):
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=1)
+    eng = gpu.Engine(spec.hidden_size, 1, spec.num_heads, spec.num_kv_heads, spec.intermediate_size, spec.vocab_size, max_seq_len=32)
+    with pytest.raises(gpu.LeafcutterError) as e:
+        eng.forward([1])
+    assert e.value.status == -7  # not finalized
+    with pytest.raises(gpu.LeafcutterError) as e:
+        eng.finalize()
+    assert e.value.status == -6  # missing tensors (the reference panics: engine.rs:84,97,101)
+    eng.close()
+    eng = synth.build_engine(spec, 32, on_device=True)
+    with pytest.raises(gpu.LeafcutterError) as e:
+        eng.forward(list(range(33)))
+    assert e.value.status == -5  # KV capacity
+    with pytest.raises(gpu.LeafcutterError) as e:
+        eng.generate([1, 2], 4, temperature=0.7)
+    assert e.value.status == -2
+    out = eng.forward([10 ** 6])  # engine.rs:137-141: out-of-range id -> zero embedding row, still finite
+    assert np.isfinite(out).all()
+    eng.close()
+
+
+def test_tiny_shape_reduced_depth(gpu, oracle):
+    """TinyLlama-1.1B dims (hidden 2048, 32 q / 4 kv heads, FFN 5632, vocab 32000, Q4_0 + Q8_0), 3 layers."""
+    from leafcutterllm_b200 import synth
+    spec = synth.TINY.with_layers(3)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=64, on_device=True)
+    prompt = synth.prompt_tokens(32, spec.vocab_size)
+    assert_close(eng.forward(prompt), om.forward(prompt), LOGIT_ABS, LOGIT_REL, "prefill")
+    toks = eng.generate(prompt, 16, stop_on_eos=False)
+    ref, margins = om.generate(prompt, 16, stop_on_eos=False, want_margins=True)
+    assert toks == ref, margins
+    eng.close()
