@@ -10,6 +10,7 @@
 // and at the end qgemv(head, final rmsnorm fused) on each sequence's last token and the
 // greedy pick.  The single-token step of a decode loop is captured in a CUDA graph.
 #include <algorithm>
+#include <cstring>
 #include <map>
 #include <string>
 #include <vector>
@@ -88,6 +89,15 @@ struct lc_model {
 
     lc_counters ctr{};
     uint64_t launches_in_call = 0;
+
+    // What the device-side per-token metadata currently describes (a decode step for these sequences at
+    // these cache positions), so that consecutive one-token calls only have to send the token ids.
+    bool meta_valid = false;
+    std::vector<int> meta_seqs, meta_pos;
+    // pinned staging for the per-step host <-> device traffic
+    int64_t* pin_tokens = nullptr;
+    int64_t* pin_next = nullptr;
+    float* pin_logits = nullptr;
 };
 
 namespace {
@@ -346,6 +356,11 @@ void finish_call(lc_model* m) {
 
 extern "C" {
 
+static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps);
+static int32_t reserve_out_tokens(lc_model* m, size_t need);
+static int32_t stage_decode_meta(lc_model* m, int n_seqs, const int32_t* seq_ids, const int64_t* toks);
+static void after_decode_steps(lc_model* m, int n_seqs, const int32_t* seq_ids, int steps);
+
 int32_t lc_model_create(const lc_model_config* cfg, lc_model** out) {
     LC_CHECK(cfg && out, LC_ERR_INVALID, "lc_model_create: null argument");
     LC_CHECK(cfg->hidden_size > 0 && cfg->num_layers > 0 && cfg->num_heads > 0 && cfg->num_kv_heads > 0 &&
@@ -565,6 +580,10 @@ int32_t lc_model_finalize(lc_model* m) {
     for (int t = 1; t <= T; t++) sc = std::max(sc, attention_scratch_bytes(t, m->nh, m->hd, m->cfg.max_seq_len));
     m->attn_scratch_bytes = sc;
     LC_TRY(dalloc((uint8_t**)&m->d_attn_scratch, sc));
+    LC_CUDA(cudaHostAlloc((void**)&m->pin_tokens, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
+    LC_CUDA(cudaHostAlloc((void**)&m->pin_next, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
+    LC_CUDA(cudaHostAlloc((void**)&m->pin_logits, (size_t)m->max_seqs * V * 4, cudaHostAllocDefault));
+    LC_TRY(reserve_out_tokens(m, (size_t)1024 * m->max_seqs));
     LC_CUDA(cudaEventCreate(&m->ev0));
     LC_CUDA(cudaEventCreate(&m->ev1));
     LC_CUDA(cudaStreamSynchronize(m->stream));
@@ -586,6 +605,9 @@ int32_t lc_model_destroy(lc_model* m) {
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_sanity};
     for (void* p : bufs) if (p) cudaFree(p);
+    if (m->pin_tokens) cudaFreeHost(m->pin_tokens);
+    if (m->pin_next) cudaFreeHost(m->pin_next);
+    if (m->pin_logits) cudaFreeHost(m->pin_logits);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     delete m;
@@ -608,6 +630,7 @@ int32_t lc_kv_clear(lc_model* m, int32_t seq_id) {
         m->seq_pages[s].clear();
         m->seq_len[s] = 0;
     }
+    m->meta_valid = false;
     return LC_OK;
 }
 
@@ -642,6 +665,22 @@ int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, co
         longest = std::max(longest, n_tokens[i]);
     }
     LC_TRY(sync_page_table(m));
+    if (longest == 1) {
+        // a decode step: token ids in (pinned staging), graph replay, picks and logits out
+        LC_TRY(reserve_out_tokens(m, (size_t)n_seqs));
+        LC_TRY(stage_decode_meta(m, n_seqs, seq_ids, tokens));
+        LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
+        LC_TRY(run_decode_steps(m, n_seqs, 1));
+        if (logits_out) LC_CUDA(cudaMemcpyAsync(m->pin_logits, m->d_logits, (size_t)n_seqs * m->V * 4, cudaMemcpyDeviceToHost, m->stream));
+        if (next_out) LC_CUDA(cudaMemcpyAsync(m->pin_next, m->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, m->stream));
+        LC_CUDA(cudaStreamSynchronize(m->stream));
+        if (logits_out) memcpy(logits_out, m->pin_logits, (size_t)n_seqs * m->V * 4);
+        if (next_out) memcpy(next_out, m->pin_next, (size_t)n_seqs * 8);
+        after_decode_steps(m, n_seqs, seq_ids, 1);
+        finish_call(m);
+        return LC_OK;
+    }
+    m->meta_valid = false;
     // Rotary index = position inside the CALL (reference mode, attention.rs:13-21) or the cache position.
     if (total <= m->t_cap) {
         std::vector<int64_t> tok; std::vector<int32_t> seq, pos, rope, last;
@@ -681,15 +720,10 @@ int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, co
     if (next_out) LC_CUDA(cudaMemcpyAsync(next_out, m->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, m->stream));
     LC_CUDA(cudaStreamSynchronize(m->stream));
     m->ctr.forward_calls += 1;
-    if (longest > 1) m->ctr.tokens_prefilled += total; else m->ctr.tokens_decoded += total;
+    m->ctr.tokens_prefilled += total;
     uint64_t used = 0;
     for (auto& pg : m->seq_pages) used += pg.size();
     m->ctr.kv_pages_in_use = used;
-    if (longest == 1) {
-        std::vector<int> ctx;
-        for (int i = 0; i < n_seqs; i++) ctx.push_back(m->seq_len[seq_ids[i]] - 1);
-        m->ctr.algo_bytes_last_step = algo_bytes_step(m, ctx);
-    }
     finish_call(m);
     return LC_OK;
 }
@@ -700,35 +734,10 @@ int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_
     return lc_forward_batch(m, 1, &seq, tokens, &n, logits_out, nullptr);
 }
 
-int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* first_tokens, int32_t steps,
-                       int64_t* out_tokens, float* out_ms) {
-    LC_TRY(check_model(m, true));
-    LC_CHECK(n_seqs >= 1 && n_seqs <= m->max_seqs && seq_ids && first_tokens && steps >= 1, LC_ERR_INVALID, "decode_loop: bad argument");
-    DeviceGuard dg(m->device);
-    std::vector<int64_t> tok(first_tokens, first_tokens + n_seqs);
-    std::vector<int32_t> seq(seq_ids, seq_ids + n_seqs), pos(n_seqs), rope(n_seqs), last(n_seqs);
-    for (int i = 0; i < n_seqs; i++) {
-        LC_CHECK(seq_ids[i] >= 0 && seq_ids[i] < m->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_ids[i], m->max_seqs - 1);
-        for (int j = 0; j < i; j++) LC_CHECK(seq_ids[j] != seq_ids[i], LC_ERR_INVALID, "sequence id %d listed twice", seq_ids[i]);
-        LC_TRY(ensure_pages(m, seq_ids[i], m->seq_len[seq_ids[i]] + steps));  // pages for the whole loop up front
-        pos[i] = m->seq_len[seq_ids[i]];
-        rope[i] = m->cfg.rope_mode ? pos[i] : 0;
-        last[i] = i;
-    }
-    LC_TRY(sync_page_table(m));
-    LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
-    size_t need = (size_t)steps * n_seqs;
-    if (need > m->out_tokens_cap) {
-        if (m->d_out_tokens) cudaFree(m->d_out_tokens);
-        m->d_out_tokens = nullptr;
-        LC_TRY(dalloc(&m->d_out_tokens, need));
-        m->out_tokens_cap = need;
-        // the graph bakes this pointer in
-        for (auto& g : m->decode_graphs) cudaGraphExecDestroy(g.second);
-        m->decode_graphs.clear();
-    }
-    LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
-
+// Queues `steps` greedy decode steps for the n_seqs sequences whose metadata is on the device.  The first
+// step of a new batch width runs eagerly (it sets kernel attributes), then one step is captured into a
+// CUDA graph that later steps replay.
+static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
     auto one_step = [&]() -> int32_t {
         LC_TRY(forward_tokens(m, n_seqs, n_seqs, true, 0));
         cudaLaunchConfig_t cfg = {};
@@ -740,34 +749,29 @@ int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, cons
         m->launches_in_call += 1;
         return LC_OK;
     };
-
     static const bool no_graph = getenv("LC_NO_GRAPH") != nullptr;
     cudaGraphExec_t exec = nullptr;
     int done_steps = 0;
     auto it = m->decode_graphs.find(n_seqs);
     if (it != m->decode_graphs.end()) exec = it->second;
-    LC_CUDA(cudaEventRecord(m->ev0, m->stream));
     if (!exec && !no_graph) {
-        // first step eagerly (sets function attributes, allocates lazily-created state), then capture
-        m->launches_in_call = 0;
+        uint64_t before = m->launches_in_call;
         LC_TRY(one_step());
-        m->graph_nodes = (int)m->launches_in_call;
+        m->graph_nodes = (int)(m->launches_in_call - before);
         done_steps = 1;
-        if (steps > 1) {
-            cudaGraph_t graph = nullptr;
-            if (cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-                uint64_t keep = m->launches_in_call;
-                int32_t st = one_step();
-                m->launches_in_call = keep;
-                cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
-                if (st == LC_OK && e == cudaSuccess && graph) {
-                    if (cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) m->decode_graphs[n_seqs] = exec;
-                    else exec = nullptr;
-                }
-                if (graph) cudaGraphDestroy(graph);
+        cudaGraph_t graph = nullptr;
+        if (cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            uint64_t keep = m->launches_in_call;
+            int32_t st = one_step();
+            m->launches_in_call = keep;
+            cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
+            if (st == LC_OK && e == cudaSuccess && graph) {
+                if (cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) m->decode_graphs[n_seqs] = exec;
+                else exec = nullptr;
             }
-            (void)cudaGetLastError();
+            if (graph) cudaGraphDestroy(graph);
         }
+        (void)cudaGetLastError();
     }
     for (int s = done_steps; s < steps; s++) {
         if (exec) {
@@ -777,6 +781,76 @@ int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, cons
             LC_TRY(one_step());
         }
     }
+    return LC_OK;
+}
+
+static int32_t reserve_out_tokens(lc_model* m, size_t need) {
+    if (need <= m->out_tokens_cap) return LC_OK;
+    if (m->d_out_tokens) cudaFree(m->d_out_tokens);
+    m->d_out_tokens = nullptr;
+    m->out_tokens_cap = 0;
+    LC_TRY(dalloc(&m->d_out_tokens, need));
+    m->out_tokens_cap = need;
+    for (auto& g : m->decode_graphs) cudaGraphExecDestroy(g.second);  // the graphs bake this pointer in
+    m->decode_graphs.clear();
+    return LC_OK;
+}
+
+// Describes a decode step (one token per listed sequence at its current cache position) on the device.
+static int32_t stage_decode_meta(lc_model* m, int n_seqs, const int32_t* seq_ids, const int64_t* toks) {
+    bool same = m->meta_valid && (int)m->meta_seqs.size() == n_seqs;
+    for (int i = 0; same && i < n_seqs; i++) same = m->meta_seqs[i] == seq_ids[i] && m->meta_pos[i] == m->seq_len[seq_ids[i]];
+    if (same) {  // positions already advanced on the device by the previous step: only the token ids travel
+        memcpy(m->pin_tokens, toks, (size_t)n_seqs * 8);
+        LC_CUDA(cudaMemcpyAsync(m->d_tokens, m->pin_tokens, (size_t)n_seqs * 8, cudaMemcpyHostToDevice, m->stream));
+        return LC_OK;
+    }
+    std::vector<int64_t> tok(toks, toks + n_seqs);
+    std::vector<int32_t> seq(seq_ids, seq_ids + n_seqs), pos(n_seqs), rope(n_seqs), last(n_seqs);
+    for (int i = 0; i < n_seqs; i++) {
+        pos[i] = m->seq_len[seq_ids[i]];
+        rope[i] = m->cfg.rope_mode ? pos[i] : 0;
+        last[i] = i;
+    }
+    LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
+    m->meta_seqs.assign(seq_ids, seq_ids + n_seqs);
+    m->meta_pos.assign(pos.begin(), pos.end());
+    m->meta_valid = true;
+    return LC_OK;
+}
+
+static void after_decode_steps(lc_model* m, int n_seqs, const int32_t* seq_ids, int steps) {
+    std::vector<int> ctx;
+    for (int i = 0; i < n_seqs; i++) {
+        m->seq_len[seq_ids[i]] += steps;
+        m->meta_pos[i] += steps;
+        ctx.push_back(m->seq_len[seq_ids[i]] - 1);
+    }
+    m->ctr.algo_bytes_last_step = algo_bytes_step(m, ctx);
+    m->ctr.tokens_decoded += (uint64_t)steps * n_seqs;
+    m->ctr.forward_calls += steps;
+    uint64_t used = 0;
+    for (auto& pg : m->seq_pages) used += pg.size();
+    m->ctr.kv_pages_in_use = used;
+}
+
+int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* first_tokens, int32_t steps,
+                       int64_t* out_tokens, float* out_ms) {
+    LC_TRY(check_model(m, true));
+    LC_CHECK(n_seqs >= 1 && n_seqs <= m->max_seqs && seq_ids && first_tokens && steps >= 1, LC_ERR_INVALID, "decode_loop: bad argument");
+    DeviceGuard dg(m->device);
+    for (int i = 0; i < n_seqs; i++) {
+        LC_CHECK(seq_ids[i] >= 0 && seq_ids[i] < m->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_ids[i], m->max_seqs - 1);
+        for (int j = 0; j < i; j++) LC_CHECK(seq_ids[j] != seq_ids[i], LC_ERR_INVALID, "sequence id %d listed twice", seq_ids[i]);
+        LC_TRY(ensure_pages(m, seq_ids[i], m->seq_len[seq_ids[i]] + steps));  // pages for the whole loop up front
+    }
+    LC_TRY(sync_page_table(m));
+    size_t need = (size_t)steps * n_seqs;
+    LC_TRY(reserve_out_tokens(m, need));
+    LC_TRY(stage_decode_meta(m, n_seqs, seq_ids, first_tokens));
+    LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
+    LC_CUDA(cudaEventRecord(m->ev0, m->stream));
+    LC_TRY(run_decode_steps(m, n_seqs, steps));
     LC_CUDA(cudaEventRecord(m->ev1, m->stream));
     LC_CUDA(cudaEventSynchronize(m->ev1));
     float ms = 0.f;
@@ -786,17 +860,7 @@ int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, cons
         LC_CUDA(cudaMemcpyAsync(out_tokens, m->d_out_tokens, need * 8, cudaMemcpyDeviceToHost, m->stream));
         LC_CUDA(cudaStreamSynchronize(m->stream));
     }
-    std::vector<int> ctx;
-    for (int i = 0; i < n_seqs; i++) {
-        m->seq_len[seq_ids[i]] += steps;
-        ctx.push_back(m->seq_len[seq_ids[i]] - 1);
-    }
-    m->ctr.algo_bytes_last_step = algo_bytes_step(m, ctx);
-    m->ctr.tokens_decoded += (uint64_t)steps * n_seqs;
-    m->ctr.forward_calls += steps;
-    uint64_t used = 0;
-    for (auto& pg : m->seq_pages) used += pg.size();
-    m->ctr.kv_pages_in_use = used;
+    after_decode_steps(m, n_seqs, seq_ids, steps);
     finish_call(m);
     return LC_OK;
 }
@@ -854,6 +918,7 @@ static int32_t probe_meta(lc_model* m, int seq_tokens) {
     LC_CHECK(seq_tokens >= 1 && seq_tokens <= m->t_cap, LC_ERR_INVALID, "probe: %d tokens outside 1..%d", seq_tokens, m->t_cap);
     LC_TRY(ensure_pages(m, 0, m->seq_len[0] + seq_tokens));
     LC_TRY(sync_page_table(m));
+    m->meta_valid = false;
     std::vector<int64_t> tok(seq_tokens, 0);
     std::vector<int32_t> seq(seq_tokens, 0), pos(seq_tokens), rope(seq_tokens), last;
     for (int i = 0; i < seq_tokens; i++) { pos[i] = m->seq_len[0] + i; rope[i] = m->cfg.rope_mode ? pos[i] : i; }
