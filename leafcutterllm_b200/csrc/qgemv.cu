@@ -20,6 +20,7 @@
 #include <cstring>
 #include "lc_kernels.h"
 #include "lc_quant.cuh"
+#include "lc_tma.cuh"
 
 namespace lc {
 
@@ -45,8 +46,6 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-constexpr int kTileRows = 32;
-constexpr int kUnitElems = 256;
 
 static inline int unit_bytes_of(uint32_t typ) {
     switch (typ) {
@@ -80,38 +79,6 @@ int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int 
         w->has_tmap = (r == CUDA_SUCCESS);
     }
     return LC_OK;
-}
-
-// ---------------------------------------------------------------------------
-// device helpers: mbarrier + TMA
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait: returns false when the phase did not complete within the spin budget.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t addr = smem_u32(bar);
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            smem_u32(dst)),
-        "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -256,20 +223,6 @@ __device__ __forceinline__ void unit_dot_q80(const uint32_t (&r)[68], const floa
 
 template <uint32_t TYPE> struct UnitBytes { static constexpr int v = 144; };
 template <> struct UnitBytes<LC_TYPE_Q8_0> { static constexpr int v = 272; };
-
-// cpu.rs:62-64
-__device__ __forceinline__ float silu_f(float v) { return v * (1.0f / (1.0f + expf(-v))); }
-
-struct GemvParams {
-    const float* x;         // [m, k]
-    float* out;             // [m, n]
-    const float* residual;  // or null
-    const float* norm_w;    // or null
-    float eps;
-    int n, k, m;
-    int epi;
-    int* error_flag;
-};
 
 // ---------------------------------------------------------------------------
 // the TMA-staged kernel
@@ -487,10 +440,12 @@ __global__ void qgemv_generic_kernel(uint32_t typ, const uint8_t* __restrict__ w
 // ---------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------
-static bool g_use_pdl = getenv("LC_NO_PDL") == nullptr;
+bool pdl_enabled() {
+    static const bool on = getenv("LC_NO_PDL") == nullptr;
+    return on;
+}
 static int* g_error_flag[16] = {};
-
-static int* error_flag_dev() {
+int* gemv_error_flag_dev() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
     if (!g_error_flag[dev]) {
@@ -498,21 +453,6 @@ static int* error_flag_dev() {
         cudaMemset(g_error_flag[dev], 0, sizeof(int));
     }
     return g_error_flag[dev];
-}
-
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = g_use_pdl ? 1 : 0;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
 template <uint32_t TYPE, int M, int WARPS, int STAGES>
@@ -526,8 +466,6 @@ static size_t tma_smem_bytes(int k) {
     return b;
 }
 
-constexpr size_t kMaxSmem = 227 * 1024;
-
 template <uint32_t TYPE, int M, int WARPS, int STAGES>
 static int32_t launch_tma_cfg(const GemvArgs& a, cudaStream_t s) {
     auto kern = qgemv_tma_kernel<TYPE, M, WARPS, STAGES>;
@@ -539,13 +477,13 @@ static int32_t launch_tma_cfg(const GemvArgs& a, cudaStream_t s) {
     }
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
-    p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = error_flag_dev();
+    p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
     int ntiles = (p.n + kTileRows - 1) / kTileRows;
     int grid = sm_count();
     if (grid > ntiles) grid = ntiles;
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap : t0;
-    LC_CUDA(launch_k(kern, dim3(grid), dim3(WARPS * 32), smem, s, *t0, *t1, p));
+    LC_CUDA(launch_pdl(kern, dim3(grid), dim3(WARPS * 32), smem, s, *t0, *t1, p));
     return LC_OK;
 }
 
@@ -553,7 +491,7 @@ template <uint32_t TYPE, int M>
 static int32_t launch_tma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = true;
     int k = a.w->k;
-    if (M == 1) {
+    if constexpr (M == 1) {
         if (tma_smem_bytes<TYPE, M, 16, 3>(k) <= kMaxSmem && k <= 4096) return launch_tma_cfg<TYPE, M, 16, 3>(a, s);
         if (tma_smem_bytes<TYPE, M, 16, 2>(k) <= kMaxSmem) return launch_tma_cfg<TYPE, M, 16, 2>(a, s);
     }
@@ -580,7 +518,7 @@ static int32_t launch_generic(const GemvArgs& a, cudaStream_t s) {
     int cap = sm_count() * 8;
     if (grid > cap) grid = cap;
     const uint8_t* w2 = a.w2 ? (const uint8_t*)a.w2->data : nullptr;
-    LC_CUDA(launch_k(qgemv_generic_kernel<8>, dim3(grid), dim3(256), 0, s, a.w->typ, (const uint8_t*)a.w->data, w2, p));
+    LC_CUDA(launch_pdl(qgemv_generic_kernel<8>, dim3(grid), dim3(256), 0, s, a.w->typ, (const uint8_t*)a.w->data, w2, p));
     return LC_OK;
 }
 
@@ -594,6 +532,12 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
                  "qgemv: gate/up matrices differ in shape or type");
     if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual, LC_ERR_INVALID, "qgemv: residual missing");
     bool tma_ok = a.w->has_tmap && (a.epi != EPI_SILU_MUL || a.w2->has_tmap);
+    static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
+    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32) {
+        bool launched = false;
+        LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
+        if (launched) return LC_OK;
+    }
     if (tma_ok) {
         for (int mt = round_m(a.m); mt >= 1; mt >>= 1) {
             // the kernel handles mt tokens per pass; when shared memory cannot hold round_m(m) token

@@ -1,0 +1,365 @@
+// Q4_K matrix-vector product on the integer tensor cores, exact in the integer domain.
+//
+//   y[t, r] = sum_k x[t, k] * w[r, k],   w = (d * sc) * q - (dmin * m)      (rust/src/kernels/mod.rs:66-98)
+//
+// The reference multiplies f32 activations with the dequantised f32 weight.  Here the f32
+// activations of each 256-element unit are first written as 24-bit fixed point against the
+// unit's own power-of-two scale, X = round(x * 2^s), |X| < 2^23, split into three balanced
+// byte planes X = P0 + 256 P1 + 65536 P2.  Then
+//   sum_k x_k q_k = 2^-s * sum_p 256^p * sum_k P_p[k] q[k]
+// and the inner sums are int8 x uint8 products accumulated in int32 -- mma.sync m16n8k32 with the
+// 4-bit weights as the A operand (16 rows x 32 k = one Q4_K sub-block) and the planes of up to two
+// tokens as the 8 B columns.  Integer arithmetic is exact and order independent; the 6-bit
+// sub-block scales are applied as integer multiplies, so the only roundings are the 2^-24 fixed
+// point of x (relative to the unit's largest |x|) and the final f32 conversion.
+//
+// Data path: the same TMA-staged [144 B x 32 rows] boxes as the f32 kernel; warp <-> unit, a thread
+// holds the A fragments of rows g and g+8 (g = lane / 4) as two 32-bit shared-memory loads per
+// 64-element group (bank-conflict free for the 144-byte row pitch).
+#include <cstdlib>
+#include "lc_kernels.h"
+#include "lc_quant.cuh"
+#include "lc_tma.cuh"
+
+namespace lc {
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+__device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ int byte_of(uint32_t w, int j) { return (int)((w >> (8 * j)) & 0xFFu); }
+
+// planes of one unit: [sub-block 8][token M][plane 3][32 bytes]
+template <int M>
+__device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
+    return ((unit * 8 + sb) * M + tok) * 96 + plane * 32;
+}
+
+template <int M, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p) {
+    constexpr int UB = 144;
+    constexpr int STAGE_BYTES = UB * kTileRows;
+    constexpr int NPAIR = (M + 1) / 2;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int nunits = p.k / kUnitElems;
+    const int ntiles = (p.n + kTileRows - 1) / kTileRows;
+    const int nmat = (p.epi == EPI_SILU_MUL) ? 2 : 1;
+
+    unsigned char* stage_base = smem + (size_t)warp * STAGES * STAGE_BYTES;
+    size_t off = (size_t)WARPS * STAGES * STAGE_BYTES;
+    unsigned char* planes = smem + off;                          // [nunits][8][M][3][32] int8
+    off += (size_t)nunits * 8 * M * 96;
+    float* sxf = reinterpret_cast<float*>(smem + off);           // [nunits][M][8]: sum of x over each sub-block
+    off += (size_t)nunits * M * 8 * 4;
+    float* inv2s = reinterpret_cast<float*>(smem + off);         // [nunits][M]: 2^-s
+    off += (size_t)nunits * M * 4;
+    float* red = reinterpret_cast<float*>(smem + off);           // [2][WARPS][M][32]
+    off += (size_t)2 * WARPS * M * 32 * 4;
+    float* gate_vals = reinterpret_cast<float*>(smem + off);     // [M][32]
+    off += (size_t)M * 32 * 4;
+    float* scratch = reinterpret_cast<float*>(smem + off);       // [32 + M]
+    off += (size_t)(32 + M) * 4;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ((off + 7) & ~(size_t)7)) + warp * STAGES;
+
+    const int units_mine = (nunits > warp) ? (nunits - warp + WARPS - 1) / WARPS : 0;
+    const int tiles_mine = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int jobs_per_tile = units_mine * nmat;
+    const int njobs = tiles_mine * jobs_per_tile;
+
+    auto issue = [&](int job) {
+        int ti = job / jobs_per_tile, rem = job % jobs_per_tile;
+        int mat = rem / units_mine, ui = rem % units_mine;
+        int tile = blockIdx.x + ti * gridDim.x;
+        int unit = warp + ui * WARPS;
+        int st = job % STAGES;
+        mbar_expect_tx(&bars[st], STAGE_BYTES);
+        tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, mat ? &tm1 : &tm0, unit * (UB / 4), tile * kTileRows, &bars[st]);
+    };
+
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; s++) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int j = 0; j < STAGES && j < njobs; j++) issue(j);  // weights do not depend on the previous kernel
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+
+    // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
+    if (p.norm_w) {
+        for (int tk = 0; tk < M; tk++) {
+            float ss = 0.f;
+            if (tk < p.m)
+                for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = p.x[(size_t)tk * p.k + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            __syncthreads();
+            if (lane == 0) scratch[warp] = ss;
+            __syncthreads();
+            if (warp == 0) {
+                float r = (lane < WARPS) ? scratch[lane] : 0.f;
+                r = warp_sum(r);
+                if (lane == 0) scratch[32 + tk] = 1.0f / sqrtf(r / (float)p.k + p.eps);
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- each warp writes the fixed-point planes of its own units ----
+    for (int ui = 0; ui < units_mine; ui++) {
+        const int unit = warp + ui * WARPS;
+#pragma unroll
+        for (int tk = 0; tk < M; tk++) {
+            float v[8];
+            const int e0 = unit * kUnitElems + 8 * lane;
+            if (tk < p.m) {
+                const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);
+                float4 u0 = xp[0], u1 = xp[1];
+                v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+                if (p.norm_w) {
+                    const float sc = scratch[32 + tk];
+                    const float4* np = reinterpret_cast<const float4*>(p.norm_w + e0);
+                    float4 n0 = np[0], n1 = np[1];
+                    const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = (v[j] * sc) * nw[j];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = 0.f;
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+            amax = warp_max(amax);
+            int ex = 0;
+            if (amax > 0.f && amax < 3.0e38f) (void)frexpf(amax, &ex);   // amax = f * 2^ex, f in [0.5, 1)
+            int s = 22 - ex;                                              // |x| * 2^s < 2^22
+            s = max(-100, min(100, s));
+            const float up = ldexpf(1.0f, s), dn = ldexpf(1.0f, -s);
+            uint32_t pw[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+            int xsum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float sv = v[j] * up;
+                sv = fminf(fmaxf(sv, -4194304.f), 4194304.f);             // NaN / Inf inputs do not reach here as finite work
+                int X = __float2int_rn(sv);
+                xsum += X;
+                int p0 = ((X + 128) & 255) - 128;
+                int X1 = (X - p0) >> 8;
+                int p1 = ((X1 + 128) & 255) - 128;
+                int p2 = (X1 - p1) >> 8;
+                pw[0][j >> 2] |= (uint32_t)(p0 & 255) << (8 * (j & 3));
+                pw[1][j >> 2] |= (uint32_t)(p1 & 255) << (8 * (j & 3));
+                pw[2][j >> 2] |= (uint32_t)(p2 & 255) << (8 * (j & 3));
+            }
+            const int sb = lane >> 2, inner = (8 * lane) & 31;
+#pragma unroll
+            for (int pl = 0; pl < 3; pl++)
+                *reinterpret_cast<uint2*>(planes + plane_off<M>(unit, sb, tk, pl) + inner) = make_uint2(pw[pl][0], pw[pl][1]);
+            xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
+            xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
+            if (t == 0) sxf[(unit * M + tk) * 8 + sb] = (float)xsum * dn;
+            if (lane == 0) inv2s[unit * M + tk] = dn;
+        }
+    }
+    __syncwarp();
+
+    // per-thread coefficients that fold the byte planes of a token pair (B columns 0-2: token A, 3-5: token B)
+    // thread t owns columns 2t and 2t+1
+    const float cA0 = (t == 0) ? 1.f : (t == 1 ? 65536.f : 0.f), cA1 = (t == 0) ? 256.f : 0.f;
+    const float cB0 = (t == 2) ? 256.f : 0.f, cB1 = (t == 1) ? 1.f : (t == 2 ? 65536.f : 0.f);
+
+    bool ok = true;
+    int job = 0;
+    for (int ti = 0; ti < tiles_mine; ti++) {
+        const int tile = blockIdx.x + ti * gridDim.x;
+        for (int mat = 0; mat < nmat; mat++) {
+            float yacc[2][2][M];  // [row group][row g / g+8][token]
+#pragma unroll
+            for (int a = 0; a < 2; a++)
+#pragma unroll
+                for (int b = 0; b < 2; b++)
+#pragma unroll
+                    for (int c = 0; c < M; c++) yacc[a][b][c] = 0.f;
+
+            for (int ui = 0; ui < units_mine; ui++, job++) {
+                const int unit = warp + ui * WARPS;
+                const int st = job % STAGES;
+                ok = ok && mbar_wait(&bars[st], (uint32_t)((job / STAGES) & 1));
+                const unsigned char* tilep = stage_base + (size_t)st * STAGE_BYTES;
+#pragma unroll
+                for (int rg = 0; rg < 2; rg++) {
+                    const unsigned char* rowA = tilep + (rg * 16 + g) * UB;
+                    const unsigned char* rowB = rowA + 8 * UB;
+                    const uint4 hA = *reinterpret_cast<const uint4*>(rowA);
+                    const uint4 hB = *reinterpret_cast<const uint4*>(rowB);
+                    uint32_t scA[2], mnA[2], scB[2], mnB[2];
+                    unpack_scales_k4(hA.y, hA.z, hA.w, &scA[0], &scA[1], &mnA[0], &mnA[1]);
+                    unpack_scales_k4(hB.y, hB.z, hB.w, &scB[0], &scB[1], &mnB[0], &mnB[1]);
+                    int alo[NPAIR][4], ahi[NPAIR][4];
+#pragma unroll
+                    for (int pr = 0; pr < NPAIR; pr++)
+#pragma unroll
+                        for (int j = 0; j < 4; j++) alo[pr][j] = ahi[pr][j] = 0;
+#pragma unroll
+                    for (int grp = 0; grp < 4; grp++) {
+                        const uint32_t wA0 = lds32(rowA + 16 + 32 * grp + 4 * t), wA1 = lds32(rowA + 32 + 32 * grp + 4 * t);
+                        const uint32_t wB0 = lds32(rowB + 16 + 32 * grp + 4 * t), wB1 = lds32(rowB + 32 + 32 * grp + 4 * t);
+                        const int sAl = byte_of(scA[grp >> 1], (2 * grp) & 3), sAh = byte_of(scA[grp >> 1], (2 * grp + 1) & 3);
+                        const int sBl = byte_of(scB[grp >> 1], (2 * grp) & 3), sBh = byte_of(scB[grp >> 1], (2 * grp + 1) & 3);
+#pragma unroll
+                        for (int pr = 0; pr < NPAIR; pr++) {
+                            const int tok = 2 * pr + (g >= 3 ? 1 : 0), pl = (g >= 3) ? g - 3 : g;
+                            const bool colv = g < 6 && tok < M;
+                            uint32_t b0 = 0, b1 = 0;
+                            int c[4];
+                            if (colv) {
+                                const unsigned char* bp = planes + plane_off<M>(unit, 2 * grp, tok, pl) + 4 * t;
+                                b0 = lds32(bp); b1 = lds32(bp + 16);
+                            }
+                            mma_u8s8(c, wA0 & 0x0F0F0F0Fu, wB0 & 0x0F0F0F0Fu, wA1 & 0x0F0F0F0Fu, wB1 & 0x0F0F0F0Fu, b0, b1);
+                            alo[pr][0] += sAl * c[0]; alo[pr][1] += sAl * c[1]; alo[pr][2] += sBl * c[2]; alo[pr][3] += sBl * c[3];
+                            b0 = b1 = 0;
+                            if (colv) {
+                                const unsigned char* bp = planes + plane_off<M>(unit, 2 * grp + 1, tok, pl) + 4 * t;
+                                b0 = lds32(bp); b1 = lds32(bp + 16);
+                            }
+                            // high nibbles stay in place: the products carry a factor 16 that is removed in f32 below
+                            mma_u8s8(c, wA0 & 0xF0F0F0F0u, wB0 & 0xF0F0F0F0u, wA1 & 0xF0F0F0F0u, wB1 & 0xF0F0F0F0u, b0, b1);
+                            ahi[pr][0] += sAh * c[0]; ahi[pr][1] += sAh * c[1]; ahi[pr][2] += sBh * c[2]; ahi[pr][3] += sBh * c[3];
+                        }
+                    }
+                    // ---- fold planes, scales and the offset term into f32 row sums ----
+                    const float dA = h2f((uint16_t)(hA.x & 0xFFFFu)), dminA = h2f((uint16_t)(hA.x >> 16));
+                    const float dB = h2f((uint16_t)(hB.x & 0xFFFFu)), dminB = h2f((uint16_t)(hB.x >> 16));
+                    // this thread's share of sum_sb m_sb * sum_k x_k: sub-blocks 2t and 2t+1
+                    const float mA0 = (float)byte_of(mnA[t >> 1], (2 * t) & 3), mA1 = (float)byte_of(mnA[t >> 1], (2 * t + 1) & 3);
+                    const float mB0 = (float)byte_of(mnB[t >> 1], (2 * t) & 3), mB1 = (float)byte_of(mnB[t >> 1], (2 * t + 1) & 3);
+#pragma unroll
+                    for (int pr = 0; pr < NPAIR; pr++) {
+                        float v[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) v[j] = (float)alo[pr][j] + (float)ahi[pr][j] * 0.0625f;
+#pragma unroll
+                        for (int which = 0; which < 2; which++) {  // token A / token B of the pair
+                            const int tok = 2 * pr + which;
+                            if (tok >= M) continue;
+                            const float c0 = which ? cB0 : cA0, c1 = which ? cB1 : cA1;
+                            float sA = c0 * v[0] + c1 * v[1];
+                            float sB = c0 * v[2] + c1 * v[3];
+                            const float* sx = sxf + (unit * M + tok) * 8;
+                            float mtA = mA0 * sx[2 * t] + mA1 * sx[2 * t + 1];
+                            float mtB = mB0 * sx[2 * t] + mB1 * sx[2 * t + 1];
+#pragma unroll
+                            for (int o = 1; o <= 2; o <<= 1) {
+                                sA += __shfl_xor_sync(0xffffffffu, sA, o);
+                                sB += __shfl_xor_sync(0xffffffffu, sB, o);
+                                mtA += __shfl_xor_sync(0xffffffffu, mtA, o);
+                                mtB += __shfl_xor_sync(0xffffffffu, mtB, o);
+                            }
+                            const float is = inv2s[unit * M + tok];
+                            yacc[rg][0][tok] += (dA * is) * sA - dminA * mtA;
+                            yacc[rg][1][tok] += (dB * is) * sB - dminB * mtB;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0 && job + STAGES < njobs) issue(job + STAGES);
+            }
+            // ---- cross-warp reduction of this (tile, matrix), in warp order ----
+            const int seq = ti * nmat + mat;
+            float* rb = red + (size_t)(seq & 1) * WARPS * M * 32;
+            if (t == 0) {
+#pragma unroll
+                for (int rg = 0; rg < 2; rg++)
+#pragma unroll
+                    for (int tk = 0; tk < M; tk++) {
+                        rb[(warp * M + tk) * 32 + rg * 16 + g] = yacc[rg][0][tk];
+                        rb[(warp * M + tk) * 32 + rg * 16 + g + 8] = yacc[rg][1][tk];
+                    }
+            }
+            __syncthreads();
+            if (warp < M) {
+                const int tk = warp;
+                float y = 0.f;
+#pragma unroll 4
+                for (int w = 0; w < WARPS; w++) y += rb[(w * M + tk) * 32 + lane];
+                const int row = tile * kTileRows + lane;
+                if (p.epi == EPI_SILU_MUL) {
+                    if (mat == 0) {
+                        gate_vals[tk * 32 + lane] = y;
+                    } else if (row < p.n && tk < p.m) {
+                        p.out[(size_t)tk * p.n + row] = silu_f(gate_vals[tk * 32 + lane]) * y;
+                    }
+                } else if (row < p.n && tk < p.m) {
+                    if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[(size_t)tk * p.n + row] + y;
+                    p.out[(size_t)tk * p.n + row] = y;
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
+template <int M, int WARPS, int STAGES>
+static size_t mma_smem_bytes(int k) {
+    int nunits = k / kUnitElems;
+    size_t b = (size_t)WARPS * STAGES * 144 * kTileRows;
+    b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * M * 8 * 4 + (size_t)nunits * M * 4;
+    b += (size_t)2 * WARPS * M * 32 * 4 + (size_t)M * 32 * 4 + (size_t)(32 + M) * 4;
+    b = (b + 7) & ~(size_t)7;
+    b += (size_t)WARPS * STAGES * 8;
+    return b;
+}
+
+template <int M, int WARPS, int STAGES>
+static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
+    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES>;
+    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k);
+    static bool attr_set = false;
+    if (!attr_set) {
+        LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+        attr_set = true;
+    }
+    GemvParams p;
+    p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
+    p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
+    int ntiles = (p.n + kTileRows - 1) / kTileRows;
+    int grid = sm_count();
+    if (grid > ntiles) grid = ntiles;
+    const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap;
+    const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap : t0;
+    LC_CUDA(launch_pdl(kern, dim3(grid), dim3(WARPS * 32), smem, s, *t0, *t1, p));
+    return LC_OK;
+}
+
+template <int M>
+static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
+    *launched = true;
+    int k = a.w->k;
+    if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
+        if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2>(a, s);
+    }
+    if (mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2>(a, s);
+    *launched = false;
+    return LC_OK;
+}
+
+int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) {
+    *launched = false;
+    if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
+    if (a.m <= 1) return launch_mma_m<1>(a, s, launched);
+    if (a.m <= 2) return launch_mma_m<2>(a, s, launched);
+    if (a.m <= 4) return launch_mma_m<4>(a, s, launched);
+    if (a.m <= 6) return launch_mma_m<6>(a, s, launched);
+    return launch_mma_m<8>(a, s, launched);
+}
+
+}  // namespace lc
