@@ -181,7 +181,7 @@ def gemv_roofline(lc, spec, reps: int = 3, copies: int = 8, warm: int = 3) -> di
     tp = os.path.join(ROOT, "profiles", "ncu_traffic.json")
     if os.path.exists(tp):
         traffic = json.load(open(tp)).get("qgemv_tma_q4k_bytes_per_launch_avg")
-    return {"bound": "hbm", "kernel": "qgemv_tma_kernel<Q4_K, m=1>", "achieved": round(achieved, 1), "peak": peak,
+    return {"bound": "hbm", "kernel": "qgemv_mma_q4k_kernel<m=1> (int8 MMA, TMA-staged)", "achieved": round(achieved, 1), "peak": peak,
             "peak_source": which + " (MEASURED_PEAKS.json hbm_gbs, burst)" if which == "measured" else which,
             "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": traffic,
             "algorithmic_bytes_per_launch_avg": total_bytes / len(bufs), "avg_launch_us": round(ms.value * 1e3 / launches, 3),
