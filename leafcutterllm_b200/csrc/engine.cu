@@ -80,6 +80,7 @@ struct lc_model {
     size_t out_tokens_cap = 0;
     int32_t* d_step_ctr = nullptr;
     void* d_attn_scratch = nullptr;
+    int* d_attn_counters = nullptr;
     size_t attn_scratch_bytes = 0;
     unsigned long long* d_sanity = nullptr;
 
@@ -229,7 +230,8 @@ int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
 }
 
 // attention_forward (attention.rs:37-118) for layer `l` on T tokens whose (normalised or raw) input is `x`.
-int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out) {
+int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out,
+                        bool decode_step) {
     LayerW& w = m->layers[l];
     GemvArgs g;
     g.x = x;
@@ -248,11 +250,19 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     float* q = m->d_qkv;
     float* k = m->d_qkv + (size_t)m->nh * m->hd;
     float* v = k + (size_t)m->nkv * m->hd;
-    LC_TRY(launch_rope_kv_append(q, k, v, m->nqkv, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_page_table,
-                                 m->pages_per_seq, m->cfg.rope_theta, m->stream));
-    LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
-                            m->cfg.max_seq_len, m->d_attn_scratch, m->stream));
-    m->launches_in_call += 1 + attention_launch_count(T, m->nh, m->cfg.max_seq_len);
+    if (decode_step) {
+        // one new token per sequence: rotation and the cache append ride inside the attention kernel
+        AttnFusion fz{k, v, m->d_tok_rope, m->cfg.rope_theta};
+        LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
+                                m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, &fz, m->stream));
+        m->launches_in_call += 1;
+    } else {
+        LC_TRY(launch_rope_kv_append(q, k, v, m->nqkv, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_page_table,
+                                     m->pages_per_seq, m->cfg.rope_theta, m->stream));
+        LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
+                                m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, nullptr, m->stream));
+        m->launches_in_call += 2;
+    }
     GemvArgs o;
     o.w = &w.o;
     o.x = m->d_attn;
@@ -282,12 +292,12 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
 }
 
 // The transformer layers (engine.rs:95-116) on T tokens described by d_tokens / d_tok_*.
-int32_t run_layers(lc_model* m, int T) {
+int32_t run_layers(lc_model* m, int T, bool decode_step) {
     LC_TRY(launch_embed(m->embed->typ, m->embed->view, m->embed->rows, m->embed->cols, m->d_tokens, T, m->d_hidden, m->stream));
     m->launches_in_call += 1;
     for (int l = 0; l < m->L; l++) {
         LayerW& w = m->layers[l];
-        LC_TRY(attention_block(m, l, m->d_hidden, w.attn_norm, T, m->d_hidden, m->d_hidden2));
+        LC_TRY(attention_block(m, l, m->d_hidden, w.attn_norm, T, m->d_hidden, m->d_hidden2, decode_step));
         LC_TRY(ffn_block(m, l, m->d_hidden2, w.ffn_norm, T, m->d_hidden2, m->d_hidden));
     }
     return LC_OK;
@@ -297,7 +307,7 @@ int32_t run_layers(lc_model* m, int T) {
 // every token is the last of its sequence (a decode step), so no gather is needed; otherwise the rows
 // listed in d_last_idx are gathered.  Logits land in d_logits rows row0.., greedy picks in d_next.
 int32_t forward_tokens(lc_model* m, int T, int n_last, bool identity_last, int row0) {
-    LC_TRY(run_layers(m, T));
+    LC_TRY(run_layers(m, T, identity_last));
     const float* last = m->d_hidden;
     if (!identity_last) {
         cudaLaunchConfig_t cfg = {};
@@ -580,6 +590,8 @@ int32_t lc_model_finalize(lc_model* m) {
     for (int t = 1; t <= T; t++) sc = std::max(sc, attention_scratch_bytes(t, m->nh, m->hd, m->cfg.max_seq_len));
     m->attn_scratch_bytes = sc;
     LC_TRY(dalloc((uint8_t**)&m->d_attn_scratch, sc));
+    LC_TRY(dalloc(&m->d_attn_counters, (size_t)T * m->nh));
+    LC_CUDA(cudaMemsetAsync(m->d_attn_counters, 0, (size_t)T * m->nh * sizeof(int), m->stream));
     LC_CUDA(cudaHostAlloc((void**)&m->pin_tokens, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
     LC_CUDA(cudaHostAlloc((void**)&m->pin_next, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
     LC_CUDA(cudaHostAlloc((void**)&m->pin_logits, (size_t)m->max_seqs * V * 4, cudaHostAllocDefault));
@@ -603,7 +615,7 @@ int32_t lc_model_destroy(lc_model* m) {
     for (void* p : m->v_pools) cudaFree(p);
     void* bufs[] = {m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
-                    m->d_attn_scratch, m->d_sanity};
+                    m->d_attn_scratch, m->d_attn_counters, m->d_sanity};
     for (void* p : bufs) if (p) cudaFree(p);
     if (m->pin_tokens) cudaFreeHost(m->pin_tokens);
     if (m->pin_next) cudaFreeHost(m->pin_next);
@@ -710,7 +722,7 @@ int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, co
                 }
                 LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
                 if (c0 + T == n_tokens[i]) LC_TRY(forward_tokens(m, T, 1, T == 1, i));
-                else LC_TRY(run_layers(m, T));
+                else LC_TRY(run_layers(m, T, false));
             }
             off += n_tokens[i];
         }
@@ -931,7 +943,7 @@ int32_t lc_probe_attention(lc_model* m, int32_t layer, const float* normed, int3
     DeviceGuard dg(m->device);
     LC_TRY(probe_meta(m, seq));
     LC_CUDA(cudaMemcpyAsync(m->d_hidden, normed, (size_t)seq * m->H * 4, cudaMemcpyHostToDevice, m->stream));
-    LC_TRY(attention_block(m, layer, m->d_hidden, nullptr, seq, nullptr, m->d_hidden2));
+    LC_TRY(attention_block(m, layer, m->d_hidden, nullptr, seq, nullptr, m->d_hidden2, false));
     LC_CUDA(cudaMemcpyAsync(out, m->d_hidden2, (size_t)seq * m->H * 4, cudaMemcpyDeviceToHost, m->stream));
     LC_CUDA(cudaStreamSynchronize(m->stream));
     m->seq_len[0] += seq;

@@ -84,9 +84,14 @@ int32_t launch_rope_kv_append(float* q, float* k, const float* v, int row_stride
 // tok_pos[i] is the cache position of token i (it attends to positions 0..tok_pos[i]).
 // scratch: split-KV partials, sized by attention_scratch_bytes().
 size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx);
+// counters: n_tok*n_heads ints, zero before the first launch (the kernel leaves them zero).
+// fuse (decode steps only, every token the single new token of its sequence): q is rotated on load and the new
+// key/value are taken from k_new/v_new (rows q_stride floats apart), rotated, and stored into the cache by this kernel,
+// so no separate rope/append launch is needed.
+struct AttnFusion { const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; };
 int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
                          const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
-                         void* scratch, cudaStream_t s);
+                         void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);
 int attention_launch_count(int n_tok, int n_heads, int max_ctx);
 
 // ---- synth.cu ----

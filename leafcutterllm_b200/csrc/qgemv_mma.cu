@@ -171,16 +171,19 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     }
     __syncwarp();
 
-    // per-thread coefficients that fold the byte planes of a token pair (B columns 0-2: token A, 3-5: token B)
-    // thread t owns columns 2t and 2t+1
+    // Thread t owns B/C columns 2t and 2t+1.  Columns 0-2 carry the byte planes of the pair's first token,
+    // 3-5 those of its second token.  Coefficients that fold this thread's two columns into each token:
     const float cA0 = (t == 0) ? 1.f : (t == 1 ? 65536.f : 0.f), cA1 = (t == 0) ? 256.f : 0.f;
     const float cB0 = (t == 2) ? 256.f : 0.f, cB1 = (t == 1) ? 1.f : (t == 2 ? 65536.f : 0.f);
+    // B fragment source of this thread: column g = lane / 4
+    const int bcol_tok = (g >= 3) ? 1 : 0, bcol_pl = (g >= 3) ? g - 3 : g;
 
     bool ok = true;
     int job = 0;
     for (int ti = 0; ti < tiles_mine; ti++) {
         const int tile = blockIdx.x + ti * gridDim.x;
         for (int mat = 0; mat < nmat; mat++) {
+            // per-thread partial row sums (the 4 threads of a row are added once per tile)
             float yacc[2][2][M];  // [row group][row g / g+8][token]
 #pragma unroll
             for (int a = 0; a < 2; a++)
@@ -192,6 +195,27 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             for (int ui = 0; ui < units_mine; ui++, job++) {
                 const int unit = warp + ui * WARPS;
                 const int st = job % STAGES;
+                // B fragments of this unit: for each sub-block the plane bytes of k-slots 4t..4t+3 and 16+4t..
+                uint32_t bf[NPAIR][8][2];
+#pragma unroll
+                for (int pr = 0; pr < NPAIR; pr++) {
+                    const int tok = 2 * pr + bcol_tok;
+                    const bool colv = g < 6 && tok < M;
+                    const unsigned char* bp = planes + plane_off<M>(unit, 0, colv ? tok : 0, bcol_pl > 2 ? 0 : bcol_pl) + 4 * t;
+#pragma unroll
+                    for (int sb = 0; sb < 8; sb++) {
+                        uint32_t v0 = lds32(bp + sb * (M * 96)), v1 = lds32(bp + sb * (M * 96) + 16);
+                        bf[pr][sb][0] = colv ? v0 : 0u;
+                        bf[pr][sb][1] = colv ? v1 : 0u;
+                    }
+                }
+                float sx2[M][2], isv[M];
+#pragma unroll
+                for (int tk = 0; tk < M; tk++) {
+                    sx2[tk][0] = sxf[(unit * M + tk) * 8 + 2 * t];
+                    sx2[tk][1] = sxf[(unit * M + tk) * 8 + 2 * t + 1];
+                    isv[tk] = inv2s[unit * M + tk];
+                }
                 ok = ok && mbar_wait(&bars[st], (uint32_t)((job / STAGES) & 1));
                 const unsigned char* tilep = stage_base + (size_t)st * STAGE_BYTES;
 #pragma unroll
@@ -214,29 +238,19 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                         const uint32_t wB0 = lds32(rowB + 16 + 32 * grp + 4 * t), wB1 = lds32(rowB + 32 + 32 * grp + 4 * t);
                         const int sAl = byte_of(scA[grp >> 1], (2 * grp) & 3), sAh = byte_of(scA[grp >> 1], (2 * grp + 1) & 3);
                         const int sBl = byte_of(scB[grp >> 1], (2 * grp) & 3), sBh = byte_of(scB[grp >> 1], (2 * grp + 1) & 3);
+                        const uint32_t a0 = wA0 & 0x0F0F0F0Fu, a1 = wB0 & 0x0F0F0F0Fu, a2 = wA1 & 0x0F0F0F0Fu, a3 = wB1 & 0x0F0F0F0Fu;
+                        // high nibbles stay in place: the products carry a factor 16 that is removed in f32 below
+                        const uint32_t h0 = wA0 & 0xF0F0F0F0u, h1 = wB0 & 0xF0F0F0F0u, h2 = wA1 & 0xF0F0F0F0u, h3 = wB1 & 0xF0F0F0F0u;
 #pragma unroll
                         for (int pr = 0; pr < NPAIR; pr++) {
-                            const int tok = 2 * pr + (g >= 3 ? 1 : 0), pl = (g >= 3) ? g - 3 : g;
-                            const bool colv = g < 6 && tok < M;
-                            uint32_t b0 = 0, b1 = 0;
                             int c[4];
-                            if (colv) {
-                                const unsigned char* bp = planes + plane_off<M>(unit, 2 * grp, tok, pl) + 4 * t;
-                                b0 = lds32(bp); b1 = lds32(bp + 16);
-                            }
-                            mma_u8s8(c, wA0 & 0x0F0F0F0Fu, wB0 & 0x0F0F0F0Fu, wA1 & 0x0F0F0F0Fu, wB1 & 0x0F0F0F0Fu, b0, b1);
+                            mma_u8s8(c, a0, a1, a2, a3, bf[pr][2 * grp][0], bf[pr][2 * grp][1]);
                             alo[pr][0] += sAl * c[0]; alo[pr][1] += sAl * c[1]; alo[pr][2] += sBl * c[2]; alo[pr][3] += sBl * c[3];
-                            b0 = b1 = 0;
-                            if (colv) {
-                                const unsigned char* bp = planes + plane_off<M>(unit, 2 * grp + 1, tok, pl) + 4 * t;
-                                b0 = lds32(bp); b1 = lds32(bp + 16);
-                            }
-                            // high nibbles stay in place: the products carry a factor 16 that is removed in f32 below
-                            mma_u8s8(c, wA0 & 0xF0F0F0F0u, wB0 & 0xF0F0F0F0u, wA1 & 0xF0F0F0F0u, wB1 & 0xF0F0F0F0u, b0, b1);
+                            mma_u8s8(c, h0, h1, h2, h3, bf[pr][2 * grp + 1][0], bf[pr][2 * grp + 1][1]);
                             ahi[pr][0] += sAh * c[0]; ahi[pr][1] += sAh * c[1]; ahi[pr][2] += sBh * c[2]; ahi[pr][3] += sBh * c[3];
                         }
                     }
-                    // ---- fold planes, scales and the offset term into f32 row sums ----
+                    // ---- fold planes, scales and the offset term into this thread's f32 partial row sums ----
                     const float dA = h2f((uint16_t)(hA.x & 0xFFFFu)), dminA = h2f((uint16_t)(hA.x >> 16));
                     const float dB = h2f((uint16_t)(hB.x & 0xFFFFu)), dminB = h2f((uint16_t)(hB.x >> 16));
                     // this thread's share of sum_sb m_sb * sum_k x_k: sub-blocks 2t and 2t+1
@@ -248,31 +262,34 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 #pragma unroll
                         for (int j = 0; j < 4; j++) v[j] = (float)alo[pr][j] + (float)ahi[pr][j] * 0.0625f;
 #pragma unroll
-                        for (int which = 0; which < 2; which++) {  // token A / token B of the pair
+                        for (int which = 0; which < 2; which++) {  // first / second token of the pair
                             const int tok = 2 * pr + which;
                             if (tok >= M) continue;
                             const float c0 = which ? cB0 : cA0, c1 = which ? cB1 : cA1;
-                            float sA = c0 * v[0] + c1 * v[1];
-                            float sB = c0 * v[2] + c1 * v[3];
-                            const float* sx = sxf + (unit * M + tok) * 8;
-                            float mtA = mA0 * sx[2 * t] + mA1 * sx[2 * t + 1];
-                            float mtB = mB0 * sx[2 * t] + mB1 * sx[2 * t + 1];
-#pragma unroll
-                            for (int o = 1; o <= 2; o <<= 1) {
-                                sA += __shfl_xor_sync(0xffffffffu, sA, o);
-                                sB += __shfl_xor_sync(0xffffffffu, sB, o);
-                                mtA += __shfl_xor_sync(0xffffffffu, mtA, o);
-                                mtB += __shfl_xor_sync(0xffffffffu, mtB, o);
-                            }
-                            const float is = inv2s[unit * M + tok];
-                            yacc[rg][0][tok] += (dA * is) * sA - dminA * mtA;
-                            yacc[rg][1][tok] += (dB * is) * sB - dminB * mtB;
+                            const float sA = c0 * v[0] + c1 * v[1];
+                            const float sB = c0 * v[2] + c1 * v[3];
+                            const float mtA = mA0 * sx2[tok][0] + mA1 * sx2[tok][1];
+                            const float mtB = mB0 * sx2[tok][0] + mB1 * sx2[tok][1];
+                            yacc[rg][0][tok] += (dA * isv[tok]) * sA - dminA * mtA;
+                            yacc[rg][1][tok] += (dB * isv[tok]) * sB - dminB * mtB;
                         }
                     }
                 }
                 __syncwarp();
                 if (lane == 0 && job + STAGES < njobs) issue(job + STAGES);
             }
+            // add the four threads that share a row (fixed order)
+#pragma unroll
+            for (int a = 0; a < 2; a++)
+#pragma unroll
+                for (int b = 0; b < 2; b++)
+#pragma unroll
+                    for (int c = 0; c < M; c++) {
+                        float v = yacc[a][b][c];
+                        v += __shfl_xor_sync(0xffffffffu, v, 1);
+                        v += __shfl_xor_sync(0xffffffffu, v, 2);
+                        yacc[a][b][c] = v;
+                    }
             // ---- cross-warp reduction of this (tile, matrix), in warp order ----
             const int seq = ti * nmat + mat;
             float* rb = red + (size_t)(seq & 1) * WARPS * M * 32;
