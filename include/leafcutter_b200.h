@@ -221,6 +221,11 @@ typedef struct lc_counters {
 int32_t lc_get_counters(const lc_model* m, lc_counters* out);
 int32_t lc_reset_counters(lc_model* m);
 
+/* Diagnostics (no counterpart in the reference): when LC_TRACE=1 was set at lc_model_finalize, the persistent
+ * decode kernel stamps the global timer (ns) of one CTA at every phase: out[2*i] = phase i entered, out[2*i+1] = done.
+ * Returns the stamps of the most recent step. */
+int32_t lc_debug_phase_trace(lc_model* m, uint64_t* out, int32_t max_entries, int32_t* n_phases);
+
 /* Layer-level probes for parity tests: run one sub-block of layer `layer` on host activations
  * through the same kernels lc_forward uses.  attention_forward (attention.rs:37-118) appends to
  * the KV cache of slot 0; ffn_forward (engine.rs:146-164). */

@@ -16,6 +16,8 @@
 #include <vector>
 #include "lc_kernels.h"
 #include "lc_synth.h"
+#include "lc_tma.cuh"
+#include "lc_mega.h"
 
 using namespace lc;
 
@@ -90,6 +92,11 @@ struct lc_model {
 
     lc_counters ctr{};
     uint64_t launches_in_call = 0;
+
+    // persistent decode-step kernel (single sequence, Q4_K): parameter block and its device tables
+    bool mega_ready = false;
+    MegaParams mega{};
+    std::vector<void*> mega_bufs;
 
     // What the device-side per-token metadata currently describes (a decode step for these sequences at
     // these cache positions), so that consecutive one-token calls only have to send the token ids.
@@ -364,6 +371,98 @@ void finish_call(lc_model* m) {
 
 }  // namespace
 
+// Builds the phase table of the persistent decode kernel when the model qualifies: every matrix Q4_K with a
+// tensor map, head_dim 128, f16 cache.  Anything else keeps the one-kernel-per-phase path.
+static int32_t setup_mega(lc_model* m) {
+    m->mega_ready = false;
+    // Opt-in: at the current state of both paths the one-kernel-per-phase graph is the faster one.
+    if (!getenv("LC_MEGA") || getenv("LC_NO_MEGA")) return LC_OK;
+    if (m->hd != 128 || m->cfg.kv_dtype != 0 || m->H % 256 || m->F % 256) return LC_OK;
+    auto okw = [](const QWeight& w) { return w.typ == LC_TYPE_Q4_K && w.has_tmap; };
+    if (!okw(m->head)) return LC_OK;
+    for (auto& w : m->layers)
+        if (!(w.fused_qkv && okw(w.qkv) && okw(w.o) && okw(w.gate) && okw(w.up) && okw(w.down))) return LC_OK;
+    int max_units = std::max(m->H, std::max(m->F, m->nh * m->hd)) / 256;
+    if (max_units > 64 || decode_mega_smem_bytes(max_units) > kMaxSmem) return LC_OK;
+    int supported = 0;
+    if (cudaDeviceGetAttribute(&supported, cudaDevAttrCooperativeLaunch, m->device) != cudaSuccess || !supported) return LC_OK;
+
+    std::vector<CUtensorMap> tm;
+    std::vector<MegaPhase> ph;
+    auto add_tm = [&](const QWeight& w) { CUtensorMap t; memcpy(&t, w.tmap, sizeof(t)); tm.push_back(t); return (int)tm.size() - 1; };
+    auto gemv = [&](const QWeight& w, const QWeight* w2, const float* x, float* out, const float* res, const float* nw, int epi, int emb) {
+        MegaPhase p{};
+        p.type = PH_GEMV; p.n = w.n; p.k = w.k; p.tm0 = add_tm(w); p.tm1 = w2 ? add_tm(*w2) : -1; p.epi = epi; p.layer = 0;
+        p.reserved = (int)ph.size(); p.x = x; p.out = out; p.residual = res; p.norm_w = nw;
+        ph.push_back(p);
+    };
+    { MegaPhase e{}; e.type = PH_EMBED; e.k = m->H; e.tm1 = -1; ph.push_back(e); }
+    for (int l = 0; l < m->L; l++) {
+        LayerW& w = m->layers[l];
+        gemv(w.qkv, nullptr, m->d_hidden, m->d_qkv, nullptr, w.attn_norm, EPI_STORE, 0);
+        MegaPhase a{}; a.type = PH_ATTN; a.layer = l; a.tm1 = -1; ph.push_back(a);
+        gemv(w.o, nullptr, m->d_attn, m->d_hidden2, m->d_hidden, nullptr, EPI_ADD_RESIDUAL, 0);
+        gemv(w.gate, &w.up, m->d_hidden2, m->d_ffn, nullptr, w.ffn_norm, EPI_SILU_MUL, 0);
+        gemv(w.down, nullptr, m->d_ffn, m->d_hidden, m->d_hidden2, nullptr, EPI_ADD_RESIDUAL, 0);
+    }
+    gemv(m->head, nullptr, m->d_hidden, m->d_logits, nullptr, m->final_norm, EPI_STORE, 0);
+    { MegaPhase a{}; a.type = PH_ARGMAX; a.tm1 = -1; ph.push_back(a); a.type = PH_FINAL; ph.push_back(a); }
+
+    CUtensorMap* d_tm = nullptr; MegaPhase* d_ph = nullptr; void** d_kp = nullptr; void** d_vp = nullptr;
+    long long* d_am = nullptr; unsigned long long* d_bar = nullptr;
+    LC_TRY(dalloc(&d_tm, tm.size())); LC_TRY(dalloc(&d_ph, ph.size())); LC_TRY(dalloc(&d_kp, m->L)); LC_TRY(dalloc(&d_vp, m->L));
+    LC_TRY(dalloc(&d_am, 1024)); LC_TRY(dalloc(&d_bar, 2));
+    m->mega_bufs = {d_tm, d_ph, d_kp, d_vp, d_am, d_bar};
+    LC_CUDA(cudaMemcpyAsync(d_tm, tm.data(), tm.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, m->stream));
+    LC_CUDA(cudaMemcpyAsync(d_ph, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice, m->stream));
+    LC_CUDA(cudaMemcpyAsync(d_kp, m->k_pools.data(), m->L * sizeof(void*), cudaMemcpyHostToDevice, m->stream));
+    LC_CUDA(cudaMemcpyAsync(d_vp, m->v_pools.data(), m->L * sizeof(void*), cudaMemcpyHostToDevice, m->stream));
+    LC_CUDA(cudaMemsetAsync(d_bar, 0, 16, m->stream));
+    LC_CUDA(cudaStreamSynchronize(m->stream));
+
+    MegaParams& P = m->mega;
+    P.tmaps = d_tm; P.phases = d_ph; P.n_phases = (int)ph.size(); P.max_units = max_units;
+    AttnParams& a = P.attn;
+    a.q = m->d_qkv; a.q_stride = m->nqkv; a.out = m->d_attn; a.n_heads = m->nh; a.kv = kv_layout(m, 0);
+    a.tok_seq = m->d_tok_seq; a.tok_pos = m->d_tok_pos; a.page_table = m->d_page_table; a.pages_per_seq = m->pages_per_seq;
+    a.chunk = 128;  // one key per thread of a 128-thread group
+    a.n_splits = (m->cfg.max_seq_len + 127) / 128;
+    if ((size_t)m->nh * a.n_splits * (m->hd + 2) * sizeof(float) > m->attn_scratch_bytes) return LC_OK;
+    a.partial = (float*)m->d_attn_scratch; a.counters = m->d_attn_counters;
+    a.k_new = m->d_qkv + (size_t)m->nh * m->hd; a.v_new = a.k_new + (size_t)m->nkv * m->hd; a.tok_rope = m->d_tok_rope;
+    a.theta = m->cfg.rope_theta;
+    P.k_pools = d_kp; P.v_pools = d_vp;
+    P.embed = (const uint8_t*)m->embed->view; P.embed_typ = m->embed->typ; P.embed_rows = (int64_t)m->embed->rows;
+    P.tokens = m->d_tokens; P.hidden = m->d_hidden; P.logits = m->d_logits; P.V = m->V; P.next = m->d_next;
+    P.tok_pos = m->d_tok_pos; P.tok_rope = m->d_tok_rope; P.rope_absolute = m->cfg.rope_mode; P.out_tokens = m->d_out_tokens;
+    P.step_ctr = m->d_step_ctr; P.argmax_scratch = d_am; P.bar = d_bar; P.error_flag = gemv_error_flag_dev(); P.eps = m->cfg.rms_eps;
+    P.trace = nullptr;
+    if (getenv("LC_TRACE")) {
+        unsigned long long* tr = nullptr;
+        LC_TRY(dalloc(&tr, (size_t)4 * ph.size()));
+        m->mega_bufs.push_back(tr);
+        P.trace = tr;
+    }
+    m->mega_ready = P.error_flag != nullptr && sm_count() <= 1024;
+    return LC_OK;
+}
+
+// A bounded wait inside a kernel ran out (TMA transaction or grid barrier): report instead of returning wrong tokens.
+static int32_t check_device_flag(lc_model* m) {
+    int* f = gemv_error_flag_dev();
+    if (!f) return LC_OK;
+    int v = 0;
+    LC_CUDA(cudaMemcpyAsync(&v, f, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    LC_CUDA(cudaStreamSynchronize(m->stream));
+    if (v != 0) {
+        cudaMemsetAsync(f, 0, sizeof(int), m->stream);
+        set_error("a bounded device-side wait ran out (%s); the results of this call are not valid",
+                  v == 2 ? "grid barrier of the persistent decode kernel" : "TMA transaction barrier");
+        return LC_ERR_CUDA;
+    }
+    return LC_OK;
+}
+
 extern "C" {
 
 static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps);
@@ -588,6 +687,7 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(dalloc(&m->d_next, m->max_seqs)); LC_TRY(dalloc(&m->d_step_ctr, 1));
     size_t sc = 16;
     for (int t = 1; t <= T; t++) sc = std::max(sc, attention_scratch_bytes(t, m->nh, m->hd, m->cfg.max_seq_len));
+    sc = std::max(sc, (size_t)m->nh * ((m->cfg.max_seq_len + 127) / 128) * (m->hd + 2) * sizeof(float));  // persistent decode kernel: 128-key splits
     m->attn_scratch_bytes = sc;
     LC_TRY(dalloc((uint8_t**)&m->d_attn_scratch, sc));
     LC_TRY(dalloc(&m->d_attn_counters, (size_t)T * m->nh));
@@ -599,6 +699,7 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_CUDA(cudaEventCreate(&m->ev0));
     LC_CUDA(cudaEventCreate(&m->ev1));
     LC_CUDA(cudaStreamSynchronize(m->stream));
+    LC_TRY(setup_mega(m));
     m->finalized = true;
     return LC_OK;
 }
@@ -611,6 +712,7 @@ int32_t lc_model_destroy(lc_model* m) {
     for (auto& kv : m->tensors) if (kv.second.dev) cudaFree(kv.second.dev);
     for (auto& w : m->layers) if (w.fused_buf) cudaFree(w.fused_buf);
     for (void* p : m->owned) cudaFree(p);
+    for (void* p : m->mega_bufs) cudaFree(p);
     for (void* p : m->k_pools) cudaFree(p);
     for (void* p : m->v_pools) cudaFree(p);
     void* bufs[] = {m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
@@ -690,7 +792,7 @@ int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, co
         if (next_out) memcpy(next_out, m->pin_next, (size_t)n_seqs * 8);
         after_decode_steps(m, n_seqs, seq_ids, 1);
         finish_call(m);
-        return LC_OK;
+        return check_device_flag(m);
     }
     m->meta_valid = false;
     // Rotary index = position inside the CALL (reference mode, attention.rs:13-21) or the cache position.
@@ -761,6 +863,15 @@ static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
         m->launches_in_call += 1;
         return LC_OK;
     };
+    if (n_seqs == 1 && m->mega_ready) {
+        // the whole step is one persistent kernel; one launch per step needs no graph
+        m->mega.out_tokens = m->d_out_tokens;
+        for (int s = 0; s < steps; s++) {
+            LC_TRY(launch_decode_mega(m->mega, m->stream));
+            m->launches_in_call += 1;
+        }
+        return LC_OK;
+    }
     static const bool no_graph = getenv("LC_NO_GRAPH") != nullptr;
     cudaGraphExec_t exec = nullptr;
     int done_steps = 0;
@@ -874,7 +985,7 @@ int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, cons
     }
     after_decode_steps(m, n_seqs, seq_ids, steps);
     finish_call(m);
-    return LC_OK;
+    return check_device_flag(m);
 }
 
 int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature, float top_p,
@@ -909,6 +1020,18 @@ int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_t
         }
     }
     *n_out = count;
+    return LC_OK;
+}
+
+int32_t lc_debug_phase_trace(lc_model* m, uint64_t* out, int32_t max_entries, int32_t* n_phases) {
+    LC_TRY(check_model(m, true));
+    LC_CHECK(out && n_phases, LC_ERR_INVALID, "null output");
+    LC_CHECK(m->mega_ready && m->mega.trace, LC_ERR_STATE, "phase tracing is off (set LC_TRACE=1 before lc_model_finalize)");
+    int n = std::min(max_entries, 4 * m->mega.n_phases);
+    DeviceGuard dg(m->device);
+    LC_CUDA(cudaMemcpyAsync(out, m->mega.trace, (size_t)n * 8, cudaMemcpyDeviceToHost, m->stream));
+    LC_CUDA(cudaStreamSynchronize(m->stream));
+    *n_phases = m->mega.n_phases;
     return LC_OK;
 }
 

@@ -40,7 +40,7 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
 }
 
 template <int M, int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+__global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p) {
     constexpr int UB = 144;
     constexpr int STAGE_BYTES = UB * kTileRows;
@@ -70,24 +70,24 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 
     const int units_mine = (nunits > warp) ? (nunits - warp + WARPS - 1) / WARPS : 0;
     const int tiles_mine = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int jobs_per_tile = units_mine * nmat;
-    const int njobs = tiles_mine * jobs_per_tile;
+    const int njobs = tiles_mine * units_mine * nmat;
 
-    auto issue = [&](int job) {
-        int ti = job / jobs_per_tile, rem = job % jobs_per_tile;
-        int mat = rem / units_mine, ui = rem % units_mine;
-        int tile = blockIdx.x + ti * gridDim.x;
-        int unit = warp + ui * WARPS;
-        int st = job % STAGES;
+    // producer cursor (lane 0): the next job to request, walked without divisions
+    int pj = 0, p_ti = 0, p_mat = 0, p_ui = 0;
+    auto issue_next = [&]() {
+        const int st = pj & (STAGES - 1);
         mbar_expect_tx(&bars[st], STAGE_BYTES);
-        tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, mat ? &tm1 : &tm0, unit * (UB / 4), tile * kTileRows, &bars[st]);
+        tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, p_mat ? &tm1 : &tm0, (warp + p_ui * WARPS) * (UB / 4),
+                    (blockIdx.x + p_ti * gridDim.x) * kTileRows, &bars[st]);
+        pj++;
+        if (++p_ui == units_mine) { p_ui = 0; if (++p_mat == nmat) { p_mat = 0; ++p_ti; } }
     };
 
     if (lane == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(&bars[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        for (int j = 0; j < STAGES && j < njobs; j++) issue(j);  // weights do not depend on the previous kernel
+        for (int j = 0; j < STAGES && j < njobs; j++) issue_next();  // weights do not depend on the previous kernel
     }
     pdl_launch_dependents();
     pdl_wait();
@@ -138,11 +138,10 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 #pragma unroll
             for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
             amax = warp_max(amax);
-            int ex = 0;
-            if (amax > 0.f && amax < 3.0e38f) (void)frexpf(amax, &ex);   // amax = f * 2^ex, f in [0.5, 1)
-            int s = 22 - ex;                                              // |x| * 2^s < 2^22
-            s = max(-100, min(100, s));
-            const float up = ldexpf(1.0f, s), dn = ldexpf(1.0f, -s);
+            // amax = f * 2^ex with f in [0.5, 1): ex from the exponent field (zero, denormal and non-finite inputs fall into the clamp)
+            const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
+            const int s = max(-100, min(100, 22 - ex));                   // |x| * 2^s < 2^22
+            const float up = __uint_as_float((uint32_t)(127 + s) << 23), dn = __uint_as_float((uint32_t)(127 - s) << 23);
             uint32_t pw[3][2] = {{0, 0}, {0, 0}, {0, 0}};
             int xsum = 0;
 #pragma unroll
@@ -178,6 +177,36 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     // B fragment source of this thread: column g = lane / 4
     const int bcol_tok = (g >= 3) ? 1 : 0, bcol_pl = (g >= 3) ? g - 3 : g;
 
+    auto load_bf = [&](int unit, uint32_t (&bf)[NPAIR][8][2]) {
+#pragma unroll
+        for (int pr = 0; pr < NPAIR; pr++) {
+            const int tok = 2 * pr + bcol_tok;
+            const bool colv = g < 6 && tok < M;
+            const unsigned char* bp = planes + plane_off<M>(unit, 0, colv ? tok : 0, bcol_pl > 2 ? 0 : bcol_pl) + 4 * t;
+#pragma unroll
+            for (int sb = 0; sb < 8; sb++) {
+                const uint32_t v0 = lds32(bp + sb * (M * 96)), v1 = lds32(bp + sb * (M * 96) + 16);
+                bf[pr][sb][0] = colv ? v0 : 0u;
+                bf[pr][sb][1] = colv ? v1 : 0u;
+            }
+        }
+    };
+    // B fragments: for each sub-block the plane bytes of k-slots 4t..4t+3 and 16+4t..; loaded once when the
+    // warp owns a single unit of k, per job otherwise
+    uint32_t bf[NPAIR][8][2];
+    float sx2[M][2], isv[M];
+    auto load_unit_consts = [&](int unit) {
+        load_bf(unit, bf);
+#pragma unroll
+        for (int tk = 0; tk < M; tk++) {
+            sx2[tk][0] = sxf[(unit * M + tk) * 8 + 2 * t];
+            sx2[tk][1] = sxf[(unit * M + tk) * 8 + 2 * t + 1];
+            isv[tk] = inv2s[unit * M + tk] * 0.0625f;  // 2^-s and the factor 16 the integer sums carry
+        }
+    };
+    const bool single_unit = units_mine == 1;
+    if (single_unit) load_unit_consts(warp);
+
     bool ok = true;
     int job = 0;
     for (int ti = 0; ti < tiles_mine; ti++) {
@@ -193,29 +222,8 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                     for (int c = 0; c < M; c++) yacc[a][b][c] = 0.f;
 
             for (int ui = 0; ui < units_mine; ui++, job++) {
-                const int unit = warp + ui * WARPS;
-                const int st = job % STAGES;
-                // B fragments of this unit: for each sub-block the plane bytes of k-slots 4t..4t+3 and 16+4t..
-                uint32_t bf[NPAIR][8][2];
-#pragma unroll
-                for (int pr = 0; pr < NPAIR; pr++) {
-                    const int tok = 2 * pr + bcol_tok;
-                    const bool colv = g < 6 && tok < M;
-                    const unsigned char* bp = planes + plane_off<M>(unit, 0, colv ? tok : 0, bcol_pl > 2 ? 0 : bcol_pl) + 4 * t;
-#pragma unroll
-                    for (int sb = 0; sb < 8; sb++) {
-                        uint32_t v0 = lds32(bp + sb * (M * 96)), v1 = lds32(bp + sb * (M * 96) + 16);
-                        bf[pr][sb][0] = colv ? v0 : 0u;
-                        bf[pr][sb][1] = colv ? v1 : 0u;
-                    }
-                }
-                float sx2[M][2], isv[M];
-#pragma unroll
-                for (int tk = 0; tk < M; tk++) {
-                    sx2[tk][0] = sxf[(unit * M + tk) * 8 + 2 * t];
-                    sx2[tk][1] = sxf[(unit * M + tk) * 8 + 2 * t + 1];
-                    isv[tk] = inv2s[unit * M + tk];
-                }
+                const int st = job & (STAGES - 1);
+                if (!single_unit) load_unit_consts(warp + ui * WARPS);
                 ok = ok && mbar_wait(&bars[st], (uint32_t)((job / STAGES) & 1));
                 const unsigned char* tilep = stage_base + (size_t)st * STAGE_BYTES;
 #pragma unroll
@@ -227,56 +235,59 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                     uint32_t scA[2], mnA[2], scB[2], mnB[2];
                     unpack_scales_k4(hA.y, hA.z, hA.w, &scA[0], &scA[1], &mnA[0], &mnA[1]);
                     unpack_scales_k4(hB.y, hB.z, hB.w, &scB[0], &scB[1], &mnB[0], &mnB[1]);
-                    int alo[NPAIR][4], ahi[NPAIR][4];
+                    // one int32 accumulator per C element: low-nibble products are scaled by 16*sc, high-nibble
+                    // products (which carry a factor 16 because the nibble stays in place) by sc
+                    int acc[NPAIR][4];
 #pragma unroll
                     for (int pr = 0; pr < NPAIR; pr++)
 #pragma unroll
-                        for (int j = 0; j < 4; j++) alo[pr][j] = ahi[pr][j] = 0;
+                        for (int j = 0; j < 4; j++) acc[pr][j] = 0;
 #pragma unroll
                     for (int grp = 0; grp < 4; grp++) {
                         const uint32_t wA0 = lds32(rowA + 16 + 32 * grp + 4 * t), wA1 = lds32(rowA + 32 + 32 * grp + 4 * t);
                         const uint32_t wB0 = lds32(rowB + 16 + 32 * grp + 4 * t), wB1 = lds32(rowB + 32 + 32 * grp + 4 * t);
-                        const int sAl = byte_of(scA[grp >> 1], (2 * grp) & 3), sAh = byte_of(scA[grp >> 1], (2 * grp + 1) & 3);
-                        const int sBl = byte_of(scB[grp >> 1], (2 * grp) & 3), sBh = byte_of(scB[grp >> 1], (2 * grp + 1) & 3);
+                        const uint32_t swA = scA[grp >> 1], swB = scB[grp >> 1];
+                        const int jl = (2 * grp) & 3;  // byte of the even sub-block in the packed scale word (0 or 2)
+                        const int sAl = (int)((jl ? (swA >> 12) : (swA << 4)) & 0xFF0u), sAh = (int)__byte_perm(swA, 0, 0x4440 + jl + 1);
+                        const int sBl = (int)((jl ? (swB >> 12) : (swB << 4)) & 0xFF0u), sBh = (int)__byte_perm(swB, 0, 0x4440 + jl + 1);
                         const uint32_t a0 = wA0 & 0x0F0F0F0Fu, a1 = wB0 & 0x0F0F0F0Fu, a2 = wA1 & 0x0F0F0F0Fu, a3 = wB1 & 0x0F0F0F0Fu;
-                        // high nibbles stay in place: the products carry a factor 16 that is removed in f32 below
                         const uint32_t h0 = wA0 & 0xF0F0F0F0u, h1 = wB0 & 0xF0F0F0F0u, h2 = wA1 & 0xF0F0F0F0u, h3 = wB1 & 0xF0F0F0F0u;
 #pragma unroll
                         for (int pr = 0; pr < NPAIR; pr++) {
                             int c[4];
                             mma_u8s8(c, a0, a1, a2, a3, bf[pr][2 * grp][0], bf[pr][2 * grp][1]);
-                            alo[pr][0] += sAl * c[0]; alo[pr][1] += sAl * c[1]; alo[pr][2] += sBl * c[2]; alo[pr][3] += sBl * c[3];
+                            acc[pr][0] += sAl * c[0]; acc[pr][1] += sAl * c[1]; acc[pr][2] += sBl * c[2]; acc[pr][3] += sBl * c[3];
                             mma_u8s8(c, h0, h1, h2, h3, bf[pr][2 * grp + 1][0], bf[pr][2 * grp + 1][1]);
-                            ahi[pr][0] += sAh * c[0]; ahi[pr][1] += sAh * c[1]; ahi[pr][2] += sBh * c[2]; ahi[pr][3] += sBh * c[3];
+                            acc[pr][0] += sAh * c[0]; acc[pr][1] += sAh * c[1]; acc[pr][2] += sBh * c[2]; acc[pr][3] += sBh * c[3];
                         }
                     }
                     // ---- fold planes, scales and the offset term into this thread's f32 partial row sums ----
-                    const float dA = h2f((uint16_t)(hA.x & 0xFFFFu)), dminA = h2f((uint16_t)(hA.x >> 16));
-                    const float dB = h2f((uint16_t)(hB.x & 0xFFFFu)), dminB = h2f((uint16_t)(hB.x >> 16));
+                    const float2 ddA = __half22float2(*reinterpret_cast<const __half2*>(&hA.x));  // (d, dmin)
+                    const float2 ddB = __half22float2(*reinterpret_cast<const __half2*>(&hB.x));
                     // this thread's share of sum_sb m_sb * sum_k x_k: sub-blocks 2t and 2t+1
-                    const float mA0 = (float)byte_of(mnA[t >> 1], (2 * t) & 3), mA1 = (float)byte_of(mnA[t >> 1], (2 * t + 1) & 3);
-                    const float mB0 = (float)byte_of(mnB[t >> 1], (2 * t) & 3), mB1 = (float)byte_of(mnB[t >> 1], (2 * t + 1) & 3);
+                    const uint32_t mwA = mnA[t >> 1], mwB = mnB[t >> 1];
+                    const int jm = (2 * t) & 3;
+                    const float mA0 = (float)((mwA >> (8 * jm)) & 0xFFu), mA1 = (float)((mwA >> (8 * jm + 8)) & 0xFFu);
+                    const float mB0 = (float)((mwB >> (8 * jm)) & 0xFFu), mB1 = (float)((mwB >> (8 * jm + 8)) & 0xFFu);
 #pragma unroll
                     for (int pr = 0; pr < NPAIR; pr++) {
-                        float v[4];
-#pragma unroll
-                        for (int j = 0; j < 4; j++) v[j] = (float)alo[pr][j] + (float)ahi[pr][j] * 0.0625f;
+                        const float v0 = (float)acc[pr][0], v1 = (float)acc[pr][1], v2 = (float)acc[pr][2], v3 = (float)acc[pr][3];
 #pragma unroll
                         for (int which = 0; which < 2; which++) {  // first / second token of the pair
                             const int tok = 2 * pr + which;
                             if (tok >= M) continue;
                             const float c0 = which ? cB0 : cA0, c1 = which ? cB1 : cA1;
-                            const float sA = c0 * v[0] + c1 * v[1];
-                            const float sB = c0 * v[2] + c1 * v[3];
+                            const float sA = c0 * v0 + c1 * v1;
+                            const float sB = c0 * v2 + c1 * v3;
                             const float mtA = mA0 * sx2[tok][0] + mA1 * sx2[tok][1];
                             const float mtB = mB0 * sx2[tok][0] + mB1 * sx2[tok][1];
-                            yacc[rg][0][tok] += (dA * isv[tok]) * sA - dminA * mtA;
-                            yacc[rg][1][tok] += (dB * isv[tok]) * sB - dminB * mtB;
+                            yacc[rg][0][tok] += (ddA.x * isv[tok]) * sA - ddA.y * mtA;
+                            yacc[rg][1][tok] += (ddB.x * isv[tok]) * sB - ddB.y * mtB;
                         }
                     }
                 }
                 __syncwarp();
-                if (lane == 0 && job + STAGES < njobs) issue(job + STAGES);
+                if (lane == 0 && pj < njobs) issue_next();
             }
             // add the four threads that share a row (fixed order)
 #pragma unroll
@@ -349,7 +360,10 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
     int ntiles = (p.n + kTileRows - 1) / kTileRows;
-    int grid = sm_count();
+    // CTAs per SM that fit shared memory (and, for the 8-warp shape, registers): with two per SM the
+    // first CTAs of the next kernel move in while the last CTAs of this one drain
+    int per_sm = (WARPS <= 8 && M <= 2 && 2 * (smem + 1024) <= kMaxSmem + 1024) ? 2 : 1;
+    int grid = sm_count() * per_sm;
     if (grid > ntiles) grid = ntiles;
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap : t0;
@@ -361,6 +375,12 @@ template <int M>
 static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = true;
     int k = a.w->k;
+    static const int cfg = getenv("LC_GEMV_CFG") ? atoi(getenv("LC_GEMV_CFG")) : 0;
+    if constexpr (M <= 2) {
+        if (cfg == 1 && mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2>(a, s);
+        if (cfg == 2 && mma_smem_bytes<M, 8, 4>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 4>(a, s);
+        if (cfg == 3 && mma_smem_bytes<M, 16, 4>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 4>(a, s);
+    }
     if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
         if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2>(a, s);
     }

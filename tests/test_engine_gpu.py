@@ -126,3 +126,33 @@ def test_tiny_shape_reduced_depth(gpu, oracle):
     ref, margins = om.generate(prompt, 16, stop_on_eos=False, want_margins=True)
     assert toks == ref, margins
     eng.close()
+
+
+@pytest.mark.parametrize("layers,heads,kv", [(2, 4, 2), (3, 2, 2)])
+def test_persistent_decode_kernel(gpu, oracle, monkeypatch, layers, heads, kv):
+    """head_dim 128 + Q4_K + f16 cache: single-sequence decode steps run as one persistent kernel per step.
+    Same tokens as the oracle and as the one-kernel-per-phase path."""
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=layers, hidden=128 * heads, heads=heads, kv=kv, ffn=768, vocab=1500)
+    monkeypatch.setenv("LC_MEGA", "1")
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=160)
+    prompt = synth.prompt_tokens(40, spec.vocab_size, 5)
+    ref, margins = om.generate(prompt, 48, stop_on_eos=False, want_margins=True)
+    toks = eng.generate(prompt, 48, stop_on_eos=False)
+    assert toks == ref, margins
+    launches = eng.counters()["kernel_launches"]
+    # step-by-step through the host API (logits out each step) agrees with the oracle's logits
+    eng.kv_clear()
+    om.kv_clear()
+    got = eng.forward(prompt)
+    want = om.forward(prompt)
+    for step in range(6):
+        nxt = int(np.argmax(want))
+        got, want = eng.forward([nxt]), om.forward([nxt])
+        assert_close(got, want, LOGIT_ABS, LOGIT_REL, f"step {step}")
+    eng.close()
+    monkeypatch.delenv("LC_MEGA")
+    eng2, _ = make_pair(gpu, oracle, spec, max_seq_len=160)
+    assert eng2.generate(prompt, 48, stop_on_eos=False) == ref
+    assert eng2.counters()["kernel_launches"] > launches  # the persistent path really was a different path
+    eng2.close()
