@@ -109,6 +109,15 @@ int32_t lc_dev_download(void* dst_host, const void* src_dev, size_t bytes);
 int32_t lc_dev_sync(void);
 int32_t lc_qmatmul_dev(uint32_t typ, const float* a_dev, const void* w_dev, size_t m, size_t k, size_t n, float* c_dev);
 int32_t lc_dequantize_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, float* out_dev);
+/* The attention core of attention_forward (rust/src/inference/attention.rs:69-113: scores / sqrt(head_dim), softmax, weighted
+ * sum of V, grouped-query head mapping) for ONE new token over a paged cache that is already on the device.  q_dev is
+ * [n_heads * head_dim], already rotated; pools are [page][kv head][page_tokens][head_dim] in f16 (kv_f32 = 0, the storage type
+ * of rust/src/cache/mod.rs:33-61) or f32; page_table_dev lists the n_pages pages of the sequence; the token attends to
+ * positions 0 .. ctx_len-1; out_dev is [n_heads * head_dim].  Queued on the library's stream (lc_dev_sync to wait).
+ * The context is split across CTAs; the split partials live in device scratch that the library allocates and keeps. */
+int32_t lc_attention_decode_dev(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
+                                int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                                int32_t page_tokens, int32_t kv_f32, float* out_dev);
 /* CUDA-event stopwatch on the library's stream: begin, queue work, end -> milliseconds. */
 int32_t lc_timer_begin(void);
 int32_t lc_timer_end(float* out_ms);

@@ -154,3 +154,65 @@ int attention_launch_count(int n_tok, int n_heads, int max_ctx) {
 }
 
 }  // namespace lc
+
+// ===========================================================================
+// Decode attention as a device-level operator of the C ABI
+// ===========================================================================
+using namespace lc;
+
+namespace {
+struct AttnOpScratch { DevBuf buf; };
+AttnOpScratch g_attn_op[16];
+
+struct AttnOpArgs {
+    const float* q; const void* k_pool; const void* v_pool; const int32_t* page_table;
+    int32_t n_pages, ctx_len, n_heads, n_kv, hd, page_tokens, kv_f32;
+    float* out;
+};
+
+int32_t attn_op_validate(const AttnOpArgs& a, const char* who) {
+    LC_CHECK(a.q && a.k_pool && a.v_pool && a.page_table && a.out, LC_ERR_INVALID, "%s: null pointer", who);
+    LC_CHECK(a.n_heads > 0 && a.n_kv > 0 && a.n_heads % a.n_kv == 0, LC_ERR_INVALID, "%s: %d heads over %d kv heads", who, a.n_heads, a.n_kv);
+    LC_CHECK(a.hd == 32 || a.hd == 64 || a.hd == 128 || a.hd == 256, LC_ERR_UNSUPPORTED, "%s: head_dim %d is not one of 32, 64, 128, 256", who, a.hd);
+    LC_CHECK(a.page_tokens > 0 && a.ctx_len >= 1 && (int64_t)a.n_pages * a.page_tokens >= a.ctx_len, LC_ERR_INVALID,
+             "%s: %d pages of %d tokens cannot hold a context of %d", who, a.n_pages, a.page_tokens, a.ctx_len);
+    return LC_OK;
+}
+
+// scratch layout: [0,256): tok_seq, tok_pos   [256, 256+4*n_heads): counters   then the split partials
+size_t attn_op_scratch_bytes(const AttnOpArgs& a) {
+    size_t ctr = ((size_t)a.n_heads * 4 + 255) & ~(size_t)255;
+    return 256 + ctr + attention_scratch_bytes(1, a.n_heads, a.hd, a.ctx_len);
+}
+
+int32_t attn_op_run(const AttnOpArgs& a, unsigned char* scratch, cudaStream_t s) {
+    const int32_t meta[2] = {0, a.ctx_len - 1};
+    size_t ctr = ((size_t)a.n_heads * 4 + 255) & ~(size_t)255;
+    LC_CUDA(cudaMemcpyAsync(scratch, meta, sizeof(meta), cudaMemcpyHostToDevice, s));
+    LC_CUDA(cudaMemsetAsync(scratch + 256, 0, ctr, s));  // the split counters must start at zero
+    KvLayout kv;
+    kv.k_pool = const_cast<void*>(a.k_pool); kv.v_pool = const_cast<void*>(a.v_pool);
+    kv.n_kv = a.n_kv; kv.hd = a.hd; kv.page_tokens = a.page_tokens; kv.kv_f32 = a.kv_f32;
+    const int32_t* meta_dev = reinterpret_cast<const int32_t*>(scratch);
+    return launch_attention(a.q, a.n_heads * a.hd, a.out, 1, a.n_heads, kv, meta_dev, meta_dev + 1, a.page_table, a.n_pages, a.ctx_len,
+                            scratch + 256 + ctr, reinterpret_cast<int*>(scratch + 256), nullptr, s);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t lc_attention_decode_dev(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
+                                int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                                int32_t page_tokens, int32_t kv_f32, float* out_dev) {
+    if (!have_device()) return LC_ERR_CUDA;
+    AttnOpArgs a{q_dev, k_pool_dev, v_pool_dev, page_table_dev, n_pages, ctx_len, n_heads, n_kv_heads, head_dim, page_tokens, kv_f32, out_dev};
+    LC_TRY(attn_op_validate(a, "lc_attention_decode_dev"));
+    int dev = 0;
+    LC_CUDA(cudaGetDevice(&dev));
+    LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
+    LC_TRY(g_attn_op[dev].buf.reserve(attn_op_scratch_bytes(a)));
+    return attn_op_run(a, (unsigned char*)g_attn_op[dev].buf.p, stream());
+}
+
+}  // extern "C"
