@@ -118,6 +118,20 @@ int32_t lc_dequantize_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, f
 int32_t lc_attention_decode_dev(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
                                 int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
                                 int32_t page_tokens, int32_t kv_f32, float* out_dev);
+/* Same operation and same kernel for callers that must not allocate device memory at call time -- code running inside a
+ * framework's allocator-owned arena, under a memory budget that is already fully handed out, or in a late phase where
+ * cudaMalloc would serialise the device.  It has no counterpart in the reference.  The split partials go to a 512 KiB array
+ * built into the library image (every GPU that loads the library holds it until the process exits); nothing is
+ * allocated or freed, by this call or by anything it uses.  Shapes whose partials do not fit
+ * (256 + 4*n_heads rounded up to 256 + n_heads * splits * (head_dim + 2) * 4 bytes > 512 KiB, where splits is about
+ * 4 * SM count / n_heads; e.g. 32 heads of 128 dims need 316 KB, 128 heads of 256 dims do not fit) are rejected with LC_ERR_INVALID.
+ * The first call on a device looks up the array's device address; make that first call outside any stream capture.
+ * All calls share the one array, which keeps the previous call's partials: the counters it needs at zero are cleared at
+ * the start of every call, and two calls that overlap on the GPU (different streams, different threads) would race --
+ * the library queues them on its single stream, keep it that way. */
+int32_t lc_attention_decode_static(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
+                                   int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                                   int32_t page_tokens, int32_t kv_f32, float* out_dev);
 /* CUDA-event stopwatch on the library's stream: begin, queue work, end -> milliseconds. */
 int32_t lc_timer_begin(void);
 int32_t lc_timer_end(float* out_ms);

@@ -72,6 +72,7 @@ SIGNATURES = {
     "lc_qmatmul_dev": (_i32, [_u32, _vp, _vp, _sz, _sz, _sz, _vp]),
     "lc_dequantize_dev": (_i32, [_u32, _vp, _sz, _vp]),
     "lc_attention_decode_dev": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "lc_attention_decode_static": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "lc_timer_begin": (_i32, []),
     "lc_timer_end": (_i32, [_f]),
     "lc_flush_l2": (_i32, []),

@@ -198,6 +198,11 @@ int32_t attn_op_run(const AttnOpArgs& a, unsigned char* scratch, cudaStream_t s)
                             scratch + 256 + ctr, reinterpret_cast<int*>(scratch + 256), nullptr, s);
 }
 
+// Scratch of lc_attention_decode_static: lives in the library image, so every GPU that loads the library
+// holds these 512 KiB until the process exits.
+constexpr size_t kStaticAttnScratchBytes = (size_t)512 << 10;
+static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
+unsigned char* g_static_attn_ptr[16] = {};
 }  // namespace
 
 extern "C" {
@@ -213,6 +218,29 @@ int32_t lc_attention_decode_dev(const float* q_dev, const void* k_pool_dev, cons
     LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
     LC_TRY(g_attn_op[dev].buf.reserve(attn_op_scratch_bytes(a)));
     return attn_op_run(a, (unsigned char*)g_attn_op[dev].buf.p, stream());
+}
+
+int32_t lc_attention_decode_static(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
+                                   int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
+                                   int32_t page_tokens, int32_t kv_f32, float* out_dev) {
+    if (!have_device()) return LC_ERR_CUDA;
+    AttnOpArgs a{q_dev, k_pool_dev, v_pool_dev, page_table_dev, n_pages, ctx_len, n_heads, n_kv_heads, head_dim, page_tokens, kv_f32, out_dev};
+    LC_TRY(attn_op_validate(a, "lc_attention_decode_static"));
+    const size_t need = attn_op_scratch_bytes(a);
+    LC_CHECK(need <= kStaticAttnScratchBytes, LC_ERR_INVALID,
+             "lc_attention_decode_static: this shape needs %zu bytes of split scratch, the built-in array holds %zu; use "
+             "lc_attention_decode_dev for larger head counts or contexts", need, kStaticAttnScratchBytes);
+    int dev = 0;
+    LC_CUDA(cudaGetDevice(&dev));
+    LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
+    if (!g_static_attn_ptr[dev]) {
+        // first call on this device: resolve the device address of the array (its host-side name is only a handle)
+        void* p = nullptr;
+        LC_CUDA(cudaGetSymbolAddress(&p, g_static_attn_scratch));
+        g_static_attn_ptr[dev] = (unsigned char*)p;
+        if (!stream()) { set_error("could not create the library stream"); return LC_ERR_CUDA; }
+    }
+    return attn_op_run(a, g_static_attn_ptr[dev], stream());
 }
 
 }  // extern "C"
