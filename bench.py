@@ -188,6 +188,53 @@ def gemv_roofline(lc, spec, reps: int = 3, copies: int = 8, warm: int = 3) -> di
             "launches_timed": launches}
 
 
+def attention_microbench(lc, n_heads=32, n_kv=32, hd=128, ctx=2100, layers=8, reps=5) -> dict:
+    """Decode attention of one token (7B shape: 32 heads of 128 dims, f16 cache, 16-token pages) through
+    lc_attention_decode_dev over `layers` distinct caches (0.28 GB, larger than L2); CUDA events on the library's stream.
+    Every call also queues an 8-byte host-to-device copy and a counter clear, so the figure is an upper bound."""
+    import ctypes as C
+    import numpy as np
+    lib, chk = lc.load(), lc._capi.check
+    pt = 16
+    n_pages = (ctx + pt - 1) // pt
+    pool_bytes = n_pages * n_kv * pt * hd * 2
+
+    def dev(nbytes):
+        p = C.c_void_p()
+        chk(lib.lc_dev_alloc(nbytes, C.byref(p)))
+        return p
+
+    ks = [dev(pool_bytes) for _ in range(layers)]
+    vs = [dev(pool_bytes) for _ in range(layers)]
+    for i, p in enumerate(ks + vs):
+        chk(lib.lc_synth_tensor_dev(1, 5, f"kv{i}".encode(), 1.0, pool_bytes // 2, p))
+    table = np.arange(n_pages, dtype=np.int32)
+    td = dev(table.nbytes)
+    chk(lib.lc_dev_upload(td, table.ctypes.data_as(C.c_void_p), table.nbytes))
+    q = np.random.default_rng(0).standard_normal(n_heads * hd).astype(np.float32)
+    qd = dev(q.nbytes)
+    chk(lib.lc_dev_upload(qd, q.ctypes.data_as(C.c_void_p), q.nbytes))
+    out = dev(n_heads * hd * 4)
+
+    def sweep():
+        for k, v in zip(ks, vs):
+            chk(lib.lc_attention_decode_dev(qd, k, v, td, n_pages, ctx, n_heads, n_kv, hd, pt, 0, out))
+
+    sweep()
+    chk(lib.lc_dev_sync())
+    chk(lib.lc_timer_begin())
+    for _ in range(reps):
+        sweep()
+    ms = C.c_float()
+    chk(lib.lc_timer_end(C.byref(ms)))
+    for p in ks + vs + [td, qd, out]:
+        lib.lc_dev_free(p)
+    us = ms.value * 1e3 / (reps * layers)
+    byt = 2 * ctx * n_kv * hd * 2
+    return {"kernel": "decode attention, 1 token", "heads": n_heads, "kv_heads": n_kv, "head_dim": hd, "context": ctx,
+            "us_per_call": round(us, 2), "kv_bytes": byt, "achieved_gbs": round(byt / us / 1e3, 1)}
+
+
 def run_ours(args):
     rank, world, local = dist_env()
     import leafcutterllm_b200 as lc
@@ -315,11 +362,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default="", choices=["", "gemv"], help="gemv: run just the isolated GEMV loop (small case for profilers)")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers)")
     ap.add_argument("--profile-range", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="context prefilled before decoding (default: the 2048 of the workload)")
     args = ap.parse_args()
-    if args.only == "gemv":
+    if args.only == "attn":
+        import leafcutterllm_b200 as lc
+        print(json.dumps(attention_microbench(lc)))
+    elif args.only == "gemv":
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth
         print(json.dumps(gemv_roofline(lc, synth.LLAMA7B, reps=1, copies=2, warm=1)))

@@ -11,6 +11,7 @@
 #include "lc_kernels.h"
 #include "lc_attn.cuh"
 #include "lc_mega.h"
+#include "lc_tma.cuh"
 
 namespace lc {
 
@@ -68,6 +69,185 @@ attention_split_kernel(AttnParams p) {
     attention_item<HD, F32, 0>(p, (int)blockIdx.x, (int)blockIdx.y, (int)threadIdx.x, sh);
 }
 
+// Decode attention with the whole key/value slice of the CTA staged in shared memory by bulk copies
+// (head_dim 128, f16 cache, 16-token pages).  One CTA per (token, kv head, split of 128 keys): the sixteen 4 KB
+// (page, kv head) slabs of K and V are requested at once on one mbarrier -- a single memory round trip instead of one
+// per pass -- and, in a fused decode step, BEFORE the grid dependency wait, because cached keys do not depend on the
+// projection kernel that precedes this one.  All q heads of the kv group are then served from the staged slice.
+constexpr int kStagedChunk = 128;
+template <int HD>
+__global__ void __launch_bounds__(kAttnWarps * 32) attention_staged_kernel(AttnParams p) {
+    static_assert(HD == 128 && kAttnWarps * 32 == HD, "one thread per key and per dim");
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __half* K_s = reinterpret_cast<__half*>(dsm);
+    __half* V_s = K_s + kStagedChunk * HD;
+    __shared__ __align__(16) float sh[6 * HD];  // q, p, four partial accumulators
+    __shared__ __align__(8) uint64_t bar;
+    const KvLayout& kv = p.kv;
+    const int n_heads = p.n_heads, gsz = n_heads / kv.n_kv;
+    const int tok = blockIdx.x / kv.n_kv, kvh = blockIdx.x % kv.n_kv, split = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool fused = p.k_new != nullptr;
+    auto stage = [&](int pos) {
+        const int t_begin = split * p.chunk, t_end = min(pos + 1, t_begin + p.chunk);
+        if (tid == 0) {
+            mbar_init(&bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (t_begin < t_end) {
+                const int32_t* pt = p.page_table + (size_t)p.tok_seq[tok] * p.pages_per_seq;
+                const int pg0 = t_begin / 16, npg = (t_end - t_begin + 15) / 16;
+                int32_t pgs[kStagedChunk / 16];
+#pragma unroll
+                for (int i = 0; i < kStagedChunk / 16; i++) pgs[i] = pt[pg0 + (i < npg ? i : 0)];  // all page ids in flight together
+                mbar_expect_tx(&bar, (uint32_t)(npg * 2 * 16 * HD * 2));
+#pragma unroll
+                for (int i = 0; i < kStagedChunk / 16; i++) {
+                    if (i < npg) {
+                        const size_t src = ((size_t)pgs[i] * kv.n_kv + kvh) * 16 * HD;
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                         smem_u32(K_s + (size_t)i * 16 * HD)),
+                                     "l"((const __half*)kv.k_pool + src), "r"(16 * HD * 2), "r"(smem_u32(&bar))
+                                     : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                         smem_u32(V_s + (size_t)i * 16 * HD)),
+                                     "l"((const __half*)kv.v_pool + src), "r"(16 * HD * 2), "r"(smem_u32(&bar))
+                                     : "memory");
+                    }
+                }
+            }
+        }
+    };
+    int pos;
+    if (fused) {  // the cache holds only earlier steps' tokens: fetch before waiting for the projection kernel
+        pos = p.tok_pos[tok];
+        stage(pos);
+        pdl_launch_dependents();
+        pdl_wait();
+    } else {      // the previous kernel wrote this call's keys into the cache
+        pdl_launch_dependents();
+        pdl_wait();
+        pos = p.tok_pos[tok];
+        stage(pos);
+    }
+    const int t_begin = split * p.chunk, t_end = min(pos + 1, t_begin + p.chunk);
+    const int n = t_end - t_begin;
+    __syncthreads();  // barrier initialised
+    bool ok = true;
+    if (n > 0) ok = mbar_wait(&bar, 0);
+    const int rp = fused ? p.tok_rope[tok] : 0;
+    if (n > 0 && fused && pos >= t_begin && pos < t_end) {
+        // the token of this step replaces the (stale) staged slot: rotate, round through f16, keep in the cache
+        const int row = pos - t_begin;
+        float kr[1], vr;
+        load_rotated<1, HD>(p.k_new + (size_t)tok * p.q_stride + kvh * HD, tid, rp, p.theta, kr);
+        vr = __ldcg(p.v_new + (size_t)tok * p.q_stride + kvh * HD + tid);
+        const __half hk = __float2half_rn(kr[0]), hv = __float2half_rn(vr);  // cache/mod.rs:35-36
+        K_s[row * HD + tid] = hk;
+        V_s[row * HD + tid] = hv;
+        const int32_t* pt = p.page_table + (size_t)p.tok_seq[tok] * p.pages_per_seq;
+        const size_t dst = (((size_t)pt[pos / 16] * kv.n_kv + kvh) * 16 + pos % 16) * HD + tid;
+        ((__half*)kv.k_pool)[dst] = hk;
+        ((__half*)kv.v_pool)[dst] = hv;
+    }
+    __syncthreads();
+    // ---- compute: short dependency chains instead of an online softmax ----
+    //  scores : thread t owns key t (its 256-byte row from shared memory, 16-byte chunks walked in an order rotated
+    //           by t so that a quarter warp never hits one bank twice), four partial sums;
+    //  softmax: one block max, one exp per key, one block sum (the three passes of attention.rs:96-102 on the slice);
+    //  p.V    : warp w takes keys 32w..32w+31, lane j takes dims 4j..4j+3 (64-bit conflict-free reads), the four warps
+    //           are added in warp order.
+    const float inv_div = sqrtf((float)HD);  // attention.rs:93
+    float* q_s = sh;                      // [128]
+    float* p_s = sh + HD;                 // [128]
+    float* acc_s = sh + 2 * HD;           // [4][128]
+    __shared__ float red_s[8];
+    __shared__ int last_s;
+    for (int hq = 0; hq < gsz; hq++) {
+        const int h = kvh * gsz + hq, item = tok * n_heads + h;
+        float* pout = p.partial + ((size_t)item * p.n_splits + split) * (HD + 2);
+        float m = -INFINITY, l = 0.f, a_out = 0.f;
+        if (n > 0) {
+            {
+                float qv[1];
+                load_rotated<1, HD>(p.q + (size_t)tok * p.q_stride + h * HD, tid, rp, p.theta, qv);
+                __syncthreads();  // the previous head is done with q_s / p_s / acc_s
+                q_s[tid] = qv[0];
+            }
+            __syncthreads();
+            float sc = -INFINITY;
+            if (tid < n) {
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+                const __half* krow = K_s + (size_t)tid * HD;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int c = (j + tid) & 15;
+                    const uint4 kq = *reinterpret_cast<const uint4*>(krow + c * 8);
+                    const float4 qa = *reinterpret_cast<const float4*>(q_s + c * 8);
+                    const float4 qb = *reinterpret_cast<const float4*>(q_s + c * 8 + 4);
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&kq);
+                    const float2 k0 = __half22float2(h2[0]), k1 = __half22float2(h2[1]), k2 = __half22float2(h2[2]), k3 = __half22float2(h2[3]);
+                    d0 = fmaf(qa.x, k0.x, d0); d1 = fmaf(qa.y, k0.y, d1); d2 = fmaf(qa.z, k1.x, d2); d3 = fmaf(qa.w, k1.y, d3);
+                    d0 = fmaf(qb.x, k2.x, d0); d1 = fmaf(qb.y, k2.y, d1); d2 = fmaf(qb.z, k3.x, d2); d3 = fmaf(qb.w, k3.y, d3);
+                }
+                sc = ((d0 + d1) + (d2 + d3)) / inv_div;
+            }
+            const float wm = warp_max(sc);
+            if (lane == 0) red_s[warp] = wm;
+            __syncthreads();
+            m = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+            const float pe = (tid < n) ? expf(sc - m) : 0.f;
+            p_s[tid] = pe;
+            const float ws = warp_sum(pe);
+            if (lane == 0) red_s[4 + warp] = ws;
+            __syncthreads();
+            l = ((red_s[4] + red_s[5]) + red_s[6]) + red_s[7];
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            const int kend = min(n, 32 * warp + 32);
+#pragma unroll 4
+            for (int k = 32 * warp; k < kend; k++) {
+                const float pk = p_s[k];
+                const uint2 vq = *reinterpret_cast<const uint2*>(V_s + (size_t)k * HD + 4 * lane);
+                const __half2* h2 = reinterpret_cast<const __half2*>(&vq);
+                const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]);
+                a0 = fmaf(pk, v0.x, a0); a1 = fmaf(pk, v0.y, a1); a2 = fmaf(pk, v1.x, a2); a3 = fmaf(pk, v1.y, a3);
+            }
+            *reinterpret_cast<float4*>(acc_s + warp * HD + 4 * lane) = make_float4(a0, a1, a2, a3);
+            __syncthreads();
+            a_out = ((acc_s[tid] + acc_s[HD + tid]) + acc_s[2 * HD + tid]) + acc_s[3 * HD + tid];
+        }
+        if (p.n_splits == 1) {
+            p.out[(size_t)item * HD + tid] = a_out / l;
+            continue;
+        }
+        if (tid == 0) { pout[0] = m; pout[1] = l; }
+        pout[2 + tid] = a_out;
+        // the last split of this (token, head) to finish merges all of them, in split order
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) last_s = (atomicAdd(&p.counters[item], 1) == p.n_splits - 1);
+        __syncthreads();
+        if (last_s) {
+            __threadfence();
+            const float* pp = p.partial + (size_t)item * p.n_splits * (HD + 2);
+            float mm = -INFINITY;
+            for (int s2 = 0; s2 < p.n_splits; s2++) mm = fmaxf(mm, __ldcg(pp + (size_t)s2 * (HD + 2)));
+            float ll = 0.f, a = 0.f;
+            for (int s2 = 0; s2 < p.n_splits; s2++) {
+                const float* ps = pp + (size_t)s2 * (HD + 2);
+                const float ms = __ldcg(ps);
+                if (ms == -INFINITY) continue;  // empty split
+                const float scl = expf(ms - mm);
+                ll += __ldcg(ps + 1) * scl;
+                a += __ldcg(ps + 2 + tid) * scl;
+            }
+            p.out[(size_t)item * HD + tid] = a / ll;
+            if (tid == 0) p.counters[item] = 0;
+        }
+    }
+    if (!ok && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
 // ---------------------------------------------------------------------------
 static bool g_attn_pdl = getenv("LC_NO_PDL") == nullptr;
 template <typename... KArgs, typename... Args>
@@ -103,6 +283,8 @@ static void split_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_s
     if (splits < 1) splits = 1;
     int ch = (max_ctx + splits - 1) / splits;
     ch = (ch + 63) / 64 * 64;
+    static const int force = getenv("LC_ATTN_CHUNK") ? atoi(getenv("LC_ATTN_CHUNK")) : 0;  // experiments only
+    if (force > 0) ch = force;
     *chunk = ch;
     *n_splits = (max_ctx + ch - 1) / ch;
     if (*n_splits < 1) *n_splits = 1;
@@ -113,13 +295,43 @@ void attention_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_spli
 size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx) {
     int chunk, splits;
     split_plan(n_tok, n_heads, max_ctx, &chunk, &splits);
-    if (splits == 1) return 16;
-    return (size_t)n_tok * n_heads * splits * (hd + 2) * sizeof(float);
+    size_t staged = (size_t)n_tok * n_heads * ((max_ctx + kStagedChunk - 1) / kStagedChunk) * (hd + 2) * sizeof(float);
+    if (n_tok * n_heads > sm_count() * 4) staged = 16;
+    size_t plain = splits == 1 ? 16 : (size_t)n_tok * n_heads * splits * (hd + 2) * sizeof(float);
+    return plain > staged ? plain : staged;
+}
+
+static bool staged_applies(const AttnParams& p, int n_tok) {
+    static const bool off = getenv("LC_ATTN_NO_STAGED") != nullptr;
+    // few tokens (decode): the split-context kernel with shared-memory staging; many tokens (prefill) keep one CTA per (token, head)
+    return !off && p.kv.hd == 128 && !p.kv.kv_f32 && p.kv.page_tokens == 16 && n_tok * p.n_heads <= sm_count() * 4;
 }
 
 template <int HD>
 static int32_t launch_attention_hd(const AttnParams& base, int n_tok, int max_ctx, cudaStream_t s) {
     AttnParams p = base;
+    if (HD == 128 && staged_applies(p, n_tok)) {
+        p.chunk = kStagedChunk;
+        p.n_splits = (max_ctx + kStagedChunk - 1) / kStagedChunk;
+        const size_t smem = (size_t)kStagedChunk * 128 * 2 * 2;
+        static bool attr_set = false;
+        if (!attr_set) {
+            LC_CUDA(cudaFuncSetAttribute(attention_staged_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(n_tok * p.kv.n_kv), (unsigned)p.n_splits);
+        cfg.blockDim = dim3(kAttnWarps * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = g_attn_pdl ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        LC_CUDA(cudaLaunchKernelEx(&cfg, attention_staged_kernel<128>, p));
+        return LC_OK;
+    }
     split_plan(n_tok, p.n_heads, max_ctx, &p.chunk, &p.n_splits);
     dim3 grid((unsigned)(n_tok * p.n_heads), (unsigned)p.n_splits);
     if (p.kv.kv_f32) LC_CUDA(launch_k(attention_split_kernel<HD, true>, grid, dim3(kAttnWarps * 32), s, p));
@@ -137,6 +349,7 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
     p.counters = counters;
     p.k_new = fuse ? fuse->k_new : nullptr; p.v_new = fuse ? fuse->v_new : nullptr;
     p.tok_rope = fuse ? fuse->tok_rope : nullptr; p.theta = fuse ? fuse->theta : 0.f;
+    p.error_flag = gemv_error_flag_dev();
     switch (kv.hd) {
         case 32: return launch_attention_hd<32>(p, n_tok, max_ctx, s);
         case 64: return launch_attention_hd<64>(p, n_tok, max_ctx, s);

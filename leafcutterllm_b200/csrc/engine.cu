@@ -223,6 +223,13 @@ KvLayout kv_layout(const lc_model* m, int layer) {
     return kv;
 }
 
+// Diagnostics: LC_ABLATE is a bit mask of phases to leave out when timing (1 attention, 2 QKV, 4 O, 8 gate/up, 16 down,
+// 32 head).  Results are meaningless with any bit set; it exists to attribute step time to phases.
+static int ablate_mask() {
+    static const int v = getenv("LC_ABLATE") ? atoi(getenv("LC_ABLATE")) : 0;
+    return v;
+}
+
 int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
     for (int t0 = 0; t0 < T; t0 += kTokTile) {
         GemvArgs g = a;
@@ -247,6 +254,7 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     if (w.fused_qkv) {
         g.w = &w.qkv;
         g.out = m->d_qkv;
+        if (!(ablate_mask() & 2))
         // the fused output is [T, nqkv] only when every token tile writes rows of nqkv floats
         LC_TRY(gemv_tiled(m, g, T, m->nqkv, m->H));
     } else {
@@ -257,7 +265,8 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     float* q = m->d_qkv;
     float* k = m->d_qkv + (size_t)m->nh * m->hd;
     float* v = k + (size_t)m->nkv * m->hd;
-    if (decode_step) {
+    if (ablate_mask() & 1) {
+    } else if (decode_step) {
         // one new token per sequence: rotation and the cache append ride inside the attention kernel
         AttnFusion fz{k, v, m->d_tok_rope, m->cfg.rope_theta};
         LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
@@ -275,6 +284,7 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     o.x = m->d_attn;
     o.out = out;
     if (residual) { o.residual = residual; o.epi = EPI_ADD_RESIDUAL; }
+    if (ablate_mask() & 4) return LC_OK;
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
 }
 
@@ -289,12 +299,13 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     g.eps = m->cfg.rms_eps;
     g.out = m->d_ffn;
     g.epi = EPI_SILU_MUL;
-    LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
+    if (!(ablate_mask() & 8)) LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
     GemvArgs d;
     d.w = &w.down;
     d.x = m->d_ffn;
     d.out = out;
     if (residual) { d.residual = residual; d.epi = EPI_ADD_RESIDUAL; }
+    if (ablate_mask() & 16) return LC_OK;
     return gemv_tiled(m, d, T, m->H, m->F);
 }
 
@@ -331,7 +342,7 @@ int32_t forward_tokens(lc_model* m, int T, int n_last, bool identity_last, int r
     h.norm_w = m->final_norm;
     h.eps = m->cfg.rms_eps;
     h.out = m->d_logits + (size_t)row0 * m->V;
-    LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
+    if (!(ablate_mask() & 32)) LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
     LC_TRY(launch_argmax(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->d_next + row0, m->stream));
     m->launches_in_call += 1;
     return LC_OK;
@@ -430,7 +441,7 @@ static int32_t setup_mega(lc_model* m) {
     if ((size_t)m->nh * a.n_splits * (m->hd + 2) * sizeof(float) > m->attn_scratch_bytes) return LC_OK;
     a.partial = (float*)m->d_attn_scratch; a.counters = m->d_attn_counters;
     a.k_new = m->d_qkv + (size_t)m->nh * m->hd; a.v_new = a.k_new + (size_t)m->nkv * m->hd; a.tok_rope = m->d_tok_rope;
-    a.theta = m->cfg.rope_theta;
+    a.theta = m->cfg.rope_theta; a.error_flag = gemv_error_flag_dev();
     P.k_pools = d_kp; P.v_pools = d_vp;
     P.embed = (const uint8_t*)m->embed->view; P.embed_typ = m->embed->typ; P.embed_rows = (int64_t)m->embed->rows;
     P.tokens = m->d_tokens; P.hidden = m->d_hidden; P.logits = m->d_logits; P.V = m->V; P.next = m->d_next;

@@ -28,6 +28,7 @@ struct AttnParams {
     const float* v_new;
     const int32_t* tok_rope;
     float theta;
+    int* error_flag;       // set when a bounded wait runs out (may be null)
 };
 
 template <int DPL, bool F32>
