@@ -82,6 +82,44 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+class Ranks:
+    """Replicas only: the ranks never exchange data on the decode path.  They meet at a barrier before and after the
+    timed region and agree on the slowest rank's time (max over ranks)."""
+
+    def __init__(self, rank: int, world: int, local: int, backend: str):
+        self.rank, self.world, self.dist, self.cuda = rank, world, None, backend == "nccl"
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            if self.cuda:
+                torch.cuda.set_device(local)
+                dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            else:
+                dist.init_process_group(backend)
+            self.dist = dist
+
+    def barrier_max(self, v: float) -> float:
+        if self.dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device="cuda" if self.cuda else "cpu")
+        if self.cuda:
+            torch.cuda.synchronize()
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        if self.cuda:
+            torch.cuda.synchronize()
+        return float(t.item())
+
+    def aggregate_rate(self, units_per_rank: float, seconds_this_rank: float) -> float:
+        """Whole-job rate: every rank did `units_per_rank` (weak scaling), the job took as long as its slowest rank."""
+        return self.world * units_per_rank / self.barrier_max(seconds_this_rank)
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
 def dist_env():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
@@ -243,22 +281,8 @@ def run_ours(args):
     if lib.lc_device_count() <= 0:
         raise SystemExit("bench.py needs a CUDA device: " + lib.lc_last_error().decode())
     lc._capi.check(lib.lc_set_device(local))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    def barrier_max(v: float) -> float:
-        if dist is None:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        torch.cuda.synchronize()
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        torch.cuda.synchronize()
-        return float(t.item())
+    ranks = Ranks(rank, world, local, "nccl")
+    barrier_max = ranks.barrier_max
 
     spec = synth.LLAMA7B
     e2e_steps = min(args.steps, 64)
@@ -324,9 +348,7 @@ def run_ours(args):
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(spec)
     eng.close()
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
     if rank == 0:
         print(json.dumps(line))
 
