@@ -122,6 +122,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_staged_kernel(AttnP
     if (fused) {  // the cache holds only earlier steps' tokens: fetch before waiting for the projection kernel
         pos = p.tok_pos[tok];
         stage(pos);
+        if (tid == 32) {
+            const unsigned part = blockIdx.y * gridDim.x + blockIdx.x, nparts = gridDim.x * gridDim.y;
+            l2_prefetch_part(p.prefetch.p[0], p.prefetch.bytes[0], part, nparts);
+            l2_prefetch_part(p.prefetch.p[1], p.prefetch.bytes[1], part, nparts);
+        }
         pdl_launch_dependents();
         pdl_wait();
     } else {      // the previous kernel wrote this call's keys into the cache
@@ -349,6 +354,7 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
     p.counters = counters;
     p.k_new = fuse ? fuse->k_new : nullptr; p.v_new = fuse ? fuse->v_new : nullptr;
     p.tok_rope = fuse ? fuse->tok_rope : nullptr; p.theta = fuse ? fuse->theta : 0.f;
+    if (fuse) p.prefetch = fuse->prefetch;
     p.error_flag = gemv_error_flag_dev();
     switch (kv.hd) {
         case 32: return launch_attention_hd<32>(p, n_tok, max_ctx, s);

@@ -230,6 +230,42 @@ static int ablate_mask() {
     return v;
 }
 
+// Decode steps only: which later weights each of a layer's five kernels (0 QKV, 1 attention, 2 O, 3 gate/up, 4 down)
+// asks the L2 cache to fetch.  Targets: 0 nothing, 1 O, 2 gate + up, 3 down, 4 the next layer's QKV, 5 the next layer's O.
+// A decode kernel is bound by latency, not by bandwidth, so HBM has room for the bytes of the kernel after it; with
+// them in L2 that kernel's tile loads return sooner.  LC_PF="a,b,c,d,e" overrides the table (experiments).
+static L2Prefetch prefetch_for(lc_model* m, int l, int kernel) {
+    static int table[5] = {0, 0, 0, 0, 0};  // off by default: measured slower (the extra reads delay the kernel's own tiles)
+    static bool parsed = false;
+    if (!parsed) {
+        parsed = true;
+        if (const char* e = getenv("LC_PF")) {
+            int v[5] = {0, 0, 0, 0, 0};
+            if (sscanf(e, "%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4]) >= 1)
+                for (int i = 0; i < 5; i++) table[i] = v[i];
+        }
+    }
+    L2Prefetch pf;
+    auto put = [&](int slot, const QWeight& w) {
+        if (w.data && w.typ == LC_TYPE_Q4_K && ((uintptr_t)w.data % 16) == 0) {
+            pf.p[slot] = w.data;
+            pf.bytes[slot] = (unsigned long long)w.n * w.row_bytes;
+        }
+    };
+    const int t = table[kernel];
+    if (t >= 1 && t <= 3) {
+        LayerW& w = m->layers[l];
+        if (t == 1) put(0, w.o);
+        if (t == 2) { put(0, w.gate); put(1, w.up); }
+        if (t == 3) put(0, w.down);
+    } else if ((t == 4 || t == 5) && l + 1 < m->L) {
+        LayerW& w = m->layers[l + 1];
+        if (t == 4 && w.fused_qkv) put(0, w.qkv);
+        if (t == 5) put(0, w.o);
+    }
+    return pf;
+}
+
 int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
     for (int t0 = 0; t0 < T; t0 += kTokTile) {
         GemvArgs g = a;
@@ -251,6 +287,7 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     g.x = x;
     g.norm_w = norm_w;
     g.eps = m->cfg.rms_eps;
+    if (decode_step) g.prefetch = prefetch_for(m, l, 0);
     if (w.fused_qkv) {
         g.w = &w.qkv;
         g.out = m->d_qkv;
@@ -269,6 +306,7 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     } else if (decode_step) {
         // one new token per sequence: rotation and the cache append ride inside the attention kernel
         AttnFusion fz{k, v, m->d_tok_rope, m->cfg.rope_theta};
+        fz.prefetch = prefetch_for(m, l, 1);
         LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
                                 m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, &fz, m->stream));
         m->launches_in_call += 1;
@@ -284,12 +322,14 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     o.x = m->d_attn;
     o.out = out;
     if (residual) { o.residual = residual; o.epi = EPI_ADD_RESIDUAL; }
+    if (decode_step) o.prefetch = prefetch_for(m, l, 2);
     if (ablate_mask() & 4) return LC_OK;
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
 }
 
 // ffn_forward (engine.rs:146-164)
-int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out) {
+int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out,
+                  bool decode_step) {
     LayerW& w = m->layers[l];
     GemvArgs g;
     g.w = &w.gate;
@@ -299,12 +339,14 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     g.eps = m->cfg.rms_eps;
     g.out = m->d_ffn;
     g.epi = EPI_SILU_MUL;
+    if (decode_step) g.prefetch = prefetch_for(m, l, 3);
     if (!(ablate_mask() & 8)) LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
     GemvArgs d;
     d.w = &w.down;
     d.x = m->d_ffn;
     d.out = out;
     if (residual) { d.residual = residual; d.epi = EPI_ADD_RESIDUAL; }
+    if (decode_step) d.prefetch = prefetch_for(m, l, 4);
     if (ablate_mask() & 16) return LC_OK;
     return gemv_tiled(m, d, T, m->H, m->F);
 }
@@ -316,7 +358,7 @@ int32_t run_layers(lc_model* m, int T, bool decode_step) {
     for (int l = 0; l < m->L; l++) {
         LayerW& w = m->layers[l];
         LC_TRY(attention_block(m, l, m->d_hidden, w.attn_norm, T, m->d_hidden, m->d_hidden2, decode_step));
-        LC_TRY(ffn_block(m, l, m->d_hidden2, w.ffn_norm, T, m->d_hidden2, m->d_hidden));
+        LC_TRY(ffn_block(m, l, m->d_hidden2, w.ffn_norm, T, m->d_hidden2, m->d_hidden, decode_step));
     }
     return LC_OK;
 }
@@ -656,6 +698,16 @@ int32_t lc_model_finalize(lc_model* m) {
     // loader.rs:192-199: tied head when output.weight is absent
     std::string head = m->tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
     LC_TRY(weight_of(m, head, V, H, &m->head, nullptr));
+
+    // scratch of the split-tile GEMV, so that no launch inside a captured decode step allocates
+    if (m->L > 0) {
+        const LayerW& w0 = m->layers[0];
+        if (w0.qkv.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(m->nqkv, H, false));
+        if (w0.o.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(H, nq, false));
+        if (w0.gate.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(F, H, true));
+        if (w0.down.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(H, F, false));
+    }
+    if (m->head.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(V, H, false));
 
     // weight sanity scan (loader.rs:241-249) and resident byte count
     LC_TRY(dalloc(&m->d_sanity, 1));
@@ -1090,7 +1142,7 @@ int32_t lc_probe_ffn(lc_model* m, int32_t layer, const float* x, int32_t seq, fl
     LC_CHECK(layer >= 0 && layer < m->L && x && out && seq >= 1 && seq <= m->t_cap, LC_ERR_INVALID, "probe_ffn: bad argument");
     DeviceGuard dg(m->device);
     LC_CUDA(cudaMemcpyAsync(m->d_hidden, x, (size_t)seq * m->H * 4, cudaMemcpyHostToDevice, m->stream));
-    LC_TRY(ffn_block(m, layer, m->d_hidden, nullptr, seq, nullptr, m->d_hidden2));
+    LC_TRY(ffn_block(m, layer, m->d_hidden, nullptr, seq, nullptr, m->d_hidden2, false));
     LC_CUDA(cudaMemcpyAsync(out, m->d_hidden2, (size_t)seq * m->H * 4, cudaMemcpyDeviceToHost, m->stream));
     LC_CUDA(cudaStreamSynchronize(m->stream));
     finish_call(m);

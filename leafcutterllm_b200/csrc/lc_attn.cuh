@@ -29,6 +29,7 @@ struct AttnParams {
     const int32_t* tok_rope;
     float theta;
     int* error_flag;       // set when a bounded wait runs out (may be null)
+    L2Prefetch prefetch;   // weights of the kernels that follow, pulled into L2 by the staged kernel
 };
 
 template <int DPL, bool F32>

@@ -74,6 +74,24 @@ __device__ __forceinline__ uint16_t f2h(float f) { return __half_as_ushort(__flo
 // prologue now / wait until the previous kernel's memory is visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Ask the L2 cache to fetch part `part` of `nparts` of [base, base + bytes) from HBM (both 16-byte aligned).  Used by a
+// kernel to pull the weights of the kernel that follows it into L2 while its own, latency-bound, work runs: the
+// caller is one thread; nothing waits for the fetch and nothing is written.
+__device__ __forceinline__ void l2_prefetch_part(const void* base, unsigned long long bytes, unsigned part, unsigned nparts) {
+    if (base == nullptr || bytes == 0) return;
+    const unsigned long long per = ((bytes + nparts - 1) / nparts + 15ull) & ~15ull;
+    const unsigned long long beg = per * part;
+    if (beg >= bytes) return;
+    unsigned long long len = bytes - beg;
+    if (len > per) len = per;
+    len &= ~15ull;
+    const char* a = reinterpret_cast<const char*>(base) + beg;
+    for (unsigned long long off = 0; off < len; off += 16384ull) {
+        const unsigned sz = (unsigned)((len - off) < 16384ull ? (len - off) : 16384ull);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a + off), "r"(sz) : "memory");
+    }
+}
 #endif
 
 }  // namespace lc

@@ -44,12 +44,18 @@ struct QWeight {
     uint32_t typ = 0;
     int n = 0, k = 0;
     size_t row_bytes = 0;
-    alignas(64) unsigned char tmap[128];  // CUtensorMap for the TMA-staged kernels
+    alignas(64) unsigned char tmap[128];      // CUtensorMap for the TMA-staged kernels: box = one 256-element unit x 32 rows
+    alignas(64) unsigned char tmap_wide[128]; // the same tensor with a box of 128 rows (tcgen05 kernel)
     bool has_tmap = false;
 };
 int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int k);
 
 enum GemvEpilogue { EPI_STORE = 0, EPI_ADD_RESIDUAL = 1, EPI_SILU_MUL = 2 };
+// Bytes a kernel asks the L2 cache to fetch for the kernel that follows it (no effect on results).
+struct L2Prefetch {
+    const void* p[2] = {nullptr, nullptr};
+    unsigned long long bytes[2] = {0, 0};
+};
 struct GemvArgs {
     const QWeight* w = nullptr;   // first matrix
     const QWeight* w2 = nullptr;  // EPI_SILU_MUL: the `up` matrix (w is `gate`)
@@ -60,9 +66,13 @@ struct GemvArgs {
     const float* norm_w = nullptr;    // when set: x is RMS-normalised with this gain before the product
     float eps = 1e-5f;
     GemvEpilogue epi = EPI_STORE;
+    L2Prefetch prefetch;              // honoured by the tensor-core Q4_K kernel
 };
 // y[m,n] = x[m,k] . dequant(W)^T, fp32 activations and accumulation.
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s);
+// Reserves the scratch a later launch_qgemv of an [n x k] matrix may need, so that none is allocated inside a stream
+// capture (two_mats: the gate/up pair of EPI_SILU_MUL).
+int32_t qgemv_reserve_scratch(int n, int k, bool two_mats);
 // Number of kernels launch_qgemv queues for these arguments (for launch accounting).
 int qgemv_launch_count(const GemvArgs& a);
 
@@ -88,7 +98,7 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx);
 // fuse (decode steps only, every token the single new token of its sequence): q is rotated on load and the new
 // key/value are taken from k_new/v_new (rows q_stride floats apart), rotated, and stored into the cache by this kernel,
 // so no separate rope/append launch is needed.
-struct AttnFusion { const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; };
+struct AttnFusion { const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; L2Prefetch prefetch; };
 int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
                          const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
                          void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);

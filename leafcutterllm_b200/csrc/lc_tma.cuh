@@ -50,6 +50,7 @@ struct GemvParams {
     int n, k, m;
     int epi;
     int* error_flag;
+    L2Prefetch prefetch;
 };
 
 
@@ -75,5 +76,7 @@ constexpr size_t kMaxSmem = 227 * 1024;
 
 // qgemv_mma.cu: Q4_K through int8 tensor-core MMAs; *launched = false when the shape does not fit.
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
+// qgemv_umma.cu: Q4_K for one or two tokens through tcgen05.mma with accumulators in tensor memory.
+int32_t launch_qgemv_umma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
 
 }  // namespace lc

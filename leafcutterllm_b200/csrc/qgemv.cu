@@ -77,6 +77,13 @@ int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int 
                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         w->has_tmap = (r == CUDA_SUCCESS);
+        if (w->has_tmap) {
+            cuuint32_t wide[2] = {(cuuint32_t)(ub / 4), 128u};
+            r = encode_fn()((CUtensorMap*)w->tmap_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)data_dev, dims, strides, wide,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            w->has_tmap = (r == CUDA_SUCCESS);
+        }
     }
     return LC_OK;
 }
@@ -533,6 +540,14 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
     if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual, LC_ERR_INVALID, "qgemv: residual missing");
     bool tma_ok = a.w->has_tmap && (a.epi != EPI_SILU_MUL || a.w2->has_tmap);
     static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
+    // The tcgen05 kernel (qgemv_umma.cu) is opt-in: inside a decode step it ties with the mma.sync kernel on the large
+    // matrices and loses on the small one (its split-tile merge and longer prologue cost more than its leaner loop saves).
+    static const bool use_umma = getenv("LC_GEMV_UMMA") != nullptr;
+    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32 && use_umma && a.m <= 2) {
+        bool launched = false;
+        LC_TRY(launch_qgemv_umma_q4k(a, s, &launched));
+        if (launched) return LC_OK;
+    }
     if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32) {
         bool launched = false;
         LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));

@@ -89,6 +89,10 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         for (int j = 0; j < STAGES && j < njobs; j++) issue_next();  // weights do not depend on the previous kernel
     }
+    if (threadIdx.x == 33) {  // a thread that issues no tile loads
+        l2_prefetch_part(p.prefetch.p[0], p.prefetch.bytes[0], blockIdx.x, gridDim.x);
+        l2_prefetch_part(p.prefetch.p[1], p.prefetch.bytes[1], blockIdx.x, gridDim.x);
+    }
     pdl_launch_dependents();
     pdl_wait();
 
@@ -359,6 +363,7 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
+    p.prefetch = a.prefetch;
     int ntiles = (p.n + kTileRows - 1) / kTileRows;
     // CTAs per SM that fit shared memory (and, for the 8-warp shape, registers): with two per SM the
     // first CTAs of the next kernel move in while the last CTAs of this one drain
