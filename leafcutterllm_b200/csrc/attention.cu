@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_staged_kernel(AttnP
         }
     };
     int pos;
-    if (fused) {  // the cache holds only earlier steps' tokens: fetch before waiting for the projection kernel
+    if (fused && p.positions_settled) {  // the cache holds only earlier steps' tokens: fetch before waiting for the projection kernel
         pos = p.tok_pos[tok];
         stage(pos);
         if (tid == 32) {
@@ -355,7 +355,9 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
     p.k_new = fuse ? fuse->k_new : nullptr; p.v_new = fuse ? fuse->v_new : nullptr;
     p.tok_rope = fuse ? fuse->tok_rope : nullptr; p.theta = fuse ? fuse->theta : 0.f;
     if (fuse) p.prefetch = fuse->prefetch;
+    p.positions_settled = (fuse && fuse->positions_settled) ? 1 : 0;
     p.error_flag = gemv_error_flag_dev();
+    if (fuse && attention_stream_applies(p, n_tok)) return launch_attention_stream(p, s);
     switch (kv.hd) {
         case 32: return launch_attention_hd<32>(p, n_tok, max_ctx, s);
         case 64: return launch_attention_hd<64>(p, n_tok, max_ctx, s);

@@ -1,0 +1,378 @@
+// Decode attention of ONE new token as a balanced stream over the paged f16 KV cache
+// (rust/src/inference/attention.rs:69-113, rust/src/cache/mod.rs:33-77; head_dim 128, 16-token pages).
+//
+// The unit of work is a (kv head, page) item: one 4 KB slab of keys and one of values.  The items of the token, in
+// (kv head, page) order, are cut into one contiguous run per CTA -- CTA c takes items [c*T/G, (c+1)*T/G) -- so every
+// SM streams the same number of bytes whatever the context length and head count, and there is a single wave.
+//
+//   producer  one thread requests the run's slabs with bulk copies into a ring of 8 KB stages (one mbarrier each),
+//             starting BEFORE the grid dependency wait: cached pages belong to earlier steps;
+//   consumers eight warps take the items round robin.  A warp scores the 16 keys of its page (two lanes per key, 16-byte
+//             chunks walked in a rotated order so a quarter warp never meets a bank twice), updates an online softmax
+//             per query head of the kv group and accumulates p.V with four dims per lane;
+//   new token the warp that owns the page holding this step's position rotates k, rounds k and v through f16 exactly
+//             as the cache does, patches its staged copy and stores the row into the cache;
+//   merge     per (kv head) segment the warps are combined in warp order, then the CTAs that share the segment in CTA
+//             order: every CTA but the segment's first publishes (max, sum, weighted V) as 64-bit words carrying a
+//             valid flag; the first one collects them, writes the head's output and leaves the slots cleared.
+//
+// The reference's three-pass softmax and this online form agree to rounding; sums are in a fixed order, so results
+// do not vary from run to run.
+#include <cstdlib>
+#include "lc_kernels.h"
+#include "lc_attn.cuh"
+#include "lc_tma.cuh"
+
+namespace lc {
+
+namespace {
+
+constexpr int kHD = 128;
+constexpr int kPage = 16;
+constexpr int kSlab = kPage * kHD * 2;       // bytes of one K (or V) slab
+constexpr int kStageBytes = 2 * kSlab;       // K then V
+constexpr int kCWarps = 8;                   // consumer warps
+constexpr int kMaxSeg = 3;                   // kv heads a CTA's run can touch (n_kv <= SM count)
+constexpr int kStateWords = 4 + kHD;         // max, sum, two pad words (16-byte alignment), weighted V
+
+struct StreamParams {
+    AttnParams a;
+    unsigned long long* slots;  // [q head][contributor][kStateWords] (f32 bits | valid << 32), zero between launches
+    int max_contrib;
+    int nstages;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+template <int GSZ>
+__global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel(StreamParams P) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    const AttnParams& p = P.a;
+    const KvLayout& kv = p.kv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = P.nstages;
+    unsigned char* ring = smem;                                             // [S][kStageBytes]
+    float* q_s = reinterpret_cast<float*>(ring + (size_t)S * kStageBytes);  // [kCWarps][GSZ][kHD] the warp's rotated queries
+    float* st_s = q_s + kCWarps * GSZ * kHD;                                // [kMaxSeg][kCWarps][GSZ][kStateWords]
+    float* cta_s = st_s + kMaxSeg * kCWarps * GSZ * kStateWords;            // [kMaxSeg][GSZ][kStateWords] combined over warps
+    uint64_t* full = reinterpret_cast<uint64_t*>(((uintptr_t)(cta_s + kMaxSeg * GSZ * kStateWords) + 7) & ~(uintptr_t)7);  // [S]
+    uint64_t* empty = full + S;                                             // [S]
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    if (!p.positions_settled) pdl_wait();  // the position itself may still be in flight
+
+    // the token's items: (kv head, page), kv head major
+    const int pos = p.tok_pos[0];
+    const int np = pos / kPage + 1;
+    const int T = kv.n_kv * np;
+    const int G = min((int)gridDim.x, T);  // CTAs that take part: each has at least one item
+    const bool active = (int)blockIdx.x < G;
+    const int i_begin = active ? (int)((long long)blockIdx.x * T / G) : 0;
+    const int i_end = active ? (int)((long long)(blockIdx.x + 1) * T / G) : 0;
+    const int n_items = i_end - i_begin;
+    const int seg0 = n_items > 0 ? i_begin / np : 0;  // first kv head of the run
+    const int32_t* pt = p.page_table + (size_t)p.tok_seq[0] * p.pages_per_seq;
+    bool ok = true;
+
+    if (warp == kCWarps) {
+        // ---- producer ----
+        if (lane == 0) {
+            int kvh = seg0, page = i_begin - seg0 * np;
+            for (int i = 0; i < n_items; i++) {
+                const int st = i % S;
+                if (i >= S) ok = mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1)) && ok;
+                const size_t src = ((size_t)pt[page] * kv.n_kv + kvh) * kPage * kHD;
+                mbar_expect_tx(&full[st], kStageBytes);
+                bulk_g2s(ring + (size_t)st * kStageBytes, (const __half*)kv.k_pool + src, kSlab, &full[st]);
+                bulk_g2s(ring + (size_t)st * kStageBytes + kSlab, (const __half*)kv.v_pool + src, kSlab, &full[st]);
+                if (++page == np) { page = 0; kvh++; }
+            }
+            if (!ok && p.error_flag) atomicExch(p.error_flag, 1);
+        }
+        return;  // the producer takes no part in the barriers below (they count the consumer threads)
+    }
+
+    // ---- consumers ----
+    pdl_wait();  // q and this step's k, v come from the projection kernel
+    const bool fused = p.k_new != nullptr;
+    const int rp = fused ? p.tok_rope[0] : 0;
+    const float inv_div = sqrtf((float)kHD);  // attention.rs:93: dot / sqrt(head_dim)
+    const int key = lane >> 1, half = lane & 1;  // scores: two lanes per key, 64 dims each
+
+    float m[GSZ], l[GSZ], acc[GSZ][4];
+    auto reset = [&]() {
+#pragma unroll
+        for (int g = 0; g < GSZ; g++) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
+    };
+    reset();
+    float* myq = q_s + (size_t)warp * GSZ * kHD;
+    int cur_seg = -1;
+    auto flush = [&](int seg) {  // this warp's state of kv head `seg` -> shared memory
+        float* dst = st_s + ((size_t)(seg - seg0) * kCWarps + warp) * GSZ * kStateWords;
+#pragma unroll
+        for (int g = 0; g < GSZ; g++) {
+            if (lane == 0) { dst[g * kStateWords] = m[g]; dst[g * kStateWords + 1] = l[g]; }
+            *reinterpret_cast<float4*>(dst + g * kStateWords + 4 + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        }
+    };
+    // every (segment, warp) slot starts empty: a warp may meet no item of a segment
+    for (int i = tid; i < kMaxSeg * kCWarps * GSZ; i += kCWarps * 32) {
+        st_s[(size_t)i * kStateWords] = -INFINITY;
+        st_s[(size_t)i * kStateWords + 1] = 0.f;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
+
+    for (int il = warp; il < n_items; il += kCWarps) {
+        const int gi = i_begin + il;
+        const int kvh = gi / np, page = gi - kvh * np;
+        if (kvh != cur_seg) {
+            if (cur_seg >= 0) flush(cur_seg);
+            reset();
+            cur_seg = kvh;
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < GSZ; g++) {  // rotated queries of the kv group (attention.rs:13-34)
+                float qv[4];
+                load_rotated<4, kHD>(p.q + (size_t)(kvh * GSZ + g) * kHD, 4 * lane, rp, p.theta, qv);
+                *reinterpret_cast<float4*>(myq + g * kHD + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            }
+            __syncwarp();
+        }
+        const int st = il % S;
+        ok = mbar_wait(&full[st], (uint32_t)((il / S) & 1)) && ok;
+        __half* K_s = reinterpret_cast<__half*>(ring + (size_t)st * kStageBytes);
+        __half* V_s = K_s + kPage * kHD;
+        int nvalid = kPage;
+        if (page == np - 1) {
+            nvalid = pos % kPage + 1;
+            if (fused) {
+                // this step's token replaces the stale staged row: rotate, round through f16 (cache/mod.rs:35-36), keep in the cache
+                const int r = pos % kPage;
+                float kr[4];
+                load_rotated<4, kHD>(p.k_new + (size_t)kvh * kHD, 4 * lane, rp, p.theta, kr);
+                const float4 vr = __ldcg(reinterpret_cast<const float4*>(p.v_new + (size_t)kvh * kHD + 4 * lane));
+                const __half2 k01 = __floats2half2_rn(kr[0], kr[1]), k23 = __floats2half2_rn(kr[2], kr[3]);
+                const __half2 v01 = __floats2half2_rn(vr.x, vr.y), v23 = __floats2half2_rn(vr.z, vr.w);
+                uint2 kw, vw;
+                kw.x = *reinterpret_cast<const uint32_t*>(&k01); kw.y = *reinterpret_cast<const uint32_t*>(&k23);
+                vw.x = *reinterpret_cast<const uint32_t*>(&v01); vw.y = *reinterpret_cast<const uint32_t*>(&v23);
+                *reinterpret_cast<uint2*>(K_s + r * kHD + 4 * lane) = kw;
+                *reinterpret_cast<uint2*>(V_s + r * kHD + 4 * lane) = vw;
+                const size_t dst = (((size_t)pt[page] * kv.n_kv + kvh) * kPage + r) * kHD + 4 * lane;
+                *reinterpret_cast<uint2*>((__half*)kv.k_pool + dst) = kw;
+                *reinterpret_cast<uint2*>((__half*)kv.v_pool + dst) = vw;
+                __syncwarp();
+            }
+        }
+        // ---- scores of the page's 16 keys ----
+        float d[GSZ];
+#pragma unroll
+        for (int g = 0; g < GSZ; g++) d[g] = 0.f;
+        const __half* krow = K_s + key * kHD + half * 64;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const int cc = (c + lane) & 7;  // rotated: the 8 lanes of a quarter warp read 8 different 16-byte bank groups
+            const uint4 kq = *reinterpret_cast<const uint4*>(krow + cc * 8);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&kq);
+            const float2 k0 = __half22float2(h2[0]), k1 = __half22float2(h2[1]), k2 = __half22float2(h2[2]), k3 = __half22float2(h2[3]);
+#pragma unroll
+            for (int g = 0; g < GSZ; g++) {
+                const float4 qa = *reinterpret_cast<const float4*>(myq + g * kHD + half * 64 + cc * 8);
+                const float4 qb = *reinterpret_cast<const float4*>(myq + g * kHD + half * 64 + cc * 8 + 4);
+                float s0 = d[g];
+                s0 = fmaf(qa.x, k0.x, s0); s0 = fmaf(qa.y, k0.y, s0); s0 = fmaf(qa.z, k1.x, s0); s0 = fmaf(qa.w, k1.y, s0);
+                s0 = fmaf(qb.x, k2.x, s0); s0 = fmaf(qb.y, k2.y, s0); s0 = fmaf(qb.z, k3.x, s0); s0 = fmaf(qb.w, k3.y, s0);
+                d[g] = s0;
+            }
+        }
+        float pk[GSZ];  // this lane's key: exp(score - max) (both lanes of a key hold it)
+#pragma unroll
+        for (int g = 0; g < GSZ; g++) {
+            float sc = d[g] + __shfl_xor_sync(0xffffffffu, d[g], 1);
+            sc = key < nvalid ? sc / inv_div : -INFINITY;
+            float mx = sc;
+#pragma unroll
+            for (int o = 16; o > 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(m[g], mx);   // finite: key 0 of every page is valid
+            const float corr = expf(m[g] - m_new);
+            const float pe = expf(sc - m_new);
+            float ps = half == 0 ? pe : 0.f;       // each key once
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+            l[g] = l[g] * corr + ps;
+            m[g] = m_new;
+            pk[g] = pe;
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[g][i] *= corr;
+        }
+        // ---- p.V: four dims per lane ----
+#pragma unroll
+        for (int j = 0; j < kPage; j++) {
+            if (j >= nvalid) break;  // rows past this step's position hold whatever the pool held before: 0 * Inf would poison the sum
+            const uint2 vq = *reinterpret_cast<const uint2*>(V_s + j * kHD + 4 * lane);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&vq);
+            const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]);
+#pragma unroll
+            for (int g = 0; g < GSZ; g++) {
+                const float pj = __shfl_sync(0xffffffffu, pk[g], 2 * j);
+                acc[g][0] = fmaf(pj, v0.x, acc[g][0]); acc[g][1] = fmaf(pj, v0.y, acc[g][1]);
+                acc[g][2] = fmaf(pj, v1.x, acc[g][2]); acc[g][3] = fmaf(pj, v1.y, acc[g][3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && il + S < n_items) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
+    }
+    if (cur_seg >= 0) flush(cur_seg);
+    asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
+
+    // ---- per (kv head, query head): the warps in warp order, then the CTAs that share the kv head in CTA order ----
+    const int nseg = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
+    const int hf = tid >> 7, dx = tid & 127;  // two (segment, query head) pairs at a time, one thread per dim
+    for (int w = hf; w < nseg * GSZ; w += 2) {
+        const int sl = w / GSZ, g = w - sl * GSZ;
+        const float* ws = st_s + ((size_t)sl * kCWarps * GSZ + g) * kStateWords;  // warp 0's state; warp stride GSZ * kStateWords
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kCWarps; i++) M = fmaxf(M, ws[(size_t)i * GSZ * kStateWords]);
+        float L = 0.f, A = 0.f;
+#pragma unroll
+        for (int i = 0; i < kCWarps; i++) {
+            const float mi = ws[(size_t)i * GSZ * kStateWords];
+            if (mi == -INFINITY) continue;  // the warp met no key of this head
+            const float e = expf(mi - M);
+            L += ws[(size_t)i * GSZ * kStateWords + 1] * e;
+            A += ws[(size_t)i * GSZ * kStateWords + 4 + dx] * e;
+        }
+        const int seg = seg0 + sl, head = seg * GSZ + g;
+        const long long first = (long long)seg * np, last = first + np - 1;
+        const int c_first = (int)(((first + 1) * G - 1) / T), c_last = (int)(((last + 1) * G - 1) / T);
+        const int nc = c_last - c_first + 1, me = (int)blockIdx.x - c_first;
+        unsigned long long* sl_base = P.slots + (size_t)head * P.max_contrib * (2 + kHD);
+        auto put = [](unsigned long long* a, float v) {
+            const unsigned long long wv = (1ull << 32) | (unsigned long long)__float_as_uint(v);
+            asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
+        };
+        auto take = [&](const unsigned long long* a) {  // bounded poll for a valid word
+            unsigned long long wv = 0;
+            bool got = false;
+            for (uint32_t it = 0; it < (1u << 20) && !got; ++it) {
+                asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv) : "l"(a) : "memory");
+                got = (wv >> 32) == 1ull;
+            }
+            ok = ok && got;
+            return __uint_as_float((uint32_t)wv);
+        };
+        if (nc > 1 && me != 0) {
+            unsigned long long* mine = sl_base + (size_t)me * (2 + kHD);
+            if (dx == 0) { put(mine, M); put(mine + 1, L); }
+            put(mine + 2 + dx, A);
+        } else {
+            for (int c = 1; c < nc; c++) {  // the head's first CTA collects the others in CTA order
+                unsigned long long* theirs = sl_base + (size_t)c * (2 + kHD);
+                const float Mc = take(theirs), Lc = take(theirs + 1), Ac = take(theirs + 2 + dx);
+                const float Mn = fmaxf(M, Mc);
+                const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);
+                A = A * e0 + Ac * e1;
+                L = L * e0 + Lc * e1;
+                M = Mn;
+                asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(theirs + 2 + dx), "l"(0ull) : "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read max and sum
+                if (dx == 0) {
+                    asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(theirs), "l"(0ull) : "memory");
+                    asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(theirs + 1), "l"(0ull) : "memory");
+                }
+            }
+            p.out[(size_t)head * kHD + dx] = A / L;
+        }
+    }
+    if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
+struct StreamScratch { DevBuf slots; };
+StreamScratch g_stream[16];
+
+int stream_max_contrib(int n_kv) { return sm_count() / n_kv + 3; }
+
+template <int GSZ>
+size_t stream_fixed_smem() {
+    return 128 + (size_t)kCWarps * GSZ * kHD * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
+           (size_t)kMaxSeg * GSZ * kStateWords * 4 + 16;
+}
+
+template <int GSZ>
+int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
+    int dev = 0;
+    LC_CUDA(cudaGetDevice(&dev));
+    LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
+    StreamParams P;
+    P.a = a;
+    P.max_contrib = stream_max_contrib(a.kv.n_kv);
+    const size_t need = (size_t)a.n_heads * P.max_contrib * (2 + kHD) * sizeof(unsigned long long);
+    StreamScratch& sc = g_stream[dev];
+    if (sc.slots.cap < need) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        LC_CUDA(cudaStreamIsCapturing(s, &cs));
+        LC_CHECK(cs == cudaStreamCaptureStatusNone, LC_ERR_STATE,
+                 "attention: the merge slots must be reserved (attention_stream_reserve) before a stream capture");
+        LC_TRY(attention_stream_reserve(a.n_heads, a.kv.n_kv));
+    }
+    P.slots = (unsigned long long*)sc.slots.p;
+    const size_t fixed = stream_fixed_smem<GSZ>();
+    int stages = (int)((kMaxSmem - fixed) / (kStageBytes + 16));
+    if (stages > 26) stages = 26;
+    P.nstages = stages;
+    const size_t smem = fixed + (size_t)stages * (kStageBytes + 16);
+    auto kern = attention_stream_kernel<GSZ>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+        attr_set = true;
+    }
+    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((kCWarps + 1) * 32), smem, s, P));
+    return LC_OK;
+}
+
+}  // namespace
+
+int32_t attention_stream_reserve(int n_heads, int n_kv) {
+    if (n_kv <= 0 || n_kv > sm_count()) return LC_OK;
+    int dev = 0;
+    LC_CUDA(cudaGetDevice(&dev));
+    LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
+    const size_t need = (size_t)n_heads * stream_max_contrib(n_kv) * (2 + kHD) * sizeof(unsigned long long);
+    StreamScratch& sc = g_stream[dev];
+    if (sc.slots.cap >= need) return LC_OK;
+    LC_CUDA(cudaStreamSynchronize(stream()));
+    LC_TRY(sc.slots.reserve(need));
+    LC_CUDA(cudaMemset(sc.slots.p, 0, sc.slots.cap));  // every word invalid; the kernel leaves them so
+    return LC_OK;
+}
+
+bool attention_stream_applies(const AttnParams& a, int n_tok) {
+    static const bool off = getenv("LC_ATTN_NO_STREAM") != nullptr;
+    const int gsz = a.kv.n_kv > 0 ? a.n_heads / a.kv.n_kv : 0;
+    return !off && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
+           (gsz == 1 || gsz == 2 || gsz == 4 || gsz == 8);
+}
+
+int32_t launch_attention_stream(const AttnParams& a, cudaStream_t s) {
+    switch (a.n_heads / a.kv.n_kv) {
+        case 1: return launch_stream<1>(a, s);
+        case 2: return launch_stream<2>(a, s);
+        case 4: return launch_stream<4>(a, s);
+        default: return launch_stream<8>(a, s);
+    }
+}
+
+}  // namespace lc

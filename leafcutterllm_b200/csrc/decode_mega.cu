@@ -420,8 +420,11 @@ __device__ __noinline__ void mega_attention(const AttnParams& p, int head, int s
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 const int t2 = t_begin + kk + u;
-                const float pk = (kk + u < k1) ? p_s[kk + u] : 0.f;
-                const float2 val = (t2 == pos) ? vnew : vv[u];
+                const bool live = kk + u < k1;
+                const float pk = live ? p_s[kk + u] : 0.f;
+                // a padding entry re-read the slice's last slot, which may be the new token's still unwritten row:
+                // whatever bytes it holds (Inf, NaN) must not meet the zero weight
+                const float2 val = (t2 == pos) ? vnew : (live ? vv[u] : make_float2(0.f, 0.f));
                 ax = fmaf(pk, val.x, ax);
                 ay = fmaf(pk, val.y, ay);
             }

@@ -307,6 +307,7 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
         // one new token per sequence: rotation and the cache append ride inside the attention kernel
         AttnFusion fz{k, v, m->d_tok_rope, m->cfg.rope_theta};
         fz.prefetch = prefetch_for(m, l, 1);
+        fz.positions_settled = l > 0;  // the first layer of a step may run while the previous step still advances the positions
         LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
                                 m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, &fz, m->stream));
         m->launches_in_call += 1;
@@ -483,7 +484,7 @@ static int32_t setup_mega(lc_model* m) {
     if ((size_t)m->nh * a.n_splits * (m->hd + 2) * sizeof(float) > m->attn_scratch_bytes) return LC_OK;
     a.partial = (float*)m->d_attn_scratch; a.counters = m->d_attn_counters;
     a.k_new = m->d_qkv + (size_t)m->nh * m->hd; a.v_new = a.k_new + (size_t)m->nkv * m->hd; a.tok_rope = m->d_tok_rope;
-    a.theta = m->cfg.rope_theta; a.error_flag = gemv_error_flag_dev();
+    a.theta = m->cfg.rope_theta; a.error_flag = gemv_error_flag_dev(); a.positions_settled = 0;
     P.k_pools = d_kp; P.v_pools = d_vp;
     P.embed = (const uint8_t*)m->embed->view; P.embed_typ = m->embed->typ; P.embed_rows = (int64_t)m->embed->rows;
     P.tokens = m->d_tokens; P.hidden = m->d_hidden; P.logits = m->d_logits; P.V = m->V; P.next = m->d_next;
@@ -699,6 +700,7 @@ int32_t lc_model_finalize(lc_model* m) {
     std::string head = m->tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
     LC_TRY(weight_of(m, head, V, H, &m->head, nullptr));
 
+    LC_TRY(attention_stream_reserve(m->nh, m->nkv));
     // scratch of the split-tile GEMV, so that no launch inside a captured decode step allocates
     if (m->L > 0) {
         const LayerW& w0 = m->layers[0];

@@ -28,9 +28,14 @@ struct AttnParams {
     const float* v_new;
     const int32_t* tok_rope;
     float theta;
+    int positions_settled; // decode-step fusion: tok_pos may be read before the grid dependency wait
     int* error_flag;       // set when a bounded wait runs out (may be null)
     L2Prefetch prefetch;   // weights of the kernels that follow, pulled into L2 by the staged kernel
 };
+
+// attention_stream.cu: one new token, head_dim 128, f16 cache of 16-token pages, as a balanced single-wave stream
+bool attention_stream_applies(const AttnParams& a, int n_tok);
+int32_t launch_attention_stream(const AttnParams& a, cudaStream_t s);
 
 template <int DPL, bool F32>
 __device__ __forceinline__ void load_slice(const void* pool, size_t elem_off, float (&out)[DPL]) {

@@ -98,11 +98,17 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx);
 // fuse (decode steps only, every token the single new token of its sequence): q is rotated on load and the new
 // key/value are taken from k_new/v_new (rows q_stride floats apart), rotated, and stored into the cache by this kernel,
 // so no separate rope/append launch is needed.
-struct AttnFusion { const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; L2Prefetch prefetch; };
+// positions_settled: tok_pos was final before the kernel ahead of this one started (true from the second layer of a
+// step on; false for the first layer, whose positions the end of the previous step may still be writing), so the
+// kernel may read it, and start fetching cached pages, before it waits for the kernel ahead of it.
+struct AttnFusion { const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; L2Prefetch prefetch; bool positions_settled = false; };
 int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
                          const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
                          void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);
 int attention_launch_count(int n_tok, int n_heads, int max_ctx);
+// Reserves (and clears) the cross-CTA merge slots of the single-token streaming kernel so that no launch inside a
+// stream capture allocates.
+int32_t attention_stream_reserve(int n_heads, int n_kv);
 
 // ---- synth.cu ----
 int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_elems, void* out_dev,

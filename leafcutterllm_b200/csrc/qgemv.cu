@@ -542,7 +542,7 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
     static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
     // The tcgen05 kernel (qgemv_umma.cu) is opt-in: inside a decode step it ties with the mma.sync kernel on the large
     // matrices and loses on the small one (its split-tile merge and longer prologue cost more than its leaner loop saves).
-    static const bool use_umma = getenv("LC_GEMV_UMMA") != nullptr;
+    const bool use_umma = getenv("LC_GEMV_UMMA") != nullptr;  // read per call so that a test can switch it
     if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32 && use_umma && a.m <= 2) {
         bool launched = false;
         LC_TRY(launch_qgemv_umma_q4k(a, s, &launched));

@@ -156,3 +156,31 @@ def test_persistent_decode_kernel(gpu, oracle, monkeypatch, layers, heads, kv):
     assert eng2.generate(prompt, 48, stop_on_eos=False) == ref
     assert eng2.counters()["kernel_launches"] > launches  # the persistent path really was a different path
     eng2.close()
+
+
+@pytest.mark.parametrize("mega", [False, True])
+def test_decode_ignores_unwritten_cache_rows(gpu, oracle, monkeypatch, mega):
+    """The rows of a KV page beyond the current position hold whatever the pool's memory held before (the pools are
+    not cleared).  Their softmax weight is zero, but 0 * NaN is NaN: kernels must not touch them.  Device memory is
+    poisoned with f16 NaNs and released just before the model is built, and decoding crosses page boundaries."""
+    import ctypes as C
+    from leafcutterllm_b200 import synth, _capi
+    lib = _capi.load()
+    bufs = []
+    poison = np.full(64 << 20, 0xFF, np.uint8)
+    for _ in range(6):
+        p = C.c_void_p()
+        _capi.check(lib.lc_dev_alloc(poison.nbytes, C.byref(p)))
+        _capi.check(lib.lc_dev_upload(p, poison.ctypes.data_as(C.c_void_p), poison.nbytes))
+        bufs.append(p)
+    for p in bufs:
+        lib.lc_dev_free(p)
+    if mega:
+        monkeypatch.setenv("LC_MEGA", "1")
+    spec = small_spec(12, 12, 12, layers=2, hidden=256, heads=2, kv=2, ffn=768, vocab=1500)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=160)
+    prompt = synth.prompt_tokens(30, spec.vocab_size, 9)
+    ref, margins = om.generate(prompt, 40, stop_on_eos=False, want_margins=True)
+    toks = eng.generate(prompt, 40, stop_on_eos=False)
+    assert toks == ref, margins
+    eng.close()
