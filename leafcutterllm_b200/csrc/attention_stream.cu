@@ -18,6 +18,7 @@
 //
 // The reference's three-pass softmax and this online form agree to rounding; sums are in a fixed order, so results
 // do not vary from run to run.
+#include <cstdio>
 #include <cstdlib>
 #include "lc_kernels.h"
 #include "lc_attn.cuh"
@@ -31,7 +32,6 @@ constexpr int kHD = 128;
 constexpr int kPage = 16;
 constexpr int kSlab = kPage * kHD * 2;       // bytes of one K (or V) slab
 constexpr int kStageBytes = 2 * kSlab;       // K then V
-constexpr int kCWarps = 8;                   // consumer warps
 constexpr int kMaxSeg = 3;                   // kv heads a CTA's run can touch (n_kv <= SM count)
 constexpr int kStateWords = 4 + kHD;         // max, sum, two pad words (16-byte alignment), weighted V
 
@@ -40,6 +40,8 @@ struct StreamParams {
     unsigned long long* slots;  // [q head][contributor][kStateWords] (f32 bits | valid << 32), zero between launches
     int max_contrib;
     int nstages;
+    unsigned long long* ring;  // diagnostics (LC_ATTN_RING): [launch slot][8] wall-clock stamps, or null
+    int ring_slot;
 };
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -48,8 +50,14 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  : "memory");
 }
 
+// Consumer warps: the per-page work is a chain of dependent shared-memory loads, shuffles and FMAs, so throughput comes
+// from the number of warps in flight -- sixteen where the per-warp state of the kv group fits, eight for wide groups.
 template <int GSZ>
-__global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel(StreamParams P) {
+__host__ __device__ constexpr int consumer_warps() { return GSZ <= 2 ? 16 : 8; }
+
+template <int GSZ>
+__global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention_stream_kernel(StreamParams P) {
+    constexpr int kCWarps = consumer_warps<GSZ>();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
     const AttnParams& p = P.a;
@@ -63,6 +71,9 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
     uint64_t* full = reinterpret_cast<uint64_t*>(((uintptr_t)(cta_s + kMaxSeg * GSZ * kStateWords) + 7) & ~(uintptr_t)7);  // [S]
     uint64_t* empty = full + S;                                             // [S]
 
+    auto gtime = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+    unsigned long long* rg = (P.ring && tid == 0) ? P.ring + (size_t)P.ring_slot * 16 : nullptr;
+    if (rg) { atomicMax(rg + 7, gtime()); if (blockIdx.x == 0) rg[0] = gtime(); else rg = nullptr; }
     if (tid == 0) {
         for (int s = 0; s < S; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -86,25 +97,26 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
     bool ok = true;
 
     if (warp == kCWarps) {
-        // ---- producer ----
-        if (lane == 0) {
-            int kvh = seg0, page = i_begin - seg0 * np;
-            for (int i = 0; i < n_items; i++) {
-                const int st = i % S;
-                if (i >= S) ok = mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1)) && ok;
-                const size_t src = ((size_t)pt[page] * kv.n_kv + kvh) * kPage * kHD;
-                mbar_expect_tx(&full[st], kStageBytes);
-                bulk_g2s(ring + (size_t)st * kStageBytes, (const __half*)kv.k_pool + src, kSlab, &full[st]);
-                bulk_g2s(ring + (size_t)st * kStageBytes + kSlab, (const __half*)kv.v_pool + src, kSlab, &full[st]);
-                if (++page == np) { page = 0; kvh++; }
-            }
-            if (!ok && p.error_flag) atomicExch(p.error_flag, 1);
+        // ---- producer: lane i requests items i, i + 32, ... -- each needs a page-table entry from global memory, and one
+        //      thread walking them one after the other made that latency, not HBM, the pace of the whole kernel ----
+        for (int i = lane; i < n_items; i += 32) {
+            const int gi = i_begin + i;
+            const int kvh = gi / np, page = gi - kvh * np;
+            const int pg = pt[page];
+            const int st = i % S;
+            if (i >= S) ok = mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1)) && ok;
+            const size_t src = ((size_t)pg * kv.n_kv + kvh) * kPage * kHD;
+            mbar_expect_tx(&full[st], kStageBytes);
+            bulk_g2s(ring + (size_t)st * kStageBytes, (const __half*)kv.k_pool + src, kSlab, &full[st]);
+            bulk_g2s(ring + (size_t)st * kStageBytes + kSlab, (const __half*)kv.v_pool + src, kSlab, &full[st]);
         }
+        if (!ok && p.error_flag) atomicExch(p.error_flag, 1);
         return;  // the producer takes no part in the barriers below (they count the consumer threads)
     }
 
     // ---- consumers ----
     pdl_wait();  // q and this step's k, v come from the projection kernel
+    if (rg) rg[1] = gtime();
     const bool fused = p.k_new != nullptr;
     const int rp = fused ? p.tok_rope[0] : 0;
     const float inv_div = sqrtf((float)kHD);  // attention.rs:93: dot / sqrt(head_dim)
@@ -118,6 +130,8 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
     reset();
     float* myq = q_s + (size_t)warp * GSZ * kHD;
     int cur_seg = -1;
+    long long wait_cycles = 0;
+    const long long loop0 = clock64();
     auto flush = [&](int seg) {  // this warp's state of kv head `seg` -> shared memory
         float* dst = st_s + ((size_t)(seg - seg0) * kCWarps + warp) * GSZ * kStateWords;
 #pragma unroll
@@ -149,8 +163,12 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
             }
             __syncwarp();
         }
+        if (rg && il == warp) rg[8] = clock64() - loop0;
         const int st = il % S;
+        const long long tw0 = clock64();
         ok = mbar_wait(&full[st], (uint32_t)((il / S) & 1)) && ok;
+        wait_cycles += clock64() - tw0;
+        if (rg && il == warp) rg[9] = clock64() - loop0;
         __half* K_s = reinterpret_cast<__half*>(ring + (size_t)st * kStageBytes);
         __half* V_s = K_s + kPage * kHD;
         int nvalid = kPage;
@@ -176,9 +194,9 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
             }
         }
         // ---- scores of the page's 16 keys ----
-        float d[GSZ];
+        float d[GSZ], d2[GSZ];  // two chains per head: even and odd chunks
 #pragma unroll
-        for (int g = 0; g < GSZ; g++) d[g] = 0.f;
+        for (int g = 0; g < GSZ; g++) d[g] = d2[g] = 0.f;
         const __half* krow = K_s + key * kHD + half * 64;
 #pragma unroll
         for (int c = 0; c < 8; c++) {
@@ -190,16 +208,18 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
             for (int g = 0; g < GSZ; g++) {
                 const float4 qa = *reinterpret_cast<const float4*>(myq + g * kHD + half * 64 + cc * 8);
                 const float4 qb = *reinterpret_cast<const float4*>(myq + g * kHD + half * 64 + cc * 8 + 4);
-                float s0 = d[g];
-                s0 = fmaf(qa.x, k0.x, s0); s0 = fmaf(qa.y, k0.y, s0); s0 = fmaf(qa.z, k1.x, s0); s0 = fmaf(qa.w, k1.y, s0);
-                s0 = fmaf(qb.x, k2.x, s0); s0 = fmaf(qb.y, k2.y, s0); s0 = fmaf(qb.z, k3.x, s0); s0 = fmaf(qb.w, k3.y, s0);
-                d[g] = s0;
+                float s0 = (c & 1) ? d2[g] : d[g], s1 = 0.f;
+                s0 = fmaf(qa.x, k0.x, s0); s1 = fmaf(qa.y, k0.y, s1); s0 = fmaf(qa.z, k1.x, s0); s1 = fmaf(qa.w, k1.y, s1);
+                s0 = fmaf(qb.x, k2.x, s0); s1 = fmaf(qb.y, k2.y, s1); s0 = fmaf(qb.z, k3.x, s0); s1 = fmaf(qb.w, k3.y, s1);
+                if (c & 1) d2[g] = s0 + s1; else d[g] = s0 + s1;
             }
         }
+        if (rg && il == warp) rg[10] = clock64() - loop0;
         float pk[GSZ];  // this lane's key: exp(score - max) (both lanes of a key hold it)
 #pragma unroll
         for (int g = 0; g < GSZ; g++) {
-            float sc = d[g] + __shfl_xor_sync(0xffffffffu, d[g], 1);
+            const float dg = d[g] + d2[g];
+            float sc = dg + __shfl_xor_sync(0xffffffffu, dg, 1);
             sc = key < nvalid ? sc / inv_div : -INFINITY;
             float mx = sc;
 #pragma unroll
@@ -216,11 +236,14 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
 #pragma unroll
             for (int i = 0; i < 4; i++) acc[g][i] *= corr;
         }
+        if (rg && il == warp) rg[11] = clock64() - loop0;
         // ---- p.V: four dims per lane ----
 #pragma unroll
         for (int j = 0; j < kPage; j++) {
-            if (j >= nvalid) break;  // rows past this step's position hold whatever the pool held before: 0 * Inf would poison the sum
-            const uint2 vq = *reinterpret_cast<const uint2*>(V_s + j * kHD + 4 * lane);
+            uint2 vq = *reinterpret_cast<const uint2*>(V_s + j * kHD + 4 * lane);
+            // rows past this step's position hold whatever the pool held before (Inf, NaN): their zero weight must
+            // meet zeros, not those bytes
+            if (j >= nvalid) vq = make_uint2(0u, 0u);
             const __half2* h2 = reinterpret_cast<const __half2*>(&vq);
             const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]);
 #pragma unroll
@@ -231,15 +254,19 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
             }
         }
         __syncwarp();
+        if (rg && il == warp) rg[12] = clock64() - loop0;
+        if (rg && il == warp + kCWarps) rg[13] = clock64() - loop0;
         if (lane == 0 && il + S < n_items) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
     }
     if (cur_seg >= 0) flush(cur_seg);
+    if (rg) { rg[2] = gtime(); rg[5] = ((unsigned long long)wait_cycles << 32) | (unsigned long long)(unsigned)(clock64() - loop0); }
     asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
+    if (rg) rg[3] = gtime();
 
     // ---- per (kv head, query head): the warps in warp order, then the CTAs that share the kv head in CTA order ----
     const int nseg = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
-    const int hf = tid >> 7, dx = tid & 127;  // two (segment, query head) pairs at a time, one thread per dim
-    for (int w = hf; w < nseg * GSZ; w += 2) {
+    const int hf = tid >> 7, dx = tid & 127;  // kCWarps / 4 (segment, query head) pairs at a time, one thread per dim
+    for (int w = hf; w < nseg * GSZ; w += kCWarps / 4) {
         const int sl = w / GSZ, g = w - sl * GSZ;
         const float* ws = st_s + ((size_t)sl * kCWarps * GSZ + g) * kStateWords;  // warp 0's state; warp stride GSZ * kStateWords
         float M = -INFINITY;
@@ -263,40 +290,70 @@ __global__ void __launch_bounds__((kCWarps + 1) * 32, 1) attention_stream_kernel
             const unsigned long long wv = (1ull << 32) | (unsigned long long)__float_as_uint(v);
             asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
         };
-        auto take = [&](const unsigned long long* a) {  // bounded poll for a valid word
-            unsigned long long wv = 0;
-            bool got = false;
-            for (uint32_t it = 0; it < (1u << 20) && !got; ++it) {
-                asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv) : "l"(a) : "memory");
-                got = (wv >> 32) == 1ull;
-            }
-            ok = ok && got;
-            return __uint_as_float((uint32_t)wv);
-        };
         if (nc > 1 && me != 0) {
             unsigned long long* mine = sl_base + (size_t)me * (2 + kHD);
             if (dx == 0) { put(mine, M); put(mine + 1, L); }
             put(mine + 2 + dx, A);
         } else {
-            for (int c = 1; c < nc; c++) {  // the head's first CTA collects the others in CTA order
-                unsigned long long* theirs = sl_base + (size_t)c * (2 + kHD);
-                const float Mc = take(theirs), Lc = take(theirs + 1), Ac = take(theirs + 2 + dx);
-                const float Mn = fmaxf(M, Mc);
-                const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);
-                A = A * e0 + Ac * e1;
-                L = L * e0 + Lc * e1;
-                M = Mn;
-                asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(theirs + 2 + dx), "l"(0ull) : "memory");
-                asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read max and sum
-                if (dx == 0) {
-                    asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(theirs), "l"(0ull) : "memory");
-                    asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(theirs + 1), "l"(0ull) : "memory");
+            // the head's first CTA collects the others in CTA order; the three words of up to four contributors are
+            // requested together so that one memory round trip serves them all
+            for (int c0 = 1; c0 < nc; c0 += 4) {
+                unsigned long long wv[4][3];
+                bool all = false;
+                for (uint32_t it = 0; it < (1u << 20) && !all; ++it) {  // bounded: poll the whole batch until every word is valid
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const unsigned long long* theirs = sl_base + (size_t)min(c0 + u, nc - 1) * (2 + kHD);
+                        asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][0]) : "l"(theirs) : "memory");
+                        asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][1]) : "l"(theirs + 1) : "memory");
+                        asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][2]) : "l"(theirs + 2 + dx) : "memory");
+                    }
+                    all = true;
+#pragma unroll
+                    for (int u = 0; u < 4; u++) all = all && (wv[u][0] >> 32) == 1ull && (wv[u][1] >> 32) == 1ull && (wv[u][2] >> 32) == 1ull;
                 }
+                ok = ok && all;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (c0 + u >= nc) break;
+                    const float Mc = __uint_as_float((uint32_t)wv[u][0]), Lc = __uint_as_float((uint32_t)wv[u][1]);
+                    const float Ac = __uint_as_float((uint32_t)wv[u][2]);
+                    const float Mn = fmaxf(M, Mc);
+                    const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);
+                    A = A * e0 + Ac * e1;
+                    L = L * e0 + Lc * e1;
+                    M = Mn;
+                }
+            }
+            if (nc > 1) {
+                for (int c = 1; c < nc; c++)
+                    asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + 2 + dx), "l"(0ull) : "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read the maxima and sums
+                if (dx < 2)
+                    for (int c = 1; c < nc; c++)
+                        asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + dx), "l"(0ull) : "memory");
             }
             p.out[(size_t)head * kHD + dx] = A / L;
         }
     }
+    if (rg) rg[4] = gtime();
+    if (P.ring && tid == 0) atomicMax(P.ring + (size_t)P.ring_slot * 16 + 6, gtime());
     if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
+unsigned long long* g_aring = nullptr;
+void dump_aring() {
+    static unsigned long long h[256 * 16];
+    if (!g_aring || cudaMemcpy(h, g_aring, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return;
+    fprintf(stderr, "[attn ring] per launch slot (ns from CTA 0's start): last cta start | wait done, warp 0 items done, all warps done, cta0 end | last cta end\n");
+    for (int i = 0; i < 256; i++) {
+        const unsigned long long* r = h + (size_t)i * 16;
+        if (!r[0]) continue;
+        fprintf(stderr, "  %4d | %7lld | %7lld %7lld %7lld %7lld | %7lld | warp 0: %llu cycles waiting for data of %llu in its loop\n", i, (long long)(r[7] - r[0]),
+                (long long)(r[1] - r[0]), (long long)(r[2] - r[0]), (long long)(r[3] - r[0]), (long long)(r[4] - r[0]), (long long)(r[6] - r[0]), r[5] >> 32,
+                r[5] & 0xffffffffull);
+        fprintf(stderr, "        warp 0 cycles from loop start: q %llu | item0: data %llu scores %llu softmax %llu pv %llu | item1 end %llu\n", r[8], r[9], r[10], r[11], r[12], r[13]);
+    }
 }
 
 struct StreamScratch { DevBuf slots; };
@@ -306,6 +363,7 @@ int stream_max_contrib(int n_kv) { return sm_count() / n_kv + 3; }
 
 template <int GSZ>
 size_t stream_fixed_smem() {
+    constexpr int kCWarps = consumer_warps<GSZ>();
     return 128 + (size_t)kCWarps * GSZ * kHD * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
            (size_t)kMaxSeg * GSZ * kStateWords * 4 + 16;
 }
@@ -328,6 +386,9 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
         LC_TRY(attention_stream_reserve(a.n_heads, a.kv.n_kv));
     }
     P.slots = (unsigned long long*)sc.slots.p;
+    static int ring_seq = 0;
+    P.ring = g_aring;
+    P.ring_slot = ring_seq++ % 256;
     const size_t fixed = stream_fixed_smem<GSZ>();
     int stages = (int)((kMaxSmem - fixed) / (kStageBytes + 16));
     if (stages > 26) stages = 26;
@@ -339,7 +400,7 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
         LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
         attr_set = true;
     }
-    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((kCWarps + 1) * 32), smem, s, P));
+    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((consumer_warps<GSZ>() + 1) * 32), smem, s, P));
     return LC_OK;
 }
 
@@ -356,6 +417,11 @@ int32_t attention_stream_reserve(int n_heads, int n_kv) {
     LC_CUDA(cudaStreamSynchronize(stream()));
     LC_TRY(sc.slots.reserve(need));
     LC_CUDA(cudaMemset(sc.slots.p, 0, sc.slots.cap));  // every word invalid; the kernel leaves them so
+    if (!g_aring && getenv("LC_ATTN_RING")) {
+        LC_CUDA(cudaMalloc(&g_aring, 256 * 16 * sizeof(unsigned long long)));
+        LC_CUDA(cudaMemset(g_aring, 0, 256 * 16 * sizeof(unsigned long long)));
+        atexit(dump_aring);
+    }
     return LC_OK;
 }
 
