@@ -356,6 +356,11 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
     p.tok_rope = fuse ? fuse->tok_rope : nullptr; p.theta = fuse ? fuse->theta : 0.f;
     if (fuse) p.prefetch = fuse->prefetch;
     p.positions_settled = (fuse && fuse->positions_settled) ? 1 : 0;
+    if (fuse && fuse->qkv_flag) {
+        p.qkvf = fuse->qkv_flag; p.outf = fuse->out_flag; p.step_ctr = fuse->step_ctr; p.node_in = fuse->node_in; p.node_out = fuse->node_out;
+        LC_CHECK(attention_stream_applies(p, n_tok) && p.outf && p.step_ctr, LC_ERR_UNSUPPORTED,
+                 "attention: flagged activations are only implemented by the single-token streaming kernel");
+    }
     p.error_flag = gemv_error_flag_dev();
     if (fuse && attention_stream_applies(p, n_tok)) return launch_attention_stream(p, s);
     switch (kv.hd) {

@@ -51,11 +51,12 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 }
 
 // Consumer warps: the per-page work is a chain of dependent shared-memory loads, shuffles and FMAs, so throughput comes
-// from the number of warps in flight -- sixteen where the per-warp state of the kv group fits, eight for wide groups.
+// from the number of warps in flight -- fifteen where the per-warp state of the kv group fits (with the producer warp
+// a CTA of 512 threads, which leaves each thread 128 registers), seven for wide groups.
 template <int GSZ>
-__host__ __device__ constexpr int consumer_warps() { return GSZ <= 2 ? 16 : 8; }
+__host__ __device__ constexpr int consumer_warps() { return GSZ <= 2 ? 15 : 7; }
 
-template <int GSZ>
+template <int GSZ, bool FLAGGED>
 __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention_stream_kernel(StreamParams P) {
     constexpr int kCWarps = consumer_warps<GSZ>();
     extern __shared__ unsigned char smem_raw[];
@@ -81,7 +82,16 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
     }
     __syncthreads();
     pdl_launch_dependents();
-    if (!p.positions_settled) pdl_wait();  // the position itself may still be in flight
+    // Dataflow mode: the projection row arrives as flagged words, so nothing here waits for the grid ahead; the step's
+    // position was final before the step's first kernel started.
+    constexpr bool flagged = FLAGGED;  // compile-time: the plain kernel carries none of the polling code
+    uint32_t epoch_in = 0, epoch_out = 0;
+    if (flagged) {
+        const uint32_t base = (uint32_t)(*p.step_ctr) * kEpochStride;
+        epoch_in = base + (uint32_t)p.node_in;
+        epoch_out = base + (uint32_t)p.node_out;
+    }
+    if (!flagged && !p.positions_settled) pdl_wait();  // the position itself may still be in flight
 
     // the token's items: (kv head, page), kv head major
     const int pos = p.tok_pos[0];
@@ -115,10 +125,28 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
     }
 
     // ---- consumers ----
-    pdl_wait();  // q and this step's k, v come from the projection kernel
+    if (!flagged) pdl_wait();  // q and this step's k, v come from the projection kernel
     if (rg) rg[1] = gtime();
-    const bool fused = p.k_new != nullptr;
-    const int rp = fused ? p.tok_rope[0] : 0;
+    const bool fused = p.k_new != nullptr || flagged;
+    const int rp_of_step = fused ? p.tok_rope[0] : 0;
+    // four dims of a head vector of the projection row, rotated (attention.rs:13-34), from plain or flagged words
+    auto head_vec = [&](const float* plain, size_t off, float (&out4)[4]) {
+        if (!flagged) { load_rotated<4, kHD>(plain + off, 4 * lane, rp_of_step, p.theta, out4); return; }
+        float own[4], other[4];
+        ok = flag_load<4>(p.qkvf + off + 4 * lane, epoch_in, own) && ok;
+        if (rp_of_step == 0) { out4[0] = own[0]; out4[1] = own[1]; out4[2] = own[2]; out4[3] = own[3]; return; }
+        const bool lowhalf = 4 * lane < kHD / 2;
+        ok = flag_load<4>(p.qkvf + off + (lowhalf ? 4 * lane + kHD / 2 : 4 * lane - kHD / 2), epoch_in, other) && ok;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int dd = (4 * lane + i) % (kHD / 2);
+            const float freq = __fdiv_rn(1.0f, powf(p.theta, __fdiv_rn(__fmul_rn(2.0f, (float)dd), (float)kHD)));
+            const float angle = __fmul_rn((float)rp_of_step, freq);
+            const float ca = cosf(angle), sa = sinf(angle);
+            out4[i] = lowhalf ? __fsub_rn(__fmul_rn(own[i], ca), __fmul_rn(other[i], sa))
+                              : __fadd_rn(__fmul_rn(other[i], sa), __fmul_rn(own[i], ca));
+        }
+    };
     const float inv_div = sqrtf((float)kHD);  // attention.rs:93: dot / sqrt(head_dim)
     const int key = lane >> 1, half = lane & 1;  // scores: two lanes per key, 64 dims each
 
@@ -158,7 +186,7 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
 #pragma unroll
             for (int g = 0; g < GSZ; g++) {  // rotated queries of the kv group (attention.rs:13-34)
                 float qv[4];
-                load_rotated<4, kHD>(p.q + (size_t)(kvh * GSZ + g) * kHD, 4 * lane, rp, p.theta, qv);
+                head_vec(p.q, (size_t)(kvh * GSZ + g) * kHD, qv);
                 *reinterpret_cast<float4*>(myq + g * kHD + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
             }
             __syncwarp();
@@ -178,8 +206,16 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                 // this step's token replaces the stale staged row: rotate, round through f16 (cache/mod.rs:35-36), keep in the cache
                 const int r = pos % kPage;
                 float kr[4];
-                load_rotated<4, kHD>(p.k_new + (size_t)kvh * kHD, 4 * lane, rp, p.theta, kr);
-                const float4 vr = __ldcg(reinterpret_cast<const float4*>(p.v_new + (size_t)kvh * kHD + 4 * lane));
+                // in the projection row k follows the n_heads query heads and v follows the kv heads of k
+                head_vec(flagged ? nullptr : p.k_new - (size_t)p.n_heads * kHD, (size_t)(p.n_heads + kvh) * kHD, kr);
+                float4 vr;
+                if (flagged) {
+                    float v4[4];
+                    ok = flag_load<4>(p.qkvf + (size_t)(p.n_heads + kv.n_kv + kvh) * kHD + 4 * lane, epoch_in, v4) && ok;
+                    vr = make_float4(v4[0], v4[1], v4[2], v4[3]);
+                } else {
+                    vr = __ldcg(reinterpret_cast<const float4*>(p.v_new + (size_t)kvh * kHD + 4 * lane));
+                }
                 const __half2 k01 = __floats2half2_rn(kr[0], kr[1]), k23 = __floats2half2_rn(kr[2], kr[3]);
                 const __half2 v01 = __floats2half2_rn(vr.x, vr.y), v23 = __floats2half2_rn(vr.z, vr.w);
                 uint2 kw, vw;
@@ -265,8 +301,9 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
 
     // ---- per (kv head, query head): the warps in warp order, then the CTAs that share the kv head in CTA order ----
     const int nseg = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
-    const int hf = tid >> 7, dx = tid & 127;  // kCWarps / 4 (segment, query head) pairs at a time, one thread per dim
-    for (int w = hf; w < nseg * GSZ; w += kCWarps / 4) {
+    constexpr int kMergeGroups = kCWarps / 4;  // whole 128-thread groups among the consumers; the last warps sit the merge out
+    const int hf = tid >> 7, dx = tid & 127;   // kMergeGroups (segment, query head) pairs at a time, one thread per dim
+    for (int w = hf < kMergeGroups ? hf : nseg * GSZ; w < nseg * GSZ; w += kMergeGroups) {
         const int sl = w / GSZ, g = w - sl * GSZ;
         const float* ws = st_s + ((size_t)sl * kCWarps * GSZ + g) * kStateWords;  // warp 0's state; warp stride GSZ * kStateWords
         float M = -INFINITY;
@@ -286,8 +323,11 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
         const int c_first = (int)(((first + 1) * G - 1) / T), c_last = (int)(((last + 1) * G - 1) / T);
         const int nc = c_last - c_first + 1, me = (int)blockIdx.x - c_first;
         unsigned long long* sl_base = P.slots + (size_t)head * P.max_contrib * (2 + kHD);
-        auto put = [](unsigned long long* a, float v) {
-            const unsigned long long wv = (1ull << 32) | (unsigned long long)__float_as_uint(v);
+        // validity tag of a slot word: this launch's output epoch in dataflow mode (never cleared: the next use carries
+        // another epoch), else 1 with the collector clearing what it read
+        const unsigned long long tag = flagged ? (unsigned long long)epoch_out : 1ull;
+        auto put = [&](unsigned long long* a, float v) {
+            const unsigned long long wv = (tag << 32) | (unsigned long long)__float_as_uint(v);
             asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
         };
         if (nc > 1 && me != 0) {
@@ -310,7 +350,7 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                     }
                     all = true;
 #pragma unroll
-                    for (int u = 0; u < 4; u++) all = all && (wv[u][0] >> 32) == 1ull && (wv[u][1] >> 32) == 1ull && (wv[u][2] >> 32) == 1ull;
+                    for (int u = 0; u < 4; u++) all = all && (wv[u][0] >> 32) == tag && (wv[u][1] >> 32) == tag && (wv[u][2] >> 32) == tag;
                 }
                 ok = ok && all;
 #pragma unroll
@@ -325,7 +365,7 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                     M = Mn;
                 }
             }
-            if (nc > 1) {
+            if (nc > 1 && !flagged) {
                 for (int c = 1; c < nc; c++)
                     asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + 2 + dx), "l"(0ull) : "memory");
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read the maxima and sums
@@ -333,7 +373,8 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                     for (int c = 1; c < nc; c++)
                         asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + dx), "l"(0ull) : "memory");
             }
-            p.out[(size_t)head * kHD + dx] = A / L;
+            if (flagged) flag_store(p.outf + (size_t)head * kHD + dx, A / L, epoch_out);
+            else p.out[(size_t)head * kHD + dx] = A / L;
         }
     }
     if (rg) rg[4] = gtime();
@@ -394,11 +435,11 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
     if (stages > 26) stages = 26;
     P.nstages = stages;
     const size_t smem = fixed + (size_t)stages * (kStageBytes + 16);
-    auto kern = attention_stream_kernel<GSZ>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    auto kern = a.qkvf ? attention_stream_kernel<GSZ, true> : attention_stream_kernel<GSZ, false>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[a.qkvf ? 1 : 0]) {
         LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        attr_set = true;
+        attr_set[a.qkvf ? 1 : 0] = true;
     }
     LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((consumer_warps<GSZ>() + 1) * 32), smem, s, P));
     return LC_OK;

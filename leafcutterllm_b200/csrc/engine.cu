@@ -81,6 +81,13 @@ struct lc_model {
     int64_t* d_out_tokens = nullptr;
     size_t out_tokens_cap = 0;
     int32_t* d_step_ctr = nullptr;
+    // Dataflow decode step (one sequence, Q4_K layers, streaming attention): the activations between the kernels of a
+    // step travel as flagged words, so no kernel waits for the grid ahead of it.  d_epoch counts decode steps and never
+    // goes back; the advance kernel at the end of every step increments it.
+    unsigned long long *f_hidden = nullptr, *f_hidden2 = nullptr, *f_qkv = nullptr, *f_attn = nullptr, *f_ffn = nullptr;
+    int32_t* d_epoch = nullptr;
+    bool dataflow_ready = false;   // the model qualifies
+    bool dataflow_step = false;    // set while the kernels of such a step are being queued
     void* d_attn_scratch = nullptr;
     int* d_attn_counters = nullptr;
     size_t attn_scratch_bytes = 0;
@@ -168,7 +175,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int32_t*
 // the token is logged.  rope_absolute: rotary position follows the cache position; otherwise it
 // stays the index inside the call (0 for a one-token call, attention.rs:13-21).
 __global__ void advance_kernel(const int64_t* __restrict__ next, int64_t* tokens, int32_t* tok_pos, int32_t* tok_rope, int n,
-                               int rope_absolute, int64_t* out_tokens, int32_t* step_ctr) {
+                               int rope_absolute, int64_t* out_tokens, int32_t* step_ctr, int32_t* epoch) {
     pdl_launch_dependents();
     pdl_wait();
     int i = threadIdx.x;
@@ -180,7 +187,10 @@ __global__ void advance_kernel(const int64_t* __restrict__ next, int64_t* tokens
         if (out_tokens) out_tokens[(size_t)step * n + i] = next[i];
     }
     __syncthreads();
-    if (i == 0) *step_ctr = step + 1;
+    if (i == 0) {
+        *step_ctr = step + 1;
+        if (epoch) *epoch = *epoch + 1;  // flagged activations of the next step carry a new epoch
+    }
 }
 
 int32_t check_model(const lc_model* m, bool need_final) {
@@ -288,6 +298,13 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     g.norm_w = norm_w;
     g.eps = m->cfg.rms_eps;
     if (decode_step) g.prefetch = prefetch_for(m, l, 0);
+    const bool df = m->dataflow_step;  // one token; nodes of layer l: 5l+1 QKV, +2 attention, +3 O, +4 gate/up, +5 down
+    if (df) {
+        g.step_ctr = m->d_epoch;
+        if (l > 0) { g.x = nullptr; g.x_flag = m->f_hidden; g.node_in = 5 * l; }
+        g.out_flag = m->f_qkv;
+        g.node_out = 5 * l + 1;
+    }
     if (w.fused_qkv) {
         g.w = &w.qkv;
         g.out = m->d_qkv;
@@ -308,6 +325,7 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
         AttnFusion fz{k, v, m->d_tok_rope, m->cfg.rope_theta};
         fz.prefetch = prefetch_for(m, l, 1);
         fz.positions_settled = l > 0;  // the first layer of a step may run while the previous step still advances the positions
+        if (df) { fz.qkv_flag = m->f_qkv; fz.out_flag = m->f_attn; fz.step_ctr = m->d_epoch; fz.node_in = 5 * l + 1; fz.node_out = 5 * l + 2; }
         LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
                                 m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, &fz, m->stream));
         m->launches_in_call += 1;
@@ -324,6 +342,12 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     o.out = out;
     if (residual) { o.residual = residual; o.epi = EPI_ADD_RESIDUAL; }
     if (decode_step) o.prefetch = prefetch_for(m, l, 2);
+    if (df) {
+        o.step_ctr = m->d_epoch;
+        o.x = nullptr; o.x_flag = m->f_attn; o.node_in = 5 * l + 2;
+        if (residual && l > 0) { o.residual = nullptr; o.residual_flag = m->f_hidden; }  // layer 0 adds the embedding row (plain)
+        o.out_flag = m->f_hidden2; o.node_out = 5 * l + 3;
+    }
     if (ablate_mask() & 4) return LC_OK;
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
 }
@@ -341,6 +365,12 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     g.out = m->d_ffn;
     g.epi = EPI_SILU_MUL;
     if (decode_step) g.prefetch = prefetch_for(m, l, 3);
+    const bool df = m->dataflow_step;
+    if (df) {
+        g.step_ctr = m->d_epoch;
+        g.x = nullptr; g.x_flag = m->f_hidden2; g.node_in = 5 * l + 3;
+        g.out_flag = m->f_ffn; g.node_out = 5 * l + 4;
+    }
     if (!(ablate_mask() & 8)) LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
     GemvArgs d;
     d.w = &w.down;
@@ -348,6 +378,12 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     d.out = out;
     if (residual) { d.residual = residual; d.epi = EPI_ADD_RESIDUAL; }
     if (decode_step) d.prefetch = prefetch_for(m, l, 4);
+    if (df) {
+        d.step_ctr = m->d_epoch;
+        d.x = nullptr; d.x_flag = m->f_ffn; d.node_in = 5 * l + 4;
+        if (residual) { d.residual = nullptr; d.residual_flag = m->f_hidden2; }
+        d.out_flag = m->f_hidden; d.node_out = 5 * l + 5;
+    }
     if (ablate_mask() & 16) return LC_OK;
     return gemv_tiled(m, d, T, m->H, m->F);
 }
@@ -385,6 +421,7 @@ int32_t forward_tokens(lc_model* m, int T, int n_last, bool identity_last, int r
     h.norm_w = m->final_norm;
     h.eps = m->cfg.rms_eps;
     h.out = m->d_logits + (size_t)row0 * m->V;
+    if (m->dataflow_step) { h.x = nullptr; h.x_flag = m->f_hidden; h.step_ctr = m->d_epoch; h.node_in = 5 * m->L; }
     if (!(ablate_mask() & 32)) LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
     LC_TRY(launch_argmax(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->d_next + row0, m->stream));
     m->launches_in_call += 1;
@@ -701,6 +738,29 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(weight_of(m, head, V, H, &m->head, nullptr));
 
     LC_TRY(attention_stream_reserve(m->nh, m->nkv));
+    {   // dataflow decode step: every matrix of the step runs on the tensor-core Q4_K kernel, attention on the streaming kernel
+        bool okk = m->L > 0 && 5 * m->L + 2 < (int)kEpochStride && m->hd == 128 && m->cfg.kv_dtype == 0 && m->page_tokens == 16 &&
+                   m->nkv <= sm_count() && m->head.typ == LC_TYPE_Q4_K && m->head.has_tmap && qgemv_mma_supports(H) &&
+                   qgemv_mma_supports(F) && qgemv_mma_supports(nq);
+        const int gsz = m->nh / m->nkv;
+        okk = okk && (gsz == 1 || gsz == 2 || gsz == 4 || gsz == 8);
+        for (int l = 0; l < m->L && okk; l++) {
+            const LayerW& w = m->layers[l];
+            okk = w.fused_qkv && w.qkv.typ == LC_TYPE_Q4_K && w.o.typ == LC_TYPE_Q4_K && w.gate.typ == LC_TYPE_Q4_K &&
+                  w.down.typ == LC_TYPE_Q4_K && w.qkv.has_tmap && w.o.has_tmap && w.gate.has_tmap && w.up.has_tmap && w.down.has_tmap;
+        }
+        if (okk) {
+            LC_TRY(dalloc(&m->f_hidden, (size_t)H)); LC_TRY(dalloc(&m->f_hidden2, (size_t)H)); LC_TRY(dalloc(&m->f_qkv, (size_t)m->nqkv));
+            LC_TRY(dalloc(&m->f_attn, (size_t)nq)); LC_TRY(dalloc(&m->f_ffn, (size_t)F)); LC_TRY(dalloc(&m->d_epoch, 1));
+            LC_CUDA(cudaMemsetAsync(m->f_hidden, 0, (size_t)H * 8, m->stream)); LC_CUDA(cudaMemsetAsync(m->f_hidden2, 0, (size_t)H * 8, m->stream));
+            LC_CUDA(cudaMemsetAsync(m->f_qkv, 0, (size_t)m->nqkv * 8, m->stream)); LC_CUDA(cudaMemsetAsync(m->f_attn, 0, (size_t)nq * 8, m->stream));
+            LC_CUDA(cudaMemsetAsync(m->f_ffn, 0, (size_t)F * 8, m->stream));
+            const int32_t one = 1;  // epoch words of zeroed buffers (0) never match
+            LC_CUDA(cudaMemcpyAsync(m->d_epoch, &one, 4, cudaMemcpyHostToDevice, m->stream));
+            LC_CUDA(cudaStreamSynchronize(m->stream));
+            m->dataflow_ready = true;
+        }
+    }
     // scratch of the split-tile GEMV, so that no launch inside a captured decode step allocates
     if (m->L > 0) {
         const LayerW& w0 = m->layers[0];
@@ -780,7 +840,8 @@ int32_t lc_model_destroy(lc_model* m) {
     for (void* p : m->mega_bufs) cudaFree(p);
     for (void* p : m->k_pools) cudaFree(p);
     for (void* p : m->v_pools) cudaFree(p);
-    void* bufs[] = {m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
+    void* bufs[] = {m->f_hidden, m->f_hidden2, m->f_qkv, m->f_attn, m->f_ffn, m->d_epoch,
+                    m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity};
     for (void* p : bufs) if (p) cudaFree(p);
@@ -918,13 +979,17 @@ int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_
 // CUDA graph that later steps replay.
 static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
     auto one_step = [&]() -> int32_t {
-        LC_TRY(forward_tokens(m, n_seqs, n_seqs, true, 0));
+        static const bool no_dataflow = getenv("LC_NO_DATAFLOW") != nullptr;
+        m->dataflow_step = n_seqs == 1 && m->dataflow_ready && !no_dataflow && ablate_mask() == 0;
+        int32_t fs = forward_tokens(m, n_seqs, n_seqs, true, 0);
+        m->dataflow_step = false;
+        LC_TRY(fs);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(std::max(32, (n_seqs + 31) / 32 * 32));
         cfg.stream = m->stream;
         LC_CUDA(cudaLaunchKernelEx(&cfg, advance_kernel, (const int64_t*)m->d_next, m->d_tokens, m->d_tok_pos, m->d_tok_rope, (int)n_seqs,
-                                   (int)m->cfg.rope_mode, m->d_out_tokens, m->d_step_ctr));
+                                   (int)m->cfg.rope_mode, m->d_out_tokens, m->d_step_ctr, m->d_epoch));
         m->launches_in_call += 1;
         return LC_OK;
     };

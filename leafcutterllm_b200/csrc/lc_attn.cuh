@@ -29,6 +29,11 @@ struct AttnParams {
     const int32_t* tok_rope;
     float theta;
     int positions_settled; // decode-step fusion: tok_pos may be read before the grid dependency wait
+    // dataflow mode of the streaming kernel (see AttnFusion): flagged projection row in, flagged output out
+    const unsigned long long* qkvf = nullptr;
+    unsigned long long* outf = nullptr;
+    const int32_t* step_ctr = nullptr;
+    int node_in = 0, node_out = 0;
     int* error_flag;       // set when a bounded wait runs out (may be null)
     L2Prefetch prefetch;   // weights of the kernels that follow, pulled into L2 by the staged kernel
 };

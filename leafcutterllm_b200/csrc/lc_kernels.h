@@ -67,7 +67,17 @@ struct GemvArgs {
     float eps = 1e-5f;
     GemvEpilogue epi = EPI_STORE;
     L2Prefetch prefetch;              // honoured by the tensor-core Q4_K kernel
+    // Dataflow mode (one token, the mma.sync Q4_K kernel): activations travel as flagged words (see flag_store) and
+    // the kernel does not wait for the grid ahead of it.  x_flag replaces x, out_flag replaces out, residual_flag
+    // replaces residual; step_ctr points at the device-side step counter and the node numbers give the epochs
+    // step * kEpochStride + node that the input must carry and the output will carry.
+    const unsigned long long* x_flag = nullptr;
+    unsigned long long* out_flag = nullptr;
+    const unsigned long long* residual_flag = nullptr;
+    const int32_t* step_ctr = nullptr;
+    int node_in = 0, node_out = 0;
 };
+constexpr uint32_t kEpochStride = 1024;  // nodes per step in the epoch numbering
 // y[m,n] = x[m,k] . dequant(W)^T, fp32 activations and accumulation.
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s);
 // Reserves the scratch a later launch_qgemv of an [n x k] matrix may need, so that none is allocated inside a stream
@@ -101,7 +111,15 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx);
 // positions_settled: tok_pos was final before the kernel ahead of this one started (true from the second layer of a
 // step on; false for the first layer, whose positions the end of the previous step may still be writing), so the
 // kernel may read it, and start fetching cached pages, before it waits for the kernel ahead of it.
-struct AttnFusion { const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; L2Prefetch prefetch; bool positions_settled = false; };
+struct AttnFusion {
+    const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; L2Prefetch prefetch; bool positions_settled = false;
+    // Dataflow mode (streaming single-token kernel): q, k_new, v_new are read from qkv_flag (the fused projection row as
+    // flagged words, q at 0, k at n_heads*hd, v after k) and the output is written to out_flag; epochs as in GemvArgs.
+    const unsigned long long* qkv_flag = nullptr;
+    unsigned long long* out_flag = nullptr;
+    const int32_t* step_ctr = nullptr;
+    int node_in = 0, node_out = 0;
+};
 int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
                          const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
                          void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);

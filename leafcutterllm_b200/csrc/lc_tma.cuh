@@ -51,6 +51,11 @@ struct GemvParams {
     int epi;
     int* error_flag;
     L2Prefetch prefetch;
+    const unsigned long long* xf = nullptr;   // dataflow mode: flagged input / output / residual (see GemvArgs)
+    unsigned long long* outf = nullptr;
+    const unsigned long long* resf = nullptr;
+    const int32_t* step_ctr = nullptr;
+    int node_in = 0, node_out = 0;
 };
 
 
@@ -76,6 +81,8 @@ constexpr size_t kMaxSmem = 227 * 1024;
 
 // qgemv_mma.cu: Q4_K through int8 tensor-core MMAs; *launched = false when the shape does not fit.
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
+// true when the single-token kernel fits shared memory for rows of k elements
+bool qgemv_mma_supports(int k);
 // qgemv_umma.cu: Q4_K for one or two tokens through tcgen05.mma with accumulators in tensor memory.
 int32_t launch_qgemv_umma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
 

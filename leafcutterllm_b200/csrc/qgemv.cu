@@ -532,26 +532,28 @@ static int32_t launch_generic(const GemvArgs& a, cudaStream_t s) {
 static int round_m(int m) { return m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8)); }
 
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
-    LC_CHECK(a.w && a.x && a.out, LC_ERR_INVALID, "qgemv: null argument");
+    LC_CHECK(a.w && (a.x || a.x_flag) && (a.out || a.out_flag), LC_ERR_INVALID, "qgemv: null argument");
+    const bool dataflow = a.x_flag || a.out_flag || a.residual_flag;
     LC_CHECK(a.m >= 1 && a.m <= 8, LC_ERR_INVALID, "qgemv: m=%d outside 1..8", a.m);
     if (a.epi == EPI_SILU_MUL)
         LC_CHECK(a.w2 && a.w2->n == a.w->n && a.w2->k == a.w->k && a.w2->typ == a.w->typ, LC_ERR_INVALID,
                  "qgemv: gate/up matrices differ in shape or type");
-    if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual, LC_ERR_INVALID, "qgemv: residual missing");
+    if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual || a.residual_flag, LC_ERR_INVALID, "qgemv: residual missing");
     bool tma_ok = a.w->has_tmap && (a.epi != EPI_SILU_MUL || a.w2->has_tmap);
     static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
     // The tcgen05 kernel (qgemv_umma.cu) is opt-in: inside a decode step it ties with the mma.sync kernel on the large
     // matrices and loses on the small one (its split-tile merge and longer prologue cost more than its leaner loop saves).
     const bool use_umma = getenv("LC_GEMV_UMMA") != nullptr;  // read per call so that a test can switch it
-    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32 && use_umma && a.m <= 2) {
+    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32 && use_umma && a.m <= 2 && !dataflow) {
         bool launched = false;
         LC_TRY(launch_qgemv_umma_q4k(a, s, &launched));
         if (launched) return LC_OK;
     }
-    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32) {
+    if (dataflow || (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32)) {
         bool launched = false;
-        LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
+        if (tma_ok && a.w->typ == LC_TYPE_Q4_K) LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
         if (launched) return LC_OK;
+        LC_CHECK(!dataflow, LC_ERR_UNSUPPORTED, "qgemv: flagged activations are only implemented by the Q4_K tensor-core kernel");
     }
     if (tma_ok) {
         for (int mt = round_m(a.m); mt >= 1; mt >>= 1) {

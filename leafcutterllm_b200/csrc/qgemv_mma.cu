@@ -94,14 +94,34 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         l2_prefetch_part(p.prefetch.p[1], p.prefetch.bytes[1], blockIdx.x, gridDim.x);
     }
     pdl_launch_dependents();
-    pdl_wait();
+    // Dataflow mode: the input words carry the epoch of this step's producer, so the kernel goes ahead as soon as the
+    // producing CTAs have written them instead of waiting for the producing grid (and everything before it) to drain.
+    const bool flagged_in = p.xf != nullptr;
+    uint32_t epoch_in = 0, epoch_out = 0;
+    if (p.step_ctr) {
+        const uint32_t base = (uint32_t)(*p.step_ctr) * kEpochStride;
+        epoch_in = base + (uint32_t)p.node_in;
+        epoch_out = base + (uint32_t)p.node_out;
+    }
+    bool in_ok = true;
+    if (!flagged_in) pdl_wait();
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
     if (p.norm_w) {
         for (int tk = 0; tk < M; tk++) {
             float ss = 0.f;
-            if (tk < p.m)
-                for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = p.x[(size_t)tk * p.k + i]; ss = fmaf(v, v, ss); }
+            if (tk < p.m) {
+                if (flagged_in) {
+                    for (int i0 = threadIdx.x; i0 < p.k; i0 += 8 * blockDim.x) {  // eight strided words in flight per thread
+                        float v[8];
+                        in_ok = flag_load_strided<8>(p.xf + i0, (int)blockDim.x, p.k - i0, epoch_in, v) && in_ok;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
+                    }
+                } else {
+                    for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = p.x[(size_t)tk * p.k + i]; ss = fmaf(v, v, ss); }
+                }
+            }
             ss = warp_sum(ss);
             __syncthreads();
             if (lane == 0) scratch[warp] = ss;
@@ -123,9 +143,13 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             float v[8];
             const int e0 = unit * kUnitElems + 8 * lane;
             if (tk < p.m) {
-                const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);
-                float4 u0 = xp[0], u1 = xp[1];
-                v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+                if (flagged_in) {
+                    in_ok = flag_load<8>(p.xf + e0, epoch_in, v) && in_ok;
+                } else {
+                    const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);
+                    float4 u0 = xp[0], u1 = xp[1];
+                    v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+                }
                 if (p.norm_w) {
                     const float sc = scratch[32 + tk];
                     const float4* np = reinterpret_cast<const float4*>(p.norm_w + e0);
@@ -324,20 +348,26 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 #pragma unroll 4
                 for (int w = 0; w < WARPS; w++) y += rb[(w * M + tk) * 32 + lane];
                 const int row = tile * kTileRows + lane;
+                bool have = false;
                 if (p.epi == EPI_SILU_MUL) {
                     if (mat == 0) {
                         gate_vals[tk * 32 + lane] = y;
                     } else if (row < p.n && tk < p.m) {
-                        p.out[(size_t)tk * p.n + row] = silu_f(gate_vals[tk * 32 + lane]) * y;
+                        y = silu_f(gate_vals[tk * 32 + lane]) * y;
+                        have = true;
                     }
                 } else if (row < p.n && tk < p.m) {
-                    if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[(size_t)tk * p.n + row] + y;
-                    p.out[(size_t)tk * p.n + row] = y;
+                    if (p.epi == EPI_ADD_RESIDUAL) y = (p.resf ? flag_value(p.resf + row) : p.residual[(size_t)tk * p.n + row]) + y;
+                    have = true;
+                }
+                if (have) {
+                    if (p.outf) flag_store(p.outf + row, y, epoch_out);  // dataflow mode is single-token
+                    else p.out[(size_t)tk * p.n + row] = y;
                 }
             }
         }
     }
-    if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    if (!(ok && in_ok) && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
 }
 
 template <int M, int WARPS, int STAGES>
@@ -364,6 +394,7 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
     p.prefetch = a.prefetch;
+    p.xf = a.x_flag; p.outf = a.out_flag; p.resf = a.residual_flag; p.step_ctr = a.step_ctr; p.node_in = a.node_in; p.node_out = a.node_out;
     int ntiles = (p.n + kTileRows - 1) / kTileRows;
     // CTAs per SM that fit shared memory (and, for the 8-warp shape, registers): with two per SM the
     // first CTAs of the next kernel move in while the last CTAs of this one drain
@@ -394,9 +425,18 @@ static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     return LC_OK;
 }
 
+bool qgemv_mma_supports(int k) {
+    return k > 0 && k % kUnitElems == 0 && (mma_smem_bytes<1, 16, 2>(k) <= kMaxSmem || mma_smem_bytes<1, 8, 2>(k) <= kMaxSmem);
+}
+
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = false;
-    if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
+    const bool dataflow = a.x_flag || a.out_flag || a.residual_flag;
+    if (dataflow) {
+        LC_CHECK(a.m == 1 && a.step_ctr && (!a.x_flag || ((uintptr_t)a.x_flag % 16) == 0), LC_ERR_INVALID,
+                 "qgemv: flagged activations need a single token, the step counter and 16-byte aligned words");
+    }
+    if ((!a.x_flag && ((uintptr_t)a.x % 16) != 0) || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
     if (a.m <= 1) return launch_mma_m<1>(a, s, launched);
     if (a.m <= 2) return launch_mma_m<2>(a, s, launched);
     if (a.m <= 4) return launch_mma_m<4>(a, s, launched);
