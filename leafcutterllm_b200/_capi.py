@@ -8,6 +8,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libleafcutter_b200.so")
 
 LC_OK = 0
+LC_ERR_INVALID, LC_ERR_UNSUPPORTED, LC_ERR_CUDA, LC_ERR_OOM, LC_ERR_KV_FULL, LC_ERR_MISSING, LC_ERR_STATE = -1, -2, -3, -4, -5, -6, -7
 STATUS_NAMES = {0: "LC_OK", -1: "LC_ERR_INVALID", -2: "LC_ERR_UNSUPPORTED", -3: "LC_ERR_CUDA", -4: "LC_ERR_OOM",
                 -5: "LC_ERR_KV_FULL", -6: "LC_ERR_MISSING", -7: "LC_ERR_STATE"}
 

@@ -56,6 +56,7 @@ struct GemvParams {
     const unsigned long long* resf = nullptr;
     const int32_t* step_ctr = nullptr;
     int node_in = 0, node_out = 0;
+    unsigned long long* ring = nullptr;  // diagnostics (LC_GEMV_RING): 8 wall-clock words of this launch, or null
 };
 
 

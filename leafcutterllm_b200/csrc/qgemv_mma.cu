@@ -16,6 +16,7 @@
 // Data path: the same TMA-staged [144 B x 32 rows] boxes as the f32 kernel; warp <-> unit, a thread
 // holds the A fragments of rows g and g+8 (g = lane / 4) as two 32-bit shared-memory loads per
 // 64-element group (bank-conflict free for the 144-byte row pitch).
+#include <cstdio>
 #include <cstdlib>
 #include "lc_kernels.h"
 #include "lc_quant.cuh"
@@ -52,6 +53,12 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     const int ntiles = (p.n + kTileRows - 1) / kTileRows;
     const int nmat = (p.epi == EPI_SILU_MUL) ? 2 : 1;
 
+    auto gtime = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+    unsigned long long* rg = nullptr;
+    if (p.ring && threadIdx.x == 0) {
+        atomicMax(p.ring + 7, gtime());  // the last CTA to start
+        if (blockIdx.x == 0) { rg = p.ring; rg[0] = gtime(); rg[5] = ((unsigned long long)p.n << 32) | (unsigned)p.k; }
+    }
     unsigned char* stage_base = smem + (size_t)warp * STAGES * STAGE_BYTES;
     size_t off = (size_t)WARPS * STAGES * STAGE_BYTES;
     unsigned char* planes = smem + off;                          // [nunits][8][M][3][32] int8
@@ -105,6 +112,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     }
     bool in_ok = true;
     if (!flagged_in) pdl_wait();
+    if (rg) rg[1] = gtime();
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
     if (p.norm_w) {
@@ -197,6 +205,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         }
     }
     __syncwarp();
+    if (rg) rg[2] = gtime();
 
     // Thread t owns B/C columns 2t and 2t+1.  Columns 0-2 carry the byte planes of the pair's first token,
     // 3-5 those of its second token.  Coefficients that fold this thread's two columns into each token:
@@ -367,8 +376,30 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             }
         }
     }
+    if (rg) rg[3] = gtime();
+    if (p.ring && threadIdx.x == 0) atomicMax(p.ring + 6, gtime());  // the last CTA to finish
     if (!(ok && in_ok) && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
 }
+
+namespace {
+unsigned long long* g_mring = nullptr;
+int g_mring_seq = 0;
+void dump_mring() {
+    static unsigned long long h[1024 * 8];
+    if (!g_mring || cudaMemcpy(h, g_mring, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return;
+    fprintf(stderr, "[gemv ring] per launch slot, ns relative to CTA 0's start of the slot before:\n"
+                    "  slot n k | cta0 start, last cta start | dependency met, planes done, cta0 end | last cta end\n");
+    unsigned long long base = 0;
+    for (int i = 0; i < 1024; i++) {
+        const unsigned long long* r = h + (size_t)i * 8;
+        if (!r[0]) continue;
+        if (!base) base = r[0];
+        fprintf(stderr, "  %4d %6llu %6llu | %7lld %7lld | %7lld %7lld %7lld | %7lld\n", i, r[5] >> 32, r[5] & 0xffffffffu, (long long)(r[0] - base),
+                (long long)(r[7] - base), (long long)(r[1] - base), (long long)(r[2] - base), (long long)(r[3] - base), (long long)(r[6] - base));
+        base = r[0];
+    }
+}
+}  // namespace
 
 template <int M, int WARPS, int STAGES>
 static size_t mma_smem_bytes(int k) {
@@ -394,6 +425,15 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
     p.prefetch = a.prefetch;
+    static const bool want_ring = getenv("LC_GEMV_RING") != nullptr;
+    if (want_ring) {
+        if (!g_mring) {
+            LC_CUDA(cudaMalloc(&g_mring, 1024 * 8 * sizeof(unsigned long long)));
+            LC_CUDA(cudaMemset(g_mring, 0, 1024 * 8 * sizeof(unsigned long long)));
+            atexit(dump_mring);
+        }
+        p.ring = g_mring + (size_t)(g_mring_seq++ % 1024) * 8;
+    }
     p.xf = a.x_flag; p.outf = a.out_flag; p.resf = a.residual_flag; p.step_ctr = a.step_ctr; p.node_in = a.node_in; p.node_out = a.node_out;
     int ntiles = (p.n + kTileRows - 1) / kTileRows;
     // CTAs per SM that fit shared memory (and, for the 8-warp shape, registers): with two per SM the

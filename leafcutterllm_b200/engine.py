@@ -37,6 +37,26 @@ class Engine:
         self.vocab_size = vocab_size
         self.max_seqs = max_seqs
 
+    @classmethod
+    def load(cls, path: str, max_seq_len: int = 0, kv_dtype: str = "f16", rope_mode: str = "call_relative", max_seqs: int = 1,
+             kv_page_tokens: int = 16, kv_pool_tokens: int = 0, device: int = 0) -> "Engine":
+        """`Engine::load(path)` (rust/src/inference/engine.rs:18-49): a GGUF v3 file, parsed and uploaded by the library.
+        max_seq_len > 0 caps the KV capacity (the file's context length can be far more than a test wants to allocate)."""
+        over = ModelConfig()
+        over.max_seq_len = max_seq_len
+        over.kv_dtype = {"f16": 0, "f32": 1}[kv_dtype]
+        over.rope_mode = {"call_relative": 0, "absolute": 1}[rope_mode]
+        over.max_seqs, over.kv_page_tokens, over.kv_pool_tokens, over.device = max_seqs, kv_page_tokens, kv_pool_tokens, device
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        check(load().lc_model_load_gguf(str(path).encode(), C.byref(over), C.byref(self._h)))
+        cfg = ModelConfig()
+        check(load().lc_model_get_config(self._h, C.byref(cfg)))
+        self.cfg = cfg
+        self.vocab_size = cfg.vocab_size
+        self.max_seqs = max(1, cfg.max_seqs)
+        return self
+
     # ---- weights -------------------------------------------------------
     def set_tensor(self, name: str, typ: int, dims: Sequence[int], data) -> None:
         """`dims` in GGUF order (fastest first); `data` = raw block bytes."""
