@@ -5,11 +5,13 @@
 // (kv head, page) order, are cut into one contiguous run per CTA -- CTA c takes items [c*T/G, (c+1)*T/G) -- so every
 // SM streams the same number of bytes whatever the context length and head count, and there is a single wave.
 //
-//   producer  one thread requests the run's slabs with bulk copies into a ring of 8 KB stages (one mbarrier each),
-//             starting BEFORE the grid dependency wait: cached pages belong to earlier steps;
-//   consumers eight warps take the items round robin.  A warp scores the 16 keys of its page (two lanes per key, 16-byte
-//             chunks walked in a rotated order so a quarter warp never meets a bank twice), updates an online softmax
-//             per query head of the kv group and accumulates p.V with four dims per lane;
+//   producer  a warp requests the run's slabs with bulk copies into a ring of stages (one mbarrier each), each lane
+//             looking up its own page-table entries, starting BEFORE the kernel looks at its input: cached pages belong
+//             to earlier steps.  Keys are copied row by row into a 272-byte pitch, values as one 4 KB piece;
+//   consumers the other warps take the items round robin.  A warp scores the 16 keys of its page (lane = key, the two half
+//             warps take the two halves of the head; with the padded pitch a 16-byte chunk of 8 consecutive keys spans
+//             all banks and the query chunk is one broadcast read), updates an online softmax per query head of the kv
+//             group and accumulates p.V with four dims per lane;
 //   new token the warp that owns the page holding this step's position rotates k, rounds k and v through f16 exactly
 //             as the cache does, patches its staged copy and stores the row into the cache;
 //   merge     per (kv head) segment the warps are combined in warp order, then the CTAs that share the segment in CTA
@@ -20,6 +22,7 @@
 // do not vary from run to run.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include "lc_kernels.h"
 #include "lc_attn.cuh"
 #include "lc_tma.cuh"
@@ -30,8 +33,12 @@ namespace {
 
 constexpr int kHD = 128;
 constexpr int kPage = 16;
-constexpr int kSlab = kPage * kHD * 2;       // bytes of one K (or V) slab
-constexpr int kStageBytes = 2 * kSlab;       // K then V
+constexpr int kSlab = kPage * kHD * 2;       // bytes of one K (or V) slab in the cache
+// A stage: the page's keys as two TMA boxes of 16 rows x 64 dims (128-byte rows, 128-byte swizzle: the 16-byte chunk j of
+// row r sits at chunk j ^ (r & 7), which is what lets ldmatrix read 8 rows of one chunk without a bank conflict), then
+// the page's values as one 4 KB piece.
+constexpr int kKHalf = kPage * 128;          // one box
+constexpr int kStageBytes = 2 * kSlab;
 constexpr int kMaxSeg = 3;                   // kv heads a CTA's run can touch (n_kv <= SM count)
 constexpr int kStateWords = 4 + kHD;         // max, sum, two pad words (16-byte alignment), weighted V
 
@@ -57,10 +64,11 @@ template <int GSZ>
 __host__ __device__ constexpr int consumer_warps() { return GSZ <= 2 ? 15 : 7; }
 
 template <int GSZ, bool FLAGGED>
-__global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention_stream_kernel(StreamParams P) {
+__global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1)
+attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P) {
     constexpr int kCWarps = consumer_warps<GSZ>();
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1 KB
     const AttnParams& p = P.a;
     const KvLayout& kv = p.kv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -117,8 +125,11 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
             if (i >= S) ok = mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1)) && ok;
             const size_t src = ((size_t)pg * kv.n_kv + kvh) * kPage * kHD;
             mbar_expect_tx(&full[st], kStageBytes);
-            bulk_g2s(ring + (size_t)st * kStageBytes, (const __half*)kv.k_pool + src, kSlab, &full[st]);
-            bulk_g2s(ring + (size_t)st * kStageBytes + kSlab, (const __half*)kv.v_pool + src, kSlab, &full[st]);
+            unsigned char* dst = ring + (size_t)st * kStageBytes;
+            const int y = (pg * kv.n_kv + kvh) * kPage;  // first row of the slab in the pool seen as [rows][128]
+            tma_load_2d(dst, &ktm, 0, y, &full[st]);
+            tma_load_2d(dst + kKHalf, &ktm, 64, y, &full[st]);
+            bulk_g2s(dst + 2 * kKHalf, (const __half*)kv.v_pool + src, kSlab, &full[st]);
         }
         if (!ok && p.error_flag) atomicExch(p.error_flag, 1);
         return;  // the producer takes no part in the barriers below (they count the consumer threads)
@@ -148,12 +159,18 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
         }
     };
     const float inv_div = sqrtf((float)kHD);  // attention.rs:93: dot / sqrt(head_dim)
-    const int key = lane >> 1, half = lane & 1;  // scores: two lanes per key, 64 dims each
 
-    float m[GSZ], l[GSZ], acc[GSZ][4];
+    // Scores run on the tensor cores: C[16 keys x 8 columns] per n tile, two columns (f16 hi and lo part of q) per query
+    // head, so an n tile serves four heads and lane (row, t) of the C fragment belongs to head 4 nt + t.
+    constexpr int NT = (2 * GSZ + 7) / 8;
+    float acc[GSZ][4];
+    float m_own[NT], l_own[NT];  // running max and sum of head 4 nt + (lane & 3), kept by the lanes of that column
+    uint32_t qf[NT][8][2];       // B fragments of the segment's queries, per n tile and 16-dim k tile
     auto reset = [&]() {
 #pragma unroll
-        for (int g = 0; g < GSZ; g++) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
+        for (int nt = 0; nt < NT; nt++) { m_own[nt] = -INFINITY; l_own[nt] = 0.f; }
+#pragma unroll
+        for (int g = 0; g < GSZ; g++) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
     };
     reset();
     float* myq = q_s + (size_t)warp * GSZ * kHD;
@@ -163,9 +180,12 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
     auto flush = [&](int seg) {  // this warp's state of kv head `seg` -> shared memory
         float* dst = st_s + ((size_t)(seg - seg0) * kCWarps + warp) * GSZ * kStateWords;
 #pragma unroll
-        for (int g = 0; g < GSZ; g++) {
-            if (lane == 0) { dst[g * kStateWords] = m[g]; dst[g * kStateWords + 1] = l[g]; }
+        for (int g = 0; g < GSZ; g++)
             *reinterpret_cast<float4*>(dst + g * kStateWords + 4 + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+        if (lane < 4) {  // lanes 0-3: row 0 of the C fragment, columns of heads 4 nt + lane
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+                if (4 * nt + lane < GSZ) { dst[(4 * nt + lane) * kStateWords] = m_own[nt]; dst[(4 * nt + lane) * kStateWords + 1] = l_own[nt]; }
         }
     };
     // every (segment, warp) slot starts empty: a warp may meet no item of a segment
@@ -190,6 +210,28 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                 *reinterpret_cast<float4*>(myq + g * kHD + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
             }
             __syncwarp();
+            {
+                // B operand of mma.m16n8k16 (16 dims x 8 columns): column 2h = f16(q of head 4 nt + h), column 2h + 1 = f16 of
+                // what that rounding lost, so products with the f16 keys are exact and q keeps ~22 bits.  This lane holds
+                // column lane / 4, dims 2t, 2t+1, 2t+8, 2t+9 of each tile.
+                const int col = lane >> 2, t4 = lane & 3;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int hq = 4 * nt + (col >> 1);
+#pragma unroll
+                    for (int kt = 0; kt < 8; kt++) {
+#pragma unroll
+                        for (int r = 0; r < 2; r++) {
+                            float x0 = 0.f, x1 = 0.f;
+                            if (hq < GSZ) { x0 = myq[hq * kHD + kt * 16 + 2 * t4 + 8 * r]; x1 = myq[hq * kHD + kt * 16 + 2 * t4 + 8 * r + 1]; }
+                            __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
+                            if (col & 1) { h0 = __float2half_rn(x0 - __half2float(h0)); h1 = __float2half_rn(x1 - __half2float(h1)); }
+                            const __half2 hh = __halves2half2(h0, h1);
+                            qf[nt][kt][r] = (hq < GSZ) ? *reinterpret_cast<const uint32_t*>(&hh) : 0u;
+                        }
+                    }
+                }
+            }
         }
         if (rg && il == warp) rg[8] = clock64() - loop0;
         const int st = il % S;
@@ -197,8 +239,8 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
         ok = mbar_wait(&full[st], (uint32_t)((il / S) & 1)) && ok;
         wait_cycles += clock64() - tw0;
         if (rg && il == warp) rg[9] = clock64() - loop0;
-        __half* K_s = reinterpret_cast<__half*>(ring + (size_t)st * kStageBytes);
-        __half* V_s = K_s + kPage * kHD;
+        unsigned char* K_b = ring + (size_t)st * kStageBytes;           // two swizzled boxes: dims 0-63, dims 64-127
+        __half* V_s = reinterpret_cast<__half*>(K_b + 2 * kKHalf);
         int nvalid = kPage;
         if (page == np - 1) {
             nvalid = pos % kPage + 1;
@@ -221,7 +263,8 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                 uint2 kw, vw;
                 kw.x = *reinterpret_cast<const uint32_t*>(&k01); kw.y = *reinterpret_cast<const uint32_t*>(&k23);
                 vw.x = *reinterpret_cast<const uint32_t*>(&v01); vw.y = *reinterpret_cast<const uint32_t*>(&v23);
-                *reinterpret_cast<uint2*>(K_s + r * kHD + 4 * lane) = kw;
+                // dims 4 lane ..: box lane / 16, chunk (lane % 16) / 2 (swizzled by the row), 8 bytes into it for odd lanes
+                *reinterpret_cast<uint2*>(K_b + (lane >> 4) * kKHalf + r * 128 + (((((lane & 15) >> 1) ^ (r & 7))) << 4) + (lane & 1) * 8) = kw;
                 *reinterpret_cast<uint2*>(V_s + r * kHD + 4 * lane) = vw;
                 const size_t dst = (((size_t)pt[page] * kv.n_kv + kvh) * kPage + r) * kHD + 4 * lane;
                 *reinterpret_cast<uint2*>((__half*)kv.k_pool + dst) = kw;
@@ -229,64 +272,71 @@ __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1) attention
                 __syncwarp();
             }
         }
-        // ---- scores of the page's 16 keys ----
-        float d[GSZ], d2[GSZ];  // two chains per head: even and odd chunks
+        {
+            // ---- scores: C[16 keys x 8 columns] = K[16 x 128] . Q[128 x 8] per n tile, eight k tiles; keys through ldmatrix
+            //      from the swizzled boxes (conflict free), accumulation in f32 ----
+            float c[NT][4];
 #pragma unroll
-        for (int g = 0; g < GSZ; g++) d[g] = d2[g] = 0.f;
-        const __half* krow = K_s + key * kHD + half * 64;
+            for (int nt = 0; nt < NT; nt++) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+            const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;  // the row this lane addresses for ldmatrix
+            const uint32_t lm_row = smem_u32(K_b) + (uint32_t)(lrow * 128);
 #pragma unroll
-        for (int c = 0; c < 8; c++) {
-            const int cc = (c + lane) & 7;  // rotated: the 8 lanes of a quarter warp read 8 different 16-byte bank groups
-            const uint4 kq = *reinterpret_cast<const uint4*>(krow + cc * 8);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&kq);
-            const float2 k0 = __half22float2(h2[0]), k1 = __half22float2(h2[1]), k2 = __half22float2(h2[2]), k3 = __half22float2(h2[3]);
+            for (int kt = 0; kt < 8; kt++) {
+                const int j = (kt & 3) * 2 + (lane >> 4);  // 16-byte chunk of the 128-byte row, box kt / 4
+                uint32_t a0, a1, a2, a3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(lm_row + (kt >> 2) * kKHalf + ((j ^ (lrow & 7)) << 4)));
 #pragma unroll
-            for (int g = 0; g < GSZ; g++) {
-                const float4 qa = *reinterpret_cast<const float4*>(myq + g * kHD + half * 64 + cc * 8);
-                const float4 qb = *reinterpret_cast<const float4*>(myq + g * kHD + half * 64 + cc * 8 + 4);
-                float s0 = (c & 1) ? d2[g] : d[g], s1 = 0.f;
-                s0 = fmaf(qa.x, k0.x, s0); s1 = fmaf(qa.y, k0.y, s1); s0 = fmaf(qa.z, k1.x, s0); s1 = fmaf(qa.w, k1.y, s1);
-                s0 = fmaf(qb.x, k2.x, s0); s1 = fmaf(qb.y, k2.y, s1); s0 = fmaf(qb.z, k3.x, s0); s1 = fmaf(qb.w, k3.y, s1);
-                if (c & 1) d2[g] = s0 + s1; else d[g] = s0 + s1;
+                for (int nt = 0; nt < NT; nt++)
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(c[nt][0]), "+f"(c[nt][1]), "+f"(c[nt][2]), "+f"(c[nt][3])
+                                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(qf[nt][kt][0]), "r"(qf[nt][kt][1]));
             }
-        }
-        if (rg && il == warp) rg[10] = clock64() - loop0;
-        float pk[GSZ];  // this lane's key: exp(score - max) (both lanes of a key hold it)
+            if (rg && il == warp) rg[10] = clock64() - loop0;
+            // this lane: keys lane / 4 and lane / 4 + 8 of head 4 nt + (lane & 3) (hi + lo columns)
+            const int kg = lane >> 2;
+            float pe[NT][2];
 #pragma unroll
-        for (int g = 0; g < GSZ; g++) {
-            const float dg = d[g] + d2[g];
-            float sc = dg + __shfl_xor_sync(0xffffffffu, dg, 1);
-            sc = key < nvalid ? sc / inv_div : -INFINITY;
-            float mx = sc;
+            for (int nt = 0; nt < NT; nt++) {
+                const float s0 = (kg < nvalid) ? (c[nt][0] + c[nt][1]) / inv_div : -INFINITY;
+                const float s1 = (kg + 8 < nvalid) ? (c[nt][2] + c[nt][3]) / inv_div : -INFINITY;
+                float mx = fmaxf(s0, s1);
 #pragma unroll
-            for (int o = 16; o > 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_new = fmaxf(m[g], mx);   // finite: key 0 of every page is valid
-            const float corr = expf(m[g] - m_new);
-            const float pe = expf(sc - m_new);
-            float ps = half == 0 ? pe : 0.f;       // each key once
+                for (int o = 4; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                const float m_new = fmaxf(m_own[nt], mx);  // finite: key 0 of every page is valid
+                const float corr = expf(m_own[nt] - m_new);
+                pe[nt][0] = expf(s0 - m_new);
+                pe[nt][1] = expf(s1 - m_new);
+                float ps = pe[nt][0] + pe[nt][1];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-            l[g] = l[g] * corr + ps;
-            m[g] = m_new;
-            pk[g] = pe;
+                for (int o = 4; o < 32; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+                l_own[nt] = l_own[nt] * corr + ps;
+                m_own[nt] = m_new;
 #pragma unroll
-            for (int i = 0; i < 4; i++) acc[g][i] *= corr;
-        }
-        if (rg && il == warp) rg[11] = clock64() - loop0;
-        // ---- p.V: four dims per lane ----
+                for (int h = 0; h < 4; h++) {
+                    if (4 * nt + h < GSZ) {
+                        const float cg = __shfl_sync(0xffffffffu, corr, h);  // lane h sits in the column of head 4 nt + h
 #pragma unroll
-        for (int j = 0; j < kPage; j++) {
-            uint2 vq = *reinterpret_cast<const uint2*>(V_s + j * kHD + 4 * lane);
-            // rows past this step's position hold whatever the pool held before (Inf, NaN): their zero weight must
-            // meet zeros, not those bytes
-            if (j >= nvalid) vq = make_uint2(0u, 0u);
-            const __half2* h2 = reinterpret_cast<const __half2*>(&vq);
-            const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]);
+                        for (int i = 0; i < 4; i++) acc[4 * nt + h][i] *= cg;
+                    }
+                }
+            }
+            if (rg && il == warp) rg[11] = clock64() - loop0;
+            // ---- p.V: four dims per lane ----
 #pragma unroll
-            for (int g = 0; g < GSZ; g++) {
-                const float pj = __shfl_sync(0xffffffffu, pk[g], 2 * j);
-                acc[g][0] = fmaf(pj, v0.x, acc[g][0]); acc[g][1] = fmaf(pj, v0.y, acc[g][1]);
-                acc[g][2] = fmaf(pj, v1.x, acc[g][2]); acc[g][3] = fmaf(pj, v1.y, acc[g][3]);
+            for (int j = 0; j < kPage; j++) {
+                uint2 vq = *reinterpret_cast<const uint2*>(V_s + j * kHD + 4 * lane);
+                // rows past this step's position hold whatever the pool held before (Inf, NaN): their zero weight must
+                // meet zeros, not those bytes
+                if (j >= nvalid) vq = make_uint2(0u, 0u);
+                const __half2* h2 = reinterpret_cast<const __half2*>(&vq);
+                const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]);
+#pragma unroll
+                for (int g = 0; g < GSZ; g++) {
+                    const float pj = __shfl_sync(0xffffffffu, pe[g >> 2][j >> 3], ((j & 7) << 2) | (g & 3));
+                    acc[g][0] = fmaf(pj, v0.x, acc[g][0]); acc[g][1] = fmaf(pj, v0.y, acc[g][1]);
+                    acc[g][2] = fmaf(pj, v1.x, acc[g][2]); acc[g][3] = fmaf(pj, v1.y, acc[g][3]);
+                }
             }
         }
         __syncwarp();
@@ -405,7 +455,7 @@ int stream_max_contrib(int n_kv) { return sm_count() / n_kv + 3; }
 template <int GSZ>
 size_t stream_fixed_smem() {
     constexpr int kCWarps = consumer_warps<GSZ>();
-    return 128 + (size_t)kCWarps * GSZ * kHD * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
+    return 1024 + (size_t)kCWarps * GSZ * kHD * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
            (size_t)kMaxSeg * GSZ * kStateWords * 4 + 16;
 }
 
@@ -441,7 +491,9 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
         LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
         attr_set[a.qkvf ? 1 : 0] = true;
     }
-    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((consumer_warps<GSZ>() + 1) * 32), smem, s, P));
+    CUtensorMap ktm;
+    memcpy(&ktm, a.kv.k_tmap, sizeof(ktm));
+    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((consumer_warps<GSZ>() + 1) * 32), smem, s, ktm, P));
     return LC_OK;
 }
 
@@ -469,7 +521,7 @@ int32_t attention_stream_reserve(int n_heads, int n_kv) {
 bool attention_stream_applies(const AttnParams& a, int n_tok) {
     static const bool off = getenv("LC_ATTN_NO_STREAM") != nullptr;
     const int gsz = a.kv.n_kv > 0 ? a.n_heads / a.kv.n_kv : 0;
-    return !off && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
+    return !off && a.kv.k_tmap != nullptr && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
            (gsz == 1 || gsz == 2 || gsz == 4 || gsz == 8);
 }
 

@@ -65,6 +65,9 @@ struct lc_model {
 
     // KV cache
     std::vector<void*> k_pools, v_pools;  // per layer
+    struct alignas(64) TmapBytes { unsigned char b[128]; };
+    std::vector<TmapBytes> k_tmaps;       // per layer: tensor map over the key pool (f16 pools of 128-dim heads)
+    bool k_tmaps_ok = false;
     std::vector<int> free_pages;
     std::vector<std::vector<int>> seq_pages;
     std::vector<int> seq_len;
@@ -230,6 +233,7 @@ KvLayout kv_layout(const lc_model* m, int layer) {
     kv.hd = m->hd;
     kv.page_tokens = m->page_tokens;
     kv.kv_f32 = m->cfg.kv_dtype;
+    kv.k_tmap = m->k_tmaps_ok ? (const void*)m->k_tmaps[layer].b : nullptr;
     return kv;
 }
 
@@ -793,6 +797,13 @@ int32_t lc_model_finalize(lc_model* m) {
         LC_TRY(dalloc((uint8_t**)&m->k_pools[l], (size_t)m->pages_total * page_elems * m->kv_elt));
         LC_TRY(dalloc((uint8_t**)&m->v_pools[l], (size_t)m->pages_total * page_elems * m->kv_elt));
     }
+    if (m->hd == 128 && m->cfg.kv_dtype == 0 && m->page_tokens == 16) {  // what the streaming attention kernel reads keys through
+        m->k_tmaps.resize(m->L);
+        m->k_tmaps_ok = true;
+        for (int l = 0; l < m->L && m->k_tmaps_ok; l++)
+            m->k_tmaps_ok = make_key_pool_tmap(m->k_tmaps[l].b, m->k_pools[l], (uint64_t)m->pages_total * m->nkv * m->page_tokens);
+    }
+    m->dataflow_ready = m->dataflow_ready && m->k_tmaps_ok;
     m->free_pages.resize(m->pages_total);
     for (int i = 0; i < m->pages_total; i++) m->free_pages[i] = m->pages_total - 1 - i;
     m->seq_pages.assign(m->max_seqs, {});
@@ -979,7 +990,7 @@ int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_
 // CUDA graph that later steps replay.
 static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
     auto one_step = [&]() -> int32_t {
-        static const bool no_dataflow = getenv("LC_NO_DATAFLOW") != nullptr;
+        const bool no_dataflow = getenv("LC_NO_DATAFLOW") != nullptr;  // read when the step is queued (a captured graph keeps its mode)
         m->dataflow_step = n_seqs == 1 && m->dataflow_ready && !no_dataflow && ablate_mask() == 0;
         int32_t fs = forward_tokens(m, n_seqs, n_seqs, true, 0);
         m->dataflow_step = false;

@@ -92,7 +92,9 @@ struct KvLayout {
     void* v_pool = nullptr;
     int n_kv = 0, hd = 0, page_tokens = 16;
     int kv_f32 = 0;
+    const void* k_tmap = nullptr;  // host copy of a tensor map over k_pool (make_key_pool_tmap), or null
 };
+bool make_key_pool_tmap(void* out128, const void* pool, uint64_t rows);
 // For each of the `n_tok` new tokens (token i belongs to sequence row tok_seq[i], at cache
 // position tok_pos[i], with rotary position tok_rope[i]): rotate q and k in place
 // (rust/src/inference/attention.rs:13-34; q, k, v rows are row_stride floats apart) and store k, v into the paged cache

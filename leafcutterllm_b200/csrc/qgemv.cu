@@ -88,6 +88,20 @@ int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int 
     return LC_OK;
 }
 
+// Tensor map over an f16 key pool [rows][128 dims]: boxes of 16 rows x 64 dims (128 bytes), 128-byte swizzle, so that
+// a staged page can be read with ldmatrix without bank conflicts.  false when the driver entry point is missing.
+bool make_key_pool_tmap(void* out128, const void* pool, uint64_t rows) {
+    if (!encode_fn() || ((uintptr_t)pool % 16) != 0) return false;
+    cuuint64_t dims[2] = {128, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {256};
+    cuuint32_t box[2] = {64, 16};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()((CUtensorMap*)out128, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)pool, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // ---------------------------------------------------------------------------
 // per-unit dot products.  `r` = the lane's unit in registers, xs = x of this
 // unit for token t at xs + t*xstride (256 floats), sx = per-32 sums of x.

@@ -100,6 +100,15 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         l2_prefetch_part(p.prefetch.p[0], p.prefetch.bytes[0], blockIdx.x, gridDim.x);
         l2_prefetch_part(p.prefetch.p[1], p.prefetch.bytes[1], blockIdx.x, gridDim.x);
     }
+    // One token whose k fits one unit per warp: each warp reads its own 256 elements ONCE, for the sum of squares and for
+    // the planes, and the gains (weights: no dependency on the kernel ahead) are already in registers by then.
+    const bool one_pass = (M == 1) && p.norm_w != nullptr && nunits <= WARPS;
+    float nw0[8];
+    if (one_pass && warp < nunits) {
+        const float4* np = reinterpret_cast<const float4*>(p.norm_w + warp * kUnitElems + 8 * lane);
+        const float4 n0 = np[0], n1 = np[1];
+        nw0[0] = n0.x; nw0[1] = n0.y; nw0[2] = n0.z; nw0[3] = n0.w; nw0[4] = n1.x; nw0[5] = n1.y; nw0[6] = n1.z; nw0[7] = n1.w;
+    }
     pdl_launch_dependents();
     // Dataflow mode: the input words carry the epoch of this step's producer, so the kernel goes ahead as soon as the
     // producing CTAs have written them instead of waiting for the producing grid (and everything before it) to drain.
@@ -115,7 +124,30 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     if (rg) rg[1] = gtime();
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
-    if (p.norm_w) {
+    float v0[8];
+    float rms0 = 1.f;
+    if (one_pass) {
+        float ss = 0.f;
+        if (warp < nunits) {
+            const int e0 = warp * kUnitElems + 8 * lane;
+            if (flagged_in) {
+                in_ok = flag_load<8>(p.xf + e0, epoch_in, v0) && in_ok;
+            } else {
+                const float4* xp = reinterpret_cast<const float4*>(p.x + e0);
+                const float4 u0 = xp[0], u1 = xp[1];
+                v0[0] = u0.x; v0[1] = u0.y; v0[2] = u0.z; v0[3] = u0.w; v0[4] = u1.x; v0[5] = u1.y; v0[6] = u1.z; v0[7] = u1.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) ss = fmaf(v0[j], v0[j], ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) scratch[warp] = ss;
+        __syncthreads();
+        float r = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) r += scratch[w];  // every thread, same order
+        rms0 = 1.0f / sqrtf(r / (float)p.k + p.eps);
+    } else if (p.norm_w) {
         for (int tk = 0; tk < M; tk++) {
             float ss = 0.f;
             if (tk < p.m) {
@@ -150,7 +182,10 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         for (int tk = 0; tk < M; tk++) {
             float v[8];
             const int e0 = unit * kUnitElems + 8 * lane;
-            if (tk < p.m) {
+            if (one_pass) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = (v0[j] * rms0) * nw0[j];
+            } else if (tk < p.m) {
                 if (flagged_in) {
                     in_ok = flag_load<8>(p.xf + e0, epoch_in, v) && in_ok;
                 } else {

@@ -184,3 +184,31 @@ def test_decode_ignores_unwritten_cache_rows(gpu, oracle, monkeypatch, mega):
     toks = eng.generate(prompt, 40, stop_on_eos=False)
     assert toks == ref, margins
     eng.close()
+
+
+@pytest.mark.parametrize("heads,kv", [(4, 4), (4, 2), (8, 2)])
+def test_dataflow_step_equals_the_step_with_grid_waits(gpu, oracle, monkeypatch, heads, kv):
+    """Single-sequence decode on a Q4_K model with head_dim 128: the kernels of a step pass activations as epoch-tagged
+    words and do not wait for each other's grids.  Same tokens as the oracle, and the same bits as the mode in which
+    every kernel waits for the grid ahead of it (same kernels, same arithmetic, different hand-over)."""
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=3, hidden=128 * heads, heads=heads, kv=kv, ffn=1024, vocab=1200)
+    prompt = synth.prompt_tokens(37, spec.vocab_size, 11)
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=192)
+    ref, margins = om.generate(prompt, 56, stop_on_eos=False, want_margins=True)
+    assert eng.generate(prompt, 56, stop_on_eos=False) == ref, margins
+    eng.kv_clear()
+    logits = [eng.forward(prompt)]
+    for t in ref[:6]:
+        logits.append(eng.forward([t]))
+    eng.close()
+    monkeypatch.setenv("LC_NO_DATAFLOW", "1")
+    eng2, _ = make_pair(gpu, oracle, spec, max_seq_len=192)
+    assert eng2.generate(prompt, 56, stop_on_eos=False) == ref
+    eng2.kv_clear()
+    logits2 = [eng2.forward(prompt)]
+    for t in ref[:6]:
+        logits2.append(eng2.forward([t]))
+    eng2.close()
+    for a, b in zip(logits, logits2):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
