@@ -176,6 +176,41 @@ def cpu_baseline(spec, steps: int = 4, layers: int = 2, prompt: int = 64, thread
             "reference_faithful_note": "per-call re-dequantise + transpose of every tensor as engine.rs:95-97, same sample and scaling"}
 
 
+def gemv_sweep(lc) -> dict:
+    """Q4_K GEMV (one token) timed alone for a range of row counts: back-to-back launches over >= 600 MB of distinct
+    weights per shape, CUDA events on the library's stream.  Shows the streaming rate and the fixed cost per launch."""
+    import ctypes as C
+    lib = lc.load()
+    chk = lc._capi.check
+    rows = []
+    for (k, n) in [(4096, 4096), (4096, 12288), (4096, 32768), (4096, 131072), (11008, 4096)]:
+        nb = lib.lc_tensor_bytes(12, k * n)
+        copies = max(2, int(600e6 // nb))
+        x = C.c_void_p(); y = C.c_void_p()
+        chk(lib.lc_dev_alloc(4 * k, C.byref(x))); chk(lib.lc_dev_alloc(4 * n, C.byref(y)))
+        chk(lib.lc_synth_tensor_dev(0, 1, b"x", 1.0, k, x))
+        ws = []
+        for c in range(copies):
+            p = C.c_void_p()
+            chk(lib.lc_dev_alloc(nb, C.byref(p)))
+            chk(lib.lc_synth_tensor_dev(12, 7, f"w{c}".encode(), 0.02, k * n, p))
+            ws.append(p)
+        for p in ws:
+            chk(lib.lc_qmatmul_dev(12, x, p, 1, k, n, y))
+        chk(lib.lc_dev_sync()); chk(lib.lc_timer_begin())
+        reps = 5
+        for _ in range(reps):
+            for p in ws:
+                chk(lib.lc_qmatmul_dev(12, x, p, 1, k, n, y))
+        ms = C.c_float(); chk(lib.lc_timer_end(C.byref(ms)))
+        for p in ws:
+            lib.lc_dev_free(p)
+        lib.lc_dev_free(x); lib.lc_dev_free(y)
+        us = ms.value * 1e3 / (reps * copies)
+        rows.append({"k": k, "n": n, "MB": round(nb / 1e6, 2), "us_per_launch": round(us, 2), "GBps": round(nb / us / 1e3, 1)})
+    return {"kernel": "Q4_K GEMV, one token" + (" (tcgen05 variant)" if os.environ.get("LC_GEMV_UMMA") else ""), "sweep": rows}
+
+
 def gemv_roofline(lc, spec, reps: int = 3, copies: int = 8, warm: int = 3) -> dict:
     """The dominant kernel (quantised GEMV, one launch per weight matrix) timed alone with CUDA events on the
     library's stream over 8 distinct copies of a layer's matrices (0.9 GB, larger than L2)."""
@@ -284,7 +319,7 @@ def run_ours(args):
     ranks = Ranks(rank, world, local, "nccl")
     barrier_max = ranks.barrier_max
 
-    spec = synth.LLAMA7B
+    spec = synth.LLAMA7B if args.layers <= 0 else synth.LLAMA7B.with_layers(args.layers)
     e2e_steps = min(args.steps, 64)
     plen = args.prompt_len
     cap = plen + args.warmup + args.steps + e2e_steps + 3 + 64
@@ -343,6 +378,8 @@ def run_ours(args):
         "step_roofline": {"algorithmic_bytes_per_step": int(algo), "achieved_gbs": round(algo / (ms_max / args.steps * 1e-3) / 1e9, 1),
                           "peak_gbs": peak, "frac": round(algo / (ms_max / args.steps * 1e-3) / 1e9 / peak, 4), "peak_source": which},
     }
+    if args.layers > 0:
+        line["not_the_metric"] = f"profiling case: {args.layers} of 32 layers"
     if rank == 0:
         line["roofline"] = gemv_roofline(lc, spec)
         if world == 1 and not args.no_cpu:
@@ -384,13 +421,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers)")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
     ap.add_argument("--profile-range", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop")
+    ap.add_argument("--layers", type=int, default=0, help="profiling only: keep this many of the 32 layers (the printed number is then not the metric)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="context prefilled before decoding (default: the 2048 of the workload)")
     args = ap.parse_args()
     if args.only == "attn":
         import leafcutterllm_b200 as lc
         print(json.dumps(attention_microbench(lc)))
+    elif args.only == "gemv-sweep":
+        import leafcutterllm_b200 as lc
+        print(json.dumps(gemv_sweep(lc)))
     elif args.only == "gemv":
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth

@@ -115,6 +115,23 @@ __device__ __forceinline__ bool flag_load_strided(const unsigned long long* p, i
     for (int i = 0; i < N; i++) v[i] = (i * stride < limit) ? __uint_as_float((uint32_t)w[i]) : 0.f;
     return all;
 }
+// A warp waits for 256 consecutive words by watching eight of them (the last of every 32: producers write 32 rows per
+// tile), so that a kernel whose input is still being produced does not sweep its whole input through L2 over and over
+// while the producers need that bandwidth for their weights.  The caller still fetches with flag_load afterwards.
+__device__ __forceinline__ bool flag_watch_unit(const unsigned long long* unit_base, uint32_t epoch) {
+    const int lane = threadIdx.x & 31;
+    bool all = false;
+    for (uint32_t it = 0; it < (1u << 20) && !all; ++it) {
+        bool mine = true;
+        if (lane < 8) {
+            unsigned long long w;
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(unit_base + 32 * lane + 31) : "memory");
+            mine = (uint32_t)(w >> 32) == epoch;
+        }
+        all = __all_sync(0xffffffffu, mine);
+    }
+    return all;
+}
 // the value of a word known to be complete
 __device__ __forceinline__ float flag_value(const unsigned long long* p) {
     unsigned long long w;

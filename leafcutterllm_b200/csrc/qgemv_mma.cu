@@ -131,6 +131,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         if (warp < nunits) {
             const int e0 = warp * kUnitElems + 8 * lane;
             if (flagged_in) {
+                in_ok = flag_watch_unit(p.xf + warp * kUnitElems, epoch_in) && in_ok;
                 in_ok = flag_load<8>(p.xf + e0, epoch_in, v0) && in_ok;
             } else {
                 const float4* xp = reinterpret_cast<const float4*>(p.x + e0);
@@ -187,6 +188,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 for (int j = 0; j < 8; j++) v[j] = (v0[j] * rms0) * nw0[j];
             } else if (tk < p.m) {
                 if (flagged_in) {
+                    in_ok = flag_watch_unit(p.xf + unit * kUnitElems, epoch_in) && in_ok;
                     in_ok = flag_load<8>(p.xf + e0, epoch_in, v) && in_ok;
                 } else {
                     const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);

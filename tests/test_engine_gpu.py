@@ -194,6 +194,7 @@ def test_dataflow_step_equals_the_step_with_grid_waits(gpu, oracle, monkeypatch,
     from leafcutterllm_b200 import synth
     spec = small_spec(12, 12, 12, layers=3, hidden=128 * heads, heads=heads, kv=kv, ffn=1024, vocab=1200)
     prompt = synth.prompt_tokens(37, spec.vocab_size, 11)
+    monkeypatch.setenv("LC_DATAFLOW", "1")
     eng, om = make_pair(gpu, oracle, spec, max_seq_len=192)
     ref, margins = om.generate(prompt, 56, stop_on_eos=False, want_margins=True)
     assert eng.generate(prompt, 56, stop_on_eos=False) == ref, margins
@@ -201,8 +202,9 @@ def test_dataflow_step_equals_the_step_with_grid_waits(gpu, oracle, monkeypatch,
     logits = [eng.forward(prompt)]
     for t in ref[:6]:
         logits.append(eng.forward([t]))
+    launches = eng.counters()["kernel_launches"]
     eng.close()
-    monkeypatch.setenv("LC_NO_DATAFLOW", "1")
+    monkeypatch.delenv("LC_DATAFLOW")
     eng2, _ = make_pair(gpu, oracle, spec, max_seq_len=192)
     assert eng2.generate(prompt, 56, stop_on_eos=False) == ref
     eng2.kv_clear()
