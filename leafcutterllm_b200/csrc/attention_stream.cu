@@ -74,8 +74,10 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = P.nstages;
     unsigned char* ring = smem;                                             // [S][kStageBytes]
-    float* q_s = reinterpret_cast<float*>(ring + (size_t)S * kStageBytes);  // [kCWarps][GSZ][kHD] the warp's rotated queries
-    float* st_s = q_s + kCWarps * GSZ * kHD;                                // [kMaxSeg][kCWarps][GSZ][kStateWords]
+    constexpr int NTc = (2 * GSZ + 7) / 8;                                  // n tiles of the score product (see below)
+    float* q_s = reinterpret_cast<float*>(ring + (size_t)S * kStageBytes);  // [kMaxSeg][GSZ][kHD] rotated queries of the run's kv heads
+    uint32_t* qf_s = reinterpret_cast<uint32_t*>(q_s + kMaxSeg * GSZ * kHD);  // [kMaxSeg][NTc][16][32] their B fragments, lane-major
+    float* st_s = reinterpret_cast<float*>(qf_s + kMaxSeg * NTc * 16 * 32);   // [kMaxSeg][kCWarps][GSZ][kStateWords]
     float* cta_s = st_s + kMaxSeg * kCWarps * GSZ * kStateWords;            // [kMaxSeg][GSZ][kStateWords] combined over warps
     uint64_t* full = reinterpret_cast<uint64_t*>(((uintptr_t)(cta_s + kMaxSeg * GSZ * kStateWords) + 7) & ~(uintptr_t)7);  // [S]
     uint64_t* empty = full + S;                                             // [S]
@@ -158,7 +160,9 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
                               : __fadd_rn(__fmul_rn(other[i], sa), __fmul_rn(own[i], ca));
         }
     };
-    const float inv_div = sqrtf((float)kHD);  // attention.rs:93: dot / sqrt(head_dim)
+    // attention.rs:93-102: softmax(dot / sqrt(head_dim)).  Scores are kept multiplied by log2(e) so that every exponential is a
+    // single ex2; the running maximum is in the same units and goes back to natural units when a warp's state is written out.
+    const float sc_log2e = 1.4426950408889634f / sqrtf((float)kHD);
 
     // Scores run on the tensor cores: C[16 keys x 8 columns] per n tile, two columns (f16 hi and lo part of q) per query
     // head, so an n tile serves four heads and lane (row, t) of the C fragment belongs to head 4 nt + t.
@@ -173,7 +177,6 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
         for (int g = 0; g < GSZ; g++) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
     };
     reset();
-    float* myq = q_s + (size_t)warp * GSZ * kHD;
     int cur_seg = -1;
     long long wait_cycles = 0;
     const long long loop0 = clock64();
@@ -185,7 +188,10 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
         if (lane < 4) {  // lanes 0-3: row 0 of the C fragment, columns of heads 4 nt + lane
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
-                if (4 * nt + lane < GSZ) { dst[(4 * nt + lane) * kStateWords] = m_own[nt]; dst[(4 * nt + lane) * kStateWords + 1] = l_own[nt]; }
+                if (4 * nt + lane < GSZ) {
+                    dst[(4 * nt + lane) * kStateWords] = m_own[nt] * 0.6931471805599453f;  // back to natural-log units
+                    dst[(4 * nt + lane) * kStateWords + 1] = l_own[nt];
+                }
         }
     };
     // every (segment, warp) slot starts empty: a warp may meet no item of a segment
@@ -193,51 +199,57 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
         st_s[(size_t)i * kStateWords] = -INFINITY;
         st_s[(size_t)i * kStateWords + 1] = 0.f;
     }
+    // ---- the queries of the run's kv heads, once per CTA: warp w stages head vector w, w + kCWarps, ... (rotated,
+    //      attention.rs:13-34), then the B fragments of the score product are cut from them ----
+    const int nseg_run = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
+    for (int hv = warp; hv < nseg_run * GSZ; hv += kCWarps) {
+        const int sl = hv / GSZ, g = hv - sl * GSZ;
+        float qv[4];
+        head_vec(p.q, (size_t)((seg0 + sl) * GSZ + g) * kHD, qv);
+        *reinterpret_cast<float4*>(q_s + (size_t)hv * kHD + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
+    // B operand of mma.m16n8k16 (16 dims x 8 columns): column 2h = f16(q of head 4 nt + h), column 2h + 1 = f16 of what
+    // that rounding lost, so products with the f16 keys are exact and q keeps ~22 bits.  Lane (col = lane / 4, t = lane % 4)
+    // holds column col, dims 2t, 2t+1 (register 0) and 2t+8, 2t+9 (register 1) of each 16-dim tile.
+    for (int w = warp; w < nseg_run * NTc * 8; w += kCWarps) {  // one (segment, n tile, k tile) per warp and turn
+        const int kt = w & 7, nt = (w >> 3) % NTc, sl = (w >> 3) / NTc;
+        const int col = lane >> 2, t4 = lane & 3, hq = 4 * nt + (col >> 1);
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            uint32_t word = 0u;
+            if (hq < GSZ) {
+                const float2 x = *reinterpret_cast<const float2*>(q_s + (size_t)(sl * GSZ + hq) * kHD + kt * 16 + 2 * t4 + 8 * r);
+                __half h0 = __float2half_rn(x.x), h1 = __float2half_rn(x.y);
+                if (col & 1) { h0 = __float2half_rn(x.x - __half2float(h0)); h1 = __float2half_rn(x.y - __half2float(h1)); }
+                const __half2 hh = __halves2half2(h0, h1);
+                word = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+            qf_s[(((size_t)sl * NTc + nt) * 16 + kt * 2 + r) * 32 + lane] = word;
+        }
+    }
     asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
 
+    // this warp's items: il = warp, warp + kCWarps, ...; their kv head, page, stage and stage phase follow without divisions
+    int kvh_i = n_items > 0 ? (i_begin + warp) / np : 0, page_i = n_items > 0 ? (i_begin + warp) - kvh_i * np : 0;
+    int st_i = warp % S, par_i = (warp / S) & 1;
     for (int il = warp; il < n_items; il += kCWarps) {
-        const int gi = i_begin + il;
-        const int kvh = gi / np, page = gi - kvh * np;
+        const int kvh = kvh_i, page = page_i, st = st_i, st_par = par_i;
+        page_i += kCWarps;
+        while (page_i >= np) { page_i -= np; kvh_i++; }
+        st_i += kCWarps;
+        while (st_i >= S) { st_i -= S; par_i ^= 1; }
         if (kvh != cur_seg) {
             if (cur_seg >= 0) flush(cur_seg);
             reset();
             cur_seg = kvh;
-            __syncwarp();
 #pragma unroll
-            for (int g = 0; g < GSZ; g++) {  // rotated queries of the kv group (attention.rs:13-34)
-                float qv[4];
-                head_vec(p.q, (size_t)(kvh * GSZ + g) * kHD, qv);
-                *reinterpret_cast<float4*>(myq + g * kHD + 4 * lane) = make_float4(qv[0], qv[1], qv[2], qv[3]);
-            }
-            __syncwarp();
-            {
-                // B operand of mma.m16n8k16 (16 dims x 8 columns): column 2h = f16(q of head 4 nt + h), column 2h + 1 = f16 of
-                // what that rounding lost, so products with the f16 keys are exact and q keeps ~22 bits.  This lane holds
-                // column lane / 4, dims 2t, 2t+1, 2t+8, 2t+9 of each tile.
-                const int col = lane >> 2, t4 = lane & 3;
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const int hq = 4 * nt + (col >> 1);
-#pragma unroll
-                    for (int kt = 0; kt < 8; kt++) {
-#pragma unroll
-                        for (int r = 0; r < 2; r++) {
-                            float x0 = 0.f, x1 = 0.f;
-                            if (hq < GSZ) { x0 = myq[hq * kHD + kt * 16 + 2 * t4 + 8 * r]; x1 = myq[hq * kHD + kt * 16 + 2 * t4 + 8 * r + 1]; }
-                            __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
-                            if (col & 1) { h0 = __float2half_rn(x0 - __half2float(h0)); h1 = __float2half_rn(x1 - __half2float(h1)); }
-                            const __half2 hh = __halves2half2(h0, h1);
-                            qf[nt][kt][r] = (hq < GSZ) ? *reinterpret_cast<const uint32_t*>(&hh) : 0u;
-                        }
-                    }
-                }
-            }
+                for (int i = 0; i < 16; i++) qf[nt][i >> 1][i & 1] = qf_s[(((size_t)(kvh - seg0) * NTc + nt) * 16 + i) * 32 + lane];
         }
         if (rg && il == warp) rg[8] = clock64() - loop0;
-        const int st = il % S;
-        const long long tw0 = clock64();
-        ok = mbar_wait(&full[st], (uint32_t)((il / S) & 1)) && ok;
-        wait_cycles += clock64() - tw0;
+        ok = mbar_wait(&full[st], (uint32_t)st_par) && ok;
         if (rg && il == warp) rg[9] = clock64() - loop0;
         unsigned char* K_b = ring + (size_t)st * kStageBytes;           // two swizzled boxes: dims 0-63, dims 64-127
         __half* V_s = reinterpret_cast<__half*>(K_b + 2 * kKHalf);
@@ -298,15 +310,16 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
             float pe[NT][2];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const float s0 = (kg < nvalid) ? (c[nt][0] + c[nt][1]) / inv_div : -INFINITY;
-                const float s1 = (kg + 8 < nvalid) ? (c[nt][2] + c[nt][3]) / inv_div : -INFINITY;
+                // scores in units of log2(e): (dot / sqrt(head_dim)) * log2(e), so that exp() is one ex2
+                const float s0 = (kg < nvalid) ? (c[nt][0] + c[nt][1]) * sc_log2e : -INFINITY;
+                const float s1 = (kg + 8 < nvalid) ? (c[nt][2] + c[nt][3]) * sc_log2e : -INFINITY;
                 float mx = fmaxf(s0, s1);
 #pragma unroll
                 for (int o = 4; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
                 const float m_new = fmaxf(m_own[nt], mx);  // finite: key 0 of every page is valid
-                const float corr = expf(m_own[nt] - m_new);
-                pe[nt][0] = expf(s0 - m_new);
-                pe[nt][1] = expf(s1 - m_new);
+                const float corr = exp2f(m_own[nt] - m_new);
+                pe[nt][0] = exp2f(s0 - m_new);
+                pe[nt][1] = exp2f(s1 - m_new);
                 float ps = pe[nt][0] + pe[nt][1];
 #pragma unroll
                 for (int o = 4; o < 32; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
@@ -455,7 +468,8 @@ int stream_max_contrib(int n_kv) { return sm_count() / n_kv + 3; }
 template <int GSZ>
 size_t stream_fixed_smem() {
     constexpr int kCWarps = consumer_warps<GSZ>();
-    return 1024 + (size_t)kCWarps * GSZ * kHD * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
+    constexpr int NTc = (2 * GSZ + 7) / 8;
+    return 1024 + (size_t)kMaxSeg * GSZ * kHD * 4 + (size_t)kMaxSeg * NTc * 16 * 32 * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
            (size_t)kMaxSeg * GSZ * kStateWords * 4 + 16;
 }
 

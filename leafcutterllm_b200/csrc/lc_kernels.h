@@ -46,6 +46,7 @@ struct QWeight {
     size_t row_bytes = 0;
     alignas(64) unsigned char tmap[128];      // CUtensorMap for the TMA-staged kernels: box = one 256-element unit x 32 rows
     alignas(64) unsigned char tmap_wide[128]; // the same tensor with a box of 128 rows (tcgen05 kernel)
+    alignas(64) unsigned char tmap_half[128]; // ... and of 16 rows (finer tiles where they balance the SMs better)
     bool has_tmap = false;
 };
 int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int k);

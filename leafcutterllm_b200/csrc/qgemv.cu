@@ -84,6 +84,13 @@ int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int 
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             w->has_tmap = (r == CUDA_SUCCESS);
         }
+        if (w->has_tmap) {
+            cuuint32_t half[2] = {(cuuint32_t)(ub / 4), 16u};
+            r = encode_fn()((CUtensorMap*)w->tmap_half, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)data_dev, dims, strides, half,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            w->has_tmap = (r == CUDA_SUCCESS);
+        }
     }
     return LC_OK;
 }

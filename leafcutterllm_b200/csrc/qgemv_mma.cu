@@ -40,17 +40,19 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
     return ((unit * 8 + sb) * M + tok) * 96 + plane * 32;
 }
 
-template <int M, int WARPS, int STAGES>
+// RG = 16-row groups per tile (2: 32-row tiles; 1: 16-row tiles, chosen when that spreads the rows more evenly over the SMs).
+template <int M, int WARPS, int STAGES, int RG = 2>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p) {
     constexpr int UB = 144;
-    constexpr int STAGE_BYTES = UB * kTileRows;
+    constexpr int TR = 16 * RG;  // rows per tile
+    constexpr int STAGE_BYTES = UB * TR;
     constexpr int NPAIR = (M + 1) / 2;
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int nunits = p.k / kUnitElems;
-    const int ntiles = (p.n + kTileRows - 1) / kTileRows;
+    const int ntiles = (p.n + TR - 1) / TR;
     const int nmat = (p.epi == EPI_SILU_MUL) ? 2 : 1;
 
     auto gtime = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
@@ -85,7 +87,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         const int st = pj & (STAGES - 1);
         mbar_expect_tx(&bars[st], STAGE_BYTES);
         tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, p_mat ? &tm1 : &tm0, (warp + p_ui * WARPS) * (UB / 4),
-                    (blockIdx.x + p_ti * gridDim.x) * kTileRows, &bars[st]);
+                    (blockIdx.x + p_ti * gridDim.x) * TR, &bars[st]);
         pj++;
         if (++p_ui == units_mine) { p_ui = 0; if (++p_mat == nmat) { p_mat = 0; ++p_ti; } }
     };
@@ -287,9 +289,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         const int tile = blockIdx.x + ti * gridDim.x;
         for (int mat = 0; mat < nmat; mat++) {
             // per-thread partial row sums (the 4 threads of a row are added once per tile)
-            float yacc[2][2][M];  // [row group][row g / g+8][token]
+            float yacc[RG][2][M];  // [row group][row g / g+8][token]
 #pragma unroll
-            for (int a = 0; a < 2; a++)
+            for (int a = 0; a < RG; a++)
 #pragma unroll
                 for (int b = 0; b < 2; b++)
 #pragma unroll
@@ -301,7 +303,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 ok = ok && mbar_wait(&bars[st], (uint32_t)((job / STAGES) & 1));
                 const unsigned char* tilep = stage_base + (size_t)st * STAGE_BYTES;
 #pragma unroll
-                for (int rg = 0; rg < 2; rg++) {
+                for (int rg = 0; rg < RG; rg++) {
                     const unsigned char* rowA = tilep + (rg * 16 + g) * UB;
                     const unsigned char* rowB = rowA + 8 * UB;
                     const uint4 hA = *reinterpret_cast<const uint4*>(rowA);
@@ -365,7 +367,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             }
             // add the four threads that share a row (fixed order)
 #pragma unroll
-            for (int a = 0; a < 2; a++)
+            for (int a = 0; a < RG; a++)
 #pragma unroll
                 for (int b = 0; b < 2; b++)
 #pragma unroll
@@ -380,7 +382,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             float* rb = red + (size_t)(seq & 1) * WARPS * M * 32;
             if (t == 0) {
 #pragma unroll
-                for (int rg = 0; rg < 2; rg++)
+                for (int rg = 0; rg < RG; rg++)
 #pragma unroll
                     for (int tk = 0; tk < M; tk++) {
                         rb[(warp * M + tk) * 32 + rg * 16 + g] = yacc[rg][0][tk];
@@ -393,7 +395,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 float y = 0.f;
 #pragma unroll 4
                 for (int w = 0; w < WARPS; w++) y += rb[(w * M + tk) * 32 + lane];
-                const int row = tile * kTileRows + lane;
+                const int row = lane < TR ? tile * TR + lane : p.n;  // lanes past the tile's rows hold nothing
                 bool have = false;
                 if (p.epi == EPI_SILU_MUL) {
                     if (mat == 0) {
@@ -438,10 +440,10 @@ void dump_mring() {
 }
 }  // namespace
 
-template <int M, int WARPS, int STAGES>
+template <int M, int WARPS, int STAGES, int RG = 2>
 static size_t mma_smem_bytes(int k) {
     int nunits = k / kUnitElems;
-    size_t b = (size_t)WARPS * STAGES * 144 * kTileRows;
+    size_t b = (size_t)WARPS * STAGES * 144 * 16 * RG;
     b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * M * 8 * 4 + (size_t)nunits * M * 4;
     b += (size_t)2 * WARPS * M * 32 * 4 + (size_t)M * 32 * 4 + (size_t)(32 + M) * 4;
     b = (b + 7) & ~(size_t)7;
@@ -449,10 +451,10 @@ static size_t mma_smem_bytes(int k) {
     return b;
 }
 
-template <int M, int WARPS, int STAGES>
+template <int M, int WARPS, int STAGES, int RG = 2>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
-    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES>;
-    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k);
+    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, RG>;
+    size_t smem = mma_smem_bytes<M, WARPS, STAGES, RG>(a.w->k);
     static bool attr_set = false;
     if (!attr_set) {
         LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
@@ -472,14 +474,14 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
         p.ring = g_mring + (size_t)(g_mring_seq++ % 1024) * 8;
     }
     p.xf = a.x_flag; p.outf = a.out_flag; p.resf = a.residual_flag; p.step_ctr = a.step_ctr; p.node_in = a.node_in; p.node_out = a.node_out;
-    int ntiles = (p.n + kTileRows - 1) / kTileRows;
+    int ntiles = (p.n + 16 * RG - 1) / (16 * RG);
     // CTAs per SM that fit shared memory (and, for the 8-warp shape, registers): with two per SM the
     // first CTAs of the next kernel move in while the last CTAs of this one drain
     int per_sm = (WARPS <= 8 && M <= 2 && 2 * (smem + 1024) <= kMaxSmem + 1024) ? 2 : 1;
     int grid = sm_count() * per_sm;
     if (grid > ntiles) grid = ntiles;
-    const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap;
-    const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap : t0;
+    const CUtensorMap* t0 = (const CUtensorMap*)(RG == 1 ? a.w->tmap_half : a.w->tmap);
+    const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)(RG == 1 ? a.w2->tmap_half : a.w2->tmap) : t0;
     LC_CUDA(launch_pdl(kern, dim3(grid), dim3(WARPS * 32), smem, s, *t0, *t1, p));
     return LC_OK;
 }
@@ -493,6 +495,15 @@ static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
         if (cfg == 1 && mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2>(a, s);
         if (cfg == 2 && mma_smem_bytes<M, 8, 4>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 4>(a, s);
         if (cfg == 3 && mma_smem_bytes<M, 16, 4>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 4>(a, s);
+    }
+    if constexpr (M == 1) {
+        // 16-row tiles where they lower the most rows any SM gets (11008 rows over 148 SMs: 80 instead of 96).  Opt-in:
+        // measured 1.59 ms per decode step against 1.52 ms with 32-row tiles -- twice the per-tile reductions and
+        // barriers cost more than the better balance returns.
+        static const bool half_tiles = getenv("LC_GEMV_HALF_TILES") != nullptr;
+        const int G = sm_count();
+        const int rows32 = ((a.w->n + 31) / 32 + G - 1) / G * 32, rows16 = ((a.w->n + 15) / 16 + G - 1) / G * 16;
+        if (half_tiles && rows16 < rows32 && mma_smem_bytes<1, 16, 4, 1>(k) <= kMaxSmem) return launch_mma_cfg<1, 16, 4, 1>(a, s);
     }
     if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
         if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2>(a, s);
