@@ -358,6 +358,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
         if (lane == 0 && il + S < n_items) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[st])) : "memory");
     }
     if (cur_seg >= 0) flush(cur_seg);
+    if (P.ring && tid == 0) atomicMax(P.ring + (size_t)P.ring_slot * 16 + 14, gtime());  // the last CTA whose warp 0 finished its items
     if (rg) { rg[2] = gtime(); rg[5] = ((unsigned long long)wait_cycles << 32) | (unsigned long long)(unsigned)(clock64() - loop0); }
     asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
     if (rg) rg[3] = gtime();
@@ -398,14 +399,15 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
             if (dx == 0) { put(mine, M); put(mine + 1, L); }
             put(mine + 2 + dx, A);
         } else {
-            // the head's first CTA collects the others in CTA order; the three words of up to four contributors are
+            // the head's first CTA collects the others in CTA order; the three words of up to eight contributors are
             // requested together so that one memory round trip serves them all
-            for (int c0 = 1; c0 < nc; c0 += 4) {
-                unsigned long long wv[4][3];
+            constexpr int kBatch = 8;
+            for (int c0 = 1; c0 < nc; c0 += kBatch) {
+                unsigned long long wv[kBatch][3];
                 bool all = false;
                 for (uint32_t it = 0; it < (1u << 20) && !all; ++it) {  // bounded: poll the whole batch until every word is valid
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
+                    for (int u = 0; u < kBatch; u++) {
                         const unsigned long long* theirs = sl_base + (size_t)min(c0 + u, nc - 1) * (2 + kHD);
                         asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][0]) : "l"(theirs) : "memory");
                         asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][1]) : "l"(theirs + 1) : "memory");
@@ -413,11 +415,11 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
                     }
                     all = true;
 #pragma unroll
-                    for (int u = 0; u < 4; u++) all = all && (wv[u][0] >> 32) == tag && (wv[u][1] >> 32) == tag && (wv[u][2] >> 32) == tag;
+                    for (int u = 0; u < kBatch; u++) all = all && (wv[u][0] >> 32) == tag && (wv[u][1] >> 32) == tag && (wv[u][2] >> 32) == tag;
                 }
                 ok = ok && all;
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < kBatch; u++) {
                     if (c0 + u >= nc) break;
                     const float Mc = __uint_as_float((uint32_t)wv[u][0]), Lc = __uint_as_float((uint32_t)wv[u][1]);
                     const float Ac = __uint_as_float((uint32_t)wv[u][2]);
@@ -456,7 +458,7 @@ void dump_aring() {
         fprintf(stderr, "  %4d | %7lld | %7lld %7lld %7lld %7lld | %7lld | warp 0: %llu cycles waiting for data of %llu in its loop\n", i, (long long)(r[7] - r[0]),
                 (long long)(r[1] - r[0]), (long long)(r[2] - r[0]), (long long)(r[3] - r[0]), (long long)(r[4] - r[0]), (long long)(r[6] - r[0]), r[5] >> 32,
                 r[5] & 0xffffffffull);
-        fprintf(stderr, "        warp 0 cycles from loop start: q %llu | item0: data %llu scores %llu softmax %llu pv %llu | item1 end %llu\n", r[8], r[9], r[10], r[11], r[12], r[13]);
+        fprintf(stderr, "        warp 0 cycles from loop start: q %llu | item0: data %llu scores %llu softmax %llu pv %llu | item1 end %llu | last CTA's items done %lld ns\n", r[8], r[9], r[10], r[11], r[12], r[13], (long long)(r[14] - r[0]));
     }
 }
 

@@ -217,21 +217,26 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
             const int s = max(-100, min(100, 22 - ex));                   // |x| * 2^s < 2^22
             const float up = __uint_as_float((uint32_t)(127 + s) << 23), dn = __uint_as_float((uint32_t)(127 - s) << 23);
-            uint32_t pw[3][2] = {{0, 0}, {0, 0}, {0, 0}};
+            // balanced base-256 digits X = P0 + 256 P1 + 65536 P2, each in [-128, 127]: a digit is the sign-extended low byte
+            // of what is left, so the byte to store is simply that low byte; four of them are gathered with byte permutes
+            uint32_t pw[3][2];
             int xsum = 0;
+            int d0[8], d1[8], d2[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 float sv = v[j] * up;
                 sv = fminf(fmaxf(sv, -4194304.f), 4194304.f);             // NaN / Inf inputs do not reach here as finite work
-                int X = __float2int_rn(sv);
+                const int X = __float2int_rn(sv);
                 xsum += X;
-                int p0 = ((X + 128) & 255) - 128;
-                int X1 = (X - p0) >> 8;
-                int p1 = ((X1 + 128) & 255) - 128;
-                int p2 = (X1 - p1) >> 8;
-                pw[0][j >> 2] |= (uint32_t)(p0 & 255) << (8 * (j & 3));
-                pw[1][j >> 2] |= (uint32_t)(p1 & 255) << (8 * (j & 3));
-                pw[2][j >> 2] |= (uint32_t)(p2 & 255) << (8 * (j & 3));
+                d0[j] = X;
+                d1[j] = (X - (int)(signed char)X) >> 8;
+                d2[j] = (d1[j] - (int)(signed char)d1[j]) >> 8;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                pw[0][h] = __byte_perm(__byte_perm(d0[4 * h], d0[4 * h + 1], 0x0040), __byte_perm(d0[4 * h + 2], d0[4 * h + 3], 0x0040), 0x5410);
+                pw[1][h] = __byte_perm(__byte_perm(d1[4 * h], d1[4 * h + 1], 0x0040), __byte_perm(d1[4 * h + 2], d1[4 * h + 3], 0x0040), 0x5410);
+                pw[2][h] = __byte_perm(__byte_perm(d2[4 * h], d2[4 * h + 1], 0x0040), __byte_perm(d2[4 * h + 2], d2[4 * h + 3], 0x0040), 0x5410);
             }
             const int sb = lane >> 2, inner = (8 * lane) & 31;
 #pragma unroll
