@@ -15,8 +15,8 @@
 //   new token the warp that owns the page holding this step's position rotates k, rounds k and v through f16 exactly
 //             as the cache does, patches its staged copy and stores the row into the cache;
 //   merge     per (kv head) segment the warps are combined in warp order, then the CTAs that share the segment in CTA
-//             order: every CTA but the segment's first publishes (max, sum, weighted V) as 64-bit words carrying a
-//             valid flag; the first one collects them, writes the head's output and leaves the slots cleared.
+//             order: every CTA but the segment's last publishes (max, sum, weighted V) as 64-bit words carrying a
+//             valid flag; the last one collects them, writes the head's output and leaves the slots cleared.
 //
 // The reference's three-pass softmax and this online form agree to rounding; sums are in a fixed order, so results
 // do not vary from run to run.
@@ -51,12 +51,6 @@ struct StreamParams {
     int ring_slot;
 };
 
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
 // Consumer warps: the per-page work is a chain of dependent shared-memory loads, shuffles and FMAs, so throughput comes
 // from the number of warps in flight -- fifteen where the per-warp state of the kv group fits (with the producer warp
 // a CTA of 512 threads, which leaves each thread 128 registers), seven for wide groups.
@@ -65,7 +59,7 @@ __host__ __device__ constexpr int consumer_warps() { return GSZ <= 2 ? 15 : 7; }
 
 template <int GSZ, bool FLAGGED>
 __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1)
-attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P) {
+attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_constant__ CUtensorMap vtm, StreamParams P) {
     constexpr int kCWarps = consumer_warps<GSZ>();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1 KB
@@ -125,13 +119,13 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
             const int pg = pt[page];
             const int st = i % S;
             if (i >= S) ok = mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1)) && ok;
-            const size_t src = ((size_t)pg * kv.n_kv + kvh) * kPage * kHD;
             mbar_expect_tx(&full[st], kStageBytes);
             unsigned char* dst = ring + (size_t)st * kStageBytes;
             const int y = (pg * kv.n_kv + kvh) * kPage;  // first row of the slab in the pool seen as [rows][128]
             tma_load_2d(dst, &ktm, 0, y, &full[st]);
             tma_load_2d(dst + kKHalf, &ktm, 64, y, &full[st]);
-            bulk_g2s(dst + 2 * kKHalf, (const __half*)kv.v_pool + src, kSlab, &full[st]);
+            tma_load_2d(dst + 2 * kKHalf, &vtm, 0, y, &full[st]);
+            tma_load_2d(dst + 3 * kKHalf, &vtm, 64, y, &full[st]);
         }
         if (!ok && p.error_flag) atomicExch(p.error_flag, 1);
         return;  // the producer takes no part in the barriers below (they count the consumer threads)
@@ -167,14 +161,18 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
     // Scores run on the tensor cores: C[16 keys x 8 columns] per n tile, two columns (f16 hi and lo part of q) per query
     // head, so an n tile serves four heads and lane (row, t) of the C fragment belongs to head 4 nt + t.
     constexpr int NT = (2 * GSZ + 7) / 8;
-    float acc[GSZ][4];
+    // p.V accumulators as C fragments of D[16 dims x 8 columns] per m tile (8 of them): this lane holds dims lane / 4 and
+    // lane / 4 + 8 of each tile, columns hi / lo of head 4 nt + (lane & 3)
+    float acc[NT][8][4];
     float m_own[NT], l_own[NT];  // running max and sum of head 4 nt + (lane & 3), kept by the lanes of that column
     uint32_t qf[NT][8][2];       // B fragments of the segment's queries, per n tile and 16-dim k tile
     auto reset = [&]() {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) { m_own[nt] = -INFINITY; l_own[nt] = 0.f; }
 #pragma unroll
-        for (int g = 0; g < GSZ; g++) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int mt = 0; mt < 8; mt++) acc[nt][mt][0] = acc[nt][mt][1] = acc[nt][mt][2] = acc[nt][mt][3] = 0.f;
     };
     reset();
     int cur_seg = -1;
@@ -182,9 +180,19 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
     const long long loop0 = clock64();
     auto flush = [&](int seg) {  // this warp's state of kv head `seg` -> shared memory
         float* dst = st_s + ((size_t)(seg - seg0) * kCWarps + warp) * GSZ * kStateWords;
+        {   // hi + lo columns of this lane's head: dims lane / 4 (+ 8) of every m tile
+            const int t4 = lane & 3, dg = lane >> 2;
 #pragma unroll
-        for (int g = 0; g < GSZ; g++)
-            *reinterpret_cast<float4*>(dst + g * kStateWords + 4 + 4 * lane) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+            for (int nt = 0; nt < NT; nt++)
+                if (4 * nt + t4 < GSZ) {
+                    float* hd = dst + (4 * nt + t4) * kStateWords + 4;
+#pragma unroll
+                    for (int mt = 0; mt < 8; mt++) {
+                        hd[mt * 16 + dg] = acc[nt][mt][0] + acc[nt][mt][1];
+                        hd[mt * 16 + dg + 8] = acc[nt][mt][2] + acc[nt][mt][3];
+                    }
+                }
+        }
         if (lane < 4) {  // lanes 0-3: row 0 of the C fragment, columns of heads 4 nt + lane
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
@@ -252,7 +260,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
         ok = mbar_wait(&full[st], (uint32_t)st_par) && ok;
         if (rg && il == warp) rg[9] = clock64() - loop0;
         unsigned char* K_b = ring + (size_t)st * kStageBytes;           // two swizzled boxes: dims 0-63, dims 64-127
-        __half* V_s = reinterpret_cast<__half*>(K_b + 2 * kKHalf);
+        unsigned char* V_b = K_b + 2 * kKHalf;                          // values: the same two-box layout
         int nvalid = kPage;
         if (page == np - 1) {
             nvalid = pos % kPage + 1;
@@ -277,12 +285,18 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
                 vw.x = *reinterpret_cast<const uint32_t*>(&v01); vw.y = *reinterpret_cast<const uint32_t*>(&v23);
                 // dims 4 lane ..: box lane / 16, chunk (lane % 16) / 2 (swizzled by the row), 8 bytes into it for odd lanes
                 *reinterpret_cast<uint2*>(K_b + (lane >> 4) * kKHalf + r * 128 + (((((lane & 15) >> 1) ^ (r & 7))) << 4) + (lane & 1) * 8) = kw;
-                *reinterpret_cast<uint2*>(V_s + r * kHD + 4 * lane) = vw;
+                *reinterpret_cast<uint2*>(V_b + (lane >> 4) * kKHalf + r * 128 + (((((lane & 15) >> 1) ^ (r & 7))) << 4) + (lane & 1) * 8) = vw;
                 const size_t dst = (((size_t)pt[page] * kv.n_kv + kvh) * kPage + r) * kHD + 4 * lane;
                 *reinterpret_cast<uint2*>((__half*)kv.k_pool + dst) = kw;
                 *reinterpret_cast<uint2*>((__half*)kv.v_pool + dst) = vw;
-                __syncwarp();
             }
+            // value rows past this step's position hold whatever the pool held before (Inf, NaN): the tensor core would
+            // multiply them with their zero weights, so they are cleared in the staged copy (a row is 128 bytes in each box)
+            for (int ch = lane; ch < (kPage - nvalid) * 16; ch += 32) {
+                const int rr = nvalid + (ch >> 4), cj = ch & 15;
+                *reinterpret_cast<uint4*>(V_b + (cj >> 3) * kKHalf + rr * 128 + ((cj & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
         }
         {
             // ---- scores: C[16 keys x 8 columns] = K[16 x 128] . Q[128 x 8] per n tile, eight k tiles; keys through ldmatrix
@@ -325,31 +339,48 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
                 for (int o = 4; o < 32; o <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
                 l_own[nt] = l_own[nt] * corr + ps;
                 m_own[nt] = m_new;
+                if (__any_sync(0xffffffffu, corr != 1.f)) {  // the running maximum moved: rescale this lane's own columns
 #pragma unroll
-                for (int h = 0; h < 4; h++) {
-                    if (4 * nt + h < GSZ) {
-                        const float cg = __shfl_sync(0xffffffffu, corr, h);  // lane h sits in the column of head 4 nt + h
+                    for (int mt = 0; mt < 8; mt++)
 #pragma unroll
-                        for (int i = 0; i < 4; i++) acc[4 * nt + h][i] *= cg;
-                    }
+                        for (int i = 0; i < 4; i++) acc[nt][mt][i] *= corr;
                 }
             }
             if (rg && il == warp) rg[11] = clock64() - loop0;
-            // ---- p.V: four dims per lane ----
+            // ---- p.V on the tensor cores: D[16 dims x 8 columns] += V^T[16 dims x 16 keys] . P[16 keys x 8 columns] per m tile;
+            //      the weights as f16 hi / lo columns like the queries, the values transposed by ldmatrix ----
+            uint32_t pf[NT][2];
+            {
+                const int col = lane >> 2, t4 = lane & 3, hl = col >> 1;
+                const int src0 = ((2 * t4) << 2) | hl, src1 = ((2 * t4 + 1) << 2) | hl;  // lanes holding keys 2t, 2t+1 (and +8) of head hl
 #pragma unroll
-            for (int j = 0; j < kPage; j++) {
-                uint2 vq = *reinterpret_cast<const uint2*>(V_s + j * kHD + 4 * lane);
-                // rows past this step's position hold whatever the pool held before (Inf, NaN): their zero weight must
-                // meet zeros, not those bytes
-                if (j >= nvalid) vq = make_uint2(0u, 0u);
-                const __half2* h2 = reinterpret_cast<const __half2*>(&vq);
-                const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]);
-#pragma unroll
-                for (int g = 0; g < GSZ; g++) {
-                    const float pj = __shfl_sync(0xffffffffu, pe[g >> 2][j >> 3], ((j & 7) << 2) | (g & 3));
-                    acc[g][0] = fmaf(pj, v0.x, acc[g][0]); acc[g][1] = fmaf(pj, v0.y, acc[g][1]);
-                    acc[g][2] = fmaf(pj, v1.x, acc[g][2]); acc[g][3] = fmaf(pj, v1.y, acc[g][3]);
+                for (int nt = 0; nt < NT; nt++) {
+                    float x00 = __shfl_sync(0xffffffffu, pe[nt][0], src0), x01 = __shfl_sync(0xffffffffu, pe[nt][0], src1);
+                    float x10 = __shfl_sync(0xffffffffu, pe[nt][1], src0), x11 = __shfl_sync(0xffffffffu, pe[nt][1], src1);
+                    if (4 * nt + hl >= GSZ) { x00 = x01 = x10 = x11 = 0.f; }
+                    __half h00 = __float2half_rn(x00), h01 = __float2half_rn(x01), h10 = __float2half_rn(x10), h11 = __float2half_rn(x11);
+                    if (col & 1) {
+                        h00 = __float2half_rn(x00 - __half2float(h00)); h01 = __float2half_rn(x01 - __half2float(h01));
+                        h10 = __float2half_rn(x10 - __half2float(h10)); h11 = __float2half_rn(x11 - __half2float(h11));
+                    }
+                    const __half2 b0 = __halves2half2(h00, h01), b1 = __halves2half2(h10, h11);
+                    pf[nt][0] = *reinterpret_cast<const uint32_t*>(&b0);
+                    pf[nt][1] = *reinterpret_cast<const uint32_t*>(&b1);
                 }
+            }
+            const int vkey = (lane & 7) + ((lane >> 4) & 1) * 8;  // the key row this lane addresses for the transposing ldmatrix
+            const uint32_t lv_row = smem_u32(V_b) + (uint32_t)(vkey * 128);
+#pragma unroll
+            for (int mt = 0; mt < 8; mt++) {
+                const int j = (mt & 3) * 2 + ((lane >> 3) & 1);  // dims chunk: tiles 0/2 take dims 0-7, tiles 1/3 dims 8-15 of the m tile
+                uint32_t a0, a1, a2, a3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(lv_row + (mt >> 2) * kKHalf + ((j ^ (vkey & 7)) << 4)));
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(acc[nt][mt][0]), "+f"(acc[nt][mt][1]), "+f"(acc[nt][mt][2]), "+f"(acc[nt][mt][3])
+                                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(pf[nt][0]), "r"(pf[nt][1]));
             }
         }
         __syncwarp();
@@ -394,21 +425,25 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
             const unsigned long long wv = (tag << 32) | (unsigned long long)__float_as_uint(v);
             asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
         };
-        if (nc > 1 && me != 0) {
+        if (nc > 1 && me != nc - 1) {
             unsigned long long* mine = sl_base + (size_t)me * (2 + kHD);
             if (dx == 0) { put(mine, M); put(mine + 1, L); }
             put(mine + 2 + dx, A);
         } else {
-            // the head's first CTA collects the others in CTA order; the three words of up to eight contributors are
-            // requested together so that one memory round trip serves them all
+            // The head's LAST CTA collects the others and adds everything in CTA order.  CTAs are dispatched in index order
+            // as SMs come free, so the highest index is the one most likely to have started last: when it gets here the
+            // others' words are usually already in L2 and one round trip fetches them.  The three words of up to eight
+            // contributors are requested together.
             constexpr int kBatch = 8;
-            for (int c0 = 1; c0 < nc; c0 += kBatch) {
+            const float M_own = M, L_own = L, A_own = A;
+            M = -INFINITY; L = 0.f; A = 0.f;
+            for (int c0 = 0; c0 < nc - 1; c0 += kBatch) {
                 unsigned long long wv[kBatch][3];
                 bool all = false;
                 for (uint32_t it = 0; it < (1u << 20) && !all; ++it) {  // bounded: poll the whole batch until every word is valid
 #pragma unroll
                     for (int u = 0; u < kBatch; u++) {
-                        const unsigned long long* theirs = sl_base + (size_t)min(c0 + u, nc - 1) * (2 + kHD);
+                        const unsigned long long* theirs = sl_base + (size_t)min(c0 + u, nc - 2) * (2 + kHD);
                         asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][0]) : "l"(theirs) : "memory");
                         asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][1]) : "l"(theirs + 1) : "memory");
                         asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][2]) : "l"(theirs + 2 + dx) : "memory");
@@ -420,22 +455,29 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, StreamParams P)
                 ok = ok && all;
 #pragma unroll
                 for (int u = 0; u < kBatch; u++) {
-                    if (c0 + u >= nc) break;
+                    if (c0 + u >= nc - 1) break;
                     const float Mc = __uint_as_float((uint32_t)wv[u][0]), Lc = __uint_as_float((uint32_t)wv[u][1]);
                     const float Ac = __uint_as_float((uint32_t)wv[u][2]);
                     const float Mn = fmaxf(M, Mc);
-                    const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);
+                    const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);  // exp(-inf) = 0 for the empty start
                     A = A * e0 + Ac * e1;
                     L = L * e0 + Lc * e1;
                     M = Mn;
                 }
             }
+            {   // this CTA's own share comes last
+                const float Mn = fmaxf(M, M_own);
+                const float e0 = expf(M - Mn), e1 = expf(M_own - Mn);
+                A = A * e0 + A_own * e1;
+                L = L * e0 + L_own * e1;
+                M = Mn;
+            }
             if (nc > 1 && !flagged) {
-                for (int c = 1; c < nc; c++)
+                for (int c = 0; c < nc - 1; c++)
                     asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + 2 + dx), "l"(0ull) : "memory");
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read the maxima and sums
                 if (dx < 2)
-                    for (int c = 1; c < nc; c++)
+                    for (int c = 0; c < nc - 1; c++)
                         asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + dx), "l"(0ull) : "memory");
             }
             if (flagged) flag_store(p.outf + (size_t)head * kHD + dx, A / L, epoch_out);
@@ -507,9 +549,10 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
         LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
         attr_set[a.qkvf ? 1 : 0] = true;
     }
-    CUtensorMap ktm;
+    CUtensorMap ktm, vtm;
     memcpy(&ktm, a.kv.k_tmap, sizeof(ktm));
-    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((consumer_warps<GSZ>() + 1) * 32), smem, s, ktm, P));
+    memcpy(&vtm, a.kv.v_tmap, sizeof(vtm));
+    LC_CUDA(launch_pdl(kern, dim3(sm_count()), dim3((consumer_warps<GSZ>() + 1) * 32), smem, s, ktm, vtm, P));
     return LC_OK;
 }
 
@@ -537,7 +580,7 @@ int32_t attention_stream_reserve(int n_heads, int n_kv) {
 bool attention_stream_applies(const AttnParams& a, int n_tok) {
     static const bool off = getenv("LC_ATTN_NO_STREAM") != nullptr;
     const int gsz = a.kv.n_kv > 0 ? a.n_heads / a.kv.n_kv : 0;
-    return !off && a.kv.k_tmap != nullptr && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
+    return !off && a.kv.k_tmap != nullptr && a.kv.v_tmap != nullptr && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
            (gsz == 1 || gsz == 2 || gsz == 4 || gsz == 8);
 }
 

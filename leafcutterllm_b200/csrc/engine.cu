@@ -66,7 +66,7 @@ struct lc_model {
     // KV cache
     std::vector<void*> k_pools, v_pools;  // per layer
     struct alignas(64) TmapBytes { unsigned char b[128]; };
-    std::vector<TmapBytes> k_tmaps;       // per layer: tensor map over the key pool (f16 pools of 128-dim heads)
+    std::vector<TmapBytes> k_tmaps, v_tmaps;  // per layer: tensor maps over the key and value pools (f16 pools of 128-dim heads)
     bool k_tmaps_ok = false;
     std::vector<int> free_pages;
     std::vector<std::vector<int>> seq_pages;
@@ -234,6 +234,7 @@ KvLayout kv_layout(const lc_model* m, int layer) {
     kv.page_tokens = m->page_tokens;
     kv.kv_f32 = m->cfg.kv_dtype;
     kv.k_tmap = m->k_tmaps_ok ? (const void*)m->k_tmaps[layer].b : nullptr;
+    kv.v_tmap = m->k_tmaps_ok ? (const void*)m->v_tmaps[layer].b : nullptr;
     return kv;
 }
 
@@ -799,9 +800,11 @@ int32_t lc_model_finalize(lc_model* m) {
     }
     if (m->hd == 128 && m->cfg.kv_dtype == 0 && m->page_tokens == 16) {  // what the streaming attention kernel reads keys through
         m->k_tmaps.resize(m->L);
+        m->v_tmaps.resize(m->L);
         m->k_tmaps_ok = true;
         for (int l = 0; l < m->L && m->k_tmaps_ok; l++)
-            m->k_tmaps_ok = make_key_pool_tmap(m->k_tmaps[l].b, m->k_pools[l], (uint64_t)m->pages_total * m->nkv * m->page_tokens);
+            m->k_tmaps_ok = make_key_pool_tmap(m->k_tmaps[l].b, m->k_pools[l], (uint64_t)m->pages_total * m->nkv * m->page_tokens) &&
+                            make_key_pool_tmap(m->v_tmaps[l].b, m->v_pools[l], (uint64_t)m->pages_total * m->nkv * m->page_tokens);
     }
     m->dataflow_ready = m->dataflow_ready && m->k_tmaps_ok;
     m->free_pages.resize(m->pages_total);

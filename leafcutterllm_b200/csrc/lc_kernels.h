@@ -93,7 +93,8 @@ struct KvLayout {
     void* v_pool = nullptr;
     int n_kv = 0, hd = 0, page_tokens = 16;
     int kv_f32 = 0;
-    const void* k_tmap = nullptr;  // host copy of a tensor map over k_pool (make_key_pool_tmap), or null
+    const void* k_tmap = nullptr;  // host copies of tensor maps over k_pool and v_pool (make_key_pool_tmap), or null
+    const void* v_tmap = nullptr;
 };
 bool make_key_pool_tmap(void* out128, const void* pool, uint64_t rows);
 // For each of the `n_tok` new tokens (token i belongs to sequence row tok_seq[i], at cache
