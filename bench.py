@@ -211,6 +211,46 @@ def gemv_sweep(lc) -> dict:
     return {"kernel": "Q4_K GEMV, one token" + (" (tcgen05 variant)" if os.environ.get("LC_GEMV_UMMA") else ""), "sweep": rows}
 
 
+def gemm_microbench(lc, tokens=(64, 512), small: bool = False) -> dict:
+    """The many-token tensor-core product (Q4_K weights dequantised on the fly, tcgen05) timed alone on the 7B shapes:
+    per shape and token count the time of one launch pair (activation split + product) over distinct weight copies
+    larger than L2, CUDA events on the library's stream."""
+    import ctypes as C
+    lib = lc.load()
+    chk = lc._capi.check
+    rows = []
+    shapes = [(4096, 12288), (4096, 4096), (11008, 4096)] if not small else [(4096, 4096)]
+    for m in tokens:
+        for (k, n) in shapes:
+            nb = lib.lc_tensor_bytes(12, k * n)
+            copies = max(2, int((200e6 if small else 600e6) // nb))
+            x = C.c_void_p(); y = C.c_void_p()
+            chk(lib.lc_dev_alloc(4 * k * m, C.byref(x))); chk(lib.lc_dev_alloc(4 * n * m, C.byref(y)))
+            chk(lib.lc_synth_tensor_dev(0, 1, b"x", 1.0, k * m, x))
+            ws = []
+            for c in range(copies):
+                p = C.c_void_p()
+                chk(lib.lc_dev_alloc(nb, C.byref(p)))
+                chk(lib.lc_synth_tensor_dev(12, 7, f"g{c}".encode(), 0.02, k * n, p))
+                ws.append(p)
+            for p in ws[:2]:
+                chk(lib.lc_qmatmul_dev(12, x, p, m, k, n, y))
+            chk(lib.lc_dev_sync()); chk(lib.lc_timer_begin())
+            reps = 1 if small else 3
+            for _ in range(reps):
+                for p in ws:
+                    chk(lib.lc_qmatmul_dev(12, x, p, m, k, n, y))
+            ms = C.c_float(); chk(lib.lc_timer_end(C.byref(ms)))
+            for p in ws:
+                lib.lc_dev_free(p)
+            lib.lc_dev_free(x); lib.lc_dev_free(y)
+            us = ms.value * 1e3 / (reps * copies)
+            rows.append({"tokens": m, "k": k, "n": n, "weight_MB": round(nb / 1e6, 2), "us_per_launch": round(us, 1),
+                         "weight_GBps": round(nb / us / 1e3, 1), "TFLOPs": round(2.0 * m * k * n / us / 1e6, 1)})
+    return {"kernel": "qgemm_umma_q4k_kernel (tcgen05 kind::f16, %s products per k step)" % os.environ.get("LC_GEMM_TERMS", "3"),
+            "rows": rows}
+
+
 def gemv_roofline(lc, spec, reps: int = 3, copies: int = 8, warm: int = 3) -> dict:
     """The dominant kernel (quantised GEMV, one launch per weight matrix) timed alone with CUDA events on the
     library's stream over 8 distinct copies of a layer's matrices (0.9 GB, larger than L2)."""
@@ -421,7 +461,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemm", "gemm-small"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
     ap.add_argument("--profile-range", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: keep this many of the 32 layers (the printed number is then not the metric)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="context prefilled before decoding (default: the 2048 of the workload)")
@@ -432,6 +472,9 @@ def main():
     elif args.only == "gemv-sweep":
         import leafcutterllm_b200 as lc
         print(json.dumps(gemv_sweep(lc)))
+    elif args.only in ("gemm", "gemm-small"):
+        import leafcutterllm_b200 as lc
+        print(json.dumps(gemm_microbench(lc, tokens=(64,) if args.only == "gemm-small" else (64, 512), small=args.only == "gemm-small")))
     elif args.only == "gemv":
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth

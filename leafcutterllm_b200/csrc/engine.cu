@@ -92,6 +92,7 @@ struct lc_model {
     bool dataflow_ready = false;   // the model qualifies
     bool dataflow_step = false;    // set while the kernels of such a step are being queued
     void* d_attn_scratch = nullptr;
+    GemmWorkspace gemm_ws;  // f16 activation halves for the many-token tensor-core product
     int* d_attn_counters = nullptr;
     size_t attn_scratch_bytes = 0;
     unsigned long long* d_sanity = nullptr;
@@ -282,6 +283,14 @@ static L2Prefetch prefetch_for(lc_model* m, int l, int kernel) {
 }
 
 int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
+    if (qgemm_applies(a, T, m->gemm_ws)) {
+        // nine tokens and more: one pass over the weights on the tcgen05 tensor cores (activation split + product)
+        a.m = T;
+        int launches = 0;
+        LC_TRY(launch_qgemm(a, m->gemm_ws, m->stream, &launches));
+        m->launches_in_call += launches;
+        return LC_OK;
+    }
     for (int t0 = 0; t0 < T; t0 += kTokTile) {
         GemvArgs g = a;
         g.m = std::min(kTokTile, T - t0);
@@ -822,6 +831,7 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(dalloc(&m->d_hidden, (size_t)T * H)); LC_TRY(dalloc(&m->d_hidden2, (size_t)T * H));
     LC_TRY(dalloc(&m->d_qkv, (size_t)T * m->nqkv)); LC_TRY(dalloc(&m->d_attn, (size_t)T * nq));
     LC_TRY(dalloc(&m->d_ffn, (size_t)T * F));
+    LC_TRY(qgemm_workspace_alloc(&m->gemm_ws, T, std::max(std::max(H, F), nq)));
     LC_TRY(dalloc(&m->d_last, (size_t)m->max_seqs * H)); LC_TRY(dalloc(&m->d_logits, (size_t)m->max_seqs * V));
     LC_TRY(dalloc(&m->d_next, m->max_seqs)); LC_TRY(dalloc(&m->d_step_ctr, 1));
     size_t sc = 16;
@@ -859,6 +869,7 @@ int32_t lc_model_destroy(lc_model* m) {
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity};
     for (void* p : bufs) if (p) cudaFree(p);
+    qgemm_workspace_free(&m->gemm_ws);
     if (m->pin_tokens) cudaFreeHost(m->pin_tokens);
     if (m->pin_next) cudaFreeHost(m->pin_next);
     if (m->pin_logits) cudaFreeHost(m->pin_logits);

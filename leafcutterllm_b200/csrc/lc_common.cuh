@@ -67,6 +67,32 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+// Block-wide sum in a fixed order (deterministic): warp shuffles, then warp 0 over the per-warp sums.
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float r = (threadIdx.x < nw) ? sh[threadIdx.x] : 0.0f;
+    if (w == 0) r = warp_sum(r);
+    if (threadIdx.x == 0) sh[0] = r;
+    __syncthreads();
+    return sh[0];
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+    v = warp_max(v);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) sh[w] = v;
+    __syncthreads();
+    float r = (threadIdx.x < nw) ? sh[threadIdx.x] : -INFINITY;
+    if (w == 0) r = warp_max(r);
+    if (threadIdx.x == 0) sh[0] = r;
+    __syncthreads();
+    return sh[0];
+}
+
 __device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 __device__ __forceinline__ uint16_t f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
 

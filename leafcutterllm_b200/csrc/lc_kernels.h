@@ -87,6 +87,26 @@ int32_t qgemv_reserve_scratch(int n, int k, bool two_mats);
 // Number of kernels launch_qgemv queues for these arguments (for launch accounting).
 int qgemv_launch_count(const GemvArgs& a);
 
+// ---- qgemm_umma.cu ----
+// The same product for many tokens (prefill chunks, batched decode) on tcgen05 tensor cores with the weights
+// dequantised on the fly.  The workspace holds the activations as f16 high/low halves and the per-token scales.
+struct GemmWorkspace {
+    void* xh = nullptr;          // [2][t_cap][k] f16: high halves, low halves
+    void* sx = nullptr;          // [2][t_cap][k / 16] f16: sums over 32-element sub-blocks, eight + eight zeros per 256-element unit
+    float* tok_scale = nullptr;  // [t_cap]
+    float* partial = nullptr;    // sums of the shares of k when a product is split over several CTAs per tile
+    size_t partial_bytes = 0;
+    int t_cap = 0, k_max = 0;
+};
+int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max);
+void qgemm_workspace_free(GemmWorkspace* ws);
+// true when launch_qgemm implements these arguments for T tokens (Q4_K weights, T at least LC_GEMM_MIN_TOKENS, default 9)
+bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws);
+// a.m = number of tokens; queues two kernels (activation preparation, product), three when k is split (reduction)
+int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s, int* launches = nullptr);
+// Tensor map over f16 activations [2 halves][rows][k] with a box of 64 elements x box_rows rows x both halves, 128-byte swizzle.
+bool make_act_tmap(void* out128, const void* base, uint64_t k, uint64_t rows, uint32_t box_rows);
+
 // ---- attention.cu ----
 struct KvLayout {
     void* k_pool = nullptr;  // [pages][n_kv][page_tokens][hd]  (f16 or f32)

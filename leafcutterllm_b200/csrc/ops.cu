@@ -2,6 +2,7 @@
 // (rust/src/backend/mod.rs:18-46) plus RoPE, argmax and the shard-order
 // quantised GEMMs, and the host-pointer C entry points built on them.
 #include <mutex>
+#include <algorithm>
 #include "lc_kernels.h"
 #include "lc_quant.cuh"
 
@@ -28,32 +29,6 @@ __global__ void vec_scale_mul_kernel(const float* a, float s, const float* b, si
 __device__ __forceinline__ float silu1(float v) { return __fmul_rn(v, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v)))); }
 __global__ void silu_kernel(const float* x, size_t n, float* o) { EW_LOOP(n) o[i] = silu1(x[i]); }
 __global__ void silu_mul_kernel(const float* g, const float* u, size_t n, float* o) { EW_LOOP(n) o[i] = __fmul_rn(silu1(g[i]), u[i]); }
-
-// Block-wide sum in a fixed order (deterministic): warp shuffles, then warp 0 over the per-warp sums.
-__device__ __forceinline__ float block_sum(float v, float* sh) {
-    v = warp_sum(v);
-    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    __syncthreads();
-    if (lane == 0) sh[w] = v;
-    __syncthreads();
-    float r = (threadIdx.x < nw) ? sh[threadIdx.x] : 0.0f;
-    if (w == 0) r = warp_sum(r);
-    if (threadIdx.x == 0) sh[0] = r;
-    __syncthreads();
-    return sh[0];
-}
-__device__ __forceinline__ float block_max(float v, float* sh) {
-    v = warp_max(v);
-    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    __syncthreads();
-    if (lane == 0) sh[w] = v;
-    __syncthreads();
-    float r = (threadIdx.x < nw) ? sh[threadIdx.x] : -INFINITY;
-    if (w == 0) r = warp_max(r);
-    if (threadIdx.x == 0) sh[0] = r;
-    __syncthreads();
-    return sh[0];
-}
 
 // cpu.rs:49-60: scale = 1/sqrt(mean(x^2)+eps); out = (x*scale)*w
 __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, size_t hidden,
@@ -399,6 +374,39 @@ int32_t lc_dequantize_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, f
     return launch_dequant(typ, bytes_dev, n_elems, out_dev, stream());
 }
 
+// Rows of `a` against a quantised matrix: token tiles of at most 8 rows per pass of the matrix-vector kernels, or -- for
+// nine rows and more of Q4_K -- chunks of up to 512 rows through the tensor-core product (qgemm_umma.cu).
+static int32_t qmatmul_rows(const QWeight& w, const float* a_dev, size_t m, float* c_dev) {
+    static GemmWorkspace ws;  // callers are serialised (L1 mutex / single library stream)
+    GemvArgs probe;
+    probe.w = &w;
+    probe.x = a_dev;
+    probe.out = c_dev;
+    const int chunk = 512;
+    if (w.typ == LC_TYPE_Q4_K && w.has_tmap && m >= 9) {
+        if (!ws.xh || ws.k_max < w.k) {
+            qgemm_workspace_free(&ws);
+            LC_TRY(qgemm_workspace_alloc(&ws, chunk, w.k));
+        }
+    }
+    for (size_t m0 = 0; m0 < m;) {
+        GemvArgs ga;
+        ga.w = &w;
+        ga.x = a_dev + m0 * w.k;
+        ga.out = c_dev + m0 * w.n;
+        const int left = (int)std::min<size_t>(m - m0, (size_t)chunk);
+        if (ws.xh && qgemm_applies(ga, left, ws)) {
+            ga.m = left;
+            LC_TRY(launch_qgemm(ga, ws, stream()));
+        } else {
+            ga.m = std::min(left, 8);
+            LC_TRY(launch_qgemv(ga, stream()));
+        }
+        m0 += ga.m;
+    }
+    return LC_OK;
+}
+
 int32_t lc_qmatmul(uint32_t typ, const float* a, const void* w_blocks, size_t m, size_t k, size_t n, float* c) {
     LC_CHECK(a && w_blocks && c, LC_ERR_INVALID, "lc_qmatmul: null pointer");
     QuantGeom g;
@@ -411,15 +419,7 @@ int32_t lc_qmatmul(uint32_t typ, const float* a, const void* w_blocks, size_t m,
     LC_TRY(S->c.reserve(m * n * 4 + 4));
     QWeight w;
     LC_TRY(qweight_init(&w, typ, S->b.p, (int)n, (int)k));
-    // Token tiles of at most 8 rows of `a` per pass over the weights.
-    for (size_t m0 = 0; m0 < m; m0 += 8) {
-        GemvArgs ga;
-        ga.w = &w;
-        ga.x = (float*)S->a.p + m0 * k;
-        ga.m = (int)((m - m0) < 8 ? (m - m0) : 8);
-        ga.out = (float*)S->c.p + m0 * n;
-        LC_TRY(launch_qgemv(ga, stream()));
-    }
+    LC_TRY(qmatmul_rows(w, (float*)S->a.p, m, (float*)S->c.p));
     return down(c, S->c, m * n * 4);
 }
 int32_t lc_qmatmul_dev(uint32_t typ, const float* a_dev, const void* w_dev, size_t m, size_t k, size_t n, float* c_dev) {
@@ -429,15 +429,7 @@ int32_t lc_qmatmul_dev(uint32_t typ, const float* a_dev, const void* w_dev, size
     LC_CHECK(k % g.block_elems == 0, LC_ERR_INVALID, "lc_qmatmul_dev: k=%zu is not a multiple of the block size %u", k, g.block_elems);
     QWeight w;
     LC_TRY(qweight_init(&w, typ, w_dev, (int)n, (int)k));
-    for (size_t m0 = 0; m0 < m; m0 += 8) {
-        GemvArgs ga;
-        ga.w = &w;
-        ga.x = a_dev + m0 * k;
-        ga.m = (int)((m - m0) < 8 ? (m - m0) : 8);
-        ga.out = c_dev + m0 * n;
-        LC_TRY(launch_qgemv(ga, stream()));
-    }
-    return LC_OK;
+    return qmatmul_rows(w, a_dev, m, c_dev);
 }
 
 int32_t lc_q8_0_matmul_shard(const float* a, const float* scales, const int8_t* qs, size_t m, size_t k, size_t n, float* c) {

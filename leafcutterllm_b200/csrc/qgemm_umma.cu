@@ -1,0 +1,693 @@
+// Q4_K weights times MANY tokens (prefill chunks, batched decode steps of nine or more sequences) on the
+// 5th-generation tensor cores: the dense contraction of the path (Tensor::matmul with m > 1, rust/src/tensor.rs:107-135,
+// over weights that the reference dequantises per call, rust/src/model/loader.rs:213-224).
+//
+//   y[t, r] = sum_k x[t, k] * w[r, k],      w = d * sc * q - dmin * m       (rust/src/kernels/mod.rs:54-98)
+//
+// Weights stay as raw GGUF blocks in HBM; nothing dequantised is ever written back, and no weight is ever rounded: per
+// 256-element unit and row the sum is regrouped as
+//
+//   d * sum_k (sc * q)[k] * x[t, k]  -  dmin * sum_sub m[sub] * sx[t, sub],       sx = sum of x over the 32-element sub-block
+//
+// where sc * q <= 63 * 15 and m <= 63 are small integers, exact in f16.  Both sums run on the tensor cores with f32
+// accumulation; the two f16 scales of the unit are applied to the finished sums in f32.  One CTA owns 128 weight rows
+// (the M of tcgen05.mma) and up to 64 tokens, and walks k unit by unit:
+//
+//   producer   one thread: TMA boxes of raw blocks [144 B x 128 rows] per unit, per 64-element chunk of k the
+//              activation tile [64 x N] of f16 (128-byte rows, hardware swizzle 128B) as high halves and, right behind
+//              them, low halves of the split below, and per four units the tile of sub-block sums;
+//   unpack     two groups of 128 threads take the units in turn (for gate/up: one matrix each); thread r owns row r:
+//              nibbles -> (1024 + q) as f16 by a byte permute, times sc minus 1024 sc in one HFMA2 (exact), written
+//              with tcgen05.st straight into TENSOR MEMORY as the A operand (lane = row, one 32-bit column = two
+//              consecutive k): 1.4 instructions per weight, and unpacked weights never cross shared memory;
+//   multiply   one thread issues tcgen05.mma kind::f16, M=128, K=16, A from tensor memory, B from the swizzled tile.
+//              Activations are x = hi + lo in f16 (2^-22 together); the high and the low tile lie one after the other,
+//              so ONE instruction with N = 2 x tokens forms both products (two column ranges, added in the drain);
+//              LC_GEMM_TERMS=1 keeps only the high halves (plain f16 activations, 2^-11);
+//   drain      when a unit's products are complete the owning group reads its row of the sums with tcgen05.ld and adds
+//              d * sum - dmin * minsum into the row's f32 results, which live in registers for the whole kernel;
+//   epilogue   undo the per-token power-of-two scale, then store / add the residual / SiLU(gate) * up.
+//
+// Activations are prepared by xprep_kernel: optional RMS norm (rust/src/backend/cpu.rs:49-60), a power-of-two scale per
+// token that brings its largest magnitude into [0.5, 1) (so neither half leaves the f16 range), the hi/lo split, and
+// the sub-block sums.  All products of a tile are issued by one thread, in order: results are deterministic.
+//
+// Every wait is bounded; a wait that runs out sets the library's device error flag and the CTA winds down (tensor
+// memory freed, no copy left in flight).
+#include <cstdio>
+#include <cstdlib>
+#include <cuda_fp16.h>
+#include "lc_kernels.h"
+#include "lc_quant.cuh"
+#include "lc_tma.cuh"
+
+namespace lc {
+
+namespace {
+
+constexpr int kRows = 128;     // weight rows per CTA = MMA M
+constexpr int kChunkK = 64;    // k per pipeline step: one 128-byte swizzled row of f16
+constexpr int kMaxTok = 64;    // tokens per CTA (a multiple of 16)
+constexpr int kMaxRaw = 4;     // raw unit boxes in flight
+constexpr int kMaxB = 8;       // activation chunks in flight
+constexpr int kThreads = 384;  // warps 0 and 3 producers, warps 1-2 the two issuers, warps 4..7 and 8..11 the two unpack groups
+constexpr int kUnitBytes = 144;
+// tensor-memory columns
+constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kColsPerPipe:
+constexpr uint32_t kColsPerPipe = 192;   //   [0, 2N) sum (sc q) x_hi | sum (sc q) x_lo, [128, 128 + N) sum m sx, of the step in progress
+constexpr uint32_t kColA = 384;          // four A stages of 32 columns (64 k each): stages 2g, 2g + 1 belong to pipeline g
+
+struct GemmParams {
+    float* out;             // [T, n]
+    const float* residual;  // or null
+    const float* tok_scale; // [T] power of two that xprep divided token t by
+    int n, k, T;
+    int N;                  // tokens per CTA, padded to a multiple of 16: the box height of the activation tensor maps
+    int epi;                // GemvEpilogue
+    int terms;              // 3: activations as high + low halves; 1: high halves only
+    int raw_stages, b_stages;
+    int ksplit;             // CTAs along k per tile (gridDim.z); > 1: every CTA writes its two groups' sums to `partial`
+    float* partial;         // [ksplit][2 groups][T][n] f32
+    int* error_flag;
+    long long* trace;       // diagnostics (LC_GEMM_TRACE): [5 roles][256] SM clock stamps of CTA (0, 0), or null
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------------------------------
+// Shared-memory operand descriptor, K-major, 128-byte swizzle: start address and the byte distance between 8-row groups
+// in 16-byte units, descriptor version 1, layout code 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;                 // leading byte offset: unused with a swizzled K-major tile
+    d |= (uint64_t)(1024u >> 4) << 32;      // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// f32 accumulate, f16 x f16, both K-major, M = 128
+__host__ __device__ constexpr uint32_t idesc_f16(int n_tok) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(n_tok >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+}
+// D[tmem] (+)= A[tmem] * B[smem]^T
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---- unpacking ---------------------------------------------------------------------------------------------------------
+struct HdrQ4K { float d, dmin; uint32_t sc_lo, sc_hi, mn_lo, mn_hi; };
+__device__ __forceinline__ void load_hdr(const unsigned char* rp, HdrQ4K& h) {
+    const uint4 w = *reinterpret_cast<const uint4*>(rp);  // d, dmin, 12 scale bytes (mod.rs:66-75)
+    h.d = h2f((uint16_t)(w.x & 0xFFFFu));
+    h.dmin = h2f((uint16_t)(w.x >> 16));
+    unpack_scales_k4(w.y, w.z, w.w, &h.sc_lo, &h.sc_hi, &h.mn_lo, &h.mn_hi);
+}
+// bytes b0, b1 (or b2, b3) of v, each < 64, as the f16 pair (1024 + b0, 1024 + b1): 0x64 is the high byte of 1024.0
+__device__ __forceinline__ uint32_t bias_pair(uint32_t v, int upper) { return __byte_perm(v, 0x64646464u, upper ? 0x5342u : 0x5140u); }
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t h2_pair(float v) {  // (v, v) as f16x2; v is a small integer
+    const __half2 h = __float2half2_rn(v);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// Chunk c of a unit = group c of mod.rs:77-96: 32 bytes whose low nibbles are elements 0..31 under sc[2c] and whose high
+// nibbles are elements 32..63 under sc[2c + 1].  Column j of `col` holds (sc q) of elements 2j, 2j + 1, exact in f16:
+// (1024 + q) * sc - 1024 * sc is one fused multiply-add whose exact result, at most 945, needs no rounding.
+__device__ __forceinline__ void unpack_chunk(const unsigned char* rp, const HdrQ4K& h, int c, uint32_t (&col)[32]) {
+    const uint32_t scw = c < 2 ? h.sc_lo : h.sc_hi;
+    const int sh = (c & 1) * 16;
+    const float fa = (float)((scw >> sh) & 0xFFu), fb = (float)((scw >> (sh + 8)) & 0xFFu);
+    const uint32_t sa = h2_pair(fa), sb = h2_pair(fb), ka = h2_pair(-1024.0f * fa), kb = h2_pair(-1024.0f * fb);
+    const uint4* q = reinterpret_cast<const uint4*>(rp + 16 + 32 * c);
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const uint4 v = q[half];
+        const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; wi++) {
+            const uint32_t lo4 = vv[wi] & 0x0F0F0F0Fu, hi4 = (vv[wi] >> 4) & 0x0F0F0F0Fu;
+            const int j = half * 8 + wi * 2;
+            col[j] = h2_fma(bias_pair(lo4, 0), sa, ka);
+            col[j + 1] = h2_fma(bias_pair(lo4, 1), sa, ka);
+            col[16 + j] = h2_fma(bias_pair(hi4, 0), sb, kb);
+            col[16 + j + 1] = h2_fma(bias_pair(hi4, 1), sb, kb);
+        }
+    }
+}
+// the eight m of a unit as four f16 pairs, then four columns of zeros (k' = 8..15 of the min product)
+__device__ __forceinline__ void unpack_mins(const HdrQ4K& h, uint32_t (&col)[8]) {
+    const uint32_t one = h2_pair(1.0f), k = h2_pair(-1024.0f);
+    col[0] = h2_fma(bias_pair(h.mn_lo, 0), one, k);
+    col[1] = h2_fma(bias_pair(h.mn_lo, 1), one, k);
+    col[2] = h2_fma(bias_pair(h.mn_hi, 0), one, k);
+    col[3] = h2_fma(bias_pair(h.mn_hi, 1), one, k);
+    col[4] = col[5] = col[6] = col[7] = 0u;
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+}  // namespace
+
+// One token per CTA: optional RMS norm, power-of-two scale, hi/lo split to f16, sub-block sums.
+// xh: [hi rows | lo rows at lo_offset] of K f16; sx: the same for the sums, rows of K/16 f16 -- per 256-element unit the
+// eight sub-block sums followed by eight zeros.
+__global__ void __launch_bounds__(256)
+xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int K, __half* __restrict__ xh,
+             size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
+    extern __shared__ float row[];
+    __shared__ float sh[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)t * K;
+    float acc = 0.f, mx = 0.f;
+    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        *reinterpret_cast<float4*>(row + i) = v;
+        acc = fmaf(v.x, v.x, acc); acc = fmaf(v.y, v.y, acc); acc = fmaf(v.z, v.z, acc); acc = fmaf(v.w, v.w, acc);
+    }
+    float scale = 1.f;
+    if (norm_w) {
+        const float ss = block_sum(acc, sh);
+        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));  // cpu.rs:52-55
+    }
+    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<float4*>(row + i);
+        if (norm_w) {
+            const float4 g = *reinterpret_cast<const float4*>(norm_w + i);
+            v.x = __fmul_rn(__fmul_rn(v.x, scale), g.x); v.y = __fmul_rn(__fmul_rn(v.y, scale), g.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, scale), g.z); v.w = __fmul_rn(__fmul_rn(v.w, scale), g.w);
+            *reinterpret_cast<float4*>(row + i) = v;
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));  // NaN does not raise the maximum
+    }
+    mx = block_max(mx, sh);
+    int e = 0;
+    if (mx > 0.f && mx < INFINITY) (void)frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1)
+    const float down = ldexpf(1.0f, -e);
+    if (threadIdx.x == 0) tok_scale[t] = ldexpf(1.0f, e);
+    __half* hi = xh + (size_t)t * K;
+    __half* lo = hi + lo_offset;
+    __half* sxh = sx + (size_t)t * (K / 16);
+    __half* sxl = sxh + sx_lo_offset;
+    // K is a multiple of 256 and a thread takes 4 consecutive elements: eight neighbouring lanes cover one sub-block,
+    // and inactive lanes of the last round belong to whole sub-blocks that do not exist
+    for (int i0 = 0; i0 < K; i0 += blockDim.x * 4) {
+        const int i = i0 + threadIdx.x * 4;
+        float part = 0.f;
+        if (i < K) {
+            const float4 v = *reinterpret_cast<float4*>(row + i);
+            const float a = v.x * down, b = v.y * down, c = v.z * down, d = v.w * down;
+            const __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(c, d);
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+            const __half2 l0 = __floats2half2_rn(a - f0.x, b - f0.y), l1 = __floats2half2_rn(c - f1.x, d - f1.y);
+            uint2 ph, pl;
+            ph.x = *reinterpret_cast<const uint32_t*>(&h0); ph.y = *reinterpret_cast<const uint32_t*>(&h1);
+            pl.x = *reinterpret_cast<const uint32_t*>(&l0); pl.y = *reinterpret_cast<const uint32_t*>(&l1);
+            *reinterpret_cast<uint2*>(hi + i) = ph;
+            *reinterpret_cast<uint2*>(lo + i) = pl;
+            // the sum of what the product will see: the two halves of every element
+            const float2 g0 = __half22float2(l0), g1 = __half22float2(l1);
+            part = ((f0.x + g0.x) + (f0.y + g0.y)) + ((f1.x + g1.x) + (f1.y + g1.y));
+        }
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        if (i < K && (threadIdx.x & 7) == 0) {
+            const int sub = i >> 5, unit = sub >> 3, idx = unit * 16 + (sub & 7);
+            const __half sh_ = __float2half_rn(part);
+            sxh[idx] = sh_;
+            sxl[idx] = __float2half_rn(part - __half2float(sh_));
+            sxh[idx + 8] = __float2half_rn(0.f);
+            sxl[idx + 8] = __float2half_rn(0.f);
+        }
+    }
+}
+
+// grid = (row tiles, token tiles).  tmw0 / tmw1: raw blocks of the matrix (and of `up` for EPI_SILU_MUL), box = one unit
+// x 128 rows.  tmx: the prepared activations [2 halves][t_cap rows][k] f16, box = 64 elements x N rows x both halves,
+// 128-byte swizzle; tms: the sub-block sums [2][t_cap rows][k / 16], same box.
+//
+// The (unit, matrix) steps are dealt in turn to two independent pipelines g = 0, 1, each made of an unpack group of 128
+// threads, an issuing thread and a set of accumulators: a thread needs ~100 cycles to issue one tcgen05 instruction
+// whatever its shape, so one issuer cannot keep the tensor pipe busy with N <= 128, and while one pipeline reads its
+// finished sums out of tensor memory the other one multiplies.
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_constant__ CUtensorMap tmw1,
+                      const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tms, GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, tok0 = blockIdx.y * kMaxTok;
+    const int N = p.N;
+    // this CTA's share of k: whole groups of four units (one tile of sub-block sums), so that only its last tile can be short
+    const int nquads = (p.k / kUnitElems + 3) / 4;
+    const int u_begin = (int)((long long)blockIdx.z * nquads / p.ksplit) * 4;
+    const int u_end = min((int)((long long)(blockIdx.z + 1) * nquads / p.ksplit) * 4, p.k / kUnitElems);
+    const int nunits = u_end - u_begin;  // units are numbered from u_begin below
+    const int nmat = (p.epi == EPI_SILU_MUL) ? 2 : 1;
+    const int nseq = nunits * nmat;  // (unit, matrix) steps in order; step s belongs to pipeline s & 1
+    const int RS = p.raw_stages, BS = p.b_stages;
+    const bool two = p.terms == 3;
+    constexpr uint32_t raw_bytes = kUnitBytes * kRows;
+    const uint32_t b_half = (uint32_t)N * 128u, b_bytes = 2u * b_half;
+
+    unsigned char* bt = smem;                              // [BS][hi N x 128 B | lo N x 128 B], 1024-byte aligned stages
+    unsigned char* st = bt + (size_t)BS * b_bytes;         // [2][the same for the sub-block sums of four units]
+    unsigned char* raw = st + (size_t)2 * b_bytes;         // [RS][raw_bytes]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + (size_t)RS * raw_bytes);
+    uint64_t* raw_full = bars;                 // [kMaxRaw] producer -> unpack (transaction bytes)
+    uint64_t* raw_empty = raw_full + kMaxRaw;  // [kMaxRaw] unpack -> producer (128 arrivals)
+    uint64_t* b_full = raw_empty + kMaxRaw;    // [kMaxB]   producer -> multiply
+    uint64_t* b_empty = b_full + kMaxB;        // [kMaxB]   multiply (a commit per matrix) -> producer
+    uint64_t* s_full = b_empty + kMaxB;        // [2]       sub-block sums of four units: producer -> multiply
+    uint64_t* s_empty = s_full + 2;            // [2]       multiply (a commit per step that used them) -> producer
+    uint64_t* a_full = s_empty + 2;            // [4]       unpack -> multiply (128 arrivals); stages 2g, 2g+1 are pipeline g's
+    uint64_t* a_empty = a_full + 4;            // [4]       multiply (commit) -> unpack
+    uint64_t* d_full = a_empty + 4;            // [2]       the sums of a step of pipeline g are complete (commit)
+    uint64_t* d_empty = d_full + 2;            // [2]       pipeline g has read them (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
+
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < kMaxRaw; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
+        for (int i = 0; i < kMaxB; i++) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], nmat); }
+        for (int i = 0; i < 2; i++) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4 * nmat); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128); }
+        for (int i = 0; i < 4; i++) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool ok = true;
+    int tr_n = 0;
+    const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0;
+    auto stamp = [&](int role, int tag) {
+        if (tracing && tr_n < 256) p.trace[role * 256 + tr_n++] = ((long long)tag << 48) | (clock64() & 0xFFFFFFFFFFFFll);
+    };
+    float* xchg = reinterpret_cast<float*>(bt);  // after the last product: [128 rows][N + 1] f32 handed from group 1 to group 0
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer of the activations
+        // activation chunks in k order (and, with the first chunk of every four units, their sub-block sums): one
+        // 3-D box brings the high and the low halves of a chunk
+        if (lane == 0) {
+            pdl_wait();
+            const int b_total = nunits * 4;
+            for (int b_next = 0; b_next < b_total && ok; b_next++) {
+                const int sb = b_next % BS;
+                if (!mbar_wait(&b_empty[sb], ((b_next / BS) & 1) ^ 1)) { ok = false; break; }
+                if ((b_next & 15) == 0) {
+                    const int q = b_next >> 4, ss = q & 1;
+                    if (!mbar_wait(&s_empty[ss], ((q >> 1) & 1) ^ 1)) { ok = false; break; }
+                    mbar_expect_tx(&s_full[ss], b_bytes);
+                    tma_load_3d(st + (size_t)ss * b_bytes, &tms, (u_begin / 4 + q) * 64, tok0, 0, &s_full[ss]);
+                }
+                mbar_expect_tx(&b_full[sb], b_bytes);
+                tma_load_3d(bt + (size_t)sb * b_bytes, &tmx, (u_begin * 4 + b_next) * kChunkK, tok0, 0, &b_full[sb]);
+                stamp(0, 2);
+            }
+        }
+    } else if (warp == 3) {
+        // ---------------------------------------------------------------- producer of the raw boxes, (unit, matrix) order
+        // a thread of its own: every TMA or barrier instruction costs its issuing thread ~100 cycles, and the weights
+        // do not depend on the kernel ahead of this one, so this stream starts before the wait for it
+        if (lane == 0) {
+            for (int s = 0; s < nseq && ok; s++) {
+                const int sr = s % RS;
+                if (!mbar_wait(&raw_empty[sr], ((s / RS) & 1) ^ 1)) { ok = false; break; }
+                const int u = s / nmat, mat = s - u * nmat;
+                mbar_expect_tx(&raw_full[sr], raw_bytes);
+                tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + u) * (kUnitBytes / 4), tile * kRows, &raw_full[sr]);
+            }
+        }
+    } else if (warp == 1 || warp == 2) {
+        // ---------------------------------------------------------------- multiply: the issuer of pipeline g
+        pdl_wait();
+        const int g = warp - 1;
+        if (lane == 0) {
+            const uint32_t idesc_main = idesc_f16(two ? 2 * N : N), idesc_min = idesc_f16(N);
+            const uint32_t d_main = tmem + kColD + g * kColsPerPipe, d_min = d_main + 2 * kMaxTok;
+            int j = 0;
+            for (int s = g; s < nseq && ok; s += 2, j++) {
+                const int u = s / nmat;
+                // the accumulators still hold the previous step of this pipeline until its group has read them
+                stamp(1 + g, 5);
+                if (j > 0 && !mbar_wait(&d_empty[g], (j - 1) & 1)) { ok = false; break; }
+                stamp(1 + g, 6);
+                tc_fence_after();
+                for (int c = 0; c < 4 && ok; c++) {
+                    const int b_it = u * 4 + c, sb = b_it % BS;
+                    if (!mbar_wait(&b_full[sb], (b_it / BS) & 1)) { ok = false; break; }
+                    const int sa = 2 * g + (c & 1), fill = (c & 1) ? 2 * j + (c >> 1) : 3 * j + (c >> 1);
+                    if (!mbar_wait(&a_full[sa], fill & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    stamp(1 + g, 3);
+                    const uint64_t bdesc = umma_desc_sw128(smem_u32(bt + (size_t)sb * b_bytes));
+                    const uint32_t a_t = tmem + kColA + sa * 32;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        umma_f16_ts(d_main, a_t + ks * 8, bdesc + (uint64_t)(ks * 2), idesc_main, (uint32_t)((c | ks) != 0));
+                    umma_commit(&a_empty[sa]);
+                    umma_commit(&b_empty[sb]);
+                    stamp(1 + g, 4);
+                }
+                if (!ok) break;
+                {   // the min sums: A = the eight m of the unit (the fifth filling of stage 2g), B = this unit's 16 columns of the sums tile
+                    const int q = u >> 2, ss = q & 1, sa = 2 * g;
+                    if (!mbar_wait(&s_full[ss], (q >> 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait(&a_full[sa], (3 * j + 2) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t sdesc = umma_desc_sw128(smem_u32(st + (size_t)ss * b_bytes)) + (uint64_t)((u & 3) * 2);
+                    umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc, idesc_min, 0u);
+                    if (two) umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc + (uint64_t)(b_half >> 4), idesc_min, 1u);
+                    umma_commit(&a_empty[sa]);
+                    umma_commit(&s_empty[ss]);
+                }
+                umma_commit(&d_full[g]);
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------------------------------------------------------- unpack + drain, then epilogue
+        const int g = (warp - 4) >> 2;                // pipeline
+        const int quarter = warp & 3;                 // the tensor-memory lanes this warp may touch
+        const int row = quarter * 32 + lane;          // row of the tile owned by this thread
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t d_main = tmem + lane_base + kColD + g * kColsPerPipe, d_min = d_main + 2 * kMaxTok;
+        const bool tr = quarter == 0 && lane == 0;
+        // a wait whose outcome the whole warp shares: the tensor-memory instructions below are warp-wide
+        auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
+        float y[kMaxTok];
+#pragma unroll
+        for (int t = 0; t < kMaxTok; t++) y[t] = 0.f;
+        pdl_wait();
+        int j = 0;
+        for (int s = g; s < nseq && ok; s += 2, j++) {
+            const int sr = s % RS;
+            if (tr) stamp(3 + g, 1);
+            ok = wait_all(&raw_full[sr], (s / RS) & 1);
+            if (!ok) break;
+            if (tr) stamp(3 + g, 2);
+            const unsigned char* rp = raw + (size_t)sr * raw_bytes + (size_t)row * kUnitBytes;
+            HdrQ4K hdr;
+            load_hdr(rp, hdr);
+            for (int c = 0; c < 4 && ok; c++) {
+                uint32_t col[32];
+                unpack_chunk(rp, hdr, c, col);
+                const int sa = 2 * g + (c & 1), fill = (c & 1) ? 2 * j + (c >> 1) : 3 * j + (c >> 1);
+                ok = wait_all(&a_empty[sa], (fill & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_t = tmem + lane_base + kColA + sa * 32;
+                tmem_st16(a_t, col);
+                tmem_st16(a_t + 16, col + 16);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(&a_full[sa]);
+            }
+            if (!ok) break;
+            mbar_arrive(&raw_empty[sr]);  // this row's bytes of the unit are consumed
+            {   // the eight m as a fifth, short filling of stage 2g
+                uint32_t mc[8];
+                unpack_mins(hdr, mc);
+                ok = wait_all(&a_empty[2 * g], ((3 * j + 2) & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                tmem_st8(tmem + lane_base + kColA + 2 * g * 32, mc);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(&a_full[2 * g]);
+            }
+            // drain: y += d * (main_hi + main_lo) - dmin * min
+            if (tr) stamp(3 + g, 5);
+            ok = wait_all(&d_full[g], j & 1);
+            if (!ok) break;
+            if (tr) stamp(3 + g, 6);
+            tc_fence_after();
+            const float d = hdr.d, ndmin = -hdr.dmin;
+#pragma unroll
+            for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
+                if (t0 < N) {
+                    uint32_t a[16], b[16], m[16];
+                    tmem_ld16(d_main + t0, a);
+                    if (two) tmem_ld16(d_main + N + t0, b);
+                    tmem_ld16(d_min + t0, m);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        float v = __uint_as_float(a[i]);
+                        if (two) v += __uint_as_float(b[i]);
+                        y[t0 + i] = fmaf(d, v, y[t0 + i]);
+                        y[t0 + i] = fmaf(ndmin, __uint_as_float(m[i]), y[t0 + i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&d_empty[g]);
+            if (tr) stamp(3 + g, 7);
+        }
+        pdl_launch_dependents();
+        if (p.ksplit > 1) {
+            // a share of k: both groups leave their sums (scaled back per token) for the reduction kernel
+            const int grow = tile * kRows + row;
+            float* dst = p.partial + ((size_t)(blockIdx.z * 2 + g) * p.T) * p.n;
+            if (ok && grow < p.n) {
+#pragma unroll
+                for (int t = 0; t < kMaxTok; t++) {
+                    const int tok = tok0 + t;
+                    if (t < N && tok < p.T) dst[(size_t)tok * p.n + grow] = y[t] * __ldg(p.tok_scale + tok);
+                }
+            }
+        } else {
+            // every product of the tile has completed (both groups waited for their last step): shared memory is free
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const int ld = N + 1;
+            if (g == 1 && ok) {
+#pragma unroll
+                for (int t = 0; t < kMaxTok; t++)
+                    if (t < N) xchg[row * ld + t] = y[t];
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (g == 0 && ok) {
+                const int grow = tile * kRows + row;
+                if (grow < p.n) {
+#pragma unroll
+                    for (int t = 0; t < kMaxTok; t++) {
+                        const int tok = tok0 + t;
+                        if (t < N && tok < p.T) {
+                            const float sc = __ldg(p.tok_scale + tok);
+                            const float other = xchg[row * ld + t];
+                            const size_t o = (size_t)tok * p.n + grow;
+                            float v;
+                            if (nmat == 2) v = __fmul_rn(silu_f(y[t] * sc), other * sc);  // engine.rs:146-164: group 0 holds gate, group 1 up
+                            else v = (y[t] + other) * sc;                                 // the two groups hold alternate units
+                            if (p.epi == EPI_ADD_RESIDUAL) v = __fadd_rn(p.residual[o], v);
+                            p.out[o] = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && p.error_flag) atomicExch(p.error_flag, 3);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// Sums the shares of k that the product kernel left in `partial` ([slices][T][n], slice = 2 * share + group), in slice
+// order, and applies the epilogue.  With two matrices even slices belong to gate and odd ones to up.
+__global__ void __launch_bounds__(256)
+qgemm_reduce_kernel(const float* __restrict__ partial, int slices, size_t plane, int epi, const float* __restrict__ residual,
+                    float* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= plane) return;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    for (int sl = 0; sl < slices; sl++) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)sl * plane + i);
+        float4& d = (epi == EPI_SILU_MUL && (sl & 1)) ? b : a;
+        d.x += v.x; d.y += v.y; d.z += v.z; d.w += v.w;
+    }
+    if (epi == EPI_SILU_MUL) {
+        a.x = __fmul_rn(silu_f(a.x), b.x); a.y = __fmul_rn(silu_f(a.y), b.y);
+        a.z = __fmul_rn(silu_f(a.z), b.z); a.w = __fmul_rn(silu_f(a.w), b.w);
+    } else if (epi == EPI_ADD_RESIDUAL) {
+        const float4 r = *reinterpret_cast<const float4*>(residual + i);
+        a.x = __fadd_rn(r.x, a.x); a.y = __fadd_rn(r.y, a.y); a.z = __fadd_rn(r.z, a.z); a.w = __fadd_rn(r.w, a.w);
+    }
+    *reinterpret_cast<float4*>(out + i) = a;
+}
+
+// ---- host side --------------------------------------------------------------------------------------------------------
+int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max) {
+    LC_CHECK(ws && t_cap > 0 && k_max > 0, LC_ERR_INVALID, "qgemm workspace: bad size");
+    ws->t_cap = (t_cap + 15) & ~15;
+    ws->k_max = k_max;
+    const size_t bytes = (size_t)2 * ws->t_cap * k_max * sizeof(__half);
+    LC_CUDA(cudaMalloc(&ws->xh, bytes));
+    LC_CUDA(cudaMemset(ws->xh, 0, bytes));  // rows past the tokens of a call are multiplied too (and dropped): keep them finite
+    LC_CUDA(cudaMalloc(&ws->sx, bytes / 16));
+    LC_CUDA(cudaMemset(ws->sx, 0, bytes / 16));
+    LC_CUDA(cudaMalloc((void**)&ws->tok_scale, (size_t)ws->t_cap * sizeof(float)));
+    ws->partial_bytes = (size_t)64 << 20;
+    LC_CUDA(cudaMalloc((void**)&ws->partial, ws->partial_bytes));
+    return LC_OK;
+}
+void qgemm_workspace_free(GemmWorkspace* ws) {
+    if (!ws) return;
+    if (ws->xh) cudaFree(ws->xh);
+    if (ws->sx) cudaFree(ws->sx);
+    if (ws->tok_scale) cudaFree(ws->tok_scale);
+    if (ws->partial) cudaFree(ws->partial);
+    ws->partial = nullptr;
+    ws->xh = nullptr;
+    ws->sx = nullptr;
+    ws->tok_scale = nullptr;
+}
+
+static int gemm_min_tokens() {
+    static const int v = getenv("LC_GEMM_MIN_TOKENS") ? atoi(getenv("LC_GEMM_MIN_TOKENS")) : 9;
+    return v;
+}
+bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws) {
+    if (!a.w || !ws.xh || a.x_flag || a.out_flag || a.residual_flag) return false;
+    if (a.w->typ != LC_TYPE_Q4_K || !a.w->has_tmap || a.w->k % kUnitElems != 0) return false;
+    if (a.epi == EPI_SILU_MUL && (!a.w2 || a.w2->typ != a.w->typ || !a.w2->has_tmap)) return false;
+    if (T < gemm_min_tokens() || T > ws.t_cap || a.w->k > ws.k_max) return false;
+    if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return false;
+    return true;
+}
+
+int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s, int* launches) {
+    const int T = a.m, K = a.w->k, n = a.w->n;
+    LC_CHECK(qgemm_applies(a, T, ws), LC_ERR_INVALID, "qgemm: arguments outside what the kernel implements");
+    if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual != nullptr, LC_ERR_INVALID, "qgemm: residual missing");
+    const int terms = (getenv("LC_GEMM_TERMS") && atoi(getenv("LC_GEMM_TERMS")) == 1) ? 1 : 3;  // read per call so that a test can switch it
+    // activations: [t_cap rows of high halves | t_cap rows of low halves], each row k elements of this matrix
+    const size_t lo_offset = (size_t)ws.t_cap * K, sx_lo_offset = (size_t)ws.t_cap * (K / 16);
+    {
+        const size_t smem = (size_t)K * sizeof(float);
+        static size_t attr_set = 0;
+        if (smem > 48 * 1024 && smem > attr_set) {
+            LC_CUDA(cudaFuncSetAttribute(xprep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set = smem;
+        }
+        LC_CUDA(launch_pdl(xprep_kernel, dim3(T), dim3(256), smem, s, a.x, a.norm_w, a.eps, K, (__half*)ws.xh, lo_offset, (__half*)ws.sx,
+                           sx_lo_offset, ws.tok_scale));
+    }
+    const int N = std::min(kMaxTok, (T + 15) & ~15);
+    alignas(64) CUtensorMap tmx, tms;
+    LC_CHECK(make_act_tmap(&tmx, ws.xh, (uint64_t)K, (uint64_t)ws.t_cap, (uint32_t)N), LC_ERR_CUDA, "qgemm: activation tensor map");
+    LC_CHECK(make_act_tmap(&tms, ws.sx, (uint64_t)K / 16, (uint64_t)ws.t_cap, (uint32_t)N), LC_ERR_CUDA, "qgemm: sums tensor map");
+    GemmParams p;
+    p.out = a.out; p.residual = a.residual; p.tok_scale = ws.tok_scale;
+    p.n = n; p.k = K; p.T = T; p.N = N; p.epi = (int)a.epi; p.terms = terms;
+    const int nmat = a.epi == EPI_SILU_MUL ? 2 : 1;
+    p.raw_stages = kMaxRaw;
+    const size_t raw_bytes = (size_t)p.raw_stages * kUnitBytes * kRows, b_bytes = (size_t)2 * N * 128;
+    const size_t fixed = 1024 + raw_bytes + 2 * b_bytes + 512;
+    p.b_stages = std::min(kMaxB, (int)((kMaxSmem - fixed) / b_bytes));
+    LC_CHECK(p.b_stages >= 4, LC_ERR_UNSUPPORTED, "qgemm: shared memory too small");
+    p.error_flag = gemv_error_flag_dev();
+    p.trace = nullptr;
+    static long long* d_trace = nullptr;
+    const bool want_trace = getenv("LC_GEMM_TRACE") != nullptr;
+    if (want_trace) {
+        if (!d_trace) LC_CUDA(cudaMalloc((void**)&d_trace, 1280 * sizeof(long long)));
+        LC_CUDA(cudaMemsetAsync(d_trace, 0, 1280 * sizeof(long long), s));
+        p.trace = d_trace;
+    }
+    const size_t smem = fixed + (size_t)p.b_stages * b_bytes;
+    static size_t attr_set = 0;
+    if (smem > attr_set) {
+        LC_CUDA(cudaFuncSetAttribute(qgemm_umma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = smem;
+    }
+    const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap_wide;
+    const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap_wide : t0;
+    // Few tiles (a batched decode step on the square matrices): split k over several CTAs so that all SMs work; the
+    // shares are summed, in a fixed order, by a small second kernel.  Cost model: waves x steps per CTA, plus four
+    // steps' worth of prologue and epilogue per wave.
+    const int tiles = (n + kRows - 1) / kRows, ttiles = (T + kMaxTok - 1) / kMaxTok, nquads = (K / kUnitElems + 3) / 4;
+    int ks = 1;
+    {
+        const int sms = sm_count();
+        long best = -1;
+        for (int c = 1; c <= std::min(8, nquads); c++) {
+            if (c > 1 && (size_t)c * 2 * T * n * sizeof(float) > ws.partial_bytes) break;
+            if (c > 1 && (n % 4 != 0 || T > 2 * kMaxTok)) break;
+            const long waves = ((long)tiles * ttiles * c + sms - 1) / sms;
+            const long cost = waves * (((nquads + c - 1) / c) * 4 * nmat + 4) + (c > 1 ? 3 : 0);
+            if (best < 0 || cost < best) { best = cost; ks = c; }
+        }
+        if (getenv("LC_GEMM_NO_SPLIT")) ks = 1;
+    }
+    p.ksplit = ks;
+    p.partial = ws.partial;
+    dim3 grid((unsigned)tiles, (unsigned)ttiles, (unsigned)ks);
+    LC_CUDA(launch_pdl(qgemm_umma_q4k_kernel, grid, dim3(kThreads), smem, s, *t0, *t1, tmx, tms, p));
+    if (ks > 1) {
+        const size_t plane = (size_t)T * n;
+        LC_CUDA(launch_pdl(qgemm_reduce_kernel, dim3((unsigned)((plane / 4 + 255) / 256)), dim3(256), 0, s, (const float*)ws.partial, 2 * ks,
+                           plane, (int)a.epi, a.residual, a.out));
+    }
+    if (launches) *launches = ks > 1 ? 3 : 2;
+    if (want_trace) {
+        static long long h[1280];
+        LC_CUDA(cudaStreamSynchronize(s));
+        LC_CUDA(cudaMemcpy(h, d_trace, sizeof(h), cudaMemcpyDeviceToHost));
+        long long t0c = 0;
+        for (int r = 0; r < 5; r++)
+            if (h[r * 256] && (!t0c || (h[r * 256] & 0xFFFFFFFFFFFFll) < t0c)) t0c = h[r * 256] & 0xFFFFFFFFFFFFll;
+        const char* names[5] = {"producer", "issuer0", "issuer1", "unpack0", "unpack1"};
+        for (int r = 0; r < 5; r++) {
+            fprintf(stderr, "[gemm trace n=%d k=%d T=%d] %s:", n, K, T, names[r]);
+            for (int i = 0; i < 120 && h[r * 256 + i]; i++)
+                fprintf(stderr, " %d@%lld", (int)(h[r * 256 + i] >> 48), (h[r * 256 + i] & 0xFFFFFFFFFFFFll) - t0c);
+            fprintf(stderr, "\n");
+        }
+    }
+    return LC_OK;
+}
+
+}  // namespace lc

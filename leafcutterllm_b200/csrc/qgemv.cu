@@ -109,6 +109,20 @@ bool make_key_pool_tmap(void* out128, const void* pool, uint64_t rows) {
     return r == CUDA_SUCCESS;
 }
 
+bool make_act_tmap(void* out128, const void* base, uint64_t k, uint64_t rows, uint32_t box_rows) {
+    // three dimensions: element, row, half (high halves, then `rows` rows further on the low halves); one box takes
+    // 64 elements x box_rows rows of both halves and lands as [half][row][128 B]
+    if (!encode_fn() || ((uintptr_t)base % 16) != 0 || (k * 2) % 16 != 0 || box_rows == 0 || box_rows > 256) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, 2};
+    cuuint64_t strides[2] = {(cuuint64_t)k * 2, (cuuint64_t)k * 2 * rows};
+    cuuint32_t box[3] = {64, box_rows, 2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode_fn()((CUtensorMap*)out128, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void*)base, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // ---------------------------------------------------------------------------
 // per-unit dot products.  `r` = the lane's unit in registers, xs = x of this
 // unit for token t at xs + t*xstride (256 floats), sx = per-32 sums of x.

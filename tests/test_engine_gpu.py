@@ -92,6 +92,32 @@ def test_batched_sequences_match_single(gpu, oracle):
     eng.close()
 
 
+def test_many_sequences_decode_through_the_tensor_core_gemm(gpu, oracle):
+    """Twelve sequences: the ragged prefill (49 tokens in one call) and every decode step (12 tokens) go through the
+    many-token tcgen05 product instead of the matrix-vector kernels; tokens must still equal the oracle's, sequence by
+    sequence, and a second engine must reproduce the first bit for bit (one issuing order, no atomics)."""
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=2, hidden=512, heads=4, kv=2, ffn=768, vocab=640)
+    lens = [3, 7, 1, 9, 2, 5, 4, 6, 1, 3, 2, 6]
+    ids = list(range(12))
+    prompts = [synth.prompt_tokens(n, spec.vocab_size, 40 + i).tolist() for i, n in enumerate(lens)]
+    runs = []
+    for _ in range(2):
+        eng, om = make_pair(gpu, oracle, spec, max_seq_len=48, max_seqs=12)
+        logits, nxt = eng.forward_batch(ids, prompts)
+        toks, _ms = eng.decode_loop(ids, nxt, 6)
+        runs.append((logits.copy(), nxt.copy(), toks.copy()))
+        if len(runs) == 1:
+            for i, p in enumerate(prompts):
+                om.kv_clear()
+                assert_close(logits[i], om.forward(p), LOGIT_ABS, LOGIT_REL, f"sequence {i}")
+                ref, margins = om.generate(p, 7, stop_on_eos=False, want_margins=True)
+                assert [int(nxt[i])] + toks[:, i].tolist() == ref, (i, margins)
+        eng.close()
+    assert np.array_equal(runs[0][0].view(np.uint32), runs[1][0].view(np.uint32))
+    assert np.array_equal(runs[0][2], runs[1][2])
+
+
 def test_error_paths(gpu):
     from leafcutterllm_b200 import synth
     spec = small_spec(12, 12, 12, layers=1)
