@@ -348,6 +348,40 @@ def attention_microbench(lc, n_heads=32, n_kv=32, hd=128, ctx=2100, layers=8, re
             "us_per_call": round(us, 2), "kv_bytes": byt, "achieved_gbs": round(byt / us / 1e3, 1)}
 
 
+def batched_decode(lc, synth, spec, local: int, n_seqs: int = 64, steps: int = 32, warm: int = 3) -> dict:
+    """BASELINE.json configs[2]: the same model under continuous batching -- 64 sequences whose context lengths are
+    uniform in [128, 4096] from seed 777, paged f16 KV cache (16-token pages), greedy decode.  Every sequence is
+    prefilled with its own seeded prompt (through the many-token tensor-core product), then `steps` decode steps are
+    timed on the device (CUDA events around the graph replays).  Bytes per step = weights once + every sequence's KV."""
+    import numpy as np
+    rng = np.random.default_rng(777)
+    ctx = rng.integers(128, 4097, n_seqs)
+    pool = int(sum((int(c) + warm + steps + 2 + 15) // 16 * 16 for c in ctx))
+    t0 = time.perf_counter()
+    eng = synth.build_engine(spec, 4096 + warm + steps + 16, on_device=True, device=local, max_seqs=n_seqs, kv_pool_tokens=pool)
+    first = []
+    for s_ in range(n_seqs):
+        prompt = synth.prompt_tokens(int(ctx[s_]), spec.vocab_size, 1000 + s_)
+        _, nxt = eng.forward_batch([s_], [prompt], want_logits=False)
+        first.append(int(nxt[0]))
+    t_prefill = time.perf_counter() - t0
+    ids = list(range(n_seqs))
+    toks, _ = eng.decode_loop(ids, first, warm)
+    eng.reset_counters()
+    toks, ms = eng.decode_loop(ids, toks[-1].tolist(), steps)
+    ctr = eng.counters()
+    eng.close()
+    peak, which = measured_peaks()
+    algo = ctr["algo_bytes_last_step"]
+    per_step = ms / steps
+    return {"workload": "configs[2]: 64 sequences, context lengths uniform in [128, 4096] (seed 777), paged f16 KV cache, greedy decode",
+            "value": round(n_seqs * steps / (ms * 1e-3), 1), "unit": "tok/s", "ms_per_step": round(per_step, 3), "steps": steps,
+            "sequences": n_seqs, "mean_context": round(float(ctx.mean()), 1), "tokens_prefilled": int(ctx.sum()),
+            "build_and_prefill_s": round(t_prefill, 2), "algorithmic_bytes_per_step": int(algo),
+            "achieved_gbs": round(algo / (per_step * 1e-3) / 1e9, 1), "peak_gbs": peak, "frac": round(algo / (per_step * 1e-3) / 1e9 / peak, 4),
+            "peak_source": which, "gpu_launches": int(ctr["kernel_launches"])}
+
+
 def run_ours(args):
     rank, world, local = dist_env()
     import leafcutterllm_b200 as lc
@@ -425,6 +459,8 @@ def run_ours(args):
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(spec)
     eng.close()
+    if rank == 0 and world == 1 and not args.no_bs64 and args.layers <= 0:
+        line["bs64"] = batched_decode(lc, synth, spec, local)
     ranks.close()
     if rank == 0:
         print(json.dumps(line))
@@ -461,7 +497,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemm", "gemm-small"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
+    ap.add_argument("--no-bs64", action="store_true", help="skip the 64-sequence continuous-batching leg (configs[2])")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemm", "gemm-small", "bs64"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
     ap.add_argument("--profile-range", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: keep this many of the 32 layers (the printed number is then not the metric)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="context prefilled before decoding (default: the 2048 of the workload)")
@@ -472,6 +509,14 @@ def main():
     elif args.only == "gemv-sweep":
         import leafcutterllm_b200 as lc
         print(json.dumps(gemv_sweep(lc)))
+    elif args.only == "bs64":
+        import leafcutterllm_b200 as lc
+        from leafcutterllm_b200 import synth
+        spec = synth.LLAMA7B if args.layers <= 0 else synth.LLAMA7B.with_layers(args.layers)
+        out = batched_decode(lc, synth, spec, 0, steps=min(args.steps, 32))
+        if args.layers > 0:
+            out["not_the_metric"] = f"profiling case: {args.layers} of 32 layers"
+        print(json.dumps(out))
     elif args.only in ("gemm", "gemm-small"):
         import leafcutterllm_b200 as lc
         print(json.dumps(gemm_microbench(lc, tokens=(64,) if args.only == "gemm-small" else (64, 512), small=args.only == "gemm-small")))
