@@ -13,14 +13,15 @@
 // accumulation; the two f16 scales of the unit are applied to the finished sums in f32.  One CTA owns 128 weight rows
 // (the M of tcgen05.mma) and up to 64 tokens, and walks k unit by unit:
 //
-//   producer   one thread: TMA boxes of raw blocks [144 B x 128 rows] per unit, per 64-element chunk of k the
-//              activation tile [64 x N] of f16 (128-byte rows, hardware swizzle 128B) as high halves and, right behind
-//              them, low halves of the split below, and per four units the tile of sub-block sums;
+//   producers  two threads: one requests the TMA boxes of raw blocks [144 B x 128 rows] per unit, the other per
+//              64-element chunk of k the activation tile [64 x N] of f16 (128-byte rows, hardware swizzle 128B) as high
+//              halves and, right behind them, low halves of the split below (one 3-D box), and per four units the tile
+//              of sub-block sums;
 //   unpack     two groups of 128 threads take the units in turn (for gate/up: one matrix each); thread r owns row r:
 //              nibbles -> (1024 + q) as f16 by a byte permute, times sc minus 1024 sc in one HFMA2 (exact), written
 //              with tcgen05.st straight into TENSOR MEMORY as the A operand (lane = row, one 32-bit column = two
 //              consecutive k): 1.4 instructions per weight, and unpacked weights never cross shared memory;
-//   multiply   one thread issues tcgen05.mma kind::f16, M=128, K=16, A from tensor memory, B from the swizzled tile.
+//   multiply   one thread per group issues tcgen05.mma kind::f16, M=128, K=16, A from tensor memory, B from the swizzled tile.
 //              Activations are x = hi + lo in f16 (2^-22 together); the high and the low tile lie one after the other,
 //              so ONE instruction with N = 2 x tokens forms both products (two column ranges, added in the drain);
 //              LC_GEMM_TERMS=1 keeps only the high halves (plain f16 activations, 2^-11);
@@ -30,7 +31,8 @@
 //
 // Activations are prepared by xprep_kernel: optional RMS norm (rust/src/backend/cpu.rs:49-60), a power-of-two scale per
 // token that brings its largest magnitude into [0.5, 1) (so neither half leaves the f16 range), the hi/lo split, and
-// the sub-block sums.  All products of a tile are issued by one thread, in order: results are deterministic.
+// the sub-block sums.  Every accumulator is written by one thread's products, in program order, and the two groups'
+// results are added in a fixed order: results are deterministic.
 //
 // Every wait is bounded; a wait that runs out sets the library's device error flag and the CTA winds down (tensor
 // memory freed, no copy left in flight).
