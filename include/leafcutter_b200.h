@@ -195,6 +195,25 @@ int32_t lc_model_destroy(lc_model* m);
 int32_t lc_model_load_gguf(const char* path, const lc_model_config* overrides, lc_model** out);
 int32_t lc_model_get_config(const lc_model* m, lc_model_config* out);
 
+/* ---- ShardEngine (rust/src/inference/shard_engine.rs:18-167): a model split into per-layer "LEAFSHDR" shards ----
+ * lc_shard_engine_load     <-> ShardEngine::load_with_cache(manifest_path, num_layers) (:34-61): reads manifest.json
+ *                              (rust/src/shard/loader.rs:13-50) and every shard (format.rs, loader.rs:300-367: F32, Q8_0 or
+ *                              Q4_0 blocks along the rows of [k][n] matrices) once; all layers stay in device memory.
+ *                              max_seq_len > 0 caps the KV capacity the manifest asks for.
+ * lc_shard_engine_forward  <-> ShardEngine::forward(&tokens) (:99-167): logits of the last token (logits_out [vocab], may be
+ *                              null) and its greedy pick (next_out, may be null); the cache grows by n.
+ * lc_shard_engine_generate <-> ShardEngine::generate (:74-97): clears the cache, first token from the prefill, at most
+ *                              max_tokens tokens, stops after token 2; temperature > 0 returns LC_ERR_UNSUPPORTED.
+ * lc_shard_engine_reset_kv_cache / _kv_cache_memory_bytes <-> reset_kv_cache (:64-66) / kv_cache_memory_mb (:69-71). */
+typedef struct lc_shard_engine lc_shard_engine;
+int32_t lc_shard_engine_load(const char* manifest_path, int32_t max_seq_len, int32_t device, lc_shard_engine** out);
+int32_t lc_shard_engine_forward(lc_shard_engine* e, const int64_t* tokens, int32_t n, float* logits_out, int64_t* next_out);
+int32_t lc_shard_engine_generate(lc_shard_engine* e, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature,
+                                 float top_p, int64_t* out_tokens, int32_t* n_out);
+int32_t lc_shard_engine_reset_kv_cache(lc_shard_engine* e);
+int32_t lc_shard_engine_kv_cache_memory_bytes(lc_shard_engine* e, uint64_t* out);
+int32_t lc_shard_engine_destroy(lc_shard_engine* e);
+
 /* KVCache::clear (rust/src/cache/mod.rs:26-30) for one sequence slot (seq_id < max_seqs); -1 = all. */
 int32_t lc_kv_clear(lc_model* m, int32_t seq_id);
 /* KVCache::memory_bytes (cache/mod.rs:80-84): bytes of K and V held for the live tokens. */

@@ -281,6 +281,12 @@ int32_t launch_rope_kv_append(float* q, float* k, const float* v, int row_stride
     return LC_OK;
 }
 
+// (token, head) pairs up to which decode attention uses the split-context kernel with shared-memory staging
+static int staged_pair_limit() {
+    static const int mult = getenv("LC_ATTN_STAGED_LIMIT") ? atoi(getenv("LC_ATTN_STAGED_LIMIT")) : 4;
+    return sm_count() * mult;
+}
+
 static void split_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_splits) {
     int want_ctas = sm_count() * 4;
     int base = n_tok * n_heads;
@@ -301,7 +307,7 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx) {
     int chunk, splits;
     split_plan(n_tok, n_heads, max_ctx, &chunk, &splits);
     size_t staged = (size_t)n_tok * n_heads * ((max_ctx + kStagedChunk - 1) / kStagedChunk) * (hd + 2) * sizeof(float);
-    if (n_tok * n_heads > sm_count() * 4) staged = 16;
+    if (n_tok * n_heads > staged_pair_limit()) staged = 16;
     size_t plain = splits == 1 ? 16 : (size_t)n_tok * n_heads * splits * (hd + 2) * sizeof(float);
     return plain > staged ? plain : staged;
 }
@@ -309,7 +315,7 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx) {
 static bool staged_applies(const AttnParams& p, int n_tok) {
     static const bool off = getenv("LC_ATTN_NO_STAGED") != nullptr;
     // few tokens (decode): the split-context kernel with shared-memory staging; many tokens (prefill) keep one CTA per (token, head)
-    return !off && p.kv.hd == 128 && !p.kv.kv_f32 && p.kv.page_tokens == 16 && n_tok * p.n_heads <= sm_count() * 4;
+    return !off && p.kv.hd == 128 && !p.kv.kv_f32 && p.kv.page_tokens == 16 && n_tok * p.n_heads <= staged_pair_limit();
 }
 
 template <int HD>

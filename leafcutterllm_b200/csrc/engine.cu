@@ -234,6 +234,7 @@ KvLayout kv_layout(const lc_model* m, int layer) {
     kv.hd = m->hd;
     kv.page_tokens = m->page_tokens;
     kv.kv_f32 = m->cfg.kv_dtype;
+    kv.pool_pages = m->pages_total;
     kv.k_tmap = m->k_tmaps_ok ? (const void*)m->k_tmaps[layer].b : nullptr;
     kv.v_tmap = m->k_tmaps_ok ? (const void*)m->v_tmaps[layer].b : nullptr;
     return kv;
@@ -561,8 +562,8 @@ static int32_t check_device_flag(lc_model* m) {
     LC_CUDA(cudaStreamSynchronize(m->stream));
     if (v != 0) {
         cudaMemsetAsync(f, 0, sizeof(int), m->stream);
-        set_error("a bounded device-side wait ran out (%s); the results of this call are not valid",
-                  v == 2 ? "grid barrier of the persistent decode kernel" : "TMA transaction barrier");
+        set_error("a device-side check failed (code %d: %s); the results of this call are not valid", v,
+                  v == 2 ? "grid barrier of the persistent decode kernel" : v >= 20 ? "an index outside its range" : "a bounded wait ran out");
         return LC_ERR_CUDA;
     }
     return LC_OK;

@@ -113,6 +113,7 @@ struct KvLayout {
     void* v_pool = nullptr;
     int n_kv = 0, hd = 0, page_tokens = 16;
     int kv_f32 = 0;
+    int pool_pages = 0;      // pages in each pool (0 = unknown); kernels that check their page-table entries use it
     const void* k_tmap = nullptr;  // host copies of tensor maps over k_pool and v_pool (make_key_pool_tmap), or null
     const void* v_tmap = nullptr;
 };

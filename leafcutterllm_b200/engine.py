@@ -159,3 +159,55 @@ class Engine:
             self.close()
         except Exception:
             pass
+
+
+class ShardEngine:
+    """Host-side mirror of the reference's `ShardEngine` (rust/src/inference/shard_engine.rs:18-97): a model split into a
+    manifest.json and per-layer LEAFSHDR shard files.  The reference maps one layer at a time from disk; here every shard
+    is read once and kept in device memory, which is what `load_with_cache(path, num_layers)` asks for there."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    @classmethod
+    def load(cls, manifest_path: str, max_seq_len: int = 0, device: int = 0) -> "ShardEngine":
+        h = C.c_void_p()
+        check(load().lc_shard_engine_load(str(manifest_path).encode(), max_seq_len, device, C.byref(h)))
+        return cls(h)
+
+    @classmethod
+    def load_with_cache(cls, manifest_path: str, cache_slots: int, max_seq_len: int = 0, device: int = 0) -> "ShardEngine":
+        del cache_slots  # every layer is resident
+        return cls.load(manifest_path, max_seq_len, device)
+
+    def forward(self, tokens: Iterable[int], vocab_size: int) -> np.ndarray:
+        t = np.ascontiguousarray(list(tokens), dtype=np.int64)
+        out = np.empty(vocab_size, np.float32)
+        check(load().lc_shard_engine_forward(self._h, _p(t), t.size, _p(out), None))
+        return out
+
+    def generate(self, tokens: Iterable[int], max_tokens: int, temperature: float = 0.0, top_p: float = 1.0) -> list:
+        t = np.ascontiguousarray(list(tokens), dtype=np.int64)
+        out = np.empty(max_tokens, np.int64)
+        n_out = C.c_int32()
+        check(load().lc_shard_engine_generate(self._h, _p(t), t.size, max_tokens, temperature, top_p, _p(out), C.byref(n_out)))
+        return out[: n_out.value].tolist()
+
+    def reset_kv_cache(self) -> None:
+        check(load().lc_shard_engine_reset_kv_cache(self._h))
+
+    def kv_cache_memory_mb(self) -> float:
+        out = C.c_uint64()
+        check(load().lc_shard_engine_kv_cache_memory_bytes(self._h, C.byref(out)))
+        return out.value / (1024.0 * 1024.0)
+
+    def close(self) -> None:
+        if self._h:
+            load().lc_shard_engine_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
