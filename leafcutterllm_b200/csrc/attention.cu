@@ -294,6 +294,9 @@ static void split_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_s
     if (splits < 1) splits = 1;
     int ch = (max_ctx + splits - 1) / splits;
     ch = (ch + 63) / 64 * 64;
+    // A batched decode step (up to 256 tokens, each over its own long context): contexts differ widely, and the CTA of the
+    // longest one would run on alone at the end; 1024-key pieces keep the tail short (64 sequences: 2.66 -> 2.49 ms for 4 layers).
+    if (n_tok <= 256 && ch > 1024) ch = 1024;
     static const int force = getenv("LC_ATTN_CHUNK") ? atoi(getenv("LC_ATTN_CHUNK")) : 0;  // experiments only
     if (force > 0) ch = force;
     *chunk = ch;

@@ -60,6 +60,34 @@ __device__ __forceinline__ void load_slice(const void* pool, size_t elem_off, fl
     }
 }
 
+// The same slice kept as it lies in the cache (16-byte pieces), so that a pass's loads can be in flight while the pass
+// before it is still being computed without doubling the registers that hold them as f32.
+template <int DPL, bool F32>
+struct RawSlice { uint4 v[F32 ? DPL / 4 : DPL / 8]; };
+template <int DPL, bool F32>
+__device__ __forceinline__ void load_raw(const void* pool, size_t elem_off, RawSlice<DPL, F32>& r) {
+    const uint4* p = F32 ? reinterpret_cast<const uint4*>((const float*)pool + elem_off) : reinterpret_cast<const uint4*>((const __half*)pool + elem_off);
+#pragma unroll
+    for (int i = 0; i < (F32 ? DPL / 4 : DPL / 8); i++) r.v[i] = p[i];
+}
+template <int DPL, bool F32>
+__device__ __forceinline__ void widen(const RawSlice<DPL, F32>& r, float (&out)[DPL]) {
+    if (F32) {
+#pragma unroll
+        for (int i = 0; i < DPL / 4; i++) {
+            out[4 * i] = __uint_as_float(r.v[i].x); out[4 * i + 1] = __uint_as_float(r.v[i].y);
+            out[4 * i + 2] = __uint_as_float(r.v[i].z); out[4 * i + 3] = __uint_as_float(r.v[i].w);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < DPL / 8; i++) {
+            const __half2* h = reinterpret_cast<const __half2*>(&r.v[i]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) { float2 f = __half22float2(h[j]); out[8 * i + 2 * j] = f.x; out[8 * i + 2 * j + 1] = f.y; }
+        }
+    }
+}
+
 // Dims d0 .. d0+DPL-1 of a head vector at `base`, rotated by position `rp` (attention.rs:13-34: pairs
 // (d, d + hd/2), freq = 1 / theta^(2d/hd)).  rp == 0 is the identity and skips the trigonometry.
 template <int DPL, int HD>
@@ -144,12 +172,13 @@ __device__ __forceinline__ void attention_item(const AttnParams& p, int item, in
         };
         // Cached keys are loaded unconditionally (padding lanes re-read the first key of the slice) so that the
         // loads of both keys of a pass are in flight together; the token of this step is handled after the loop.
-        auto fetch = [&](int t, bool valid, float (&kr)[DPL], float (&vr)[DPL]) {
+        typedef RawSlice<DPL, F32> Raw;
+        auto fetch = [&](int t, bool valid, Raw& kr, Raw& vr) {
             const size_t a = key_addr(valid ? t : t_begin);
-            load_slice<DPL, F32>(kv.k_pool, a, kr);
-            load_slice<DPL, F32>(kv.v_pool, a, vr);
+            load_raw<DPL, F32>(kv.k_pool, a, kr);
+            load_raw<DPL, F32>(kv.v_pool, a, vr);
         };
-        auto update = [&](bool valid, const float (&kr)[DPL], const float (&vr)[DPL]) {
+        auto update_f = [&](bool valid, const float (&kr)[DPL], const float (&vr)[DPL]) {
             float dot = 0.f;
 #pragma unroll
             for (int i = 0; i < DPL; i++) dot = fmaf(qr[i], kr[i], dot);
@@ -170,18 +199,36 @@ __device__ __forceinline__ void attention_item(const AttnParams& p, int item, in
                 for (int i = 0; i < DPL; i++) acc[i] = fmaf(pexp, vr[i], acc[i]);
             }
         };
+        auto update = [&](bool valid, const Raw& kraw, const Raw& vraw) {
+            float kr[DPL], vr[DPL];
+            widen<DPL, F32>(kraw, kr);
+            widen<DPL, F32>(vraw, vr);
+            update_f(valid, kr, vr);
+        };
 
         const bool has_new = p.k_new != nullptr && pos >= t_begin && pos < t_end;
         const int t_cached = has_new ? pos : t_end;  // the slot of the new token is not read from the cache
         if (t_begin < t_cached) {
+            // software pipeline: the loads of pass i + 1 are issued before pass i is computed
+            Raw ka, va, kb, vb;
+            {
+                const int ta = t_begin + warp * KPW + grp, tb = ta + KPI;
+                fetch(ta, ta < t_cached, ka, va);
+                fetch(tb, tb < t_cached, kb, vb);
+            }
             for (int t0 = t_begin; t0 < t_cached; t0 += 2 * KPI) {
                 const int ta = t0 + warp * KPW + grp, tb = ta + KPI;
-                const bool va = ta < t_cached, vb = tb < t_cached;
-                float ka[DPL], vva[DPL], kb[DPL], vvb[DPL];
-                fetch(ta, va, ka, vva);
-                fetch(tb, vb, kb, vvb);
-                update(va, ka, vva);
-                update(vb, kb, vvb);
+                const bool va_ok = ta < t_cached, vb_ok = tb < t_cached;
+                Raw nka, nva, nkb, nvb;
+                const bool more = t0 + 2 * KPI < t_cached;
+                if (more) {
+                    const int na = ta + 2 * KPI, nb = tb + 2 * KPI;
+                    fetch(na, na < t_cached, nka, nva);
+                    fetch(nb, nb < t_cached, nkb, nvb);
+                }
+                update(va_ok, ka, va);
+                update(vb_ok, kb, vb);
+                if (more) { ka = nka; va = nva; kb = nkb; vb = nvb; }
             }
         }
         if (has_new) {
@@ -199,7 +246,7 @@ __device__ __forceinline__ void attention_item(const AttnParams& p, int item, in
 #pragma unroll
                 for (int i = 0; i < DPL; i++) { kr[i] = __half2float(__float2half_rn(kr[i])); vr[i] = __half2float(__float2half_rn(vr[i])); }
             }
-            update(warp == 0 && grp == 0, kr, vr);  // counted once: by the first key group of the first warp
+            update_f(warp == 0 && grp == 0, kr, vr);  // counted once: by the first key group of the first warp
         }
         // merge the key groups of the warp (lanes with equal `sub` hold the same dims), fixed order
 #pragma unroll
