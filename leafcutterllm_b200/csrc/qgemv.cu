@@ -618,6 +618,11 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
             return launch_qgemv(hi, s);
         }
     }
+    {
+        bool launched = false;
+        LC_TRY(launch_qgemv_kq(a, s, &launched));  // Q5_K / Q6_K with whole 256-element blocks
+        if (launched) return LC_OK;
+    }
     return launch_generic(a, s);
 }
 
