@@ -93,6 +93,8 @@ struct lc_model {
     bool dataflow_step = false;    // set while the kernels of such a step are being queued
     void* d_attn_scratch = nullptr;
     GemmWorkspace gemm_ws;  // f16 activation halves for the many-token tensor-core product
+    bool any_unfused_qkv = false;  // some layer's q/k/v differ in type
+    float* d_qkv_parts = nullptr;  // then: [T][nq] | [T][nkv hd] | [T][nkv hd] before they are interleaved into d_qkv
     int* d_attn_counters = nullptr;
     size_t attn_scratch_bytes = 0;
     unsigned long long* d_sanity = nullptr;
@@ -326,9 +328,26 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
         if (!(ablate_mask() & 2))
         // the fused output is [T, nqkv] only when every token tile writes rows of nqkv floats
         LC_TRY(gemv_tiled(m, g, T, m->nqkv, m->H));
-    } else {
-        // separate projections write into column blocks of d_qkv; stride handled by per-token launches
-        LC_CHECK(false, LC_ERR_UNSUPPORTED, "q/k/v projections of layer %d differ in type and cannot be fused", l);
+    } else if (!(ablate_mask() & 2)) {
+        // q/k/v of different types: three products.  One token writes straight into its row of d_qkv; several tokens go
+        // through contiguous parts and are interleaved into the [T][nq + 2 nkv hd] rows the attention kernels expect.
+        LC_CHECK(!df, LC_ERR_STATE, "dataflow step with unfused projections");
+        const int nq = m->nh * m->hd, nkvd = m->nkv * m->hd;
+        const QWeight* ws3[3] = {&w.q, &w.k, &w.v};
+        const int ns[3] = {nq, nkvd, nkvd};
+        size_t part_off = 0, col_off = 0;
+        for (int i = 0; i < 3; i++) {
+            g.w = ws3[i];
+            g.out = T == 1 ? m->d_qkv + col_off : m->d_qkv_parts + part_off;
+            LC_TRY(gemv_tiled(m, g, T, ns[i], m->H));
+            if (T > 1) {
+                LC_CUDA(cudaMemcpy2DAsync(m->d_qkv + col_off, (size_t)m->nqkv * 4, g.out, (size_t)ns[i] * 4, (size_t)ns[i] * 4, (size_t)T,
+                                          cudaMemcpyDeviceToDevice, m->stream));
+                m->launches_in_call += 1;
+            }
+            part_off += (size_t)T * ns[i];
+            col_off += ns[i];
+        }
     }
     KvLayout kv = kv_layout(m, l);
     float* q = m->d_qkv;
@@ -715,9 +734,10 @@ int32_t lc_model_finalize(lc_model* m) {
         LC_TRY(weight_of(m, p + "attn_q.weight", nq, H, &w.q, &tq));
         LC_TRY(weight_of(m, p + "attn_k.weight", nkvd, H, &w.k, &tk));
         LC_TRY(weight_of(m, p + "attn_v.weight", nkvd, H, &w.v, &tv));
-        LC_CHECK(tq->typ == tk->typ && tq->typ == tv->typ, LC_ERR_UNSUPPORTED,
-                 "layer %d: q/k/v projections have different quant types (%u, %u, %u)", l, tq->typ, tk->typ, tv->typ);
-        {   // one [nq + 2 nkv, H] matrix so the three projections are one pass
+        if (tq->typ != tk->typ || tq->typ != tv->typ) {
+            // mixed files ("Q4_K_M" keeps attn_v in Q6_K): three separate products per layer
+            m->any_unfused_qkv = true;
+        } else {   // one [nq + 2 nkv, H] matrix so the three projections are one pass
             size_t total = tq->nbytes + tk->nbytes + tv->nbytes;
             uint8_t* buf = nullptr;
             LC_TRY(dalloc(&buf, total));
@@ -833,6 +853,7 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(dalloc(&m->d_qkv, (size_t)T * m->nqkv)); LC_TRY(dalloc(&m->d_attn, (size_t)T * nq));
     LC_TRY(dalloc(&m->d_ffn, (size_t)T * F));
     LC_TRY(qgemm_workspace_alloc(&m->gemm_ws, T, std::max(std::max(H, F), nq)));
+    if (m->any_unfused_qkv) LC_TRY(dalloc(&m->d_qkv_parts, (size_t)T * m->nqkv));
     LC_TRY(dalloc(&m->d_last, (size_t)m->max_seqs * H)); LC_TRY(dalloc(&m->d_logits, (size_t)m->max_seqs * V));
     LC_TRY(dalloc(&m->d_next, m->max_seqs)); LC_TRY(dalloc(&m->d_step_ctr, 1));
     size_t sc = 16;
@@ -868,7 +889,7 @@ int32_t lc_model_destroy(lc_model* m) {
     void* bufs[] = {m->f_hidden, m->f_hidden2, m->f_qkv, m->f_attn, m->f_ffn, m->d_epoch,
                     m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
-                    m->d_attn_scratch, m->d_attn_counters, m->d_sanity};
+                    m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};
     for (void* p : bufs) if (p) cudaFree(p);
     qgemm_workspace_free(&m->gemm_ws);
     if (m->pin_tokens) cudaFreeHost(m->pin_tokens);

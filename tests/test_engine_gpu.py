@@ -118,6 +118,46 @@ def test_many_sequences_decode_through_the_tensor_core_gemm(gpu, oracle):
     assert np.array_equal(runs[0][2], runs[1][2])
 
 
+def test_mixed_quant_types_like_q4_k_m(gpu, oracle):
+    """A "Q4_K_M" file keeps attn_v and ffn_down in Q6_K while q, k, o, gate and up are Q4_K: the three projections of a
+    layer then cannot be one matrix (three products per layer) and the Q6_K matrices run through the K-quant kernel.
+    Prefill (17 tokens: the unfused parts are interleaved into the q/k/v rows), decode and greedy tokens against the oracle."""
+    from leafcutterllm_b200 import Engine, synth
+    H, Fd, V, nh, nkv, L = 256, 512, 384, 2, 1, 2
+    r = np.random.default_rng(8)
+
+    def q6k(rows, cols):  # random blocks with small scales (no host quantiser for Q6_K): |w| stays below ~0.3
+        raw = r.integers(0, 256, (rows * cols // 256, 210), dtype=np.uint8)
+        raw[:, 192:208] = r.integers(-40, 41, (raw.shape[0], 16)).astype(np.int8).view(np.uint8)
+        d = np.float16(r.uniform(2e-5, 2e-4, raw.shape[0])).view(np.uint16)
+        raw[:, 208] = d & 0xFF
+        raw[:, 209] = d >> 8
+        return raw.ravel()
+
+    eng = Engine(H, L, nh, nkv, Fd, V, max_seq_len=64)
+    om = oracle.OracleModel(H, L, nh, nkv, Fd, V, max_seq_len=64)
+    hd = H // nh
+    tensors = [("token_embd.weight", 12, (H, V)), ("output_norm.weight", 0, (H,)), ("output.weight", 14, (H, V))]
+    for l in range(L):
+        p = f"blk.{l}."
+        tensors += [(p + "attn_norm.weight", 0, (H,)), (p + "attn_q.weight", 12, (H, nh * hd)), (p + "attn_k.weight", 12, (H, nkv * hd)),
+                    (p + "attn_v.weight", 14, (H, nkv * hd)), (p + "attn_output.weight", 12, (nh * hd, H)), (p + "ffn_norm.weight", 0, (H,)),
+                    (p + "ffn_gate.weight", 12, (H, Fd)), (p + "ffn_up.weight", 12, (H, Fd)), (p + "ffn_down.weight", 14, (Fd, H))]
+    for name, typ, dims in tensors:
+        n = int(np.prod(dims))
+        data = np.ones(n, np.float32).view(np.uint8) if typ == 0 else (q6k(dims[1], dims[0]) if typ == 14 else synth.host_tensor(typ, 21, name, n))
+        eng.set_tensor(name, typ, dims, data)
+        om.set_tensor(name, typ, list(dims), data)
+    eng.finalize()
+    prompt = synth.prompt_tokens(17, V, 2)
+    assert_close(eng.forward(prompt), om.forward(prompt), LOGIT_ABS, LOGIT_REL, "prefill logits, mixed types")
+    nxt = 5
+    assert_close(eng.forward([nxt]), om.forward([nxt]), LOGIT_ABS, LOGIT_REL, "decode logits, mixed types")
+    ref, margins = om.generate(prompt, 10, stop_on_eos=False, want_margins=True)
+    assert eng.generate(prompt, 10, stop_on_eos=False) == ref, margins
+    eng.close()
+
+
 def test_error_paths(gpu):
     from leafcutterllm_b200 import synth
     spec = small_spec(12, 12, 12, layers=1)
