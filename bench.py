@@ -211,6 +211,39 @@ def gemv_sweep(lc) -> dict:
     return {"kernel": "Q4_K GEMV, one token" + (" (tcgen05 variant)" if os.environ.get("LC_GEMV_UMMA") else ""), "sweep": rows}
 
 
+def gemv_types(lc) -> dict:
+    """One-token matrix-vector product per ggml type on two 7B shapes, timed alone over >= 300 MB of distinct weights (any
+    bytes do for timing: the buffers are filled by the f32 generator and read as blocks of the type)."""
+    import ctypes as C
+    lib = lc.load()
+    chk = lc._capi.check
+    rows = []
+    for typ, name in [(12, "Q4_K"), (13, "Q5_K"), (14, "Q6_K"), (2, "Q4_0"), (8, "Q8_0"), (20, "IQ4_NL"), (1, "F16")]:
+        for (k, n) in [(4096, 4096), (11008, 4096)]:
+            nb = lib.lc_tensor_bytes(typ, k * n)
+            copies = max(2, int(300e6 // nb))
+            x = C.c_void_p(); y = C.c_void_p()
+            chk(lib.lc_dev_alloc(4 * k, C.byref(x))); chk(lib.lc_dev_alloc(4 * n, C.byref(y)))
+            chk(lib.lc_synth_tensor_dev(0, 1, b"x", 1.0, k, x))
+            ws = []
+            for c in range(copies):
+                p = C.c_void_p(); chk(lib.lc_dev_alloc(nb + 16, C.byref(p)))
+                chk(lib.lc_synth_tensor_dev(0, 7, f"t{c}".encode(), 0.02, nb // 4, p)); ws.append(p)
+            for p in ws:
+                chk(lib.lc_qmatmul_dev(typ, x, p, 1, k, n, y))
+            chk(lib.lc_dev_sync()); chk(lib.lc_timer_begin())
+            for _ in range(3):
+                for p in ws:
+                    chk(lib.lc_qmatmul_dev(typ, x, p, 1, k, n, y))
+            ms = C.c_float(); chk(lib.lc_timer_end(C.byref(ms)))
+            us = ms.value * 1e3 / (3 * copies)
+            rows.append({"type": name, "k": k, "n": n, "MB": round(nb / 1e6, 2), "us_per_launch": round(us, 1), "GBps": round(nb / us / 1e3, 1)})
+            for p in ws:
+                lib.lc_dev_free(p)
+            lib.lc_dev_free(x); lib.lc_dev_free(y)
+    return {"kernel": "matrix-vector product, one token, per ggml type", "rows": rows}
+
+
 def gemm_microbench(lc, tokens=(64, 512), small: bool = False) -> dict:
     """The many-token tensor-core product (Q4_K weights dequantised on the fly, tcgen05) timed alone on the 7B shapes:
     per shape and token count the time of one launch pair (activation split + product) over distinct weight copies
@@ -498,7 +531,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-bs64", action="store_true", help="skip the 64-sequence continuous-batching leg (configs[2])")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemm", "gemm-small", "bs64"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
     ap.add_argument("--profile-range", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: keep this many of the 32 layers (the printed number is then not the metric)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="context prefilled before decoding (default: the 2048 of the workload)")
@@ -509,6 +542,9 @@ def main():
     elif args.only == "gemv-sweep":
         import leafcutterllm_b200 as lc
         print(json.dumps(gemv_sweep(lc)))
+    elif args.only == "gemv-types":
+        import leafcutterllm_b200 as lc
+        print(json.dumps(gemv_types(lc)))
     elif args.only == "bs64":
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth

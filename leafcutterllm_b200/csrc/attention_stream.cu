@@ -113,12 +113,17 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     if (warp == kCWarps) {
         // ---- producer: lane i requests items i, i + 32, ... -- each needs a page-table entry from global memory, and one
         //      thread walking them one after the other made that latency, not HBM, the pace of the whole kernel ----
-        for (int i = lane; i < n_items; i += 32) {
+        // Producing lanes: min(32, S), so that a lane's items all use one stage and a lane only ever waits for the
+        // consumption of its OWN previous item.  With 32 lanes over fewer stages a lane could wait for an item that a lane
+        // of the same round has yet to request; lanes that need no wait can be held at the reconvergence point behind the
+        // waiting ones, and then nobody requests it.
+        const int PL = S < 32 ? S : 32;
+        for (int i = lane; lane < PL && i < n_items; i += PL) {
             const int gi = i_begin + i;
             const int kvh = gi / np, page = gi - kvh * np;
             const int pg = pt[page];
             const int st = i % S;
-            if (i >= S) ok = mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1)) && ok;
+            if (i >= S && !mbar_wait(&empty[st], (uint32_t)((i / S - 1) & 1))) { ok = false; break; }  // never arm a barrier that is still pending
             mbar_expect_tx(&full[st], kStageBytes);
             unsigned char* dst = ring + (size_t)st * kStageBytes;
             const int y = (pg * kv.n_kv + kvh) * kPage;  // first row of the slab in the pool seen as [rows][128]
