@@ -101,7 +101,7 @@ constexpr size_t kMaxSmem = 227 * 1024;
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
 // true when the single-token kernel fits shared memory for rows of k elements
 bool qgemv_mma_supports(int k);
-// qgemv_kq.cu: Q5_K and Q6_K, up to eight tokens, plain loads; *launched = false for other types or shapes.
+// qgemv_kq.cu: Q5_K, Q6_K, F16 and F32, up to eight tokens, plain loads; *launched = false for other types or shapes.
 int32_t launch_qgemv_kq(const GemvArgs& a, cudaStream_t s, bool* launched);
 // qgemv_umma.cu: Q4_K for one or two tokens through tcgen05.mma with accumulators in tensor memory.
 int32_t launch_qgemv_umma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);

@@ -620,7 +620,7 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
     }
     {
         bool launched = false;
-        LC_TRY(launch_qgemv_kq(a, s, &launched));  // Q5_K / Q6_K with whole 256-element blocks
+        LC_TRY(launch_qgemv_kq(a, s, &launched));  // Q5_K / Q6_K with whole 256-element blocks, F16 / F32 rows
         if (launched) return LC_OK;
     }
     return launch_generic(a, s);

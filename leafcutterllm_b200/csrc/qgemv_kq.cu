@@ -1,4 +1,4 @@
-// Matrix-vector products over Q5_K and Q6_K weights (rust/src/kernels/mod.rs:101-180): the types a "Q4_K_M" or "Q5_K_M"
+// Matrix-vector products over Q5_K and Q6_K weights (rust/src/kernels/mod.rs:101-180), and over IQ4_NL and plain F16 / F32 matrices: the types a "Q4_K_M" or "Q5_K_M"
 // GGUF file mixes with Q4_K (attn_v, ffn_down, output).  One warp per group of one or two output rows; a few lanes share a 256-element
 // super-block, each taking the elements that live in the same 16 bytes of every plane of the block, so that a block's
 // bytes are read once, in 16-byte (Q5_K) or 2-byte (Q6_K: 210-byte blocks are only 2-byte aligned) pieces, and unpacked
@@ -217,12 +217,194 @@ int32_t launch_kq(const GemvArgs& a, cudaStream_t s) {
     return LC_OK;
 }
 
+// F16 / F32 matrices (unquantised GGUF files, rust/src/model/loader.rs:213-224): one warp per row, eight weights per lane
+// and load, activations from L1.  Pure streaming: 2 or 4 bytes per weight.
+template <bool F32, int M>
+__global__ void __launch_bounds__(kWarps * 32)
+qgemv_dense_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ w2, GemvParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scale_sh[M];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (p.norm_w) {
+        for (int t = warp; t < p.m; t += kWarps) {
+            float ss = 0.f;
+            for (int i = lane; i < p.k; i += 32) { const float v = p.x[(size_t)t * p.k + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) scale_sh[t] = 1.0f / sqrtf(ss / (float)p.k + p.eps);
+        }
+        __syncthreads();
+    }
+    float scale[M];
+#pragma unroll
+    for (int t = 0; t < M; t++) scale[t] = (p.norm_w && t < p.m) ? scale_sh[t] : 1.f;
+    const size_t row_bytes = (size_t)p.k * (F32 ? 4 : 2);
+    const int two = p.epi == EPI_SILU_MUL ? 1 : 0;
+    for (int row = blockIdx.x * kWarps + warp; row < p.n; row += gridDim.x * kWarps) {
+        float acc[M], acc2[M];
+#pragma unroll
+        for (int t = 0; t < M; t++) acc[t] = acc2[t] = 0.f;
+        for (int e = lane * 8; e < p.k; e += 256) {
+            float wv[8], wv2[8];
+            auto load8 = [&](const uint8_t* base, float (&o)[8]) {
+                if (F32) {
+                    const float4 a = __ldg(reinterpret_cast<const float4*>(base + (size_t)row * row_bytes) + e / 4);
+                    const float4 b = __ldg(reinterpret_cast<const float4*>(base + (size_t)row * row_bytes) + e / 4 + 1);
+                    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+                } else {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(base + (size_t)row * row_bytes) + e / 8);
+                    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { const float2 f = __half22float2(h[j]); o[2 * j] = f.x; o[2 * j + 1] = f.y; }
+                }
+            };
+            load8(w, wv);
+            if (two) load8(w2, wv2);
+#pragma unroll
+            for (int t = 0; t < M; t++) {
+                if (t >= p.m) break;
+                const float4 xa = __ldg(reinterpret_cast<const float4*>(p.x + (size_t)t * p.k + e));
+                const float4 xb = __ldg(reinterpret_cast<const float4*>(p.x + (size_t)t * p.k + e) + 1);
+                float x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                if (p.norm_w) {
+                    const float4 ga = __ldg(reinterpret_cast<const float4*>(p.norm_w + e));
+                    const float4 gb = __ldg(reinterpret_cast<const float4*>(p.norm_w + e) + 1);
+                    const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+                    for (int j = 0; j < 8; j++) x[j] = (x[j] * scale[t]) * g[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) { acc[t] = fmaf(x[j], wv[j], acc[t]); if (two) acc2[t] = fmaf(x[j], wv2[j], acc2[t]); }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < M; t++) {
+            if (t >= p.m) break;
+            float y = warp_sum(acc[t]);
+            const float y2 = two ? warp_sum(acc2[t]) : 0.f;
+            if (lane == 0) {
+                if (two) y = silu_f(y) * y2;
+                else if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[(size_t)t * p.n + row] + y;
+                p.out[(size_t)t * p.n + row] = y;
+            }
+        }
+    }
+}
+
+template <bool F32, int M>
+int32_t launch_dense(const GemvArgs& a, cudaStream_t s) {
+    GemvParams p;
+    p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
+    p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = nullptr;
+    int grid = (p.n + kWarps - 1) / kWarps;
+    const int cap = sm_count() * 8;
+    if (grid > cap) grid = cap;
+    const uint8_t* w2 = a.w2 ? (const uint8_t*)a.w2->data : nullptr;
+    LC_CUDA(launch_pdl(qgemv_dense_kernel<F32, M>, dim3(grid), dim3(kWarps * 32), 0, s, (const uint8_t*)a.w->data, w2, p));
+    return LC_OK;
+}
+
+// IQ4_NL (mod.rs:186-216): 18-byte blocks of 32 weights, f16 scale, nibble e & 1 of byte e >> 1 indexes the reference's
+// own 16-entry table.  One warp per row, a lane per block and turn; the table sits in shared memory.
+template <int M>
+__global__ void __launch_bounds__(kWarps * 32)
+qgemv_iq4nl_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ w2, GemvParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scale_sh[M];
+    __shared__ float lut[16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x < 16) {
+        const float T[16] = {-1.0f, -0.6962f, -0.5251f, -0.3952f, -0.2893f, -0.1957f, -0.1107f, -0.0322f,
+                             0.0322f, 0.1107f, 0.1957f, 0.2893f, 0.3952f, 0.5251f, 0.6962f, 1.0f};
+        lut[threadIdx.x] = T[threadIdx.x];
+    }
+    if (p.norm_w) {
+        for (int t = warp; t < p.m; t += kWarps) {
+            float ss = 0.f;
+            for (int i = lane; i < p.k; i += 32) { const float v = p.x[(size_t)t * p.k + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) scale_sh[t] = 1.0f / sqrtf(ss / (float)p.k + p.eps);
+        }
+    }
+    __syncthreads();
+    float scale[M];
+#pragma unroll
+    for (int t = 0; t < M; t++) scale[t] = (p.norm_w && t < p.m) ? scale_sh[t] : 1.f;
+    const int nb = p.k / 32;
+    const size_t row_bytes = (size_t)nb * 18;
+    const int two = p.epi == EPI_SILU_MUL ? 1 : 0;
+    for (int row = blockIdx.x * kWarps + warp; row < p.n; row += gridDim.x * kWarps) {
+        float acc[M], acc2[M];
+#pragma unroll
+        for (int t = 0; t < M; t++) acc[t] = acc2[t] = 0.f;
+        for (int b = lane; b < nb; b += 32) {
+            float wv[32], wv2[32];
+            auto load_block = [&](const uint8_t* base, float (&o)[32]) {
+                const uint8_t* bp = base + (size_t)row * row_bytes + (size_t)b * 18;
+                const float sc = h2f(__ldg(reinterpret_cast<const uint16_t*>(bp)));
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t q = ldg16x2(bp + 2 + 4 * i);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const uint32_t byte = (q >> (8 * j)) & 0xFFu;
+                        o[8 * i + 2 * j] = __fmul_rn(sc, lut[byte & 0x0Fu]);
+                        o[8 * i + 2 * j + 1] = __fmul_rn(sc, lut[byte >> 4]);
+                    }
+                }
+            };
+            load_block(w, wv);
+            if (two) load_block(w2, wv2);
+#pragma unroll
+            for (int t = 0; t < M; t++) {
+                if (t >= p.m) break;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    float x[16];
+                    load_x16(p, t, b * 32 + 16 * h, scale[t], x);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) { acc[t] = fmaf(x[j], wv[16 * h + j], acc[t]); if (two) acc2[t] = fmaf(x[j], wv2[16 * h + j], acc2[t]); }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < M; t++) {
+            if (t >= p.m) break;
+            float y = warp_sum(acc[t]);
+            const float y2 = two ? warp_sum(acc2[t]) : 0.f;
+            if (lane == 0) {
+                if (two) y = silu_f(y) * y2;
+                else if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[(size_t)t * p.n + row] + y;
+                p.out[(size_t)t * p.n + row] = y;
+            }
+        }
+    }
+}
+
+template <int M>
+int32_t launch_iq4nl(const GemvArgs& a, cudaStream_t s) {
+    GemvParams p;
+    p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
+    p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = nullptr;
+    int grid = (p.n + kWarps - 1) / kWarps;
+    const int cap = sm_count() * 8;
+    if (grid > cap) grid = cap;
+    const uint8_t* w2 = a.w2 ? (const uint8_t*)a.w2->data : nullptr;
+    LC_CUDA(launch_pdl(qgemv_iq4nl_kernel<M>, dim3(grid), dim3(kWarps * 32), 0, s, (const uint8_t*)a.w->data, w2, p));
+    return LC_OK;
+}
+
 }  // namespace
 
 int32_t launch_qgemv_kq(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = false;
     const uint32_t typ = a.w->typ;
-    if ((typ != LC_TYPE_Q6_K && typ != LC_TYPE_Q5_K) || a.w->k % 256 != 0 || a.m < 1 || a.m > 8) return LC_OK;
+    const bool kq = typ == LC_TYPE_Q6_K || typ == LC_TYPE_Q5_K, dense = typ == LC_TYPE_F16 || typ == LC_TYPE_F32, iq = typ == LC_TYPE_IQ4_NL;
+    if ((!kq && !dense && !iq) || a.m < 1 || a.m > 8) return LC_OK;
+    if (iq && (a.w->k % 32 != 0 || a.m > 2)) return LC_OK;  // a lane holds a whole block per matrix in registers: one or two tokens
+    if (kq && a.w->k % 256 != 0) return LC_OK;
+    if (dense && a.w->k % 8 != 0) return LC_OK;  // rows must stay 16-byte aligned and split into groups of eight
     if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
     if (((uintptr_t)a.w->data % 16) != 0 || (a.w2 && ((uintptr_t)a.w2->data % 16) != 0)) return LC_OK;
     *launched = true;
@@ -235,8 +417,19 @@ int32_t launch_qgemv_kq(const GemvArgs& a, cudaStream_t s, bool* launched) {
         default: return launch_kq<T, 8>(a, s);                \
     }
     if (typ == LC_TYPE_Q6_K) { KQ(LC_TYPE_Q6_K) }
-    KQ(LC_TYPE_Q5_K)
+    if (typ == LC_TYPE_Q5_K) { KQ(LC_TYPE_Q5_K) }
 #undef KQ
+#define DN(F)                                                 \
+    switch (mt) {                                             \
+        case 1: return launch_dense<F, 1>(a, s);              \
+        case 2: return launch_dense<F, 2>(a, s);              \
+        case 4: return launch_dense<F, 4>(a, s);              \
+        default: return launch_dense<F, 8>(a, s);             \
+    }
+    if (typ == LC_TYPE_F32) { DN(true) }
+    if (typ == LC_TYPE_F16) { DN(false) }
+#undef DN
+    return mt == 1 ? launch_iq4nl<1>(a, s) : launch_iq4nl<2>(a, s);
 }
 
 }  // namespace lc

@@ -89,6 +89,7 @@ QM_CASES = [
     (8, 1, 2048, 3200), (8, 5, 512, 70), (8, 1, 64, 48),
     (13, 1, 512, 40), (14, 2, 512, 40), (20, 1, 128, 40), (0, 2, 100, 24), (1, 1, 100, 24),
     (13, 1, 4096, 300), (13, 5, 2816, 64), (13, 8, 256, 19), (14, 1, 4096, 300), (14, 3, 11008, 40), (14, 8, 768, 21),
+    (20, 1, 4096, 300), (20, 2, 2816, 33), (0, 3, 512, 40), (1, 1, 4096, 300), (1, 8, 256, 19), (1, 2, 11008, 33),
 ]
 
 
