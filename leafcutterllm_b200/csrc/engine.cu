@@ -287,7 +287,7 @@ static L2Prefetch prefetch_for(lc_model* m, int l, int kernel) {
 
 int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
     if (qgemm_applies(a, T, m->gemm_ws)) {
-        // nine tokens and more: one pass over the weights on the tcgen05 tensor cores (activation split + product)
+        // five tokens and more: one pass over the weights on the tcgen05 tensor cores (activation split + product)
         a.m = T;
         int launches = 0;
         LC_TRY(launch_qgemm(a, m->gemm_ws, m->stream, &launches));

@@ -100,7 +100,8 @@ struct GemmWorkspace {
 };
 int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max);
 void qgemm_workspace_free(GemmWorkspace* ws);
-// true when launch_qgemm implements these arguments for T tokens (Q4_K weights, T at least LC_GEMM_MIN_TOKENS, default 9)
+// true when launch_qgemm implements these arguments for T tokens (Q4_K weights, T at least LC_GEMM_MIN_TOKENS, default 5: up to four tokens the
+// matrix-vector kernels are faster, from five on they would run their 8-token form, which this product beats)
 bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws);
 // a.m = number of tokens; queues two kernels (activation preparation, product), three when k is split (reduction)
 int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s, int* launches = nullptr);

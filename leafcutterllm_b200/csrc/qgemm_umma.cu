@@ -1,4 +1,4 @@
-// Q4_K weights times MANY tokens (prefill chunks, batched decode steps of nine or more sequences) on the
+// Q4_K weights times MANY tokens (prefill chunks, batched decode steps of five or more sequences) on the
 // 5th-generation tensor cores: the dense contraction of the path (Tensor::matmul with m > 1, rust/src/tensor.rs:107-135,
 // over weights that the reference dequantises per call, rust/src/model/loader.rs:213-224).
 //
@@ -588,7 +588,7 @@ void qgemm_workspace_free(GemmWorkspace* ws) {
 }
 
 static int gemm_min_tokens() {
-    static const int v = getenv("LC_GEMM_MIN_TOKENS") ? atoi(getenv("LC_GEMM_MIN_TOKENS")) : 9;
+    static const int v = getenv("LC_GEMM_MIN_TOKENS") ? atoi(getenv("LC_GEMM_MIN_TOKENS")) : 5;
     return v;
 }
 bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws) {
