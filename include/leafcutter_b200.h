@@ -195,6 +195,46 @@ int32_t lc_model_destroy(lc_model* m);
 int32_t lc_model_load_gguf(const char* path, const lc_model_config* overrides, lc_model** out);
 int32_t lc_model_get_config(const lc_model* m, lc_model_config* out);
 
+/* ---- Pre-flight checks of a GGUF file: capability report + corruption scan ----
+ * lc_scan_blocks / lc_scan_blocks_dev: the per-tensor body of scan_for_corruption (rust/src/model/loader.rs:301-422) on the
+ * GPU: blocks_total = ceil(n_elems / block size) (:325), blocks_bad = blocks whose scale -- d, and for most types the
+ * half-word at byte 2 read as dmin (:366-381) -- is NaN, infinite or above 1e4 in magnitude (:385-392).  Every type code
+ * of QuantType::from_u32 (rust/src/model/quant.rs:71-100) is accepted; F32 / F16 / BF16 and unknown codes have no blocks
+ * and report 0 / 0 as the reference skips them (:309-322). */
+int32_t lc_scan_blocks(uint32_t typ, const void* bytes, size_t n_elems, uint64_t* blocks_total, uint64_t* blocks_bad);
+int32_t lc_scan_blocks_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, uint64_t* blocks_total, uint64_t* blocks_bad);
+
+/* One row of CorruptionReport::corrupted_tensors (loader.rs:286-292, 404-413). */
+typedef struct lc_corrupt_tensor {
+    char name[112];
+    uint32_t ggml_type;
+    uint32_t reserved;
+    uint64_t blocks_total;
+    uint64_t blocks_bad;
+} lc_corrupt_tensor;
+
+/* GGUFModel::capability_report (loader.rs:54-104) and scan_for_corruption (loader.rs:301-422) of one file. */
+typedef struct lc_gguf_report {
+    char architecture[16];          /* ModelArchitecture::name (rust/src/model/arch.rs:41-51): "Llama", "Qwen2", "Qwen3.5", ... */
+    int32_t arch_supported;         /* arch.rs:71-77 */
+    int32_t total_tensors;          /* QuantSummary::total_tensors (rust/src/model/gguf.rs:319) */
+    int32_t tensors_by_type[32];    /* index = ggml type code; codes from_u32 does not know are not counted (gguf.rs:321) */
+    uint32_t unsupported_types;     /* bit c: a tensor of type code c is present and the type has no dequantiser (quant.rs:243-254) */
+    int32_t n_missing;              /* blk.N.<suffix> absent, N < min(layers, 4), the 9 suffixes of arch.rs:83-96 */
+    int32_t n_extra;                /* distinct blk.*.weight tensors whose suffix is neither mapped nor a known extra (loader.rs:74-89) */
+    int32_t can_run;                /* arch_supported && no unsupported type && nothing missing (loader.rs:91-93) */
+    int32_t n_corrupt_tensors;      /* tensors with at least one bad block */
+    uint64_t total_blocks_checked;  /* blocks of the tensors that have a bad block (loader.rs:404-406 counts only those) */
+    uint64_t total_bad_blocks;
+    lc_model_config config;         /* GGUFModel::extract_config (loader.rs:106-141) */
+} lc_gguf_report;
+
+/* scan != 0 runs the corruption scan (every block-type tensor of the file is sent through the device once).
+ * corrupt[0 .. min(n_corrupt_tensors, corrupt_cap)) is filled in file order.  names (optional) receives one line per
+ * finding, "missing <tensor>\n" then "extra <tensor>\n" (sorted), cut at names_cap - 1 characters and 0-terminated. */
+int32_t lc_gguf_inspect(const char* path, int32_t scan, lc_gguf_report* report, lc_corrupt_tensor* corrupt, int32_t corrupt_cap,
+                        char* names, size_t names_cap);
+
 /* ---- ShardEngine (rust/src/inference/shard_engine.rs:18-167): a model split into per-layer "LEAFSHDR" shards ----
  * lc_shard_engine_load     <-> ShardEngine::load_with_cache(manifest_path, num_layers) (:34-61): reads manifest.json
  *                              (rust/src/shard/loader.rs:13-50) and every shard (format.rs, loader.rs:300-367: F32, Q8_0 or

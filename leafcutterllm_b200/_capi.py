@@ -34,6 +34,18 @@ class Counters(C.Structure):
                 ("reserved", C.c_uint64 * 7)]
 
 
+class CorruptTensor(C.Structure):
+    _fields_ = [("name", C.c_char * 112), ("ggml_type", C.c_uint32), ("reserved", C.c_uint32), ("blocks_total", C.c_uint64),
+                ("blocks_bad", C.c_uint64)]
+
+
+class GgufReport(C.Structure):
+    _fields_ = [("architecture", C.c_char * 16), ("arch_supported", C.c_int32), ("total_tensors", C.c_int32),
+                ("tensors_by_type", C.c_int32 * 32), ("unsupported_types", C.c_uint32), ("n_missing", C.c_int32),
+                ("n_extra", C.c_int32), ("can_run", C.c_int32), ("n_corrupt_tensors", C.c_int32),
+                ("total_blocks_checked", C.c_uint64), ("total_bad_blocks", C.c_uint64), ("config", ModelConfig)]
+
+
 TOKEN_CB = C.CFUNCTYPE(None, C.c_int64, C.c_void_p)
 
 _f = C.POINTER(C.c_float)
@@ -88,6 +100,9 @@ SIGNATURES = {
     "lc_model_destroy": (_i32, [_vp]),
     "lc_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(ModelConfig), C.POINTER(_vp)]),
     "lc_model_get_config": (_i32, [_vp, C.POINTER(ModelConfig)]),
+    "lc_scan_blocks": (_i32, [_u32, _vp, _sz, C.POINTER(_u64), C.POINTER(_u64)]),
+    "lc_scan_blocks_dev": (_i32, [_u32, _vp, _sz, C.POINTER(_u64), C.POINTER(_u64)]),
+    "lc_gguf_inspect": (_i32, [C.c_char_p, _i32, C.POINTER(GgufReport), C.POINTER(CorruptTensor), _i32, C.c_char_p, _sz]),
     "lc_shard_engine_load": (_i32, [C.c_char_p, _i32, _i32, C.POINTER(_vp)]),
     "lc_shard_engine_forward": (_i32, [_vp, _vp, _i32, _vp, _vp]),
     "lc_shard_engine_generate": (_i32, [_vp, _vp, _i32, _i32, C.c_float, C.c_float, _vp, C.POINTER(_i32)]),

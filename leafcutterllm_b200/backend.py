@@ -108,6 +108,15 @@ def dequantize(typ: int, data, n_elems: int) -> np.ndarray:
     return out
 
 
+def scan_blocks(typ: int, data, n_elems: int):
+    """The per-tensor body of `scan_for_corruption` (rust/src/model/loader.rs:318-402) on the GPU: returns
+    (blocks_total, blocks_bad).  Accepts every type code of the reference's type table; types without blocks give (0, 0)."""
+    data = np.ascontiguousarray(np.frombuffer(data, dtype=np.uint8) if not isinstance(data, np.ndarray) else data.view(np.uint8))
+    total, bad = C.c_uint64(), C.c_uint64()
+    check(load().lc_scan_blocks(typ, _p(data), n_elems, C.byref(total), C.byref(bad)))
+    return int(total.value), int(bad.value)
+
+
 def qmatmul(typ: int, a, w_blocks, m: int, k: int, n: int) -> np.ndarray:
     """a[m,k] . dequant(W)^T with W = raw GGUF blocks of an [n, k] weight (blocks along k)."""
     a = _f32(a).ravel()

@@ -6,6 +6,8 @@
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <unistd.h>
+#include <algorithm>
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <string>
@@ -110,12 +112,16 @@ struct Mapping {
     }
 };
 
-}  // namespace
-
-extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* overrides, lc_model** out) {
-    LC_CHECK(path && out, LC_ERR_INVALID, "lc_model_load_gguf: null argument");
-    *out = nullptr;
+struct Parsed {
     Mapping mp;
+    std::map<std::string, Value> md;
+    std::vector<TensorInfo> infos;
+    uint64_t data_offset = 0;
+};
+
+// GGUFile::open (gguf.rs:76-119): header, metadata, tensor table, start of the aligned data section.
+int32_t parse_gguf(const char* path, Parsed* out) {
+    Mapping& mp = out->mp;
     mp.fd = open(path, O_RDONLY);
     LC_CHECK(mp.fd >= 0, LC_ERR_INVALID, "cannot open %s", path);
     struct stat st;
@@ -131,13 +137,14 @@ extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* o
     LC_CHECK(version == kVersion, LC_ERR_UNSUPPORTED, "%s: unsupported GGUF version %u", path, version);  // gguf.rs:87-89
     LC_CHECK(n_tensors < (1u << 24) && n_meta < (1u << 24), LC_ERR_INVALID, "%s: implausible header counts", path);
 
-    std::map<std::string, Value> md;
+    std::map<std::string, Value>& md = out->md;
     for (uint64_t i = 0; i < n_meta && r.ok; i++) {
         std::string key = r.str();
         uint32_t typ = r.get<uint32_t>();
         md[key] = r.value(typ);
     }
-    std::vector<TensorInfo> infos((size_t)n_tensors);
+    std::vector<TensorInfo>& infos = out->infos;
+    infos.resize((size_t)n_tensors);
     for (uint64_t i = 0; i < n_tensors && r.ok; i++) {
         TensorInfo& t = infos[(size_t)i];
         t.name = r.str();
@@ -152,8 +159,12 @@ extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* o
     int64_t alignment = 32;  // gguf.rs:104-113
     (void)meta_int(md, "general.alignment", &alignment);
     LC_CHECK(alignment > 0, LC_ERR_INVALID, "%s: general.alignment is %lld", path, (long long)alignment);
-    const uint64_t data_offset = (r.pos + (uint64_t)alignment - 1) / (uint64_t)alignment * (uint64_t)alignment;
+    out->data_offset = (r.pos + (uint64_t)alignment - 1) / (uint64_t)alignment * (uint64_t)alignment;
+    return LC_OK;
+}
 
+// GGUFModel::extract_config (loader.rs:106-141) over the architecture's key prefix (arch.rs:54-64).
+void config_from_metadata(const std::map<std::string, Value>& md, lc_model_config* out) {
     // architecture -> key prefix (arch.rs:24-64): mistral and unknown files use the llama.* keys
     std::string arch = "llama";
     {
@@ -190,6 +201,23 @@ extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* o
         if (it != md.end() && it->second.kind == Value::ARRAY) cfg.vocab_size = (int32_t)it->second.i;
     }
     if (pick("rope.freq_base", &v)) cfg.rope_theta = (float)v;  // loader.rs:130-131 (read through the integer accessor)
+    *out = cfg;
+}
+
+}  // namespace
+
+extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* overrides, lc_model** out) {
+    LC_CHECK(path && out, LC_ERR_INVALID, "lc_model_load_gguf: null argument");
+    *out = nullptr;
+    Parsed parsed;
+    LC_TRY(parse_gguf(path, &parsed));
+    Mapping& mp = parsed.mp;
+    std::map<std::string, Value>& md = parsed.md;
+    std::vector<TensorInfo>& infos = parsed.infos;
+    const uint64_t data_offset = parsed.data_offset;
+
+    lc_model_config cfg;
+    config_from_metadata(md, &cfg);
     if (overrides) {
         // switches the file does not carry; a positive max_seq_len caps the KV capacity the model is built with
         if (overrides->max_seq_len > 0) cfg.max_seq_len = overrides->max_seq_len;
@@ -227,5 +255,121 @@ extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* o
     int32_t s = lc_model_finalize(m);
     if (s != LC_OK) return fail(s);
     *out = m;
+    return LC_OK;
+}
+
+// GGUFModel::capability_report (loader.rs:54-104) + scan_for_corruption (loader.rs:301-422).
+extern "C" int32_t lc_gguf_inspect(const char* path, int32_t scan, lc_gguf_report* report, lc_corrupt_tensor* corrupt,
+                                   int32_t corrupt_cap, char* names, size_t names_cap) {
+    LC_CHECK(path && report, LC_ERR_INVALID, "lc_gguf_inspect: null argument");
+    LC_CHECK(corrupt_cap == 0 || corrupt != nullptr, LC_ERR_INVALID, "lc_gguf_inspect: corrupt_cap without a buffer");
+    memset(report, 0, sizeof(*report));
+    if (names && names_cap) names[0] = 0;
+    Parsed parsed;
+    LC_TRY(parse_gguf(path, &parsed));
+    config_from_metadata(parsed.md, &report->config);
+
+    // ModelArchitecture::detect / name / is_supported (arch.rs:24-77)
+    std::string arch_key;
+    {
+        auto it = parsed.md.find("general.architecture");
+        if (it != parsed.md.end() && it->second.kind == Value::STRING) arch_key = it->second.s;
+    }
+    static const struct { const char* key; const char* name; bool supported; } kArch[] = {
+        {"llama", "Llama", true}, {"qwen2", "Qwen2", true}, {"qwen35", "Qwen3.5", false},
+        {"mistral", "Mistral", true}, {"phi", "Phi", false}, {"gemma", "Gemma", false}};
+    const char* arch_name = "Unknown";
+    bool arch_ok = false;
+    for (const auto& a : kArch)
+        if (arch_key == a.key) { arch_name = a.name; arch_ok = a.supported; }
+    snprintf(report->architecture, sizeof(report->architecture), "%s", arch_name);
+    report->arch_supported = arch_ok ? 1 : 0;
+
+    // GGUFile::quant_summary (gguf.rs:317-331)
+    report->total_tensors = (int32_t)parsed.infos.size();
+    for (const TensorInfo& t : parsed.infos) {
+        uint32_t e, bb;
+        int kind;
+        const bool known = t.typ == 0 || t.typ == 1 || t.typ == 30 || scan_geom(t.typ, &e, &bb, &kind);
+        if (!known) continue;
+        report->tensors_by_type[t.typ]++;
+        QuantGeom g;
+        if (!quant_geom(t.typ, &g)) report->unsupported_types |= 1u << t.typ;  // quant.rs:243-254: the same eight types
+    }
+
+    // missing tensors of the first layers, unrecognised blk.* tensors (loader.rs:59-89)
+    static const char* kMapped[9] = {"attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight", "ffn_gate.weight",
+                                     "ffn_up.weight", "ffn_down.weight", "attn_norm.weight", "ffn_norm.weight"};
+    std::vector<std::string> extra_known;  // arch.rs:99-117
+    if (arch_key == "qwen35")
+        extra_known = {"attn_gate.weight", "attn_qkv.weight", "post_attention_norm.weight", "attn_q_norm.weight",
+                       "attn_k_norm.weight", "attn_q.weight", "attn_v.weight"};
+    else if (arch_key == "llama")
+        extra_known = {"attn_norm.bias", "ffn_norm.bias"};
+    std::map<std::string, const TensorInfo*> by_name;
+    for (const TensorInfo& t : parsed.infos) by_name.emplace(t.name, &t);
+    std::vector<std::string> missing, extra;
+    const int sample_layers = report->config.num_layers < 4 ? report->config.num_layers : 4;
+    for (int l = 0; l < sample_layers; l++)
+        for (const char* sfx : kMapped) {
+            std::string n = "blk." + std::to_string(l) + "." + sfx;
+            if (!by_name.count(n)) missing.push_back(n);
+        }
+    auto ends_with = [](const std::string& s, const char* tail) {
+        size_t n = strlen(tail);
+        return s.size() >= n && s.compare(s.size() - n, n, tail) == 0;
+    };
+    for (const TensorInfo& t : parsed.infos) {
+        if (t.name.rfind("blk.", 0) != 0 || !ends_with(t.name, ".weight")) continue;
+        // splitn(3, '.').nth(2): what follows the second dot, or "" when there is none
+        std::string sfx;
+        size_t d1 = t.name.find('.');
+        size_t d2 = d1 == std::string::npos ? d1 : t.name.find('.', d1 + 1);
+        if (d2 != std::string::npos) sfx = t.name.substr(d2 + 1);
+        bool known = false;
+        for (const char* m : kMapped) known = known || sfx == m;
+        for (const std::string& m : extra_known) known = known || sfx == m;
+        if (!known) extra.push_back(t.name);
+    }
+    std::sort(extra.begin(), extra.end());
+    extra.erase(std::unique(extra.begin(), extra.end()), extra.end());
+    report->n_missing = (int32_t)missing.size();
+    report->n_extra = (int32_t)extra.size();
+    report->can_run = (arch_ok && report->unsupported_types == 0 && missing.empty()) ? 1 : 0;
+    if (names && names_cap) {
+        std::string text;
+        for (const std::string& n : missing) text += "missing " + n + "\n";
+        for (const std::string& n : extra) text += "extra " + n + "\n";
+        snprintf(names, names_cap, "%s", text.c_str());
+    }
+    if (!scan) return LC_OK;
+
+    // scan_for_corruption: every tensor of a block type, in file order
+    if (!have_device()) return LC_ERR_CUDA;
+    for (const TensorInfo& t : parsed.infos) {
+        uint32_t e, bb;
+        int kind;
+        if (!scan_geom(t.typ, &e, &bb, &kind)) continue;
+        size_t count = 1;  // an empty dimension list multiplies out to 1 (loader.rs:324)
+        for (uint64_t d : t.dims) count *= (size_t)d;
+        const size_t nbytes = (count + e - 1) / e * bb;
+        const uint64_t start = parsed.data_offset + t.offset;
+        LC_CHECK(start <= parsed.mp.size && nbytes <= parsed.mp.size - (size_t)start, LC_ERR_INVALID,
+                 "%s: tensor %s reaches past the end of the file", path, t.name.c_str());
+        uint64_t total = 0, bad = 0;
+        LC_TRY(lc_scan_blocks(t.typ, (const uint8_t*)parsed.mp.base + start, count, &total, &bad));
+        if (bad == 0) continue;
+        if (report->n_corrupt_tensors < corrupt_cap) {
+            lc_corrupt_tensor& c = corrupt[report->n_corrupt_tensors];
+            memset(&c, 0, sizeof(c));
+            snprintf(c.name, sizeof(c.name), "%s", t.name.c_str());
+            c.ggml_type = t.typ;
+            c.blocks_total = total;
+            c.blocks_bad = bad;
+        }
+        report->n_corrupt_tensors++;
+        report->total_blocks_checked += total;
+        report->total_bad_blocks += bad;
+    }
     return LC_OK;
 }

@@ -7,6 +7,10 @@ namespace lc {
 
 // ---- dequant.cu ----
 int32_t launch_dequant(uint32_t typ, const void* w, size_t n_elems, float* out, cudaStream_t s);
+// Block-scale scan (scan.cu): geometry of every block type the reference's type table knows and how its scales are
+// read; the launch adds the number of bad blocks to one 64-bit word on the device.
+bool scan_geom(uint32_t typ, uint32_t* block_elems, uint32_t* block_bytes, int* kind);
+int32_t launch_scan_scales(uint32_t typ, const void* raw_dev, size_t n_blocks, unsigned long long* counter_dev, cudaStream_t s);
 // Adds to *count the number of elements that dequantise to NaN / Inf / |v| > 100
 // (the condition of rust/src/model/loader.rs:241-249).
 int32_t launch_sanity_scan(uint32_t typ, const void* w, size_t n_elems, unsigned long long* count, cudaStream_t s);

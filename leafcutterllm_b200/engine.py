@@ -161,6 +161,40 @@ class Engine:
             pass
 
 
+def inspect_gguf(path: str, scan: bool = True, max_corrupt: int = 256) -> dict:
+    """`GGUFModel::capability_report` (rust/src/model/loader.rs:54-104) and, with `scan`, `scan_for_corruption`
+    (loader.rs:301-422, the block scales checked on the GPU) of one GGUF file, as a dict with the reference's field names."""
+    rep = _capi.GgufReport()
+    rows = (_capi.CorruptTensor * max(1, max_corrupt))()
+    names = C.create_string_buffer(1 << 16)
+    check(load().lc_gguf_inspect(str(path).encode(), 1 if scan else 0, C.byref(rep), rows, max_corrupt, names, len(names)))
+    lines = names.value.decode().splitlines()
+    by_type = {code: int(n) for code, n in enumerate(rep.tensors_by_type) if n}
+    cfg = rep.config
+    out = {
+        "architecture": rep.architecture.decode(),
+        "arch_supported": bool(rep.arch_supported),
+        "quant_summary": {"total_tensors": int(rep.total_tensors), "types": by_type,
+                          "unsupported": [c for c in range(32) if rep.unsupported_types >> c & 1]},
+        "missing_tensors": [ln[len("missing "):] for ln in lines if ln.startswith("missing ")],
+        "extra_tensors": [ln[len("extra "):] for ln in lines if ln.startswith("extra ")],
+        "n_missing": int(rep.n_missing), "n_extra": int(rep.n_extra),
+        "can_run": bool(rep.can_run),
+        "config": {"hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_heads,
+                   "num_key_value_heads": cfg.num_kv_heads, "intermediate_size": cfg.intermediate_size,
+                   "max_position_embeddings": cfg.max_seq_len, "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta},
+    }
+    if scan:
+        n = min(int(rep.n_corrupt_tensors), max_corrupt)
+        out["corruption"] = {
+            "corrupted_tensors": [{"name": rows[i].name.decode(), "quant_type": int(rows[i].ggml_type),
+                                   "blocks_total": int(rows[i].blocks_total), "blocks_bad": int(rows[i].blocks_bad),
+                                   "bad_percentage": 100.0 * rows[i].blocks_bad / max(1, rows[i].blocks_total)} for i in range(n)],
+            "n_corrupt_tensors": int(rep.n_corrupt_tensors),
+            "total_blocks_checked": int(rep.total_blocks_checked), "total_bad_blocks": int(rep.total_bad_blocks)}
+    return out
+
+
 class ShardEngine:
     """Host-side mirror of the reference's `ShardEngine` (rust/src/inference/shard_engine.rs:18-97): a model split into a
     manifest.json and per-layer LEAFSHDR shard files.  The reference maps one layer at a time from disk; here every shard

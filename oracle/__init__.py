@@ -57,6 +57,7 @@ def lib() -> C.CDLL:
             "orc_kv_clear": (None, [vp]), "orc_kv_memory_bytes": (sz, [vp]),
             "orc_forward": (C.c_int, [vp, vp, sz, vp]), "orc_forward_hidden": (C.c_int, [vp, vp, sz, vp, vp]),
             "orc_generate": (C.c_int, [vp, vp, sz, sz, C.c_int, vp, C.POINTER(sz), vp]),
+            "orc_scan_blocks": (C.c_int, [C.c_uint32, vp, sz, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
             "orc_last_error": (C.c_char_p, [vp]), "orc_sanitized_count": (sz, [vp]),
             "orc_timers": (None, [vp, vp, C.c_int]),
             "orc_attention": (C.c_int, [vp, C.c_int, vp, sz, vp]), "orc_ffn": (C.c_int, [vp, C.c_int, vp, sz, vp]),
@@ -82,6 +83,14 @@ def dequantize(typ: int, data, n: int) -> np.ndarray:
     if lib().orc_dequantize(typ, _p(d), n, _p(out)) != 0:
         raise ValueError(f"unsupported type {typ}")
     return out
+
+
+def scan_blocks(typ: int, data, n: int):
+    """(blocks_total, blocks_bad) of one tensor as scan_for_corruption counts them (rust/src/model/loader.rs:318-402)."""
+    d = np.ascontiguousarray(data).view(np.uint8).ravel()
+    total, bad = C.c_uint64(), C.c_uint64()
+    lib().orc_scan_blocks(typ, _p(d), n, C.byref(total), C.byref(bad))
+    return int(total.value), int(bad.value)
 
 
 def matmul(a, b, m, k, n):

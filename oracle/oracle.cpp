@@ -725,6 +725,54 @@ int orc_dequantize(uint32_t typ, const uint8_t* data, size_t n_elems, float* out
     return dequantize_any(typ, data, out, n_elems);
 }
 size_t orc_sanitize(float* v, size_t n) { return sanitize_weights(v, n); }
+
+// scan_for_corruption, the body run per tensor (rust/src/model/loader.rs:318-402).  Block sizes and bytes for every type
+// code of QuantType::from_u32 (rust/src/model/quant.rs:71-100, 160-238).  Returns 0 and leaves the counts at zero for
+// types the scan skips (F32, F16, BF16, unknown codes: loader.rs:309-322).
+int orc_scan_blocks(uint32_t typ, const uint8_t* raw, size_t n_elems, uint64_t* blocks_total, uint64_t* blocks_bad) {
+    *blocks_total = 0;
+    *blocks_bad = 0;
+    size_t bs = 0, bb = 0;
+    switch (typ) {
+        case 2: bs = 32; bb = 18; break;    case 3: bs = 32; bb = 20; break;    case 6: bs = 32; bb = 22; break;
+        case 7: bs = 32; bb = 24; break;    case 8: bs = 32; bb = 34; break;    case 9: bs = 32; bb = 36; break;
+        case 10: bs = 256; bb = 84; break;  case 11: bs = 256; bb = 110; break; case 12: bs = 256; bb = 144; break;
+        case 13: bs = 256; bb = 176; break; case 14: bs = 256; bb = 210; break; case 15: bs = 256; bb = 292; break;
+        case 16: bs = 256; bb = 66; break;  case 17: bs = 256; bb = 74; break;  case 18: bs = 256; bb = 98; break;
+        case 19: bs = 256; bb = 110; break; case 20: bs = 32; bb = 18; break;   case 21: bs = 256; bb = 136; break;
+        case 22: bs = 256; bb = 136; break; case 23: bs = 256; bb = 162; break; case 24: bs = 256; bb = 162; break;
+        case 25: bs = 256; bb = 176; break;
+        default: return 0;
+    }
+    const size_t num_blocks = (n_elems + bs - 1) / bs;  // loader.rs:325
+    auto h = [](const uint8_t* p) { return f16_to_f32((uint16_t)(p[0] | (p[1] << 8))); };
+    auto f = [](const uint8_t* p) { float v; memcpy(&v, p, 4); return v; };
+    auto is_bad = [](float v) { return std::isnan(v) || std::isinf(v) || std::fabs(v) > 1e4f; };  // loader.rs:385-392
+    uint64_t bad = 0;
+    for (size_t i = 0; i < num_blocks; i++) {
+        const uint8_t* block = raw + i * bb;
+        float d, dmin = 0.0f;
+        bool has_dmin = false;
+        if (typ == 14) {          // Q6_K: the f16 at bytes 208..209 (loader.rs:341-349)
+            d = h(block + 208);
+        } else if (typ == 15) {   // Q8_K: f32 at 0 (loader.rs:350-357)
+            d = f(block);
+        } else if (typ == 9) {    // Q8_1: f32 at 0 and f32 at 4 (loader.rs:358-367)
+            d = f(block);
+            dmin = f(block + 4);
+            has_dmin = true;
+        } else {                  // every other type: f16 at 0, and f16 at 2 as dmin when the block has 4 bytes (loader.rs:368-381)
+            d = h(block);
+            if (bb >= 4) { dmin = h(block + 2); has_dmin = true; }
+        }
+        bool block_bad = is_bad(d);
+        if (has_dmin && is_bad(dmin)) block_bad = true;
+        if (block_bad) bad++;
+    }
+    *blocks_total = num_blocks;
+    *blocks_bad = bad;
+    return 0;
+}
 size_t orc_tensor_bytes(uint32_t typ, size_t count) {
     size_t be, bb;
     if (!quant_geometry(typ, &be, &bb)) return count;  // gguf.rs:307-313
