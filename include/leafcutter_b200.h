@@ -271,11 +271,24 @@ int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_
 int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* tokens,
                          const int32_t* n_tokens, float* logits_out, int64_t* next_out);
 
+/* sampler::sample_top_p (rust/src/inference/sampler.rs:6-50) on the GPU with the uniform draw u in [0, 1) supplied by the
+ * caller (the reference's `rng.gen::<f32>()`, :39): logits / temperature, softmax, stable descending sort, the shortest
+ * prefix whose running f32 sum exceeds top_p, pick = first position with u * kept_sum <= running sum.  All f32 sums run in
+ * the reference's order; temperature <= 0 is its greedy branch (ties: the last maximum).  n >= 1 (the reference panics on
+ * an empty slice). */
+int32_t lc_sample_top_p(const float* logits, size_t n, float temperature, float top_p, float u, int64_t* token);
+/* Seeded stochastic generation: after this call lc_generate accepts temperature > 0; the draw counter restarts at 0.
+ * lc_seeded_uniform(seed, i) is draw i: 24 random bits scaled to [0, 1) (the grid of rand's f32 sampling, not its stream). */
+int32_t lc_model_set_seed(lc_model* m, uint64_t seed);
+float lc_seeded_uniform(uint64_t seed, uint64_t index);
+
 typedef void (*lc_token_cb)(int64_t token, void* user);
 /* Engine::generate (engine.rs:51-76) / Go inference.Model.Generate (pkg/inference/speculative.go:18-20):
  * clears the cache of slot 0, prefills, emits the first token from the prefill logits, then up to
- * max_tokens-1 decode steps.  temperature <= 0 selects greedy (sampler.rs:7-10); the stochastic
- * branch draws from an unseeded RNG in the reference and returns LC_ERR_UNSUPPORTED here.
+ * max_tokens-1 decode steps.  temperature <= 0 selects greedy (sampler.rs:7-10).  The stochastic
+ * branch (sampler.rs:12-50) draws from an unseeded RNG in the reference: here it returns LC_ERR_UNSUPPORTED
+ * until lc_model_set_seed has been called, and then uses the draws lc_seeded_uniform(seed, 0), (seed, 1), ...
+ * one per emitted token, through the same arithmetic as lc_sample_top_p.
  * stop_on_eos != 0 keeps the reference's stop on token id 2 (engine.rs:60-63,70-72). */
 int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature,
                     float top_p, int32_t stop_on_eos, int64_t* out_tokens, int32_t* n_out, lc_token_cb cb,

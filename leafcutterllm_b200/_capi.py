@@ -100,6 +100,9 @@ SIGNATURES = {
     "lc_model_destroy": (_i32, [_vp]),
     "lc_model_load_gguf": (_i32, [C.c_char_p, C.POINTER(ModelConfig), C.POINTER(_vp)]),
     "lc_model_get_config": (_i32, [_vp, C.POINTER(ModelConfig)]),
+    "lc_sample_top_p": (_i32, [_vp, _sz, C.c_float, C.c_float, C.c_float, C.POINTER(C.c_int64)]),
+    "lc_model_set_seed": (_i32, [_vp, _u64]),
+    "lc_seeded_uniform": (C.c_float, [_u64, _u64]),
     "lc_scan_blocks": (_i32, [_u32, _vp, _sz, C.POINTER(_u64), C.POINTER(_u64)]),
     "lc_scan_blocks_dev": (_i32, [_u32, _vp, _sz, C.POINTER(_u64), C.POINTER(_u64)]),
     "lc_gguf_inspect": (_i32, [C.c_char_p, _i32, C.POINTER(GgufReport), C.POINTER(CorruptTensor), _i32, C.c_char_p, _sz]),

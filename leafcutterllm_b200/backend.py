@@ -177,11 +177,17 @@ def apply_rotary_emb(x, seq_len: int, num_heads: int, head_dim: int, theta: floa
     return x
 
 
-def sample_top_p(logits, temperature: float, top_p: float) -> int:
-    """sampler::sample_top_p (rust/src/inference/sampler.rs:6-10): greedy branch only."""
-    if temperature > 0.0:
-        raise NotImplementedError("the reference's stochastic branch draws from an unseeded RNG; only greedy is reproduced")
+def sample_top_p(logits, temperature: float, top_p: float, u: float = None) -> int:
+    """sampler::sample_top_p (rust/src/inference/sampler.rs:6-50).  Greedy for temperature <= 0; the stochastic branch
+    needs the uniform draw `u` in [0, 1) that the reference takes from its unseeded generator (:38-39)."""
     v = _f32(logits).ravel()
-    out = np.zeros(1, np.int64)
-    check(load().lc_argmax(_p(v), v.size, _p(out)))
-    return int(out[0])
+    if temperature > 0.0 and u is None:
+        raise ValueError("sample_top_p: the stochastic branch needs the uniform draw u (the reference's rng.gen::<f32>())")
+    out = C.c_int64()
+    check(load().lc_sample_top_p(_p(v), v.size, float(temperature), float(top_p), float(u or 0.0), C.byref(out)))
+    return int(out.value)
+
+
+def seeded_uniform(seed: int, index: int) -> float:
+    """Draw `index` of a seeded generation (see Engine.generate(seed=...))."""
+    return float(load().lc_seeded_uniform(seed, index))

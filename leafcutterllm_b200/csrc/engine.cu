@@ -80,6 +80,8 @@ struct lc_model {
     int32_t *d_tok_seq = nullptr, *d_tok_pos = nullptr, *d_tok_rope = nullptr, *d_last_idx = nullptr;
     float *d_hidden = nullptr, *d_hidden2 = nullptr, *d_qkv = nullptr, *d_attn = nullptr, *d_ffn = nullptr;
     float *d_last = nullptr, *d_logits = nullptr;
+    bool seeded = false;          // lc_model_set_seed: stochastic sampling allowed, draws from seeded_uniform(seed, draws++)
+    uint64_t seed = 0, draws = 0;
     int64_t* d_next = nullptr;
     int64_t* d_out_tokens = nullptr;
     size_t out_tokens_cap = 0;
@@ -1167,23 +1169,38 @@ int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, cons
     return check_device_flag(m);
 }
 
+int32_t lc_model_set_seed(lc_model* m, uint64_t seed) {
+    LC_TRY(check_model(m, false));
+    m->seeded = true;
+    m->seed = seed;
+    m->draws = 0;
+    return LC_OK;
+}
+
 int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature, float top_p,
                     int32_t stop_on_eos, int64_t* out_tokens, int32_t* n_out, lc_token_cb cb, void* user) {
-    (void)top_p;
     LC_TRY(check_model(m, true));
     LC_CHECK(tokens && n >= 1 && max_tokens >= 1 && out_tokens && n_out, LC_ERR_INVALID, "lc_generate: bad argument");
-    LC_CHECK(temperature <= 0.0f, LC_ERR_UNSUPPORTED,
-             "stochastic sampling draws from an unseeded generator in the reference (rust/src/inference/sampler.rs:41) and is not "
-             "reproduced; pass temperature <= 0 for greedy");
+    const bool stochastic = temperature > 0.0f;
+    LC_CHECK(!stochastic || m->seeded, LC_ERR_UNSUPPORTED,
+             "stochastic sampling draws from an unseeded generator in the reference (rust/src/inference/sampler.rs:38-39); call "
+             "lc_model_set_seed first for a seeded draw sequence, or pass temperature <= 0 for greedy");
     LC_TRY(lc_kv_clear(m, 0));  // engine.rs:52
     int32_t seq = 0;
     int64_t next = 0;
+    // sample_top_p on the logits of the last forward (engine.rs:57, 69): they are still in device memory
+    auto pick = [&](int64_t* tok) -> int32_t {
+        if (!stochastic) return LC_OK;  // the greedy pick came back with the forward
+        DeviceGuard dg(m->device);
+        return sample_top_p_sync(m->d_logits, (size_t)m->V, temperature, top_p, seeded_uniform(m->seed, m->draws++), tok, m->stream);
+    };
     LC_TRY(lc_forward_batch(m, 1, &seq, tokens, &n, nullptr, &next));  // engine.rs:55-57
+    LC_TRY(pick(&next));
     int count = 0;
     out_tokens[count++] = next;
     if (cb) cb(next, user);
     if (!(stop_on_eos && next == 2)) {
-        if (!cb && !stop_on_eos && max_tokens > 1) {
+        if (!cb && !stop_on_eos && !stochastic && max_tokens > 1) {
             // nothing observes the tokens one by one: keep the loop on the device
             LC_TRY(lc_decode_loop(m, 1, &seq, &next, max_tokens - 1, out_tokens + 1, nullptr));
             count = max_tokens;
@@ -1192,6 +1209,7 @@ int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_t
                 int32_t one = 1;
                 int64_t cur = next;
                 LC_TRY(lc_forward_batch(m, 1, &seq, &cur, &one, nullptr, &next));
+                LC_TRY(pick(&next));
                 out_tokens[count++] = next;
                 if (cb) cb(next, user);
                 if (stop_on_eos && next == 2) break;

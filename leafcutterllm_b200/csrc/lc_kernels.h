@@ -7,6 +7,11 @@ namespace lc {
 
 // ---- dequant.cu ----
 int32_t launch_dequant(uint32_t typ, const void* w, size_t n_elems, float* out, cudaStream_t s);
+// sampler::sample_top_p with the caller's uniform draw (sampler.cu); the _sync form reads the token back and takes the
+// greedy branch for temperature <= 0.  seeded_uniform: draw `index` of a seeded generation, in [0, 1) on the 2^-24 grid.
+int32_t launch_sample_top_p(const float* logits_dev, size_t n, float temperature, float top_p, float u, int64_t* token_dev, cudaStream_t s);
+int32_t sample_top_p_sync(const float* logits_dev, size_t n, float temperature, float top_p, float u, int64_t* token_host, cudaStream_t s);
+float seeded_uniform(uint64_t seed, uint64_t index);
 // Block-scale scan (scan.cu): geometry of every block type the reference's type table knows and how its scales are
 // read; the launch adds the number of bad blocks to one 64-bit word on the device.
 bool scan_geom(uint32_t typ, uint32_t* block_elems, uint32_t* block_bytes, int* kind);

@@ -109,7 +109,11 @@ class Engine:
         return logits, nxt
 
     def generate(self, tokens: Iterable[int], max_tokens: int, temperature: float = 0.0, top_p: float = 1.0,
-                 stop_on_eos: bool = True, on_token: Optional[Callable[[int], None]] = None) -> list:
+                 stop_on_eos: bool = True, on_token: Optional[Callable[[int], None]] = None, seed: Optional[int] = None) -> list:
+        """`Engine::generate` (rust/src/inference/engine.rs:51-76).  temperature > 0 needs `seed`: the reference draws from an
+        unseeded generator, here token i uses `seeded_uniform(seed, i)` in `sample_top_p`'s arithmetic."""
+        if seed is not None:
+            check(load().lc_model_set_seed(self._h, int(seed)))
         t = np.ascontiguousarray(list(tokens), dtype=np.int64)
         out = np.empty(max_tokens, np.int64)
         n_out = C.c_int32()

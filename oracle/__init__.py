@@ -57,6 +57,7 @@ def lib() -> C.CDLL:
             "orc_kv_clear": (None, [vp]), "orc_kv_memory_bytes": (sz, [vp]),
             "orc_forward": (C.c_int, [vp, vp, sz, vp]), "orc_forward_hidden": (C.c_int, [vp, vp, sz, vp, vp]),
             "orc_generate": (C.c_int, [vp, vp, sz, sz, C.c_int, vp, C.POINTER(sz), vp]),
+            "orc_sample_top_p": (sz, [vp, sz, C.c_float, C.c_float, C.c_float]),
             "orc_scan_blocks": (C.c_int, [C.c_uint32, vp, sz, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
             "orc_last_error": (C.c_char_p, [vp]), "orc_sanitized_count": (sz, [vp]),
             "orc_timers": (None, [vp, vp, C.c_int]),
@@ -83,6 +84,12 @@ def dequantize(typ: int, data, n: int) -> np.ndarray:
     if lib().orc_dequantize(typ, _p(d), n, _p(out)) != 0:
         raise ValueError(f"unsupported type {typ}")
     return out
+
+
+def sample_top_p(logits, temperature: float, top_p: float, u: float = 0.0) -> int:
+    """sampler::sample_top_p (rust/src/inference/sampler.rs:6-50) with the uniform draw `u` passed in."""
+    v = _f32(logits).ravel()
+    return int(lib().orc_sample_top_p(_p(v), v.size, temperature, top_p, u))
 
 
 def scan_blocks(typ: int, data, n: int):

@@ -23,6 +23,7 @@
 //     0..3, then the scalar tail (simd.rs:373-410).
 //   * everything else is scalar f32 in source order with glibc libm.
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -794,6 +795,36 @@ void orc_softmax(const float* x, size_t hidden, size_t rows, float* o) { softmax
 float orc_sum_sq(const float* x, size_t n) { return sum_sq(x, n); }
 void orc_rope(float* x, size_t seq, size_t heads, size_t hd, float theta, size_t pos0) { apply_rotary_emb(x, seq, heads, hd, theta, pos0); }
 size_t orc_argmax(const float* v, size_t n) { return argmax_last(v, n); }
+
+// sampler::sample_top_p (rust/src/inference/sampler.rs:6-50) with the uniform draw passed in (the reference takes it from
+// thread_rng, :38-39).  NaN probabilities (which its comparator calls equal to everything) are not expected.
+size_t orc_sample_top_p(const float* logits, size_t n, float temperature, float top_p, float u) {
+    if (temperature <= 0.0f) return argmax_last(logits, n);                                   // :7-10
+    std::vector<std::pair<size_t, float>> probs(n);
+    for (size_t i = 0; i < n; i++) probs[i] = {i, logits[i] / temperature};                   // :13
+    float max_logit = -INFINITY;
+    for (size_t i = 0; i < n; i++) max_logit = fmaxf(max_logit, probs[i].second);             // :16
+    float exp_sum = 0.0f;
+    for (size_t i = 0; i < n; i++) exp_sum += expf(probs[i].second - max_logit);              // :17
+    for (size_t i = 0; i < n; i++) probs[i].second = expf(probs[i].second - max_logit) / exp_sum;  // :18-20
+    std::stable_sort(probs.begin(), probs.end(),
+                     [](const std::pair<size_t, float>& a, const std::pair<size_t, float>& b) { return a.second > b.second; });  // :23-25
+    float cumsum = 0.0f;
+    size_t cutoff = n - 1;
+    for (size_t i = 0; i < n; i++) {                                                          // :28-32
+        cumsum += probs[i].second;
+        if (cumsum > top_p) { cutoff = i; break; }
+    }
+    float sum = 0.0f;
+    for (size_t i = 0; i <= cutoff; i++) sum += probs[i].second;                              // :37
+    const float rand_val = u * sum;                                                           // :39
+    float cum = 0.0f;
+    for (size_t i = 0; i <= cutoff; i++) {                                                    // :41-47
+        cum += probs[i].second;
+        if (rand_val <= cum) return probs[i].first;
+    }
+    return probs[cutoff].first;                                                               // :49
+}
 
 // Quantised matmul, y[m,n] = a[m,k] . deq(W)^T with W raw GGUF blocks [n rows][k/blk]:
 // loader.rs:205-235 dequant + tensor.rs:107-135 matmul.
