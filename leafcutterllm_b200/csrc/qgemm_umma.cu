@@ -662,12 +662,15 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
             const long cost = waves * (((nquads + c - 1) / c) * 4 * nmat + 4) + (c > 1 ? 3 : 0);
             if (best < 0 || cost < best) { best = cost; ks = c; }
         }
-        // gate/up with fewer tiles than SMs: two shares measured better than the model says (64 sequences, 4 layers:
-        // 2.59 -> 2.47 ms per step), the 4096 -> 12288 product flat for any split
-        if (nmat == 2 && ks == 1 && tiles * ttiles < sms && nquads >= 2 && n % 4 == 0 && T <= 2 * kMaxTok &&
-            (size_t)2 * 2 * T * n * sizeof(float) <= ws.partial_bytes)
-            ks = 2;
+        // gate/up with fewer tiles than SMs: shares measured better than the model says (64 sequences, 4 layers, ms per step:
+        // one share 2.59, two 2.47, three 2.42, four 2.44), the 4096 -> 12288 product flat for any split
+        if (nmat == 2 && ks == 1 && tiles * ttiles < sms && nquads >= 2 && n % 4 == 0 && T <= 2 * kMaxTok) {
+            const int want = nquads >= 3 ? 3 : 2;
+            if ((size_t)want * 2 * T * n * sizeof(float) <= ws.partial_bytes) ks = want;
+        }
         if (getenv("LC_GEMM_NO_SPLIT")) ks = 1;
+        if (nmat == 2 && getenv("LC_GEMM_KSPLIT_GU") && T <= 2 * kMaxTok && n % 4 == 0)  // experiments: gate/up only
+            ks = std::max(1, std::min(atoi(getenv("LC_GEMM_KSPLIT_GU")), std::min(8, nquads)));
         if (getenv("LC_GEMM_KSPLIT") && T <= 2 * kMaxTok && n % 4 == 0) ks = std::max(1, std::min(atoi(getenv("LC_GEMM_KSPLIT")), std::min(8, nquads)));  // experiments
     }
     p.ksplit = ks;
