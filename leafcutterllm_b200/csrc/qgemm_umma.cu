@@ -183,7 +183,7 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 // One token per CTA: optional RMS norm, power-of-two scale, hi/lo split to f16, sub-block sums.
 // xh: [hi rows | lo rows at lo_offset] of K f16; sx: the same for the sums, rows of K/16 f16 -- per 256-element unit the
 // eight sub-block sums followed by eight zeros.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int K, __half* __restrict__ xh,
              size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
     extern __shared__ float row[];
@@ -614,7 +614,9 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
             LC_CUDA(cudaFuncSetAttribute(xprep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set = smem;
         }
-        LC_CUDA(launch_pdl(xprep_kernel, dim3(T), dim3(256), smem, s, a.x, a.norm_w, a.eps, K, (__half*)ws.xh, lo_offset, (__half*)ws.sx,
+        // a token's row is short (16 - 44 KB) and its three passes are latency: many threads, one or a few float4 each
+        static const int xthreads = getenv("LC_XPREP_THREADS") ? atoi(getenv("LC_XPREP_THREADS")) : 1024;
+        LC_CUDA(launch_pdl(xprep_kernel, dim3(T), dim3(K >= 4096 ? xthreads : 256), smem, s, a.x, a.norm_w, a.eps, K, (__half*)ws.xh, lo_offset, (__half*)ws.sx,
                            sx_lo_offset, ws.tok_scale));
     }
     const int N = std::min(kMaxTok, (T + 15) & ~15);
