@@ -381,7 +381,7 @@ def attention_microbench(lc, n_heads=32, n_kv=32, hd=128, ctx=2100, layers=8, re
             "us_per_call": round(us, 2), "kv_bytes": byt, "achieved_gbs": round(byt / us / 1e3, 1)}
 
 
-def batched_decode(lc, synth, spec, local: int, n_seqs: int = 64, steps: int = 32, warm: int = 3) -> dict:
+def batched_decode(lc, synth, spec, local: int, n_seqs: int = 64, steps: int = 32, warm: int = 3, profile_range: bool = False) -> dict:
     """BASELINE.json configs[2]: the same model under continuous batching -- 64 sequences whose context lengths are
     uniform in [128, 4096] from seed 777, paged f16 KV cache (16-token pages), greedy decode.  Every sequence is
     prefilled with its own seeded prompt (through the many-token tensor-core product), then `steps` decode steps are
@@ -401,7 +401,12 @@ def batched_decode(lc, synth, spec, local: int, n_seqs: int = 64, steps: int = 3
     ids = list(range(n_seqs))
     toks, _ = eng.decode_loop(ids, first, warm)
     eng.reset_counters()
+    if profile_range:  # a profiler started with --profile-from-start off sees the timed steps only, not the prefill
+        import torch
+        torch.cuda.cudart().cudaProfilerStart()
     toks, ms = eng.decode_loop(ids, toks[-1].tolist(), steps)
+    if profile_range:
+        torch.cuda.cudart().cudaProfilerStop()
     ctr = eng.counters()
     eng.close()
     peak, which = measured_peaks()
@@ -549,7 +554,7 @@ def main():
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth
         spec = synth.LLAMA7B if args.layers <= 0 else synth.LLAMA7B.with_layers(args.layers)
-        out = batched_decode(lc, synth, spec, 0, steps=min(args.steps, 32))
+        out = batched_decode(lc, synth, spec, 0, steps=min(args.steps, 32), profile_range=args.profile_range)
         if args.layers > 0:
             out["not_the_metric"] = f"profiling case: {args.layers} of 32 layers"
         print(json.dumps(out))
