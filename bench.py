@@ -132,8 +132,10 @@ def cpu_baseline(spec, steps: int = 4, layers: int = 2, prompt: int = 64, thread
     import oracle
     from leafcutterllm_b200 import synth
     oracle.build()
-    if threads:
-        oracle.lib().orc_set_num_threads(threads)
+    if not threads:
+        # every host core this process may run on, set explicitly: a launcher may export OMP_NUM_THREADS=1 to its ranks
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.lib().orc_set_num_threads(threads)
     cores = oracle.lib().orc_num_threads()
     sub = spec.with_layers(layers)
 
