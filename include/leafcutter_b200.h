@@ -243,13 +243,15 @@ int32_t lc_gguf_inspect(const char* path, int32_t scan, lc_gguf_report* report, 
  * lc_shard_engine_forward  <-> ShardEngine::forward(&tokens) (:99-167): logits of the last token (logits_out [vocab], may be
  *                              null) and its greedy pick (next_out, may be null); the cache grows by n.
  * lc_shard_engine_generate <-> ShardEngine::generate (:74-97): clears the cache, first token from the prefill, at most
- *                              max_tokens tokens, stops after token 2; temperature > 0 returns LC_ERR_UNSUPPORTED.
+ *                              max_tokens tokens, stops after token 2; temperature > 0 needs lc_shard_engine_set_seed first
+ *                              (draws and arithmetic as in lc_generate), else LC_ERR_UNSUPPORTED.
  * lc_shard_engine_reset_kv_cache / _kv_cache_memory_bytes <-> reset_kv_cache (:64-66) / kv_cache_memory_mb (:69-71). */
 typedef struct lc_shard_engine lc_shard_engine;
 int32_t lc_shard_engine_load(const char* manifest_path, int32_t max_seq_len, int32_t device, lc_shard_engine** out);
 int32_t lc_shard_engine_forward(lc_shard_engine* e, const int64_t* tokens, int32_t n, float* logits_out, int64_t* next_out);
 int32_t lc_shard_engine_generate(lc_shard_engine* e, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature,
                                  float top_p, int64_t* out_tokens, int32_t* n_out);
+int32_t lc_shard_engine_set_seed(lc_shard_engine* e, uint64_t seed);
 int32_t lc_shard_engine_reset_kv_cache(lc_shard_engine* e);
 int32_t lc_shard_engine_kv_cache_memory_bytes(lc_shard_engine* e, uint64_t* out);
 int32_t lc_shard_engine_destroy(lc_shard_engine* e);

@@ -109,6 +109,7 @@ SIGNATURES = {
     "lc_shard_engine_load": (_i32, [C.c_char_p, _i32, _i32, C.POINTER(_vp)]),
     "lc_shard_engine_forward": (_i32, [_vp, _vp, _i32, _vp, _vp]),
     "lc_shard_engine_generate": (_i32, [_vp, _vp, _i32, _i32, C.c_float, C.c_float, _vp, C.POINTER(_i32)]),
+    "lc_shard_engine_set_seed": (_i32, [_vp, _u64]),
     "lc_shard_engine_reset_kv_cache": (_i32, [_vp]),
     "lc_shard_engine_kv_cache_memory_bytes": (_i32, [_vp, C.POINTER(_u64)]),
     "lc_shard_engine_destroy": (_i32, [_vp]),

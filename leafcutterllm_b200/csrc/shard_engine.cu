@@ -139,6 +139,8 @@ struct ShardMat {
 
 struct lc_shard_engine {
     int device = 0;
+    bool seeded = false;  // lc_shard_engine_set_seed: temperature > 0 allowed, draws seeded_uniform(seed, draws++)
+    uint64_t seed = 0, draws = 0;
     cudaStream_t stream = nullptr;
     int L = 0, H = 0, nh = 0, nkv = 0, hd = 0, F = 0, V = 0, nqkv = 0, max_seq = 0;
     float theta = 10000.f;
@@ -527,18 +529,36 @@ extern "C" int32_t lc_shard_engine_forward(lc_shard_engine* e, const int64_t* to
 }
 
 // ShardEngine::generate (shard_engine.rs:74-97): clears the cache, first token from the prefill, stops after token 2.
+extern "C" int32_t lc_shard_engine_set_seed(lc_shard_engine* e, uint64_t seed) {
+    LC_CHECK(e != nullptr, LC_ERR_INVALID, "lc_shard_engine_set_seed: null engine");
+    e->seeded = true;
+    e->seed = seed;
+    e->draws = 0;
+    return LC_OK;
+}
+
 extern "C" int32_t lc_shard_engine_generate(lc_shard_engine* e, const int64_t* tokens, int32_t n, int32_t max_tokens, float temperature, float top_p,
                                             int64_t* out_tokens, int32_t* n_out) {
-    (void)top_p;
     LC_CHECK(e && tokens && n >= 1 && max_tokens >= 1 && out_tokens && n_out, LC_ERR_INVALID, "lc_shard_engine_generate: bad argument");
-    LC_CHECK(temperature <= 0.f, LC_ERR_UNSUPPORTED, "sampling with temperature > 0 draws from an unseeded generator in the reference; only greedy is implemented");
+    const bool stochastic = temperature > 0.f;
+    LC_CHECK(!stochastic || e->seeded, LC_ERR_UNSUPPORTED,
+             "sampling with temperature > 0 draws from an unseeded generator in the reference (rust/src/inference/sampler.rs:38-39); call "
+             "lc_shard_engine_set_seed first, or pass temperature <= 0 for greedy");
+    // sample_top_p on the logits the forward left on the device (shard_engine.rs:82, 90)
+    auto pick = [&](int64_t* tok) -> int32_t {
+        if (!stochastic) return LC_OK;
+        LC_CUDA(cudaSetDevice(e->device));
+        return sample_top_p_sync(e->d_logits, (size_t)e->V, temperature, top_p, seeded_uniform(e->seed, e->draws++), tok, e->stream);
+    };
     e->seq_len = 0;
     int64_t next = 0;
     LC_TRY(lc_shard_engine_forward(e, tokens, n, nullptr, &next));
+    LC_TRY(pick(&next));
     int count = 0;
     out_tokens[count++] = next;
     while (next != 2 && count < max_tokens) {
         LC_TRY(lc_shard_engine_forward(e, &next, 1, nullptr, &next));
+        LC_TRY(pick(&next));
         out_tokens[count++] = next;
     }
     *n_out = count;

@@ -224,7 +224,11 @@ class ShardEngine:
         check(load().lc_shard_engine_forward(self._h, _p(t), t.size, _p(out), None))
         return out
 
-    def generate(self, tokens: Iterable[int], max_tokens: int, temperature: float = 0.0, top_p: float = 1.0) -> list:
+    def generate(self, tokens: Iterable[int], max_tokens: int, temperature: float = 0.0, top_p: float = 1.0,
+                 seed: Optional[int] = None) -> list:
+        """`ShardEngine::generate` (rust/src/inference/shard_engine.rs:74-97); temperature > 0 needs `seed` (see Engine.generate)."""
+        if seed is not None:
+            check(load().lc_shard_engine_set_seed(self._h, int(seed)))
         t = np.ascontiguousarray(list(tokens), dtype=np.int64)
         out = np.empty(max_tokens, np.int64)
         n_out = C.c_int32()

@@ -69,6 +69,28 @@ def test_shard_engine_matches_the_oracle(gpu, oracle, tmp_path, fmt):
     eng.close()
 
 
+def test_shard_engine_seeded_sampling(gpu, oracle, tmp_path):
+    """temperature > 0 after a seed: forward, sample_top_p (rust/src/inference/sampler.rs:12-50) with the documented draws."""
+    from leafcutterllm_b200 import LeafcutterError, ShardEngine, seeded_uniform
+    path, _ = shard_util.write_model(str(tmp_path / "shards"), random_weights(3), CFG, shard_util.Q8_0)
+    eng = ShardEngine.load_with_cache(path, CFG["num_layers"])
+    prompt = np.random.default_rng(8).integers(3, CFG["vocab_size"], 11).tolist()
+    with pytest.raises(LeafcutterError, match="LC_ERR_UNSUPPORTED"):
+        eng.generate(prompt, 4, temperature=0.7, top_p=0.9)
+    got = eng.generate(prompt, 9, temperature=1.3, top_p=0.9, seed=5)
+    assert got == eng.generate(prompt, 9, temperature=1.3, top_p=0.9, seed=5)
+    eng.reset_kv_cache()
+    want, feed = [], list(prompt)
+    for i in range(9):
+        tok = oracle.sample_top_p(eng.forward(feed, CFG["vocab_size"]), 1.3, 0.9, seeded_uniform(5, i))
+        want.append(tok)
+        feed = [tok]
+        if tok == 2:   # ShardEngine::generate stops after token 2 (shard_engine.rs:84-86, 92-94)
+            break
+    assert got == want and got != eng.generate(prompt, 9)
+    eng.close()
+
+
 def test_shard_loader_rejects_broken_files(gpu, tmp_path):
     from leafcutterllm_b200 import LeafcutterError, ShardEngine
     w = random_weights(3)
