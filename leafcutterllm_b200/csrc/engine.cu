@@ -385,6 +385,9 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
         o.out_flag = m->f_hidden2; o.node_out = 5 * l + 3;
     }
     if (ablate_mask() & 4) return LC_OK;
+    if (residual && out == m->d_hidden2 && w.ffn_norm) {  // in a layer of the forward pass the FFN reads `out` next, through its norm
+        o.prep_next = true; o.next_norm_w = w.ffn_norm; o.next_eps = m->cfg.rms_eps;
+    }
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
 }
 
@@ -407,6 +410,8 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         g.x = nullptr; g.x_flag = m->f_hidden2; g.node_in = 5 * l + 3;
         g.out_flag = m->f_ffn; g.node_out = 5 * l + 4;
     }
+    g.prep_next = !(ablate_mask() & 16);  // the down projection reads d_ffn next, without a norm
+    g.next_norm_w = nullptr;
     if (!(ablate_mask() & 8)) LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
     GemvArgs d;
     d.w = &w.down;
@@ -421,6 +426,10 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         d.out_flag = m->f_hidden; d.node_out = 5 * l + 5;
     }
     if (ablate_mask() & 16) return LC_OK;
+    if (residual && out == m->d_hidden && l + 1 < m->L && m->layers[l + 1].attn_norm && !(ablate_mask() & 2)) {
+        // the next layer's q/k/v product(s) read `out` through that layer's attention norm
+        d.prep_next = true; d.next_norm_w = m->layers[l + 1].attn_norm; d.next_eps = m->cfg.rms_eps;
+    }
     return gemv_tiled(m, d, T, m->H, m->F);
 }
 

@@ -77,6 +77,11 @@ struct GemvArgs {
     float eps = 1e-5f;
     GemvEpilogue epi = EPI_STORE;
     L2Prefetch prefetch;              // honoured by the tensor-core Q4_K kernel
+    // Many-token product only: the caller promises that the next product reads `out` (all m rows) as its input with this
+    // gain (null: no norm) -- the kernel that sums the shares of k then also prepares that input, saving a launch.
+    bool prep_next = false;
+    const float* next_norm_w = nullptr;
+    float next_eps = 1e-5f;
     // Dataflow mode (one token, the mma.sync Q4_K kernel): activations travel as flagged words (see flag_store) and
     // the kernel does not wait for the grid ahead of it.  x_flag replaces x, out_flag replaces out, residual_flag
     // replaces residual; step_ctr points at the device-side step counter and the node numbers give the epochs
@@ -106,6 +111,11 @@ struct GemmWorkspace {
     float* partial = nullptr;    // sums of the shares of k when a product is split over several CTAs per tile
     size_t partial_bytes = 0;
     int t_cap = 0, k_max = 0;
+    // what xh / sx / tok_scale hold when the summing kernel of the previous product prepared them (see GemvArgs::prep_next);
+    // valid for the very next product only
+    mutable const float* prep_x = nullptr;
+    mutable const float* prep_norm = nullptr;
+    mutable int prep_k = 0, prep_t = 0;
 };
 int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max);
 void qgemm_workspace_free(GemmWorkspace* ws);

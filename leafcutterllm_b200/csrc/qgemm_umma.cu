@@ -183,21 +183,12 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 // One token per CTA: optional RMS norm, power-of-two scale, hi/lo split to f16, sub-block sums.
 // xh: [hi rows | lo rows at lo_offset] of K f16; sx: the same for the sums, rows of K/16 f16 -- per 256-element unit the
 // eight sub-block sums followed by eight zeros.
-__global__ void __launch_bounds__(1024)
-xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int K, __half* __restrict__ xh,
-             size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
-    extern __shared__ float row[];
-    __shared__ float sh[32];
-    pdl_wait();
-    pdl_launch_dependents();
-    const int t = blockIdx.x;
-    const float* xr = x + (size_t)t * K;
-    float acc = 0.f, mx = 0.f;
-    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
-        const float4 v = *reinterpret_cast<const float4*>(xr + i);
-        *reinterpret_cast<float4*>(row + i) = v;
-        acc = fmaf(v.x, v.x, acc); acc = fmaf(v.y, v.y, acc); acc = fmaf(v.z, v.z, acc); acc = fmaf(v.w, v.w, acc);
-    }
+// The passes of the preparation over a token's row held in shared memory; `acc` = this thread's part of the sum of
+// squares, accumulated over elements 4 * tid + 4 * blockDim * j in that order.
+__device__ __forceinline__ void xprep_row(float* row, float acc, const float* __restrict__ norm_w, float eps, int K, int t,
+                                          __half* __restrict__ xh, size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset,
+                                          float* __restrict__ tok_scale, float* sh) {
+    float mx = 0.f;
     float scale = 1.f;
     if (norm_w) {
         const float ss = block_sum(acc, sh);
@@ -254,6 +245,24 @@ xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, floa
             sxl[idx + 8] = __float2half_rn(0.f);
         }
     }
+}
+
+__global__ void __launch_bounds__(1024)
+xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int K, __half* __restrict__ xh,
+             size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
+    extern __shared__ float row[];
+    __shared__ float sh[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)t * K;
+    float acc = 0.f;
+    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        *reinterpret_cast<float4*>(row + i) = v;
+        acc = fmaf(v.x, v.x, acc); acc = fmaf(v.y, v.y, acc); acc = fmaf(v.z, v.z, acc); acc = fmaf(v.w, v.w, acc);
+    }
+    xprep_row(row, acc, norm_w, eps, K, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
 }
 
 // grid = (row tiles, token tiles).  tmw0 / tmw1: raw blocks of the matrix (and of `up` for EPI_SILU_MUL), box = one unit
@@ -560,6 +569,42 @@ qgemm_reduce_kernel(const float* __restrict__ partial, int slices, size_t plane,
     *reinterpret_cast<float4*>(out + i) = a;
 }
 
+// qgemm_reduce_kernel for one token per CTA, followed by the preparation of that token's finished row as the input of the
+// next product (xprep_kernel's passes on the row while it is still in shared memory).  Same sums in the same order as
+// the two kernels it replaces; the block size must be the one xprep_kernel would be launched with for K = n.
+__global__ void __launch_bounds__(1024)
+qgemm_reduce_prep_kernel(const float* __restrict__ partial, int slices, int T, int n, int epi, const float* __restrict__ residual,
+                         float* __restrict__ out, const float* __restrict__ next_norm_w, float next_eps, __half* __restrict__ xh,
+                         size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
+    extern __shared__ float row[];
+    __shared__ float sh[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const size_t plane = (size_t)T * n;
+    float acc = 0.f;
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+        const size_t idx = (size_t)t * n + i;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        for (int sl = 0; sl < slices; sl++) {
+            const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)sl * plane + idx);
+            float4& d = (epi == EPI_SILU_MUL && (sl & 1)) ? b : a;
+            d.x += v.x; d.y += v.y; d.z += v.z; d.w += v.w;
+        }
+        if (epi == EPI_SILU_MUL) {
+            a.x = __fmul_rn(silu_f(a.x), b.x); a.y = __fmul_rn(silu_f(a.y), b.y);
+            a.z = __fmul_rn(silu_f(a.z), b.z); a.w = __fmul_rn(silu_f(a.w), b.w);
+        } else if (epi == EPI_ADD_RESIDUAL) {
+            const float4 r = *reinterpret_cast<const float4*>(residual + idx);
+            a.x = __fadd_rn(r.x, a.x); a.y = __fadd_rn(r.y, a.y); a.z = __fadd_rn(r.z, a.z); a.w = __fadd_rn(r.w, a.w);
+        }
+        *reinterpret_cast<float4*>(out + idx) = a;
+        *reinterpret_cast<float4*>(row + i) = a;
+        acc = fmaf(a.x, a.x, acc); acc = fmaf(a.y, a.y, acc); acc = fmaf(a.z, a.z, acc); acc = fmaf(a.w, a.w, acc);
+    }
+    xprep_row(row, acc, next_norm_w, next_eps, n, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
+}
+
 // ---- host side --------------------------------------------------------------------------------------------------------
 int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max) {
     LC_CHECK(ws && t_cap > 0 && k_max > 0, LC_ERR_INVALID, "qgemm workspace: bad size");
@@ -607,7 +652,10 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     const int terms = (getenv("LC_GEMM_TERMS") && atoi(getenv("LC_GEMM_TERMS")) == 1) ? 1 : 3;  // read per call so that a test can switch it
     // activations: [t_cap rows of high halves | t_cap rows of low halves], each row k elements of this matrix
     const size_t lo_offset = (size_t)ws.t_cap * K, sx_lo_offset = (size_t)ws.t_cap * (K / 16);
-    {
+    // the summing kernel of the product before this one may have prepared exactly this input (GemvArgs::prep_next)
+    const bool prepared = ws.prep_x == a.x && ws.prep_norm == a.norm_w && ws.prep_k == K && ws.prep_t == T && a.x != nullptr;
+    ws.prep_x = nullptr;
+    if (!prepared) {
         const size_t smem = (size_t)K * sizeof(float);
         static size_t attr_set = 0;
         if (smem > 48 * 1024 && smem > attr_set) {
@@ -681,10 +729,25 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     LC_CUDA(launch_pdl(qgemm_umma_q4k_kernel, grid, dim3(kThreads), smem, s, *t0, *t1, tmx, tms, p));
     if (ks > 1) {
         const size_t plane = (size_t)T * n;
-        LC_CUDA(launch_pdl(qgemm_reduce_kernel, dim3((unsigned)((plane / 4 + 255) / 256)), dim3(256), 0, s, (const float*)ws.partial, 2 * ks,
-                           plane, (int)a.epi, a.residual, a.out));
+        static const bool no_fused_prep = getenv("LC_GEMM_NO_FUSED_PREP") != nullptr;
+        if (a.prep_next && !no_fused_prep && n % kUnitElems == 0 && n <= ws.k_max) {
+            // one CTA per token sums the shares and prepares the row for the next product, whose k is this n
+            const size_t rsmem = (size_t)n * sizeof(float);
+            static size_t rattr = 0;
+            if (rsmem > 48 * 1024 && rsmem > rattr) {
+                LC_CUDA(cudaFuncSetAttribute(qgemm_reduce_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rsmem));
+                rattr = rsmem;
+            }
+            LC_CUDA(launch_pdl(qgemm_reduce_prep_kernel, dim3(T), dim3(n >= 4096 ? 1024 : 256), rsmem, s, (const float*)ws.partial, 2 * ks, T, n,
+                               (int)a.epi, a.residual, a.out, a.next_norm_w, a.next_eps, (__half*)ws.xh, (size_t)ws.t_cap * n, (__half*)ws.sx,
+                               (size_t)ws.t_cap * (n / 16), ws.tok_scale));
+            ws.prep_x = a.out; ws.prep_norm = a.next_norm_w; ws.prep_k = n; ws.prep_t = T;
+        } else {
+            LC_CUDA(launch_pdl(qgemm_reduce_kernel, dim3((unsigned)((plane / 4 + 255) / 256)), dim3(256), 0, s, (const float*)ws.partial, 2 * ks,
+                               plane, (int)a.epi, a.residual, a.out));
+        }
     }
-    if (launches) *launches = ks > 1 ? 3 : 2;
+    if (launches) *launches = (prepared ? 1 : 2) + (ks > 1 ? 1 : 0);
     if (want_trace) {
         static long long h[1280];
         LC_CUDA(cudaStreamSynchronize(s));
