@@ -143,6 +143,10 @@ __device__ __forceinline__ void attention_item(const AttnParams& p, int item, in
     const int tok = item / n_heads, h = item % n_heads;
     const int pos = p.tok_pos[tok];
     const int ctx = pos + 1;  // causal: positions 0..tok_pos (attention.rs:81-83)
+    // pieces of the context that hold at least one key of this token; a CTA of a piece past them has nothing to add and
+    // leaves at once (the merge below counts the live pieces only)
+    const int live = (p.n_splits == 1) ? 1 : min(p.n_splits, (ctx + p.chunk - 1) / p.chunk);
+    if (split >= live) return;
     const int t_begin = split * p.chunk;
     const int t_end = min(ctx, t_begin + p.chunk);
     float* pout = p.partial + ((size_t)item * p.n_splits + split) * (HD + 2);
@@ -296,17 +300,17 @@ __device__ __forceinline__ void attention_item(const AttnParams& p, int item, in
     group_sync<BAR>(bar_id);
     if (tid == 0) {
         const int done = atomicAdd(&p.counters[item], 1);
-        *sm_last = (done == p.n_splits - 1);
+        *sm_last = (done == live - 1);
     }
     group_sync<BAR>(bar_id);
     if (!*sm_last) return;
     __threadfence();
     const float* pp = p.partial + (size_t)item * p.n_splits * (HD + 2);
     float mm = -INFINITY;
-    for (int s = 0; s < p.n_splits; s++) mm = fmaxf(mm, __ldcg(pp + (size_t)s * (HD + 2)));
+    for (int s = 0; s < live; s++) mm = fmaxf(mm, __ldcg(pp + (size_t)s * (HD + 2)));
     for (int d = tid; d < HD; d += kAttnWarps * 32) {
         float ll = 0.f, a = 0.f;
-        for (int s = 0; s < p.n_splits; s++) {
+        for (int s = 0; s < live; s++) {
             const float* ps = pp + (size_t)s * (HD + 2);
             const float ms = __ldcg(ps);
             if (ms == -INFINITY) continue;  // empty split
