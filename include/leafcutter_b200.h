@@ -118,17 +118,21 @@ int32_t lc_dequantize_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, f
 int32_t lc_attention_decode_dev(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
                                 int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
                                 int32_t page_tokens, int32_t kv_f32, float* out_dev);
-/* Same operation and same kernel for callers that must not allocate device memory at call time -- code running inside a
+/* Same operation and same kernels for callers that must not allocate device memory at call time -- code running inside a
  * framework's allocator-owned arena, under a memory budget that is already fully handed out, or in a late phase where
- * cudaMalloc would serialise the device.  It has no counterpart in the reference.  The split partials go to a 512 KiB array
- * built into the library image (every GPU that loads the library holds it until the process exits); nothing is
- * allocated or freed, by this call or by anything it uses.  Shapes whose partials do not fit
- * (256 + 4*n_heads rounded up to 256 + n_heads * splits * (head_dim + 2) * 4 bytes > 512 KiB, where splits is about
- * 4 * SM count / n_heads; e.g. 32 heads of 128 dims need 316 KB, 128 heads of 256 dims do not fit) are rejected with LC_ERR_INVALID.
- * The first call on a device looks up the array's device address; make that first call outside any stream capture.
- * All calls share the one array, which keeps the previous call's partials: the counters it needs at zero are cleared at
- * the start of every call, and two calls that overlap on the GPU (different streams, different threads) would race --
- * the library queues them on its single stream, keep it that way. */
+ * cudaMalloc would serialise the device.  It has no counterpart in the reference.  The split partials go to a 1 MiB array
+ * built into the library image (every GPU that loads the library holds it until the process exits), and the word the
+ * kernels raise when a bounded wait runs out is part of the image too: nothing is allocated or freed, by this call or
+ * by anything it uses, also when it is the first call a process makes into the library.
+ * Size rule: 256 bytes of bookkeeping + 4 * n_heads rounded up to 256 + the partials must fit 1 MiB, where the partials are
+ * n_heads * pieces * (head_dim + 2) * 4 bytes and pieces = ceil(ctx_len / 128) (the context is cut into 128-key pieces, so
+ * the need grows with the context; a context under a few hundred keys may be cut finer, into at most 4 * SM count / n_heads
+ * pieces of 64 keys).  32 heads of 128 dims are accepted up to ctx_len 7936 and refused from 7937 on;
+ * 128 heads of 256 dims fit up to ctx_len 896.  Shapes that do not fit are rejected with LC_ERR_INVALID.
+ * The first call on a device looks up the device addresses of the array and of that word; make that first call outside
+ * any stream capture.  All calls share the one array, which keeps the previous call's partials: the counters it needs
+ * at zero are cleared at the start of every call, and two calls that overlap on the GPU (different streams, different
+ * threads) would race -- the library queues them on its single stream, keep it that way. */
 int32_t lc_attention_decode_static(const float* q_dev, const void* k_pool_dev, const void* v_pool_dev, const int32_t* page_table_dev,
                                    int32_t n_pages, int32_t ctx_len, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
                                    int32_t page_tokens, int32_t kv_f32, float* out_dev);
@@ -317,11 +321,6 @@ typedef struct lc_counters {
 } lc_counters;
 int32_t lc_get_counters(const lc_model* m, lc_counters* out);
 int32_t lc_reset_counters(lc_model* m);
-
-/* Diagnostics (no counterpart in the reference): when LC_TRACE=1 was set at lc_model_finalize, the persistent
- * decode kernel stamps the global timer (ns) of one CTA at every phase: out[2*i] = phase i entered, out[2*i+1] = done.
- * Returns the stamps of the most recent step. */
-int32_t lc_debug_phase_trace(lc_model* m, uint64_t* out, int32_t max_entries, int32_t* n_phases);
 
 /* Layer-level probes for parity tests: run one sub-block of layer `layer` on host activations
  * through the same kernels lc_forward uses.  attention_forward (attention.rs:37-118) appends to

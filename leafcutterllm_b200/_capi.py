@@ -122,7 +122,6 @@ SIGNATURES = {
     "lc_decode_loop": (_i32, [_vp, _i32, _vp, _vp, _i32, _vp, _f]),
     "lc_get_counters": (_i32, [_vp, C.POINTER(Counters)]),
     "lc_reset_counters": (_i32, [_vp]),
-    "lc_debug_phase_trace": (_i32, [_vp, _vp, _i32, C.POINTER(_i32)]),
     "lc_probe_attention": (_i32, [_vp, _i32, _vp, _i32, _vp]),
     "lc_probe_ffn": (_i32, [_vp, _i32, _vp, _i32, _vp]),
 }

@@ -10,7 +10,6 @@
 // finish merges the splits in split order.  The reference's three-pass softmax and this one agree to rounding.
 #include "lc_kernels.h"
 #include "lc_attn.cuh"
-#include "lc_mega.h"
 #include "lc_tma.cuh"
 
 namespace lc {
@@ -122,11 +121,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_staged_kernel(AttnP
     if (fused && p.positions_settled) {  // the cache holds only earlier steps' tokens: fetch before waiting for the projection kernel
         pos = p.tok_pos[tok];
         stage(pos);
-        if (tid == 32) {
-            const unsigned part = blockIdx.y * gridDim.x + blockIdx.x, nparts = gridDim.x * gridDim.y;
-            l2_prefetch_part(p.prefetch.p[0], p.prefetch.bytes[0], part, nparts);
-            l2_prefetch_part(p.prefetch.p[1], p.prefetch.bytes[1], part, nparts);
-        }
         pdl_launch_dependents();
         pdl_wait();
     } else {      // the previous kernel wrote this call's keys into the cache
@@ -282,10 +276,7 @@ int32_t launch_rope_kv_append(float* q, float* k, const float* v, int row_stride
 }
 
 // (token, head) pairs up to which decode attention uses the split-context kernel with shared-memory staging
-static int staged_pair_limit() {
-    static const int mult = getenv("LC_ATTN_STAGED_LIMIT") ? atoi(getenv("LC_ATTN_STAGED_LIMIT")) : 4;
-    return sm_count() * mult;
-}
+static int staged_pair_limit() { return sm_count() * 4; }
 
 static void split_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_splits) {
     int want_ctas = sm_count() * 4;
@@ -297,14 +288,10 @@ static void split_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_s
     // A batched decode step (up to 256 tokens, each over its own long context): contexts differ widely, and the CTA of the
     // longest one would run on alone at the end; 1024-key pieces keep the tail short (64 sequences: 2.66 -> 2.49 ms for 4 layers).
     if (n_tok <= 256 && ch > 1024) ch = 1024;
-    static const int force = getenv("LC_ATTN_CHUNK") ? atoi(getenv("LC_ATTN_CHUNK")) : 0;  // experiments only
-    if (force > 0) ch = force;
     *chunk = ch;
     *n_splits = (max_ctx + ch - 1) / ch;
     if (*n_splits < 1) *n_splits = 1;
 }
-
-void attention_plan(int n_tok, int n_heads, int max_ctx, int* chunk, int* n_splits) { split_plan(n_tok, n_heads, max_ctx, chunk, n_splits); }
 
 size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx) {
     int chunk, splits;
@@ -316,9 +303,8 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx) {
 }
 
 static bool staged_applies(const AttnParams& p, int n_tok) {
-    static const bool off = getenv("LC_ATTN_NO_STAGED") != nullptr;
     // few tokens (decode): the split-context kernel with shared-memory staging; many tokens (prefill) keep one CTA per (token, head)
-    return !off && p.kv.hd == 128 && !p.kv.kv_f32 && p.kv.page_tokens == 16 && n_tok * p.n_heads <= staged_pair_limit();
+    return p.kv.hd == 128 && !p.kv.kv_f32 && p.kv.page_tokens == 16 && n_tok * p.n_heads <= staged_pair_limit();
 }
 
 template <int HD>
@@ -328,11 +314,7 @@ static int32_t launch_attention_hd(const AttnParams& base, int n_tok, int max_ct
         p.chunk = kStagedChunk;
         p.n_splits = (max_ctx + kStagedChunk - 1) / kStagedChunk;
         const size_t smem = (size_t)kStagedChunk * 128 * 2 * 2;
-        static bool attr_set = false;
-        if (!attr_set) {
-            LC_CUDA(cudaFuncSetAttribute(attention_staged_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set = true;
-        }
+        LC_CUDA(ensure_smem_limit((const void*)attention_staged_kernel<128>, smem));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(n_tok * p.kv.n_kv), (unsigned)p.n_splits);
         cfg.blockDim = dim3(kAttnWarps * 32);
@@ -363,15 +345,9 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
     p.counters = counters;
     p.k_new = fuse ? fuse->k_new : nullptr; p.v_new = fuse ? fuse->v_new : nullptr;
     p.tok_rope = fuse ? fuse->tok_rope : nullptr; p.theta = fuse ? fuse->theta : 0.f;
-    if (fuse) p.prefetch = fuse->prefetch;
     p.positions_settled = (fuse && fuse->positions_settled) ? 1 : 0;
-    if (fuse && fuse->qkv_flag) {
-        p.qkvf = fuse->qkv_flag; p.outf = fuse->out_flag; p.step_ctr = fuse->step_ctr; p.node_in = fuse->node_in; p.node_out = fuse->node_out;
-        LC_CHECK(attention_stream_applies(p, n_tok) && p.outf && p.step_ctr, LC_ERR_UNSUPPORTED,
-                 "attention: flagged activations are only implemented by the single-token streaming kernel");
-    }
     p.error_flag = gemv_error_flag_dev();
-    if (fuse && attention_stream_applies(p, n_tok)) return launch_attention_stream(p, s);
+    if (fuse && fuse->stream_slots && attention_stream_applies(p, n_tok)) return launch_attention_stream(p, fuse->stream_slots, s);
     switch (kv.hd) {
         case 32: return launch_attention_hd<32>(p, n_tok, max_ctx, s);
         case 64: return launch_attention_hd<64>(p, n_tok, max_ctx, s);
@@ -381,11 +357,6 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
             set_error("attention: head_dim %d is not one of 32, 64, 128, 256", kv.hd);
             return LC_ERR_UNSUPPORTED;
     }
-}
-
-int attention_launch_count(int n_tok, int n_heads, int max_ctx) {
-    (void)n_tok; (void)n_heads; (void)max_ctx;
-    return 1;
 }
 
 }  // namespace lc
@@ -434,8 +405,8 @@ int32_t attn_op_run(const AttnOpArgs& a, unsigned char* scratch, cudaStream_t s)
 }
 
 // Scratch of lc_attention_decode_static: lives in the library image, so every GPU that loads the library
-// holds these 512 KiB until the process exits.
-constexpr size_t kStaticAttnScratchBytes = (size_t)512 << 10;
+// holds this 1 MiB until the process exits.
+constexpr size_t kStaticAttnScratchBytes = (size_t)1 << 20;
 static __device__ __align__(256) unsigned char g_static_attn_scratch[kStaticAttnScratchBytes];
 unsigned char* g_static_attn_ptr[16] = {};
 }  // namespace

@@ -57,7 +57,7 @@ struct StreamParams {
 template <int GSZ>
 __host__ __device__ constexpr int consumer_warps() { return GSZ <= 2 ? 15 : 7; }
 
-template <int GSZ, bool FLAGGED>
+template <int GSZ>
 __global__ void __launch_bounds__((consumer_warps<GSZ>() + 1) * 32, 1)
 attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_constant__ CUtensorMap vtm, StreamParams P) {
     constexpr int kCWarps = consumer_warps<GSZ>();
@@ -86,16 +86,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     }
     __syncthreads();
     pdl_launch_dependents();
-    // Dataflow mode: the projection row arrives as flagged words, so nothing here waits for the grid ahead; the step's
-    // position was final before the step's first kernel started.
-    constexpr bool flagged = FLAGGED;  // compile-time: the plain kernel carries none of the polling code
-    uint32_t epoch_in = 0, epoch_out = 0;
-    if (flagged) {
-        const uint32_t base = (uint32_t)(*p.step_ctr) * kEpochStride;
-        epoch_in = base + (uint32_t)p.node_in;
-        epoch_out = base + (uint32_t)p.node_out;
-    }
-    if (!flagged && !p.positions_settled) pdl_wait();  // the position itself may still be in flight
+    if (!p.positions_settled) pdl_wait();  // the position itself may still be in flight
 
     // the token's items: (kv head, page), kv head major
     const int pos = p.tok_pos[0];
@@ -137,28 +128,12 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     }
 
     // ---- consumers ----
-    if (!flagged) pdl_wait();  // q and this step's k, v come from the projection kernel
+    pdl_wait();  // q and this step's k, v come from the projection kernel
     if (rg) rg[1] = gtime();
-    const bool fused = p.k_new != nullptr || flagged;
+    const bool fused = p.k_new != nullptr;
     const int rp_of_step = fused ? p.tok_rope[0] : 0;
-    // four dims of a head vector of the projection row, rotated (attention.rs:13-34), from plain or flagged words
-    auto head_vec = [&](const float* plain, size_t off, float (&out4)[4]) {
-        if (!flagged) { load_rotated<4, kHD>(plain + off, 4 * lane, rp_of_step, p.theta, out4); return; }
-        float own[4], other[4];
-        ok = flag_load<4>(p.qkvf + off + 4 * lane, epoch_in, own) && ok;
-        if (rp_of_step == 0) { out4[0] = own[0]; out4[1] = own[1]; out4[2] = own[2]; out4[3] = own[3]; return; }
-        const bool lowhalf = 4 * lane < kHD / 2;
-        ok = flag_load<4>(p.qkvf + off + (lowhalf ? 4 * lane + kHD / 2 : 4 * lane - kHD / 2), epoch_in, other) && ok;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int dd = (4 * lane + i) % (kHD / 2);
-            const float freq = __fdiv_rn(1.0f, powf(p.theta, __fdiv_rn(__fmul_rn(2.0f, (float)dd), (float)kHD)));
-            const float angle = __fmul_rn((float)rp_of_step, freq);
-            const float ca = cosf(angle), sa = sinf(angle);
-            out4[i] = lowhalf ? __fsub_rn(__fmul_rn(own[i], ca), __fmul_rn(other[i], sa))
-                              : __fadd_rn(__fmul_rn(other[i], sa), __fmul_rn(own[i], ca));
-        }
-    };
+    // four dims of a head vector of the projection row, rotated (attention.rs:13-34)
+    auto head_vec = [&](const float* plain, size_t off, float (&out4)[4]) { load_rotated<4, kHD>(plain + off, 4 * lane, rp_of_step, p.theta, out4); };
     // attention.rs:93-102: softmax(dot / sqrt(head_dim)).  Scores are kept multiplied by log2(e) so that every exponential is a
     // single ex2; the running maximum is in the same units and goes back to natural units when a warp's state is written out.
     const float sc_log2e = 1.4426950408889634f / sqrtf((float)kHD);
@@ -274,15 +249,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
                 const int r = pos % kPage;
                 float kr[4];
                 // in the projection row k follows the n_heads query heads and v follows the kv heads of k
-                head_vec(flagged ? nullptr : p.k_new - (size_t)p.n_heads * kHD, (size_t)(p.n_heads + kvh) * kHD, kr);
-                float4 vr;
-                if (flagged) {
-                    float v4[4];
-                    ok = flag_load<4>(p.qkvf + (size_t)(p.n_heads + kv.n_kv + kvh) * kHD + 4 * lane, epoch_in, v4) && ok;
-                    vr = make_float4(v4[0], v4[1], v4[2], v4[3]);
-                } else {
-                    vr = __ldcg(reinterpret_cast<const float4*>(p.v_new + (size_t)kvh * kHD + 4 * lane));
-                }
+                head_vec(p.k_new - (size_t)p.n_heads * kHD, (size_t)(p.n_heads + kvh) * kHD, kr);
+                const float4 vr = __ldcg(reinterpret_cast<const float4*>(p.v_new + (size_t)kvh * kHD + 4 * lane));
                 const __half2 k01 = __floats2half2_rn(kr[0], kr[1]), k23 = __floats2half2_rn(kr[2], kr[3]);
                 const __half2 v01 = __floats2half2_rn(vr.x, vr.y), v23 = __floats2half2_rn(vr.z, vr.w);
                 uint2 kw, vw;
@@ -423,9 +391,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
         const int c_first = (int)(((first + 1) * G - 1) / T), c_last = (int)(((last + 1) * G - 1) / T);
         const int nc = c_last - c_first + 1, me = (int)blockIdx.x - c_first;
         unsigned long long* sl_base = P.slots + (size_t)head * P.max_contrib * (2 + kHD);
-        // validity tag of a slot word: this launch's output epoch in dataflow mode (never cleared: the next use carries
-        // another epoch), else 1 with the collector clearing what it read
-        const unsigned long long tag = flagged ? (unsigned long long)epoch_out : 1ull;
+        // validity tag of a slot word; the collector clears what it read
+        const unsigned long long tag = 1ull;
         auto put = [&](unsigned long long* a, float v) {
             const unsigned long long wv = (tag << 32) | (unsigned long long)__float_as_uint(v);
             asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
@@ -477,7 +444,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
                 L = L * e0 + L_own * e1;
                 M = Mn;
             }
-            if (nc > 1 && !flagged) {
+            if (nc > 1) {
                 for (int c = 0; c < nc - 1; c++)
                     asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + 2 + dx), "l"(0ull) : "memory");
                 asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read the maxima and sums
@@ -485,8 +452,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
                     for (int c = 0; c < nc - 1; c++)
                         asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + dx), "l"(0ull) : "memory");
             }
-            if (flagged) flag_store(p.outf + (size_t)head * kHD + dx, A / L, epoch_out);
-            else p.out[(size_t)head * kHD + dx] = A / L;
+            p.out[(size_t)head * kHD + dx] = A / L;
         }
     }
     if (rg) rg[4] = gtime();
@@ -509,9 +475,6 @@ void dump_aring() {
     }
 }
 
-struct StreamScratch { DevBuf slots; };
-StreamScratch g_stream[16];
-
 int stream_max_contrib(int n_kv) { return sm_count() / n_kv + 3; }
 
 template <int GSZ>
@@ -523,23 +486,19 @@ size_t stream_fixed_smem() {
 }
 
 template <int GSZ>
-int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
-    int dev = 0;
-    LC_CUDA(cudaGetDevice(&dev));
-    LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
+int32_t launch_stream(const AttnParams& a, unsigned long long* slots, cudaStream_t s) {
     StreamParams P;
     P.a = a;
     P.max_contrib = stream_max_contrib(a.kv.n_kv);
-    const size_t need = (size_t)a.n_heads * P.max_contrib * (2 + kHD) * sizeof(unsigned long long);
-    StreamScratch& sc = g_stream[dev];
-    if (sc.slots.cap < need) {
+    P.slots = slots;
+    if (!g_aring && getenv("LC_ATTN_RING")) {  // diagnostics: wall-clock stamps per launch, printed at exit
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-        LC_CUDA(cudaStreamIsCapturing(s, &cs));
-        LC_CHECK(cs == cudaStreamCaptureStatusNone, LC_ERR_STATE,
-                 "attention: the merge slots must be reserved (attention_stream_reserve) before a stream capture");
-        LC_TRY(attention_stream_reserve(a.n_heads, a.kv.n_kv));
+        if (cudaStreamIsCapturing(s, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone &&
+            cudaMalloc(&g_aring, 256 * 16 * sizeof(unsigned long long)) == cudaSuccess) {
+            cudaMemset(g_aring, 0, 256 * 16 * sizeof(unsigned long long));
+            atexit(dump_aring);
+        }
     }
-    P.slots = (unsigned long long*)sc.slots.p;
     static int ring_seq = 0;
     P.ring = g_aring;
     P.ring_slot = ring_seq++ % 256;
@@ -548,12 +507,8 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
     if (stages > 26) stages = 26;
     P.nstages = stages;
     const size_t smem = fixed + (size_t)stages * (kStageBytes + 16);
-    auto kern = a.qkvf ? attention_stream_kernel<GSZ, true> : attention_stream_kernel<GSZ, false>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[a.qkvf ? 1 : 0]) {
-        LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        attr_set[a.qkvf ? 1 : 0] = true;
-    }
+    auto kern = attention_stream_kernel<GSZ>;
+    LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     CUtensorMap ktm, vtm;
     memcpy(&ktm, a.kv.k_tmap, sizeof(ktm));
     memcpy(&vtm, a.kv.v_tmap, sizeof(vtm));
@@ -563,38 +518,23 @@ int32_t launch_stream(const AttnParams& a, cudaStream_t s) {
 
 }  // namespace
 
-int32_t attention_stream_reserve(int n_heads, int n_kv) {
-    if (n_kv <= 0 || n_kv > sm_count()) return LC_OK;
-    int dev = 0;
-    LC_CUDA(cudaGetDevice(&dev));
-    LC_CHECK(dev >= 0 && dev < 16, LC_ERR_INVALID, "device ordinal %d out of range", dev);
-    const size_t need = (size_t)n_heads * stream_max_contrib(n_kv) * (2 + kHD) * sizeof(unsigned long long);
-    StreamScratch& sc = g_stream[dev];
-    if (sc.slots.cap >= need) return LC_OK;
-    LC_CUDA(cudaStreamSynchronize(stream()));
-    LC_TRY(sc.slots.reserve(need));
-    LC_CUDA(cudaMemset(sc.slots.p, 0, sc.slots.cap));  // every word invalid; the kernel leaves them so
-    if (!g_aring && getenv("LC_ATTN_RING")) {
-        LC_CUDA(cudaMalloc(&g_aring, 256 * 16 * sizeof(unsigned long long)));
-        LC_CUDA(cudaMemset(g_aring, 0, 256 * 16 * sizeof(unsigned long long)));
-        atexit(dump_aring);
-    }
-    return LC_OK;
+size_t attention_stream_slot_bytes(int n_heads, int n_kv) {
+    if (n_kv <= 0 || n_kv > sm_count() || n_heads % n_kv != 0) return 0;
+    return (size_t)n_heads * stream_max_contrib(n_kv) * (2 + kHD) * sizeof(unsigned long long);
 }
 
 bool attention_stream_applies(const AttnParams& a, int n_tok) {
-    static const bool off = getenv("LC_ATTN_NO_STREAM") != nullptr;
     const int gsz = a.kv.n_kv > 0 ? a.n_heads / a.kv.n_kv : 0;
-    return !off && a.kv.k_tmap != nullptr && a.kv.v_tmap != nullptr && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
+    return a.kv.k_tmap != nullptr && a.kv.v_tmap != nullptr && n_tok == 1 && a.kv.hd == kHD && !a.kv.kv_f32 && a.kv.page_tokens == kPage && a.kv.n_kv <= sm_count() &&
            (gsz == 1 || gsz == 2 || gsz == 4 || gsz == 8);
 }
 
-int32_t launch_attention_stream(const AttnParams& a, cudaStream_t s) {
+int32_t launch_attention_stream(const AttnParams& a, unsigned long long* slots, cudaStream_t s) {
     switch (a.n_heads / a.kv.n_kv) {
-        case 1: return launch_stream<1>(a, s);
-        case 2: return launch_stream<2>(a, s);
-        case 4: return launch_stream<4>(a, s);
-        default: return launch_stream<8>(a, s);
+        case 1: return launch_stream<1>(a, slots, s);
+        case 2: return launch_stream<2>(a, slots, s);
+        case 4: return launch_stream<4>(a, slots, s);
+        default: return launch_stream<8>(a, slots, s);
     }
 }
 

@@ -3,7 +3,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
+#include <utility>
 #include "lc_common.cuh"
 
 namespace lc {
@@ -55,6 +57,20 @@ int sm_count() {
         g_sms[dev] = v;
     }
     return g_sms[dev];
+}
+
+cudaError_t ensure_smem_limit(const void* kern, size_t bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    static std::map<std::pair<int, const void*>, size_t> done;
+    std::lock_guard<std::mutex> lk(g_rt_mutex);
+    auto key = std::make_pair(dev, kern);
+    auto it = done.find(key);
+    if (it != done.end() && it->second >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) done[key] = bytes;
+    return e;
 }
 
 bool quant_geom(uint32_t typ, QuantGeom* g) {

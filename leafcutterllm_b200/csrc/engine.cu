@@ -17,7 +17,6 @@
 #include "lc_kernels.h"
 #include "lc_synth.h"
 #include "lc_tma.cuh"
-#include "lc_mega.h"
 
 using namespace lc;
 
@@ -86,13 +85,7 @@ struct lc_model {
     int64_t* d_out_tokens = nullptr;
     size_t out_tokens_cap = 0;
     int32_t* d_step_ctr = nullptr;
-    // Dataflow decode step (one sequence, Q4_K layers, streaming attention): the activations between the kernels of a
-    // step travel as flagged words, so no kernel waits for the grid ahead of it.  d_epoch counts decode steps and never
-    // goes back; the advance kernel at the end of every step increments it.
-    unsigned long long *f_hidden = nullptr, *f_hidden2 = nullptr, *f_qkv = nullptr, *f_attn = nullptr, *f_ffn = nullptr;
-    int32_t* d_epoch = nullptr;
-    bool dataflow_ready = false;   // the model qualifies
-    bool dataflow_step = false;    // set while the kernels of such a step are being queued
+    unsigned long long* d_stream_slots = nullptr;  // cross-CTA merge slots of the single-token attention kernel (zero between launches)
     void* d_attn_scratch = nullptr;
     GemmWorkspace gemm_ws;  // f16 activation halves for the many-token tensor-core product
     bool any_unfused_qkv = false;  // some layer's q/k/v differ in type
@@ -107,11 +100,6 @@ struct lc_model {
 
     lc_counters ctr{};
     uint64_t launches_in_call = 0;
-
-    // persistent decode-step kernel (single sequence, Q4_K): parameter block and its device tables
-    bool mega_ready = false;
-    MegaParams mega{};
-    std::vector<void*> mega_bufs;
 
     // What the device-side per-token metadata currently describes (a decode step for these sequences at
     // these cache positions), so that consecutive one-token calls only have to send the token ids.
@@ -183,7 +171,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int32_t*
 // the token is logged.  rope_absolute: rotary position follows the cache position; otherwise it
 // stays the index inside the call (0 for a one-token call, attention.rs:13-21).
 __global__ void advance_kernel(const int64_t* __restrict__ next, int64_t* tokens, int32_t* tok_pos, int32_t* tok_rope, int n,
-                               int rope_absolute, int64_t* out_tokens, int32_t* step_ctr, int32_t* epoch) {
+                               int rope_absolute, int64_t* out_tokens, int32_t* step_ctr) {
     pdl_launch_dependents();
     pdl_wait();
     int i = threadIdx.x;
@@ -195,10 +183,7 @@ __global__ void advance_kernel(const int64_t* __restrict__ next, int64_t* tokens
         if (out_tokens) out_tokens[(size_t)step * n + i] = next[i];
     }
     __syncthreads();
-    if (i == 0) {
-        *step_ctr = step + 1;
-        if (epoch) *epoch = *epoch + 1;  // flagged activations of the next step carry a new epoch
-    }
+    if (i == 0) *step_ctr = step + 1;
 }
 
 int32_t check_model(const lc_model* m, bool need_final) {
@@ -244,49 +229,6 @@ KvLayout kv_layout(const lc_model* m, int layer) {
     return kv;
 }
 
-// Diagnostics: LC_ABLATE is a bit mask of phases to leave out when timing (1 attention, 2 QKV, 4 O, 8 gate/up, 16 down,
-// 32 head).  Results are meaningless with any bit set; it exists to attribute step time to phases.
-static int ablate_mask() {
-    static const int v = getenv("LC_ABLATE") ? atoi(getenv("LC_ABLATE")) : 0;
-    return v;
-}
-
-// Decode steps only: which later weights each of a layer's five kernels (0 QKV, 1 attention, 2 O, 3 gate/up, 4 down)
-// asks the L2 cache to fetch.  Targets: 0 nothing, 1 O, 2 gate + up, 3 down, 4 the next layer's QKV, 5 the next layer's O.
-// A decode kernel is bound by latency, not by bandwidth, so HBM has room for the bytes of the kernel after it; with
-// them in L2 that kernel's tile loads return sooner.  LC_PF="a,b,c,d,e" overrides the table (experiments).
-static L2Prefetch prefetch_for(lc_model* m, int l, int kernel) {
-    static int table[5] = {0, 0, 0, 0, 0};  // off by default: measured slower (the extra reads delay the kernel's own tiles)
-    static bool parsed = false;
-    if (!parsed) {
-        parsed = true;
-        if (const char* e = getenv("LC_PF")) {
-            int v[5] = {0, 0, 0, 0, 0};
-            if (sscanf(e, "%d,%d,%d,%d,%d", &v[0], &v[1], &v[2], &v[3], &v[4]) >= 1)
-                for (int i = 0; i < 5; i++) table[i] = v[i];
-        }
-    }
-    L2Prefetch pf;
-    auto put = [&](int slot, const QWeight& w) {
-        if (w.data && w.typ == LC_TYPE_Q4_K && ((uintptr_t)w.data % 16) == 0) {
-            pf.p[slot] = w.data;
-            pf.bytes[slot] = (unsigned long long)w.n * w.row_bytes;
-        }
-    };
-    const int t = table[kernel];
-    if (t >= 1 && t <= 3) {
-        LayerW& w = m->layers[l];
-        if (t == 1) put(0, w.o);
-        if (t == 2) { put(0, w.gate); put(1, w.up); }
-        if (t == 3) put(0, w.down);
-    } else if ((t == 4 || t == 5) && l + 1 < m->L) {
-        LayerW& w = m->layers[l + 1];
-        if (t == 4 && w.fused_qkv) put(0, w.qkv);
-        if (t == 5) put(0, w.o);
-    }
-    return pf;
-}
-
 int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
     if (qgemm_applies(a, T, m->gemm_ws)) {
         // five tokens and more: one pass over the weights on the tcgen05 tensor cores (activation split + product)
@@ -316,24 +258,14 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     g.x = x;
     g.norm_w = norm_w;
     g.eps = m->cfg.rms_eps;
-    if (decode_step) g.prefetch = prefetch_for(m, l, 0);
-    const bool df = m->dataflow_step;  // one token; nodes of layer l: 5l+1 QKV, +2 attention, +3 O, +4 gate/up, +5 down
-    if (df) {
-        g.step_ctr = m->d_epoch;
-        if (l > 0) { g.x = nullptr; g.x_flag = m->f_hidden; g.node_in = 5 * l; }
-        g.out_flag = m->f_qkv;
-        g.node_out = 5 * l + 1;
-    }
     if (w.fused_qkv) {
         g.w = &w.qkv;
         g.out = m->d_qkv;
-        if (!(ablate_mask() & 2))
         // the fused output is [T, nqkv] only when every token tile writes rows of nqkv floats
         LC_TRY(gemv_tiled(m, g, T, m->nqkv, m->H));
-    } else if (!(ablate_mask() & 2)) {
+    } else {
         // q/k/v of different types: three products.  One token writes straight into its row of d_qkv; several tokens go
         // through contiguous parts and are interleaved into the [T][nq + 2 nkv hd] rows the attention kernels expect.
-        LC_CHECK(!df, LC_ERR_STATE, "dataflow step with unfused projections");
         const int nq = m->nh * m->hd, nkvd = m->nkv * m->hd;
         const QWeight* ws3[3] = {&w.q, &w.k, &w.v};
         const int ns[3] = {nq, nkvd, nkvd};
@@ -355,13 +287,11 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     float* q = m->d_qkv;
     float* k = m->d_qkv + (size_t)m->nh * m->hd;
     float* v = k + (size_t)m->nkv * m->hd;
-    if (ablate_mask() & 1) {
-    } else if (decode_step) {
+    if (decode_step) {
         // one new token per sequence: rotation and the cache append ride inside the attention kernel
         AttnFusion fz{k, v, m->d_tok_rope, m->cfg.rope_theta};
-        fz.prefetch = prefetch_for(m, l, 1);
         fz.positions_settled = l > 0;  // the first layer of a step may run while the previous step still advances the positions
-        if (df) { fz.qkv_flag = m->f_qkv; fz.out_flag = m->f_attn; fz.step_ctr = m->d_epoch; fz.node_in = 5 * l + 1; fz.node_out = 5 * l + 2; }
+        fz.stream_slots = m->d_stream_slots;
         LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
                                 m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, &fz, m->stream));
         m->launches_in_call += 1;
@@ -377,14 +307,6 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     o.x = m->d_attn;
     o.out = out;
     if (residual) { o.residual = residual; o.epi = EPI_ADD_RESIDUAL; }
-    if (decode_step) o.prefetch = prefetch_for(m, l, 2);
-    if (df) {
-        o.step_ctr = m->d_epoch;
-        o.x = nullptr; o.x_flag = m->f_attn; o.node_in = 5 * l + 2;
-        if (residual && l > 0) { o.residual = nullptr; o.residual_flag = m->f_hidden; }  // layer 0 adds the embedding row (plain)
-        o.out_flag = m->f_hidden2; o.node_out = 5 * l + 3;
-    }
-    if (ablate_mask() & 4) return LC_OK;
     if (residual && out == m->d_hidden2 && w.ffn_norm) {  // in a layer of the forward pass the FFN reads `out` next, through its norm
         o.prep_next = true; o.next_norm_w = w.ffn_norm; o.next_eps = m->cfg.rms_eps;
     }
@@ -403,30 +325,15 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     g.eps = m->cfg.rms_eps;
     g.out = m->d_ffn;
     g.epi = EPI_SILU_MUL;
-    if (decode_step) g.prefetch = prefetch_for(m, l, 3);
-    const bool df = m->dataflow_step;
-    if (df) {
-        g.step_ctr = m->d_epoch;
-        g.x = nullptr; g.x_flag = m->f_hidden2; g.node_in = 5 * l + 3;
-        g.out_flag = m->f_ffn; g.node_out = 5 * l + 4;
-    }
-    g.prep_next = !(ablate_mask() & 16);  // the down projection reads d_ffn next, without a norm
+    g.prep_next = true;  // the down projection reads d_ffn next, without a norm
     g.next_norm_w = nullptr;
-    if (!(ablate_mask() & 8)) LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
+    LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
     GemvArgs d;
     d.w = &w.down;
     d.x = m->d_ffn;
     d.out = out;
     if (residual) { d.residual = residual; d.epi = EPI_ADD_RESIDUAL; }
-    if (decode_step) d.prefetch = prefetch_for(m, l, 4);
-    if (df) {
-        d.step_ctr = m->d_epoch;
-        d.x = nullptr; d.x_flag = m->f_ffn; d.node_in = 5 * l + 4;
-        if (residual) { d.residual = nullptr; d.residual_flag = m->f_hidden2; }
-        d.out_flag = m->f_hidden; d.node_out = 5 * l + 5;
-    }
-    if (ablate_mask() & 16) return LC_OK;
-    if (residual && out == m->d_hidden && l + 1 < m->L && m->layers[l + 1].attn_norm && !(ablate_mask() & 2)) {
+    if (residual && out == m->d_hidden && l + 1 < m->L && m->layers[l + 1].attn_norm) {
         // the next layer's q/k/v product(s) read `out` through that layer's attention norm
         d.prep_next = true; d.next_norm_w = m->layers[l + 1].attn_norm; d.next_eps = m->cfg.rms_eps;
     }
@@ -466,8 +373,7 @@ int32_t forward_tokens(lc_model* m, int T, int n_last, bool identity_last, int r
     h.norm_w = m->final_norm;
     h.eps = m->cfg.rms_eps;
     h.out = m->d_logits + (size_t)row0 * m->V;
-    if (m->dataflow_step) { h.x = nullptr; h.x_flag = m->f_hidden; h.step_ctr = m->d_epoch; h.node_in = 5 * m->L; }
-    if (!(ablate_mask() & 32)) LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
+    LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
     LC_TRY(launch_argmax(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->d_next + row0, m->stream));
     m->launches_in_call += 1;
     return LC_OK;
@@ -507,82 +413,6 @@ void finish_call(lc_model* m) {
 
 }  // namespace
 
-// Builds the phase table of the persistent decode kernel when the model qualifies: every matrix Q4_K with a
-// tensor map, head_dim 128, f16 cache.  Anything else keeps the one-kernel-per-phase path.
-static int32_t setup_mega(lc_model* m) {
-    m->mega_ready = false;
-    // Opt-in: at the current state of both paths the one-kernel-per-phase graph is the faster one.
-    if (!getenv("LC_MEGA") || getenv("LC_NO_MEGA")) return LC_OK;
-    if (m->hd != 128 || m->cfg.kv_dtype != 0 || m->H % 256 || m->F % 256) return LC_OK;
-    auto okw = [](const QWeight& w) { return w.typ == LC_TYPE_Q4_K && w.has_tmap; };
-    if (!okw(m->head)) return LC_OK;
-    for (auto& w : m->layers)
-        if (!(w.fused_qkv && okw(w.qkv) && okw(w.o) && okw(w.gate) && okw(w.up) && okw(w.down))) return LC_OK;
-    int max_units = std::max(m->H, std::max(m->F, m->nh * m->hd)) / 256;
-    if (max_units > 64 || decode_mega_smem_bytes(max_units) > kMaxSmem) return LC_OK;
-    int supported = 0;
-    if (cudaDeviceGetAttribute(&supported, cudaDevAttrCooperativeLaunch, m->device) != cudaSuccess || !supported) return LC_OK;
-
-    std::vector<CUtensorMap> tm;
-    std::vector<MegaPhase> ph;
-    auto add_tm = [&](const QWeight& w) { CUtensorMap t; memcpy(&t, w.tmap, sizeof(t)); tm.push_back(t); return (int)tm.size() - 1; };
-    auto gemv = [&](const QWeight& w, const QWeight* w2, const float* x, float* out, const float* res, const float* nw, int epi, int emb) {
-        MegaPhase p{};
-        p.type = PH_GEMV; p.n = w.n; p.k = w.k; p.tm0 = add_tm(w); p.tm1 = w2 ? add_tm(*w2) : -1; p.epi = epi; p.layer = 0;
-        p.reserved = (int)ph.size(); p.x = x; p.out = out; p.residual = res; p.norm_w = nw;
-        ph.push_back(p);
-    };
-    { MegaPhase e{}; e.type = PH_EMBED; e.k = m->H; e.tm1 = -1; ph.push_back(e); }
-    for (int l = 0; l < m->L; l++) {
-        LayerW& w = m->layers[l];
-        gemv(w.qkv, nullptr, m->d_hidden, m->d_qkv, nullptr, w.attn_norm, EPI_STORE, 0);
-        MegaPhase a{}; a.type = PH_ATTN; a.layer = l; a.tm1 = -1; ph.push_back(a);
-        gemv(w.o, nullptr, m->d_attn, m->d_hidden2, m->d_hidden, nullptr, EPI_ADD_RESIDUAL, 0);
-        gemv(w.gate, &w.up, m->d_hidden2, m->d_ffn, nullptr, w.ffn_norm, EPI_SILU_MUL, 0);
-        gemv(w.down, nullptr, m->d_ffn, m->d_hidden, m->d_hidden2, nullptr, EPI_ADD_RESIDUAL, 0);
-    }
-    gemv(m->head, nullptr, m->d_hidden, m->d_logits, nullptr, m->final_norm, EPI_STORE, 0);
-    { MegaPhase a{}; a.type = PH_ARGMAX; a.tm1 = -1; ph.push_back(a); a.type = PH_FINAL; ph.push_back(a); }
-
-    CUtensorMap* d_tm = nullptr; MegaPhase* d_ph = nullptr; void** d_kp = nullptr; void** d_vp = nullptr;
-    long long* d_am = nullptr; unsigned long long* d_bar = nullptr;
-    LC_TRY(dalloc(&d_tm, tm.size())); LC_TRY(dalloc(&d_ph, ph.size())); LC_TRY(dalloc(&d_kp, m->L)); LC_TRY(dalloc(&d_vp, m->L));
-    LC_TRY(dalloc(&d_am, 1024)); LC_TRY(dalloc(&d_bar, 2));
-    m->mega_bufs = {d_tm, d_ph, d_kp, d_vp, d_am, d_bar};
-    LC_CUDA(cudaMemcpyAsync(d_tm, tm.data(), tm.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice, m->stream));
-    LC_CUDA(cudaMemcpyAsync(d_ph, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice, m->stream));
-    LC_CUDA(cudaMemcpyAsync(d_kp, m->k_pools.data(), m->L * sizeof(void*), cudaMemcpyHostToDevice, m->stream));
-    LC_CUDA(cudaMemcpyAsync(d_vp, m->v_pools.data(), m->L * sizeof(void*), cudaMemcpyHostToDevice, m->stream));
-    LC_CUDA(cudaMemsetAsync(d_bar, 0, 16, m->stream));
-    LC_CUDA(cudaStreamSynchronize(m->stream));
-
-    MegaParams& P = m->mega;
-    P.tmaps = d_tm; P.phases = d_ph; P.n_phases = (int)ph.size(); P.max_units = max_units;
-    AttnParams& a = P.attn;
-    a.q = m->d_qkv; a.q_stride = m->nqkv; a.out = m->d_attn; a.n_heads = m->nh; a.kv = kv_layout(m, 0);
-    a.tok_seq = m->d_tok_seq; a.tok_pos = m->d_tok_pos; a.page_table = m->d_page_table; a.pages_per_seq = m->pages_per_seq;
-    a.chunk = 128;  // one key per thread of a 128-thread group
-    a.n_splits = (m->cfg.max_seq_len + 127) / 128;
-    if ((size_t)m->nh * a.n_splits * (m->hd + 2) * sizeof(float) > m->attn_scratch_bytes) return LC_OK;
-    a.partial = (float*)m->d_attn_scratch; a.counters = m->d_attn_counters;
-    a.k_new = m->d_qkv + (size_t)m->nh * m->hd; a.v_new = a.k_new + (size_t)m->nkv * m->hd; a.tok_rope = m->d_tok_rope;
-    a.theta = m->cfg.rope_theta; a.error_flag = gemv_error_flag_dev(); a.positions_settled = 0;
-    P.k_pools = d_kp; P.v_pools = d_vp;
-    P.embed = (const uint8_t*)m->embed->view; P.embed_typ = m->embed->typ; P.embed_rows = (int64_t)m->embed->rows;
-    P.tokens = m->d_tokens; P.hidden = m->d_hidden; P.logits = m->d_logits; P.V = m->V; P.next = m->d_next;
-    P.tok_pos = m->d_tok_pos; P.tok_rope = m->d_tok_rope; P.rope_absolute = m->cfg.rope_mode; P.out_tokens = m->d_out_tokens;
-    P.step_ctr = m->d_step_ctr; P.argmax_scratch = d_am; P.bar = d_bar; P.error_flag = gemv_error_flag_dev(); P.eps = m->cfg.rms_eps;
-    P.trace = nullptr;
-    if (getenv("LC_TRACE")) {
-        unsigned long long* tr = nullptr;
-        LC_TRY(dalloc(&tr, (size_t)4 * ph.size()));
-        m->mega_bufs.push_back(tr);
-        P.trace = tr;
-    }
-    m->mega_ready = P.error_flag != nullptr && sm_count() <= 1024;
-    return LC_OK;
-}
-
 // A bounded wait inside a kernel ran out (TMA transaction or grid barrier): report instead of returning wrong tokens.
 static int32_t check_device_flag(lc_model* m) {
     int* f = gemv_error_flag_dev();
@@ -593,7 +423,7 @@ static int32_t check_device_flag(lc_model* m) {
     if (v != 0) {
         cudaMemsetAsync(f, 0, sizeof(int), m->stream);
         set_error("a device-side check failed (code %d: %s); the results of this call are not valid", v,
-                  v == 2 ? "grid barrier of the persistent decode kernel" : v >= 20 ? "an index outside its range" : "a bounded wait ran out");
+                  v >= 20 ? "an index outside its range" : "a bounded wait ran out");
         return LC_ERR_CUDA;
     }
     return LC_OK;
@@ -783,40 +613,6 @@ int32_t lc_model_finalize(lc_model* m) {
     std::string head = m->tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
     LC_TRY(weight_of(m, head, V, H, &m->head, nullptr));
 
-    LC_TRY(attention_stream_reserve(m->nh, m->nkv));
-    {   // dataflow decode step: every matrix of the step runs on the tensor-core Q4_K kernel, attention on the streaming kernel
-        bool okk = m->L > 0 && 5 * m->L + 2 < (int)kEpochStride && m->hd == 128 && m->cfg.kv_dtype == 0 && m->page_tokens == 16 &&
-                   m->nkv <= sm_count() && m->head.typ == LC_TYPE_Q4_K && m->head.has_tmap && qgemv_mma_supports(H) &&
-                   qgemv_mma_supports(F) && qgemv_mma_supports(nq);
-        const int gsz = m->nh / m->nkv;
-        okk = okk && (gsz == 1 || gsz == 2 || gsz == 4 || gsz == 8);
-        for (int l = 0; l < m->L && okk; l++) {
-            const LayerW& w = m->layers[l];
-            okk = w.fused_qkv && w.qkv.typ == LC_TYPE_Q4_K && w.o.typ == LC_TYPE_Q4_K && w.gate.typ == LC_TYPE_Q4_K &&
-                  w.down.typ == LC_TYPE_Q4_K && w.qkv.has_tmap && w.o.has_tmap && w.gate.has_tmap && w.up.has_tmap && w.down.has_tmap;
-        }
-        if (okk) {
-            LC_TRY(dalloc(&m->f_hidden, (size_t)H)); LC_TRY(dalloc(&m->f_hidden2, (size_t)H)); LC_TRY(dalloc(&m->f_qkv, (size_t)m->nqkv));
-            LC_TRY(dalloc(&m->f_attn, (size_t)nq)); LC_TRY(dalloc(&m->f_ffn, (size_t)F)); LC_TRY(dalloc(&m->d_epoch, 1));
-            LC_CUDA(cudaMemsetAsync(m->f_hidden, 0, (size_t)H * 8, m->stream)); LC_CUDA(cudaMemsetAsync(m->f_hidden2, 0, (size_t)H * 8, m->stream));
-            LC_CUDA(cudaMemsetAsync(m->f_qkv, 0, (size_t)m->nqkv * 8, m->stream)); LC_CUDA(cudaMemsetAsync(m->f_attn, 0, (size_t)nq * 8, m->stream));
-            LC_CUDA(cudaMemsetAsync(m->f_ffn, 0, (size_t)F * 8, m->stream));
-            const int32_t one = 1;  // epoch words of zeroed buffers (0) never match
-            LC_CUDA(cudaMemcpyAsync(m->d_epoch, &one, 4, cudaMemcpyHostToDevice, m->stream));
-            LC_CUDA(cudaStreamSynchronize(m->stream));
-            m->dataflow_ready = true;
-        }
-    }
-    // scratch of the split-tile GEMV, so that no launch inside a captured decode step allocates
-    if (m->L > 0) {
-        const LayerW& w0 = m->layers[0];
-        if (w0.qkv.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(m->nqkv, H, false));
-        if (w0.o.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(H, nq, false));
-        if (w0.gate.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(F, H, true));
-        if (w0.down.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(H, F, false));
-    }
-    if (m->head.typ == LC_TYPE_Q4_K) LC_TRY(qgemv_reserve_scratch(V, H, false));
-
     // weight sanity scan (loader.rs:241-249) and resident byte count
     LC_TRY(dalloc(&m->d_sanity, 1));
     LC_CUDA(cudaMemsetAsync(m->d_sanity, 0, 8, m->stream));
@@ -847,7 +643,14 @@ int32_t lc_model_finalize(lc_model* m) {
             m->k_tmaps_ok = make_key_pool_tmap(m->k_tmaps[l].b, m->k_pools[l], (uint64_t)m->pages_total * m->nkv * m->page_tokens) &&
                             make_key_pool_tmap(m->v_tmaps[l].b, m->v_pools[l], (uint64_t)m->pages_total * m->nkv * m->page_tokens);
     }
-    m->dataflow_ready = m->dataflow_ready && m->k_tmaps_ok;
+    if (m->k_tmaps_ok) {
+        // merge slots of the single-token attention kernel: one set per model, because a captured decode step keeps the pointer
+        const size_t slot_bytes = attention_stream_slot_bytes(m->nh, m->nkv);
+        if (slot_bytes) {
+            LC_TRY(dalloc((uint8_t**)&m->d_stream_slots, slot_bytes));
+            LC_CUDA(cudaMemsetAsync(m->d_stream_slots, 0, slot_bytes, m->stream));
+        }
+    }
     m->free_pages.resize(m->pages_total);
     for (int i = 0; i < m->pages_total; i++) m->free_pages[i] = m->pages_total - 1 - i;
     m->seq_pages.assign(m->max_seqs, {});
@@ -869,7 +672,6 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(dalloc(&m->d_next, m->max_seqs)); LC_TRY(dalloc(&m->d_step_ctr, 1));
     size_t sc = 16;
     for (int t = 1; t <= T; t++) sc = std::max(sc, attention_scratch_bytes(t, m->nh, m->hd, m->cfg.max_seq_len));
-    sc = std::max(sc, (size_t)m->nh * ((m->cfg.max_seq_len + 127) / 128) * (m->hd + 2) * sizeof(float));  // persistent decode kernel: 128-key splits
     m->attn_scratch_bytes = sc;
     LC_TRY(dalloc((uint8_t**)&m->d_attn_scratch, sc));
     LC_TRY(dalloc(&m->d_attn_counters, (size_t)T * m->nh));
@@ -881,7 +683,6 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_CUDA(cudaEventCreate(&m->ev0));
     LC_CUDA(cudaEventCreate(&m->ev1));
     LC_CUDA(cudaStreamSynchronize(m->stream));
-    LC_TRY(setup_mega(m));
     m->finalized = true;
     return LC_OK;
 }
@@ -894,11 +695,9 @@ int32_t lc_model_destroy(lc_model* m) {
     for (auto& kv : m->tensors) if (kv.second.dev) cudaFree(kv.second.dev);
     for (auto& w : m->layers) if (w.fused_buf) cudaFree(w.fused_buf);
     for (void* p : m->owned) cudaFree(p);
-    for (void* p : m->mega_bufs) cudaFree(p);
     for (void* p : m->k_pools) cudaFree(p);
     for (void* p : m->v_pools) cudaFree(p);
-    void* bufs[] = {m->f_hidden, m->f_hidden2, m->f_qkv, m->f_attn, m->f_ffn, m->d_epoch,
-                    m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
+    void* bufs[] = {m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};
     for (void* p : bufs) if (p) cudaFree(p);
@@ -1037,31 +836,16 @@ int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_
 // CUDA graph that later steps replay.
 static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
     auto one_step = [&]() -> int32_t {
-        // Opt-in (LC_DATAFLOW=1): with the one-pass prologue and the tensor-core attention the step with grid waits
-        // measures 1.56 ms and this mode 1.64 ms.  Read when the step is queued (a captured graph keeps its mode).
-        const bool want_dataflow = getenv("LC_DATAFLOW") != nullptr;
-        m->dataflow_step = n_seqs == 1 && m->dataflow_ready && want_dataflow && ablate_mask() == 0;
-        int32_t fs = forward_tokens(m, n_seqs, n_seqs, true, 0);
-        m->dataflow_step = false;
-        LC_TRY(fs);
+        LC_TRY(forward_tokens(m, n_seqs, n_seqs, true, 0));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(std::max(32, (n_seqs + 31) / 32 * 32));
         cfg.stream = m->stream;
         LC_CUDA(cudaLaunchKernelEx(&cfg, advance_kernel, (const int64_t*)m->d_next, m->d_tokens, m->d_tok_pos, m->d_tok_rope, (int)n_seqs,
-                                   (int)m->cfg.rope_mode, m->d_out_tokens, m->d_step_ctr, m->d_epoch));
+                                   (int)m->cfg.rope_mode, m->d_out_tokens, m->d_step_ctr));
         m->launches_in_call += 1;
         return LC_OK;
     };
-    if (n_seqs == 1 && m->mega_ready) {
-        // the whole step is one persistent kernel; one launch per step needs no graph
-        m->mega.out_tokens = m->d_out_tokens;
-        for (int s = 0; s < steps; s++) {
-            LC_TRY(launch_decode_mega(m->mega, m->stream));
-            m->launches_in_call += 1;
-        }
-        return LC_OK;
-    }
     static const bool no_graph = getenv("LC_NO_GRAPH") != nullptr;
     cudaGraphExec_t exec = nullptr;
     int done_steps = 0;
@@ -1226,18 +1010,6 @@ int32_t lc_generate(lc_model* m, const int64_t* tokens, int32_t n, int32_t max_t
         }
     }
     *n_out = count;
-    return LC_OK;
-}
-
-int32_t lc_debug_phase_trace(lc_model* m, uint64_t* out, int32_t max_entries, int32_t* n_phases) {
-    LC_TRY(check_model(m, true));
-    LC_CHECK(out && n_phases, LC_ERR_INVALID, "null output");
-    LC_CHECK(m->mega_ready && m->mega.trace, LC_ERR_STATE, "phase tracing is off (set LC_TRACE=1 before lc_model_finalize)");
-    int n = std::min(max_entries, 4 * m->mega.n_phases);
-    DeviceGuard dg(m->device);
-    LC_CUDA(cudaMemcpyAsync(out, m->mega.trace, (size_t)n * 8, cudaMemcpyDeviceToHost, m->stream));
-    LC_CUDA(cudaStreamSynchronize(m->stream));
-    *n_phases = m->mega.n_phases;
     return LC_OK;
 }
 

@@ -29,18 +29,13 @@ struct AttnParams {
     const int32_t* tok_rope;
     float theta;
     int positions_settled; // decode-step fusion: tok_pos may be read before the grid dependency wait
-    // dataflow mode of the streaming kernel (see AttnFusion): flagged projection row in, flagged output out
-    const unsigned long long* qkvf = nullptr;
-    unsigned long long* outf = nullptr;
-    const int32_t* step_ctr = nullptr;
-    int node_in = 0, node_out = 0;
     int* error_flag;       // set when a bounded wait runs out (may be null)
-    L2Prefetch prefetch;   // weights of the kernels that follow, pulled into L2 by the staged kernel
 };
 
 // attention_stream.cu: one new token, head_dim 128, f16 cache of 16-token pages, as a balanced single-wave stream
 bool attention_stream_applies(const AttnParams& a, int n_tok);
-int32_t launch_attention_stream(const AttnParams& a, cudaStream_t s);
+// slots: attention_stream_slot_bytes(n_heads, n_kv) bytes of zeroed device memory owned by the caller (left zeroed)
+int32_t launch_attention_stream(const AttnParams& a, unsigned long long* slots, cudaStream_t s);
 
 template <int DPL, bool F32>
 __device__ __forceinline__ void load_slice(const void* pool, size_t elem_off, float (&out)[DPL]) {

@@ -55,17 +55,11 @@ struct QWeight {
     size_t row_bytes = 0;
     alignas(64) unsigned char tmap[128];      // CUtensorMap for the TMA-staged kernels: box = one 256-element unit x 32 rows
     alignas(64) unsigned char tmap_wide[128]; // the same tensor with a box of 128 rows (tcgen05 kernel)
-    alignas(64) unsigned char tmap_half[128]; // ... and of 16 rows (finer tiles where they balance the SMs better)
     bool has_tmap = false;
 };
 int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int k);
 
 enum GemvEpilogue { EPI_STORE = 0, EPI_ADD_RESIDUAL = 1, EPI_SILU_MUL = 2 };
-// Bytes a kernel asks the L2 cache to fetch for the kernel that follows it (no effect on results).
-struct L2Prefetch {
-    const void* p[2] = {nullptr, nullptr};
-    unsigned long long bytes[2] = {0, 0};
-};
 struct GemvArgs {
     const QWeight* w = nullptr;   // first matrix
     const QWeight* w2 = nullptr;  // EPI_SILU_MUL: the `up` matrix (w is `gate`)
@@ -76,31 +70,14 @@ struct GemvArgs {
     const float* norm_w = nullptr;    // when set: x is RMS-normalised with this gain before the product
     float eps = 1e-5f;
     GemvEpilogue epi = EPI_STORE;
-    L2Prefetch prefetch;              // honoured by the tensor-core Q4_K kernel
     // Many-token product only: the caller promises that the next product reads `out` (all m rows) as its input with this
     // gain (null: no norm) -- the kernel that sums the shares of k then also prepares that input, saving a launch.
     bool prep_next = false;
     const float* next_norm_w = nullptr;
     float next_eps = 1e-5f;
-    // Dataflow mode (one token, the mma.sync Q4_K kernel): activations travel as flagged words (see flag_store) and
-    // the kernel does not wait for the grid ahead of it.  x_flag replaces x, out_flag replaces out, residual_flag
-    // replaces residual; step_ctr points at the device-side step counter and the node numbers give the epochs
-    // step * kEpochStride + node that the input must carry and the output will carry.
-    const unsigned long long* x_flag = nullptr;
-    unsigned long long* out_flag = nullptr;
-    const unsigned long long* residual_flag = nullptr;
-    const int32_t* step_ctr = nullptr;
-    int node_in = 0, node_out = 0;
 };
-constexpr uint32_t kEpochStride = 1024;  // nodes per step in the epoch numbering
 // y[m,n] = x[m,k] . dequant(W)^T, fp32 activations and accumulation.
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s);
-// Reserves the scratch a later launch_qgemv of an [n x k] matrix may need, so that none is allocated inside a stream
-// capture (two_mats: the gate/up pair of EPI_SILU_MUL).
-int32_t qgemv_reserve_scratch(int n, int k, bool two_mats);
-// Number of kernels launch_qgemv queues for these arguments (for launch accounting).
-int qgemv_launch_count(const GemvArgs& a);
-
 // ---- qgemm_umma.cu ----
 // The same product for many tokens (prefill chunks, batched decode) on tcgen05 tensor cores with the weights
 // dequantised on the fly.  The workspace holds the activations as f16 high/low halves and the per-token scales.
@@ -157,21 +134,17 @@ size_t attention_scratch_bytes(int n_tok, int n_heads, int hd, int max_ctx);
 // step on; false for the first layer, whose positions the end of the previous step may still be writing), so the
 // kernel may read it, and start fetching cached pages, before it waits for the kernel ahead of it.
 struct AttnFusion {
-    const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; L2Prefetch prefetch; bool positions_settled = false;
-    // Dataflow mode (streaming single-token kernel): q, k_new, v_new are read from qkv_flag (the fused projection row as
-    // flagged words, q at 0, k at n_heads*hd, v after k) and the output is written to out_flag; epochs as in GemvArgs.
-    const unsigned long long* qkv_flag = nullptr;
-    unsigned long long* out_flag = nullptr;
-    const int32_t* step_ctr = nullptr;
-    int node_in = 0, node_out = 0;
+    const float* k_new; const float* v_new; const int32_t* tok_rope; float theta; bool positions_settled = false;
+    // Cross-CTA merge slots of the single-token streaming kernel (attention_stream_slot_bytes of them, all zero before the
+    // first launch; the kernel leaves them zero).  They belong to the caller -- one set per model -- because a captured
+    // decode step keeps the pointer.
+    unsigned long long* stream_slots = nullptr;
 };
 int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
                          const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
                          void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);
-int attention_launch_count(int n_tok, int n_heads, int max_ctx);
-// Reserves (and clears) the cross-CTA merge slots of the single-token streaming kernel so that no launch inside a
-// stream capture allocates.
-int32_t attention_stream_reserve(int n_heads, int n_kv);
+// Bytes of merge slots the single-token streaming kernel needs for this head geometry (0: the kernel does not apply).
+size_t attention_stream_slot_bytes(int n_heads, int n_kv);
 
 // ---- synth.cu ----
 int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_elems, void* out_dev,

@@ -67,12 +67,6 @@ struct GemvParams {
     int n, k, m;
     int epi;
     int* error_flag;
-    L2Prefetch prefetch;
-    const unsigned long long* xf = nullptr;   // dataflow mode: flagged input / output / residual (see GemvArgs)
-    unsigned long long* outf = nullptr;
-    const unsigned long long* resf = nullptr;
-    const int32_t* step_ctr = nullptr;
-    int node_in = 0, node_out = 0;
     unsigned long long* ring = nullptr;  // diagnostics (LC_GEMV_RING): 8 wall-clock words of this launch, or null
 };
 
@@ -103,7 +97,5 @@ int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
 bool qgemv_mma_supports(int k);
 // qgemv_kq.cu: Q5_K, Q6_K, F16 and F32, up to eight tokens, plain loads; *launched = false for other types or shapes.
 int32_t launch_qgemv_kq(const GemvArgs& a, cudaStream_t s, bool* launched);
-// qgemv_umma.cu: Q4_K for one or two tokens through tcgen05.mma with accumulators in tensor memory.
-int32_t launch_qgemv_umma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
 
 }  // namespace lc

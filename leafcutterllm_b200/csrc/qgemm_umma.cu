@@ -637,7 +637,7 @@ static int gemm_min_tokens() {
     return v;
 }
 bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws) {
-    if (!a.w || !ws.xh || a.x_flag || a.out_flag || a.residual_flag) return false;
+    if (!a.w || !ws.xh) return false;
     if (a.w->typ != LC_TYPE_Q4_K || !a.w->has_tmap || a.w->k % kUnitElems != 0) return false;
     if (a.epi == EPI_SILU_MUL && (!a.w2 || a.w2->typ != a.w->typ || !a.w2->has_tmap)) return false;
     if (T < gemm_min_tokens() || T > ws.t_cap || a.w->k > ws.k_max) return false;
@@ -657,11 +657,7 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     ws.prep_x = nullptr;
     if (!prepared) {
         const size_t smem = (size_t)K * sizeof(float);
-        static size_t attr_set = 0;
-        if (smem > 48 * 1024 && smem > attr_set) {
-            LC_CUDA(cudaFuncSetAttribute(xprep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr_set = smem;
-        }
+        if (smem > 48 * 1024) LC_CUDA(ensure_smem_limit((const void*)xprep_kernel, smem));
         // a token's row is short (16 - 44 KB) and its three passes are latency: many threads, one or a few float4 each
         // (64 sequences, 4 layers: 2.43 / 2.40 / 2.40 ms per step with 256 / 512 / 1024 threads)
         LC_CUDA(launch_pdl(xprep_kernel, dim3(T), dim3(K >= 4096 ? 1024 : 256), smem, s, a.x, a.norm_w, a.eps, K, (__half*)ws.xh, lo_offset, (__half*)ws.sx,
@@ -690,11 +686,7 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
         p.trace = d_trace;
     }
     const size_t smem = fixed + (size_t)p.b_stages * b_bytes;
-    static size_t attr_set = 0;
-    if (smem > attr_set) {
-        LC_CUDA(cudaFuncSetAttribute(qgemm_umma_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = smem;
-    }
+    LC_CUDA(ensure_smem_limit((const void*)qgemm_umma_q4k_kernel, smem));
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap_wide;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap_wide : t0;
     // Few tiles (a batched decode step on the square matrices): split k over several CTAs so that all SMs work; the
@@ -718,10 +710,6 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
             const int want = nquads >= 3 ? 3 : 2;
             if ((size_t)want * 2 * T * n * sizeof(float) <= ws.partial_bytes) ks = want;
         }
-        if (getenv("LC_GEMM_NO_SPLIT")) ks = 1;
-        if (nmat == 2 && getenv("LC_GEMM_KSPLIT_GU") && T <= 2 * kMaxTok && n % 4 == 0)  // experiments: gate/up only
-            ks = std::max(1, std::min(atoi(getenv("LC_GEMM_KSPLIT_GU")), std::min(8, nquads)));
-        if (getenv("LC_GEMM_KSPLIT") && T <= 2 * kMaxTok && n % 4 == 0) ks = std::max(1, std::min(atoi(getenv("LC_GEMM_KSPLIT")), std::min(8, nquads)));  // experiments
     }
     p.ksplit = ks;
     p.partial = ws.partial;
@@ -729,15 +717,10 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     LC_CUDA(launch_pdl(qgemm_umma_q4k_kernel, grid, dim3(kThreads), smem, s, *t0, *t1, tmx, tms, p));
     if (ks > 1) {
         const size_t plane = (size_t)T * n;
-        static const bool no_fused_prep = getenv("LC_GEMM_NO_FUSED_PREP") != nullptr;
-        if (a.prep_next && !no_fused_prep && n % kUnitElems == 0 && n <= ws.k_max) {
+        if (a.prep_next && n % kUnitElems == 0 && n <= ws.k_max) {
             // one CTA per token sums the shares and prepares the row for the next product, whose k is this n
             const size_t rsmem = (size_t)n * sizeof(float);
-            static size_t rattr = 0;
-            if (rsmem > 48 * 1024 && rsmem > rattr) {
-                LC_CUDA(cudaFuncSetAttribute(qgemm_reduce_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rsmem));
-                rattr = rsmem;
-            }
+            if (rsmem > 48 * 1024) LC_CUDA(ensure_smem_limit((const void*)qgemm_reduce_prep_kernel, rsmem));
             LC_CUDA(launch_pdl(qgemm_reduce_prep_kernel, dim3(T), dim3(n >= 4096 ? 1024 : 256), rsmem, s, (const float*)ws.partial, 2 * ks, T, n,
                                (int)a.epi, a.residual, a.out, a.next_norm_w, a.next_eps, (__half*)ws.xh, (size_t)ws.t_cap * n, (__half*)ws.sx,
                                (size_t)ws.t_cap * (n / 16), ws.tok_scale));

@@ -84,13 +84,6 @@ int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int 
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             w->has_tmap = (r == CUDA_SUCCESS);
         }
-        if (w->has_tmap) {
-            cuuint32_t half[2] = {(cuuint32_t)(ub / 4), 16u};
-            r = encode_fn()((CUtensorMap*)w->tmap_half, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)data_dev, dims, strides, half,
-                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            w->has_tmap = (r == CUDA_SUCCESS);
-        }
     }
     return LC_OK;
 }
@@ -486,13 +479,17 @@ bool pdl_enabled() {
     static const bool on = getenv("LC_NO_PDL") == nullptr;
     return on;
 }
+// The word kernels raise when a bounded wait runs out.  It lives in the library image (zero when the image is loaded on a
+// device), so looking it up allocates nothing: entry points that promise not to allocate can use every kernel.
+static __device__ int g_error_flag_word;
 static int* g_error_flag[16] = {};
 int* gemv_error_flag_dev() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
     if (!g_error_flag[dev]) {
-        if (cudaMalloc(&g_error_flag[dev], sizeof(int)) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
-        cudaMemset(g_error_flag[dev], 0, sizeof(int));
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_error_flag_word) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+        g_error_flag[dev] = (int*)p;
     }
     return g_error_flag[dev];
 }
@@ -512,11 +509,7 @@ template <uint32_t TYPE, int M, int WARPS, int STAGES>
 static int32_t launch_tma_cfg(const GemvArgs& a, cudaStream_t s) {
     auto kern = qgemv_tma_kernel<TYPE, M, WARPS, STAGES>;
     size_t smem = tma_smem_bytes<TYPE, M, WARPS, STAGES>(a.w->k);
-    static bool attr_set = false;
-    if (!attr_set) {
-        LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        attr_set = true;
-    }
+    LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
@@ -567,28 +560,18 @@ static int32_t launch_generic(const GemvArgs& a, cudaStream_t s) {
 static int round_m(int m) { return m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8)); }
 
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
-    LC_CHECK(a.w && (a.x || a.x_flag) && (a.out || a.out_flag), LC_ERR_INVALID, "qgemv: null argument");
-    const bool dataflow = a.x_flag || a.out_flag || a.residual_flag;
+    LC_CHECK(a.w && a.x && a.out, LC_ERR_INVALID, "qgemv: null argument");
     LC_CHECK(a.m >= 1 && a.m <= 8, LC_ERR_INVALID, "qgemv: m=%d outside 1..8", a.m);
     if (a.epi == EPI_SILU_MUL)
         LC_CHECK(a.w2 && a.w2->n == a.w->n && a.w2->k == a.w->k && a.w2->typ == a.w->typ, LC_ERR_INVALID,
                  "qgemv: gate/up matrices differ in shape or type");
-    if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual || a.residual_flag, LC_ERR_INVALID, "qgemv: residual missing");
+    if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual, LC_ERR_INVALID, "qgemv: residual missing");
     bool tma_ok = a.w->has_tmap && (a.epi != EPI_SILU_MUL || a.w2->has_tmap);
     static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
-    // The tcgen05 kernel (qgemv_umma.cu) is opt-in: inside a decode step it ties with the mma.sync kernel on the large
-    // matrices and loses on the small one (its split-tile merge and longer prologue cost more than its leaner loop saves).
-    const bool use_umma = getenv("LC_GEMV_UMMA") != nullptr;  // read per call so that a test can switch it
-    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32 && use_umma && a.m <= 2 && !dataflow) {
+    if (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32) {
         bool launched = false;
-        LC_TRY(launch_qgemv_umma_q4k(a, s, &launched));
+        LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
         if (launched) return LC_OK;
-    }
-    if (dataflow || (tma_ok && a.w->typ == LC_TYPE_Q4_K && !force_fp32)) {
-        bool launched = false;
-        if (tma_ok && a.w->typ == LC_TYPE_Q4_K) LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
-        if (launched) return LC_OK;
-        LC_CHECK(!dataflow, LC_ERR_UNSUPPORTED, "qgemv: flagged activations are only implemented by the Q4_K tensor-core kernel");
     }
     if (tma_ok) {
         for (int mt = round_m(a.m); mt >= 1; mt >>= 1) {
@@ -624,11 +607,6 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
         if (launched) return LC_OK;
     }
     return launch_generic(a, s);
-}
-
-int qgemv_launch_count(const GemvArgs& a) {
-    (void)a;
-    return 1;
 }
 
 }  // namespace lc

@@ -40,11 +40,11 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
     return ((unit * 8 + sb) * M + tok) * 96 + plane * 32;
 }
 
-// RG = 16-row groups per tile (2: 32-row tiles; 1: 16-row tiles, chosen when that spreads the rows more evenly over the SMs).
-template <int M, int WARPS, int STAGES, int RG = 2>
+template <int M, int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p) {
     constexpr int UB = 144;
+    constexpr int RG = 2;        // 16-row MMA groups per tile
     constexpr int TR = 16 * RG;  // rows per tile
     constexpr int STAGE_BYTES = UB * TR;
     constexpr int NPAIR = (M + 1) / 2;
@@ -98,10 +98,6 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         for (int j = 0; j < STAGES && j < njobs; j++) issue_next();  // weights do not depend on the previous kernel
     }
-    if (threadIdx.x == 33) {  // a thread that issues no tile loads
-        l2_prefetch_part(p.prefetch.p[0], p.prefetch.bytes[0], blockIdx.x, gridDim.x);
-        l2_prefetch_part(p.prefetch.p[1], p.prefetch.bytes[1], blockIdx.x, gridDim.x);
-    }
     // One token whose k fits one unit per warp: each warp reads its own 256 elements ONCE, for the sum of squares and for
     // the planes, and the gains (weights: no dependency on the kernel ahead) are already in registers by then.
     const bool one_pass = (M == 1) && p.norm_w != nullptr && nunits <= WARPS;
@@ -112,17 +108,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         nw0[0] = n0.x; nw0[1] = n0.y; nw0[2] = n0.z; nw0[3] = n0.w; nw0[4] = n1.x; nw0[5] = n1.y; nw0[6] = n1.z; nw0[7] = n1.w;
     }
     pdl_launch_dependents();
-    // Dataflow mode: the input words carry the epoch of this step's producer, so the kernel goes ahead as soon as the
-    // producing CTAs have written them instead of waiting for the producing grid (and everything before it) to drain.
-    const bool flagged_in = p.xf != nullptr;
-    uint32_t epoch_in = 0, epoch_out = 0;
-    if (p.step_ctr) {
-        const uint32_t base = (uint32_t)(*p.step_ctr) * kEpochStride;
-        epoch_in = base + (uint32_t)p.node_in;
-        epoch_out = base + (uint32_t)p.node_out;
-    }
-    bool in_ok = true;
-    if (!flagged_in) pdl_wait();
+    pdl_wait();
     if (rg) rg[1] = gtime();
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
@@ -132,14 +118,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         float ss = 0.f;
         if (warp < nunits) {
             const int e0 = warp * kUnitElems + 8 * lane;
-            if (flagged_in) {
-                in_ok = flag_watch_unit(p.xf + warp * kUnitElems, epoch_in) && in_ok;
-                in_ok = flag_load<8>(p.xf + e0, epoch_in, v0) && in_ok;
-            } else {
-                const float4* xp = reinterpret_cast<const float4*>(p.x + e0);
-                const float4 u0 = xp[0], u1 = xp[1];
-                v0[0] = u0.x; v0[1] = u0.y; v0[2] = u0.z; v0[3] = u0.w; v0[4] = u1.x; v0[5] = u1.y; v0[6] = u1.z; v0[7] = u1.w;
-            }
+            const float4* xp = reinterpret_cast<const float4*>(p.x + e0);
+            const float4 u0 = xp[0], u1 = xp[1];
+            v0[0] = u0.x; v0[1] = u0.y; v0[2] = u0.z; v0[3] = u0.w; v0[4] = u1.x; v0[5] = u1.y; v0[6] = u1.z; v0[7] = u1.w;
 #pragma unroll
             for (int j = 0; j < 8; j++) ss = fmaf(v0[j], v0[j], ss);
         }
@@ -154,16 +135,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         for (int tk = 0; tk < M; tk++) {
             float ss = 0.f;
             if (tk < p.m) {
-                if (flagged_in) {
-                    for (int i0 = threadIdx.x; i0 < p.k; i0 += 8 * blockDim.x) {  // eight strided words in flight per thread
-                        float v[8];
-                        in_ok = flag_load_strided<8>(p.xf + i0, (int)blockDim.x, p.k - i0, epoch_in, v) && in_ok;
-#pragma unroll
-                        for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
-                    }
-                } else {
-                    for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = p.x[(size_t)tk * p.k + i]; ss = fmaf(v, v, ss); }
-                }
+                for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = p.x[(size_t)tk * p.k + i]; ss = fmaf(v, v, ss); }
             }
             ss = warp_sum(ss);
             __syncthreads();
@@ -189,14 +161,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[j] = (v0[j] * rms0) * nw0[j];
             } else if (tk < p.m) {
-                if (flagged_in) {
-                    in_ok = flag_watch_unit(p.xf + unit * kUnitElems, epoch_in) && in_ok;
-                    in_ok = flag_load<8>(p.xf + e0, epoch_in, v) && in_ok;
-                } else {
-                    const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);
-                    float4 u0 = xp[0], u1 = xp[1];
-                    v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
-                }
+                const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);
+                float4 u0 = xp[0], u1 = xp[1];
+                v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
                 if (p.norm_w) {
                     const float sc = scratch[32 + tk];
                     const float4* np = reinterpret_cast<const float4*>(p.norm_w + e0);
@@ -410,19 +377,16 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                         have = true;
                     }
                 } else if (row < p.n && tk < p.m) {
-                    if (p.epi == EPI_ADD_RESIDUAL) y = (p.resf ? flag_value(p.resf + row) : p.residual[(size_t)tk * p.n + row]) + y;
+                    if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[(size_t)tk * p.n + row] + y;
                     have = true;
                 }
-                if (have) {
-                    if (p.outf) flag_store(p.outf + row, y, epoch_out);  // dataflow mode is single-token
-                    else p.out[(size_t)tk * p.n + row] = y;
-                }
+                if (have) p.out[(size_t)tk * p.n + row] = y;
             }
         }
     }
     if (rg) rg[3] = gtime();
     if (p.ring && threadIdx.x == 0) atomicMax(p.ring + 6, gtime());  // the last CTA to finish
-    if (!(ok && in_ok) && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
 }
 
 namespace {
@@ -445,10 +409,10 @@ void dump_mring() {
 }
 }  // namespace
 
-template <int M, int WARPS, int STAGES, int RG = 2>
+template <int M, int WARPS, int STAGES>
 static size_t mma_smem_bytes(int k) {
     int nunits = k / kUnitElems;
-    size_t b = (size_t)WARPS * STAGES * 144 * 16 * RG;
+    size_t b = (size_t)WARPS * STAGES * 144 * kTileRows;
     b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * M * 8 * 4 + (size_t)nunits * M * 4;
     b += (size_t)2 * WARPS * M * 32 * 4 + (size_t)M * 32 * 4 + (size_t)(32 + M) * 4;
     b = (b + 7) & ~(size_t)7;
@@ -456,19 +420,14 @@ static size_t mma_smem_bytes(int k) {
     return b;
 }
 
-template <int M, int WARPS, int STAGES, int RG = 2>
+template <int M, int WARPS, int STAGES>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
-    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, RG>;
-    size_t smem = mma_smem_bytes<M, WARPS, STAGES, RG>(a.w->k);
-    static bool attr_set = false;
-    if (!attr_set) {
-        LC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        attr_set = true;
-    }
+    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES>;
+    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k);
+    LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
-    p.prefetch = a.prefetch;
     static const bool want_ring = getenv("LC_GEMV_RING") != nullptr;
     if (want_ring) {
         if (!g_mring) {
@@ -478,15 +437,14 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
         }
         p.ring = g_mring + (size_t)(g_mring_seq++ % 1024) * 8;
     }
-    p.xf = a.x_flag; p.outf = a.out_flag; p.resf = a.residual_flag; p.step_ctr = a.step_ctr; p.node_in = a.node_in; p.node_out = a.node_out;
-    int ntiles = (p.n + 16 * RG - 1) / (16 * RG);
+    int ntiles = (p.n + kTileRows - 1) / kTileRows;
     // CTAs per SM that fit shared memory (and, for the 8-warp shape, registers): with two per SM the
     // first CTAs of the next kernel move in while the last CTAs of this one drain
     int per_sm = (WARPS <= 8 && M <= 2 && 2 * (smem + 1024) <= kMaxSmem + 1024) ? 2 : 1;
     int grid = sm_count() * per_sm;
     if (grid > ntiles) grid = ntiles;
-    const CUtensorMap* t0 = (const CUtensorMap*)(RG == 1 ? a.w->tmap_half : a.w->tmap);
-    const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)(RG == 1 ? a.w2->tmap_half : a.w2->tmap) : t0;
+    const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap;
+    const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap : t0;
     LC_CUDA(launch_pdl(kern, dim3(grid), dim3(WARPS * 32), smem, s, *t0, *t1, p));
     return LC_OK;
 }
@@ -495,21 +453,6 @@ template <int M>
 static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = true;
     int k = a.w->k;
-    static const int cfg = getenv("LC_GEMV_CFG") ? atoi(getenv("LC_GEMV_CFG")) : 0;
-    if constexpr (M <= 2) {
-        if (cfg == 1 && mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2>(a, s);
-        if (cfg == 2 && mma_smem_bytes<M, 8, 4>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 4>(a, s);
-        if (cfg == 3 && mma_smem_bytes<M, 16, 4>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 4>(a, s);
-    }
-    if constexpr (M == 1) {
-        // 16-row tiles where they lower the most rows any SM gets (11008 rows over 148 SMs: 80 instead of 96).  Opt-in:
-        // measured 1.59 ms per decode step against 1.52 ms with 32-row tiles -- twice the per-tile reductions and
-        // barriers cost more than the better balance returns.
-        static const bool half_tiles = getenv("LC_GEMV_HALF_TILES") != nullptr;
-        const int G = sm_count();
-        const int rows32 = ((a.w->n + 31) / 32 + G - 1) / G * 32, rows16 = ((a.w->n + 15) / 16 + G - 1) / G * 16;
-        if (half_tiles && rows16 < rows32 && mma_smem_bytes<1, 16, 4, 1>(k) <= kMaxSmem) return launch_mma_cfg<1, 16, 4, 1>(a, s);
-    }
     if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
         if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2>(a, s);
     }
@@ -524,12 +467,7 @@ bool qgemv_mma_supports(int k) {
 
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = false;
-    const bool dataflow = a.x_flag || a.out_flag || a.residual_flag;
-    if (dataflow) {
-        LC_CHECK(a.m == 1 && a.step_ctr && (!a.x_flag || ((uintptr_t)a.x_flag % 16) == 0), LC_ERR_INVALID,
-                 "qgemv: flagged activations need a single token, the step counter and 16-byte aligned words");
-    }
-    if ((!a.x_flag && ((uintptr_t)a.x % 16) != 0) || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
+    if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
     if (a.m <= 1) return launch_mma_m<1>(a, s, launched);
     if (a.m <= 2) return launch_mma_m<2>(a, s, launched);
     if (a.m <= 4) return launch_mma_m<4>(a, s, launched);

@@ -118,25 +118,6 @@ def test_qmatmul_vs_oracle(gpu, oracle, typ, m, k, n):
     assert_close(got, want, 2e-5 * scale, 1e-4, f"qmatmul typ={typ} {m}x{k}x{n}")
 
 
-@pytest.mark.parametrize("m,k,n", [(1, 256, 128), (1, 4096, 640), (2, 2816, 300), (1, 11008, 256), (2, 4096, 4096)])
-def test_qmatmul_q4k_tensor_memory_kernel(gpu, oracle, monkeypatch, m, k, n):
-    """The opt-in tcgen05 kernel (weights unpacked into tensor memory, work split by 128-row x 256-k blocks with tiles
-    finished across CTAs): one and two tokens, a single k unit, row counts that are not a multiple of 128, more blocks
-    per CTA than k units and fewer."""
-    from leafcutterllm_b200 import synth
-    monkeypatch.setenv("LC_GEMV_UMMA", "1")
-    w = synth.host_tensor(12, 41, f"umma_{k}_{n}", n * k)
-    a = rng(k + n + m).standard_normal(m * k).astype(np.float32)
-    got = gpu.qmatmul(12, a, w, m, k, n)
-    got2 = gpu.qmatmul(12, a, w, m, k, n)  # the split-tile slots are left clean: a second launch gives the same bits
-    want = oracle.qmatmul(12, a, w, m, k, n)
-    assert np.array_equal(got.view(np.uint32), got2.view(np.uint32))
-    assert_close(got, want, 2e-5 * np.abs(want).max(), 1e-4, f"tcgen05 qmatmul {m}x{k}x{n}")
-    monkeypatch.delenv("LC_GEMV_UMMA")
-    ref = gpu.qmatmul(12, a, w, m, k, n)  # the default kernel: same integer arithmetic, different f32 summation order
-    assert_close(got, ref, 2e-6 * np.abs(want).max(), 1e-5, "tcgen05 vs mma.sync kernel")
-
-
 @pytest.mark.parametrize("m,k,n", [(9, 256, 128), (16, 512, 128), (64, 4096, 512), (40, 2816, 300), (130, 1024, 256), (200, 11008, 128)])
 def test_qmatmul_q4k_many_tokens_tensor_core_gemm(gpu, oracle, monkeypatch, m, k, n):
     """Nine tokens and more go through the tcgen05 product (weights dequantised into tensor memory as f16 high/low halves,

@@ -77,8 +77,10 @@ def test_static_scratch_attention_matches_allocating_entry_point(gpu, n_heads, n
             q = r.standard_normal((n_heads, hd)).astype(np.float32)
             qd = d.put(q)
             args = (qd, kd, vd, td, n_pages, ctx, n_heads, n_kv, hd, page_tokens, 0)
-            gpu._capi.check(lib.lc_attention_decode_dev(*args, out_a))
+            # the entry point under test goes first: run alone in a fresh process, it is then the first call of the
+            # process that launches a kernel, so nothing it relies on can have been allocated by an earlier call
             gpu._capi.check(lib.lc_attention_decode_static(*args, out_b))
+            gpu._capi.check(lib.lc_attention_decode_dev(*args, out_a))
             gpu._capi.check(lib.lc_dev_sync())
             a, b = d.get(out_a, (n_heads, hd)), d.get(out_b, (n_heads, hd))
             assert np.abs(a - b).max() <= 1e-6, f"call {call}: the two entry points disagree"
@@ -89,8 +91,8 @@ def test_static_scratch_attention_matches_allocating_entry_point(gpu, n_heads, n
 
 
 def test_static_scratch_rejects_what_does_not_fit(gpu):
-    """128 heads of 256 dims: the split partials (about 660 KB) exceed the 512 KiB array.  Every buffer is real and
-    large enough, so nothing invalid could run whatever the call decides."""
+    """128 heads of 256 dims over 4096 keys: the split partials (about 4 MB) exceed the 1 MiB array.  Every buffer is real
+    and large enough, so nothing invalid could run whatever the call decides."""
     lib = gpu.load()
     n_heads, n_kv, hd, ctx, page_tokens = 128, 1, 256, 4096, 16
     n_pages = ctx // page_tokens
@@ -107,5 +109,34 @@ def test_static_scratch_rejects_what_does_not_fit(gpu):
         gpu._capi.check(lib.lc_attention_decode_dev(qd, kd, vd, td, n_pages, ctx, n_heads, n_kv, hd, page_tokens, 0, out))  # the allocating one takes it
         gpu._capi.check(lib.lc_dev_sync())
         assert lib.lc_attention_decode_static(None, kd, vd, td, n_pages, ctx, n_heads, n_kv, hd, page_tokens, 0, out) == -1
+    finally:
+        d.close()
+
+
+@pytest.mark.parametrize("ctx,accepted", [(7936, True), (7937, False)])
+def test_static_scratch_size_rule_at_its_edge(gpu, ctx, accepted):
+    """32 heads of 128 dims: 62 pieces of 128 keys are the most whose partials fit the array, so a context of 7936 is
+    taken (and agrees with the allocating entry point) and one of 7937 is refused."""
+    lib = gpu.load()
+    n_heads, n_kv, hd, page_tokens = 32, 2, 128, 16
+    n_pages = (ctx + page_tokens - 1) // page_tokens
+    r = np.random.default_rng(ctx)
+    d = Dev(gpu)
+    try:
+        K = r.standard_normal((n_pages, n_kv, page_tokens, hd)).astype(np.float16)
+        V = r.standard_normal((n_pages, n_kv, page_tokens, hd)).astype(np.float16)
+        kd, vd = d.put(K), d.put(V)
+        td = d.put(np.arange(n_pages, dtype=np.int32))
+        qd = d.put(r.standard_normal((n_heads, hd)).astype(np.float32))
+        out_a, out_b = d.empty(n_heads * hd * 4), d.empty(n_heads * hd * 4)
+        args = (qd, kd, vd, td, n_pages, ctx, n_heads, n_kv, hd, page_tokens, 0)
+        rc = lib.lc_attention_decode_static(*args, out_b)
+        if not accepted:
+            assert rc == -1 and b"built-in array" in lib.lc_last_error()
+            return
+        gpu._capi.check(rc)
+        gpu._capi.check(lib.lc_attention_decode_dev(*args, out_a))
+        gpu._capi.check(lib.lc_dev_sync())
+        assert np.abs(d.get(out_a, (n_heads, hd)) - d.get(out_b, (n_heads, hd))).max() <= 1e-6
     finally:
         d.close()
