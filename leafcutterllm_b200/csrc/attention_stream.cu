@@ -75,12 +75,18 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     float* cta_s = st_s + kMaxSeg * kCWarps * GSZ * kStateWords;            // [kMaxSeg][GSZ][kStateWords] combined over warps
     uint64_t* full = reinterpret_cast<uint64_t*>(((uintptr_t)(cta_s + kMaxSeg * GSZ * kStateWords) + 7) & ~(uintptr_t)7);  // [S]
     uint64_t* empty = full + S;                                             // [S]
+    // armed[st] = how many times the producer has armed stage st.  A stage's rounds are consumed by DIFFERENT warps, and a
+    // parity wait cannot tell "round r has not completed" from "round r - 1 has not completed": a warp that reached its
+    // round-r item while the stage's round r - 1 data was still in flight would pass the wait and read the wrong page
+    // (seen with cold caches, when copies requested together land microseconds apart).  So a consumer of round r >= 1
+    // first waits until the producer says it has armed round r -- which it only does after round r - 1 was consumed.
+    volatile int* armed = reinterpret_cast<volatile int*>(empty + S);       // [S]
 
     auto gtime = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
     unsigned long long* rg = (P.ring && tid == 0) ? P.ring + (size_t)P.ring_slot * 16 : nullptr;
     if (rg) { atomicMax(rg + 7, gtime()); if (blockIdx.x == 0) rg[0] = gtime(); else rg = nullptr; }
     if (tid == 0) {
-        for (int s = 0; s < S; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); armed[s] = 0; }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -104,8 +110,9 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     if (warp == kCWarps) {
         // ---- producer: lane i requests items i, i + 32, ... -- each needs a page-table entry from global memory, and one
         //      thread walking them one after the other made that latency, not HBM, the pace of the whole kernel ----
-        // Producing lanes: min(32, S), so that a lane's items all use one stage and a lane only ever waits for the
-        // consumption of its OWN previous item.  With 32 lanes over fewer stages a lane could wait for an item that a lane
+        // Producing lanes: min(32, S) = S (at most 26 stages fit), so that a lane's items all use one stage and a lane only
+        // ever waits for the consumption of its OWN previous item: it has seen every earlier phase of that stage's
+        // `empty` barrier complete, which keeps its parity waits unambiguous.  With 32 lanes over fewer stages a lane could wait for an item that a lane
         // of the same round has yet to request; lanes that need no wait can be held at the reconvergence point behind the
         // waiting ones, and then nobody requests it.
         const int PL = S < 32 ? S : 32;
@@ -122,6 +129,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
             tma_load_2d(dst + kKHalf, &ktm, 64, y, &full[st]);
             tma_load_2d(dst + 2 * kKHalf, &vtm, 0, y, &full[st]);
             tma_load_2d(dst + 3 * kKHalf, &vtm, 64, y, &full[st]);
+            __threadfence_block();      // the arming above is visible before the count below
+            armed[st] = i / S + 1;
         }
         if (!ok && p.error_flag) atomicExch(p.error_flag, 1);
         return;  // the producer takes no part in the barriers below (they count the consumer threads)
@@ -220,13 +229,13 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
 
     // this warp's items: il = warp, warp + kCWarps, ...; their kv head, page, stage and stage phase follow without divisions
     int kvh_i = n_items > 0 ? (i_begin + warp) / np : 0, page_i = n_items > 0 ? (i_begin + warp) - kvh_i * np : 0;
-    int st_i = warp % S, par_i = (warp / S) & 1;
+    int st_i = warp % S, rnd_i = warp / S;
     for (int il = warp; il < n_items; il += kCWarps) {
-        const int kvh = kvh_i, page = page_i, st = st_i, st_par = par_i;
+        const int kvh = kvh_i, page = page_i, st = st_i, rnd = rnd_i, st_par = rnd_i & 1;
         page_i += kCWarps;
         while (page_i >= np) { page_i -= np; kvh_i++; }
         st_i += kCWarps;
-        while (st_i >= S) { st_i -= S; par_i ^= 1; }
+        while (st_i >= S) { st_i -= S; rnd_i++; }
         if (kvh != cur_seg) {
             if (cur_seg >= 0) flush(cur_seg);
             reset();
@@ -237,6 +246,12 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
                 for (int i = 0; i < 16; i++) qf[nt][i >> 1][i & 1] = qf_s[(((size_t)(kvh - seg0) * NTc + nt) * 16 + i) * 32 + lane];
         }
         if (rg && il == warp) rg[8] = clock64() - loop0;
+        if (rnd > 0) {  // see `armed`: wait until this round of the stage has been armed (bounded)
+            bool seen = false;
+            for (uint32_t it = 0; it < (1u << 24) && !seen; ++it) seen = armed[st] > rnd;
+            __threadfence_block();
+            ok = ok && seen;
+        }
         ok = mbar_wait(&full[st], (uint32_t)st_par) && ok;
         if (rg && il == warp) rg[9] = clock64() - loop0;
         unsigned char* K_b = ring + (size_t)st * kStageBytes;           // two swizzled boxes: dims 0-63, dims 64-127
@@ -503,10 +518,10 @@ int32_t launch_stream(const AttnParams& a, unsigned long long* slots, cudaStream
     P.ring = g_aring;
     P.ring_slot = ring_seq++ % 256;
     const size_t fixed = stream_fixed_smem<GSZ>();
-    int stages = (int)((kMaxSmem - fixed) / (kStageBytes + 16));
+    int stages = (int)((kMaxSmem - fixed) / (kStageBytes + 20));
     if (stages > 26) stages = 26;
     P.nstages = stages;
-    const size_t smem = fixed + (size_t)stages * (kStageBytes + 16);
+    const size_t smem = fixed + (size_t)stages * (kStageBytes + 20);
     auto kern = attention_stream_kernel<GSZ>;
     LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     CUtensorMap ktm, vtm;

@@ -60,6 +60,19 @@ struct QWeight {
 int32_t qweight_init(QWeight* w, uint32_t typ, const void* data_dev, int n, int k);
 
 enum GemvEpilogue { EPI_STORE = 0, EPI_ADD_RESIDUAL = 1, EPI_SILU_MUL = 2 };
+// The experts of one mixture-of-experts layer as ONE product launch (Q4_K experts of equal shape).  The router leaves,
+// per expert, how many (token, choice) slots it received and their list (slot = token * top_k + choice, ascending);
+// the product of expert e reads the input row of each of its slots (row slot / top_k when x_by_token, else row slot)
+// and writes the result to row `slot` of out.  All pointers are device memory.
+struct GemvGroup {
+    const void* tmaps = nullptr;    // [n_experts] tensor maps (128 bytes each) of the first matrix
+    const void* tmaps2 = nullptr;   // EPI_SILU_MUL: those of the `up` matrices
+    const int32_t* counts = nullptr;
+    const int32_t* lists = nullptr; // [n_experts][list_stride]
+    int list_stride = 0, n_experts = 0, top_k = 0;
+    int max_tokens = 0;             // most slots any expert can receive in this call (= tokens of the call)
+    bool x_by_token = false;
+};
 struct GemvArgs {
     const QWeight* w = nullptr;   // first matrix
     const QWeight* w2 = nullptr;  // EPI_SILU_MUL: the `up` matrix (w is `gate`)
@@ -70,6 +83,7 @@ struct GemvArgs {
     const float* norm_w = nullptr;    // when set: x is RMS-normalised with this gain before the product
     float eps = 1e-5f;
     GemvEpilogue epi = EPI_STORE;
+    const GemvGroup* group = nullptr;  // set: w / w2 only give the experts' common shape and type
     // Many-token product only: the caller promises that the next product reads `out` (all m rows) as its input with this
     // gain (null: no norm) -- the kernel that sums the shares of k then also prepares that input, saving a launch.
     bool prep_next = false;
@@ -145,6 +159,31 @@ int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, in
                          void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);
 // Bytes of merge slots the single-token streaming kernel needs for this head geometry (0: the kernel does not apply).
 size_t attention_stream_slot_bytes(int n_heads, int n_kv);
+
+// ---- moe.cu ----
+constexpr int kMaxExperts = 64;
+constexpr int kMaxTopK = 8;
+struct MoeRouteArgs {
+    const float* x = nullptr;         // [T, H] the FFN input before its norm
+    const float* norm_w = nullptr;    // FFN norm gain (null: x is used as it is)
+    float eps = 1e-5f;
+    int H = 0, T = 0;
+    const float* w_router = nullptr;  // [n_experts, H] f32
+    int n_experts = 0, top_k = 0;
+    int32_t* sel = nullptr;           // [T, top_k] chosen experts, ascending
+    float* wsel = nullptr;            // [T, top_k] their softmax weights
+    // calls of at most 64 tokens may also ask for the experts' slot lists (see GemvGroup); `touched` (optional) is
+    // increased by the number of experts that received at least one slot
+    int32_t* counts = nullptr;
+    int32_t* lists = nullptr;
+    int list_stride = 0;
+    unsigned long long* touched = nullptr;
+};
+int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s);
+// out[t] = residual[t] + sum_j wsel[t][j] * y[row(t, j)] in ascending expert order; mode 0: row = t * top_k + j,
+// mode 1: row = sel[t][j] * t_stride + t (every expert's outputs for every token, a plane of t_stride rows per expert)
+int32_t launch_moe_combine(const float* y, const int32_t* sel, const float* wsel, int top_k, int H, int T, int mode, size_t t_stride,
+                           const float* residual, float* out, cudaStream_t s);
 
 // ---- synth.cu ----
 int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_elems, void* out_dev,

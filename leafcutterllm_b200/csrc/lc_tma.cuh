@@ -69,7 +69,14 @@ struct GemvParams {
     int* error_flag;
     unsigned long long* ring = nullptr;  // diagnostics (LC_GEMV_RING): 8 wall-clock words of this launch, or null
 };
-
+// Expert grouping of one launch (device pointers; see GemvGroup): all zero for a plain product.
+struct GemvGroupParams {
+    const CUtensorMap* tm0;
+    const CUtensorMap* tm1;
+    const int32_t* cnt;
+    const int32_t* list;
+    int list_stride, top_k, x_by_token, passes;
+};
 
 // Launch with the programmatic-dependent-launch attribute (off when LC_NO_PDL is set).
 bool pdl_enabled();
@@ -93,6 +100,7 @@ constexpr size_t kMaxSmem = 227 * 1024;
 
 // qgemv_mma.cu: Q4_K through int8 tensor-core MMAs; *launched = false when the shape does not fit.
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched);
+int32_t launch_qgemv_mma_q4k_grouped(const GemvArgs& a, cudaStream_t s, bool* launched);
 // true when the single-token kernel fits shared memory for rows of k elements
 bool qgemv_mma_supports(int k);
 // qgemv_kq.cu: Q5_K, Q6_K, F16 and F32, up to eight tokens, plain loads; *launched = false for other types or shapes.

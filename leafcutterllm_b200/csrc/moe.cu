@@ -1,0 +1,156 @@
+// Mixture-of-experts routing for the FFN position of a decoder layer.  The reference has dense FFNs only
+// (rust/src/inference/engine.rs:146-164); the definition implemented here is this project's own and is the one the
+// CPU checker restates:
+//   router logits = rms_norm(x) . W_r^T with f32 router weights;
+//   the top_k experts by logit, equal logits going to the HIGHER expert index (the tie rule of the reference's
+//   greedy pick, rust/src/inference/sampler.rs:6-10);
+//   gate weights = softmax over the selected logits;
+//   output = residual + sum over the selected experts, in ascending expert index, of weight * expert_ffn(rms_norm(x)).
+//
+// moe_route_kernel   one CTA per block of 64 tokens: RMS scale per token, one warp per (token, expert) dot product,
+//                    one thread per token picks and weighs, and -- when the whole call fits one block -- expert e's
+//                    thread lists the (token, choice) slots it received, in token order, for the grouped expert product.
+// moe_combine_kernel out[t] = residual[t] + sum_j w[t][j] * y[row(t, j)], j in ascending expert order.
+#include "lc_kernels.h"
+
+namespace lc {
+
+namespace {
+
+constexpr int kRouteTokens = 64;   // tokens per CTA of the router
+constexpr int kRouteThreads = 1024;
+
+__device__ __forceinline__ int32_t total_key_f(float f) {  // orders f32 bit patterns like Rust's f32::total_cmp
+    int32_t b = __float_as_int(f);
+    return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1);
+}
+
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int H, int T, const float* __restrict__ w_router,
+                 int E, int K, int32_t* __restrict__ sel, float* __restrict__ wsel, int32_t* __restrict__ cnt, int32_t* __restrict__ lists,
+                 int list_stride, unsigned long long* __restrict__ touched) {
+    __shared__ float scale_s[kRouteTokens];
+    __shared__ float logit_s[kRouteTokens * kMaxExperts];
+    __shared__ int sel_s[kRouteTokens * kMaxTopK];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int t0 = blockIdx.x * kRouteTokens, nt = min(kRouteTokens, T - t0);
+    for (int t = warp; t < nt; t += nwarps) {  // cpu.rs:49-60: 1 / sqrt(mean(x^2) + eps)
+        const float* xr = x + (size_t)(t0 + t) * H;
+        float ss = 0.f;
+        for (int i = lane; i < H; i += 32) ss = fmaf(xr[i], xr[i], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) scale_s[t] = norm_w ? 1.0f / sqrtf(ss / (float)H + eps) : 1.0f;
+    }
+    __syncthreads();
+    for (int pe = warp; pe < nt * E; pe += nwarps) {
+        const int t = pe / E, e = pe - t * E;
+        const float* xr = x + (size_t)(t0 + t) * H;
+        const float* wr = w_router + (size_t)e * H;
+        const float sc = scale_s[t];
+        float acc = 0.f;
+        for (int i = lane; i < H; i += 32) {
+            const float xn = norm_w ? (xr[i] * sc) * norm_w[i] : xr[i];
+            acc = fmaf(xn, wr[i], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) logit_s[t * kMaxExperts + e] = acc;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < nt) {
+        const int t = threadIdx.x;
+        const float* lg = logit_s + t * kMaxExperts;
+        unsigned long long used = 0ull;
+        for (int kk = 0; kk < K; kk++) {
+            int best = -1;
+            for (int e = 0; e < E; e++) {
+                if ((used >> e) & 1ull) continue;
+                if (best < 0 || total_key_f(lg[e]) >= total_key_f(lg[best])) best = e;  // ties: the later index wins
+            }
+            used |= 1ull << best;
+        }
+        float mx = -INFINITY;
+        for (int e = 0; e < E; e++) if ((used >> e) & 1ull) mx = fmaxf(mx, lg[e]);
+        float sum = 0.f;
+        for (int e = 0; e < E; e++) if ((used >> e) & 1ull) sum = sum + expf(lg[e] - mx);
+        int j = 0;
+        for (int e = 0; e < E; e++) {
+            if (!((used >> e) & 1ull)) continue;
+            sel[(size_t)(t0 + t) * K + j] = e;                       // ascending expert index
+            wsel[(size_t)(t0 + t) * K + j] = expf(lg[e] - mx) / sum;
+            sel_s[t * kMaxTopK + j] = e;
+            j++;
+        }
+    }
+    if (lists == nullptr) return;   // many-token calls run every expert on every token and only need sel / wsel
+    __syncthreads();
+    if ((int)threadIdx.x < E) {
+        const int e = threadIdx.x;
+        int n = 0;
+        for (int t = 0; t < nt; t++)
+            for (int j = 0; j < K; j++)
+                if (sel_s[t * kMaxTopK + j] == e) lists[(size_t)e * list_stride + n++] = (t0 + t) * K + j;
+        cnt[e] = n;
+        if (touched && n > 0) atomicAdd(touched, 1ull);
+    }
+}
+
+// mode 0: row(t, j) = t * K + j (one row per slot); mode 1: row(t, j) = sel[t][j] * T_stride + t (a plane per expert)
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ sel, const float* __restrict__ wsel, int K, int H, int T,
+                                   int mode, size_t t_stride, const float* __restrict__ residual, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i4 = threadIdx.x; i4 < H / 4; i4 += blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < K; j++) {
+            const size_t row = mode == 0 ? (size_t)t * K + j : (size_t)sel[(size_t)t * K + j] * t_stride + t;
+            const float w = wsel[(size_t)t * K + j];
+            const float4 v = *reinterpret_cast<const float4*>(y + row * H + 4 * (size_t)i4);
+            acc.x = acc.x + w * v.x; acc.y = acc.y + w * v.y; acc.z = acc.z + w * v.z; acc.w = acc.w + w * v.w;
+        }
+        if (residual) {
+            const float4 r = *reinterpret_cast<const float4*>(residual + (size_t)t * H + 4 * (size_t)i4);
+            acc.x = r.x + acc.x; acc.y = r.y + acc.y; acc.z = r.z + acc.z; acc.w = r.w + acc.w;
+        }
+        *reinterpret_cast<float4*>(out + (size_t)t * H + 4 * (size_t)i4) = acc;
+    }
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+}  // namespace
+
+int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s) {
+    LC_CHECK(a.x && a.w_router && a.sel && a.wsel && a.T >= 1 && a.H >= 1, LC_ERR_INVALID, "moe route: null argument");
+    LC_CHECK(a.n_experts >= 1 && a.n_experts <= kMaxExperts && a.top_k >= 1 && a.top_k <= kMaxTopK && a.top_k <= a.n_experts, LC_ERR_INVALID,
+             "moe route: %d experts / top %d outside 1..%d / 1..%d", a.n_experts, a.top_k, kMaxExperts, kMaxTopK);
+    const bool want_lists = a.lists != nullptr;
+    if (want_lists) LC_CHECK(a.T <= kRouteTokens && a.counts && a.list_stride >= a.T, LC_ERR_INVALID, "moe route: slot lists need a call of at most %d tokens", kRouteTokens);
+    const unsigned grid = (unsigned)((a.T + kRouteTokens - 1) / kRouteTokens);
+    LC_CUDA(launch_dep(moe_route_kernel, dim3(grid), dim3(kRouteThreads), s, a.x, a.norm_w, a.eps, a.H, a.T, a.w_router, a.n_experts, a.top_k, a.sel,
+                       a.wsel, a.counts, a.lists, a.list_stride, a.touched));
+    return LC_OK;
+}
+
+int32_t launch_moe_combine(const float* y, const int32_t* sel, const float* wsel, int top_k, int H, int T, int mode, size_t t_stride,
+                           const float* residual, float* out, cudaStream_t s) {
+    LC_CHECK(y && sel && wsel && out && H % 4 == 0 && T >= 1, LC_ERR_INVALID, "moe combine: bad argument");
+    LC_CUDA(launch_dep(moe_combine_kernel, dim3((unsigned)T), dim3(256), s, y, sel, wsel, top_k, H, T, mode, t_stride, residual, out));
+    return LC_OK;
+}
+
+}  // namespace lc

@@ -40,15 +40,43 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
     return ((unit * 8 + sb) * M + tok) * 96 + plane * 32;
 }
 
-template <int M, int WARPS, int STAGES>
+// GROUPED: one launch over the experts of a mixture-of-experts layer.  blockIdx.y = expert * passes + pass; the CTA
+// reads how many tokens the router sent to its expert and leaves at once when its pass has none, takes the expert's
+// tensor maps from a device array, gathers its (up to M) input rows through the expert's slot list and writes each
+// result row to its slot.  The plain instantiation carries none of this.
+template <int M, int WARPS, int STAGES, bool GROUPED = false>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
-qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p) {
+qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p, GemvGroupParams gp) {
     constexpr int UB = 144;
+    const CUtensorMap* t0p = &tm0;
+    const CUtensorMap* t1p = &tm1;
+    int m_act = p.m;
+    extern __shared__ __align__(128) unsigned char smem[];
+    int* s_slot = reinterpret_cast<int*>(smem);  // GROUPED: the first 64 bytes of shared memory hold the CTA's slots
+    if constexpr (GROUPED) {
+        pdl_launch_dependents();
+        pdl_wait();  // the router's counts and lists come from the kernel ahead
+        const int e = blockIdx.y / gp.passes, pass = blockIdx.y - e * gp.passes;
+        m_act = min(M, gp.cnt[e] - pass * M);
+        if (m_act <= 0) return;
+        t0p = gp.tm0 + e;
+        t1p = gp.tm1 + e;
+        if (threadIdx.x < M) s_slot[threadIdx.x] = (int)threadIdx.x < m_act ? gp.list[(size_t)e * gp.list_stride + pass * M + threadIdx.x] : 0;
+        __syncthreads();
+    }
+    // row of x / of out that token slot tk of this CTA reads / writes
+    auto xrow = [&](int tk) -> const float* {
+        if constexpr (GROUPED) return p.x + (size_t)(gp.x_by_token ? s_slot[tk] / gp.top_k : s_slot[tk]) * p.k;
+        else return p.x + (size_t)tk * p.k;
+    };
+    auto orow = [&](int tk) -> size_t {
+        if constexpr (GROUPED) return (size_t)s_slot[tk] * p.n;
+        else return (size_t)tk * p.n;
+    };
     constexpr int RG = 2;        // 16-row MMA groups per tile
     constexpr int TR = 16 * RG;  // rows per tile
     constexpr int STAGE_BYTES = UB * TR;
     constexpr int NPAIR = (M + 1) / 2;
-    extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int nunits = p.k / kUnitElems;
@@ -61,8 +89,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         atomicMax(p.ring + 7, gtime());  // the last CTA to start
         if (blockIdx.x == 0) { rg = p.ring; rg[0] = gtime(); rg[5] = ((unsigned long long)p.n << 32) | (unsigned)p.k; }
     }
-    unsigned char* stage_base = smem + (size_t)warp * STAGES * STAGE_BYTES;
-    size_t off = (size_t)WARPS * STAGES * STAGE_BYTES;
+    constexpr size_t kHead = GROUPED ? 128 : 0;  // keeps the stages 128-byte aligned behind the slots
+    unsigned char* stage_base = smem + kHead + (size_t)warp * STAGES * STAGE_BYTES;
+    size_t off = kHead + (size_t)WARPS * STAGES * STAGE_BYTES;
     unsigned char* planes = smem + off;                          // [nunits][8][M][3][32] int8
     off += (size_t)nunits * 8 * M * 96;
     float* sxf = reinterpret_cast<float*>(smem + off);           // [nunits][M][8]: sum of x over each sub-block
@@ -86,7 +115,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     auto issue_next = [&]() {
         const int st = pj & (STAGES - 1);
         mbar_expect_tx(&bars[st], STAGE_BYTES);
-        tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, p_mat ? &tm1 : &tm0, (warp + p_ui * WARPS) * (UB / 4),
+        tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, p_mat ? t1p : t0p, (warp + p_ui * WARPS) * (UB / 4),
                     (blockIdx.x + p_ti * gridDim.x) * TR, &bars[st]);
         pj++;
         if (++p_ui == units_mine) { p_ui = 0; if (++p_mat == nmat) { p_mat = 0; ++p_ti; } }
@@ -107,8 +136,10 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         const float4 n0 = np[0], n1 = np[1];
         nw0[0] = n0.x; nw0[1] = n0.y; nw0[2] = n0.z; nw0[3] = n0.w; nw0[4] = n1.x; nw0[5] = n1.y; nw0[6] = n1.z; nw0[7] = n1.w;
     }
-    pdl_launch_dependents();
-    pdl_wait();
+    if constexpr (!GROUPED) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
     if (rg) rg[1] = gtime();
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
@@ -118,7 +149,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         float ss = 0.f;
         if (warp < nunits) {
             const int e0 = warp * kUnitElems + 8 * lane;
-            const float4* xp = reinterpret_cast<const float4*>(p.x + e0);
+            const float4* xp = reinterpret_cast<const float4*>(xrow(0) + e0);
             const float4 u0 = xp[0], u1 = xp[1];
             v0[0] = u0.x; v0[1] = u0.y; v0[2] = u0.z; v0[3] = u0.w; v0[4] = u1.x; v0[5] = u1.y; v0[6] = u1.z; v0[7] = u1.w;
 #pragma unroll
@@ -134,8 +165,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     } else if (p.norm_w) {
         for (int tk = 0; tk < M; tk++) {
             float ss = 0.f;
-            if (tk < p.m) {
-                for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = p.x[(size_t)tk * p.k + i]; ss = fmaf(v, v, ss); }
+            if (tk < m_act) {
+                const float* xr = xrow(tk);
+                for (int i = threadIdx.x; i < p.k; i += blockDim.x) { float v = xr[i]; ss = fmaf(v, v, ss); }
             }
             ss = warp_sum(ss);
             __syncthreads();
@@ -160,8 +192,8 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             if (one_pass) {
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[j] = (v0[j] * rms0) * nw0[j];
-            } else if (tk < p.m) {
-                const float4* xp = reinterpret_cast<const float4*>(p.x + (size_t)tk * p.k + e0);
+            } else if (tk < m_act) {
+                const float4* xp = reinterpret_cast<const float4*>(xrow(tk) + e0);
                 float4 u0 = xp[0], u1 = xp[1];
                 v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
                 if (p.norm_w) {
@@ -372,15 +404,15 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 if (p.epi == EPI_SILU_MUL) {
                     if (mat == 0) {
                         gate_vals[tk * 32 + lane] = y;
-                    } else if (row < p.n && tk < p.m) {
+                    } else if (row < p.n && tk < m_act) {
                         y = silu_f(gate_vals[tk * 32 + lane]) * y;
                         have = true;
                     }
-                } else if (row < p.n && tk < p.m) {
-                    if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[(size_t)tk * p.n + row] + y;
+                } else if (row < p.n && tk < m_act) {
+                    if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[orow(tk) + row] + y;
                     have = true;
                 }
-                if (have) p.out[(size_t)tk * p.n + row] = y;
+                if (have) p.out[orow(tk) + row] = y;
             }
         }
     }
@@ -417,12 +449,12 @@ static size_t mma_smem_bytes(int k) {
     b += (size_t)2 * WARPS * M * 32 * 4 + (size_t)M * 32 * 4 + (size_t)(32 + M) * 4;
     b = (b + 7) & ~(size_t)7;
     b += (size_t)WARPS * STAGES * 8;
-    return b;
+    return b + 128;  // head room for the slot words of the grouped form
 }
 
-template <int M, int WARPS, int STAGES>
+template <int M, int WARPS, int STAGES, bool GROUPED = false>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
-    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES>;
+    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, GROUPED>;
     size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k);
     LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
@@ -445,7 +477,16 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     if (grid > ntiles) grid = ntiles;
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap : t0;
-    LC_CUDA(launch_pdl(kern, dim3(grid), dim3(WARPS * 32), smem, s, *t0, *t1, p));
+    GemvGroupParams gp{};
+    unsigned gy = 1;
+    if constexpr (GROUPED) {
+        const GemvGroup& g = *a.group;
+        gp.tm0 = (const CUtensorMap*)g.tmaps; gp.tm1 = (const CUtensorMap*)(g.tmaps2 ? g.tmaps2 : g.tmaps);
+        gp.cnt = g.counts; gp.list = g.lists; gp.list_stride = g.list_stride; gp.top_k = g.top_k; gp.x_by_token = g.x_by_token ? 1 : 0;
+        gp.passes = (g.max_tokens + M - 1) / M;
+        gy = (unsigned)(g.n_experts * gp.passes);
+    }
+    LC_CUDA(launch_pdl(kern, dim3(grid, gy), dim3(WARPS * 32), smem, s, *t0, *t1, p, gp));
     return LC_OK;
 }
 
@@ -463,6 +504,26 @@ static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
 
 bool qgemv_mma_supports(int k) {
     return k > 0 && k % kUnitElems == 0 && (mma_smem_bytes<1, 16, 2>(k) <= kMaxSmem || mma_smem_bytes<1, 8, 2>(k) <= kMaxSmem);
+}
+
+// One launch over the experts of a layer (see the kernel's GROUPED note).  Token tile = the smallest of 1, 2, 4, 8 that
+// holds the call's tokens; more than eight tokens make several passes per expert.
+template <int M, int WARPS>
+static int32_t launch_grouped_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
+    if (mma_smem_bytes<M, WARPS, 2>(a.w->k) > kMaxSmem) return LC_OK;
+    *launched = true;
+    return launch_mma_cfg<M, WARPS, 2, true>(a, s);
+}
+int32_t launch_qgemv_mma_q4k_grouped(const GemvArgs& a, cudaStream_t s, bool* launched) {
+    *launched = false;
+    const GemvGroup* g = a.group;
+    LC_CHECK(g && g->tmaps && g->counts && g->lists && g->n_experts > 0 && g->max_tokens > 0 && g->top_k > 0 && !a.residual, LC_ERR_INVALID,
+             "grouped qgemv: incomplete expert group");
+    if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
+    if (g->max_tokens <= 1) return launch_grouped_m<1, 16>(a, s, launched);
+    if (g->max_tokens <= 2) return launch_grouped_m<2, 16>(a, s, launched);
+    if (g->max_tokens <= 4) return launch_grouped_m<4, 16>(a, s, launched);
+    return launch_grouped_m<8, 8>(a, s, launched);
 }
 
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) {

@@ -35,6 +35,35 @@ def test_config1_full_depth_matches_the_oracle_fixture(gpu):
     eng.close()
 
 
+def test_config2_two_layers_matches_the_oracle_fixture(gpu):
+    """7B shape at two layers, 2048-token prompt, 32 decode steps at contexts 2048 .. 2079 (tests/golden/make_cfg2_golden.py):
+    the single-sequence decode step at the benchmark's context length -- the streaming attention kernel with ~28 pages per
+    CTA and every head merged across several CTAs, the 4096- and 11008-wide Q4_K matrix-vector products -- against the
+    CPU oracle, logits step by step through the host API and tokens through the device-resident loop."""
+    from leafcutterllm_b200 import synth
+    path = os.path.join(HERE, "golden", "cfg2_llama7b_q4_k_2layers.json")
+    gold = json.load(open(path))
+    spec = synth.LLAMA7B.with_layers(2)
+    n, steps = gold["prompt_len"], len(gold["tokens"]) - 1
+    eng = synth.build_engine(spec, n + steps + 16, on_device=True)
+    prompt = synth.prompt_tokens(n, spec.vocab_size, 0)
+    assert prompt[:8].tolist() == gold["prompt_head"]
+
+    def check(logits, g, what):
+        assert_close(logits[:16], g["first16"], LOGIT_ABS, LOGIT_REL, what)
+        assert abs(np.sqrt((logits.astype(np.float64) ** 2).sum()) - g["l2"]) < 1e-3 * g["l2"], what
+        assert int(np.argmax(logits)) == g["argmax"] or g["margin"] < 1e-3, (what, g["margin"])
+
+    check(eng.forward(prompt), gold["steps"][0], "prefill")
+    for i in range(1, steps + 1):
+        check(eng.forward([gold["tokens"][i - 1]]), gold["steps"][i], f"decode step {i} (context {n + i - 1})")
+    assert eng.kv_length() == n + steps
+    toks = eng.generate(prompt, steps + 1, stop_on_eos=False)  # prefill again, then the steps as graph replays on the device
+    bad = [i for i, (a, b) in enumerate(zip(toks, gold["tokens"])) if a != b]
+    assert not bad, f"first divergence at step {bad[0]}, oracle top-2 margin there {gold['steps'][bad[0]]['margin']}"
+    eng.close()
+
+
 def test_7b_shape_two_layers_against_the_oracle(gpu, oracle):
     from leafcutterllm_b200 import synth
     spec = synth.LLAMA7B.with_layers(2)

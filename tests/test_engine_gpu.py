@@ -118,6 +118,58 @@ def test_many_sequences_decode_through_the_tensor_core_gemm(gpu, oracle):
     assert np.array_equal(runs[0][2], runs[1][2])
 
 
+def test_batched_decode_attention_over_several_context_pieces(gpu, oracle):
+    """80 sequences x 8 heads of 128 dims = 640 (token, head) pairs: past four per SM, so the batched decode step runs
+    the split-context attention kernel with the context cut into 1024-key pieces and the pieces merged through the
+    scratch partials.  Contexts sit on both sides of the piece edges (1023 / 1024 / 1025, 2047 / 2049, 4090) and most are
+    short, so many (pair, piece) CTAs have no key at all and leave at once.  Prefill logits and four decode steps are
+    compared with the oracle sequence by sequence."""
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=1, hidden=1024, heads=8, kv=2, ffn=512, vocab=512)
+    special = [5, 1023, 1024, 1025, 2047, 2049, 2500, 4090]
+    r = np.random.default_rng(5)
+    lens = special + [int(v) for v in r.integers(1, 200, 80 - len(special))]
+    ids = list(range(80))
+    steps = 4
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=4096, max_seqs=80, kv_pool_tokens=sum((n + steps + 15) // 16 * 16 for n in lens))
+    prompts = [synth.prompt_tokens(n, spec.vocab_size, 100 + i).tolist() for i, n in enumerate(lens)]
+    logits, nxt = eng.forward_batch(ids, prompts)
+    step_logits, cur = [], nxt.copy()
+    for _ in range(steps):  # every sequence advances by one token per call: the 80-token batched decode step
+        lg, cur = eng.forward_batch(ids, [[int(t)] for t in cur])
+        step_logits.append(lg.copy())
+    for i, p in enumerate(prompts):
+        if i >= len(special) and i % 6:  # every special context and a sample of the short ones go through the oracle
+            continue
+        om.kv_clear()
+        want = om.forward(p)
+        assert_close(logits[i], want, LOGIT_ABS, LOGIT_REL, f"prefill of sequence {i} ({lens[i]} tokens)")
+        for s_ in range(steps):
+            tok = int(oracle.argmax(want))
+            want = om.forward([tok])
+            assert_close(step_logits[s_][i], want, LOGIT_ABS, LOGIT_REL, f"sequence {i} (context {lens[i]}), decode step {s_}")
+    eng.close()
+
+
+def test_a_second_model_does_not_disturb_a_captured_decode_step(gpu, oracle):
+    """Scratch that a captured decode graph points at belongs to its model: a small model captures its step, then a
+    model with more heads is created on the same device (which used to regrow a shared buffer), and the small model
+    must keep decoding the oracle's tokens."""
+    from leafcutterllm_b200 import synth
+    small = small_spec(12, 12, 12, layers=2, hidden=256, heads=2, kv=2, ffn=512, vocab=900)
+    big = small_spec(12, 12, 12, layers=1, hidden=2048, heads=16, kv=16, ffn=512, vocab=600)
+    eng, om = make_pair(gpu, oracle, small, max_seq_len=96)
+    prompt = synth.prompt_tokens(20, small.vocab_size, 3)
+    ref, margins = om.generate(prompt, 30, stop_on_eos=False, want_margins=True)
+    assert eng.generate(prompt, 10, stop_on_eos=False) == ref[:10], margins   # captures the one-sequence step
+    eng2 = synth.build_engine(big, 64, on_device=True)
+    assert len(eng2.generate(synth.prompt_tokens(9, big.vocab_size, 4), 6, stop_on_eos=False)) == 6
+    assert eng.generate(prompt, 30, stop_on_eos=False) == ref, margins         # replays the graph captured before eng2 existed
+    eng2.close()
+    assert eng.generate(prompt, 30, stop_on_eos=False) == ref, margins
+    eng.close()
+
+
 def test_mixed_quant_types_like_q4_k_m(gpu, oracle):
     """A "Q4_K_M" file keeps attn_v and ffn_down in Q6_K while q, k, o, gate and up are Q4_K: the three projections of a
     layer then cannot be one matrix (three products per layer) and the Q6_K matrices run through the K-quant kernel.
