@@ -38,10 +38,17 @@ struct LayerW {
     const float* attn_norm = nullptr;
     const float* ffn_norm = nullptr;
     void* fused_buf = nullptr;
+    // mixture-of-experts FFN (no counterpart in the reference): f32 router [n_experts, H], the experts' three matrices,
+    // and -- when every expert is Q4_K with a tensor map -- device arrays of those maps for the one-launch grouped product
+    const float* router = nullptr;
+    std::vector<QWeight> egate, eup, edown;
+    void *tm_gate = nullptr, *tm_up = nullptr, *tm_down = nullptr;
+    bool grouped_ok = false;
 };
 
 constexpr int kPrefillChunk = 512;
 constexpr int kTokTile = 8;
+constexpr int kMoeGroupedTokens = 64;  // calls of at most this many tokens run the experts as one grouped launch
 
 }  // namespace
 
@@ -86,6 +93,13 @@ struct lc_model {
     size_t out_tokens_cap = 0;
     int32_t* d_step_ctr = nullptr;
     unsigned long long* d_stream_slots = nullptr;  // cross-CTA merge slots of the single-token attention kernel (zero between launches)
+    // mixture-of-experts scratch: the router's picks and weights per token, per-expert slot counts and lists, the slots'
+    // FFN hidden rows and outputs (calls of up to kMoeGroupedTokens tokens), every expert's output plane (larger calls)
+    int32_t *d_moe_sel = nullptr, *d_moe_cnt = nullptr, *d_moe_lists = nullptr;
+    float *d_moe_w = nullptr, *d_moe_h = nullptr, *d_moe_y = nullptr, *d_moe_yall = nullptr;
+    unsigned long long* d_moe_touched = nullptr;  // experts that received a token, summed over layers and steps since the last read
+    uint64_t expert_bytes_each = 0, expert_bytes_all = 0;
+    double touched_per_step = 0.0;
     void* d_attn_scratch = nullptr;
     GemmWorkspace gemm_ws;  // f16 activation halves for the many-token tensor-core product
     bool any_unfused_qkv = false;  // some layer's q/k/v differ in type
@@ -313,9 +327,54 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
 }
 
+// Mixture-of-experts FFN in place of ffn_forward (moe.cu has the definition): router, then either ONE grouped launch per
+// projection over the experts that received tokens (Q4_K experts, calls of up to 64 tokens), or every expert on every
+// token through the ordinary products (prefill chunks, other quant types), then the weighted sum of the chosen experts.
+int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out) {
+    LayerW& w = m->layers[l];
+    const int E = m->cfg.n_experts, K = m->cfg.top_k;
+    const bool grouped = w.grouped_ok && T <= kMoeGroupedTokens;
+    MoeRouteArgs r;
+    r.x = x; r.norm_w = norm_w; r.eps = m->cfg.rms_eps; r.H = m->H; r.T = T; r.w_router = w.router; r.n_experts = E; r.top_k = K;
+    r.sel = m->d_moe_sel; r.wsel = m->d_moe_w;
+    if (grouped) { r.counts = m->d_moe_cnt; r.lists = m->d_moe_lists; r.list_stride = kMoeGroupedTokens; r.touched = m->d_moe_touched; }
+    LC_TRY(launch_moe_route(r, m->stream));
+    m->launches_in_call += 1;
+    if (grouped) {
+        GemvGroup g1;
+        g1.tmaps = w.tm_gate; g1.tmaps2 = w.tm_up; g1.counts = m->d_moe_cnt; g1.lists = m->d_moe_lists; g1.list_stride = kMoeGroupedTokens;
+        g1.n_experts = E; g1.top_k = K; g1.max_tokens = T; g1.x_by_token = true;
+        GemvArgs a;
+        a.w = &w.egate[0]; a.w2 = &w.eup[0]; a.x = x; a.norm_w = norm_w; a.eps = m->cfg.rms_eps; a.out = m->d_moe_h; a.epi = EPI_SILU_MUL;
+        a.m = std::min(T, kTokTile); a.group = &g1;
+        LC_TRY(launch_qgemv(a, m->stream));
+        GemvGroup g2 = g1;
+        g2.tmaps = w.tm_down; g2.tmaps2 = nullptr; g2.x_by_token = false;
+        GemvArgs d;
+        d.w = &w.edown[0]; d.x = m->d_moe_h; d.out = m->d_moe_y; d.m = std::min(T, kTokTile); d.group = &g2;
+        LC_TRY(launch_qgemv(d, m->stream));
+        LC_TRY(launch_moe_combine(m->d_moe_y, m->d_moe_sel, m->d_moe_w, K, m->H, T, 0, 0, residual, out, m->stream));
+        m->launches_in_call += 3;
+        return LC_OK;
+    }
+    for (int e = 0; e < E; e++) {
+        GemvArgs g;
+        g.w = &w.egate[e]; g.w2 = &w.eup[e]; g.x = x; g.norm_w = norm_w; g.eps = m->cfg.rms_eps; g.out = m->d_ffn; g.epi = EPI_SILU_MUL;
+        g.prep_next = true;  // the expert's down projection reads d_ffn next, without a norm
+        LC_TRY(gemv_tiled(m, g, T, m->F, m->H));
+        GemvArgs d;
+        d.w = &w.edown[e]; d.x = m->d_ffn; d.out = m->d_moe_yall + (size_t)e * m->t_cap * m->H;
+        LC_TRY(gemv_tiled(m, d, T, m->H, m->F));
+    }
+    LC_TRY(launch_moe_combine(m->d_moe_yall, m->d_moe_sel, m->d_moe_w, K, m->H, T, 1, (size_t)m->t_cap, residual, out, m->stream));
+    m->launches_in_call += 1;
+    return LC_OK;
+}
+
 // ffn_forward (engine.rs:146-164)
 int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out,
                   bool decode_step) {
+    if (m->cfg.n_experts > 0) return moe_block(m, l, x, norm_w, T, residual, out);
     LayerW& w = m->layers[l];
     GemvArgs g;
     g.w = &w.gate;
@@ -381,6 +440,8 @@ int32_t forward_tokens(lc_model* m, int T, int n_last, bool identity_last, int r
 
 uint64_t algo_bytes_step(const lc_model* m, const std::vector<int>& ctx_lens) {
     uint64_t b = m->ctr.weight_bytes;  // every matrix and gain once
+    if (m->cfg.n_experts > 0)          // ... but only the experts that received a token (average per layer of the last steps)
+        b = b - m->expert_bytes_all + (uint64_t)(m->touched_per_step * (double)m->expert_bytes_each);
     // the embedding table is not streamed: one row per token instead
     if (m->embed) {
         bool tied = m->tensors.find("output.weight") == m->tensors.end();
@@ -445,7 +506,10 @@ int32_t lc_model_create(const lc_model_config* cfg, lc_model** out) {
              cfg->hidden_size, cfg->num_heads);
     LC_CHECK(cfg->num_heads % cfg->num_kv_heads == 0, LC_ERR_INVALID, "num_heads %d is not a multiple of num_kv_heads %d",
              cfg->num_heads, cfg->num_kv_heads);
-    LC_CHECK(cfg->n_experts == 0, LC_ERR_UNSUPPORTED, "mixture-of-experts FFN is not implemented in this build");
+    LC_CHECK(cfg->n_experts >= 0 && cfg->n_experts <= kMaxExperts, LC_ERR_INVALID, "n_experts %d outside 0..%d", cfg->n_experts, kMaxExperts);
+    if (cfg->n_experts > 0)
+        LC_CHECK(cfg->top_k >= 1 && cfg->top_k <= kMaxTopK && cfg->top_k <= cfg->n_experts, LC_ERR_INVALID,
+                 "top_k %d outside 1..min(%d, n_experts = %d)", cfg->top_k, kMaxTopK, cfg->n_experts);
     if (!have_device()) return LC_ERR_CUDA;
     LC_CHECK(cfg->device >= 0 && cfg->device < lc_device_count(), LC_ERR_INVALID, "device %d not present", cfg->device);
     DeviceGuard dg(cfg->device);
@@ -562,6 +626,58 @@ static int32_t weight_of(lc_model* m, const std::string& name, int n, int k, QWe
     return qweight_init(w, t.typ, t.view, n, k);
 }
 
+// One expert's matrix: the tensor "blk.L.expert.E.<which>.weight", or rows [e * n, (e + 1) * n) of the stacked
+// three-dimensional tensor "blk.L.<which>_exps.weight" that GGUF files of mixture models carry.
+static int32_t expert_weight(lc_model* m, int l, int e, const char* which, int n, int k, QWeight* w) {
+    const std::string p = "blk." + std::to_string(l) + ".";
+    const std::string single = p + "expert." + std::to_string(e) + "." + which + ".weight";
+    if (m->tensors.count(single)) return weight_of(m, single, n, k, w, nullptr);
+    const std::string stacked = p + which + "_exps.weight";
+    auto it = m->tensors.find(stacked);
+    LC_CHECK(it != m->tensors.end(), LC_ERR_MISSING, "missing tensor %s (or %s)", single.c_str(), stacked.c_str());
+    DevTensor& t = it->second;
+    LC_CHECK((int)t.cols == k && t.rows == (size_t)n * m->cfg.n_experts, LC_ERR_INVALID, "tensor %s is [%zu x %zu], expected [%d x %d] per expert",
+             stacked.c_str(), t.rows, t.cols, n, k);
+    QuantGeom g;
+    LC_CHECK(quant_geom(t.typ, &g), LC_ERR_UNSUPPORTED, "tensor %s: unsupported type", stacked.c_str());
+    const size_t row_bytes = (size_t)k / g.block_elems * g.block_bytes;
+    return qweight_init(w, t.typ, (const uint8_t*)t.view + (size_t)e * n * row_bytes, n, k);
+}
+
+static int32_t finalize_experts(lc_model* m, int l) {
+    LayerW& w = m->layers[l];
+    const int E = m->cfg.n_experts, H = m->H, F = m->F;
+    const std::string p = "blk." + std::to_string(l) + ".";
+    LC_TRY(gain_f32(m, p + "ffn_gate_inp.weight", E * H, &w.router));
+    w.egate.resize(E); w.eup.resize(E); w.edown.resize(E);
+    bool q4k = true;
+    for (int e = 0; e < E; e++) {
+        LC_TRY(expert_weight(m, l, e, "ffn_gate", F, H, &w.egate[e]));
+        LC_TRY(expert_weight(m, l, e, "ffn_up", F, H, &w.eup[e]));
+        LC_TRY(expert_weight(m, l, e, "ffn_down", H, F, &w.edown[e]));
+        LC_CHECK(w.egate[e].typ == w.eup[e].typ, LC_ERR_UNSUPPORTED, "layer %d expert %d: gate/up projections have different quant types", l, e);
+        for (const QWeight* q : {&w.egate[e], &w.eup[e], &w.edown[e]}) q4k = q4k && q->typ == LC_TYPE_Q4_K && q->has_tmap;
+    }
+    w.grouped_ok = q4k && qgemv_mma_supports(H) && qgemv_mma_supports(F);
+    if (w.grouped_ok) {
+        std::vector<unsigned char> host((size_t)E * 128);
+        const std::vector<QWeight>* sets[3] = {&w.egate, &w.eup, &w.edown};
+        void** dst[3] = {&w.tm_gate, &w.tm_up, &w.tm_down};
+        for (int i = 0; i < 3; i++) {
+            for (int e = 0; e < E; e++) memcpy(&host[(size_t)e * 128], (*sets[i])[e].tmap, 128);
+            LC_TRY(dalloc((uint8_t**)dst[i], host.size()));
+            m->owned.push_back(*dst[i]);
+            LC_CUDA(cudaMemcpyAsync(*dst[i], host.data(), host.size(), cudaMemcpyHostToDevice, m->stream));
+            LC_CUDA(cudaStreamSynchronize(m->stream));
+        }
+    }
+    uint64_t each = 0;
+    for (const QWeight* q : {&w.egate[0], &w.eup[0], &w.edown[0]}) each += (uint64_t)q->n * q->row_bytes;
+    m->expert_bytes_each = each;
+    m->expert_bytes_all += each * E;
+    return LC_OK;
+}
+
 int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(check_model(m, false));
     LC_CHECK(!m->finalized, LC_ERR_STATE, "model already finalized");
@@ -594,11 +710,15 @@ int32_t lc_model_finalize(lc_model* m) {
             LC_TRY(qweight_init(&w.qkv, tq->typ, buf, m->nqkv, H));
         }
         LC_TRY(weight_of(m, p + "attn_output.weight", H, nq, &w.o, nullptr));
-        DevTensor *tg = nullptr, *tu = nullptr;
-        LC_TRY(weight_of(m, p + "ffn_gate.weight", F, H, &w.gate, &tg));
-        LC_TRY(weight_of(m, p + "ffn_up.weight", F, H, &w.up, &tu));
-        LC_CHECK(tg->typ == tu->typ, LC_ERR_UNSUPPORTED, "layer %d: gate/up projections have different quant types", l);
-        LC_TRY(weight_of(m, p + "ffn_down.weight", H, F, &w.down, nullptr));
+        if (m->cfg.n_experts > 0) {
+            LC_TRY(finalize_experts(m, l));
+        } else {
+            DevTensor *tg = nullptr, *tu = nullptr;
+            LC_TRY(weight_of(m, p + "ffn_gate.weight", F, H, &w.gate, &tg));
+            LC_TRY(weight_of(m, p + "ffn_up.weight", F, H, &w.up, &tu));
+            LC_CHECK(tg->typ == tu->typ, LC_ERR_UNSUPPORTED, "layer %d: gate/up projections have different quant types", l);
+            LC_TRY(weight_of(m, p + "ffn_down.weight", H, F, &w.down, nullptr));
+        }
         LC_TRY(gain_f32(m, p + "attn_norm.weight", H, &w.attn_norm));
         LC_TRY(gain_f32(m, p + "ffn_norm.weight", H, &w.ffn_norm));
     }
@@ -668,6 +788,15 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(dalloc(&m->d_ffn, (size_t)T * F));
     LC_TRY(qgemm_workspace_alloc(&m->gemm_ws, T, std::max(std::max(H, F), nq)));
     if (m->any_unfused_qkv) LC_TRY(dalloc(&m->d_qkv_parts, (size_t)T * m->nqkv));
+    if (m->cfg.n_experts > 0) {
+        const int E = m->cfg.n_experts, K = m->cfg.top_k;
+        LC_TRY(dalloc(&m->d_moe_sel, (size_t)T * K)); LC_TRY(dalloc(&m->d_moe_w, (size_t)T * K));
+        LC_TRY(dalloc(&m->d_moe_cnt, (size_t)E)); LC_TRY(dalloc(&m->d_moe_lists, (size_t)E * kMoeGroupedTokens));
+        LC_TRY(dalloc(&m->d_moe_h, (size_t)kMoeGroupedTokens * K * F)); LC_TRY(dalloc(&m->d_moe_y, (size_t)kMoeGroupedTokens * K * H));
+        LC_TRY(dalloc(&m->d_moe_yall, (size_t)E * T * H));
+        LC_TRY(dalloc(&m->d_moe_touched, 1));
+        LC_CUDA(cudaMemsetAsync(m->d_moe_touched, 0, 8, m->stream));
+    }
     LC_TRY(dalloc(&m->d_last, (size_t)m->max_seqs * H)); LC_TRY(dalloc(&m->d_logits, (size_t)m->max_seqs * V));
     LC_TRY(dalloc(&m->d_next, m->max_seqs)); LC_TRY(dalloc(&m->d_step_ctr, 1));
     size_t sc = 16;
@@ -697,7 +826,8 @@ int32_t lc_model_destroy(lc_model* m) {
     for (void* p : m->owned) cudaFree(p);
     for (void* p : m->k_pools) cudaFree(p);
     for (void* p : m->v_pools) cudaFree(p);
-    void* bufs[] = {m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
+    void* bufs[] = {m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
+                    m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};
     for (void* p : bufs) if (p) cudaFree(p);
@@ -917,6 +1047,13 @@ static int32_t stage_decode_meta(lc_model* m, int n_seqs, const int32_t* seq_ids
 }
 
 static void after_decode_steps(lc_model* m, int n_seqs, const int32_t* seq_ids, int steps) {
+    if (m->d_moe_touched) {  // experts touched, summed over the layers of these steps (grouped calls count them; others touch all)
+        unsigned long long t = 0;
+        if (cudaMemcpyAsync(&t, m->d_moe_touched, 8, cudaMemcpyDeviceToHost, m->stream) == cudaSuccess &&
+            cudaMemsetAsync(m->d_moe_touched, 0, 8, m->stream) == cudaSuccess && cudaStreamSynchronize(m->stream) == cudaSuccess)
+            m->touched_per_step = n_seqs <= kMoeGroupedTokens && m->layers[0].grouped_ok ? (double)t / std::max(steps, 1)
+                                                                                           : (double)m->L * m->cfg.n_experts;
+    }
     std::vector<int> ctx;
     for (int i = 0; i < n_seqs; i++) {
         m->seq_len[seq_ids[i]] += steps;

@@ -561,6 +561,13 @@ static int round_m(int m) { return m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
 
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
     LC_CHECK(a.w && a.x && a.out, LC_ERR_INVALID, "qgemv: null argument");
+    if (a.group) {  // the experts of a mixture-of-experts layer in one launch (Q4_K only)
+        bool launched = false;
+        LC_CHECK(a.w->typ == LC_TYPE_Q4_K && a.w->has_tmap, LC_ERR_UNSUPPORTED, "grouped qgemv: experts must be Q4_K with tensor maps");
+        LC_TRY(launch_qgemv_mma_q4k_grouped(a, s, &launched));
+        LC_CHECK(launched, LC_ERR_UNSUPPORTED, "grouped qgemv: rows of %d elements do not fit the kernel", a.w->k);
+        return LC_OK;
+    }
     LC_CHECK(a.m >= 1 && a.m <= 8, LC_ERR_INVALID, "qgemv: m=%d outside 1..8", a.m);
     if (a.epi == EPI_SILU_MUL)
         LC_CHECK(a.w2 && a.w2->n == a.w->n && a.w2->k == a.w->k && a.w2->typ == a.w->typ, LC_ERR_INVALID,

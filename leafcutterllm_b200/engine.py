@@ -23,8 +23,9 @@ class Engine:
     def __init__(self, hidden_size: int, num_layers: int, num_heads: int, num_kv_heads: int, intermediate_size: int,
                  vocab_size: int, max_seq_len: int = 4096, rope_theta: float = 10000.0, rms_eps: float = 1e-5,
                  kv_dtype: str = "f16", rope_mode: str = "call_relative", max_seqs: int = 1, kv_page_tokens: int = 16,
-                 kv_pool_tokens: int = 0, device: int = 0):
+                 kv_pool_tokens: int = 0, device: int = 0, n_experts: int = 0, top_k: int = 0):
         cfg = ModelConfig()
+        cfg.n_experts, cfg.top_k = n_experts, top_k
         cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads = hidden_size, num_layers, num_heads, num_kv_heads
         cfg.intermediate_size, cfg.max_seq_len, cfg.vocab_size = intermediate_size, max_seq_len, vocab_size
         cfg.rope_theta, cfg.rms_eps = rope_theta, rms_eps

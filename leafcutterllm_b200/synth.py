@@ -34,6 +34,8 @@ class ModelSpec:
     embed_type: int = TYPE_Q4_K
     head_type: int = TYPE_Q4_K
     tied_head: bool = False
+    n_experts: int = 0   # > 0: a mixture-of-experts FFN in every layer (f32 router + n_experts SwiGLU experts, top_k of them per token)
+    top_k: int = 0
 
     @property
     def head_dim(self) -> int:
@@ -55,6 +57,14 @@ class ModelSpec:
             yield p + "attn_v.weight", self.layer_type, (H, nkv), "normal"
             yield p + "attn_output.weight", self.layer_type, (nq, H), "normal"
             yield p + "ffn_norm.weight", TYPE_F32, (H,), "ones"
+            if self.n_experts > 0:
+                yield p + "ffn_gate_inp.weight", TYPE_F32, (H, self.n_experts), "normal"
+                for e in range(self.n_experts):
+                    q = f"{p}expert.{e}."
+                    yield q + "ffn_gate.weight", self.layer_type, (H, F), "normal"
+                    yield q + "ffn_up.weight", self.layer_type, (H, F), "normal"
+                    yield q + "ffn_down.weight", self.layer_type, (F, H), "normal"
+                continue
             yield p + "ffn_gate.weight", self.layer_type, (H, F), "normal"
             yield p + "ffn_up.weight", self.layer_type, (H, F), "normal"
             yield p + "ffn_down.weight", self.layer_type, (F, H), "normal"
@@ -68,6 +78,10 @@ class ModelSpec:
 TINY = ModelSpec("tinyllama-1.1b-shape-q4_0", 22, 2048, 32, 4, 5632, 32000, 10000.0, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q8_0)
 # Llama-2-7B shape, Q4_K throughout.
 LLAMA7B = ModelSpec("llama2-7b-shape-q4_k", 32, 4096, 32, 32, 11008, 32000, 10000.0, TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K)
+# Mixtral-8x7B shape: 8 experts of FFN 14336, two per token, 32 q / 8 kv heads, Q4_K (router f32).
+MIXTRAL = ModelSpec("mixtral-8x7b-shape-q4_k", 32, 4096, 32, 8, 14336, 32000, 10000.0, TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K, n_experts=8, top_k=2)
+# Llama-3-70B shape, Q4_K.
+LLAMA70B = ModelSpec("llama3-70b-shape-q4_k", 80, 8192, 64, 8, 28672, 128256, 500000.0, TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K)
 
 
 def host_tensor(typ: int, seed: int, name: str, n_elems: int, sigma: float = SIGMA) -> np.ndarray:
@@ -96,7 +110,8 @@ def build_engine(spec: ModelSpec, max_seq_len: int, seed: int = WEIGHT_SEED, on_
     kernel (no host copy); False runs the host generator and uploads."""
     from .engine import Engine
     eng = Engine(spec.hidden_size, spec.num_layers, spec.num_heads, spec.num_kv_heads, spec.intermediate_size,
-                 spec.vocab_size, max_seq_len=max_seq_len, rope_theta=spec.rope_theta, **engine_kwargs)
+                 spec.vocab_size, max_seq_len=max_seq_len, rope_theta=spec.rope_theta, n_experts=spec.n_experts, top_k=spec.top_k,
+                 **engine_kwargs)
     for name, typ, dims, kind in spec.tensors():
         if kind == "ones" or not on_device:
             eng.set_tensor(name, typ, dims, tensor_bytes(spec, name, typ, dims, kind, seed))

@@ -45,7 +45,7 @@ def make_pair(lc, oracle, spec, max_seq_len=256, seed=1234, on_device=False, ora
     if engine_kwargs.get("rope_mode") == "absolute":
         okw["rope_absolute"] = True
     om = oracle.OracleModel(spec.hidden_size, spec.num_layers, spec.num_heads, spec.num_kv_heads, spec.intermediate_size,
-                            spec.vocab_size, max_seq_len=max_seq_len, rope_theta=spec.rope_theta, **okw)
+                            spec.vocab_size, max_seq_len=max_seq_len, rope_theta=spec.rope_theta, n_experts=spec.n_experts, top_k=spec.top_k, **okw)
     for name, typ, dims, kind in spec.tensors():
         if on_device and kind != "ones":
             data = eng.get_tensor(name, typ, dims)
