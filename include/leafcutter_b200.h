@@ -167,14 +167,54 @@ typedef struct lc_model_config {
     float rms_eps;            /* 0 -> 1e-5, the constant at rust/src/inference/engine.rs:102,111,121 */
     int32_t kv_dtype;         /* 0 = f16 storage as rust/src/cache/mod.rs:33-61; 1 = f32 */
     int32_t rope_mode;        /* 0 = position inside the call, as attention.rs:13-21; 1 = absolute position */
-    int32_t n_experts;        /* 0 = dense FFN (mixture-of-experts has no counterpart in the reference) */
+    int32_t n_experts;        /* 0 = dense FFN; > 0: router + n_experts SwiGLU experts per layer, top_k per token (mixture-of-experts
+                                 has no counterpart in the reference; the definition is at lc_forward) */
     int32_t top_k;
     int32_t max_seqs;         /* concurrent sequences; 0 -> 1 */
     int32_t kv_page_tokens;   /* tokens per KV page; 0 -> 16 */
     int64_t kv_pool_tokens;   /* KV pool size in tokens over all sequences; 0 -> max_seqs * max_seq_len */
     int32_t device;           /* CUDA device ordinal */
-    int32_t reserved[7];
+    int32_t tp_size;          /* model-parallel ranks the model is cut into; 0 or 1 = whole model; 0 after lc_dist_init = that world */
+    int32_t tp_rank;          /* which of them this handle holds (0 after lc_dist_init = that rank) */
+    int32_t reserved[5];
 } lc_model_config;
+
+/* ---- Model parallelism (no counterpart in the reference, which runs on one device) ----
+ * A model of tp_size ranks is cut the usual tensor-parallel way; every dimension below is the WHOLE model's, and every rank is
+ * handed the WHOLE tensor by lc_model_set_tensor / lc_model_synth_tensor and keeps its own part (lc_shard_plan says which):
+ *   attn_q / attn_k / attn_v, ffn_gate / ffn_up, output.weight   by output rows (whole heads, whole vocabulary slices);
+ *   attn_output, ffn_down                                         by input columns, on quant-block boundaries;
+ *   norms, token_embd, the router                                 whole on every rank;
+ *   mixture-of-experts layers                                     whole experts, n_experts / tp_size consecutive ones per rank.
+ * The KV cache is cut by kv head.  Per layer there are two sums over the ranks -- after attn_output and after ffn_down
+ * (or the experts' weighted sum) -- taken in rank order, so every rank holds bit-identical activations; the greedy pick is
+ * the maximum over the ranks of (logit, global index), equal logits going to the higher index as on one device.
+ * Requirements: num_heads, num_kv_heads, vocab_size, intermediate_size (or n_experts) divisible by tp_size, the column
+ * parts whole quant blocks.
+ *
+ * One process per GPU: rank 0 calls lc_dist_unique_id and hands the 128 bytes to the other ranks by its own means; every
+ * rank then calls lc_dist_init(rank, world, id) with its device current, BEFORE lc_model_create, and creates the model with
+ * tp_size = tp_rank = 0 (or the same numbers).  All ranks must make the same model-level calls in the same order.  The
+ * sums run as NCCL all-reduces (lc_dist_init loads libnccl.so.2 at run time) or, for payloads up to 2 MiB when every peer's
+ * buffer could be mapped, as one kernel per sum that reads the peers' partial rows over NVLink in rank order; waits in
+ * that kernel are bounded and end in LC_ERR_CUDA.  lc_dist_set_backend(0) forces NCCL, (1) asks for the peer-memory kernel.
+ *
+ * One process, one GPU, several ranks (testing a cut model where only one GPU is at hand): create tp_size handles with
+ * explicit tp_size / tp_rank on the same device, load and finalize each, then lc_model_group(handles, tp_size).  Calls on
+ * handles[0] then drive all ranks in lock step on the one stream and the sums run as one kernel over all ranks' rows. */
+int32_t lc_dist_unique_id(void* out_id128);
+int32_t lc_dist_init(int32_t rank, int32_t world, const void* id128);
+int32_t lc_dist_set_backend(int32_t peer_memory);
+int32_t lc_dist_finalize(void);
+/* Microseconds per sum of `count` floats over the ranks, averaged over `iters` back-to-back sums on the library's stream
+ * (CUDA events; a measurement helper for the all-reduce that sits between a layer's products). */
+int32_t lc_dist_time_allreduce(size_t count, int32_t iters, float* out_us);
+int32_t lc_model_group(lc_model** handles, int32_t n);
+/* Which part of a tensor a rank keeps: kind 0 = all of it, 1 = rows [first, first + count) (dims[1] index; for stacked expert
+ * tensors rows of the flattened [dims[2] * dims[1]] matrix), 2 = columns [first, first + count) of every row (dims[0] index),
+ * 3 = nothing (an expert that lives on another rank).  Pure host arithmetic: needs no GPU. */
+int32_t lc_shard_plan(const lc_model_config* cfg, const char* name, const uint64_t* dims, int32_t ndims, int32_t* kind,
+                      uint64_t* first, uint64_t* count);
 
 /* Engine::load without the file: create, then hand over each tensor, then finalize.
  * rust/src/inference/engine.rs:18-49, rust/src/model/loader.rs:145-203. */

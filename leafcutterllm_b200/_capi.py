@@ -24,7 +24,7 @@ class ModelConfig(C.Structure):
                 ("vocab_size", C.c_int32), ("rope_theta", C.c_float), ("rms_eps", C.c_float),
                 ("kv_dtype", C.c_int32), ("rope_mode", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32),
                 ("max_seqs", C.c_int32), ("kv_page_tokens", C.c_int32), ("kv_pool_tokens", C.c_int64),
-                ("device", C.c_int32), ("reserved", C.c_int32 * 7)]
+                ("device", C.c_int32), ("tp_size", C.c_int32), ("tp_rank", C.c_int32), ("reserved", C.c_int32 * 5)]
 
 
 class Counters(C.Structure):
@@ -124,6 +124,13 @@ SIGNATURES = {
     "lc_reset_counters": (_i32, [_vp]),
     "lc_probe_attention": (_i32, [_vp, _i32, _vp, _i32, _vp]),
     "lc_probe_ffn": (_i32, [_vp, _i32, _vp, _i32, _vp]),
+    "lc_dist_unique_id": (_i32, [_vp]),
+    "lc_dist_init": (_i32, [_i32, _i32, _vp]),
+    "lc_dist_set_backend": (_i32, [_i32]),
+    "lc_dist_finalize": (_i32, []),
+    "lc_dist_time_allreduce": (_i32, [_sz, _i32, C.POINTER(C.c_float)]),
+    "lc_model_group": (_i32, [C.POINTER(_vp), _i32]),
+    "lc_shard_plan": (_i32, [C.POINTER(ModelConfig), C.c_char_p, _vp, _i32, C.POINTER(_i32), C.POINTER(_u64), C.POINTER(_u64)]),
 }
 
 

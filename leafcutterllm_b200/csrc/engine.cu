@@ -64,8 +64,20 @@ struct lc_model {
     const float* final_norm = nullptr;
     std::vector<void*> owned;  // f32 copies of norm gains etc.
 
-    // geometry
+    // geometry: H, L, hd are the model's; nh, nkv, F, V, nqkv are THIS RANK'S part when the model is cut across ranks
+    // (tp > 1: heads, kv heads, FFN rows and vocabulary rows divided by tp; experts e0 .. e0 + El - 1 of a mixture layer)
     int H = 0, L = 0, nh = 0, nkv = 0, hd = 0, F = 0, V = 0, nqkv = 0;
+    int tp = 1, rank = 0, v0 = 0, e0 = 0, El = 0;
+    bool use_dist = false;               // the ranks are other processes (lc_dist_init); else members lists them, or tp == 1
+    std::vector<lc_model*> members;      // rank 0 of an in-process group: every rank's handle in rank order (itself first)
+    lc_model* leader = nullptr;          // a rank > 0 of such a group
+    float* d_part[2] = {nullptr, nullptr};   // where the column-cut products leave their partial rows for the sum over the ranks
+    bool part_owned = false;
+    long long* d_key[2] = {nullptr, nullptr};  // greedy pick of the local vocabulary slice as (total-order key << 32 | global index)
+    long long* d_key_max = nullptr;
+    float* d_logits_all = nullptr;       // dist: the ranks' logit slices gathered for the host
+    int sums_in_call = 0;                // alternates the partial-row slots
+    float* pending_dst = nullptr;        // where the next sum over the ranks has to land
     int page_tokens = 16, pages_per_seq = 0, pages_total = 0, max_seqs = 1, t_cap = 0;
     size_t kv_elt = 2;
 
@@ -149,6 +161,47 @@ std::string canonical_name(const std::string& in) {
         }
     }
     return in;
+}
+
+// Which part of a tensor rank `rank` of `tp` keeps (see the model-parallelism note of the C header).
+enum { SHARD_ALL = 0, SHARD_ROWS = 1, SHARD_COLS = 2, SHARD_NONE = 3 };
+struct ShardPlan { int kind = SHARD_ALL; uint64_t first = 0, count = 0; };
+bool ends_with(const std::string& s, const char* suf) {
+    const size_t n = strlen(suf);
+    return s.size() >= n && s.compare(s.size() - n, n, suf) == 0;
+}
+int32_t shard_plan(const lc_model_config& c, int tp, int rank, const std::string& key, const uint64_t* dims, int ndims, ShardPlan* out) {
+    ShardPlan pl;
+    uint64_t total_rows = 1;
+    for (int i = 1; i < ndims; i++) total_rows *= dims[i];
+    pl.count = total_rows;
+    *out = pl;
+    if (tp <= 1) return LC_OK;
+    LC_CHECK(rank >= 0 && rank < tp, LC_ERR_INVALID, "rank %d outside 0..%d", rank, tp - 1);
+    const bool expert_one = key.find(".expert.") != std::string::npos;
+    if (expert_one) {  // blk.L.expert.E.<proj>.weight: a whole expert, on the rank that owns it
+        const size_t at = key.find(".expert.") + 8;
+        const int e = atoi(key.c_str() + at), per = c.n_experts > 0 ? c.n_experts / tp : 0;
+        LC_CHECK(per > 0 && c.n_experts % tp == 0, LC_ERR_INVALID, "%d experts cannot be dealt to %d ranks", c.n_experts, tp);
+        if (e < rank * per || e >= (rank + 1) * per) { pl.kind = SHARD_NONE; pl.count = 0; }
+        *out = pl;
+        return LC_OK;
+    }
+    const bool rows = ends_with(key, "attn_q.weight") || ends_with(key, "attn_k.weight") || ends_with(key, "attn_v.weight") ||
+                      ends_with(key, "ffn_gate.weight") || ends_with(key, "ffn_up.weight") || key == "output.weight" ||
+                      ends_with(key, "ffn_gate_exps.weight") || ends_with(key, "ffn_up_exps.weight") || ends_with(key, "ffn_down_exps.weight");
+    const bool cols = ends_with(key, "attn_output.weight") || ends_with(key, "ffn_down.weight");
+    if (rows) {
+        LC_CHECK(ndims >= 2 && total_rows % tp == 0, LC_ERR_INVALID, "tensor %s: %llu rows cannot be cut into %d equal parts", key.c_str(),
+                 (unsigned long long)total_rows, tp);
+        pl.kind = SHARD_ROWS; pl.count = total_rows / tp; pl.first = pl.count * rank;
+    } else if (cols) {
+        LC_CHECK(ndims == 2 && dims[0] % tp == 0, LC_ERR_INVALID, "tensor %s: %llu columns cannot be cut into %d equal parts", key.c_str(),
+                 (unsigned long long)dims[0], tp);
+        pl.kind = SHARD_COLS; pl.count = dims[0] / tp; pl.first = pl.count * rank;
+    }
+    *out = pl;
+    return LC_OK;
 }
 
 struct DeviceGuard {
@@ -264,6 +317,14 @@ int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
     return LC_OK;
 }
 
+// Where a product whose input columns are cut across the ranks writes: `out` itself for a whole model, else the rank's
+// partial-row slot (the sum over the ranks, issued by the caller, then lands in `out`).
+float* partial_dst(lc_model* m, float* out) {
+    if (m->tp == 1) return out;
+    m->pending_dst = out;
+    return m->d_part[m->sums_in_call & 1];
+}
+
 // attention_forward (attention.rs:37-118) for layer `l` on T tokens whose (normalised or raw) input is `x`.
 int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out,
                         bool decode_step) {
@@ -319,9 +380,9 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     GemvArgs o;
     o.w = &w.o;
     o.x = m->d_attn;
-    o.out = out;
-    if (residual) { o.residual = residual; o.epi = EPI_ADD_RESIDUAL; }
-    if (residual && out == m->d_hidden2 && w.ffn_norm) {  // in a layer of the forward pass the FFN reads `out` next, through its norm
+    o.out = partial_dst(m, out);  // cut model: this rank's heads give a partial row; the caller sums the ranks into `out`
+    if (residual && (m->tp == 1 || m->rank == 0)) { o.residual = residual; o.epi = EPI_ADD_RESIDUAL; }  // the residual enters the sum once
+    if (m->tp == 1 && residual && out == m->d_hidden2 && w.ffn_norm) {  // in a layer of the forward pass the FFN reads `out` next, through its norm
         o.prep_next = true; o.next_norm_w = w.ffn_norm; o.next_eps = m->cfg.rms_eps;
     }
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
@@ -332,18 +393,21 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
 // token through the ordinary products (prefill chunks, other quant types), then the weighted sum of the chosen experts.
 int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T, const float* residual, float* out) {
     LayerW& w = m->layers[l];
-    const int E = m->cfg.n_experts, K = m->cfg.top_k;
+    const int E = m->cfg.n_experts, K = m->cfg.top_k, El = m->El, e0 = m->e0;  // this rank's experts: e0 .. e0 + El - 1
     const bool grouped = w.grouped_ok && T <= kMoeGroupedTokens;
+    if (m->tp > 1 && m->rank != 0) residual = nullptr;  // the residual enters the sum over the ranks once
+    out = partial_dst(m, out);
     MoeRouteArgs r;
     r.x = x; r.norm_w = norm_w; r.eps = m->cfg.rms_eps; r.H = m->H; r.T = T; r.w_router = w.router; r.n_experts = E; r.top_k = K;
     r.sel = m->d_moe_sel; r.wsel = m->d_moe_w;
     if (grouped) { r.counts = m->d_moe_cnt; r.lists = m->d_moe_lists; r.list_stride = kMoeGroupedTokens; r.touched = m->d_moe_touched; }
+    r.local_first = e0; r.local_count = El;
     LC_TRY(launch_moe_route(r, m->stream));
     m->launches_in_call += 1;
     if (grouped) {
         GemvGroup g1;
-        g1.tmaps = w.tm_gate; g1.tmaps2 = w.tm_up; g1.counts = m->d_moe_cnt; g1.lists = m->d_moe_lists; g1.list_stride = kMoeGroupedTokens;
-        g1.n_experts = E; g1.top_k = K; g1.max_tokens = T; g1.x_by_token = true;
+        g1.tmaps = w.tm_gate; g1.tmaps2 = w.tm_up; g1.counts = m->d_moe_cnt + e0; g1.lists = m->d_moe_lists + (size_t)e0 * kMoeGroupedTokens;
+        g1.list_stride = kMoeGroupedTokens; g1.n_experts = El; g1.top_k = K; g1.max_tokens = T; g1.x_by_token = true;
         GemvArgs a;
         a.w = &w.egate[0]; a.w2 = &w.eup[0]; a.x = x; a.norm_w = norm_w; a.eps = m->cfg.rms_eps; a.out = m->d_moe_h; a.epi = EPI_SILU_MUL;
         a.m = std::min(T, kTokTile); a.group = &g1;
@@ -353,11 +417,12 @@ int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         GemvArgs d;
         d.w = &w.edown[0]; d.x = m->d_moe_h; d.out = m->d_moe_y; d.m = std::min(T, kTokTile); d.group = &g2;
         LC_TRY(launch_qgemv(d, m->stream));
-        LC_TRY(launch_moe_combine(m->d_moe_y, m->d_moe_sel, m->d_moe_w, K, m->H, T, 0, 0, residual, out, m->stream));
+        LC_TRY(launch_moe_combine(m->d_moe_y, m->d_moe_sel, m->d_moe_w, K, m->H, T, 0, 0, e0, El, residual, out, m->stream));
         m->launches_in_call += 3;
         return LC_OK;
     }
-    for (int e = 0; e < E; e++) {
+    (void)E;
+    for (int e = 0; e < El; e++) {
         GemvArgs g;
         g.w = &w.egate[e]; g.w2 = &w.eup[e]; g.x = x; g.norm_w = norm_w; g.eps = m->cfg.rms_eps; g.out = m->d_ffn; g.epi = EPI_SILU_MUL;
         g.prep_next = true;  // the expert's down projection reads d_ffn next, without a norm
@@ -366,7 +431,7 @@ int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         d.w = &w.edown[e]; d.x = m->d_ffn; d.out = m->d_moe_yall + (size_t)e * m->t_cap * m->H;
         LC_TRY(gemv_tiled(m, d, T, m->H, m->F));
     }
-    LC_TRY(launch_moe_combine(m->d_moe_yall, m->d_moe_sel, m->d_moe_w, K, m->H, T, 1, (size_t)m->t_cap, residual, out, m->stream));
+    LC_TRY(launch_moe_combine(m->d_moe_yall, m->d_moe_sel, m->d_moe_w, K, m->H, T, 1, (size_t)m->t_cap, e0, El, residual, out, m->stream));
     m->launches_in_call += 1;
     return LC_OK;
 }
@@ -390,51 +455,97 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     GemvArgs d;
     d.w = &w.down;
     d.x = m->d_ffn;
-    d.out = out;
-    if (residual) { d.residual = residual; d.epi = EPI_ADD_RESIDUAL; }
-    if (residual && out == m->d_hidden && l + 1 < m->L && m->layers[l + 1].attn_norm) {
+    d.out = partial_dst(m, out);
+    if (residual && (m->tp == 1 || m->rank == 0)) { d.residual = residual; d.epi = EPI_ADD_RESIDUAL; }
+    if (m->tp == 1 && residual && out == m->d_hidden && l + 1 < m->L && m->layers[l + 1].attn_norm) {
         // the next layer's q/k/v product(s) read `out` through that layer's attention norm
         d.prep_next = true; d.next_norm_w = m->layers[l + 1].attn_norm; d.next_eps = m->cfg.rms_eps;
     }
     return gemv_tiled(m, d, T, m->H, m->F);
 }
 
-// The transformer layers (engine.rs:95-116) on T tokens described by d_tokens / d_tok_*.
-int32_t run_layers(lc_model* m, int T, bool decode_step) {
-    LC_TRY(launch_embed(m->embed->typ, m->embed->view, m->embed->rows, m->embed->cols, m->d_tokens, T, m->d_hidden, m->stream));
-    m->launches_in_call += 1;
-    for (int l = 0; l < m->L; l++) {
-        LayerW& w = m->layers[l];
-        LC_TRY(attention_block(m, l, m->d_hidden, w.attn_norm, T, m->d_hidden, m->d_hidden2, decode_step));
-        LC_TRY(ffn_block(m, l, m->d_hidden2, w.ffn_norm, T, m->d_hidden2, m->d_hidden, decode_step));
+// The handles that make up the model `m` leads: itself, or every rank of an in-process group.
+std::vector<lc_model*> ranks_of(lc_model* m) {
+    if (!m->members.empty()) return m->members;
+    return std::vector<lc_model*>(1, m);
+}
+
+// Sum over the ranks of the partial rows the last column-cut product left, into each rank's pending destination.
+int32_t reduce_ranks(lc_model* lead, size_t count) {
+    if (lead->tp == 1) return LC_OK;
+    const int slot = lead->sums_in_call & 1;
+    std::vector<lc_model*> R = ranks_of(lead);
+    if (lead->use_dist) {
+        LC_TRY(dist_allreduce_sum(slot, lead->pending_dst, count, lead->stream));
+    } else {
+        LC_CHECK((int)R.size() == lead->tp, LC_ERR_STATE, "a model cut into %d ranks needs lc_dist_init or lc_model_group before it can run", lead->tp);
+        const float* src[8]; float* dst[8];
+        for (int r = 0; r < lead->tp; r++) { src[r] = R[r]->d_part[slot]; dst[r] = R[r]->pending_dst; }
+        LC_TRY(launch_group_sum(src, dst, lead->tp, count, lead->stream));
+    }
+    for (lc_model* m : R) { m->sums_in_call++; m->pending_dst = nullptr; }
+    lead->launches_in_call += 1;
+    return LC_OK;
+}
+
+// The transformer layers (engine.rs:95-116) on T tokens described by d_tokens / d_tok_*, for every rank of the model.
+int32_t run_layers(lc_model* lead, int T, bool decode_step) {
+    std::vector<lc_model*> R = ranks_of(lead);
+    for (lc_model* m : R) {
+        m->sums_in_call = 0;
+        LC_TRY(launch_embed(m->embed->typ, m->embed->view, m->embed->rows, m->embed->cols, m->d_tokens, T, m->d_hidden, m->stream));
+        m->launches_in_call += 1;
+    }
+    const size_t count = (size_t)T * lead->H;
+    for (int l = 0; l < lead->L; l++) {
+        for (lc_model* m : R) LC_TRY(attention_block(m, l, m->d_hidden, m->layers[l].attn_norm, T, m->d_hidden, m->d_hidden2, decode_step));
+        LC_TRY(reduce_ranks(lead, count));
+        for (lc_model* m : R) LC_TRY(ffn_block(m, l, m->d_hidden2, m->layers[l].ffn_norm, T, m->d_hidden2, m->d_hidden, decode_step));
+        LC_TRY(reduce_ranks(lead, count));
     }
     return LC_OK;
 }
 
 // Engine::forward (engine.rs:78-132): layers, then final norm + head on n_last rows.  identity_last:
 // every token is the last of its sequence (a decode step), so no gather is needed; otherwise the rows
-// listed in d_last_idx are gathered.  Logits land in d_logits rows row0.., greedy picks in d_next.
-int32_t forward_tokens(lc_model* m, int T, int n_last, bool identity_last, int row0) {
-    LC_TRY(run_layers(m, T, identity_last));
-    const float* last = m->d_hidden;
-    if (!identity_last) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(n_last);
-        cfg.blockDim = dim3(256);
-        cfg.stream = m->stream;
-        LC_CUDA(cudaLaunchKernelEx(&cfg, gather_rows_kernel, (const float*)m->d_hidden, (const int32_t*)m->d_last_idx, m->H, m->d_last));
+// listed in d_last_idx are gathered.  Logits (of this rank's vocabulary rows) land in d_logits rows row0.., greedy picks in d_next.
+int32_t forward_tokens(lc_model* lead, int T, int n_last, bool identity_last, int row0) {
+    LC_TRY(run_layers(lead, T, identity_last));
+    std::vector<lc_model*> R = ranks_of(lead);
+    for (lc_model* m : R) {
+        const float* last = m->d_hidden;
+        if (!identity_last) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(n_last);
+            cfg.blockDim = dim3(256);
+            cfg.stream = m->stream;
+            LC_CUDA(cudaLaunchKernelEx(&cfg, gather_rows_kernel, (const float*)m->d_hidden, (const int32_t*)m->d_last_idx, m->H, m->d_last));
+            m->launches_in_call += 1;
+            last = m->d_last;
+        }
+        GemvArgs h;
+        h.w = &m->head;
+        h.x = last;
+        h.norm_w = m->final_norm;
+        h.eps = m->cfg.rms_eps;
+        h.out = m->d_logits + (size_t)row0 * m->V;
+        LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
+        if (m->tp == 1) LC_TRY(launch_argmax(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->d_next + row0, m->stream));
+        else LC_TRY(launch_argmax_key(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->v0, m->d_key[0] + row0, m->stream));
         m->launches_in_call += 1;
-        last = m->d_last;
     }
-    GemvArgs h;
-    h.w = &m->head;
-    h.x = last;
-    h.norm_w = m->final_norm;
-    h.eps = m->cfg.rms_eps;
-    h.out = m->d_logits + (size_t)row0 * m->V;
-    LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
-    LC_TRY(launch_argmax(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->d_next + row0, m->stream));
-    m->launches_in_call += 1;
+    if (lead->tp > 1) {  // the pick over the whole vocabulary: the largest (logit, global index) key of the ranks
+        if (lead->use_dist) {
+            LC_TRY(dist_allreduce_max(0, lead->d_key_max, (size_t)(row0 + n_last), lead->stream));
+        } else {
+            LC_CHECK((int)R.size() == lead->tp, LC_ERR_STATE, "a model cut into %d ranks needs lc_dist_init or lc_model_group before it can run", lead->tp);
+            const long long* src[8]; long long* dst[8];
+            for (int r = 0; r < lead->tp; r++) { src[r] = R[r]->d_key[0]; dst[r] = R[r]->d_key_max; }
+            LC_TRY(launch_group_max(src, dst, lead->tp, (size_t)(row0 + n_last), lead->stream));
+        }
+        for (lc_model* m : R) LC_TRY(launch_key_to_token(m->d_key_max + row0, n_last, m->d_next + row0, m->stream));
+        lead->launches_in_call += 1 + (uint64_t)R.size();
+    }
     return LC_OK;
 }
 
@@ -519,8 +630,24 @@ int32_t lc_model_create(const lc_model_config* cfg, lc_model** out) {
     if (m->cfg.max_seqs <= 0) m->cfg.max_seqs = 1;
     if (m->cfg.kv_page_tokens <= 0) m->cfg.kv_page_tokens = 16;
     m->device = cfg->device;
-    m->H = cfg->hidden_size; m->L = cfg->num_layers; m->nh = cfg->num_heads; m->nkv = cfg->num_kv_heads;
-    m->hd = m->H / m->nh; m->F = cfg->intermediate_size; m->V = cfg->vocab_size;
+    // model parallelism: explicit in the config, or the world of lc_dist_init
+    int tp = cfg->tp_size, rk = cfg->tp_rank;
+    if (tp <= 0) { tp = dist_active() ? dist_world() : 1; rk = dist_active() ? dist_rank() : 0; }
+    if (tp < 1 || tp > 8 || rk < 0 || rk >= tp) { delete m; set_error("tp_size %d / tp_rank %d outside 1..8 / 0..tp_size-1", tp, rk); return LC_ERR_INVALID; }
+    const bool experts = cfg->n_experts > 0;
+    if (tp > 1 && (cfg->num_heads % tp || cfg->num_kv_heads % tp || cfg->vocab_size % tp || (experts ? cfg->n_experts % tp : cfg->intermediate_size % tp))) {
+        delete m;
+        set_error("a model of %d heads / %d kv heads / vocabulary %d / %s %d cannot be cut into %d ranks", cfg->num_heads, cfg->num_kv_heads,
+                  cfg->vocab_size, experts ? "experts" : "FFN rows", experts ? cfg->n_experts : cfg->intermediate_size, tp);
+        return LC_ERR_INVALID;
+    }
+    m->tp = tp; m->rank = rk;
+    m->cfg.tp_size = tp; m->cfg.tp_rank = rk;
+    m->use_dist = tp > 1 && dist_active() && dist_world() == tp && dist_rank() == rk;
+    m->H = cfg->hidden_size; m->L = cfg->num_layers; m->nh = cfg->num_heads / tp; m->nkv = cfg->num_kv_heads / tp;
+    m->hd = m->H / cfg->num_heads; m->F = experts ? cfg->intermediate_size : cfg->intermediate_size / tp; m->V = cfg->vocab_size / tp;
+    m->v0 = m->V * rk;
+    m->El = experts ? cfg->n_experts / tp : 0; m->e0 = m->El * rk;
     m->nqkv = (m->nh + 2 * m->nkv) * m->hd;
     m->page_tokens = m->cfg.kv_page_tokens;
     m->max_seqs = m->cfg.max_seqs;
@@ -535,23 +662,35 @@ int32_t lc_model_create(const lc_model_config* cfg, lc_model** out) {
     return LC_OK;
 }
 
-static int32_t put_tensor(lc_model* m, const char* name, uint32_t typ, const uint64_t* dims, int32_t ndims, DevTensor** out_t) {
+// Registers a tensor given by its WHOLE dims and allocates this rank's part of it.  *out_t = null when the rank keeps
+// nothing of it (an expert of another rank).
+static int32_t put_tensor(lc_model* m, const char* name, uint32_t typ, const uint64_t* dims, int32_t ndims, DevTensor** out_t, ShardPlan* out_plan,
+                          QuantGeom* out_geom) {
     LC_TRY(check_model(m, false));
     LC_CHECK(!m->finalized, LC_ERR_STATE, "model already finalized");
     LC_CHECK(name && dims && ndims >= 1 && ndims <= 4, LC_ERR_INVALID, "set_tensor: bad argument");
     QuantGeom g;
     LC_CHECK(quant_geom(typ, &g), LC_ERR_UNSUPPORTED, "tensor %s: unsupported ggml type %u", name, typ);
-    size_t count = 1;
-    for (int i = 0; i < ndims; i++) count *= dims[i];
     LC_CHECK(dims[0] % g.block_elems == 0, LC_ERR_INVALID, "tensor %s: row length %llu is not a whole number of blocks", name,
              (unsigned long long)dims[0]);
     std::string key = canonical_name(name);
+    ShardPlan pl;
+    LC_TRY(shard_plan(m->cfg, m->tp, m->rank, key, dims, ndims, &pl));
+    *out_plan = pl;
+    *out_geom = g;
+    *out_t = nullptr;
+    if (pl.kind == SHARD_NONE) return LC_OK;
+    if (pl.kind == SHARD_COLS)
+        LC_CHECK(pl.count % g.block_elems == 0 && pl.first % g.block_elems == 0, LC_ERR_INVALID,
+                 "tensor %s: a column part of %llu elements is not a whole number of %u-element blocks", name, (unsigned long long)pl.count, g.block_elems);
+    uint64_t total_rows = 1;
+    for (int i = 1; i < ndims; i++) total_rows *= dims[i];
     DevTensor t;
     t.typ = typ;
     t.dims.assign(dims, dims + ndims);
-    t.nbytes = lc_tensor_bytes(typ, count);
-    t.cols = dims[0];  // loader.rs:155: GGUF dims are fastest-first, rows = dims[1]
-    t.rows = ndims >= 2 ? count / dims[0] : 1;
+    t.cols = pl.kind == SHARD_COLS ? pl.count : dims[0];  // loader.rs:155: GGUF dims are fastest-first, rows = dims[1]
+    t.rows = pl.kind == SHARD_ROWS ? pl.count : total_rows;
+    t.nbytes = lc_tensor_bytes(typ, t.rows * t.cols);
     auto it = m->tensors.find(key);
     if (it != m->tensors.end() && it->second.dev) cudaFree(it->second.dev);
     LC_TRY(dalloc((uint8_t**)&t.dev, t.nbytes));
@@ -567,9 +706,22 @@ int32_t lc_model_set_tensor(lc_model* m, const char* name, uint32_t typ, const u
     DeviceGuard dg(m->device);
     LC_CHECK(bytes, LC_ERR_INVALID, "set_tensor: null bytes");
     DevTensor* t = nullptr;
-    LC_TRY(put_tensor(m, name, typ, dims, ndims, &t));
-    LC_CHECK(t->nbytes == nbytes, LC_ERR_INVALID, "tensor %s: %zu bytes given, %zu expected", name, nbytes, t->nbytes);
-    LC_CUDA(cudaMemcpyAsync(t->dev, bytes, nbytes, cudaMemcpyHostToDevice, m->stream));
+    ShardPlan pl;
+    QuantGeom g;
+    LC_TRY(put_tensor(m, name, typ, dims, ndims, &t, &pl, &g));
+    size_t count = 1;
+    for (int i = 0; i < ndims; i++) count *= dims[i];
+    LC_CHECK(lc_tensor_bytes(typ, count) == nbytes, LC_ERR_INVALID, "tensor %s: %zu bytes given, %zu expected", name, nbytes, lc_tensor_bytes(typ, count));
+    if (!t) return LC_OK;
+    const size_t full_row_bytes = (size_t)dims[0] / g.block_elems * g.block_bytes;
+    const uint8_t* src = (const uint8_t*)bytes;
+    if (pl.kind == SHARD_COLS) {
+        const size_t part = (size_t)pl.count / g.block_elems * g.block_bytes, off = (size_t)pl.first / g.block_elems * g.block_bytes;
+        LC_CUDA(cudaMemcpy2DAsync(t->dev, part, src + off, full_row_bytes, part, t->rows, cudaMemcpyHostToDevice, m->stream));
+    } else {
+        const size_t off = pl.kind == SHARD_ROWS ? (size_t)pl.first * full_row_bytes : 0;
+        LC_CUDA(cudaMemcpyAsync(t->dev, src + off, t->nbytes, cudaMemcpyHostToDevice, m->stream));
+    }
     LC_CUDA(cudaStreamSynchronize(m->stream));
     return LC_OK;
 }
@@ -579,11 +731,15 @@ int32_t lc_model_synth_tensor(lc_model* m, const char* name, uint32_t typ, const
     LC_TRY(check_model(m, false));
     DeviceGuard dg(m->device);
     DevTensor* t = nullptr;
-    LC_TRY(put_tensor(m, name, typ, dims, ndims, &t));
-    size_t count = 1;
-    for (int i = 0; i < ndims; i++) count *= dims[i];
+    ShardPlan pl;
+    QuantGeom g;
+    LC_TRY(put_tensor(m, name, typ, dims, ndims, &t, &pl, &g));
+    if (!t) return LC_OK;
     std::string key = canonical_name(name);
-    LC_TRY(launch_synth(typ, seed, lcs_fnv1a(key.c_str()), sigma, count, t->dev, m->stream));
+    const size_t row_blocks = (size_t)dims[0] / g.block_elems;
+    const size_t row0 = pl.kind == SHARD_ROWS ? (size_t)pl.first : 0;
+    const size_t blk0 = pl.kind == SHARD_COLS ? (size_t)pl.first / g.block_elems : 0;
+    LC_TRY(launch_synth_part(typ, seed, lcs_fnv1a(key.c_str()), sigma, row_blocks, row0, t->rows, blk0, t->cols / g.block_elems, t->dev, m->stream));
     LC_CUDA(cudaStreamSynchronize(m->stream));
     return LC_OK;
 }
@@ -635,13 +791,13 @@ static int32_t expert_weight(lc_model* m, int l, int e, const char* which, int n
     const std::string stacked = p + which + "_exps.weight";
     auto it = m->tensors.find(stacked);
     LC_CHECK(it != m->tensors.end(), LC_ERR_MISSING, "missing tensor %s (or %s)", single.c_str(), stacked.c_str());
-    DevTensor& t = it->second;
-    LC_CHECK((int)t.cols == k && t.rows == (size_t)n * m->cfg.n_experts, LC_ERR_INVALID, "tensor %s is [%zu x %zu], expected [%d x %d] per expert",
+    DevTensor& t = it->second;  // this rank's experts e0 .. e0 + El - 1 of the stacked tensor
+    LC_CHECK((int)t.cols == k && t.rows == (size_t)n * m->El, LC_ERR_INVALID, "tensor %s is [%zu x %zu], expected [%d x %d] per expert",
              stacked.c_str(), t.rows, t.cols, n, k);
     QuantGeom g;
     LC_CHECK(quant_geom(t.typ, &g), LC_ERR_UNSUPPORTED, "tensor %s: unsupported type", stacked.c_str());
     const size_t row_bytes = (size_t)k / g.block_elems * g.block_bytes;
-    return qweight_init(w, t.typ, (const uint8_t*)t.view + (size_t)e * n * row_bytes, n, k);
+    return qweight_init(w, t.typ, (const uint8_t*)t.view + (size_t)(e - m->e0) * n * row_bytes, n, k);
 }
 
 static int32_t finalize_experts(lc_model* m, int l) {
@@ -649,22 +805,23 @@ static int32_t finalize_experts(lc_model* m, int l) {
     const int E = m->cfg.n_experts, H = m->H, F = m->F;
     const std::string p = "blk." + std::to_string(l) + ".";
     LC_TRY(gain_f32(m, p + "ffn_gate_inp.weight", E * H, &w.router));
-    w.egate.resize(E); w.eup.resize(E); w.edown.resize(E);
+    const int El = m->El;  // the experts this rank holds: e0 .. e0 + El - 1, stored at 0 .. El - 1
+    w.egate.resize(El); w.eup.resize(El); w.edown.resize(El);
     bool q4k = true;
-    for (int e = 0; e < E; e++) {
-        LC_TRY(expert_weight(m, l, e, "ffn_gate", F, H, &w.egate[e]));
-        LC_TRY(expert_weight(m, l, e, "ffn_up", F, H, &w.eup[e]));
-        LC_TRY(expert_weight(m, l, e, "ffn_down", H, F, &w.edown[e]));
-        LC_CHECK(w.egate[e].typ == w.eup[e].typ, LC_ERR_UNSUPPORTED, "layer %d expert %d: gate/up projections have different quant types", l, e);
+    for (int e = 0; e < El; e++) {
+        LC_TRY(expert_weight(m, l, m->e0 + e, "ffn_gate", F, H, &w.egate[e]));
+        LC_TRY(expert_weight(m, l, m->e0 + e, "ffn_up", F, H, &w.eup[e]));
+        LC_TRY(expert_weight(m, l, m->e0 + e, "ffn_down", H, F, &w.edown[e]));
+        LC_CHECK(w.egate[e].typ == w.eup[e].typ, LC_ERR_UNSUPPORTED, "layer %d expert %d: gate/up projections have different quant types", l, m->e0 + e);
         for (const QWeight* q : {&w.egate[e], &w.eup[e], &w.edown[e]}) q4k = q4k && q->typ == LC_TYPE_Q4_K && q->has_tmap;
     }
     w.grouped_ok = q4k && qgemv_mma_supports(H) && qgemv_mma_supports(F);
     if (w.grouped_ok) {
-        std::vector<unsigned char> host((size_t)E * 128);
+        std::vector<unsigned char> host((size_t)El * 128);
         const std::vector<QWeight>* sets[3] = {&w.egate, &w.eup, &w.edown};
         void** dst[3] = {&w.tm_gate, &w.tm_up, &w.tm_down};
         for (int i = 0; i < 3; i++) {
-            for (int e = 0; e < E; e++) memcpy(&host[(size_t)e * 128], (*sets[i])[e].tmap, 128);
+            for (int e = 0; e < El; e++) memcpy(&host[(size_t)e * 128], (*sets[i])[e].tmap, 128);
             LC_TRY(dalloc((uint8_t**)dst[i], host.size()));
             m->owned.push_back(*dst[i]);
             LC_CUDA(cudaMemcpyAsync(*dst[i], host.data(), host.size(), cudaMemcpyHostToDevice, m->stream));
@@ -674,7 +831,8 @@ static int32_t finalize_experts(lc_model* m, int l) {
     uint64_t each = 0;
     for (const QWeight* q : {&w.egate[0], &w.eup[0], &w.edown[0]}) each += (uint64_t)q->n * q->row_bytes;
     m->expert_bytes_each = each;
-    m->expert_bytes_all += each * E;
+    m->expert_bytes_all += each * El;
+    (void)E;
     return LC_OK;
 }
 
@@ -730,8 +888,14 @@ int32_t lc_model_finalize(lc_model* m) {
     }
     LC_TRY(gain_f32(m, "output_norm.weight", H, &m->final_norm));
     // loader.rs:192-199: tied head when output.weight is absent
-    std::string head = m->tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
-    LC_TRY(weight_of(m, head, V, H, &m->head, nullptr));
+    if (m->tensors.count("output.weight")) {
+        LC_TRY(weight_of(m, "output.weight", V, H, &m->head, nullptr));
+    } else {  // tied: this rank's vocabulary rows of the (whole) embedding table
+        const DevTensor& e = *m->embed;
+        LC_CHECK((int)e.rows == m->cfg.vocab_size, LC_ERR_INVALID, "token_embd.weight has %zu rows, vocabulary is %d", e.rows, m->cfg.vocab_size);
+        const size_t row_bytes = e.nbytes / e.rows;
+        LC_TRY(qweight_init(&m->head, e.typ, (const uint8_t*)e.view + (size_t)m->v0 * row_bytes, V, H));
+    }
 
     // weight sanity scan (loader.rs:241-249) and resident byte count
     LC_TRY(dalloc(&m->d_sanity, 1));
@@ -799,6 +963,20 @@ int32_t lc_model_finalize(lc_model* m) {
     }
     LC_TRY(dalloc(&m->d_last, (size_t)m->max_seqs * H)); LC_TRY(dalloc(&m->d_logits, (size_t)m->max_seqs * V));
     LC_TRY(dalloc(&m->d_next, m->max_seqs)); LC_TRY(dalloc(&m->d_step_ctr, 1));
+    if (m->tp > 1) {
+        // partial rows of the column-cut products and the greedy-pick keys: in the buffers the other ranks can read when the
+        // ranks are processes (a collective call: every rank finalizes its model at the same point), else plain memory
+        LC_TRY(dalloc(&m->d_key_max, (size_t)m->max_seqs));
+        if (m->use_dist) {
+            LC_CHECK(m->max_seqs <= 512, LC_ERR_UNSUPPORTED, "a model cut across processes decodes at most 512 sequences together");
+            LC_TRY(dist_reserve((size_t)T * H * sizeof(float)));
+            for (int i = 0; i < 2; i++) { m->d_part[i] = dist_slot(i); m->d_key[i] = dist_key_slot(i); }
+            LC_TRY(dalloc(&m->d_logits_all, (size_t)m->max_seqs * m->cfg.vocab_size));
+        } else {
+            for (int i = 0; i < 2; i++) { LC_TRY(dalloc(&m->d_part[i], (size_t)T * H)); LC_TRY(dalloc(&m->d_key[i], (size_t)m->max_seqs)); }
+            m->part_owned = true;
+        }
+    }
     size_t sc = 16;
     for (int t = 1; t <= T; t++) sc = std::max(sc, attention_scratch_bytes(t, m->nh, m->hd, m->cfg.max_seq_len));
     m->attn_scratch_bytes = sc;
@@ -807,7 +985,7 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_CUDA(cudaMemsetAsync(m->d_attn_counters, 0, (size_t)T * m->nh * sizeof(int), m->stream));
     LC_CUDA(cudaHostAlloc((void**)&m->pin_tokens, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
     LC_CUDA(cudaHostAlloc((void**)&m->pin_next, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
-    LC_CUDA(cudaHostAlloc((void**)&m->pin_logits, (size_t)m->max_seqs * V * 4, cudaHostAllocDefault));
+    LC_CUDA(cudaHostAlloc((void**)&m->pin_logits, (size_t)m->max_seqs * m->cfg.vocab_size * 4, cudaHostAllocDefault));
     LC_TRY(reserve_out_tokens(m, (size_t)1024 * m->max_seqs));
     LC_CUDA(cudaEventCreate(&m->ev0));
     LC_CUDA(cudaEventCreate(&m->ev1));
@@ -826,7 +1004,14 @@ int32_t lc_model_destroy(lc_model* m) {
     for (void* p : m->owned) cudaFree(p);
     for (void* p : m->k_pools) cudaFree(p);
     for (void* p : m->v_pools) cudaFree(p);
-    void* bufs[] = {m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
+    if (m->part_owned) for (int i = 0; i < 2; i++) { cudaFree(m->d_part[i]); cudaFree(m->d_key[i]); }
+    if (m->leader) {  // leaving a group: the leader must not drive this handle any more
+        auto& mem = m->leader->members;
+        for (lc_model* x : mem) if (x != m->leader) x->leader = nullptr;
+        mem.clear();
+    }
+    for (lc_model* x : m->members) if (x != m) x->leader = nullptr;
+    void* bufs[] = {m->d_key_max, m->d_logits_all, m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
                     m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};
@@ -848,16 +1033,50 @@ int32_t lc_model_get_config(const lc_model* m, lc_model_config* out) {
     return LC_OK;
 }
 
-int32_t lc_kv_clear(lc_model* m, int32_t seq_id) {
-    LC_TRY(check_model(m, true));
-    LC_CHECK(seq_id >= -1 && seq_id < m->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_id, m->max_seqs - 1);
-    for (int s = 0; s < m->max_seqs; s++) {
-        if (seq_id >= 0 && s != seq_id) continue;
-        for (int p : m->seq_pages[s]) m->free_pages.push_back(p);
-        m->seq_pages[s].clear();
-        m->seq_len[s] = 0;
+// A handle that another handle drives (rank > 0 of an in-process group) takes no model-level calls of its own.
+static int32_t check_drivable(const lc_model* m) {
+    LC_CHECK(m->leader == nullptr, LC_ERR_STATE, "this handle is rank %d of a group: make the call on the group's first handle", m->rank);
+    return LC_OK;
+}
+
+int32_t lc_model_group(lc_model** handles, int32_t n) {
+    LC_CHECK(handles && n >= 2 && n <= 8, LC_ERR_INVALID, "lc_model_group: 2..8 handles");
+    for (int r = 0; r < n; r++) {
+        lc_model* m = handles[r];
+        LC_TRY(check_model(m, true));
+        LC_CHECK(m->tp == n && m->rank == r && !m->use_dist && m->members.empty() && !m->leader, LC_ERR_INVALID,
+                 "lc_model_group: handle %d must be rank %d of %d, not yet grouped and not a rank of lc_dist_init", r, r, n);
+        LC_CHECK(m->device == handles[0]->device && m->H == handles[0]->H && m->L == handles[0]->L && m->t_cap == handles[0]->t_cap &&
+                     m->max_seqs == handles[0]->max_seqs && m->cfg.max_seq_len == handles[0]->cfg.max_seq_len,
+                 LC_ERR_INVALID, "lc_model_group: the handles must be parts of one model on one device");
     }
-    m->meta_valid = false;
+    handles[0]->members.assign(handles, handles + n);
+    for (int r = 1; r < n; r++) handles[r]->leader = handles[0];
+    return LC_OK;
+}
+
+int32_t lc_shard_plan(const lc_model_config* cfg, const char* name, const uint64_t* dims, int32_t ndims, int32_t* kind, uint64_t* first,
+                      uint64_t* count) {
+    LC_CHECK(cfg && name && dims && ndims >= 1 && ndims <= 4 && kind && first && count, LC_ERR_INVALID, "lc_shard_plan: bad argument");
+    ShardPlan pl;
+    LC_TRY(shard_plan(*cfg, cfg->tp_size, cfg->tp_rank, canonical_name(name), dims, ndims, &pl));
+    *kind = pl.kind; *first = pl.first; *count = pl.count;
+    return LC_OK;
+}
+
+int32_t lc_kv_clear(lc_model* lead, int32_t seq_id) {
+    LC_TRY(check_model(lead, true));
+    LC_TRY(check_drivable(lead));
+    LC_CHECK(seq_id >= -1 && seq_id < lead->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_id, lead->max_seqs - 1);
+    for (lc_model* m : ranks_of(lead)) {
+        for (int s = 0; s < m->max_seqs; s++) {
+            if (seq_id >= 0 && s != seq_id) continue;
+            for (int p : m->seq_pages[s]) m->free_pages.push_back(p);
+            m->seq_pages[s].clear();
+            m->seq_len[s] = 0;
+        }
+        m->meta_valid = false;
+    }
     return LC_OK;
 }
 
@@ -866,7 +1085,7 @@ int32_t lc_kv_memory_bytes(const lc_model* m, uint64_t* out) {
     LC_CHECK(out, LC_ERR_INVALID, "null output");
     uint64_t tokens = 0;
     for (int v : m->seq_len) tokens += v;
-    *out = tokens * (uint64_t)m->L * 2 * m->nkv * m->hd * m->kv_elt;  // cache/mod.rs:80-84
+    *out = tokens * (uint64_t)m->L * 2 * m->cfg.num_kv_heads * m->hd * m->kv_elt;  // cache/mod.rs:80-84, over all ranks
     return LC_OK;
 }
 
@@ -877,82 +1096,116 @@ int32_t lc_kv_length(const lc_model* m, int32_t seq_id, int32_t* out) {
     return LC_OK;
 }
 
-int32_t lc_forward_batch(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* tokens, const int32_t* n_tokens,
+// The logits rows [0, n_rows) of the whole vocabulary on the host: a whole model copies them; a cut model puts the ranks'
+// vocabulary slices side by side (an all-gather when the ranks are processes).
+static int32_t fetch_logits(lc_model* lead, int n_rows, float* host_out) {
+    const int Vfull = lead->cfg.vocab_size, Vl = lead->V;
+    if (lead->tp == 1) {
+        LC_CUDA(cudaMemcpyAsync(lead->pin_logits, lead->d_logits, (size_t)n_rows * Vfull * 4, cudaMemcpyDeviceToHost, lead->stream));
+        LC_CUDA(cudaStreamSynchronize(lead->stream));
+        memcpy(host_out, lead->pin_logits, (size_t)n_rows * Vfull * 4);
+        return LC_OK;
+    }
+    if (lead->use_dist) {
+        LC_TRY(dist_allgather(lead->d_logits, lead->d_logits_all, (size_t)n_rows * Vl * 4, lead->stream));
+        LC_CUDA(cudaMemcpyAsync(lead->pin_logits, lead->d_logits_all, (size_t)n_rows * Vfull * 4, cudaMemcpyDeviceToHost, lead->stream));
+        LC_CUDA(cudaStreamSynchronize(lead->stream));
+        for (int r = 0; r < lead->tp; r++)
+            for (int row = 0; row < n_rows; row++)
+                memcpy(host_out + (size_t)row * Vfull + (size_t)r * Vl, lead->pin_logits + ((size_t)r * n_rows + row) * Vl, (size_t)Vl * 4);
+        return LC_OK;
+    }
+    std::vector<lc_model*> R = ranks_of(lead);
+    for (int r = 0; r < lead->tp; r++)
+        LC_CUDA(cudaMemcpy2DAsync(lead->pin_logits + (size_t)r * Vl, (size_t)Vfull * 4, R[r]->d_logits, (size_t)Vl * 4, (size_t)Vl * 4, (size_t)n_rows,
+                                  cudaMemcpyDeviceToHost, lead->stream));
+    LC_CUDA(cudaStreamSynchronize(lead->stream));
+    memcpy(host_out, lead->pin_logits, (size_t)n_rows * Vfull * 4);
+    return LC_OK;
+}
+
+int32_t lc_forward_batch(lc_model* lead, int32_t n_seqs, const int32_t* seq_ids, const int64_t* tokens, const int32_t* n_tokens,
                          float* logits_out, int64_t* next_out) {
-    LC_TRY(check_model(m, true));
-    LC_CHECK(n_seqs >= 1 && n_seqs <= m->max_seqs && seq_ids && tokens && n_tokens, LC_ERR_INVALID, "forward_batch: bad argument");
-    DeviceGuard dg(m->device);
+    LC_TRY(check_model(lead, true));
+    LC_TRY(check_drivable(lead));
+    LC_CHECK(n_seqs >= 1 && n_seqs <= lead->max_seqs && seq_ids && tokens && n_tokens, LC_ERR_INVALID, "forward_batch: bad argument");
+    DeviceGuard dg(lead->device);
+    std::vector<lc_model*> R = ranks_of(lead);
     int total = 0, longest = 0;
     for (int i = 0; i < n_seqs; i++) {
-        LC_CHECK(seq_ids[i] >= 0 && seq_ids[i] < m->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_ids[i], m->max_seqs - 1);
+        LC_CHECK(seq_ids[i] >= 0 && seq_ids[i] < lead->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_ids[i], lead->max_seqs - 1);
         for (int j = 0; j < i; j++) LC_CHECK(seq_ids[j] != seq_ids[i], LC_ERR_INVALID, "sequence id %d listed twice", seq_ids[i]);
         LC_CHECK(n_tokens[i] >= 1, LC_ERR_INVALID, "sequence %d has no tokens in this call", seq_ids[i]);
-        LC_TRY(ensure_pages(m, seq_ids[i], m->seq_len[seq_ids[i]] + n_tokens[i]));
+        for (lc_model* m : R) LC_TRY(ensure_pages(m, seq_ids[i], m->seq_len[seq_ids[i]] + n_tokens[i]));
         total += n_tokens[i];
         longest = std::max(longest, n_tokens[i]);
     }
-    LC_TRY(sync_page_table(m));
+    for (lc_model* m : R) LC_TRY(sync_page_table(m));
     if (longest == 1) {
         // a decode step: token ids in (pinned staging), graph replay, picks and logits out
-        LC_TRY(reserve_out_tokens(m, (size_t)n_seqs));
-        LC_TRY(stage_decode_meta(m, n_seqs, seq_ids, tokens));
-        LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
-        LC_TRY(run_decode_steps(m, n_seqs, 1));
-        if (logits_out) LC_CUDA(cudaMemcpyAsync(m->pin_logits, m->d_logits, (size_t)n_seqs * m->V * 4, cudaMemcpyDeviceToHost, m->stream));
-        if (next_out) LC_CUDA(cudaMemcpyAsync(m->pin_next, m->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, m->stream));
-        LC_CUDA(cudaStreamSynchronize(m->stream));
-        if (logits_out) memcpy(logits_out, m->pin_logits, (size_t)n_seqs * m->V * 4);
-        if (next_out) memcpy(next_out, m->pin_next, (size_t)n_seqs * 8);
-        after_decode_steps(m, n_seqs, seq_ids, 1);
-        finish_call(m);
-        return check_device_flag(m);
+        for (lc_model* m : R) {
+            LC_TRY(reserve_out_tokens(m, (size_t)n_seqs));
+            LC_TRY(stage_decode_meta(m, n_seqs, seq_ids, tokens));
+            LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
+        }
+        LC_TRY(run_decode_steps(lead, n_seqs, 1));
+        if (next_out) LC_CUDA(cudaMemcpyAsync(lead->pin_next, lead->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, lead->stream));
+        if (logits_out) LC_TRY(fetch_logits(lead, n_seqs, logits_out));
+        LC_CUDA(cudaStreamSynchronize(lead->stream));
+        if (next_out) memcpy(next_out, lead->pin_next, (size_t)n_seqs * 8);
+        for (lc_model* m : R) { after_decode_steps(m, n_seqs, seq_ids, 1); finish_call(m); }
+        return check_device_flag(lead);
     }
-    m->meta_valid = false;
+    for (lc_model* m : R) m->meta_valid = false;
     // Rotary index = position inside the CALL (reference mode, attention.rs:13-21) or the cache position.
-    if (total <= m->t_cap) {
+    if (total <= lead->t_cap) {
         std::vector<int64_t> tok; std::vector<int32_t> seq, pos, rope, last;
         int off = 0;
         for (int i = 0; i < n_seqs; i++) {
             for (int t = 0; t < n_tokens[i]; t++) {
-                int p = m->seq_len[seq_ids[i]] + t;
+                int p = lead->seq_len[seq_ids[i]] + t;
                 tok.push_back(tokens[off + t]); seq.push_back(seq_ids[i]); pos.push_back(p);
-                rope.push_back(m->cfg.rope_mode ? p : t);
+                rope.push_back(lead->cfg.rope_mode ? p : t);
             }
             off += n_tokens[i];
             last.push_back(off - 1);
         }
-        LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
-        LC_TRY(forward_tokens(m, total, n_seqs, total == n_seqs, 0));
+        for (lc_model* m : R) LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
+        LC_TRY(forward_tokens(lead, total, n_seqs, total == n_seqs, 0));
     } else {
         // long prompts: one sequence after the other, each in chunks of t_cap tokens over its growing cache
         int off = 0;
         for (int i = 0; i < n_seqs; i++) {
-            for (int c0 = 0; c0 < n_tokens[i]; c0 += m->t_cap) {
-                int T = std::min(m->t_cap, n_tokens[i] - c0);
+            for (int c0 = 0; c0 < n_tokens[i]; c0 += lead->t_cap) {
+                int T = std::min(lead->t_cap, n_tokens[i] - c0);
                 std::vector<int64_t> tok(T); std::vector<int32_t> seq(T, seq_ids[i]), pos(T), rope(T), last(1, T - 1);
                 for (int t = 0; t < T; t++) {
                     tok[t] = tokens[off + c0 + t];
-                    pos[t] = m->seq_len[seq_ids[i]] + c0 + t;
-                    rope[t] = m->cfg.rope_mode ? pos[t] : (c0 + t);
+                    pos[t] = lead->seq_len[seq_ids[i]] + c0 + t;
+                    rope[t] = lead->cfg.rope_mode ? pos[t] : (c0 + t);
                 }
-                LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
-                if (c0 + T == n_tokens[i]) LC_TRY(forward_tokens(m, T, 1, T == 1, i));
-                else LC_TRY(run_layers(m, T, false));
+                for (lc_model* m : R) LC_TRY(upload_meta(m, tok, seq, pos, rope, last));
+                if (c0 + T == n_tokens[i]) LC_TRY(forward_tokens(lead, T, 1, T == 1, i));
+                else LC_TRY(run_layers(lead, T, false));
             }
             off += n_tokens[i];
         }
     }
-    for (int i = 0; i < n_seqs; i++) m->seq_len[seq_ids[i]] += n_tokens[i];
-    if (logits_out) LC_CUDA(cudaMemcpyAsync(logits_out, m->d_logits, (size_t)n_seqs * m->V * 4, cudaMemcpyDeviceToHost, m->stream));
-    if (next_out) LC_CUDA(cudaMemcpyAsync(next_out, m->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, m->stream));
-    LC_CUDA(cudaStreamSynchronize(m->stream));
-    m->ctr.forward_calls += 1;
-    m->ctr.tokens_prefilled += total;
-    uint64_t used = 0;
-    for (auto& pg : m->seq_pages) used += pg.size();
-    m->ctr.kv_pages_in_use = used;
-    finish_call(m);
-    return LC_OK;
+    for (lc_model* m : R)
+        for (int i = 0; i < n_seqs; i++) m->seq_len[seq_ids[i]] += n_tokens[i];
+    if (next_out) LC_CUDA(cudaMemcpyAsync(lead->pin_next, lead->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, lead->stream));
+    if (logits_out) LC_TRY(fetch_logits(lead, n_seqs, logits_out));
+    LC_CUDA(cudaStreamSynchronize(lead->stream));
+    if (next_out) memcpy(next_out, lead->pin_next, (size_t)n_seqs * 8);
+    for (lc_model* m : R) {
+        m->ctr.forward_calls += 1;
+        m->ctr.tokens_prefilled += total;
+        uint64_t used = 0;
+        for (auto& pg : m->seq_pages) used += pg.size();
+        m->ctr.kv_pages_in_use = used;
+        finish_call(m);
+    }
+    return check_device_flag(lead);
 }
 
 int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_out) {
@@ -963,34 +1216,39 @@ int32_t lc_forward(lc_model* m, const int64_t* tokens, int32_t n, float* logits_
 
 // Queues `steps` greedy decode steps for the n_seqs sequences whose metadata is on the device.  The first
 // step of a new batch width runs eagerly (it sets kernel attributes), then one step is captured into a
-// CUDA graph that later steps replay.
+// CUDA graph that later steps replay.  For an in-process group the one graph holds every rank's kernels.
 static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
+    std::vector<lc_model*> R = ranks_of(m);
     auto one_step = [&]() -> int32_t {
         LC_TRY(forward_tokens(m, n_seqs, n_seqs, true, 0));
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(1);
-        cfg.blockDim = dim3(std::max(32, (n_seqs + 31) / 32 * 32));
-        cfg.stream = m->stream;
-        LC_CUDA(cudaLaunchKernelEx(&cfg, advance_kernel, (const int64_t*)m->d_next, m->d_tokens, m->d_tok_pos, m->d_tok_rope, (int)n_seqs,
-                                   (int)m->cfg.rope_mode, m->d_out_tokens, m->d_step_ctr));
-        m->launches_in_call += 1;
+        for (lc_model* r : R) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1);
+            cfg.blockDim = dim3(std::max(32, (n_seqs + 31) / 32 * 32));
+            cfg.stream = r->stream;
+            LC_CUDA(cudaLaunchKernelEx(&cfg, advance_kernel, (const int64_t*)r->d_next, r->d_tokens, r->d_tok_pos, r->d_tok_rope, (int)n_seqs,
+                                       (int)r->cfg.rope_mode, r->d_out_tokens, r->d_step_ctr));
+            r->launches_in_call += 1;
+        }
         return LC_OK;
     };
+    auto launches_now = [&]() { uint64_t t = 0; for (lc_model* r : R) t += r->launches_in_call; return t; };
     static const bool no_graph = getenv("LC_NO_GRAPH") != nullptr;
     cudaGraphExec_t exec = nullptr;
     int done_steps = 0;
     auto it = m->decode_graphs.find(n_seqs);
     if (it != m->decode_graphs.end()) exec = it->second;
     if (!exec && !no_graph) {
-        uint64_t before = m->launches_in_call;
+        uint64_t before = launches_now();
         LC_TRY(one_step());
-        m->graph_nodes = (int)(m->launches_in_call - before);
+        m->graph_nodes = (int)(launches_now() - before);
         done_steps = 1;
         cudaGraph_t graph = nullptr;
         if (cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-            uint64_t keep = m->launches_in_call;
+            std::vector<uint64_t> keep;
+            for (lc_model* r : R) keep.push_back(r->launches_in_call);
             int32_t st = one_step();
-            m->launches_in_call = keep;
+            for (size_t i = 0; i < R.size(); i++) R[i]->launches_in_call = keep[i];
             cudaError_t e = cudaStreamEndCapture(m->stream, &graph);
             if (st == LC_OK && e == cudaSuccess && graph) {
                 if (cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) m->decode_graphs[n_seqs] = exec;
@@ -1018,8 +1276,9 @@ static int32_t reserve_out_tokens(lc_model* m, size_t need) {
     m->out_tokens_cap = 0;
     LC_TRY(dalloc(&m->d_out_tokens, need));
     m->out_tokens_cap = need;
-    for (auto& g : m->decode_graphs) cudaGraphExecDestroy(g.second);  // the graphs bake this pointer in
-    m->decode_graphs.clear();
+    lc_model* owner = m->leader ? m->leader : m;  // the graphs bake this pointer in; a group's graphs live on its first handle
+    for (auto& g : owner->decode_graphs) cudaGraphExecDestroy(g.second);
+    owner->decode_graphs.clear();
     return LC_OK;
 }
 
@@ -1052,7 +1311,7 @@ static void after_decode_steps(lc_model* m, int n_seqs, const int32_t* seq_ids, 
         if (cudaMemcpyAsync(&t, m->d_moe_touched, 8, cudaMemcpyDeviceToHost, m->stream) == cudaSuccess &&
             cudaMemsetAsync(m->d_moe_touched, 0, 8, m->stream) == cudaSuccess && cudaStreamSynchronize(m->stream) == cudaSuccess)
             m->touched_per_step = n_seqs <= kMoeGroupedTokens && m->layers[0].grouped_ok ? (double)t / std::max(steps, 1)
-                                                                                           : (double)m->L * m->cfg.n_experts;
+                                                                                           : (double)m->L * m->El;
     }
     std::vector<int> ctx;
     for (int i = 0; i < n_seqs; i++) {
@@ -1068,35 +1327,38 @@ static void after_decode_steps(lc_model* m, int n_seqs, const int32_t* seq_ids, 
     m->ctr.kv_pages_in_use = used;
 }
 
-int32_t lc_decode_loop(lc_model* m, int32_t n_seqs, const int32_t* seq_ids, const int64_t* first_tokens, int32_t steps,
+int32_t lc_decode_loop(lc_model* lead, int32_t n_seqs, const int32_t* seq_ids, const int64_t* first_tokens, int32_t steps,
                        int64_t* out_tokens, float* out_ms) {
-    LC_TRY(check_model(m, true));
-    LC_CHECK(n_seqs >= 1 && n_seqs <= m->max_seqs && seq_ids && first_tokens && steps >= 1, LC_ERR_INVALID, "decode_loop: bad argument");
-    DeviceGuard dg(m->device);
-    for (int i = 0; i < n_seqs; i++) {
-        LC_CHECK(seq_ids[i] >= 0 && seq_ids[i] < m->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_ids[i], m->max_seqs - 1);
-        for (int j = 0; j < i; j++) LC_CHECK(seq_ids[j] != seq_ids[i], LC_ERR_INVALID, "sequence id %d listed twice", seq_ids[i]);
-        LC_TRY(ensure_pages(m, seq_ids[i], m->seq_len[seq_ids[i]] + steps));  // pages for the whole loop up front
+    LC_TRY(check_model(lead, true));
+    LC_TRY(check_drivable(lead));
+    LC_CHECK(n_seqs >= 1 && n_seqs <= lead->max_seqs && seq_ids && first_tokens && steps >= 1, LC_ERR_INVALID, "decode_loop: bad argument");
+    DeviceGuard dg(lead->device);
+    std::vector<lc_model*> R = ranks_of(lead);
+    const size_t need = (size_t)steps * n_seqs;
+    for (lc_model* m : R) {
+        for (int i = 0; i < n_seqs; i++) {
+            LC_CHECK(seq_ids[i] >= 0 && seq_ids[i] < m->max_seqs, LC_ERR_INVALID, "sequence id %d outside 0..%d", seq_ids[i], m->max_seqs - 1);
+            for (int j = 0; j < i; j++) LC_CHECK(seq_ids[j] != seq_ids[i], LC_ERR_INVALID, "sequence id %d listed twice", seq_ids[i]);
+            LC_TRY(ensure_pages(m, seq_ids[i], m->seq_len[seq_ids[i]] + steps));  // pages for the whole loop up front
+        }
+        LC_TRY(sync_page_table(m));
+        LC_TRY(reserve_out_tokens(m, need));
+        LC_TRY(stage_decode_meta(m, n_seqs, seq_ids, first_tokens));
+        LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
     }
-    LC_TRY(sync_page_table(m));
-    size_t need = (size_t)steps * n_seqs;
-    LC_TRY(reserve_out_tokens(m, need));
-    LC_TRY(stage_decode_meta(m, n_seqs, seq_ids, first_tokens));
-    LC_CUDA(cudaMemsetAsync(m->d_step_ctr, 0, 4, m->stream));
-    LC_CUDA(cudaEventRecord(m->ev0, m->stream));
-    LC_TRY(run_decode_steps(m, n_seqs, steps));
-    LC_CUDA(cudaEventRecord(m->ev1, m->stream));
-    LC_CUDA(cudaEventSynchronize(m->ev1));
+    LC_CUDA(cudaEventRecord(lead->ev0, lead->stream));
+    LC_TRY(run_decode_steps(lead, n_seqs, steps));
+    LC_CUDA(cudaEventRecord(lead->ev1, lead->stream));
+    LC_CUDA(cudaEventSynchronize(lead->ev1));
     float ms = 0.f;
-    LC_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    LC_CUDA(cudaEventElapsedTime(&ms, lead->ev0, lead->ev1));
     if (out_ms) *out_ms = ms;
     if (out_tokens) {
-        LC_CUDA(cudaMemcpyAsync(out_tokens, m->d_out_tokens, need * 8, cudaMemcpyDeviceToHost, m->stream));
-        LC_CUDA(cudaStreamSynchronize(m->stream));
+        LC_CUDA(cudaMemcpyAsync(out_tokens, lead->d_out_tokens, need * 8, cudaMemcpyDeviceToHost, lead->stream));
+        LC_CUDA(cudaStreamSynchronize(lead->stream));
     }
-    after_decode_steps(m, n_seqs, seq_ids, steps);
-    finish_call(m);
-    return check_device_flag(m);
+    for (lc_model* m : R) { after_decode_steps(m, n_seqs, seq_ids, steps); finish_call(m); }
+    return check_device_flag(lead);
 }
 
 int32_t lc_model_set_seed(lc_model* m, uint64_t seed) {

@@ -178,15 +178,39 @@ struct MoeRouteArgs {
     int32_t* lists = nullptr;
     int list_stride = 0;
     unsigned long long* touched = nullptr;
+    int local_first = 0, local_count = 0;  // experts this rank holds (0 count = all): only those are counted in `touched`
 };
 int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s);
 // out[t] = residual[t] + sum_j wsel[t][j] * y[row(t, j)] in ascending expert order; mode 0: row = t * top_k + j,
-// mode 1: row = sel[t][j] * t_stride + t (every expert's outputs for every token, a plane of t_stride rows per expert)
+// mode 1: row = (sel[t][j] - local_first) * t_stride + t (every local expert's outputs for every token, a plane of t_stride
+// rows per expert); only the experts local_first .. local_first + local_count - 1 are added
 int32_t launch_moe_combine(const float* y, const int32_t* sel, const float* wsel, int top_k, int H, int T, int mode, size_t t_stride,
-                           const float* residual, float* out, cudaStream_t s);
+                           int local_first, int local_count, const float* residual, float* out, cudaStream_t s);
+
+// ---- dist.cu: sums over the ranks of a model cut across GPUs ----
+bool dist_active();
+int dist_rank();
+int dist_world();
+bool dist_peer_memory();
+int32_t dist_reserve(size_t slot_bytes);            // collective: room for sums of slot_bytes bytes
+float* dist_slot(int i);                            // where this rank writes the partial rows of a sum (i = 0, 1 alternate)
+long long* dist_key_slot(int i);                    // ... and its greedy-pick keys
+int32_t dist_allreduce_sum(int i, float* dst, size_t count, cudaStream_t s);
+int32_t dist_allreduce_max(int i, long long* dst, size_t count, cudaStream_t s);
+int32_t dist_allgather(const void* src, void* dst, size_t bytes, cudaStream_t s);
+// the same sums for ranks that are handles of one process on one GPU: one kernel over all ranks' rows
+int32_t launch_group_sum(const float* const* src, float* const* dst, int n, size_t count, cudaStream_t s);
+int32_t launch_group_max(const long long* const* src, long long* const* dst, int n, size_t count, cudaStream_t s);
 
 // ---- synth.cu ----
 int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_elems, void* out_dev,
                      cudaStream_t s);
+// Part of a [rows][row_blocks blocks] tensor: rows [row0, row0 + rows) x blocks [blk0, blk0 + blks) of every row, written
+// densely; the bytes equal the same region of the whole tensor.
+int32_t launch_synth_part(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t row_blocks, size_t row0, size_t rows,
+                          size_t blk0, size_t blks, void* out_dev, cudaStream_t s);
+// Greedy pick per row as a key: (total-order key of the maximum << 32) | (index_base + index), last of equal maxima.
+int32_t launch_argmax_key(const float* v, size_t n, size_t rows, int index_base, long long* out_keys, cudaStream_t s);
+int32_t launch_key_to_token(const long long* keys, size_t rows, int64_t* out_tokens, cudaStream_t s);
 
 }  // namespace lc

@@ -28,7 +28,7 @@ __device__ __forceinline__ int32_t total_key_f(float f) {  // orders f32 bit pat
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int H, int T, const float* __restrict__ w_router,
                  int E, int K, int32_t* __restrict__ sel, float* __restrict__ wsel, int32_t* __restrict__ cnt, int32_t* __restrict__ lists,
-                 int list_stride, unsigned long long* __restrict__ touched) {
+                 int list_stride, unsigned long long* __restrict__ touched, int local_first, int local_count) {
     __shared__ float scale_s[kRouteTokens];
     __shared__ float logit_s[kRouteTokens * kMaxExperts];
     __shared__ int sel_s[kRouteTokens * kMaxTopK];
@@ -92,20 +92,24 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, 
             for (int j = 0; j < K; j++)
                 if (sel_s[t * kMaxTopK + j] == e) lists[(size_t)e * list_stride + n++] = (t0 + t) * K + j;
         cnt[e] = n;
-        if (touched && n > 0) atomicAdd(touched, 1ull);
+        if (touched && n > 0 && e >= local_first && e < local_first + local_count) atomicAdd(touched, 1ull);
     }
 }
 
-// mode 0: row(t, j) = t * K + j (one row per slot); mode 1: row(t, j) = sel[t][j] * T_stride + t (a plane per expert)
+// mode 0: row(t, j) = t * K + j (one row per slot); mode 1: row(t, j) = (sel[t][j] - local_first) * T_stride + t (a plane per
+// local expert).  Only experts local_first .. local_first + local_count - 1 are added (a rank of a cut model adds its own).
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ sel, const float* __restrict__ wsel, int K, int H, int T,
-                                   int mode, size_t t_stride, const float* __restrict__ residual, float* __restrict__ out) {
+                                   int mode, size_t t_stride, int local_first, int local_count, const float* __restrict__ residual,
+                                   float* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     for (int i4 = threadIdx.x; i4 < H / 4; i4 += blockDim.x) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int j = 0; j < K; j++) {
-            const size_t row = mode == 0 ? (size_t)t * K + j : (size_t)sel[(size_t)t * K + j] * t_stride + t;
+            const int e = sel[(size_t)t * K + j];
+            if (e < local_first || e >= local_first + local_count) continue;
+            const size_t row = mode == 0 ? (size_t)t * K + j : (size_t)(e - local_first) * t_stride + t;
             const float w = wsel[(size_t)t * K + j];
             const float4 v = *reinterpret_cast<const float4*>(y + row * H + 4 * (size_t)i4);
             acc.x = acc.x + w * v.x; acc.y = acc.y + w * v.y; acc.z = acc.z + w * v.z; acc.w = acc.w + w * v.w;
@@ -142,14 +146,14 @@ int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s) {
     if (want_lists) LC_CHECK(a.T <= kRouteTokens && a.counts && a.list_stride >= a.T, LC_ERR_INVALID, "moe route: slot lists need a call of at most %d tokens", kRouteTokens);
     const unsigned grid = (unsigned)((a.T + kRouteTokens - 1) / kRouteTokens);
     LC_CUDA(launch_dep(moe_route_kernel, dim3(grid), dim3(kRouteThreads), s, a.x, a.norm_w, a.eps, a.H, a.T, a.w_router, a.n_experts, a.top_k, a.sel,
-                       a.wsel, a.counts, a.lists, a.list_stride, a.touched));
+                       a.wsel, a.counts, a.lists, a.list_stride, a.touched, a.local_first, a.local_count > 0 ? a.local_count : a.n_experts));
     return LC_OK;
 }
 
 int32_t launch_moe_combine(const float* y, const int32_t* sel, const float* wsel, int top_k, int H, int T, int mode, size_t t_stride,
-                           const float* residual, float* out, cudaStream_t s) {
+                           int local_first, int local_count, const float* residual, float* out, cudaStream_t s) {
     LC_CHECK(y && sel && wsel && out && H % 4 == 0 && T >= 1, LC_ERR_INVALID, "moe combine: bad argument");
-    LC_CUDA(launch_dep(moe_combine_kernel, dim3((unsigned)T), dim3(256), s, y, sel, wsel, top_k, H, T, mode, t_stride, residual, out));
+    LC_CUDA(launch_dep(moe_combine_kernel, dim3((unsigned)T), dim3(256), s, y, sel, wsel, top_k, H, T, mode, t_stride, local_first, local_count, residual, out));
     return LC_OK;
 }
 

@@ -150,6 +150,37 @@ __device__ __forceinline__ int32_t total_key(float f) {
     return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1);
 }
 // sampler.rs:6-10: max_by keeps the last of equal maxima -> compare (key, index) pairs.
+// The same pick kept as its key, with the index offset by index_base: the maximum of such keys over vocabulary slices is
+// the pick over the whole vocabulary, equal maxima still going to the higher index.
+__global__ void argmax_key_kernel(const float* __restrict__ v, size_t n, int index_base, long long* out) {
+    __shared__ long long shk[32];
+    const float* row = v + (size_t)blockIdx.x * n;
+    long long best = LLONG_MIN;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
+        long long key = ((long long)total_key(row[i]) << 32) | (long long)(uint32_t)(index_base + (int)i);
+        best = key > best ? key : best;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) shk[w] = best;
+    __syncthreads();
+    if (w == 0) {
+        best = lane < nw ? shk[lane] : LLONG_MIN;
+        for (int o = 16; o > 0; o >>= 1) {
+            long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (lane == 0) out[blockIdx.x] = best;
+    }
+}
+__global__ void key_to_token_kernel(const long long* __restrict__ keys, size_t rows, int64_t* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows) out[i] = (int64_t)(uint32_t)(keys[i] & 0xffffffffll);
+}
+
 __global__ void argmax_kernel(const float* __restrict__ v, size_t n, int64_t* out) {
     __shared__ long long shk[32];
     const float* row = v + (size_t)blockIdx.x * n;
@@ -240,6 +271,18 @@ int32_t launch_rope(float* x, size_t seq, size_t heads, size_t hd, float theta, 
 int32_t launch_argmax(const float* v, size_t n, size_t rows, int64_t* out, cudaStream_t s) {
     if (rows == 0 || n == 0) return LC_OK;
     argmax_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, out);
+    LC_CUDA(cudaGetLastError());
+    return LC_OK;
+}
+int32_t launch_argmax_key(const float* v, size_t n, size_t rows, int index_base, long long* out_keys, cudaStream_t s) {
+    if (rows == 0 || n == 0) return LC_OK;
+    argmax_key_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, index_base, out_keys);
+    LC_CUDA(cudaGetLastError());
+    return LC_OK;
+}
+int32_t launch_key_to_token(const long long* keys, size_t rows, int64_t* out_tokens, cudaStream_t s) {
+    if (rows == 0) return LC_OK;
+    key_to_token_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, s>>>(keys, rows, out_tokens);
     LC_CUDA(cudaGetLastError());
     return LC_OK;
 }

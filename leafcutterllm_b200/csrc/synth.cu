@@ -14,6 +14,34 @@ __global__ void synth_kernel(uint32_t typ, uint64_t seed, uint64_t name_hash, fl
     for (; b < n_blocks; b += stride) lcs_synth_block(typ, seed, name_hash, sigma, b, out + b * block_bytes);
 }
 
+__global__ void synth_part_kernel(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t row_blocks, size_t row0, size_t rows,
+                                  size_t blk0, size_t blks, uint32_t block_bytes, uint8_t* out) {
+    const size_t total = rows * blks;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t r = i / blks, c = i - r * blks;
+        lcs_synth_block(typ, seed, name_hash, sigma, (row0 + r) * row_blocks + blk0 + c, out + i * block_bytes);
+    }
+}
+
+int32_t launch_synth_part(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t row_blocks, size_t row0, size_t rows,
+                          size_t blk0, size_t blks, void* out_dev, cudaStream_t s) {
+    QuantGeom g;
+    LC_CHECK(quant_geom(typ, &g), LC_ERR_UNSUPPORTED, "synth: unsupported ggml type %u", typ);
+    LC_CHECK(typ == LC_TYPE_F32 || typ == LC_TYPE_F16 || typ == LC_TYPE_Q4_0 || typ == LC_TYPE_Q8_0 || typ == LC_TYPE_Q4_K,
+             LC_ERR_UNSUPPORTED, "synth: no quantiser for ggml type %u", typ);
+    LC_CHECK(blk0 + blks <= row_blocks, LC_ERR_INVALID, "synth: blocks %zu..%zu outside a row of %zu", blk0, blk0 + blks, row_blocks);
+    const size_t total = rows * blks;
+    if (total == 0) return LC_OK;
+    size_t grid = (total + 63) / 64;
+    const size_t cap = (size_t)sm_count() * 32;
+    if (grid > cap) grid = cap;
+    synth_part_kernel<<<(unsigned)grid, 64, 0, s>>>(typ, seed, name_hash, sigma, row_blocks, row0, rows, blk0, blks, g.block_bytes, (uint8_t*)out_dev);
+    LC_CUDA(cudaGetLastError());
+    return LC_OK;
+}
+
 int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_elems, void* out_dev,
                      cudaStream_t s) {
     QuantGeom g;

@@ -23,9 +23,10 @@ class Engine:
     def __init__(self, hidden_size: int, num_layers: int, num_heads: int, num_kv_heads: int, intermediate_size: int,
                  vocab_size: int, max_seq_len: int = 4096, rope_theta: float = 10000.0, rms_eps: float = 1e-5,
                  kv_dtype: str = "f16", rope_mode: str = "call_relative", max_seqs: int = 1, kv_page_tokens: int = 16,
-                 kv_pool_tokens: int = 0, device: int = 0, n_experts: int = 0, top_k: int = 0):
+                 kv_pool_tokens: int = 0, device: int = 0, n_experts: int = 0, top_k: int = 0, tp_size: int = 0, tp_rank: int = 0):
         cfg = ModelConfig()
         cfg.n_experts, cfg.top_k = n_experts, top_k
+        cfg.tp_size, cfg.tp_rank = tp_size, tp_rank
         cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads = hidden_size, num_layers, num_heads, num_kv_heads
         cfg.intermediate_size, cfg.max_seq_len, cfg.vocab_size = intermediate_size, max_seq_len, vocab_size
         cfg.rope_theta, cfg.rms_eps = rope_theta, rms_eps
@@ -57,6 +58,15 @@ class Engine:
         self.vocab_size = cfg.vocab_size
         self.max_seqs = max(1, cfg.max_seqs)
         return self
+
+    @staticmethod
+    def group(engines: Sequence["Engine"]) -> "Engine":
+        """Ranks 0 .. n-1 of one cut model, all in this process on one device: calls on the first engine then drive every
+        rank in lock step (`lc_model_group`).  Returns that first engine."""
+        arr = (C.c_void_p * len(engines))(*[e._h for e in engines])
+        check(load().lc_model_group(arr, len(engines)))
+        engines[0]._group = list(engines)
+        return engines[0]
 
     # ---- weights -------------------------------------------------------
     def set_tensor(self, name: str, typ: int, dims: Sequence[int], data) -> None:
