@@ -206,6 +206,14 @@ int32_t lc_dist_unique_id(void* out_id128);
 int32_t lc_dist_init(int32_t rank, int32_t world, const void* id128);
 int32_t lc_dist_set_backend(int32_t peer_memory);
 int32_t lc_dist_finalize(void);
+/* What lc_dist_init set up: world 1 / rank 0 without it; *peer_memory = 1 once the ranks' buffers are mapped into each other
+ * (known after the first model is finalized or lc_dist_time_allreduce has run), 0 while the sums go through NCCL. */
+int32_t lc_dist_info(int32_t* rank, int32_t* world, int32_t* peer_memory);
+/* Diagnostics after LC_ERR_CUDA from a cut model: out8[0] != 0 when a wait of a sum ran out, then out8[1..7] = the sum's number,
+ * the rank whose value was missing, the value's index, the tag found in its place, whether the kernel also sent, whether it
+ * was the greedy-pick maximum, the number of values.  Reading clears the record.  LC_DIST_TIMEOUT_MS (default 10000) bounds
+ * those waits. */
+int32_t lc_dist_debug(uint32_t* out8);
 /* Microseconds per sum of `count` floats over the ranks, averaged over `iters` back-to-back sums on the library's stream
  * (CUDA events; a measurement helper for the all-reduce that sits between a layer's products). */
 int32_t lc_dist_time_allreduce(size_t count, int32_t iters, float* out_us);

@@ -128,6 +128,8 @@ SIGNATURES = {
     "lc_dist_init": (_i32, [_i32, _i32, _vp]),
     "lc_dist_set_backend": (_i32, [_i32]),
     "lc_dist_finalize": (_i32, []),
+    "lc_dist_debug": (_i32, [_vp]),
+    "lc_dist_info": (_i32, [C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32)]),
     "lc_dist_time_allreduce": (_i32, [_sz, _i32, C.POINTER(C.c_float)]),
     "lc_model_group": (_i32, [C.POINTER(_vp), _i32]),
     "lc_shard_plan": (_i32, [C.POINTER(ModelConfig), C.c_char_p, _vp, _i32, C.POINTER(_i32), C.POINTER(_u64), C.POINTER(_u64)]),

@@ -29,9 +29,7 @@ namespace lc {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr size_t kFlagBytes = 4096;          // head of the shared buffer: one epoch word per peer
-constexpr size_t kKeyBytes = 4096;           // per slot: greedy-pick keys, up to 512 sequences
-constexpr size_t kPeerSumLimit = (size_t)2 << 20;  // larger sums go through NCCL
+constexpr int kLLWords = 32768;              // values per rank and sum on the peer-memory path (128 KiB of f32); larger sums use NCCL
 
 // ---- NCCL through dlopen ----
 typedef struct { char internal[128]; } NcclId;
@@ -89,100 +87,109 @@ struct DistState {
     int rank = 0, world = 1, device = 0;
     NcclComm comm = nullptr;
     int want_peer = 1;
+    bool setup_done = false;
     // peer-memory path
     bool peer_ok = false;
-    unsigned char* local = nullptr;     // [flags | slot 0 | slot 1 | keys 0 | keys 1]
-    size_t slot_bytes = 0;
-    unsigned char* peer[kMaxRanks] = {};
-    unsigned* d_epoch = nullptr;        // sums taken so far (device side, so that a replayed graph keeps counting)
+    unsigned long long* local = nullptr;    // [slot 2][source rank][kLLWords] tagged words
+    unsigned long long* peer[kMaxRanks] = {};
+    unsigned* d_epoch = nullptr;            // sums taken so far (device side, so that a replayed graph keeps counting)
     unsigned* d_ticket = nullptr;
-    float* plain_slot[2] = {nullptr, nullptr};  // NCCL only: ordinary device memory for the partial rows
 };
 DistState g_dist;
 
-struct PeerParams {
-    const unsigned char* peer[kMaxRanks];  // every rank's shared buffer as seen from here (own included)
-    unsigned* flags;                       // own flag words
+struct LLParams {
+    unsigned long long* peer[kMaxRanks];   // every rank's buffer as seen from here (own included)
     unsigned* epoch;
     unsigned* ticket;
     int* error_flag;
+    unsigned* debug;                       // 8 words written by the first wait that runs out: what it was waiting for
+    unsigned long long timeout_ns;
     int rank, world;
-    size_t src_off;                        // byte offset of the partial rows inside each buffer
 };
 
 __device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
-// Step 1 and 2 of a sum: announce, then wait for every peer.  Returns false when the wait ran out (10 s).
-__device__ __forceinline__ bool peer_barrier(const PeerParams& P, unsigned e) {
-    __shared__ int s_ok;
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if (blockIdx.x == 0 && (int)threadIdx.x < P.world) {
-        __threadfence_system();  // the rows the kernel ahead wrote are visible to the peers before the flag is
-        unsigned* theirs = reinterpret_cast<unsigned*>(const_cast<unsigned char*>(P.peer[threadIdx.x])) + P.rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
-    }
-    if ((int)threadIdx.x < P.world) {
-        const unsigned long long t0 = gtimer();
-        unsigned v = 0;
-        bool ok = false;
-        while (true) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(P.flags + threadIdx.x) : "memory");
-            if ((int)(v - e) >= 0) { ok = true; break; }
-            if (gtimer() - t0 > 10000000000ull) break;
-        }
-        if (!ok) s_ok = 0;
-    }
-    __syncthreads();
-    return s_ok != 0;
+__device__ __forceinline__ void st_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
 }
 
-__device__ __forceinline__ void peer_finish(const PeerParams& P, unsigned e, bool ok) {
+// One sum (or maximum of keys) over the ranks.  Every value travels as a 64-bit word: its 32 bits and, in the upper half,
+// the number e of the sum it belongs to.  A rank WRITES its words into slot e & 1, row `rank`, of every rank's buffer
+// (plain stores over NVLink, nothing waits for them), then polls its OWN buffer until row r of every rank r carries the
+// tag e, and adds the rows in rank order.  An aligned 64-bit access is single-copy atomic, so a matching tag delivers
+// the value: no flag, no fence.  push = 0: the producing kernel already wrote this rank's words (see GemvPush).
+// KEYS: the values are 64-bit greedy-pick keys, sent as two words each; the result is their maximum.
+template <bool KEYS>
+__global__ void __launch_bounds__(256) peer_ll_kernel(LLParams P, const void* __restrict__ src, void* __restrict__ dst, size_t count, int push) {
+    pdl_launch_dependents();
+    // Everything ahead on the stream has finished: src is written, and the sum count is the one the previous sum left.  (A
+    // gather-only launch must wait too: with small grids a whole chain of dependent kernels can be resident at once, and a
+    // kernel that skipped the wait would read the count before the previous sum's kernel has moved it.)
+    pdl_wait();
+    const unsigned e = *P.epoch + 1; // stable for the whole kernel: only this kernel's last CTA moves it, after everyone read it
+    const size_t row = (size_t)kLLWords, slot = (size_t)(e & 1u) * P.world * row;
+    const size_t words = KEYS ? 2 * count : count;
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    if (push) {
+        for (size_t w = tid; w < words; w += stride) {
+            unsigned bits;
+            if (KEYS) {
+                const unsigned long long k = (unsigned long long)reinterpret_cast<const long long*>(src)[w >> 1];
+                bits = (w & 1) ? (unsigned)k : (unsigned)(k >> 32);
+            } else {
+                bits = __float_as_uint(reinterpret_cast<const float*>(src)[w]);
+            }
+            const unsigned long long word = ((unsigned long long)e << 32) | bits;
+            for (int r = 0; r < P.world; r++) st_sys_u64(P.peer[r] + slot + (size_t)P.rank * row + w, word);
+        }
+    }
+    const unsigned long long* mine = P.peer[P.rank] + slot;
+    bool ok = true;
+    const unsigned long long t0 = gtimer();
+    for (size_t i = tid; i < count; i += stride) {
+        float acc = 0.f;
+        long long best = 0;
+        for (int r = 0; r < P.world; r++) {  // rank order: the same bits on every rank
+            const unsigned long long* q = mine + (size_t)r * row + (KEYS ? 2 * i : i);
+            unsigned long long a = 0, b = 0;
+            for (unsigned spin = 0;; spin++) {
+                a = ld_sys_u64(q);
+                if (KEYS) b = ld_sys_u64(q + 1);
+                if ((unsigned)(a >> 32) == e && (!KEYS || (unsigned)(b >> 32) == e)) break;
+                if ((spin & 1023u) == 1023u && gtimer() - t0 > P.timeout_ns) {
+                    ok = false;
+                    if (P.debug && atomicCAS(P.debug, 0u, 1u) == 0u) {
+                        P.debug[1] = e; P.debug[2] = (unsigned)r; P.debug[3] = (unsigned)i; P.debug[4] = (unsigned)(a >> 32);
+                        P.debug[5] = (unsigned)push; P.debug[6] = KEYS ? 1u : 0u; P.debug[7] = (unsigned)count;
+                    }
+                    break;
+                }
+            }
+            if (KEYS) {
+                const long long k = (long long)((a << 32) | (b & 0xffffffffull));
+                best = (r == 0 || k > best) ? k : best;
+            } else {
+                const float v = __uint_as_float((unsigned)a);
+                acc = r ? acc + v : v;
+            }
+        }
+        if (KEYS) reinterpret_cast<long long*>(dst)[i] = best;
+        else reinterpret_cast<float*>(dst)[i] = acc;
+    }
+    if (!ok && P.error_flag) atomicExch(P.error_flag, 3);
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (!ok && P.error_flag) atomicExch(P.error_flag, 3);
         const unsigned t = atomicAdd(P.ticket, 1u);
-        if (t == gridDim.x - 1) {  // the last CTA of this sum: the next kernel on the stream sees the new count
+        if (t == gridDim.x - 1) {  // the last CTA: every CTA has read the count, the next kernel on the stream sees the new one
             *P.ticket = 0;
             __threadfence();
             *P.epoch = e;
         }
     }
-}
-
-__global__ void __launch_bounds__(256) peer_sum_kernel(PeerParams P, float* __restrict__ dst, size_t count4) {
-    const unsigned e = *P.epoch + 1;
-    const bool ok = peer_barrier(P, e);
-    if (ok) {
-        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += (size_t)gridDim.x * blockDim.x) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < P.world; r++) {  // rank order: the same bits on every rank
-                const float4* src = reinterpret_cast<const float4*>(P.peer[r] + P.src_off) + i;
-                float4 v;
-                asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src) : "memory");
-                acc.x = r ? acc.x + v.x : v.x; acc.y = r ? acc.y + v.y : v.y; acc.z = r ? acc.z + v.z : v.z; acc.w = r ? acc.w + v.w : v.w;
-            }
-            reinterpret_cast<float4*>(dst)[i] = acc;
-        }
-    }
-    peer_finish(P, e, ok);
-}
-
-__global__ void __launch_bounds__(256) peer_max_kernel(PeerParams P, long long* __restrict__ dst, size_t count) {
-    const unsigned e = *P.epoch + 1;
-    const bool ok = peer_barrier(P, e);
-    if (ok) {
-        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
-            long long best = 0;
-            for (int r = 0; r < P.world; r++) {
-                long long v;
-                asm volatile("ld.relaxed.sys.global.s64 %0, [%1];" : "=l"(v) : "l"(reinterpret_cast<const long long*>(P.peer[r] + P.src_off) + i) : "memory");
-                best = (r == 0 || v > best) ? v : best;
-            }
-            dst[i] = best;
-        }
-    }
-    peer_finish(P, e, ok);
 }
 
 struct GroupPtrs { const void* src[kMaxRanks]; void* dst[kMaxRanks]; int n; };
@@ -204,13 +211,31 @@ __global__ void group_max_kernel(GroupPtrs g, size_t count) {
     }
 }
 
-PeerParams peer_params(size_t src_off) {
-    PeerParams P{};
+LLParams ll_params() {
+    LLParams P{};
     for (int r = 0; r < g_dist.world; r++) P.peer[r] = g_dist.peer[r];
-    P.flags = reinterpret_cast<unsigned*>(g_dist.local);
     P.epoch = g_dist.d_epoch; P.ticket = g_dist.d_ticket; P.error_flag = gemv_error_flag_dev();
-    P.rank = g_dist.rank; P.world = g_dist.world; P.src_off = src_off;
+    P.debug = g_dist.d_epoch + 2;
+    static const unsigned long long ms = getenv("LC_DIST_TIMEOUT_MS") ? strtoull(getenv("LC_DIST_TIMEOUT_MS"), nullptr, 10) : 10000ull;
+    P.timeout_ns = ms * 1000000ull;
+    P.rank = g_dist.rank; P.world = g_dist.world;
     return P;
+}
+
+template <bool KEYS>
+int32_t launch_ll(const void* src, void* dst, size_t count, int push, cudaStream_t s) {
+    LLParams P = ll_params();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)std::min<size_t>(64, (count + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LC_CUDA(cudaLaunchKernelEx(&cfg, peer_ll_kernel<KEYS>, P, src, dst, count, push));
+    return LC_OK;
 }
 
 }  // namespace
@@ -219,30 +244,16 @@ bool dist_active() { return g_dist.on; }
 int dist_rank() { return g_dist.on ? g_dist.rank : 0; }
 int dist_world() { return g_dist.on ? g_dist.world : 1; }
 bool dist_peer_memory() { return g_dist.on && g_dist.peer_ok; }
+size_t dist_peer_capacity() { return dist_peer_memory() ? (size_t)kLLWords : 0; }
 
-// Collective over the ranks: (re)creates the partial-row buffers so that each slot holds slot_bytes.
-int32_t dist_reserve(size_t slot_bytes) {
+// Collective over the ranks, once: the buffer of tagged words, mapped into every peer (or the agreement that it cannot be).
+int32_t dist_setup() {
     DistState& d = g_dist;
     LC_CHECK(d.on, LC_ERR_STATE, "lc_dist_init has not been called");
-    slot_bytes = (slot_bytes + 255) & ~(size_t)255;
-    if (slot_bytes <= d.slot_bytes) return LC_OK;
+    if (d.setup_done) return LC_OK;
     cudaStream_t s = stream();
     LC_CUDA(cudaStreamSynchronize(s));
-    for (int i = 0; i < 2; i++) { if (d.plain_slot[i]) cudaFree(d.plain_slot[i]); d.plain_slot[i] = nullptr; }
-    const bool had_shared = d.local != nullptr;
-    for (int r = 0; r < d.world; r++) { if (r != d.rank && d.peer[r]) cudaIpcCloseMemHandle(d.peer[r]); d.peer[r] = nullptr; }
-    if (had_shared) {  // nobody frees a buffer that a peer may still have mapped: everyone closes, then everyone meets here
-        long long* d_one = nullptr;
-        LC_CUDA(cudaMalloc((void**)&d_one, 8));
-        LC_CUDA(cudaMemsetAsync(d_one, 0, 8, s));
-        LC_NCCL(g_nccl.AllReduce(d_one, d_one, 1, kNcclInt64, kNcclMax, d.comm, s));
-        LC_CUDA(cudaStreamSynchronize(s));
-        cudaFree(d_one);
-    }
-    if (d.local) { cudaFree(d.local); d.local = nullptr; }
-    d.peer_ok = false;
-    d.slot_bytes = slot_bytes;
-    const size_t total = kFlagBytes + 2 * slot_bytes + 2 * kKeyBytes;
+    const size_t total = (size_t)2 * d.world * kLLWords * sizeof(unsigned long long);
     int mine_ok = 0;
     cudaIpcMemHandle_t handle;
     memset(&handle, 0, sizeof(handle));
@@ -271,7 +282,7 @@ int32_t dist_reserve(size_t slot_bytes) {
             if (r == d.rank) { d.peer[r] = d.local; continue; }
             void* p = nullptr;
             if (cudaIpcOpenMemHandle(&p, all[r].h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { (void)cudaGetLastError(); opened = 0; break; }
-            d.peer[r] = (unsigned char*)p;
+            d.peer[r] = (unsigned long long*)p;
         }
     }
     // all ranks must agree: the smallest of the `opened` words
@@ -285,54 +296,49 @@ int32_t dist_reserve(size_t slot_bytes) {
     d.peer_ok = v == 1;
     if (!d.peer_ok) {
         for (int r = 0; r < d.world; r++) { if (r != d.rank && d.peer[r]) cudaIpcCloseMemHandle(d.peer[r]); d.peer[r] = nullptr; }
+        // everyone has closed what it opened before anyone frees (the all-reduce above is behind us; one more meeting point)
+        LC_CUDA(cudaMalloc((void**)&d_flag, 8));
+        LC_CUDA(cudaMemsetAsync(d_flag, 0, 8, s));
+        LC_NCCL(g_nccl.AllReduce(d_flag, d_flag, 1, kNcclInt64, kNcclMax, d.comm, s));
+        LC_CUDA(cudaStreamSynchronize(s));
+        cudaFree(d_flag);
         if (d.local) { cudaFree(d.local); d.local = nullptr; }
-        for (int i = 0; i < 2; i++) LC_CUDA(cudaMalloc((void**)&d.plain_slot[i], slot_bytes + kKeyBytes));
     }
-    if (!d.d_epoch) {
-        LC_CUDA(cudaMalloc((void**)&d.d_epoch, 8));
-        LC_CUDA(cudaMemset(d.d_epoch, 0, 8));
-        d.d_ticket = d.d_epoch + 1;
-    }
+    LC_CUDA(cudaMalloc((void**)&d.d_epoch, 40));   // sum count, ticket, 8 words of diagnostics
+    LC_CUDA(cudaMemset(d.d_epoch, 0, 40));
+    d.d_ticket = d.d_epoch + 1;
+    d.setup_done = true;
     return LC_OK;
 }
 
-// Where a rank writes the partial rows of its next sum (i = 0, 1: consecutive sums alternate) / its greedy-pick keys.
-float* dist_slot(int i) {
+// dst[0 .. count) = sum over the ranks of their src rows, rank order.  src and dst are this rank's ordinary device memory.
+int32_t dist_allreduce_sum(const float* src, float* dst, size_t count, cudaStream_t s) {
     DistState& d = g_dist;
-    if (d.peer_ok) return reinterpret_cast<float*>(d.local + kFlagBytes + (size_t)(i & 1) * d.slot_bytes);
-    return d.plain_slot[i & 1];
-}
-long long* dist_key_slot(int i) {
-    DistState& d = g_dist;
-    if (d.peer_ok) return reinterpret_cast<long long*>(d.local + kFlagBytes + 2 * d.slot_bytes + (size_t)(i & 1) * kKeyBytes);
-    return reinterpret_cast<long long*>(reinterpret_cast<unsigned char*>(d.plain_slot[i & 1]) + d.slot_bytes);
-}
-
-// dst[0 .. count) = sum over the ranks of their slot `i` rows, rank order
-int32_t dist_allreduce_sum(int i, float* dst, size_t count, cudaStream_t s) {
-    DistState& d = g_dist;
-    LC_CHECK(d.on && count * 4 <= d.slot_bytes && count % 4 == 0, LC_ERR_INVALID, "dist sum: %zu floats do not fit the reserved slot", count);
-    if (d.peer_ok && count * 4 <= kPeerSumLimit) {
-        PeerParams P = peer_params(kFlagBytes + (size_t)(i & 1) * d.slot_bytes);
-        const unsigned grid = (unsigned)std::min<size_t>(32, (count / 4 + 255) / 256);
-        peer_sum_kernel<<<grid, 256, 0, s>>>(P, dst, count / 4);
-        LC_CUDA(cudaGetLastError());
-        return LC_OK;
-    }
-    LC_NCCL(g_nccl.AllReduce(dist_slot(i), dst, count, kNcclFloat32, kNcclSum, d.comm, s));
+    LC_CHECK(d.on && d.setup_done, LC_ERR_STATE, "dist sum before lc_dist_init / the model's finalize");
+    if (d.peer_ok && count <= (size_t)kLLWords) return launch_ll<false>(src, dst, count, 1, s);
+    LC_NCCL(g_nccl.AllReduce(src, dst, count, kNcclFloat32, kNcclSum, d.comm, s));
     return LC_OK;
 }
-
-int32_t dist_allreduce_max(int i, long long* dst, size_t count, cudaStream_t s) {
+// The second half of such a sum when the kernel that produced the rows already wrote this rank's tagged words to every rank.
+int32_t dist_gather_sum(float* dst, size_t count, cudaStream_t s) {
     DistState& d = g_dist;
-    LC_CHECK(d.on && count * 8 <= kKeyBytes, LC_ERR_INVALID, "dist max: %zu keys do not fit", count);
-    if (d.peer_ok) {
-        PeerParams P = peer_params(kFlagBytes + 2 * d.slot_bytes + (size_t)(i & 1) * kKeyBytes);
-        peer_max_kernel<<<1, 256, 0, s>>>(P, dst, count);
-        LC_CUDA(cudaGetLastError());
-        return LC_OK;
-    }
-    LC_NCCL(g_nccl.AllReduce(dist_key_slot(i), dst, count, kNcclInt64, kNcclMax, d.comm, s));
+    LC_CHECK(d.on && d.peer_ok && count <= (size_t)kLLWords, LC_ERR_STATE, "dist gather: the peer-memory path is not set up for %zu values", count);
+    return launch_ll<false>(nullptr, dst, count, 0, s);
+}
+// What a producing kernel needs to write its output rows as tagged words of the NEXT sum into every rank's buffer.
+bool dist_push_desc(size_t count, GemvPush* out) {
+    DistState& d = g_dist;
+    if (!d.on || !d.peer_ok || count > (size_t)kLLWords) return false;
+    for (int r = 0; r < kMaxRanks; r++) out->peer[r] = r < d.world ? d.peer[r] : nullptr;
+    out->epoch = d.d_epoch; out->world = d.world; out->rank = d.rank; out->row_words = kLLWords;
+    return true;
+}
+
+int32_t dist_allreduce_max(const long long* src, long long* dst, size_t count, cudaStream_t s) {
+    DistState& d = g_dist;
+    LC_CHECK(d.on && d.setup_done, LC_ERR_STATE, "dist max before lc_dist_init / the model's finalize");
+    if (d.peer_ok && 2 * count <= (size_t)kLLWords) return launch_ll<true>(src, dst, count, 1, s);
+    LC_NCCL(g_nccl.AllReduce(src, dst, count, kNcclInt64, kNcclMax, d.comm, s));
     return LC_OK;
 }
 
@@ -393,8 +399,27 @@ int32_t lc_dist_init(int32_t rank, int32_t world, const void* id128) {
 }
 
 int32_t lc_dist_set_backend(int32_t peer_memory) {
-    LC_CHECK(g_dist.slot_bytes == 0, LC_ERR_STATE, "lc_dist_set_backend must come before the first model is finalized");
+    LC_CHECK(!g_dist.setup_done, LC_ERR_STATE, "lc_dist_set_backend must come before the first model is finalized");
     g_dist.want_peer = peer_memory ? 1 : 0;
+    return LC_OK;
+}
+
+int32_t lc_dist_info(int32_t* rank, int32_t* world, int32_t* peer_memory) {
+    if (rank) *rank = dist_rank();
+    if (world) *world = dist_world();
+    if (peer_memory) *peer_memory = dist_peer_memory() ? 1 : 0;
+    return LC_OK;
+}
+
+// Diagnostics: the record left by the first wait of a sum that ran out ([0] != 0 when there is one): sum number, the rank
+// whose word was missing, the word index, the tag found there, whether the kernel also sent, whether it was a key maximum,
+// the number of values.  Reading clears it.
+int32_t lc_dist_debug(uint32_t* out8) {
+    LC_CHECK(out8, LC_ERR_INVALID, "null output");
+    memset(out8, 0, 32);
+    if (!g_dist.on || !g_dist.d_epoch) return LC_OK;
+    LC_CUDA(cudaMemcpy(out8, g_dist.d_epoch + 2, 32, cudaMemcpyDeviceToHost));
+    LC_CUDA(cudaMemset(g_dist.d_epoch + 2, 0, 32));
     return LC_OK;
 }
 
@@ -403,8 +428,16 @@ int32_t lc_dist_finalize(void) {
     if (!d.on) return LC_OK;
     cudaStreamSynchronize(stream());
     for (int r = 0; r < d.world; r++) if (r != d.rank && d.peer[r]) cudaIpcCloseMemHandle(d.peer[r]);
+    if (d.comm && d.local) {  // nobody frees a buffer that a peer may still have mapped: everyone closes, then everyone meets
+        long long* one = nullptr;
+        if (cudaMalloc((void**)&one, 8) == cudaSuccess) {
+            cudaMemsetAsync(one, 0, 8, stream());
+            g_nccl.AllReduce(one, one, 1, kNcclInt64, kNcclMax, d.comm, stream());
+            cudaStreamSynchronize(stream());
+            cudaFree(one);
+        }
+    }
     if (d.local) cudaFree(d.local);
-    for (int i = 0; i < 2; i++) if (d.plain_slot[i]) cudaFree(d.plain_slot[i]);
     if (d.d_epoch) cudaFree(d.d_epoch);
     if (d.comm) g_nccl.CommDestroy(d.comm);
     d = DistState{};
@@ -414,23 +447,24 @@ int32_t lc_dist_finalize(void) {
 int32_t lc_dist_time_allreduce(size_t count, int32_t iters, float* out_us) {
     LC_CHECK(out_us && iters >= 1 && count >= 4 && count % 4 == 0, LC_ERR_INVALID, "lc_dist_time_allreduce: bad argument");
     LC_CHECK(g_dist.on, LC_ERR_STATE, "lc_dist_init has not been called");
-    LC_TRY(dist_reserve(count * 4));
+    LC_TRY(dist_setup());
     cudaStream_t s = stream();
-    float* dst = nullptr;
+    float *src = nullptr, *dst = nullptr;
+    LC_CUDA(cudaMalloc((void**)&src, count * 4));
     LC_CUDA(cudaMalloc((void**)&dst, count * 4));
-    for (int i = 0; i < 2; i++) LC_CUDA(cudaMemsetAsync(dist_slot(i), 0, count * 4, s));
+    LC_CUDA(cudaMemsetAsync(src, 0, count * 4, s));
     cudaEvent_t e0, e1;
     LC_CUDA(cudaEventCreate(&e0));
     LC_CUDA(cudaEventCreate(&e1));
-    for (int i = 0; i < 4; i++) LC_TRY(dist_allreduce_sum(i, dst, count, s));
+    for (int i = 0; i < 4; i++) LC_TRY(dist_allreduce_sum(src, dst, count, s));
     LC_CUDA(cudaEventRecord(e0, s));
-    for (int i = 0; i < iters; i++) LC_TRY(dist_allreduce_sum(i, dst, count, s));
+    for (int i = 0; i < iters; i++) LC_TRY(dist_allreduce_sum(src, dst, count, s));
     LC_CUDA(cudaEventRecord(e1, s));
     LC_CUDA(cudaEventSynchronize(e1));
     float ms = 0.f;
     LC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
     *out_us = ms * 1000.f / (float)iters;
-    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaFree(dst);
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaFree(src); cudaFree(dst);
     int flag = 0;
     if (int* f = gemv_error_flag_dev()) { LC_CUDA(cudaMemcpy(&flag, f, 4, cudaMemcpyDeviceToHost)); if (flag) cudaMemset(f, 0, 4); }
     LC_CHECK(flag == 0, LC_ERR_CUDA, "a rank did not arrive at a sum within ten seconds");

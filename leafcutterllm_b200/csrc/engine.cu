@@ -71,13 +71,13 @@ struct lc_model {
     bool use_dist = false;               // the ranks are other processes (lc_dist_init); else members lists them, or tp == 1
     std::vector<lc_model*> members;      // rank 0 of an in-process group: every rank's handle in rank order (itself first)
     lc_model* leader = nullptr;          // a rank > 0 of such a group
-    float* d_part[2] = {nullptr, nullptr};   // where the column-cut products leave their partial rows for the sum over the ranks
-    bool part_owned = false;
-    long long* d_key[2] = {nullptr, nullptr};  // greedy pick of the local vocabulary slice as (total-order key << 32 | global index)
+    float* d_part = nullptr;             // where the column-cut products leave their partial rows for the sum over the ranks
+    long long* d_key = nullptr;          // greedy pick of the local vocabulary slice as (total-order key << 32 | global index)
     long long* d_key_max = nullptr;
     float* d_logits_all = nullptr;       // dist: the ranks' logit slices gathered for the host
-    int sums_in_call = 0;                // alternates the partial-row slots
     float* pending_dst = nullptr;        // where the next sum over the ranks has to land
+    bool pending_pushed = false;         // ... and whether the product already sent its rows to the ranks
+    GemvPush push_desc;
     int page_tokens = 16, pages_per_seq = 0, pages_total = 0, max_seqs = 1, t_cap = 0;
     size_t kv_elt = 2;
 
@@ -322,7 +322,17 @@ int32_t gemv_tiled(lc_model* m, GemvArgs a, int T, int n_out, int k_in) {
 float* partial_dst(lc_model* m, float* out) {
     if (m->tp == 1) return out;
     m->pending_dst = out;
-    return m->d_part[m->sums_in_call & 1];
+    m->pending_pushed = false;
+    return m->d_part;
+}
+// A matrix-vector product of up to four tokens that ends in a sum over ranks in other processes can write its rows
+// straight into the ranks' buffers (one NVLink trip, no kernel boundary before the transfer); the sum then only gathers.
+void try_push(lc_model* m, GemvArgs* a, int T) {
+    static const bool off = getenv("LC_DIST_NO_PUSH") != nullptr;  // diagnostics: every sum as its own send + gather kernel
+    if (off || !m->use_dist || T > 4 || !qgemv_push_supported(*a)) return;
+    if (!dist_push_desc((size_t)T * m->H, &m->push_desc)) return;
+    a->push = &m->push_desc;
+    m->pending_pushed = true;
 }
 
 // attention_forward (attention.rs:37-118) for layer `l` on T tokens whose (normalised or raw) input is `x`.
@@ -385,6 +395,8 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     if (m->tp == 1 && residual && out == m->d_hidden2 && w.ffn_norm) {  // in a layer of the forward pass the FFN reads `out` next, through its norm
         o.prep_next = true; o.next_norm_w = w.ffn_norm; o.next_eps = m->cfg.rms_eps;
     }
+    o.m = T;
+    if (m->tp > 1) try_push(m, &o, T);
     return gemv_tiled(m, o, T, m->H, m->nh * m->hd);
 }
 
@@ -461,6 +473,8 @@ int32_t ffn_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         // the next layer's q/k/v product(s) read `out` through that layer's attention norm
         d.prep_next = true; d.next_norm_w = m->layers[l + 1].attn_norm; d.next_eps = m->cfg.rms_eps;
     }
+    d.m = T;
+    if (m->tp > 1) try_push(m, &d, T);
     return gemv_tiled(m, d, T, m->H, m->F);
 }
 
@@ -473,17 +487,17 @@ std::vector<lc_model*> ranks_of(lc_model* m) {
 // Sum over the ranks of the partial rows the last column-cut product left, into each rank's pending destination.
 int32_t reduce_ranks(lc_model* lead, size_t count) {
     if (lead->tp == 1) return LC_OK;
-    const int slot = lead->sums_in_call & 1;
     std::vector<lc_model*> R = ranks_of(lead);
     if (lead->use_dist) {
-        LC_TRY(dist_allreduce_sum(slot, lead->pending_dst, count, lead->stream));
+        if (lead->pending_pushed) LC_TRY(dist_gather_sum(lead->pending_dst, count, lead->stream));
+        else LC_TRY(dist_allreduce_sum(lead->d_part, lead->pending_dst, count, lead->stream));
     } else {
         LC_CHECK((int)R.size() == lead->tp, LC_ERR_STATE, "a model cut into %d ranks needs lc_dist_init or lc_model_group before it can run", lead->tp);
         const float* src[8]; float* dst[8];
-        for (int r = 0; r < lead->tp; r++) { src[r] = R[r]->d_part[slot]; dst[r] = R[r]->pending_dst; }
+        for (int r = 0; r < lead->tp; r++) { src[r] = R[r]->d_part; dst[r] = R[r]->pending_dst; }
         LC_TRY(launch_group_sum(src, dst, lead->tp, count, lead->stream));
     }
-    for (lc_model* m : R) { m->sums_in_call++; m->pending_dst = nullptr; }
+    for (lc_model* m : R) m->pending_dst = nullptr;
     lead->launches_in_call += 1;
     return LC_OK;
 }
@@ -492,7 +506,6 @@ int32_t reduce_ranks(lc_model* lead, size_t count) {
 int32_t run_layers(lc_model* lead, int T, bool decode_step) {
     std::vector<lc_model*> R = ranks_of(lead);
     for (lc_model* m : R) {
-        m->sums_in_call = 0;
         LC_TRY(launch_embed(m->embed->typ, m->embed->view, m->embed->rows, m->embed->cols, m->d_tokens, T, m->d_hidden, m->stream));
         m->launches_in_call += 1;
     }
@@ -531,16 +544,16 @@ int32_t forward_tokens(lc_model* lead, int T, int n_last, bool identity_last, in
         h.out = m->d_logits + (size_t)row0 * m->V;
         LC_TRY(gemv_tiled(m, h, n_last, m->V, m->H));
         if (m->tp == 1) LC_TRY(launch_argmax(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->d_next + row0, m->stream));
-        else LC_TRY(launch_argmax_key(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->v0, m->d_key[0] + row0, m->stream));
+        else LC_TRY(launch_argmax_key(m->d_logits + (size_t)row0 * m->V, m->V, n_last, m->v0, m->d_key + row0, m->stream));
         m->launches_in_call += 1;
     }
     if (lead->tp > 1) {  // the pick over the whole vocabulary: the largest (logit, global index) key of the ranks
         if (lead->use_dist) {
-            LC_TRY(dist_allreduce_max(0, lead->d_key_max, (size_t)(row0 + n_last), lead->stream));
+            LC_TRY(dist_allreduce_max(lead->d_key, lead->d_key_max, (size_t)(row0 + n_last), lead->stream));
         } else {
             LC_CHECK((int)R.size() == lead->tp, LC_ERR_STATE, "a model cut into %d ranks needs lc_dist_init or lc_model_group before it can run", lead->tp);
             const long long* src[8]; long long* dst[8];
-            for (int r = 0; r < lead->tp; r++) { src[r] = R[r]->d_key[0]; dst[r] = R[r]->d_key_max; }
+            for (int r = 0; r < lead->tp; r++) { src[r] = R[r]->d_key; dst[r] = R[r]->d_key_max; }
             LC_TRY(launch_group_max(src, dst, lead->tp, (size_t)(row0 + n_last), lead->stream));
         }
         for (lc_model* m : R) LC_TRY(launch_key_to_token(m->d_key_max + row0, n_last, m->d_next + row0, m->stream));
@@ -967,14 +980,11 @@ int32_t lc_model_finalize(lc_model* m) {
         // partial rows of the column-cut products and the greedy-pick keys: in the buffers the other ranks can read when the
         // ranks are processes (a collective call: every rank finalizes its model at the same point), else plain memory
         LC_TRY(dalloc(&m->d_key_max, (size_t)m->max_seqs));
-        if (m->use_dist) {
-            LC_CHECK(m->max_seqs <= 512, LC_ERR_UNSUPPORTED, "a model cut across processes decodes at most 512 sequences together");
-            LC_TRY(dist_reserve((size_t)T * H * sizeof(float)));
-            for (int i = 0; i < 2; i++) { m->d_part[i] = dist_slot(i); m->d_key[i] = dist_key_slot(i); }
+        LC_TRY(dalloc(&m->d_key, (size_t)m->max_seqs));
+        LC_TRY(dalloc(&m->d_part, (size_t)T * H));
+        if (m->use_dist) {  // a collective call: every rank finalizes its model at the same point
+            LC_TRY(dist_setup());
             LC_TRY(dalloc(&m->d_logits_all, (size_t)m->max_seqs * m->cfg.vocab_size));
-        } else {
-            for (int i = 0; i < 2; i++) { LC_TRY(dalloc(&m->d_part[i], (size_t)T * H)); LC_TRY(dalloc(&m->d_key[i], (size_t)m->max_seqs)); }
-            m->part_owned = true;
         }
     }
     size_t sc = 16;
@@ -1004,14 +1014,13 @@ int32_t lc_model_destroy(lc_model* m) {
     for (void* p : m->owned) cudaFree(p);
     for (void* p : m->k_pools) cudaFree(p);
     for (void* p : m->v_pools) cudaFree(p);
-    if (m->part_owned) for (int i = 0; i < 2; i++) { cudaFree(m->d_part[i]); cudaFree(m->d_key[i]); }
     if (m->leader) {  // leaving a group: the leader must not drive this handle any more
         auto& mem = m->leader->members;
         for (lc_model* x : mem) if (x != m->leader) x->leader = nullptr;
         mem.clear();
     }
     for (lc_model* x : m->members) if (x != m) x->leader = nullptr;
-    void* bufs[] = {m->d_key_max, m->d_logits_all, m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
+    void* bufs[] = {m->d_part, m->d_key, m->d_key_max, m->d_logits_all, m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
                     m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};

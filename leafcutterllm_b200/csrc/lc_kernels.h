@@ -73,6 +73,13 @@ struct GemvGroup {
     int max_tokens = 0;             // most slots any expert can receive in this call (= tokens of the call)
     bool x_by_token = false;
 };
+// A product whose output rows are one rank's share of a sum over the ranks can write them straight into every rank's
+// buffer as tagged words (dist.cu): word tk * n + row of row `rank`, slot (sum number) & 1, sum number = *epoch + 1.
+struct GemvPush {
+    unsigned long long* peer[8] = {};
+    const unsigned* epoch = nullptr;
+    int world = 0, rank = 0, row_words = 0;
+};
 struct GemvArgs {
     const QWeight* w = nullptr;   // first matrix
     const QWeight* w2 = nullptr;  // EPI_SILU_MUL: the `up` matrix (w is `gate`)
@@ -84,6 +91,7 @@ struct GemvArgs {
     float eps = 1e-5f;
     GemvEpilogue epi = EPI_STORE;
     const GemvGroup* group = nullptr;  // set: w / w2 only give the experts' common shape and type
+    const GemvPush* push = nullptr;    // set (see qgemv_push_supported): the rows go to the ranks' buffers instead of `out`
     // Many-token product only: the caller promises that the next product reads `out` (all m rows) as its input with this
     // gain (null: no norm) -- the kernel that sums the shares of k then also prepares that input, saving a launch.
     bool prep_next = false;
@@ -92,6 +100,8 @@ struct GemvArgs {
 };
 // y[m,n] = x[m,k] . dequant(W)^T, fp32 activations and accumulation.
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s);
+// true when launch_qgemv would run these arguments on the kernel that implements GemvArgs::push
+bool qgemv_push_supported(const GemvArgs& a);
 // ---- qgemm_umma.cu ----
 // The same product for many tokens (prefill chunks, batched decode) on tcgen05 tensor cores with the weights
 // dequantised on the fly.  The workspace holds the activations as f16 high/low halves and the per-token scales.
@@ -192,11 +202,11 @@ bool dist_active();
 int dist_rank();
 int dist_world();
 bool dist_peer_memory();
-int32_t dist_reserve(size_t slot_bytes);            // collective: room for sums of slot_bytes bytes
-float* dist_slot(int i);                            // where this rank writes the partial rows of a sum (i = 0, 1 alternate)
-long long* dist_key_slot(int i);                    // ... and its greedy-pick keys
-int32_t dist_allreduce_sum(int i, float* dst, size_t count, cudaStream_t s);
-int32_t dist_allreduce_max(int i, long long* dst, size_t count, cudaStream_t s);
+int32_t dist_setup();                               // collective, once (the first model's finalize): maps the ranks' buffers
+int32_t dist_allreduce_sum(const float* src, float* dst, size_t count, cudaStream_t s);
+int32_t dist_allreduce_max(const long long* src, long long* dst, size_t count, cudaStream_t s);
+bool dist_push_desc(size_t count, GemvPush* out);   // false: sums of `count` values do not take the peer-memory path
+int32_t dist_gather_sum(float* dst, size_t count, cudaStream_t s);  // completes a sum whose rows the producer pushed
 int32_t dist_allgather(const void* src, void* dst, size_t bytes, cudaStream_t s);
 // the same sums for ranks that are handles of one process on one GPU: one kernel over all ranks' rows
 int32_t launch_group_sum(const float* const* src, float* const* dst, int n, size_t count, cudaStream_t s);

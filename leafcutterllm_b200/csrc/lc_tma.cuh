@@ -67,6 +67,7 @@ struct GemvParams {
     int n, k, m;
     int epi;
     int* error_flag;
+    GemvPush push;          // world > 0: the output rows leave as tagged words (see GemvPush)
     unsigned long long* ring = nullptr;  // diagnostics (LC_GEMV_RING): 8 wall-clock words of this launch, or null
 };
 // Expert grouping of one launch (device pointers; see GemvGroup): all zero for a plain product.

@@ -557,6 +557,12 @@ static int32_t launch_generic(const GemvArgs& a, cudaStream_t s) {
     return LC_OK;
 }
 
+bool qgemv_push_supported(const GemvArgs& a) {
+    static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
+    return a.w && !a.group && a.w->typ == LC_TYPE_Q4_K && a.w->has_tmap && a.epi != EPI_SILU_MUL && !force_fp32 && a.m >= 1 && a.m <= 8 &&
+           qgemv_mma_supports(a.w->k) && ((uintptr_t)a.x % 16) == 0 && (!a.norm_w || ((uintptr_t)a.norm_w % 16) == 0);
+}
+
 static int round_m(int m) { return m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8)); }
 
 int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
@@ -580,6 +586,7 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
         LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
         if (launched) return LC_OK;
     }
+    LC_CHECK(a.push == nullptr, LC_ERR_STATE, "qgemv: rows cannot leave as tagged words from this kernel (qgemv_push_supported was not asked)");
     if (tma_ok) {
         for (int mt = round_m(a.m); mt >= 1; mt >>= 1) {
             // the kernel handles mt tokens per pass; when shared memory cannot hold round_m(m) token

@@ -141,6 +141,8 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         pdl_wait();
     }
     if (rg) rg[1] = gtime();
+    // rows that are this rank's share of a sum over the ranks: the number of that sum (stable: the kernel ahead has finished)
+    const unsigned push_e = p.push.world > 0 ? *p.push.epoch + 1u : 0u;
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
     float v0[8];
@@ -412,7 +414,16 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                     if (p.epi == EPI_ADD_RESIDUAL) y = p.residual[orow(tk) + row] + y;
                     have = true;
                 }
-                if (have) p.out[orow(tk) + row] = y;
+                if (have) {
+                    if (!GROUPED && p.push.world > 0) {
+                        const unsigned long long word = ((unsigned long long)push_e << 32) | (unsigned long long)__float_as_uint(y);
+                        const size_t at = ((size_t)(push_e & 1u) * p.push.world + p.push.rank) * p.push.row_words + orow(tk) + row;
+                        for (int r = 0; r < p.push.world; r++)
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.push.peer[r] + at), "l"(word) : "memory");
+                    } else {
+                        p.out[orow(tk) + row] = y;
+                    }
+                }
             }
         }
     }
@@ -460,6 +471,7 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
     p.n = a.w->n; p.k = a.w->k; p.m = a.m; p.epi = (int)a.epi; p.error_flag = gemv_error_flag_dev();
+    if (a.push) p.push = *a.push;
     static const bool want_ring = getenv("LC_GEMV_RING") != nullptr;
     if (want_ring) {
         if (!g_mring) {
