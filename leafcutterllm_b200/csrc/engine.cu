@@ -420,6 +420,7 @@ int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         GemvGroup g1;
         g1.tmaps = w.tm_gate; g1.tmaps2 = w.tm_up; g1.counts = m->d_moe_cnt + e0; g1.lists = m->d_moe_lists + (size_t)e0 * kMoeGroupedTokens;
         g1.list_stride = kMoeGroupedTokens; g1.n_experts = El; g1.top_k = K; g1.max_tokens = T; g1.x_by_token = true;
+        g1.typical_tokens = (T * K + E - 1) / E;
         GemvArgs a;
         a.w = &w.egate[0]; a.w2 = &w.eup[0]; a.x = x; a.norm_w = norm_w; a.eps = m->cfg.rms_eps; a.out = m->d_moe_h; a.epi = EPI_SILU_MUL;
         a.m = std::min(T, kTokTile); a.group = &g1;

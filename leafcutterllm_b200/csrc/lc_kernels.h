@@ -71,6 +71,7 @@ struct GemvGroup {
     const int32_t* lists = nullptr; // [n_experts][list_stride]
     int list_stride = 0, n_experts = 0, top_k = 0;
     int max_tokens = 0;             // most slots any expert can receive in this call (= tokens of the call)
+    int typical_tokens = 0;         // what an expert receives on average (tokens * top_k / experts, rounded up); 0 = unknown
     bool x_by_token = false;
 };
 // A product whose output rows are one rank's share of a sum over the ranks can write them straight into every rank's

@@ -16,6 +16,7 @@
 // Data path: the same TMA-staged [144 B x 32 rows] boxes as the f32 kernel; warp <-> unit, a thread
 // holds the A fragments of rows g and g+8 (g = lane / 4) as two 32-bit shared-memory loads per
 // 64-element group (bank-conflict free for the 144-byte row pitch).
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include "lc_kernels.h"
@@ -532,10 +533,20 @@ int32_t launch_qgemv_mma_q4k_grouped(const GemvArgs& a, cudaStream_t s, bool* la
     LC_CHECK(g && g->tmaps && g->counts && g->lists && g->n_experts > 0 && g->max_tokens > 0 && g->top_k > 0 && !a.residual, LC_ERR_INVALID,
              "grouped qgemv: incomplete expert group");
     if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
-    if (g->max_tokens <= 1) return launch_grouped_m<1, 16>(a, s, launched);
-    if (g->max_tokens <= 2) return launch_grouped_m<2, 16>(a, s, launched);
-    if (g->max_tokens <= 4) return launch_grouped_m<4, 16>(a, s, launched);
-    return launch_grouped_m<8, 8>(a, s, launched);
+    // Token tile: the smallest of 1, 2, 4, 8 that holds what an expert typically receives (tokens * top_k / experts of the layer),
+    // as long as the fixed-point planes of a whole row fit shared memory (14336-element rows leave room for two tokens); an
+    // expert with more tokens than the tile makes several passes, and passes without tokens leave at once.
+    const int want = std::max(1, std::min(g->max_tokens, g->typical_tokens > 0 ? g->typical_tokens : g->max_tokens));
+    if (want > 4) { LC_TRY((launch_grouped_m<8, 8>(a, s, launched))); if (*launched) return LC_OK; }
+    if (want > 2) {
+        LC_TRY((launch_grouped_m<4, 16>(a, s, launched))); if (*launched) return LC_OK;
+        LC_TRY((launch_grouped_m<4, 8>(a, s, launched))); if (*launched) return LC_OK;
+    }
+    if (want > 1) {
+        LC_TRY((launch_grouped_m<2, 16>(a, s, launched))); if (*launched) return LC_OK;
+        LC_TRY((launch_grouped_m<2, 8>(a, s, launched))); if (*launched) return LC_OK;
+    }
+    return launch_grouped_m<1, 16>(a, s, launched);
 }
 
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) {

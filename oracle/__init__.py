@@ -62,6 +62,8 @@ def lib() -> C.CDLL:
             "orc_last_error": (C.c_char_p, [vp]), "orc_sanitized_count": (sz, [vp]),
             "orc_timers": (None, [vp, vp, C.c_int]),
             "orc_attention": (C.c_int, [vp, C.c_int, vp, sz, vp]), "orc_ffn": (C.c_int, [vp, C.c_int, vp, sz, vp]),
+            "orc_synth_tensor": (C.c_int, [u32, C.c_uint64, C.c_char_p, f, sz, vp]),
+            "orc_synth_tokens": (None, [C.c_uint64, sz, C.c_int64, vp]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
@@ -76,6 +78,20 @@ def _p(a):
 
 def _f32(a):
     return np.ascontiguousarray(a, np.float32)
+
+
+def synth_tensor(typ: int, seed: int, name: str, sigma: float, n_elems: int) -> np.ndarray:
+    """Raw block bytes of the benchmark's synthetic tensor (seed, name): the same bytes the CUDA library's generator makes."""
+    out = np.empty(lib().orc_tensor_bytes(typ, n_elems), np.uint8)
+    if lib().orc_synth_tensor(typ, seed, name.encode(), sigma, n_elems, _p(out)) != 0:
+        raise ValueError(f"no synthetic generator for ggml type {typ}")
+    return out
+
+
+def synth_tokens(seed: int, n: int, vocab: int) -> np.ndarray:
+    out = np.empty(n, np.int64)
+    lib().orc_synth_tokens(seed, n, vocab, _p(out))
+    return out
 
 
 def dequantize(typ: int, data, n: int) -> np.ndarray:

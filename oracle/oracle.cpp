@@ -35,6 +35,7 @@
 #include <chrono>
 #ifdef _OPENMP
 #include <omp.h>
+#include "../leafcutterllm_b200/csrc/lc_synth.h"
 #endif
 
 
@@ -1016,6 +1017,31 @@ int orc_attention(void* h, int layer, const float* normed, size_t seq, float* ou
     attention_forward((Model*)h, (size_t)layer, normed, seq, out);
     return 0;
 }
+// The benchmark's synthetic inputs (the project's counter-based generator and GGUF-order quantisers, a header shared
+// with the CUDA library so that both sides can make identical bytes) for callers that must not load the CUDA library:
+// the timed CPU arm of the benchmark.  Inputs only; no arithmetic of the path.
+int orc_synth_tensor(uint32_t typ, uint64_t seed, const char* name, float sigma, size_t n_elems, void* out_bytes) {
+    uint32_t be = 0, bb = 0;
+    switch (typ) {
+        case 0: be = 1; bb = 4; break;
+        case 1: be = 1; bb = 2; break;
+        case 2: be = 32; bb = 18; break;
+        case 8: be = 32; bb = 34; break;
+        case 12: be = 256; bb = 144; break;
+        default: return -1;
+    }
+    if (!name || !out_bytes || n_elems % be) return -1;
+    const size_t nb = n_elems / be;
+    const uint64_t h = lcs_fnv1a(name);
+    uint8_t* out = (uint8_t*)out_bytes;
+#pragma omp parallel for schedule(static)
+    for (long long b = 0; b < (long long)nb; b++) lcs_synth_block(typ, seed, h, sigma, (uint64_t)b, out + (size_t)b * bb);
+    return 0;
+}
+void orc_synth_tokens(uint64_t seed, size_t n, int64_t vocab, int64_t* out) {
+    for (size_t i = 0; i < n; i++) out[i] = (int64_t)lcs_uniform_int(seed, i, (uint64_t)vocab);
+}
+
 int orc_ffn(void* h, int layer, const float* x, size_t seq, float* out) {
     Model* m = (Model*)h;
     std::string p = "blk." + std::to_string(layer) + ".";

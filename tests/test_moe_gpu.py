@@ -140,3 +140,22 @@ def test_moe_config_errors(gpu):
     with pytest.raises(gpu.LeafcutterError) as e:
         gpu.Engine(256, 1, 2, 2, 512, 100, max_seq_len=16, n_experts=65, top_k=2)
     assert e.value.status == -1
+
+
+def test_moe_long_expert_rows_take_narrower_token_tiles(gpu, oracle):
+    """Experts whose down projection reads 8192-element rows: the fixed-point planes of eight tokens no longer fit shared
+    memory, so the grouped launch falls back to four-token tiles and more passes per expert."""
+    from leafcutterllm_b200 import synth
+    spec = moe_spec(layers=1, hidden=256, ffn=8192, n_experts=4, top_k=2)
+    lens = [3, 7, 1, 9, 2, 5, 4, 6, 1, 3, 2, 6]
+    ids = list(range(12))
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=48, max_seqs=12)
+    prompts = [synth.prompt_tokens(n, spec.vocab_size, 90 + i).tolist() for i, n in enumerate(lens)]
+    logits, nxt = eng.forward_batch(ids, prompts)
+    toks, _ms = eng.decode_loop(ids, nxt, 3)
+    for i, p in enumerate(prompts):
+        om.kv_clear()
+        assert_close(logits[i], om.forward(p), LOGIT_ABS, LOGIT_REL, f"sequence {i}")
+        ref, margins = om.generate(p, 4, stop_on_eos=False, want_margins=True)
+        assert [int(nxt[i])] + toks[:, i].tolist() == ref, (i, margins)
+    eng.close()

@@ -69,3 +69,15 @@ def test_device_generator_matches_host_bytes(gpu, typ):
     gpu._capi.check(lib.lc_dev_download(dev.ctypes.data_as(C.c_void_p), p, host.size))
     lib.lc_dev_free(p)
     assert np.array_equal(dev, host)
+
+
+def test_oracle_side_generator_makes_the_same_bytes(lc, oracle):
+    """The CPU arm of the benchmark builds its inputs inside the oracle library (so that it never loads the CUDA library);
+    its generator must make the bytes the CUDA library's host generator makes."""
+    import numpy as np
+    from leafcutterllm_b200 import synth
+    for typ, n in [(12, 256 * 40), (2, 32 * 70), (8, 32 * 70), (0, 1000), (1, 1000)]:
+        a = synth.host_tensor(typ, 1234, "blk.3.ffn_up.weight", n)
+        b = oracle.synth_tensor(typ, 1234, "blk.3.ffn_up.weight", synth.SIGMA, n)
+        assert np.array_equal(a, b), typ
+    assert np.array_equal(synth.prompt_tokens(50, 32000, 3), oracle.synth_tokens(synth.PROMPT_SEED + 3, 50, 32000))
