@@ -44,8 +44,10 @@ constexpr int kStateWords = 4 + kHD;         // max, sum, two pad words (16-byte
 
 struct StreamParams {
     AttnParams a;
-    unsigned long long* slots;  // [q head][contributor][kStateWords] (f32 bits | valid << 32), zero between launches
+    unsigned long long* slots;  // polled merge: [q head][contributor][2 + kHD] words (f32 bits | valid << 32), zero between launches;
+                                // ticket merge: the same room as f32 [q head][contributor][2 + kHD], then one ticket word per kv head
     int max_contrib;
+    int ticket_merge;           // see the merge at the end of the kernel
     int nstages;
     unsigned long long* ring;  // diagnostics (LC_ATTN_RING): [launch slot][8] wall-clock stamps, or null
     int ring_slot;
@@ -81,6 +83,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     // (seen with cold caches, when copies requested together land microseconds apart).  So a consumer of round r >= 1
     // first waits until the producer says it has armed round r -- which it only does after round r - 1 was consumed.
     volatile int* armed = reinterpret_cast<volatile int*>(empty + S);       // [S]
+    volatile int* s_last = armed + S;                                       // merge: this CTA took the last ticket of a head
 
     auto gtime = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
     unsigned long long* rg = (P.ring && tid == 0) ? P.ring + (size_t)P.ring_slot * 16 : nullptr;
@@ -98,7 +101,9 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     const int pos = p.tok_pos[0];
     const int np = pos / kPage + 1;
     const int T = kv.n_kv * np;
-    const int G = min((int)gridDim.x, T);  // CTAs that take part: each has at least one item
+    // CTAs that take part: about four items each where a head has that many pages (fewer, larger shares to add up).  The
+    // share per CTA never exceeds one head's pages (T / min(4, np) >= n_kv CTAs), so a run touches at most two kv heads.
+    const int G = min((int)gridDim.x, max(1, T / max(1, min(4, np))));
     const bool active = (int)blockIdx.x < G;
     const int i_begin = active ? (int)((long long)blockIdx.x * T / G) : 0;
     const int i_end = active ? (int)((long long)(blockIdx.x + 1) * T / G) : 0;
@@ -382,92 +387,164 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     asm volatile("bar.sync 1, %0;" ::"r"(kCWarps * 32) : "memory");
     if (rg) rg[3] = gtime();
 
-    // ---- per (kv head, query head): the warps in warp order, then the CTAs that share the kv head in CTA order ----
-    const int nseg = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
-    constexpr int kMergeGroups = kCWarps / 4;  // whole 128-thread groups among the consumers; the last warps sit the merge out
-    const int hf = tid >> 7, dx = tid & 127;   // kMergeGroups (segment, query head) pairs at a time, one thread per dim
-    for (int w = hf < kMergeGroups ? hf : nseg * GSZ; w < nseg * GSZ; w += kMergeGroups) {
-        const int sl = w / GSZ, g = w - sl * GSZ;
-        const float* ws = st_s + ((size_t)sl * kCWarps * GSZ + g) * kStateWords;  // warp 0's state; warp stride GSZ * kStateWords
-        float M = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < kCWarps; i++) M = fmaxf(M, ws[(size_t)i * GSZ * kStateWords]);
-        float L = 0.f, A = 0.f;
-#pragma unroll
-        for (int i = 0; i < kCWarps; i++) {
-            const float mi = ws[(size_t)i * GSZ * kStateWords];
-            if (mi == -INFINITY) continue;  // the warp met no key of this head
-            const float e = expf(mi - M);
-            L += ws[(size_t)i * GSZ * kStateWords + 1] * e;
-            A += ws[(size_t)i * GSZ * kStateWords + 4 + dx] * e;
-        }
-        const int seg = seg0 + sl, head = seg * GSZ + g;
-        const long long first = (long long)seg * np, last = first + np - 1;
-        const int c_first = (int)(((first + 1) * G - 1) / T), c_last = (int)(((last + 1) * G - 1) / T);
-        const int nc = c_last - c_first + 1, me = (int)blockIdx.x - c_first;
-        unsigned long long* sl_base = P.slots + (size_t)head * P.max_contrib * (2 + kHD);
-        // validity tag of a slot word; the collector clears what it read
-        const unsigned long long tag = 1ull;
-        auto put = [&](unsigned long long* a, float v) {
-            const unsigned long long wv = (tag << 32) | (unsigned long long)__float_as_uint(v);
-            asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
-        };
-        if (nc > 1 && me != nc - 1) {
-            unsigned long long* mine = sl_base + (size_t)me * (2 + kHD);
-            if (dx == 0) { put(mine, M); put(mine + 1, L); }
-            put(mine + 2 + dx, A);
-        } else {
-            // The head's LAST CTA collects the others and adds everything in CTA order.  CTAs are dispatched in index order
-            // as SMs come free, so the highest index is the one most likely to have started last: when it gets here the
-            // others' words are usually already in L2 and one round trip fetches them.  The three words of up to eight
-            // contributors are requested together.
-            constexpr int kBatch = 8;
-            const float M_own = M, L_own = L, A_own = A;
-            M = -INFINITY; L = 0.f; A = 0.f;
-            for (int c0 = 0; c0 < nc - 1; c0 += kBatch) {
-                unsigned long long wv[kBatch][3];
-                bool all = false;
-                for (uint32_t it = 0; it < (1u << 20) && !all; ++it) {  // bounded: poll the whole batch until every word is valid
-#pragma unroll
-                    for (int u = 0; u < kBatch; u++) {
-                        const unsigned long long* theirs = sl_base + (size_t)min(c0 + u, nc - 2) * (2 + kHD);
-                        asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][0]) : "l"(theirs) : "memory");
-                        asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][1]) : "l"(theirs + 1) : "memory");
-                        asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][2]) : "l"(theirs + 2 + dx) : "memory");
+    // Two ways to add the CTAs' shares of a head, fixed per model (P.ticket_merge):
+    //  * few CTAs per head (many kv heads): every CTA but the head's last publishes words that carry a valid flag and leaves;
+    //    the last one polls them -- nobody pays a fence or an atomic;
+    //  * many CTAs per head (one or a few kv heads per GPU, as in a model cut across GPUs): tickets, see below.
+    if (!P.ticket_merge) {
+        // ---- per (kv head, query head): the warps in warp order, then the CTAs that share the kv head in CTA order ----
+        const int nseg = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
+        constexpr int kMergeGroups = kCWarps / 4;  // whole 128-thread groups among the consumers; the last warps sit the merge out
+        const int hf = tid >> 7, dx = tid & 127;   // kMergeGroups (segment, query head) pairs at a time, one thread per dim
+        for (int w = hf < kMergeGroups ? hf : nseg * GSZ; w < nseg * GSZ; w += kMergeGroups) {
+            const int sl = w / GSZ, g = w - sl * GSZ;
+            const float* ws = st_s + ((size_t)sl * kCWarps * GSZ + g) * kStateWords;  // warp 0's state; warp stride GSZ * kStateWords
+            float M = -INFINITY;
+    #pragma unroll
+            for (int i = 0; i < kCWarps; i++) M = fmaxf(M, ws[(size_t)i * GSZ * kStateWords]);
+            float L = 0.f, A = 0.f;
+    #pragma unroll
+            for (int i = 0; i < kCWarps; i++) {
+                const float mi = ws[(size_t)i * GSZ * kStateWords];
+                if (mi == -INFINITY) continue;  // the warp met no key of this head
+                const float e = expf(mi - M);
+                L += ws[(size_t)i * GSZ * kStateWords + 1] * e;
+                A += ws[(size_t)i * GSZ * kStateWords + 4 + dx] * e;
+            }
+            const int seg = seg0 + sl, head = seg * GSZ + g;
+            const long long first = (long long)seg * np, last = first + np - 1;
+            const int c_first = (int)(((first + 1) * G - 1) / T), c_last = (int)(((last + 1) * G - 1) / T);
+            const int nc = c_last - c_first + 1, me = (int)blockIdx.x - c_first;
+            unsigned long long* sl_base = P.slots + (size_t)head * P.max_contrib * (2 + kHD);
+            // validity tag of a slot word; the collector clears what it read
+            const unsigned long long tag = 1ull;
+            auto put = [&](unsigned long long* a, float v) {
+                const unsigned long long wv = (tag << 32) | (unsigned long long)__float_as_uint(v);
+                asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(a), "l"(wv) : "memory");
+            };
+            if (nc > 1 && me != nc - 1) {
+                unsigned long long* mine = sl_base + (size_t)me * (2 + kHD);
+                if (dx == 0) { put(mine, M); put(mine + 1, L); }
+                put(mine + 2 + dx, A);
+            } else {
+                // The head's LAST CTA collects the others and adds everything in CTA order.  CTAs are dispatched in index order
+                // as SMs come free, so the highest index is the one most likely to have started last: when it gets here the
+                // others' words are usually already in L2 and one round trip fetches them.  The three words of up to eight
+                // contributors are requested together.
+                constexpr int kBatch = 8;
+                const float M_own = M, L_own = L, A_own = A;
+                M = -INFINITY; L = 0.f; A = 0.f;
+                for (int c0 = 0; c0 < nc - 1; c0 += kBatch) {
+                    unsigned long long wv[kBatch][3];
+                    bool all = false;
+                    for (uint32_t it = 0; it < (1u << 20) && !all; ++it) {  // bounded: poll the whole batch until every word is valid
+    #pragma unroll
+                        for (int u = 0; u < kBatch; u++) {
+                            const unsigned long long* theirs = sl_base + (size_t)min(c0 + u, nc - 2) * (2 + kHD);
+                            asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][0]) : "l"(theirs) : "memory");
+                            asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][1]) : "l"(theirs + 1) : "memory");
+                            asm volatile("ld.global.relaxed.gpu.u64 %0, [%1];" : "=l"(wv[u][2]) : "l"(theirs + 2 + dx) : "memory");
+                        }
+                        all = true;
+    #pragma unroll
+                        for (int u = 0; u < kBatch; u++) all = all && (wv[u][0] >> 32) == tag && (wv[u][1] >> 32) == tag && (wv[u][2] >> 32) == tag;
                     }
-                    all = true;
-#pragma unroll
-                    for (int u = 0; u < kBatch; u++) all = all && (wv[u][0] >> 32) == tag && (wv[u][1] >> 32) == tag && (wv[u][2] >> 32) == tag;
+                    ok = ok && all;
+    #pragma unroll
+                    for (int u = 0; u < kBatch; u++) {
+                        if (c0 + u >= nc - 1) break;
+                        const float Mc = __uint_as_float((uint32_t)wv[u][0]), Lc = __uint_as_float((uint32_t)wv[u][1]);
+                        const float Ac = __uint_as_float((uint32_t)wv[u][2]);
+                        const float Mn = fmaxf(M, Mc);
+                        const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);  // exp(-inf) = 0 for the empty start
+                        A = A * e0 + Ac * e1;
+                        L = L * e0 + Lc * e1;
+                        M = Mn;
+                    }
                 }
-                ok = ok && all;
-#pragma unroll
-                for (int u = 0; u < kBatch; u++) {
-                    if (c0 + u >= nc - 1) break;
-                    const float Mc = __uint_as_float((uint32_t)wv[u][0]), Lc = __uint_as_float((uint32_t)wv[u][1]);
-                    const float Ac = __uint_as_float((uint32_t)wv[u][2]);
-                    const float Mn = fmaxf(M, Mc);
-                    const float e0 = expf(M - Mn), e1 = expf(Mc - Mn);  // exp(-inf) = 0 for the empty start
-                    A = A * e0 + Ac * e1;
-                    L = L * e0 + Lc * e1;
+                {   // this CTA's own share comes last
+                    const float Mn = fmaxf(M, M_own);
+                    const float e0 = expf(M - Mn), e1 = expf(M_own - Mn);
+                    A = A * e0 + A_own * e1;
+                    L = L * e0 + L_own * e1;
                     M = Mn;
                 }
+                if (nc > 1) {
+                    for (int c = 0; c < nc - 1; c++)
+                        asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + 2 + dx), "l"(0ull) : "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read the maxima and sums
+                    if (dx < 2)
+                        for (int c = 0; c < nc - 1; c++)
+                            asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + dx), "l"(0ull) : "memory");
+                }
+                p.out[(size_t)head * kHD + dx] = A / L;
             }
-            {   // this CTA's own share comes last
-                const float Mn = fmaxf(M, M_own);
-                const float e0 = expf(M - Mn), e1 = expf(M_own - Mn);
-                A = A * e0 + A_own * e1;
-                L = L * e0 + L_own * e1;
-                M = Mn;
+        }
+    } else {
+        // ---- per kv head of the run: the warps in warp order; then, where several CTAs share the head, every CTA leaves its
+        //      share in global memory and takes a ticket, and the CTA that takes the LAST ticket adds all shares in CTA order
+        //      (so the result does not depend on who arrives last).  No polling: with one kv head per GPU (a cut model) a
+        //      head spans dozens of CTAs, and a collector that polled them a few at a time paid one L2 round trip per batch. ----
+        const int nseg = n_items > 0 ? (i_end - 1) / np - seg0 + 1 : 0;
+        constexpr int kCThreads = kCWarps * 32;
+        float* part = reinterpret_cast<float*>(P.slots);                                                   // [q head][contributor][2 + kHD]
+        unsigned* tickets = reinterpret_cast<unsigned*>(P.slots) + (size_t)p.n_heads * P.max_contrib * (2 + kHD);  // [kv head], zero between launches
+        for (int sl = 0; sl < nseg; sl++) {
+            const int seg = seg0 + sl;
+            const long long first = (long long)seg * np, last = first + np - 1;
+            const int c_first = (int)(((first + 1) * G - 1) / T), c_last = (int)(((last + 1) * G - 1) / T);
+            const int nc = c_last - c_first + 1, me = (int)blockIdx.x - c_first;
+            for (int w = tid; w < GSZ * kHD; w += kCThreads) {
+                const int g = w / kHD, dx = w - g * kHD;
+                const float* ws = st_s + ((size_t)sl * kCWarps * GSZ + g) * kStateWords;  // warp 0's state; warp stride GSZ * kStateWords
+                float M = -INFINITY;
+    #pragma unroll
+                for (int i = 0; i < kCWarps; i++) M = fmaxf(M, ws[(size_t)i * GSZ * kStateWords]);
+                float L = 0.f, A = 0.f;
+    #pragma unroll
+                for (int i = 0; i < kCWarps; i++) {
+                    const float mi = ws[(size_t)i * GSZ * kStateWords];
+                    if (mi == -INFINITY) continue;  // the warp met no key of this head
+                    const float e = expf(mi - M);
+                    L += ws[(size_t)i * GSZ * kStateWords + 1] * e;
+                    A += ws[(size_t)i * GSZ * kStateWords + 4 + dx] * e;
+                }
+                const int head = seg * GSZ + g;
+                if (nc == 1) {
+                    p.out[(size_t)head * kHD + dx] = A / L;
+                } else {
+                    float* mine = part + ((size_t)head * P.max_contrib + me) * (2 + kHD);
+                    if (dx == 0) { mine[0] = M; mine[1] = L; }
+                    mine[2 + dx] = A;
+                }
             }
             if (nc > 1) {
-                for (int c = 0; c < nc - 1; c++)
-                    asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + 2 + dx), "l"(0ull) : "memory");
-                asm volatile("bar.sync %0, 128;" ::"r"(2 + hf) : "memory");  // every thread of the pair has read the maxima and sums
-                if (dx < 2)
-                    for (int c = 0; c < nc - 1; c++)
-                        asm volatile("st.global.relaxed.gpu.u64 [%0], %1;" ::"l"(sl_base + (size_t)c * (2 + kHD) + dx), "l"(0ull) : "memory");
+                __threadfence();  // this CTA's share is in global memory before its ticket is
+                asm volatile("bar.sync 1, %0;" ::"r"(kCThreads) : "memory");
+                if (tid == 0) *s_last = atomicAdd(tickets + seg, 1u) == (unsigned)(nc - 1) ? 1 : 0;
+                asm volatile("bar.sync 1, %0;" ::"r"(kCThreads) : "memory");
+                if (*s_last) {
+                    __threadfence();
+                    for (int w = tid; w < GSZ * kHD; w += kCThreads) {
+                        const int g = w / kHD, dx = w - g * kHD, head = seg * GSZ + g;
+                        const float* base = part + (size_t)head * P.max_contrib * (2 + kHD);
+                        float M = -INFINITY;
+                        for (int c = 0; c < nc; c++) M = fmaxf(M, __ldcg(base + (size_t)c * (2 + kHD)));
+                        float L = 0.f, A = 0.f;
+    #pragma unroll 4
+                        for (int c = 0; c < nc; c++) {  // CTA order
+                            const float* q = base + (size_t)c * (2 + kHD);
+                            const float Mc = __ldcg(q), Lc = __ldcg(q + 1), Ac = __ldcg(q + 2 + dx);
+                            const float e = expf(Mc - M);  // exp(-inf) = 0 for a share without keys
+                            L += Lc * e;
+                            A += Ac * e;
+                        }
+                        p.out[(size_t)head * kHD + dx] = A / L;
+                    }
+                    if (tid == 0) tickets[seg] = 0;  // every CTA of the head has taken its ticket: ready for the next launch
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kCThreads) : "memory");
             }
-            p.out[(size_t)head * kHD + dx] = A / L;
         }
     }
     if (rg) rg[4] = gtime();
@@ -497,7 +574,7 @@ size_t stream_fixed_smem() {
     constexpr int kCWarps = consumer_warps<GSZ>();
     constexpr int NTc = (2 * GSZ + 7) / 8;
     return 1024 + (size_t)kMaxSeg * GSZ * kHD * 4 + (size_t)kMaxSeg * NTc * 16 * 32 * 4 + (size_t)kMaxSeg * kCWarps * GSZ * kStateWords * 4 +
-           (size_t)kMaxSeg * GSZ * kStateWords * 4 + 16;
+           (size_t)kMaxSeg * GSZ * kStateWords * 4 + 32;
 }
 
 template <int GSZ>
@@ -505,6 +582,7 @@ int32_t launch_stream(const AttnParams& a, unsigned long long* slots, cudaStream
     StreamParams P;
     P.a = a;
     P.max_contrib = stream_max_contrib(a.kv.n_kv);
+    P.ticket_merge = P.max_contrib > 12 ? 1 : 0;  // by geometry only, so that a model never changes the slots' format
     P.slots = slots;
     if (!g_aring && getenv("LC_ATTN_RING")) {  // diagnostics: wall-clock stamps per launch, printed at exit
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
