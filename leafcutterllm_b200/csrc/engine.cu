@@ -75,6 +75,8 @@ struct lc_model {
     long long* d_key = nullptr;          // greedy pick of the local vocabulary slice as (total-order key << 32 | global index)
     long long* d_key_max = nullptr;
     float* d_logits_all = nullptr;       // dist: the ranks' logit slices gathered for the host
+    PrefillTile* d_tiles = nullptr;      // the call's tokens as runs of up to 64 consecutive positions of one sequence
+    int n_tiles = 0;
     float* pending_dst = nullptr;        // where the next sum over the ranks has to land
     bool pending_pushed = false;         // ... and whether the product already sent its rows to the ranks
     GemvPush push_desc;
@@ -383,8 +385,12 @@ int32_t attention_block(lc_model* m, int l, const float* x, const float* norm_w,
     } else {
         LC_TRY(launch_rope_kv_append(q, k, v, m->nqkv, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_page_table,
                                      m->pages_per_seq, m->cfg.rope_theta, m->stream));
-        LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
-                                m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, nullptr, m->stream));
+        static const bool no_tc = getenv("LC_PREFILL_FMA") != nullptr;  // diagnostics: the one-CTA-per-(token, head) kernel for every call
+        if (T >= 16 && m->n_tiles > 0 && !no_tc && attention_prefill_applies(kv, m->nh))  // a prefill chunk: tiles of 64 queries on the tensor cores
+            LC_TRY(launch_attention_prefill(q, m->nqkv, m->d_attn, m->nh, kv, m->d_tiles, m->n_tiles, m->d_page_table, m->pages_per_seq, m->stream));
+        else
+            LC_TRY(launch_attention(q, m->nqkv, m->d_attn, T, m->nh, kv, m->d_tok_seq, m->d_tok_pos, m->d_page_table, m->pages_per_seq,
+                                    m->cfg.max_seq_len, m->d_attn_scratch, m->d_attn_counters, nullptr, m->stream));
         m->launches_in_call += 2;
     }
     GemvArgs o;
@@ -587,6 +593,14 @@ int32_t upload_meta(lc_model* m, const std::vector<int64_t>& tok, const std::vec
     LC_CUDA(cudaMemcpyAsync(m->d_tok_pos, pos.data(), T * 4, cudaMemcpyHostToDevice, m->stream));
     LC_CUDA(cudaMemcpyAsync(m->d_tok_rope, rope.data(), T * 4, cudaMemcpyHostToDevice, m->stream));
     if (!last.empty()) LC_CUDA(cudaMemcpyAsync(m->d_last_idx, last.data(), last.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    // runs of consecutive positions of one sequence, cut into tiles of 64 tokens, for the tensor-core prefill attention
+    std::vector<PrefillTile> tiles;
+    for (size_t i = 0; i < T; i++) {
+        if (tiles.empty() || tiles.back().n == 64 || seq[i] != seq[i - 1] || pos[i] != pos[i - 1] + 1) tiles.push_back(PrefillTile{(int32_t)i, 0, seq[i], pos[i]});
+        tiles.back().n++;
+    }
+    m->n_tiles = (int)tiles.size();
+    if (!tiles.empty()) LC_CUDA(cudaMemcpyAsync(m->d_tiles, tiles.data(), tiles.size() * sizeof(PrefillTile), cudaMemcpyHostToDevice, m->stream));
     // the copies read pageable host vectors that die with the caller's frame
     LC_CUDA(cudaStreamSynchronize(m->stream));
     return LC_OK;
@@ -960,7 +974,7 @@ int32_t lc_model_finalize(lc_model* m) {
     // step buffers
     int T = m->t_cap;
     LC_TRY(dalloc(&m->d_tokens, T)); LC_TRY(dalloc(&m->d_tok_seq, T)); LC_TRY(dalloc(&m->d_tok_pos, T));
-    LC_TRY(dalloc(&m->d_tok_rope, T)); LC_TRY(dalloc(&m->d_last_idx, T));
+    LC_TRY(dalloc(&m->d_tok_rope, T)); LC_TRY(dalloc(&m->d_last_idx, T)); LC_TRY(dalloc(&m->d_tiles, T));
     LC_TRY(dalloc(&m->d_hidden, (size_t)T * H)); LC_TRY(dalloc(&m->d_hidden2, (size_t)T * H));
     LC_TRY(dalloc(&m->d_qkv, (size_t)T * m->nqkv)); LC_TRY(dalloc(&m->d_attn, (size_t)T * nq));
     LC_TRY(dalloc(&m->d_ffn, (size_t)T * F));
@@ -1021,7 +1035,7 @@ int32_t lc_model_destroy(lc_model* m) {
         mem.clear();
     }
     for (lc_model* x : m->members) if (x != m) x->leader = nullptr;
-    void* bufs[] = {m->d_part, m->d_key, m->d_key_max, m->d_logits_all, m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
+    void* bufs[] = {m->d_tiles, m->d_part, m->d_key, m->d_key_max, m->d_logits_all, m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
                     m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};

@@ -168,6 +168,13 @@ struct AttnFusion {
 int32_t launch_attention(const float* q, int q_stride, float* out, int n_tok, int n_heads, const KvLayout& kv,
                          const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* page_table, int pages_per_seq, int max_ctx,
                          void* scratch, int* counters, const AttnFusion* fuse, cudaStream_t s);
+// ---- attention_prefill.cu: many new tokens on the tensor cores (head_dim 128, f16 cache, 16-token pages) ----
+// up to 64 consecutive tokens of one sequence: rows tok0 .. tok0 + n - 1 of the call, the first at cache position pos0
+struct PrefillTile { int32_t tok0, n, seq, pos0; };
+bool attention_prefill_applies(const KvLayout& kv, int n_heads);
+// q is already rotated and the new keys / values are already in the cache (launch_rope_kv_append); out is [tokens, n_heads * 128]
+int32_t launch_attention_prefill(const float* q, int q_stride, float* out, int n_heads, const KvLayout& kv, const PrefillTile* tiles_dev, int n_tiles,
+                                 const int32_t* page_table, int pages_per_seq, cudaStream_t s);
 // Bytes of merge slots the single-token streaming kernel needs for this head geometry (0: the kernel does not apply).
 size_t attention_stream_slot_bytes(int n_heads, int n_kv);
 

@@ -151,6 +151,27 @@ def test_batched_decode_attention_over_several_context_pieces(gpu, oracle):
     eng.close()
 
 
+def test_prefill_attention_on_tensor_cores_ragged(gpu, oracle):
+    """head_dim 128, f16 cache: calls of 16 tokens and more run the tiled tensor-core prefill attention.  Four sequences of
+    70, 16, 129 and 33 tokens in ONE call (tiles end where a sequence ends; 129 = two full tiles and a one-token tile), then a
+    second call that appends 20 to 40 tokens to each cache (tiles that start in the middle of a page and attend to keys of
+    the earlier call), grouped-query heads (4 query heads over 2 kv heads).  Logits per sequence against the oracle."""
+    from leafcutterllm_b200 import synth
+    spec = small_spec(12, 12, 12, layers=2, hidden=512, heads=4, kv=2, ffn=512, vocab=600)
+    lens, more = [70, 16, 129, 33], [20, 40, 25, 31]
+    ids = [0, 1, 2, 3]
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=192, max_seqs=4)
+    p1 = [synth.prompt_tokens(n, spec.vocab_size, 200 + i).tolist() for i, n in enumerate(lens)]
+    p2 = [synth.prompt_tokens(n, spec.vocab_size, 300 + i).tolist() for i, n in enumerate(more)]
+    l1, _ = eng.forward_batch(ids, p1)
+    l2, _ = eng.forward_batch(ids, p2)
+    for i in ids:
+        om.kv_clear()
+        assert_close(l1[i], om.forward(p1[i]), LOGIT_ABS, LOGIT_REL, f"sequence {i}, first call")
+        assert_close(l2[i], om.forward(p2[i]), LOGIT_ABS, LOGIT_REL, f"sequence {i}, second call over the cache of the first")
+    eng.close()
+
+
 def test_a_second_model_does_not_disturb_a_captured_decode_step(gpu, oracle):
     """Scratch that a captured decode graph points at belongs to its model: a small model captures its step, then a
     model with more heads is created on the same device (which used to regrow a shared buffer), and the small model
