@@ -201,6 +201,11 @@ void config_from_metadata(const std::map<std::string, Value>& md, lc_model_confi
         if (it != md.end() && it->second.kind == Value::ARRAY) cfg.vocab_size = (int32_t)it->second.i;
     }
     if (pick("rope.freq_base", &v)) cfg.rope_theta = (float)v;  // loader.rs:130-131 (read through the integer accessor)
+    // mixture-of-experts files (no counterpart in the reference's loader): <arch>.expert_count / <arch>.expert_used_count
+    if (pick("expert_count", &v) && v > 0) {
+        cfg.n_experts = (int32_t)v;
+        cfg.top_k = pick("expert_used_count", &v) && v > 0 ? (int32_t)v : 2;
+    }
     *out = cfg;
 }
 
@@ -224,6 +229,7 @@ extern "C" int32_t lc_model_load_gguf(const char* path, const lc_model_config* o
         cfg.rms_eps = overrides->rms_eps; cfg.kv_dtype = overrides->kv_dtype; cfg.rope_mode = overrides->rope_mode;
         cfg.max_seqs = overrides->max_seqs; cfg.kv_page_tokens = overrides->kv_page_tokens;
         cfg.kv_pool_tokens = overrides->kv_pool_tokens; cfg.device = overrides->device;
+        cfg.tp_size = overrides->tp_size; cfg.tp_rank = overrides->tp_rank;  // a rank of a cut model reads the same file and keeps its part
     }
 
     lc_model* m = nullptr;

@@ -83,3 +83,38 @@ def test_load_reports_missing_and_unsupported_tensors(gpu, tmp_path):
     with pytest.raises(_capi.LeafcutterError) as e:
         Engine.load(path, max_seq_len=64)
     assert "type 31" in str(e.value)
+
+
+@pytest.mark.gpu
+def test_mixture_of_experts_file(gpu, oracle, tmp_path):
+    """A GGUF file of a mixture model: llama.expert_count / llama.expert_used_count in the metadata, the router as
+    blk.N.ffn_gate_inp.weight and the experts as the stacked three-dimensional tensors blk.N.ffn_{gate,up,down}_exps.weight.
+    The loaded model must give the logits of the tensor-by-tensor model (one tensor per expert) and of the oracle."""
+    from leafcutterllm_b200 import synth
+    from leafcutterllm_b200.engine import Engine
+    from leafcutterllm_b200.synth import ModelSpec
+    from gguf_util import T_U32
+    spec = ModelSpec("moe-file", 2, 256, 2, 2, 512, 640, 10000.0, 12, 12, 12, n_experts=4, top_k=2)
+    tensors, stacks = [], {}
+    for name, typ, dims, kind in spec.tensors():
+        data = synth.tensor_bytes(spec, name, typ, dims, kind)
+        if ".expert." in name:
+            layer, which = name.split(".")[1], name.split(".")[-2]
+            stacks.setdefault((layer, which), []).append((typ, dims, data))
+        else:
+            tensors.append((name, typ, tuple(dims), data))
+    for (layer, which), parts in stacks.items():
+        typ, dims = parts[0][0], parts[0][1]
+        tensors.append((f"blk.{layer}.{which}_exps.weight", typ, (dims[0], dims[1], spec.n_experts), np.concatenate([p[2] for p in parts])))
+    path = tmp_path / "moe.gguf"
+    md = spec_metadata(spec) + [("llama.expert_count", T_U32, spec.n_experts), ("llama.expert_used_count", T_U32, spec.top_k)]
+    write_gguf(path, md, tensors)
+    eng = Engine.load(path, max_seq_len=64)
+    assert (eng.cfg.n_experts, eng.cfg.top_k) == (4, 2)
+    ref, om = make_pair(gpu, oracle, spec, max_seq_len=64)
+    prompt = synth.prompt_tokens(13, spec.vocab_size, 5)
+    a, b = eng.forward(prompt), ref.forward(prompt)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert_close(a, om.forward(prompt), 1e-2, 1e-3, "mixture model from a file vs oracle")
+    eng.close()
+    ref.close()
