@@ -111,6 +111,7 @@ struct lc_model {
     // FFN hidden rows and outputs (calls of up to kMoeGroupedTokens tokens), every expert's output plane (larger calls)
     int32_t *d_moe_sel = nullptr, *d_moe_cnt = nullptr, *d_moe_lists = nullptr;
     float *d_moe_w = nullptr, *d_moe_h = nullptr, *d_moe_y = nullptr, *d_moe_yall = nullptr;
+    GemvPlanes moe_planes_x, moe_planes_h;  // fixed-point activations of the grouped launches: the layer's input per token, the experts' hidden rows per slot
     unsigned long long* d_moe_touched = nullptr;  // experts that received a token, summed over layers and steps since the last read
     uint64_t expert_bytes_each = 0, expert_bytes_all = 0;
     double touched_per_step = 0.0;
@@ -427,17 +428,21 @@ int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T
         g1.tmaps = w.tm_gate; g1.tmaps2 = w.tm_up; g1.counts = m->d_moe_cnt + e0; g1.lists = m->d_moe_lists + (size_t)e0 * kMoeGroupedTokens;
         g1.list_stride = kMoeGroupedTokens; g1.n_experts = El; g1.top_k = K; g1.max_tokens = T; g1.x_by_token = true;
         g1.typical_tokens = (T * K + E - 1) / E;
+        g1.planes = m->moe_planes_x;
+        LC_TRY(launch_gemv_planes(x, norm_w, m->cfg.rms_eps, m->H, T, m->moe_planes_x, m->stream));
         GemvArgs a;
-        a.w = &w.egate[0]; a.w2 = &w.eup[0]; a.x = x; a.norm_w = norm_w; a.eps = m->cfg.rms_eps; a.out = m->d_moe_h; a.epi = EPI_SILU_MUL;
+        a.w = &w.egate[0]; a.w2 = &w.eup[0]; a.x = x; a.out = m->d_moe_h; a.epi = EPI_SILU_MUL;
         a.m = std::min(T, kTokTile); a.group = &g1;
         LC_TRY(launch_qgemv(a, m->stream));
         GemvGroup g2 = g1;
-        g2.tmaps = w.tm_down; g2.tmaps2 = nullptr; g2.x_by_token = false;
+        g2.tmaps = w.tm_down; g2.tmaps2 = nullptr; g2.x_by_token = false; g2.planes = m->moe_planes_h;
+        // every slot's hidden row (slots of experts that live on other ranks hold stale values nobody reads)
+        LC_TRY(launch_gemv_planes(m->d_moe_h, nullptr, 0.f, m->F, T * K, m->moe_planes_h, m->stream));
         GemvArgs d;
         d.w = &w.edown[0]; d.x = m->d_moe_h; d.out = m->d_moe_y; d.m = std::min(T, kTokTile); d.group = &g2;
         LC_TRY(launch_qgemv(d, m->stream));
         LC_TRY(launch_moe_combine(m->d_moe_y, m->d_moe_sel, m->d_moe_w, K, m->H, T, 0, 0, e0, El, residual, out, m->stream));
-        m->launches_in_call += 3;
+        m->launches_in_call += 5;
         return LC_OK;
     }
     (void)E;
@@ -986,6 +991,14 @@ int32_t lc_model_finalize(lc_model* m) {
         LC_TRY(dalloc(&m->d_moe_cnt, (size_t)E)); LC_TRY(dalloc(&m->d_moe_lists, (size_t)E * kMoeGroupedTokens));
         LC_TRY(dalloc(&m->d_moe_h, (size_t)kMoeGroupedTokens * K * F)); LC_TRY(dalloc(&m->d_moe_y, (size_t)kMoeGroupedTokens * K * H));
         LC_TRY(dalloc(&m->d_moe_yall, (size_t)E * T * H));
+        auto planes_alloc = [&](GemvPlanes* pl, size_t rows, int k) -> int32_t {
+            const size_t units = rows * (size_t)(k / 256);
+            if (units == 0) return LC_OK;
+            LC_TRY(dalloc(&pl->planes, units * 768)); LC_TRY(dalloc(&pl->sxf, units * 8)); LC_TRY(dalloc(&pl->inv2s, units));
+            return LC_OK;
+        };
+        LC_TRY(planes_alloc(&m->moe_planes_x, (size_t)kMoeGroupedTokens, H));
+        LC_TRY(planes_alloc(&m->moe_planes_h, (size_t)kMoeGroupedTokens * K, F));
         LC_TRY(dalloc(&m->d_moe_touched, 1));
         LC_CUDA(cudaMemsetAsync(m->d_moe_touched, 0, 8, m->stream));
     }
@@ -1036,6 +1049,7 @@ int32_t lc_model_destroy(lc_model* m) {
     }
     for (lc_model* x : m->members) if (x != m) x->leader = nullptr;
     void* bufs[] = {m->d_tiles, m->d_part, m->d_key, m->d_key_max, m->d_logits_all, m->d_moe_sel, m->d_moe_w, m->d_moe_cnt, m->d_moe_lists, m->d_moe_h, m->d_moe_y, m->d_moe_yall, m->d_moe_touched,
+                    m->moe_planes_x.planes, m->moe_planes_x.sxf, m->moe_planes_x.inv2s, m->moe_planes_h.planes, m->moe_planes_h.sxf, m->moe_planes_h.inv2s,
                     m->d_stream_slots, m->d_page_table, m->d_tokens, m->d_tok_seq, m->d_tok_pos, m->d_tok_rope, m->d_last_idx, m->d_hidden, m->d_hidden2,
                     m->d_qkv, m->d_attn, m->d_ffn, m->d_last, m->d_logits, m->d_next, m->d_out_tokens, m->d_step_ctr,
                     m->d_attn_scratch, m->d_attn_counters, m->d_sanity, m->d_qkv_parts};

@@ -64,6 +64,16 @@ enum GemvEpilogue { EPI_STORE = 0, EPI_ADD_RESIDUAL = 1, EPI_SILU_MUL = 2 };
 // per expert, how many (token, choice) slots it received and their list (slot = token * top_k + choice, ascending);
 // the product of expert e reads the input row of each of its slots (row slot / top_k when x_by_token, else row slot)
 // and writes the result to row `slot` of out.  All pointers are device memory.
+// Activations of a grouped launch, written once per call by launch_gemv_planes and read by every CTA of the launch: per row
+// and 256-element unit the three balanced byte planes of the 24-bit fixed point (768 bytes), the eight sub-block sums and
+// the unit's 2^-s.
+struct GemvPlanes {
+    unsigned char* planes = nullptr;  // [rows][k / 256][8][3][32]
+    float* sxf = nullptr;             // [rows][k / 256][8]
+    float* inv2s = nullptr;           // [rows][k / 256]
+};
+inline size_t gemv_planes_bytes(size_t rows, int k) { return rows * (size_t)(k / 256) * 768; }
+int32_t launch_gemv_planes(const float* x, const float* norm_w, float eps, int k, int rows, const GemvPlanes& out, cudaStream_t s);
 struct GemvGroup {
     const void* tmaps = nullptr;    // [n_experts] tensor maps (128 bytes each) of the first matrix
     const void* tmaps2 = nullptr;   // EPI_SILU_MUL: those of the `up` matrices
@@ -72,7 +82,8 @@ struct GemvGroup {
     int list_stride = 0, n_experts = 0, top_k = 0;
     int max_tokens = 0;             // most slots any expert can receive in this call (= tokens of the call)
     int typical_tokens = 0;         // what an expert receives on average (tokens * top_k / experts, rounded up); 0 = unknown
-    bool x_by_token = false;
+    bool x_by_token = false;        // the planes are per token (row = slot / top_k) rather than per slot
+    GemvPlanes planes;              // the launch's activations (GemvArgs.x / norm_w are not read)
 };
 // A product whose output rows are one rank's share of a sum over the ranks can write them straight into every rank's
 // buffer as tagged words (dist.cu): word tk * n + row of row `rank`, slot (sum number) & 1, sum number = *epoch + 1.

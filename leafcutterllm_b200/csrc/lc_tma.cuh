@@ -76,7 +76,10 @@ struct GemvGroupParams {
     const CUtensorMap* tm1;
     const int32_t* cnt;
     const int32_t* list;
-    int list_stride, top_k, x_by_token, passes;
+    const unsigned char* planes;  // [row][unit][8 sub-blocks][3 planes][32] fixed-point activations (GemvPlanes)
+    const float* sxf;             // [row][unit][8]
+    const float* inv2s;           // [row][unit]
+    int list_stride, top_k, x_by_token;
 };
 
 // Launch with the programmatic-dependent-launch attribute (off when LC_NO_PDL is set).

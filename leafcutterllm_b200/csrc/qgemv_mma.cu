@@ -36,15 +36,19 @@ __device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *rein
 __device__ __forceinline__ int byte_of(uint32_t w, int j) { return (int)((w >> (8 * j)) & 0xFFu); }
 
 // planes of one unit: [sub-block 8][token M][plane 3][32 bytes]
+constexpr int kGroupedSlots = 64;  // most slots one expert of a grouped launch can receive
+
 template <int M>
 __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
     return ((unit * 8 + sb) * M + tok) * 96 + plane * 32;
 }
 
-// GROUPED: one launch over the experts of a mixture-of-experts layer.  blockIdx.y = expert * passes + pass; the CTA
-// reads how many tokens the router sent to its expert and leaves at once when its pass has none, takes the expert's
-// tensor maps from a device array, gathers its (up to M) input rows through the expert's slot list and writes each
-// result row to its slot.  The plain instantiation carries none of this.
+// GROUPED: one launch over the experts of a mixture-of-experts layer.  blockIdx.y = expert; the CTA reads how many
+// slots the router sent to its expert (leaving at once when none), takes the expert's tensor maps from a device array and
+// walks its tiles; per tile it makes one pass per M slots, re-requesting the tile's boxes (L2 hits) for the later passes,
+// and writes each result row to its slot.  The activations come as fixed-point planes that gemv_planes_kernel wrote once
+// for the whole launch, read per job from global memory (L2): no per-CTA norm or plane computation, and no shared memory
+// that grows with k.  The plain instantiation carries none of this.
 template <int M, int WARPS, int STAGES, bool GROUPED = false>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p, GemvGroupParams gp) {
@@ -53,25 +57,24 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     const CUtensorMap* t1p = &tm1;
     int m_act = p.m;
     extern __shared__ __align__(128) unsigned char smem[];
-    int* s_slot = reinterpret_cast<int*>(smem);  // GROUPED: the first 64 bytes of shared memory hold the CTA's slots
+    int* s_slot = reinterpret_cast<int*>(smem);  // GROUPED: the first 256 bytes of shared memory hold the expert's slots
+    int cnt = 0, npass = 1, pass = 0;
     if constexpr (GROUPED) {
         pdl_launch_dependents();
-        pdl_wait();  // the router's counts and lists come from the kernel ahead
-        const int e = blockIdx.y / gp.passes, pass = blockIdx.y - e * gp.passes;
-        m_act = min(M, gp.cnt[e] - pass * M);
-        if (m_act <= 0) return;
+        pdl_wait();  // the router's counts and lists and the planes come from the kernels ahead
+        const int e = blockIdx.y;
+        cnt = min(gp.cnt[e], min(gp.list_stride, kGroupedSlots));
+        if (cnt <= 0) return;
+        npass = (cnt + M - 1) / M;
         t0p = gp.tm0 + e;
         t1p = gp.tm1 + e;
-        if (threadIdx.x < M) s_slot[threadIdx.x] = (int)threadIdx.x < m_act ? gp.list[(size_t)e * gp.list_stride + pass * M + threadIdx.x] : 0;
+        if ((int)threadIdx.x < cnt) s_slot[threadIdx.x] = gp.list[(size_t)e * gp.list_stride + threadIdx.x];
         __syncthreads();
     }
     // row of x / of out that token slot tk of this CTA reads / writes
-    auto xrow = [&](int tk) -> const float* {
-        if constexpr (GROUPED) return p.x + (size_t)(gp.x_by_token ? s_slot[tk] / gp.top_k : s_slot[tk]) * p.k;
-        else return p.x + (size_t)tk * p.k;
-    };
+    auto xrow = [&](int tk) -> const float* { return p.x + (size_t)tk * p.k; };
     auto orow = [&](int tk) -> size_t {
-        if constexpr (GROUPED) return (size_t)s_slot[tk] * p.n;
+        if constexpr (GROUPED) return (size_t)s_slot[pass * M + tk] * p.n;
         else return (size_t)tk * p.n;
     };
     constexpr int RG = 2;        // 16-row MMA groups per tile
@@ -90,15 +93,16 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         atomicMax(p.ring + 7, gtime());  // the last CTA to start
         if (blockIdx.x == 0) { rg = p.ring; rg[0] = gtime(); rg[5] = ((unsigned long long)p.n << 32) | (unsigned)p.k; }
     }
-    constexpr size_t kHead = GROUPED ? 128 : 0;  // keeps the stages 128-byte aligned behind the slots
+    constexpr size_t kHead = GROUPED ? kGroupedSlots * 4 : 0;  // keeps the stages 128-byte aligned behind the slots
     unsigned char* stage_base = smem + kHead + (size_t)warp * STAGES * STAGE_BYTES;
     size_t off = kHead + (size_t)WARPS * STAGES * STAGE_BYTES;
+    const int nu_s = GROUPED ? 0 : nunits;                       // GROUPED reads the planes from global memory
     unsigned char* planes = smem + off;                          // [nunits][8][M][3][32] int8
-    off += (size_t)nunits * 8 * M * 96;
+    off += (size_t)nu_s * 8 * M * 96;
     float* sxf = reinterpret_cast<float*>(smem + off);           // [nunits][M][8]: sum of x over each sub-block
-    off += (size_t)nunits * M * 8 * 4;
+    off += (size_t)nu_s * M * 8 * 4;
     float* inv2s = reinterpret_cast<float*>(smem + off);         // [nunits][M]: 2^-s
-    off += (size_t)nunits * M * 4;
+    off += (size_t)nu_s * M * 4;
     float* red = reinterpret_cast<float*>(smem + off);           // [2][WARPS][M][32]
     off += (size_t)2 * WARPS * M * 32 * 4;
     float* gate_vals = reinterpret_cast<float*>(smem + off);     // [M][32]
@@ -109,17 +113,23 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 
     const int units_mine = (nunits > warp) ? (nunits - warp + WARPS - 1) / WARPS : 0;
     const int tiles_mine = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int njobs = tiles_mine * units_mine * nmat;
+    const int njobs = tiles_mine * npass * units_mine * nmat;
 
     // producer cursor (lane 0): the next job to request, walked without divisions
-    int pj = 0, p_ti = 0, p_mat = 0, p_ui = 0;
+    int pj = 0, p_ti = 0, p_pass = 0, p_mat = 0, p_ui = 0;
     auto issue_next = [&]() {
         const int st = pj & (STAGES - 1);
         mbar_expect_tx(&bars[st], STAGE_BYTES);
         tma_load_2d(stage_base + (size_t)st * STAGE_BYTES, p_mat ? t1p : t0p, (warp + p_ui * WARPS) * (UB / 4),
                     (blockIdx.x + p_ti * gridDim.x) * TR, &bars[st]);
         pj++;
-        if (++p_ui == units_mine) { p_ui = 0; if (++p_mat == nmat) { p_mat = 0; ++p_ti; } }
+        if (++p_ui == units_mine) {
+            p_ui = 0;
+            if (++p_mat == nmat) {
+                p_mat = 0;
+                if (++p_pass == npass) { p_pass = 0; ++p_ti; }
+            }
+        }
     };
 
     if (lane == 0) {
@@ -130,7 +140,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     }
     // One token whose k fits one unit per warp: each warp reads its own 256 elements ONCE, for the sum of squares and for
     // the planes, and the gains (weights: no dependency on the kernel ahead) are already in registers by then.
-    const bool one_pass = (M == 1) && p.norm_w != nullptr && nunits <= WARPS;
+    const bool one_pass = !GROUPED && (M == 1) && p.norm_w != nullptr && nunits <= WARPS;
     float nw0[8];
     if (one_pass && warp < nunits) {
         const float4* np = reinterpret_cast<const float4*>(p.norm_w + warp * kUnitElems + 8 * lane);
@@ -165,7 +175,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 #pragma unroll
         for (int w = 0; w < WARPS; w++) r += scratch[w];  // every thread, same order
         rms0 = 1.0f / sqrtf(r / (float)p.k + p.eps);
-    } else if (p.norm_w) {
+    } else if (!GROUPED && p.norm_w) {
         for (int tk = 0; tk < M; tk++) {
             float ss = 0.f;
             if (tk < m_act) {
@@ -186,7 +196,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     }
 
     // ---- each warp writes the fixed-point planes of its own units ----
-    for (int ui = 0; ui < units_mine; ui++) {
+    for (int ui = 0; ui < (GROUPED ? 0 : units_mine); ui++) {
         const int unit = warp + ui * WARPS;
 #pragma unroll
         for (int tk = 0; tk < M; tk++) {
@@ -260,17 +270,33 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     // B fragment source of this thread: column g = lane / 4
     const int bcol_tok = (g >= 3) ? 1 : 0, bcol_pl = (g >= 3) ? g - 3 : g;
 
+    // GROUPED: row of the planes arrays that each token slot of the current pass reads (set at the start of a pass)
+    int prow[M];
+#pragma unroll
+    for (int tk = 0; tk < M; tk++) prow[tk] = 0;
     auto load_bf = [&](int unit, uint32_t (&bf)[NPAIR][8][2]) {
 #pragma unroll
         for (int pr = 0; pr < NPAIR; pr++) {
             const int tok = 2 * pr + bcol_tok;
-            const bool colv = g < 6 && tok < M;
-            const unsigned char* bp = planes + plane_off<M>(unit, 0, colv ? tok : 0, bcol_pl > 2 ? 0 : bcol_pl) + 4 * t;
+            if constexpr (GROUPED) {
+                const bool colv = g < 6 && tok < m_act;
+                const int r = bcol_tok ? prow[(2 * pr + 1) < M ? 2 * pr + 1 : 0] : prow[2 * pr];
+                const unsigned char* bp = gp.planes + (unsigned)(((colv ? r : 0) * nunits + unit) * 768 + (bcol_pl > 2 ? 0 : bcol_pl) * 32 + 4 * t);
 #pragma unroll
-            for (int sb = 0; sb < 8; sb++) {
-                const uint32_t v0 = lds32(bp + sb * (M * 96)), v1 = lds32(bp + sb * (M * 96) + 16);
-                bf[pr][sb][0] = colv ? v0 : 0u;
-                bf[pr][sb][1] = colv ? v1 : 0u;
+                for (int sb = 0; sb < 8; sb++) {
+                    const uint32_t v0 = __ldg(reinterpret_cast<const uint32_t*>(bp + sb * 96)), v1 = __ldg(reinterpret_cast<const uint32_t*>(bp + sb * 96 + 16));
+                    bf[pr][sb][0] = colv ? v0 : 0u;
+                    bf[pr][sb][1] = colv ? v1 : 0u;
+                }
+            } else {
+                const bool colv = g < 6 && tok < M;
+                const unsigned char* bp = planes + plane_off<M>(unit, 0, colv ? tok : 0, bcol_pl > 2 ? 0 : bcol_pl) + 4 * t;
+#pragma unroll
+                for (int sb = 0; sb < 8; sb++) {
+                    const uint32_t v0 = lds32(bp + sb * (M * 96)), v1 = lds32(bp + sb * (M * 96) + 16);
+                    bf[pr][sb][0] = colv ? v0 : 0u;
+                    bf[pr][sb][1] = colv ? v1 : 0u;
+                }
             }
         }
     };
@@ -282,19 +308,36 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         load_bf(unit, bf);
 #pragma unroll
         for (int tk = 0; tk < M; tk++) {
-            sx2[tk][0] = sxf[(unit * M + tk) * 8 + 2 * t];
-            sx2[tk][1] = sxf[(unit * M + tk) * 8 + 2 * t + 1];
-            isv[tk] = inv2s[unit * M + tk] * 0.0625f;  // 2^-s and the factor 16 the integer sums carry
+            if constexpr (GROUPED) {
+                const unsigned at = (unsigned)(prow[tk] * nunits + unit);
+                const float2 sx = tk < m_act ? __ldg(reinterpret_cast<const float2*>(gp.sxf + at * 8 + 2 * t)) : make_float2(0.f, 0.f);
+                sx2[tk][0] = sx.x;
+                sx2[tk][1] = sx.y;
+                isv[tk] = tk < m_act ? __ldg(gp.inv2s + at) * 0.0625f : 0.f;
+            } else {
+                sx2[tk][0] = sxf[(unit * M + tk) * 8 + 2 * t];
+                sx2[tk][1] = sxf[(unit * M + tk) * 8 + 2 * t + 1];
+                isv[tk] = inv2s[unit * M + tk] * 0.0625f;  // 2^-s and the factor 16 the integer sums carry
+            }
         }
     };
-    const bool single_unit = units_mine == 1;
+    const bool single_unit = !GROUPED && units_mine == 1;
     if (single_unit) load_unit_consts(warp);
 
     bool ok = true;
-    int job = 0;
+    int job = 0, seq = 0;
     for (int ti = 0; ti < tiles_mine; ti++) {
         const int tile = blockIdx.x + ti * gridDim.x;
-        for (int mat = 0; mat < nmat; mat++) {
+        for (pass = 0; pass < npass; pass++) {
+        if constexpr (GROUPED) {
+            m_act = min(M, cnt - pass * M);
+#pragma unroll
+            for (int tk = 0; tk < M; tk++) {
+                const int slot = s_slot[pass * M + (tk < m_act ? tk : 0)];
+                prow[tk] = gp.x_by_token ? slot / gp.top_k : slot;
+            }
+        }
+        for (int mat = 0; mat < nmat; mat++, seq++) {
             // per-thread partial row sums (the 4 threads of a row are added once per tile)
             float yacc[RG][2][M];  // [row group][row g / g+8][token]
 #pragma unroll
@@ -385,7 +428,6 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                         yacc[a][b][c] = v;
                     }
             // ---- cross-warp reduction of this (tile, matrix), in warp order ----
-            const int seq = ti * nmat + mat;
             float* rb = red + (size_t)(seq & 1) * WARPS * M * 32;
             if (t == 0) {
 #pragma unroll
@@ -427,10 +469,93 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 }
             }
         }
+        }
     }
     if (rg) rg[3] = gtime();
     if (p.ring && threadIdx.x == 0) atomicMax(p.ring + 6, gtime());  // the last CTA to finish
     if (!ok && lane == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+}
+
+// The activations of a grouped launch, once per call: row r of x (RMS-normalised with gains when norm_w is given,
+// cpu.rs:49-60) as 24-bit fixed point against each 256-element unit's own power-of-two scale, split into three balanced
+// byte planes, with the eight sub-block sums and 2^-s (the arithmetic of the prologue above, bit for bit).  One CTA of
+// eight warps per row; a warp per unit.
+__global__ void __launch_bounds__(256) gemv_planes_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int k,
+                                                          unsigned char* __restrict__ planes, float* __restrict__ sxf, float* __restrict__ inv2s) {
+    __shared__ float s_part[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
+    const int nunits = k / kUnitElems;
+    const size_t row = blockIdx.x;
+    const float* xr = x + row * (size_t)k;
+    pdl_launch_dependents();
+    pdl_wait();
+    float rms = 1.f;
+    if (norm_w) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < k; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        if (lane == 0) s_part[warp] = ss;
+        __syncthreads();
+        float r = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) r += s_part[w];  // every thread, same order
+        rms = 1.0f / sqrtf(r / (float)k + eps);
+    }
+    for (int unit = warp; unit < nunits; unit += 8) {
+        const int e0 = unit * kUnitElems + 8 * lane;
+        const float4* xp = reinterpret_cast<const float4*>(xr + e0);
+        const float4 u0 = xp[0], u1 = xp[1];
+        float v[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        if (norm_w) {
+            const float4* np = reinterpret_cast<const float4*>(norm_w + e0);
+            const float4 n0 = np[0], n1 = np[1];
+            const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = (v[j] * rms) * nw[j];
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+        amax = warp_max(amax);
+        const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
+        const int s = max(-100, min(100, 22 - ex));
+        const float up = __uint_as_float((uint32_t)(127 + s) << 23), dn = __uint_as_float((uint32_t)(127 - s) << 23);
+        uint32_t pw[3][2];
+        int xsum = 0;
+        int d0[8], d1[8], d2[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float sv = v[j] * up;
+            sv = fminf(fmaxf(sv, -4194304.f), 4194304.f);
+            const int X = __float2int_rn(sv);
+            xsum += X;
+            d0[j] = X;
+            d1[j] = (X - (int)(signed char)X) >> 8;
+            d2[j] = (d1[j] - (int)(signed char)d1[j]) >> 8;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            pw[0][h] = __byte_perm(__byte_perm(d0[4 * h], d0[4 * h + 1], 0x0040), __byte_perm(d0[4 * h + 2], d0[4 * h + 3], 0x0040), 0x5410);
+            pw[1][h] = __byte_perm(__byte_perm(d1[4 * h], d1[4 * h + 1], 0x0040), __byte_perm(d1[4 * h + 2], d1[4 * h + 3], 0x0040), 0x5410);
+            pw[2][h] = __byte_perm(__byte_perm(d2[4 * h], d2[4 * h + 1], 0x0040), __byte_perm(d2[4 * h + 2], d2[4 * h + 3], 0x0040), 0x5410);
+        }
+        const int sb = lane >> 2, inner = (8 * lane) & 31;
+        const size_t at = row * nunits + unit;
+#pragma unroll
+        for (int pl = 0; pl < 3; pl++) *reinterpret_cast<uint2*>(planes + at * 768 + sb * 96 + pl * 32 + inner) = make_uint2(pw[pl][0], pw[pl][1]);
+        xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
+        xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
+        if (t == 0) sxf[at * 8 + sb] = (float)xsum * dn;
+        if (lane == 0) inv2s[at] = dn;
+    }
+}
+
+int32_t launch_gemv_planes(const float* x, const float* norm_w, float eps, int k, int rows, const GemvPlanes& out, cudaStream_t s) {
+    LC_CHECK(x && out.planes && out.sxf && out.inv2s && rows > 0 && k > 0 && k % kUnitElems == 0 && ((uintptr_t)x % 16) == 0 &&
+                 (!norm_w || ((uintptr_t)norm_w % 16) == 0),
+             LC_ERR_INVALID, "gemv planes: bad arguments");
+    LC_CUDA(launch_pdl(gemv_planes_kernel, dim3(rows), dim3(256), 0, s, x, norm_w, eps, k, out.planes, out.sxf, out.inv2s));
+    return LC_OK;
 }
 
 namespace {
@@ -454,20 +579,20 @@ void dump_mring() {
 }  // namespace
 
 template <int M, int WARPS, int STAGES>
-static size_t mma_smem_bytes(int k) {
-    int nunits = k / kUnitElems;
+static size_t mma_smem_bytes(int k, bool grouped = false) {
+    int nunits = grouped ? 0 : k / kUnitElems;
     size_t b = (size_t)WARPS * STAGES * 144 * kTileRows;
     b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * M * 8 * 4 + (size_t)nunits * M * 4;
     b += (size_t)2 * WARPS * M * 32 * 4 + (size_t)M * 32 * 4 + (size_t)(32 + M) * 4;
     b = (b + 7) & ~(size_t)7;
     b += (size_t)WARPS * STAGES * 8;
-    return b + 128;  // head room for the slot words of the grouped form
+    return b + kGroupedSlots * 4;  // head room for the slot words of the grouped form
 }
 
 template <int M, int WARPS, int STAGES, bool GROUPED = false>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, GROUPED>;
-    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k);
+    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k, GROUPED);
     LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
@@ -496,8 +621,8 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
         const GemvGroup& g = *a.group;
         gp.tm0 = (const CUtensorMap*)g.tmaps; gp.tm1 = (const CUtensorMap*)(g.tmaps2 ? g.tmaps2 : g.tmaps);
         gp.cnt = g.counts; gp.list = g.lists; gp.list_stride = g.list_stride; gp.top_k = g.top_k; gp.x_by_token = g.x_by_token ? 1 : 0;
-        gp.passes = (g.max_tokens + M - 1) / M;
-        gy = (unsigned)(g.n_experts * gp.passes);
+        gp.planes = g.planes.planes; gp.sxf = g.planes.sxf; gp.inv2s = g.planes.inv2s;
+        gy = (unsigned)g.n_experts;
     }
     LC_CUDA(launch_pdl(kern, dim3(grid, gy), dim3(WARPS * 32), smem, s, *t0, *t1, p, gp));
     return LC_OK;
@@ -523,29 +648,21 @@ bool qgemv_mma_supports(int k) {
 // holds the call's tokens; more than eight tokens make several passes per expert.
 template <int M, int WARPS>
 static int32_t launch_grouped_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
-    if (mma_smem_bytes<M, WARPS, 2>(a.w->k) > kMaxSmem) return LC_OK;
     *launched = true;
     return launch_mma_cfg<M, WARPS, 2, true>(a, s);
 }
 int32_t launch_qgemv_mma_q4k_grouped(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = false;
     const GemvGroup* g = a.group;
-    LC_CHECK(g && g->tmaps && g->counts && g->lists && g->n_experts > 0 && g->max_tokens > 0 && g->top_k > 0 && !a.residual, LC_ERR_INVALID,
-             "grouped qgemv: incomplete expert group");
-    if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
-    // Token tile: the smallest of 1, 2, 4, 8 that holds what an expert typically receives (tokens * top_k / experts of the layer),
-    // as long as the fixed-point planes of a whole row fit shared memory (14336-element rows leave room for two tokens); an
-    // expert with more tokens than the tile makes several passes, and passes without tokens leave at once.
+    LC_CHECK(g && g->tmaps && g->counts && g->lists && g->n_experts > 0 && g->max_tokens > 0 && g->top_k > 0 && !a.residual && !a.norm_w &&
+                 g->planes.planes && g->planes.sxf && g->planes.inv2s && g->list_stride <= kGroupedSlots,
+             LC_ERR_INVALID, "grouped qgemv: incomplete expert group");
+    // Token tile: the smallest of 1, 2, 4, 8 that holds what an expert typically receives (tokens * top_k / experts of the
+    // layer); an expert with more slots than the tile makes several passes per weight tile.
     const int want = std::max(1, std::min(g->max_tokens, g->typical_tokens > 0 ? g->typical_tokens : g->max_tokens));
-    if (want > 4) { LC_TRY((launch_grouped_m<8, 8>(a, s, launched))); if (*launched) return LC_OK; }
-    if (want > 2) {
-        LC_TRY((launch_grouped_m<4, 16>(a, s, launched))); if (*launched) return LC_OK;
-        LC_TRY((launch_grouped_m<4, 8>(a, s, launched))); if (*launched) return LC_OK;
-    }
-    if (want > 1) {
-        LC_TRY((launch_grouped_m<2, 16>(a, s, launched))); if (*launched) return LC_OK;
-        LC_TRY((launch_grouped_m<2, 8>(a, s, launched))); if (*launched) return LC_OK;
-    }
+    if (want > 4) return launch_grouped_m<8, 8>(a, s, launched);
+    if (want > 2) return launch_grouped_m<4, 16>(a, s, launched);
+    if (want > 1) return launch_grouped_m<2, 16>(a, s, launched);
     return launch_grouped_m<1, 16>(a, s, launched);
 }
 

@@ -22,8 +22,8 @@ def moe_spec(layer_type=12, layers=2, hidden=256, heads=2, kv=2, ffn=512, vocab=
 
 @pytest.mark.parametrize("n_experts,top_k", [(4, 2), (8, 2), (8, 1), (5, 3)])
 def test_moe_prefill_decode_and_tokens(gpu, oracle, n_experts, top_k):
-    """17-token prefill (grouped launch, three passes of eight tokens per expert), single-token decode steps (grouped
-    launch, one token) and greedy tokens."""
+    """17-token prefill (grouped launch, several passes per weight tile where an expert received more slots than the token
+    tile), single-token decode steps (grouped launch, one token) and greedy tokens."""
     from leafcutterllm_b200 import synth
     spec = moe_spec(n_experts=n_experts, top_k=top_k)
     eng, om = make_pair(gpu, oracle, spec, max_seq_len=96)
@@ -142,9 +142,9 @@ def test_moe_config_errors(gpu):
     assert e.value.status == -1
 
 
-def test_moe_long_expert_rows_take_narrower_token_tiles(gpu, oracle):
-    """Experts whose down projection reads 8192-element rows: the fixed-point planes of eight tokens no longer fit shared
-    memory, so the grouped launch falls back to four-token tiles and more passes per expert."""
+def test_moe_long_expert_rows(gpu, oracle):
+    """Experts whose down projection reads 8192-element rows (32 units per row, two per warp): the grouped launch reads the
+    fixed-point planes of each unit from global memory job by job, so the row length does not limit the token tile."""
     from leafcutterllm_b200 import synth
     spec = moe_spec(layers=1, hidden=256, ffn=8192, n_experts=4, top_k=2)
     lens = [3, 7, 1, 9, 2, 5, 4, 6, 1, 3, 2, 6]
