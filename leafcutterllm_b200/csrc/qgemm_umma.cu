@@ -7,17 +7,17 @@
 // Weights stay as raw GGUF blocks in HBM; nothing dequantised is ever written back, and no weight is ever rounded: per
 // 256-element unit and row the sum is regrouped as
 //
-//   d * sum_k (sc * q)[k] * x[t, k]  -  dmin * sum_sub m[sub] * sx[t, sub],       sx = sum of x over the 32-element sub-block
+//   d * sum_k (sc * q)[k] * x[t, k]  -  sum_sub (dmin * m[sub]) * sx[t, sub],       sx = sum of x over the 32-element sub-block
 //
-// where sc * q <= 63 * 15 and m <= 63 are small integers, exact in f16.  Both sums run on the tensor cores with f32
-// accumulation; the two f16 scales of the unit are applied to the finished sums in f32.  One CTA owns 128 weight rows
-// (the M of tcgen05.mma) and up to 64 tokens, and walks k unit by unit:
+// where sc * q <= 63 * 15 is a small integer, exact in f16, and dmin * m (17 significant bits) is carried exactly by two
+// f16.  Both sums run on the tensor cores with f32 accumulation; d is applied to the finished sum of each unit in f32.
+// One CTA owns 128 weight rows (the M of tcgen05.mma) and up to 64 tokens, and walks k unit by unit:
 //
 //   producers  two threads: one requests the TMA boxes of raw blocks [144 B x 128 rows] per unit, the other per
 //              64-element chunk of k the activation tile [64 x N] of f16 (128-byte rows, hardware swizzle 128B) as high
 //              halves and, right behind them, low halves of the split below (one 3-D box), and per four units the tile
 //              of sub-block sums;
-//   unpack     two groups of 128 threads take the units in turn (for gate/up: one matrix each); thread r owns row r:
+//   unpack     two groups of 128 threads take the units in turn; thread r owns row r:
 //              nibbles -> (1024 + q) as f16 by a byte permute, times sc minus 1024 sc in one HFMA2 (exact), written
 //              with tcgen05.st straight into TENSOR MEMORY as the A operand (lane = row, one 32-bit column = two
 //              consecutive k): 1.4 instructions per weight, and unpacked weights never cross shared memory;
@@ -25,14 +25,15 @@
 //              Activations are x = hi + lo in f16 (2^-22 together); the high and the low tile lie one after the other,
 //              so ONE instruction with N = 2 x tokens forms both products (two column ranges, added in the drain);
 //              LC_GEMM_TERMS=1 keeps only the high halves (plain f16 activations, 2^-11);
-//   drain      when a unit's products are complete the owning group reads its row of the sums with tcgen05.ld and adds
-//              d * sum - dmin * minsum into the row's f32 results, which live in registers for the whole kernel;
-//   epilogue   undo the per-token power-of-two scale, then store / add the residual / SiLU(gate) * up.
+//   drain      four warps of their own: when a unit's products are complete, thread r reads row r of the sums with
+//              tcgen05.ld and adds d * sum into the row's f32 results, which live in its registers for the whole kernel;
+//   epilogue   add the offset sums, undo the per-token power-of-two scale, then store / add the residual, or leave the
+//              tile for the summing kernel (shares of k; SiLU(gate) * up).
 //
 // Activations are prepared by xprep_kernel: optional RMS norm (rust/src/backend/cpu.rs:49-60), a power-of-two scale per
 // token that brings its largest magnitude into [0.5, 1) (so neither half leaves the f16 range), the hi/lo split, and
-// the sub-block sums.  Every accumulator is written by one thread's products, in program order, and the two groups'
-// results are added in a fixed order: results are deterministic.
+// the sub-block sums.  Every accumulator is written by one thread's products, in program order, and the drain adds the
+// units in k order: results are deterministic.
 //
 // Every wait is bounded; a wait that runs out sets the library's device error flag and the CTA winds down (tensor
 // memory freed, no copy left in flight).
@@ -52,11 +53,12 @@ constexpr int kChunkK = 64;    // k per pipeline step: one 128-byte swizzled row
 constexpr int kMaxTok = 64;    // tokens per CTA (a multiple of 16)
 constexpr int kMaxRaw = 4;     // raw unit boxes in flight
 constexpr int kMaxB = 8;       // activation chunks in flight
-constexpr int kThreads = 384;  // warps 0 and 3 producers, warps 1-2 the two issuers, warps 4..7 and 8..11 the two unpack groups
+constexpr int kThreads = 512;  // warps 0 and 3 producers, warps 1-2 the two issuers, warps 4..7 and 8..11 the two unpack groups, 12..15 the drain
+constexpr int kDRing = 8;      // units whose per-row d travel from the unpack threads to the drain at a time
 constexpr int kUnitBytes = 144;
 // tensor-memory columns
 constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kColsPerPipe:
-constexpr uint32_t kColsPerPipe = 192;   //   [0, 2N) sum (sc q) x_hi | sum (sc q) x_lo, [128, 128 + N) sum m sx, of the step in progress
+constexpr uint32_t kColsPerPipe = 192;   //   [0, 2N) sum (sc q) x_hi | sum (sc q) x_lo of the unit in progress, [128, 128 + N) -sum dmin m sx of all its units
 constexpr uint32_t kColA = 384;          // four A stages of 32 columns (64 k each): stages 2g, 2g + 1 belong to pipeline g
 
 struct GemmParams {
@@ -68,8 +70,9 @@ struct GemmParams {
     int epi;                // GemvEpilogue
     int terms;              // 3: activations as high + low halves; 1: high halves only
     int raw_stages, b_stages;
-    int ksplit;             // CTAs along k per tile (gridDim.z); > 1: every CTA writes its two groups' sums to `partial`
-    float* partial;         // [ksplit][2 groups][T][n] f32
+    int ksplit;             // CTAs along k per tile (gridDim.z)
+    int tiles, nmat;        // row tiles per matrix; matrices (2 for EPI_SILU_MUL: blockIdx.x >= tiles works on the second)
+    float* partial;         // [ksplit][nmat][T][n] f32 for the summing kernel, or null: the CTA holds the whole sum and writes `out`
     int* error_flag;
     long long* trace;       // diagnostics (LC_GEMM_TRACE): [5 roles][256] SM clock stamps of CTA (0, 0), or null
 };
@@ -163,14 +166,24 @@ __device__ __forceinline__ void unpack_chunk(const unsigned char* rp, const HdrQ
         }
     }
 }
-// the eight m of a unit as four f16 pairs, then four columns of zeros (k' = 8..15 of the min product)
+// The offset operand of a unit: p[i] = -dmin * m[i] has at most 17 significant bits, so hi = f16(p) and lo = f16(p - hi)
+// carry it exactly (lo is a multiple of 2^-24 for any f16 dmin).  Columns 0-3: the eight hi as pairs (k' = 0..7), columns
+// 4-7: the eight lo (k' = 8..15); the sums tile holds each sub-block sum at k' and k' + 8.
 __device__ __forceinline__ void unpack_mins(const HdrQ4K& h, uint32_t (&col)[8]) {
-    const uint32_t one = h2_pair(1.0f), k = h2_pair(-1024.0f);
-    col[0] = h2_fma(bias_pair(h.mn_lo, 0), one, k);
-    col[1] = h2_fma(bias_pair(h.mn_lo, 1), one, k);
-    col[2] = h2_fma(bias_pair(h.mn_hi, 0), one, k);
-    col[3] = h2_fma(bias_pair(h.mn_hi, 1), one, k);
-    col[4] = col[5] = col[6] = col[7] = 0u;
+    __half hi[8], lo[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float m = (float)(((i < 4 ? h.mn_lo : h.mn_hi) >> (8 * (i & 3))) & 0xFFu);
+        const float pr = -h.dmin * m;
+        hi[i] = __float2half_rn(pr);
+        lo[i] = __float2half_rn(pr - __half2float(hi[i]));
+    }
+#pragma unroll
+    for (int j2 = 0; j2 < 4; j2++) {
+        const __half2 a = __halves2half2(hi[2 * j2], hi[2 * j2 + 1]), b = __halves2half2(lo[2 * j2], lo[2 * j2 + 1]);
+        col[j2] = *reinterpret_cast<const uint32_t*>(&a);
+        col[4 + j2] = *reinterpret_cast<const uint32_t*>(&b);
+    }
 }
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
@@ -182,7 +195,7 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 
 // One token per CTA: optional RMS norm, power-of-two scale, hi/lo split to f16, sub-block sums.
 // xh: [hi rows | lo rows at lo_offset] of K f16; sx: the same for the sums, rows of K/16 f16 -- per 256-element unit the
-// eight sub-block sums followed by eight zeros.
+// eight sub-block sums, twice.
 // The passes of the preparation over a token's row held in shared memory; `acc` = this thread's part of the sum of
 // squares, accumulated over elements 4 * tid + 4 * blockDim * j in that order.
 __device__ __forceinline__ void xprep_row(float* row, float acc, const float* __restrict__ norm_w, float eps, int K, int t,
@@ -241,8 +254,8 @@ __device__ __forceinline__ void xprep_row(float* row, float acc, const float* __
             const __half sh_ = __float2half_rn(part);
             sxh[idx] = sh_;
             sxl[idx] = __float2half_rn(part - __half2float(sh_));
-            sxh[idx + 8] = __float2half_rn(0.f);
-            sxl[idx + 8] = __float2half_rn(0.f);
+            sxh[idx + 8] = sh_;  // a second time: the offset operand pairs each sum with the high and with the low part of -dmin * m
+            sxl[idx + 8] = sxl[idx];
         }
     }
 }
@@ -265,29 +278,34 @@ xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, floa
     xprep_row(row, acc, norm_w, eps, K, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
 }
 
-// grid = (row tiles, token tiles).  tmw0 / tmw1: raw blocks of the matrix (and of `up` for EPI_SILU_MUL), box = one unit
-// x 128 rows.  tmx: the prepared activations [2 halves][t_cap rows][k] f16, box = 64 elements x N rows x both halves,
-// 128-byte swizzle; tms: the sub-block sums [2][t_cap rows][k / 16], same box.
+// grid = (row tiles x matrices, token tiles, shares of k).  tmw0 / tmw1: raw blocks of the matrix (and of `up` for
+// EPI_SILU_MUL: CTAs past the first matrix's tiles work on the second), box = one unit x 128 rows.  tmx: the prepared
+// activations [2 halves][t_cap rows][k] f16, box = 64 elements x N rows x both halves, 128-byte swizzle; tms: the
+// sub-block sums [2][t_cap rows][k / 16], same box.
 //
-// The (unit, matrix) steps are dealt in turn to two independent pipelines g = 0, 1, each made of an unpack group of 128
-// threads, an issuing thread and a set of accumulators: a thread needs ~100 cycles to issue one tcgen05 instruction
-// whatever its shape, so one issuer cannot keep the tensor pipe busy with N <= 128, and while one pipeline reads its
-// finished sums out of tensor memory the other one multiplies.
+// Roles (16 warps): warp 0 requests the activation tiles, warp 3 the raw boxes; the units of k are dealt in turn to two
+// pipelines g = 0, 1, each made of an unpack group of four warps (4 + 4g ..), an issuing thread (warp 1 + g) and its own
+// accumulators in tensor memory: one thread issues a tcgen05.mma of this shape every ~80 cycles at best, two together reach
+// the tensor pipe's rate (~67 cycles per M128 N128 K16).  Warps 12-15 only drain: thread r owns row r's f32 results for
+// the whole kernel, reads a finished unit's sums with tcgen05.ld while both pipelines already work on the next units, and
+// writes the tile at the end.  The unpack threads never wait for a product, the drain never unpacks.
+//
+// The offset term -dmin * m needs no drain per unit: dmin * m (11 x 6 bits) is split exactly into two f16 (high part and
+// remainder), the sixteen values of a unit form one K = 16 operand against the sub-block sums stored twice, and the
+// products of all units accumulate in one set of columns per pipeline, read once at the end.
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_constant__ CUtensorMap tmw1,
                       const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tms, GemmParams p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, tok0 = blockIdx.y * kMaxTok;
+    const int mat = (int)blockIdx.x >= p.tiles ? 1 : 0, tile = (int)blockIdx.x - mat * p.tiles, tok0 = blockIdx.y * kMaxTok;
     const int N = p.N;
     // this CTA's share of k: whole groups of four units (one tile of sub-block sums), so that only its last tile can be short
     const int nquads = (p.k / kUnitElems + 3) / 4;
     const int u_begin = (int)((long long)blockIdx.z * nquads / p.ksplit) * 4;
     const int u_end = min((int)((long long)(blockIdx.z + 1) * nquads / p.ksplit) * 4, p.k / kUnitElems);
-    const int nunits = u_end - u_begin;  // units are numbered from u_begin below
-    const int nmat = (p.epi == EPI_SILU_MUL) ? 2 : 1;
-    const int nseq = nunits * nmat;  // (unit, matrix) steps in order; step s belongs to pipeline s & 1
+    const int nseq = u_end - u_begin;  // units are numbered from u_begin below; unit s belongs to pipeline s & 1
     const int RS = p.raw_stages, BS = p.b_stages;
     const bool two = p.terms == 3;
     constexpr uint32_t raw_bytes = kUnitBytes * kRows;
@@ -296,23 +314,24 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     unsigned char* bt = smem;                              // [BS][hi N x 128 B | lo N x 128 B], 1024-byte aligned stages
     unsigned char* st = bt + (size_t)BS * b_bytes;         // [2][the same for the sub-block sums of four units]
     unsigned char* raw = st + (size_t)2 * b_bytes;         // [RS][raw_bytes]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + (size_t)RS * raw_bytes);
+    float* dd = reinterpret_cast<float*>(raw + (size_t)RS * raw_bytes);  // [kDRing][128]: d of row r in unit s, unpack -> drain
+    uint64_t* bars = reinterpret_cast<uint64_t*>(dd + kDRing * kRows);
     uint64_t* raw_full = bars;                 // [kMaxRaw] producer -> unpack (transaction bytes)
     uint64_t* raw_empty = raw_full + kMaxRaw;  // [kMaxRaw] unpack -> producer (128 arrivals)
     uint64_t* b_full = raw_empty + kMaxRaw;    // [kMaxB]   producer -> multiply
-    uint64_t* b_empty = b_full + kMaxB;        // [kMaxB]   multiply (a commit per matrix) -> producer
+    uint64_t* b_empty = b_full + kMaxB;        // [kMaxB]   multiply (commit) -> producer
     uint64_t* s_full = b_empty + kMaxB;        // [2]       sub-block sums of four units: producer -> multiply
-    uint64_t* s_empty = s_full + 2;            // [2]       multiply (a commit per step that used them) -> producer
+    uint64_t* s_empty = s_full + 2;            // [2]       multiply (a commit per unit that used them) -> producer
     uint64_t* a_full = s_empty + 2;            // [4]       unpack -> multiply (128 arrivals); stages 2g, 2g+1 are pipeline g's
     uint64_t* a_empty = a_full + 4;            // [4]       multiply (commit) -> unpack
-    uint64_t* d_full = a_empty + 4;            // [2]       the sums of a step of pipeline g are complete (commit)
-    uint64_t* d_empty = d_full + 2;            // [2]       pipeline g has read them (128 arrivals)
+    uint64_t* d_full = a_empty + 4;            // [2]       the sums of a unit of pipeline g are complete (commit)
+    uint64_t* d_empty = d_full + 2;            // [2]       the drain has read them (128 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
 
     if (warp == 0 && lane == 0) {
         for (int i = 0; i < kMaxRaw; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
-        for (int i = 0; i < kMaxB; i++) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], nmat); }
-        for (int i = 0; i < 2; i++) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4 * nmat); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128); }
+        for (int i = 0; i < kMaxB; i++) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128); }
         for (int i = 0; i < 4; i++) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -331,7 +350,8 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     auto stamp = [&](int role, int tag) {
         if (tracing && tr_n < 256) p.trace[role * 256 + tr_n++] = ((long long)tag << 48) | (clock64() & 0xFFFFFFFFFFFFll);
     };
-    float* xchg = reinterpret_cast<float*>(bt);  // after the last product: [128 rows][N + 1] f32 handed from group 1 to group 0
+    // a wait whose outcome the whole warp shares: the tensor-memory instructions are warp-wide
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer of the activations
@@ -339,7 +359,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         // 3-D box brings the high and the low halves of a chunk
         if (lane == 0) {
             pdl_wait();
-            const int b_total = nunits * 4;
+            const int b_total = nseq * 4;
             for (int b_next = 0; b_next < b_total && ok; b_next++) {
                 const int sb = b_next % BS;
                 if (!mbar_wait(&b_empty[sb], ((b_next / BS) & 1) ^ 1)) { ok = false; break; }
@@ -355,16 +375,15 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             }
         }
     } else if (warp == 3) {
-        // ---------------------------------------------------------------- producer of the raw boxes, (unit, matrix) order
-        // a thread of its own: every TMA or barrier instruction costs its issuing thread ~100 cycles, and the weights
-        // do not depend on the kernel ahead of this one, so this stream starts before the wait for it
+        // ---------------------------------------------------------------- producer of the raw boxes, unit order
+        // a thread of its own: the weights do not depend on the kernel ahead of this one, so this stream starts
+        // before the wait for it
         if (lane == 0) {
             for (int s = 0; s < nseq && ok; s++) {
                 const int sr = s % RS;
                 if (!mbar_wait(&raw_empty[sr], ((s / RS) & 1) ^ 1)) { ok = false; break; }
-                const int u = s / nmat, mat = s - u * nmat;
                 mbar_expect_tx(&raw_full[sr], raw_bytes);
-                tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + u) * (kUnitBytes / 4), tile * kRows, &raw_full[sr]);
+                tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + s) * (kUnitBytes / 4), tile * kRows, &raw_full[sr]);
             }
         }
     } else if (warp == 1 || warp == 2) {
@@ -376,14 +395,13 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             const uint32_t d_main = tmem + kColD + g * kColsPerPipe, d_min = d_main + 2 * kMaxTok;
             int j = 0;
             for (int s = g; s < nseq && ok; s += 2, j++) {
-                const int u = s / nmat;
-                // the accumulators still hold the previous step of this pipeline until its group has read them
+                // the accumulators still hold the previous unit of this pipeline until the drain has read them
                 stamp(1 + g, 5);
                 if (j > 0 && !mbar_wait(&d_empty[g], (j - 1) & 1)) { ok = false; break; }
                 stamp(1 + g, 6);
                 tc_fence_after();
                 for (int c = 0; c < 4 && ok; c++) {
-                    const int b_it = u * 4 + c, sb = b_it % BS;
+                    const int b_it = s * 4 + c, sb = b_it % BS;
                     if (!mbar_wait(&b_full[sb], (b_it / BS) & 1)) { ok = false; break; }
                     const int sa = 2 * g + (c & 1), fill = (c & 1) ? 2 * j + (c >> 1) : 3 * j + (c >> 1);
                     if (!mbar_wait(&a_full[sa], fill & 1)) { ok = false; break; }
@@ -399,13 +417,14 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                     stamp(1 + g, 4);
                 }
                 if (!ok) break;
-                {   // the min sums: A = the eight m of the unit (the fifth filling of stage 2g), B = this unit's 16 columns of the sums tile
-                    const int q = u >> 2, ss = q & 1, sa = 2 * g;
+                {   // the offset term: A = the unit's sixteen halves of -dmin * m (the fifth filling of stage 2g), B = this unit's
+                    // 16 columns of the sums tile; accumulates over all units of the pipeline
+                    const int q = s >> 2, ss = q & 1, sa = 2 * g;
                     if (!mbar_wait(&s_full[ss], (q >> 1) & 1)) { ok = false; break; }
                     if (!mbar_wait(&a_full[sa], (3 * j + 2) & 1)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t sdesc = umma_desc_sw128(smem_u32(st + (size_t)ss * b_bytes)) + (uint64_t)((u & 3) * 2);
-                    umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc, idesc_min, 0u);
+                    const uint64_t sdesc = umma_desc_sw128(smem_u32(st + (size_t)ss * b_bytes)) + (uint64_t)((s & 3) * 2);
+                    umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc, idesc_min, (uint32_t)(j > 0));
                     if (two) umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc + (uint64_t)(b_half >> 4), idesc_min, 1u);
                     umma_commit(&a_empty[sa]);
                     umma_commit(&s_empty[ss]);
@@ -413,20 +432,13 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 umma_commit(&d_full[g]);
             }
         }
-    } else if (warp >= 4) {
-        // ---------------------------------------------------------------- unpack + drain, then epilogue
+    } else if (warp < 12) {
+        // ---------------------------------------------------------------- unpack
         const int g = (warp - 4) >> 2;                // pipeline
         const int quarter = warp & 3;                 // the tensor-memory lanes this warp may touch
         const int row = quarter * 32 + lane;          // row of the tile owned by this thread
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const uint32_t d_main = tmem + lane_base + kColD + g * kColsPerPipe, d_min = d_main + 2 * kMaxTok;
         const bool tr = quarter == 0 && lane == 0;
-        // a wait whose outcome the whole warp shares: the tensor-memory instructions below are warp-wide
-        auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
-        float y[kMaxTok];
-#pragma unroll
-        for (int t = 0; t < kMaxTok; t++) y[t] = 0.f;
-        pdl_wait();
         int j = 0;
         for (int s = g; s < nseq && ok; s += 2, j++) {
             const int sr = s % RS;
@@ -437,23 +449,30 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             const unsigned char* rp = raw + (size_t)sr * raw_bytes + (size_t)row * kUnitBytes;
             HdrQ4K hdr;
             load_hdr(rp, hdr);
+            // the ring is deep enough: unit s + kDRing cannot be unpacked before unit s has been drained (its raw box needs
+            // the stage of unit s + kDRing - RS, whose chunks need tensor-memory stages that the products of unit s + 2
+            // free, and those start only when the drain has released the accumulators of unit s)
+            dd[(s & (kDRing - 1)) * kRows + row] = hdr.d;
             for (int c = 0; c < 4 && ok; c++) {
                 uint32_t col[32];
                 unpack_chunk(rp, hdr, c, col);
+                if (tr) stamp(3 + g, 10);
                 const int sa = 2 * g + (c & 1), fill = (c & 1) ? 2 * j + (c >> 1) : 3 * j + (c >> 1);
                 ok = wait_all(&a_empty[sa], (fill & 1) ^ 1);
                 if (!ok) break;
                 tc_fence_after();
+                if (tr) stamp(3 + g, 11);
                 const uint32_t a_t = tmem + lane_base + kColA + sa * 32;
                 tmem_st16(a_t, col);
                 tmem_st16(a_t + 16, col + 16);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 mbar_arrive(&a_full[sa]);
+                if (tr) stamp(3 + g, 12);
             }
             if (!ok) break;
             mbar_arrive(&raw_empty[sr]);  // this row's bytes of the unit are consumed
-            {   // the eight m as a fifth, short filling of stage 2g
+            {   // the offset operand as a fifth, short filling of stage 2g
                 uint32_t mc[8];
                 unpack_mins(hdr, mc);
                 ok = wait_all(&a_empty[2 * g], ((3 * j + 2) & 1) ^ 1);
@@ -464,72 +483,81 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 tc_fence_before();
                 mbar_arrive(&a_full[2 * g]);
             }
-            // drain: y += d * (main_hi + main_lo) - dmin * min
             if (tr) stamp(3 + g, 5);
+        }
+    } else {
+        // ---------------------------------------------------------------- drain, then epilogue
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        float y[kMaxTok];
+#pragma unroll
+        for (int t = 0; t < kMaxTok; t++) y[t] = 0.f;
+        pdl_wait();
+        for (int s = 0; s < nseq && ok; s++) {
+            const int g = s & 1, j = s >> 1;
+            const uint32_t d_main = tmem + lane_base + kColD + g * kColsPerPipe;
             ok = wait_all(&d_full[g], j & 1);
             if (!ok) break;
-            if (tr) stamp(3 + g, 6);
             tc_fence_after();
-            const float d = hdr.d, ndmin = -hdr.dmin;
+            const float d = dd[(s & (kDRing - 1)) * kRows + row];
 #pragma unroll
             for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
                 if (t0 < N) {
-                    uint32_t a[16], b[16], m[16];
+                    uint32_t a[16], b[16];
                     tmem_ld16(d_main + t0, a);
                     if (two) tmem_ld16(d_main + N + t0, b);
-                    tmem_ld16(d_min + t0, m);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         float v = __uint_as_float(a[i]);
                         if (two) v += __uint_as_float(b[i]);
                         y[t0 + i] = fmaf(d, v, y[t0 + i]);
-                        y[t0 + i] = fmaf(ndmin, __uint_as_float(m[i]), y[t0 + i]);
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(&d_empty[g]);
-            if (tr) stamp(3 + g, 7);
+        }
+        // the offset sums of both pipelines (complete: each pipeline's last d_full followed its last offset product)
+        if (ok) {
+#pragma unroll
+            for (int g = 0; g < 2; g++) {
+                if (g < nseq) {
+                    const uint32_t d_min = tmem + lane_base + kColD + g * kColsPerPipe + 2 * kMaxTok;
+#pragma unroll
+                    for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
+                        if (t0 < N) {
+                            uint32_t m[16];
+                            tmem_ld16(d_min + t0, m);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int i = 0; i < 16; i++) y[t0 + i] += __uint_as_float(m[i]);
+                        }
+                    }
+                }
+            }
         }
         pdl_launch_dependents();
-        if (p.ksplit > 1) {
-            // a share of k: both groups leave their sums (scaled back per token) for the reduction kernel
-            const int grow = tile * kRows + row;
-            float* dst = p.partial + ((size_t)(blockIdx.z * 2 + g) * p.T) * p.n;
-            if (ok && grow < p.n) {
+        const int grow = tile * kRows + row;
+        if (ok && grow < p.n) {
+            if (p.partial) {
+                // a share of k, or one of the two matrices of gate/up: the sums (scaled back per token) go to the summing kernel
+                float* dst = p.partial + ((size_t)(blockIdx.z * p.nmat + mat) * p.T) * p.n;
 #pragma unroll
                 for (int t = 0; t < kMaxTok; t++) {
                     const int tok = tok0 + t;
                     if (t < N && tok < p.T) dst[(size_t)tok * p.n + grow] = y[t] * __ldg(p.tok_scale + tok);
                 }
-            }
-        } else {
-            // every product of the tile has completed (both groups waited for their last step): shared memory is free
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            const int ld = N + 1;
-            if (g == 1 && ok) {
+            } else {
 #pragma unroll
-                for (int t = 0; t < kMaxTok; t++)
-                    if (t < N) xchg[row * ld + t] = y[t];
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (g == 0 && ok) {
-                const int grow = tile * kRows + row;
-                if (grow < p.n) {
-#pragma unroll
-                    for (int t = 0; t < kMaxTok; t++) {
-                        const int tok = tok0 + t;
-                        if (t < N && tok < p.T) {
-                            const float sc = __ldg(p.tok_scale + tok);
-                            const float other = xchg[row * ld + t];
-                            const size_t o = (size_t)tok * p.n + grow;
-                            float v;
-                            if (nmat == 2) v = __fmul_rn(silu_f(y[t] * sc), other * sc);  // engine.rs:146-164: group 0 holds gate, group 1 up
-                            else v = (y[t] + other) * sc;                                 // the two groups hold alternate units
-                            if (p.epi == EPI_ADD_RESIDUAL) v = __fadd_rn(p.residual[o], v);
-                            p.out[o] = v;
-                        }
+                for (int t = 0; t < kMaxTok; t++) {
+                    const int tok = tok0 + t;
+                    if (t < N && tok < p.T) {
+                        const size_t o = (size_t)tok * p.n + grow;
+                        float v = y[t] * __ldg(p.tok_scale + tok);
+                        if (p.epi == EPI_ADD_RESIDUAL) v = __fadd_rn(p.residual[o], v);
+                        p.out[o] = v;
                     }
                 }
             }
@@ -544,7 +572,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     }
 }
 
-// Sums the shares of k that the product kernel left in `partial` ([slices][T][n], slice = 2 * share + group), in slice
+// Sums what the product kernel left in `partial` ([slices][T][n], slice = share of k * matrices + matrix), in slice
 // order, and applies the epilogue.  With two matrices even slices belong to gate and odd ones to up.
 __global__ void __launch_bounds__(256)
 qgemm_reduce_kernel(const float* __restrict__ partial, int slices, size_t plane, int epi, const float* __restrict__ residual,
@@ -616,7 +644,8 @@ int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max) {
     LC_CUDA(cudaMalloc(&ws->sx, bytes / 16));
     LC_CUDA(cudaMemset(ws->sx, 0, bytes / 16));
     LC_CUDA(cudaMalloc((void**)&ws->tok_scale, (size_t)ws->t_cap * sizeof(float)));
-    ws->partial_bytes = (size_t)64 << 20;
+    // shares of k of the batched decode step, and the two matrices of gate/up at any number of tokens
+    ws->partial_bytes = std::max((size_t)64 << 20, (size_t)2 * ws->t_cap * k_max * sizeof(float));
     LC_CUDA(cudaMalloc((void**)&ws->partial, ws->partial_bytes));
     return LC_OK;
 }
@@ -672,10 +701,12 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     p.n = n; p.k = K; p.T = T; p.N = N; p.epi = (int)a.epi; p.terms = terms;
     const int nmat = a.epi == EPI_SILU_MUL ? 2 : 1;
     p.raw_stages = kMaxRaw;
+    if (getenv("LC_GEMM_RAWSTAGES")) p.raw_stages = std::max(2, std::min(kMaxRaw, atoi(getenv("LC_GEMM_RAWSTAGES"))));
     const size_t raw_bytes = (size_t)p.raw_stages * kUnitBytes * kRows, b_bytes = (size_t)2 * N * 128;
-    const size_t fixed = 1024 + raw_bytes + 2 * b_bytes + 512;
+    const size_t fixed = 1024 + raw_bytes + 2 * b_bytes + (size_t)kDRing * kRows * sizeof(float) + 512;
     p.b_stages = std::min(kMaxB, (int)((kMaxSmem - fixed) / b_bytes));
-    LC_CHECK(p.b_stages >= 4, LC_ERR_UNSUPPORTED, "qgemm: shared memory too small");
+    if (getenv("LC_GEMM_BSTAGES")) p.b_stages = std::max(2, std::min(p.b_stages, atoi(getenv("LC_GEMM_BSTAGES"))));
+    LC_CHECK(p.b_stages >= 2, LC_ERR_UNSUPPORTED, "qgemm: shared memory too small");
     p.error_flag = gemv_error_flag_dev();
     p.trace = nullptr;
     static long long* d_trace = nullptr;
@@ -690,47 +721,48 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap_wide;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap_wide : t0;
     // Few tiles (a batched decode step on the square matrices): split k over several CTAs so that all SMs work; the
-    // shares are summed, in a fixed order, by a small second kernel.  Cost model: waves x steps per CTA, plus four
-    // steps' worth of prologue and epilogue per wave.
+    // shares are summed, in a fixed order, by a small second kernel.  Cost model: waves x units per CTA, plus four
+    // units' worth of prologue and epilogue per wave.  The two matrices of gate/up always meet in that kernel.
     const int tiles = (n + kRows - 1) / kRows, ttiles = (T + kMaxTok - 1) / kMaxTok, nquads = (K / kUnitElems + 3) / 4;
     int ks = 1;
     {
         const int sms = sm_count();
         long best = -1;
         for (int c = 1; c <= std::min(8, nquads); c++) {
-            if (c > 1 && (size_t)c * 2 * T * n * sizeof(float) > ws.partial_bytes) break;
+            if (c > 1 && (size_t)c * nmat * T * n * sizeof(float) > ws.partial_bytes) break;
             if (c > 1 && (n % 4 != 0 || T > 2 * kMaxTok)) break;
-            const long waves = ((long)tiles * ttiles * c + sms - 1) / sms;
-            const long cost = waves * (((nquads + c - 1) / c) * 4 * nmat + 4) + (c > 1 ? 3 : 0);
+            const long waves = ((long)tiles * nmat * ttiles * c + sms - 1) / sms;
+            const long cost = waves * (((nquads + c - 1) / c) * 4 + 4) + (c > 1 ? 3 : 0);
             if (best < 0 || cost < best) { best = cost; ks = c; }
         }
-        // gate/up with fewer tiles than SMs: shares measured better than the model says (64 sequences, 4 layers, ms per step:
-        // one share 2.59, two 2.47, three 2.42, four 2.44), the 4096 -> 12288 product flat for any split
-        if (nmat == 2 && ks == 1 && tiles * ttiles < sms && nquads >= 2 && n % 4 == 0 && T <= 2 * kMaxTok) {
-            const int want = nquads >= 3 ? 3 : 2;
-            if ((size_t)want * 2 * T * n * sizeof(float) <= ws.partial_bytes) ks = want;
-        }
+        static const int force_gu = getenv("LC_GEMM_KSPLIT_GU") ? atoi(getenv("LC_GEMM_KSPLIT_GU")) : 0;
+        static const int force = getenv("LC_GEMM_KSPLIT") ? atoi(getenv("LC_GEMM_KSPLIT")) : 0;
+        const int f = nmat == 2 ? force_gu : force;
+        if (f > 0 && f <= nquads && (f == 1 || (n % 4 == 0 && (size_t)f * nmat * T * n * sizeof(float) <= ws.partial_bytes))) ks = f;
     }
+    const bool summed = ks > 1 || nmat == 2;
+    if (summed) LC_CHECK((size_t)ks * nmat * T * n * sizeof(float) <= ws.partial_bytes && n % 4 == 0, LC_ERR_UNSUPPORTED, "qgemm: sums buffer too small");
     p.ksplit = ks;
-    p.partial = ws.partial;
-    dim3 grid((unsigned)tiles, (unsigned)ttiles, (unsigned)ks);
+    p.tiles = tiles; p.nmat = nmat;
+    p.partial = summed ? ws.partial : nullptr;
+    dim3 grid((unsigned)(tiles * nmat), (unsigned)ttiles, (unsigned)ks);
     LC_CUDA(launch_pdl(qgemm_umma_q4k_kernel, grid, dim3(kThreads), smem, s, *t0, *t1, tmx, tms, p));
-    if (ks > 1) {
+    if (summed) {
         const size_t plane = (size_t)T * n;
         if (a.prep_next && n % kUnitElems == 0 && n <= ws.k_max) {
             // one CTA per token sums the shares and prepares the row for the next product, whose k is this n
             const size_t rsmem = (size_t)n * sizeof(float);
             if (rsmem > 48 * 1024) LC_CUDA(ensure_smem_limit((const void*)qgemm_reduce_prep_kernel, rsmem));
-            LC_CUDA(launch_pdl(qgemm_reduce_prep_kernel, dim3(T), dim3(n >= 4096 ? 1024 : 256), rsmem, s, (const float*)ws.partial, 2 * ks, T, n,
+            LC_CUDA(launch_pdl(qgemm_reduce_prep_kernel, dim3(T), dim3(n >= 4096 ? 1024 : 256), rsmem, s, (const float*)ws.partial, nmat * ks, T, n,
                                (int)a.epi, a.residual, a.out, a.next_norm_w, a.next_eps, (__half*)ws.xh, (size_t)ws.t_cap * n, (__half*)ws.sx,
                                (size_t)ws.t_cap * (n / 16), ws.tok_scale));
             ws.prep_x = a.out; ws.prep_norm = a.next_norm_w; ws.prep_k = n; ws.prep_t = T;
         } else {
-            LC_CUDA(launch_pdl(qgemm_reduce_kernel, dim3((unsigned)((plane / 4 + 255) / 256)), dim3(256), 0, s, (const float*)ws.partial, 2 * ks,
+            LC_CUDA(launch_pdl(qgemm_reduce_kernel, dim3((unsigned)((plane / 4 + 255) / 256)), dim3(256), 0, s, (const float*)ws.partial, nmat * ks,
                                plane, (int)a.epi, a.residual, a.out));
         }
     }
-    if (launches) *launches = (prepared ? 1 : 2) + (ks > 1 ? 1 : 0);
+    if (launches) *launches = (prepared ? 1 : 2) + (summed ? 1 : 0);
     if (want_trace) {
         static long long h[1280];
         LC_CUDA(cudaStreamSynchronize(s));
