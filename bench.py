@@ -339,7 +339,7 @@ def gemv_types(lc) -> dict:
     return {"kernel": "matrix-vector product, one token, per ggml type", "rows": rows}
 
 
-def gemm_microbench(lc, tokens=(64, 512), small: bool = False) -> dict:
+def gemm_microbench(lc, tokens=(64, 512), small: bool = False, shapes=None) -> dict:
     """The many-token tensor-core product (Q4_K weights dequantised on the fly, tcgen05) timed alone on the 7B shapes:
     per shape and token count the time of one launch pair (activation split + product) over distinct weight copies
     larger than L2, CUDA events on the library's stream."""
@@ -347,7 +347,8 @@ def gemm_microbench(lc, tokens=(64, 512), small: bool = False) -> dict:
     lib = lc.load()
     chk = lc._capi.check
     rows = []
-    shapes = [(4096, 12288), (4096, 4096), (11008, 4096)] if not small else [(4096, 4096)]
+    if shapes is None:
+        shapes = [(4096, 12288), (4096, 4096), (11008, 4096)] if not small else [(4096, 4096)]
     for m in tokens:
         for (k, n) in shapes:
             nb = lib.lc_tensor_bytes(12, k * n)

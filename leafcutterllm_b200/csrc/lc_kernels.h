@@ -139,6 +139,7 @@ bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws);
 int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s, int* launches = nullptr);
 // Tensor map over f16 activations [2 halves][rows][k] with a box of 64 elements x box_rows rows x both halves, 128-byte swizzle.
 bool make_act_tmap(void* out128, const void* base, uint64_t k, uint64_t rows, uint32_t box_rows);
+bool make_act_tmap_chunks(void* out128, const void* base, uint64_t k, uint64_t rows, uint32_t box_rows, uint32_t box_chunks);
 
 // ---- attention.cu ----
 struct KvLayout {

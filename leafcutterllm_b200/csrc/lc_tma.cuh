@@ -54,6 +54,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, int x, 
         "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, int x, int y, int z, int w, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+            smem_u32(dst)),
+        "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
 
 // cpu.rs:62-64
 __device__ __forceinline__ float silu_f(float v) { return v * (1.0f / (1.0f + expf(-v))); }

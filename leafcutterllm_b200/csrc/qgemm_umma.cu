@@ -52,14 +52,16 @@ constexpr int kRows = 128;     // weight rows per CTA = MMA M
 constexpr int kChunkK = 64;    // k per pipeline step: one 128-byte swizzled row of f16
 constexpr int kMaxTok = 64;    // tokens per CTA (a multiple of 16)
 constexpr int kMaxRaw = 4;     // raw unit boxes in flight
-constexpr int kMaxB = 8;       // activation chunks in flight
+constexpr int kMaxB = 4;       // activation stages of two chunks each: two units in flight, and a stage always serves the same pipeline
 constexpr int kThreads = 512;  // warps 0 and 3 producers, warps 1-2 the two issuers, warps 4..7 and 8..11 the two unpack groups, 12..15 the drain
 constexpr int kDRing = 8;      // units whose per-row d travel from the unpack threads to the drain at a time
 constexpr int kUnitBytes = 144;
 // tensor-memory columns
-constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kColsPerPipe:
-constexpr uint32_t kColsPerPipe = 192;   //   [0, 2N) sum (sc q) x_hi | sum (sc q) x_lo of the unit in progress, [128, 128 + N) -sum dmin m sx of all its units
-constexpr uint32_t kColA = 384;          // four A stages of 32 columns (64 k each): stages 2g, 2g + 1 belong to pipeline g
+constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kColsPerPipe: [0, 2N) sum (sc q) x_hi | sum (sc q) x_lo of its unit in progress
+constexpr uint32_t kColsPerPipe = 128;
+constexpr uint32_t kColDmin = 256;       // [0, N): -sum dmin m sx of all units
+constexpr uint32_t kColA = 320;          // four A stages of 32 columns: chunk c (64 k) of every unit goes through stage c
+constexpr uint32_t kColAmin = 448;       // two stages of 8 columns for the offset operand, one per pipeline
 
 struct GemmParams {
     float* out;             // [T, n]
@@ -306,13 +308,14 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     const int u_begin = (int)((long long)blockIdx.z * nquads / p.ksplit) * 4;
     const int u_end = min((int)((long long)(blockIdx.z + 1) * nquads / p.ksplit) * 4, p.k / kUnitElems);
     const int nseq = u_end - u_begin;  // units are numbered from u_begin below; unit s belongs to pipeline s & 1
-    const int RS = p.raw_stages, BS = p.b_stages;
+    const int RS = p.raw_stages;
+    constexpr int BS = kMaxB;
     const bool two = p.terms == 3;
     constexpr uint32_t raw_bytes = kUnitBytes * kRows;
     const uint32_t b_half = (uint32_t)N * 128u, b_bytes = 2u * b_half;
 
-    unsigned char* bt = smem;                              // [BS][hi N x 128 B | lo N x 128 B], 1024-byte aligned stages
-    unsigned char* st = bt + (size_t)BS * b_bytes;         // [2][the same for the sub-block sums of four units]
+    unsigned char* bt = smem;                              // [BS][2 chunks][hi N x 128 B | lo N x 128 B], 1024-byte aligned
+    unsigned char* st = bt + (size_t)BS * 2 * b_bytes;     // [2][the same for the sub-block sums of four units]
     unsigned char* raw = st + (size_t)2 * b_bytes;         // [RS][raw_bytes]
     float* dd = reinterpret_cast<float*>(raw + (size_t)RS * raw_bytes);  // [kDRing][128]: d of row r in unit s, unpack -> drain
     uint64_t* bars = reinterpret_cast<uint64_t*>(dd + kDRing * kRows);
@@ -322,17 +325,25 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     uint64_t* b_empty = b_full + kMaxB;        // [kMaxB]   multiply (commit) -> producer
     uint64_t* s_full = b_empty + kMaxB;        // [2]       sub-block sums of four units: producer -> multiply
     uint64_t* s_empty = s_full + 2;            // [2]       multiply (a commit per unit that used them) -> producer
-    uint64_t* a_full = s_empty + 2;            // [4]       unpack -> multiply (128 arrivals); stages 2g, 2g+1 are pipeline g's
-    uint64_t* a_empty = a_full + 4;            // [4]       multiply (commit) -> unpack
-    uint64_t* d_full = a_empty + 4;            // [2]       the sums of a unit of pipeline g are complete (commit)
+    uint64_t* a_full = s_empty + 2;            // [2][4]    unpack group g filled stage c (128 arrivals) -> issuer g
+    uint64_t* a_empty = a_full + 8;            // [2][4]    issuer g's products of stage c are complete (commit) -> the other group
+    uint64_t* am_full = a_empty + 8;           // [2]       the offset operand of pipeline g (128 arrivals)
+    uint64_t* am_empty = am_full + 2;          // [2]       its product is complete (commit)
+    uint64_t* min_done = am_empty + 2;         // [2]       the offset product of a unit of pipeline g is complete: the other issuer's may follow
+    uint64_t* d_full = min_done + 2;           // [2]       the sums of a unit of pipeline g are complete (commit)
     uint64_t* d_empty = d_full + 2;            // [2]       the drain has read them (128 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
+    uint32_t* raw_issued = tmem_slot + 1;      // units whose raw box has been requested (a stage serves both groups in turn: see below)
 
     if (warp == 0 && lane == 0) {
         for (int i = 0; i < kMaxRaw; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
         for (int i = 0; i < kMaxB; i++) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128); }
-        for (int i = 0; i < 4; i++) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128);
+            mbar_init(&am_full[i], 128); mbar_init(&am_empty[i], 1); mbar_init(&min_done[i], 1);
+        }
+        for (int i = 0; i < 8; i++) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
+        *raw_issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -350,7 +361,8 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     auto stamp = [&](int role, int tag) {
         if (tracing && tr_n < 256) p.trace[role * 256 + tr_n++] = ((long long)tag << 48) | (clock64() & 0xFFFFFFFFFFFFll);
     };
-    // a wait whose outcome the whole warp shares: the tensor-memory instructions are warp-wide
+    // a wait whose outcome the whole warp shares: the tensor-memory instructions are warp-wide.  (One polling lane per warp
+    // with a shuffle behind it, and one arrival per warp, measured slower: 44.0 vs 38.6 us at 64 tokens x 4096 x 12288.)
     auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
 
     if (warp == 0) {
@@ -359,18 +371,18 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         // 3-D box brings the high and the low halves of a chunk
         if (lane == 0) {
             pdl_wait();
-            const int b_total = nseq * 4;
+            const int b_total = nseq * 2;  // pairs of chunks
             for (int b_next = 0; b_next < b_total && ok; b_next++) {
-                const int sb = b_next % BS;
-                if (!mbar_wait(&b_empty[sb], ((b_next / BS) & 1) ^ 1)) { ok = false; break; }
-                if ((b_next & 15) == 0) {
-                    const int q = b_next >> 4, ss = q & 1;
+                const int sb = b_next & (kMaxB - 1);
+                if (!mbar_wait(&b_empty[sb], ((b_next / kMaxB) & 1) ^ 1)) { ok = false; break; }
+                if ((b_next & 7) == 0) {
+                    const int q = b_next >> 3, ss = q & 1;
                     if (!mbar_wait(&s_empty[ss], ((q >> 1) & 1) ^ 1)) { ok = false; break; }
                     mbar_expect_tx(&s_full[ss], b_bytes);
                     tma_load_3d(st + (size_t)ss * b_bytes, &tms, (u_begin / 4 + q) * 64, tok0, 0, &s_full[ss]);
                 }
-                mbar_expect_tx(&b_full[sb], b_bytes);
-                tma_load_3d(bt + (size_t)sb * b_bytes, &tmx, (u_begin * 4 + b_next) * kChunkK, tok0, 0, &b_full[sb]);
+                mbar_expect_tx(&b_full[sb], 2 * b_bytes);
+                tma_load_4d(bt + (size_t)sb * 2 * b_bytes, &tmx, 0, tok0, 0, u_begin * 4 + b_next * 2, &b_full[sb]);
                 stamp(0, 2);
             }
         }
@@ -384,6 +396,9 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 if (!mbar_wait(&raw_empty[sr], ((s / RS) & 1) ^ 1)) { ok = false; break; }
                 mbar_expect_tx(&raw_full[sr], raw_bytes);
                 tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + s) * (kUnitBytes / 4), tile * kRows, &raw_full[sr]);
+                // with an odd number of stages a stage serves the two unpack groups in turn, and a group that waited for unit
+                // s before unit s - RS had landed would read that phase's parity as its own: it first waits for this count
+                asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"((uint32_t)(s + 1)) : "memory");
             }
         }
     } else if (warp == 1 || warp == 2) {
@@ -392,7 +407,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         const int g = warp - 1;
         if (lane == 0) {
             const uint32_t idesc_main = idesc_f16(two ? 2 * N : N), idesc_min = idesc_f16(N);
-            const uint32_t d_main = tmem + kColD + g * kColsPerPipe, d_min = d_main + 2 * kMaxTok;
+            const uint32_t d_main = tmem + kColD + g * kColsPerPipe, d_min = tmem + kColDmin;
             int j = 0;
             for (int s = g; s < nseq && ok; s += 2, j++) {
                 // the accumulators still hold the previous unit of this pipeline until the drain has read them
@@ -401,33 +416,35 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 stamp(1 + g, 6);
                 tc_fence_after();
                 for (int c = 0; c < 4 && ok; c++) {
-                    const int b_it = s * 4 + c, sb = b_it % BS;
-                    if (!mbar_wait(&b_full[sb], (b_it / BS) & 1)) { ok = false; break; }
-                    const int sa = 2 * g + (c & 1), fill = (c & 1) ? 2 * j + (c >> 1) : 3 * j + (c >> 1);
-                    if (!mbar_wait(&a_full[sa], fill & 1)) { ok = false; break; }
+                    const int b_it = s * 2 + (c >> 1), sb = b_it & (kMaxB - 1);  // the pair of chunks and its stage
+                    if (!(c & 1) && !mbar_wait(&b_full[sb], (b_it / kMaxB) & 1)) { ok = false; break; }
+                    if (!mbar_wait(&a_full[g * 4 + c], j & 1)) { ok = false; break; }
                     tc_fence_after();
                     stamp(1 + g, 3);
-                    const uint64_t bdesc = umma_desc_sw128(smem_u32(bt + (size_t)sb * b_bytes));
-                    const uint32_t a_t = tmem + kColA + sa * 32;
+                    const uint64_t bdesc = umma_desc_sw128(smem_u32(bt + (size_t)(sb * 2 + (c & 1)) * b_bytes));
+                    const uint32_t a_t = tmem + kColA + c * 32;
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
                         umma_f16_ts(d_main, a_t + ks * 8, bdesc + (uint64_t)(ks * 2), idesc_main, (uint32_t)((c | ks) != 0));
-                    umma_commit(&a_empty[sa]);
-                    umma_commit(&b_empty[sb]);
+                    umma_commit(&a_empty[g * 4 + c]);
+                    if (c & 1) umma_commit(&b_empty[sb]);
                     stamp(1 + g, 4);
                 }
                 if (!ok) break;
-                {   // the offset term: A = the unit's sixteen halves of -dmin * m (the fifth filling of stage 2g), B = this unit's
-                    // 16 columns of the sums tile; accumulates over all units of the pipeline
-                    const int q = s >> 2, ss = q & 1, sa = 2 * g;
+                {   // the offset term: A = the unit's sixteen halves of -dmin * m, B = this unit's 16 columns of the sums tile.
+                    // One set of columns accumulates all units; the two issuers take turns, each waiting for the other's
+                    // product of the unit before, so the additions happen in k order.
+                    const int q = s >> 2, ss = q & 1;
                     if (!mbar_wait(&s_full[ss], (q >> 1) & 1)) { ok = false; break; }
-                    if (!mbar_wait(&a_full[sa], (3 * j + 2) & 1)) { ok = false; break; }
+                    if (!mbar_wait(&am_full[g], j & 1)) { ok = false; break; }
+                    if (s > 0 && !mbar_wait(&min_done[1 - g], ((s - 1) >> 1) & 1)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t sdesc = umma_desc_sw128(smem_u32(st + (size_t)ss * b_bytes)) + (uint64_t)((s & 3) * 2);
-                    umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc, idesc_min, (uint32_t)(j > 0));
-                    if (two) umma_f16_ts(d_min, tmem + kColA + sa * 32, sdesc + (uint64_t)(b_half >> 4), idesc_min, 1u);
-                    umma_commit(&a_empty[sa]);
+                    umma_f16_ts(d_min, tmem + kColAmin + g * 8, sdesc, idesc_min, (uint32_t)(s > 0));
+                    if (two) umma_f16_ts(d_min, tmem + kColAmin + g * 8, sdesc + (uint64_t)(b_half >> 4), idesc_min, 1u);
+                    umma_commit(&am_empty[g]);
                     umma_commit(&s_empty[ss]);
+                    umma_commit(&min_done[g]);
                 }
                 umma_commit(&d_full[g]);
             }
@@ -443,46 +460,59 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         for (int s = g; s < nseq && ok; s += 2, j++) {
             const int sr = s % RS;
             if (tr) stamp(3 + g, 1);
+            {   // the request for this unit's box has been made (see the producer)
+                uint32_t seen = 0;
+                for (uint32_t it = 0; it < (1u << 24) && seen <= (uint32_t)s; ++it)
+                    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(raw_issued)) : "memory");
+                ok = __all_sync(0xffffffffu, seen > (uint32_t)s);
+                if (!ok) break;
+            }
             ok = wait_all(&raw_full[sr], (s / RS) & 1);
             if (!ok) break;
             if (tr) stamp(3 + g, 2);
             const unsigned char* rp = raw + (size_t)sr * raw_bytes + (size_t)row * kUnitBytes;
             HdrQ4K hdr;
             load_hdr(rp, hdr);
-            // the ring is deep enough: unit s + kDRing cannot be unpacked before unit s has been drained (its raw box needs
-            // the stage of unit s + kDRing - RS, whose chunks need tensor-memory stages that the products of unit s + 2
-            // free, and those start only when the drain has released the accumulators of unit s)
+            // the ring is deep enough: unit s + kDRing cannot be unpacked before unit s has been drained (its chunks need the
+            // tensor-memory stages of unit s + kDRing - 1, ..., whose products wait for the accumulators that the drain releases)
             dd[(s & (kDRing - 1)) * kRows + row] = hdr.d;
+            {   // the offset operand of this pipeline first (the header is all it needs): free once the product of the pipeline's
+                // unit before has read it, which ended long ago
+                uint32_t mc[8];
+                unpack_mins(hdr, mc);
+                ok = wait_all(&am_empty[g], (j & 1) ^ 1);
+                if (!ok) break;
+                tc_fence_after();
+                tmem_st8(tmem + lane_base + kColAmin + g * 8, mc);
+            }
             for (int c = 0; c < 4 && ok; c++) {
+                // stage c still holds the unit before this one (the other group's) until that unit's products have read it; ask
+                // now, look at the answer after the unpacking
+                const uint32_t par = (uint32_t)(((s - 1) >> 1) & 1);
+                bool free_now = s == 0 || mbar_test(&a_empty[(1 - g) * 4 + c], par);
                 uint32_t col[32];
                 unpack_chunk(rp, hdr, c, col);
                 if (tr) stamp(3 + g, 10);
-                const int sa = 2 * g + (c & 1), fill = (c & 1) ? 2 * j + (c >> 1) : 3 * j + (c >> 1);
-                ok = wait_all(&a_empty[sa], (fill & 1) ^ 1);
+                // the chunk before this one (the offset operand ahead of the first) has had the time of this unpacking to reach
+                // tensor memory
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                mbar_arrive(c > 0 ? &a_full[g * 4 + c - 1] : &am_full[g]);
+                if (!free_now) free_now = mbar_wait(&a_empty[(1 - g) * 4 + c], par);
+                ok = __all_sync(0xffffffffu, free_now);
                 if (!ok) break;
                 tc_fence_after();
                 if (tr) stamp(3 + g, 11);
-                const uint32_t a_t = tmem + lane_base + kColA + sa * 32;
+                const uint32_t a_t = tmem + lane_base + kColA + c * 32;
                 tmem_st16(a_t, col);
                 tmem_st16(a_t + 16, col + 16);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                mbar_arrive(&a_full[sa]);
                 if (tr) stamp(3 + g, 12);
             }
             if (!ok) break;
             mbar_arrive(&raw_empty[sr]);  // this row's bytes of the unit are consumed
-            {   // the offset operand as a fifth, short filling of stage 2g
-                uint32_t mc[8];
-                unpack_mins(hdr, mc);
-                ok = wait_all(&a_empty[2 * g], ((3 * j + 2) & 1) ^ 1);
-                if (!ok) break;
-                tc_fence_after();
-                tmem_st8(tmem + lane_base + kColA + 2 * g * 32, mc);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                mbar_arrive(&a_full[2 * g]);
-            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(&a_full[g * 4 + 3]);
             if (tr) stamp(3 + g, 5);
         }
     } else {
@@ -519,22 +549,17 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             tc_fence_before();
             mbar_arrive(&d_empty[g]);
         }
-        // the offset sums of both pipelines (complete: each pipeline's last d_full followed its last offset product)
-        if (ok) {
+        // the offset sums (complete: every unit's d_full followed its offset product)
+        if (ok && nseq > 0) {
+            const uint32_t d_min = tmem + lane_base + kColDmin;
 #pragma unroll
-            for (int g = 0; g < 2; g++) {
-                if (g < nseq) {
-                    const uint32_t d_min = tmem + lane_base + kColD + g * kColsPerPipe + 2 * kMaxTok;
+            for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
+                if (t0 < N) {
+                    uint32_t m[16];
+                    tmem_ld16(d_min + t0, m);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
-                        if (t0 < N) {
-                            uint32_t m[16];
-                            tmem_ld16(d_min + t0, m);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                            for (int i = 0; i < 16; i++) y[t0 + i] += __uint_as_float(m[i]);
-                        }
-                    }
+                    for (int i = 0; i < 16; i++) y[t0 + i] += __uint_as_float(m[i]);
                 }
             }
         }
@@ -694,19 +719,19 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     }
     const int N = std::min(kMaxTok, (T + 15) & ~15);
     alignas(64) CUtensorMap tmx, tms;
-    LC_CHECK(make_act_tmap(&tmx, ws.xh, (uint64_t)K, (uint64_t)ws.t_cap, (uint32_t)N), LC_ERR_CUDA, "qgemm: activation tensor map");
+    LC_CHECK(make_act_tmap_chunks(&tmx, ws.xh, (uint64_t)K, (uint64_t)ws.t_cap, (uint32_t)N, 2), LC_ERR_CUDA, "qgemm: activation tensor map");
     LC_CHECK(make_act_tmap(&tms, ws.sx, (uint64_t)K / 16, (uint64_t)ws.t_cap, (uint32_t)N), LC_ERR_CUDA, "qgemm: sums tensor map");
     GemmParams p;
     p.out = a.out; p.residual = a.residual; p.tok_scale = ws.tok_scale;
     p.n = n; p.k = K; p.T = T; p.N = N; p.epi = (int)a.epi; p.terms = terms;
     const int nmat = a.epi == EPI_SILU_MUL ? 2 : 1;
-    p.raw_stages = kMaxRaw;
-    if (getenv("LC_GEMM_RAWSTAGES")) p.raw_stages = std::max(2, std::min(kMaxRaw, atoi(getenv("LC_GEMM_RAWSTAGES"))));
-    const size_t raw_bytes = (size_t)p.raw_stages * kUnitBytes * kRows, b_bytes = (size_t)2 * N * 128;
-    const size_t fixed = 1024 + raw_bytes + 2 * b_bytes + (size_t)kDRing * kRows * sizeof(float) + 512;
-    p.b_stages = std::min(kMaxB, (int)((kMaxSmem - fixed) / b_bytes));
-    if (getenv("LC_GEMM_BSTAGES")) p.b_stages = std::max(2, std::min(p.b_stages, atoi(getenv("LC_GEMM_BSTAGES"))));
-    LC_CHECK(p.b_stages >= 2, LC_ERR_UNSUPPORTED, "qgemm: shared memory too small");
+    // eight activation stages (two units: a stage always serves the same pipeline); the raw boxes take what is left
+    const size_t b_bytes = (size_t)2 * N * 128;
+    const size_t fixed = 1024 + (size_t)(2 * kMaxB + 2) * b_bytes + (size_t)kDRing * kRows * sizeof(float) + 512;
+    p.raw_stages = std::min(kMaxRaw, (int)((kMaxSmem - fixed) / ((size_t)kUnitBytes * kRows)));
+    if (getenv("LC_GEMM_RAWSTAGES")) p.raw_stages = std::max(2, std::min(p.raw_stages, atoi(getenv("LC_GEMM_RAWSTAGES"))));
+    LC_CHECK(p.raw_stages >= 2, LC_ERR_UNSUPPORTED, "qgemm: shared memory too small");
+    p.b_stages = kMaxB;
     p.error_flag = gemv_error_flag_dev();
     p.trace = nullptr;
     static long long* d_trace = nullptr;
@@ -716,7 +741,7 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
         LC_CUDA(cudaMemsetAsync(d_trace, 0, 1280 * sizeof(long long), s));
         p.trace = d_trace;
     }
-    const size_t smem = fixed + (size_t)p.b_stages * b_bytes;
+    const size_t smem = fixed + (size_t)p.raw_stages * kUnitBytes * kRows;
     LC_CUDA(ensure_smem_limit((const void*)qgemm_umma_q4k_kernel, smem));
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap_wide;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap_wide : t0;

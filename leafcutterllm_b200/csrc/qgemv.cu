@@ -116,6 +116,20 @@ bool make_act_tmap(void* out128, const void* base, uint64_t k, uint64_t rows, ui
     return r == CUDA_SUCCESS;
 }
 
+// The same activations with a fourth dimension, the 64-element chunk of k: one box takes `box_chunks` consecutive chunks
+// x box_rows rows of both halves and lands as [chunk][half][row][128 B].
+bool make_act_tmap_chunks(void* out128, const void* base, uint64_t k, uint64_t rows, uint32_t box_rows, uint32_t box_chunks) {
+    if (!encode_fn() || ((uintptr_t)base % 16) != 0 || k % 64 != 0 || box_rows == 0 || box_rows > 256 || box_chunks == 0 || box_chunks > 256) return false;
+    cuuint64_t dims[4] = {64, (cuuint64_t)rows, 2, (cuuint64_t)(k / 64)};
+    cuuint64_t strides[3] = {(cuuint64_t)k * 2, (cuuint64_t)k * 2 * rows, 128};
+    cuuint32_t box[4] = {64, box_rows, 2, box_chunks};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = encode_fn()((CUtensorMap*)out128, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, (void*)base, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 // ---------------------------------------------------------------------------
 // per-unit dot products.  `r` = the lane's unit in registers, xs = x of this
 // unit for token t at xs + t*xstride (256 floats), sx = per-32 sums of x.
