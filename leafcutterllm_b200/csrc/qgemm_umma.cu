@@ -61,7 +61,8 @@ constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kC
 constexpr uint32_t kColsPerPipe = 128;
 constexpr uint32_t kColDmin = 256;       // [0, N): -sum dmin m sx of all units
 constexpr uint32_t kColA = 320;          // four A stages of 32 columns: chunk c (64 k) of every unit goes through stage c
-constexpr uint32_t kColAmin = 448;       // two stages of 8 columns for the offset operand, one per pipeline
+constexpr uint32_t kColAmin = 448;       // four stages of 8 columns for the offset operand: two per pipeline, so that the operand of a unit
+                                         // can be written while the pipeline's unit before is still being multiplied
 
 struct GemmParams {
     float* out;             // [T, n]
@@ -76,7 +77,7 @@ struct GemmParams {
     int tiles, nmat;        // row tiles per matrix; matrices (2 for EPI_SILU_MUL: blockIdx.x >= tiles works on the second)
     float* partial;         // [ksplit][nmat][T][n] f32 for the summing kernel, or null: the CTA holds the whole sum and writes `out`
     int* error_flag;
-    long long* trace;       // diagnostics (LC_GEMM_TRACE): [5 roles][256] SM clock stamps of CTA (0, 0), or null
+    unsigned* trace;        // diagnostics (LC_GEMM_TRACE): [7 roles][8] cycles that CTA (0, 0)'s threads spent in each kind of wait, or null
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------------------------
@@ -324,13 +325,13 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     uint64_t* b_full = raw_empty + kMaxRaw;    // [kMaxB]   producer -> multiply
     uint64_t* b_empty = b_full + kMaxB;        // [kMaxB]   multiply (commit) -> producer
     uint64_t* s_full = b_empty + kMaxB;        // [2]       sub-block sums of four units: producer -> multiply
-    uint64_t* s_empty = s_full + 2;            // [2]       multiply (a commit per unit that used them) -> producer
+    uint64_t* s_empty = s_full + 2;            // [2]       multiply (the commit behind the last offset product that used them) -> producer
     uint64_t* a_full = s_empty + 2;            // [2][4]    unpack group g filled stage c (128 arrivals) -> issuer g
     uint64_t* a_empty = a_full + 8;            // [2][4]    issuer g's products of stage c are complete (commit) -> the other group
-    uint64_t* am_full = a_empty + 8;           // [2]       the offset operand of pipeline g (128 arrivals)
-    uint64_t* am_empty = am_full + 2;          // [2]       its product is complete (commit)
-    uint64_t* min_done = am_empty + 2;         // [2]       the offset product of a unit of pipeline g is complete: the other issuer's may follow
-    uint64_t* d_full = min_done + 2;           // [2]       the sums of a unit of pipeline g are complete (commit)
+    uint64_t* am_full = a_empty + 8;           // [2][2]    the offset operand of pipeline g, stage j & 1 (128 arrivals)
+    uint64_t* am_empty = am_full + 4;          // [2][2]    its product is complete (commit)
+    uint64_t* d_full = am_empty + 4;           // [2]       all products of a unit of pipeline g are complete (commit): the drain may read its sums,
+                                               //           and the other issuer may add the next unit's offset product
     uint64_t* d_empty = d_full + 2;            // [2]       the drain has read them (128 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
     uint32_t* raw_issued = tmem_slot + 1;      // units whose raw box has been requested (a stage serves both groups in turn: see below)
@@ -339,9 +340,9 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         for (int i = 0; i < kMaxRaw; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
         for (int i = 0; i < kMaxB; i++) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128);
-            mbar_init(&am_full[i], 128); mbar_init(&am_empty[i], 1); mbar_init(&min_done[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 1); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128);
         }
+        for (int i = 0; i < 4; i++) { mbar_init(&am_full[i], 128); mbar_init(&am_empty[i], 1); }
         for (int i = 0; i < 8; i++) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
         *raw_issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -359,14 +360,25 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     // (or the idle ones at once), do their own set-up and wait for this grid's completion before they read anything.  With
     // the call behind the main loop the 64-sequence step was 0.06 ms per layer slower (the attention grid started late).
     bool ok = true;
-    int tr_n = 0;
-    const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0;
-    auto stamp = [&](int role, int tag) {
-        if (tracing && tr_n < 256) p.trace[role * 256 + tr_n++] = ((long long)tag << 48) | (clock64() & 0xFFFFFFFFFFFFll);
+    // diagnostics: cycles spent in each kind of wait (slot), and in the role's whole loop (slot 7)
+    const bool tracing = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    unsigned wacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const unsigned t_role0 = (unsigned)clock64();
+    auto twait = [&](uint64_t* bar, uint32_t parity, int slot) -> bool {
+        if (!tracing) return mbar_wait(bar, parity);
+        const unsigned t0 = (unsigned)clock64();
+        const bool r = mbar_wait(bar, parity);
+        wacc[slot] += (unsigned)clock64() - t0;
+        return r;
+    };
+    auto trace_out = [&](int role) {
+        if (!tracing) return;
+        wacc[7] = (unsigned)clock64() - t_role0;
+        for (int i = 0; i < 8; i++) p.trace[role * 8 + i] = wacc[i];
     };
     // a wait whose outcome the whole warp shares: the tensor-memory instructions are warp-wide.  (One polling lane per warp
     // with a shuffle behind it, and one arrival per warp, measured slower: 44.0 vs 38.6 us at 64 tokens x 4096 x 12288.)
-    auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity)); };
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int slot) { return __all_sync(0xffffffffu, twait(bar, parity, slot)); };
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer of the activations
@@ -377,17 +389,17 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             const int b_total = nseq * 2;  // pairs of chunks
             for (int b_next = 0; b_next < b_total && ok; b_next++) {
                 const int sb = b_next & (kMaxB - 1);
-                if (!mbar_wait(&b_empty[sb], ((b_next / kMaxB) & 1) ^ 1)) { ok = false; break; }
+                if (!twait(&b_empty[sb], ((b_next / kMaxB) & 1) ^ 1, 0)) { ok = false; break; }
                 if ((b_next & 7) == 0) {
                     const int q = b_next >> 3, ss = q & 1;
-                    if (!mbar_wait(&s_empty[ss], ((q >> 1) & 1) ^ 1)) { ok = false; break; }
+                    if (!twait(&s_empty[ss], ((q >> 1) & 1) ^ 1, 1)) { ok = false; break; }
                     mbar_expect_tx(&s_full[ss], b_bytes);
                     tma_load_3d(st + (size_t)ss * b_bytes, &tms, (u_begin / 4 + q) * 64, tok0, 0, &s_full[ss]);
                 }
                 mbar_expect_tx(&b_full[sb], 2 * b_bytes);
                 tma_load_4d(bt + (size_t)sb * 2 * b_bytes, &tmx, 0, tok0, 0, u_begin * 4 + b_next * 2, &b_full[sb]);
-                stamp(0, 2);
             }
+            trace_out(0);
         }
     } else if (warp == 3) {
         // ---------------------------------------------------------------- producer of the raw boxes, unit order
@@ -396,13 +408,14 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         if (lane == 0) {
             for (int s = 0; s < nseq && ok; s++) {
                 const int sr = s % RS;
-                if (!mbar_wait(&raw_empty[sr], ((s / RS) & 1) ^ 1)) { ok = false; break; }
+                if (!twait(&raw_empty[sr], ((s / RS) & 1) ^ 1, 0)) { ok = false; break; }
                 mbar_expect_tx(&raw_full[sr], raw_bytes);
                 tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + s) * (kUnitBytes / 4), tile * kRows, &raw_full[sr]);
                 // with an odd number of stages a stage serves the two unpack groups in turn, and a group that waited for unit
                 // s before unit s - RS had landed would read that phase's parity as its own: it first waits for this count
                 asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"((uint32_t)(s + 1)) : "memory");
             }
+            trace_out(1);
         }
     } else if (warp == 1 || warp == 2) {
         // ---------------------------------------------------------------- multiply: the issuer of pipeline g
@@ -414,16 +427,13 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             int j = 0;
             for (int s = g; s < nseq && ok; s += 2, j++) {
                 // the accumulators still hold the previous unit of this pipeline until the drain has read them
-                stamp(1 + g, 5);
-                if (j > 0 && !mbar_wait(&d_empty[g], (j - 1) & 1)) { ok = false; break; }
-                stamp(1 + g, 6);
+                if (j > 0 && !twait(&d_empty[g], (j - 1) & 1, 0)) { ok = false; break; }
                 tc_fence_after();
                 for (int c = 0; c < 4 && ok; c++) {
                     const int b_it = s * 2 + (c >> 1), sb = b_it & (kMaxB - 1);  // the pair of chunks and its stage
-                    if (!(c & 1) && !mbar_wait(&b_full[sb], (b_it / kMaxB) & 1)) { ok = false; break; }
-                    if (!mbar_wait(&a_full[g * 4 + c], j & 1)) { ok = false; break; }
+                    if (!(c & 1) && !twait(&b_full[sb], (b_it / kMaxB) & 1, 1)) { ok = false; break; }
+                    if (!twait(&a_full[g * 4 + c], j & 1, 2)) { ok = false; break; }
                     tc_fence_after();
-                    stamp(1 + g, 3);
                     const uint64_t bdesc = umma_desc_sw128(smem_u32(bt + (size_t)(sb * 2 + (c & 1)) * b_bytes));
                     const uint32_t a_t = tmem + kColA + c * 32;
 #pragma unroll
@@ -431,26 +441,25 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                         umma_f16_ts(d_main, a_t + ks * 8, bdesc + (uint64_t)(ks * 2), idesc_main, (uint32_t)((c | ks) != 0));
                     umma_commit(&a_empty[g * 4 + c]);
                     if (c & 1) umma_commit(&b_empty[sb]);
-                    stamp(1 + g, 4);
                 }
                 if (!ok) break;
                 {   // the offset term: A = the unit's sixteen halves of -dmin * m, B = this unit's 16 columns of the sums tile.
                     // One set of columns accumulates all units; the two issuers take turns, each waiting for the other's
                     // product of the unit before, so the additions happen in k order.
-                    const int q = s >> 2, ss = q & 1;
-                    if (!mbar_wait(&s_full[ss], (q >> 1) & 1)) { ok = false; break; }
-                    if (!mbar_wait(&am_full[g], j & 1)) { ok = false; break; }
-                    if (s > 0 && !mbar_wait(&min_done[1 - g], ((s - 1) >> 1) & 1)) { ok = false; break; }
+                    const int q = s >> 2, ss = q & 1, am = g * 2 + (j & 1);
+                    if (!twait(&s_full[ss], (q >> 1) & 1, 3)) { ok = false; break; }
+                    if (!twait(&am_full[am], (j >> 1) & 1, 4)) { ok = false; break; }
+                    if (s > 0 && !twait(&d_full[1 - g], ((s - 1) >> 1) & 1, 5)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t sdesc = umma_desc_sw128(smem_u32(st + (size_t)ss * b_bytes)) + (uint64_t)((s & 3) * 2);
-                    umma_f16_ts(d_min, tmem + kColAmin + g * 8, sdesc, idesc_min, (uint32_t)(s > 0));
-                    if (two) umma_f16_ts(d_min, tmem + kColAmin + g * 8, sdesc + (uint64_t)(b_half >> 4), idesc_min, 1u);
-                    umma_commit(&am_empty[g]);
-                    umma_commit(&s_empty[ss]);
-                    umma_commit(&min_done[g]);
+                    umma_f16_ts(d_min, tmem + kColAmin + am * 8, sdesc, idesc_min, (uint32_t)(s > 0));
+                    if (two) umma_f16_ts(d_min, tmem + kColAmin + am * 8, sdesc + (uint64_t)(b_half >> 4), idesc_min, 1u);
+                    umma_commit(&am_empty[am]);
+                    if ((s & 3) == 3) umma_commit(&s_empty[ss]);  // the offset products are ordered: this one is the last on the tile
                 }
                 umma_commit(&d_full[g]);
             }
+            trace_out(2 + g);
         }
     } else if (warp < 12) {
         // ---------------------------------------------------------------- unpack
@@ -462,17 +471,17 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         int j = 0;
         for (int s = g; s < nseq && ok; s += 2, j++) {
             const int sr = s % RS;
-            if (tr) stamp(3 + g, 1);
             {   // the request for this unit's box has been made (see the producer)
+                const unsigned t0 = (unsigned)clock64();
                 uint32_t seen = 0;
                 for (uint32_t it = 0; it < (1u << 24) && seen <= (uint32_t)s; ++it)
                     asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(raw_issued)) : "memory");
                 ok = __all_sync(0xffffffffu, seen > (uint32_t)s);
+                wacc[0] += (unsigned)clock64() - t0;
                 if (!ok) break;
             }
-            ok = wait_all(&raw_full[sr], (s / RS) & 1);
+            ok = wait_all(&raw_full[sr], (s / RS) & 1, 1);
             if (!ok) break;
-            if (tr) stamp(3 + g, 2);
             const unsigned char* rp = raw + (size_t)sr * raw_bytes + (size_t)row * kUnitBytes;
             HdrQ4K hdr;
             load_hdr(rp, hdr);
@@ -483,10 +492,10 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 // unit before has read it, which ended long ago
                 uint32_t mc[8];
                 unpack_mins(hdr, mc);
-                ok = wait_all(&am_empty[g], (j & 1) ^ 1);
+                ok = wait_all(&am_empty[g * 2 + (j & 1)], ((j >> 1) & 1) ^ 1, 2);
                 if (!ok) break;
                 tc_fence_after();
-                tmem_st8(tmem + lane_base + kColAmin + g * 8, mc);
+                tmem_st8(tmem + lane_base + kColAmin + (g * 2 + (j & 1)) * 8, mc);
             }
             for (int c = 0; c < 4 && ok; c++) {
                 // stage c still holds the unit before this one (the other group's) until that unit's products have read it; ask
@@ -494,30 +503,33 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 const uint32_t par = (uint32_t)(((s - 1) >> 1) & 1);
                 bool free_now = s == 0 || mbar_test(&a_empty[(1 - g) * 4 + c], par);
                 uint32_t col[32];
+                unsigned tq0 = 0;
+                if (tracing) tq0 = (unsigned)clock64();
                 unpack_chunk(rp, hdr, c, col);
-                if (tr) stamp(3 + g, 10);
+                if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[4] += t1 - tq0; tq0 = t1; }
                 // the chunk before this one (the offset operand ahead of the first) has had the time of this unpacking to reach
                 // tensor memory
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[5] += t1 - tq0; tq0 = t1; }
                 tc_fence_before();
-                mbar_arrive(c > 0 ? &a_full[g * 4 + c - 1] : &am_full[g]);
+                mbar_arrive(c > 0 ? &a_full[g * 4 + c - 1] : &am_full[g * 2 + (j & 1)]);
+                if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[6] += t1 - tq0; tq0 = t1; }
                 if (!free_now) free_now = mbar_wait(&a_empty[(1 - g) * 4 + c], par);
                 ok = __all_sync(0xffffffffu, free_now);
                 if (!ok) break;
                 tc_fence_after();
-                if (tr) stamp(3 + g, 11);
+                if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[3] += t1 - tq0; tq0 = t1; }
                 const uint32_t a_t = tmem + lane_base + kColA + c * 32;
                 tmem_st16(a_t, col);
                 tmem_st16(a_t + 16, col + 16);
-                if (tr) stamp(3 + g, 12);
             }
             if (!ok) break;
             mbar_arrive(&raw_empty[sr]);  // this row's bytes of the unit are consumed
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             mbar_arrive(&a_full[g * 4 + 3]);
-            if (tr) stamp(3 + g, 5);
         }
+        if (tr) trace_out(4 + g);
     } else {
         // ---------------------------------------------------------------- drain, then epilogue
         const int quarter = warp & 3;
@@ -530,7 +542,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         for (int s = 0; s < nseq && ok; s++) {
             const int g = s & 1, j = s >> 1;
             const uint32_t d_main = tmem + lane_base + kColD + g * kColsPerPipe;
-            ok = wait_all(&d_full[g], j & 1);
+            ok = wait_all(&d_full[g], j & 1, 0);
             if (!ok) break;
             tc_fence_after();
             const float d = dd[(s & (kDRing - 1)) * kRows + row];
@@ -552,6 +564,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             tc_fence_before();
             mbar_arrive(&d_empty[g]);
         }
+        if (quarter == 0 && lane == 0) trace_out(6);
         // the offset sums (complete: every unit's d_full followed its offset product)
         if (ok && nseq > 0) {
             const uint32_t d_min = tmem + lane_base + kColDmin;
@@ -737,11 +750,11 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     p.b_stages = kMaxB;
     p.error_flag = gemv_error_flag_dev();
     p.trace = nullptr;
-    static long long* d_trace = nullptr;
+    static unsigned* d_trace = nullptr;
     const bool want_trace = getenv("LC_GEMM_TRACE") != nullptr;
     if (want_trace) {
-        if (!d_trace) LC_CUDA(cudaMalloc((void**)&d_trace, 1280 * sizeof(long long)));
-        LC_CUDA(cudaMemsetAsync(d_trace, 0, 1280 * sizeof(long long), s));
+        if (!d_trace) LC_CUDA(cudaMalloc((void**)&d_trace, 56 * sizeof(unsigned)));
+        LC_CUDA(cudaMemsetAsync(d_trace, 0, 56 * sizeof(unsigned), s));
         p.trace = d_trace;
     }
     const size_t smem = fixed + (size_t)p.raw_stages * kUnitBytes * kRows;
@@ -797,18 +810,16 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     }
     if (launches) *launches = (prepared ? 1 : 2) + (summed ? 1 : 0);
     if (want_trace) {
-        static long long h[1280];
+        unsigned h[56];
         LC_CUDA(cudaStreamSynchronize(s));
         LC_CUDA(cudaMemcpy(h, d_trace, sizeof(h), cudaMemcpyDeviceToHost));
-        long long t0c = 0;
-        for (int r = 0; r < 5; r++)
-            if (h[r * 256] && (!t0c || (h[r * 256] & 0xFFFFFFFFFFFFll) < t0c)) t0c = h[r * 256] & 0xFFFFFFFFFFFFll;
-        const char* names[5] = {"producer", "issuer0", "issuer1", "unpack0", "unpack1"};
-        for (int r = 0; r < 5; r++) {
-            fprintf(stderr, "[gemm trace n=%d k=%d T=%d] %s:", n, K, T, names[r]);
-            for (int i = 0; i < 120 && h[r * 256 + i]; i++)
-                fprintf(stderr, " %d@%lld", (int)(h[r * 256 + i] >> 48), (h[r * 256 + i] & 0xFFFFFFFFFFFFll) - t0c);
-            fprintf(stderr, "\n");
+        const char* names[7] = {"activation producer (b_empty, s_empty)", "raw producer (raw_empty)", "issuer 0 (d_empty, b_full, a_full, s_full, am_full, other issuer's unit)",
+                                "issuer 1", "unpack 0 (raw requested, raw_full, am_empty, a_empty + vote | unpacking, wait::st, fence + arrive)", "unpack 1", "drain (d_full)"};
+        fprintf(stderr, "[gemm waits n=%d k=%d T=%d grid %ux%ux%u] cycles of CTA 0 per kind of wait | whole loop\n", n, K, T, grid.x, grid.y, grid.z);
+        for (int r = 0; r < 7; r++) {
+            fprintf(stderr, "  %-62s:", names[r]);
+            for (int i = 0; i < 7; i++) fprintf(stderr, " %7u", h[r * 8 + i]);
+            fprintf(stderr, " | %8u\n", h[r * 8 + 7]);
         }
     }
     return LC_OK;
