@@ -254,11 +254,11 @@ __device__ __forceinline__ void xprep_row(float* row, float acc, const float* __
         part += __shfl_xor_sync(0xffffffffu, part, 4);
         if (i < K && (threadIdx.x & 7) == 0) {
             const int sub = i >> 5, unit = sub >> 3, idx = unit * 16 + (sub & 7);
-            const __half sh_ = __float2half_rn(part);
+            const __half sh_ = __float2half_rn(part), sl_ = __float2half_rn(part - __half2float(sh_));
             sxh[idx] = sh_;
-            sxl[idx] = __float2half_rn(part - __half2float(sh_));
+            sxl[idx] = sl_;
             sxh[idx + 8] = sh_;  // a second time: the offset operand pairs each sum with the high and with the low part of -dmin * m
-            sxl[idx + 8] = sxl[idx];
+            sxl[idx + 8] = sl_;
         }
     }
 }
