@@ -49,7 +49,12 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
 // and writes each result row to its slot.  The activations come as fixed-point planes that gemv_planes_kernel wrote once
 // for the whole launch, read per job from global memory (L2): no per-CTA norm or plane computation, and no shared memory
 // that grows with k.  The plain instantiation carries none of this.
-template <int M, int WARPS, int STAGES, bool GROUPED = false>
+//
+// TYPE = LC_TYPE_Q4_0: the same tiles (eight 18-byte blocks = 144 bytes per 256 weights), the same planes.  A block is one
+// MMA: the 4 bytes a thread needs hold its low-nibble k-slots and, four bits up, its high-nibble ones (elements j and j + 16
+// share byte j, rust/src/kernels/mod.rs:26-31); the block's f16 scale multiplies the plane-folded sum in f32 and the
+// offset -8 d sum(x) is shared out over the four threads of a row like the min term of Q4_K.
+template <int M, int WARPS, int STAGES, bool GROUPED = false, uint32_t TYPE = LC_TYPE_Q4_K>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p, GemvGroupParams gp) {
     constexpr int UB = 144;
@@ -304,6 +309,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     // warp owns a single unit of k, per job otherwise
     uint32_t bf[NPAIR][8][2];
     float sx2[M][2], isv[M];
+    constexpr float kIsvFactor = TYPE == LC_TYPE_Q4_K ? 0.0625f : 1.0f;
     auto load_unit_consts = [&](int unit) {
         load_bf(unit, bf);
 #pragma unroll
@@ -313,11 +319,11 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 const float2 sx = tk < m_act ? __ldg(reinterpret_cast<const float2*>(gp.sxf + at * 8 + 2 * t)) : make_float2(0.f, 0.f);
                 sx2[tk][0] = sx.x;
                 sx2[tk][1] = sx.y;
-                isv[tk] = tk < m_act ? __ldg(gp.inv2s + at) * 0.0625f : 0.f;
+                isv[tk] = tk < m_act ? __ldg(gp.inv2s + at) * kIsvFactor : 0.f;
             } else {
                 sx2[tk][0] = sxf[(unit * M + tk) * 8 + 2 * t];
                 sx2[tk][1] = sxf[(unit * M + tk) * 8 + 2 * t + 1];
-                isv[tk] = inv2s[unit * M + tk] * 0.0625f;  // 2^-s and the factor 16 the integer sums carry
+                isv[tk] = inv2s[unit * M + tk] * kIsvFactor;  // 2^-s and (Q4_K) the factor 16 the integer sums carry
             }
         }
     };
@@ -352,6 +358,51 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 if (!single_unit) load_unit_consts(warp + ui * WARPS);
                 ok = ok && mbar_wait(&bars[st], (uint32_t)((job / STAGES) & 1));
                 const unsigned char* tilep = stage_base + (size_t)st * STAGE_BYTES;
+                if constexpr (TYPE == LC_TYPE_Q4_0) {
+#pragma unroll
+                    for (int rg = 0; rg < RG; rg++) {
+                        const unsigned char* rowA = tilep + (rg * 16 + g) * UB;
+                        const unsigned char* rowB = rowA + 8 * UB;
+#pragma unroll
+                        for (int b = 0; b < 8; b++) {
+                            // the four bytes of k-slots 4t .. 4t + 3 (low nibbles) and 16 + 4t .. (high nibbles): at 18 b + 2 + 4 t,
+                            // word aligned for odd b, two bytes off for even b (two aligned words and a funnel shift)
+                            uint32_t wA, wB;
+                            if (b & 1) {
+                                wA = lds32(rowA + 18 * b + 2 + 4 * t);
+                                wB = lds32(rowB + 18 * b + 2 + 4 * t);
+                            } else {
+                                wA = __funnelshift_r(lds32(rowA + 18 * b + 4 * t), lds32(rowA + 18 * b + 4 + 4 * t), 16);
+                                wB = __funnelshift_r(lds32(rowB + 18 * b + 4 * t), lds32(rowB + 18 * b + 4 + 4 * t), 16);
+                            }
+                            const float dA = __half2float(*reinterpret_cast<const __half*>(rowA + 18 * b));
+                            const float dB = __half2float(*reinterpret_cast<const __half*>(rowB + 18 * b));
+                            const uint32_t a0 = wA & 0x0F0F0F0Fu, a1 = wB & 0x0F0F0F0Fu, a2 = (wA >> 4) & 0x0F0F0F0Fu, a3 = (wB >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                            for (int pr = 0; pr < NPAIR; pr++) {
+                                int c[4];
+                                mma_u8s8(c, a0, a1, a2, a3, bf[pr][b][0], bf[pr][b][1]);
+                                const float v0 = (float)c[0], v1 = (float)c[1], v2 = (float)c[2], v3 = (float)c[3];
+#pragma unroll
+                                for (int which = 0; which < 2; which++) {
+                                    const int tok = 2 * pr + which;
+                                    if (tok >= M) continue;
+                                    const float c0 = which ? cB0 : cA0, c1 = which ? cB1 : cA1;
+                                    yacc[rg][0][tok] = fmaf(dA * isv[tok], c0 * v0 + c1 * v1, yacc[rg][0][tok]);
+                                    yacc[rg][1][tok] = fmaf(dB * isv[tok], c0 * v2 + c1 * v3, yacc[rg][1][tok]);
+                                }
+                            }
+                            // (q - 8): this thread's share of -8 d sum(x) are blocks 2t and 2t + 1
+                            if ((b >> 1) == t) {
+#pragma unroll
+                                for (int tok = 0; tok < M; tok++) {
+                                    yacc[rg][0][tok] = fmaf(-8.0f * dA, sx2[tok][b & 1], yacc[rg][0][tok]);
+                                    yacc[rg][1][tok] = fmaf(-8.0f * dB, sx2[tok][b & 1], yacc[rg][1][tok]);
+                                }
+                            }
+                        }
+                    }
+                } else {
 #pragma unroll
                 for (int rg = 0; rg < RG; rg++) {
                     const unsigned char* rowA = tilep + (rg * 16 + g) * UB;
@@ -411,6 +462,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                             yacc[rg][1][tok] += (ddB.x * isv[tok]) * sB - ddB.y * mtB;
                         }
                     }
+                }
                 }
                 __syncwarp();
                 if (lane == 0 && pj < njobs) issue_next();
@@ -589,9 +641,9 @@ static size_t mma_smem_bytes(int k, bool grouped = false) {
     return b + kGroupedSlots * 4;  // head room for the slot words of the grouped form
 }
 
-template <int M, int WARPS, int STAGES, bool GROUPED = false>
+template <int M, int WARPS, int STAGES, bool GROUPED = false, uint32_t TYPE = LC_TYPE_Q4_K>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
-    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, GROUPED>;
+    auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, GROUPED, TYPE>;
     size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k, GROUPED);
     LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
@@ -628,14 +680,14 @@ static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     return LC_OK;
 }
 
-template <int M>
+template <int M, uint32_t TYPE = LC_TYPE_Q4_K>
 static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = true;
     int k = a.w->k;
     if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
-        if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2>(a, s);
+        if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2, false, TYPE>(a, s);
     }
-    if (mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2>(a, s);
+    if (mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2, false, TYPE>(a, s);
     *launched = false;
     return LC_OK;
 }
@@ -669,6 +721,12 @@ int32_t launch_qgemv_mma_q4k_grouped(const GemvArgs& a, cudaStream_t s, bool* la
 int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = false;
     if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
+    if (a.w->typ == LC_TYPE_Q4_0) {
+        if (a.m <= 1) return launch_mma_m<1, LC_TYPE_Q4_0>(a, s, launched);
+        if (a.m <= 2) return launch_mma_m<2, LC_TYPE_Q4_0>(a, s, launched);
+        if (a.m <= 4) return launch_mma_m<4, LC_TYPE_Q4_0>(a, s, launched);
+        return LC_OK;  // wider token tiles of this type stay with the f32 kernel
+    }
     if (a.m <= 1) return launch_mma_m<1>(a, s, launched);
     if (a.m <= 2) return launch_mma_m<2>(a, s, launched);
     if (a.m <= 4) return launch_mma_m<4>(a, s, launched);
