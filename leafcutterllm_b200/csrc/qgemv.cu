@@ -595,7 +595,7 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
     if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual, LC_ERR_INVALID, "qgemv: residual missing");
     bool tma_ok = a.w->has_tmap && (a.epi != EPI_SILU_MUL || a.w2->has_tmap);
     static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
-    if (tma_ok && (a.w->typ == LC_TYPE_Q4_K || (a.w->typ == LC_TYPE_Q4_0 && a.w->k % kUnitElems == 0)) && !force_fp32) {
+    if (tma_ok && (a.w->typ == LC_TYPE_Q4_K || ((a.w->typ == LC_TYPE_Q4_0 || a.w->typ == LC_TYPE_Q8_0) && a.w->k % kUnitElems == 0)) && !force_fp32) {
         bool launched = false;
         LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
         if (launched) return LC_OK;

@@ -32,6 +32,13 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
 __device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *reinterpret_cast<const uint32_t*>(p); }
 __device__ __forceinline__ int byte_of(uint32_t w, int j) { return (int)((w >> (8 * j)) & 0xFFu); }
 
@@ -54,10 +61,12 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
 // MMA: the 4 bytes a thread needs hold its low-nibble k-slots and, four bits up, its high-nibble ones (elements j and j + 16
 // share byte j, rust/src/kernels/mod.rs:26-31); the block's f16 scale multiplies the plane-folded sum in f32 and the
 // offset -8 d sum(x) is shared out over the four threads of a row like the min term of Q4_K.
+// TYPE = LC_TYPE_Q8_0: eight 34-byte blocks = 272 bytes per 256 weights; a block is one s8 x s8 MMA (the weights are the
+// signed bytes themselves, mod.rs:47-49), no offset.
 template <int M, int WARPS, int STAGES, bool GROUPED = false, uint32_t TYPE = LC_TYPE_Q4_K>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p, GemvGroupParams gp) {
-    constexpr int UB = 144;
+    constexpr int UB = TYPE == LC_TYPE_Q8_0 ? 272 : 144;  // bytes of a row's 256 weights
     const CUtensorMap* t0p = &tm0;
     const CUtensorMap* t1p = &tm1;
     int m_act = p.m;
@@ -358,7 +367,43 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                 if (!single_unit) load_unit_consts(warp + ui * WARPS);
                 ok = ok && mbar_wait(&bars[st], (uint32_t)((job / STAGES) & 1));
                 const unsigned char* tilep = stage_base + (size_t)st * STAGE_BYTES;
-                if constexpr (TYPE == LC_TYPE_Q4_0) {
+                if constexpr (TYPE == LC_TYPE_Q8_0) {
+#pragma unroll
+                    for (int rg = 0; rg < RG; rg++) {
+                        const unsigned char* rowA = tilep + (rg * 16 + g) * UB;
+                        const unsigned char* rowB = rowA + 8 * UB;
+#pragma unroll
+                        for (int b = 0; b < 8; b++) {
+                            // k-slots 4t .. 4t + 3 at 34 b + 2 + 4 t, k-slots 16 + 4t .. sixteen bytes on: word aligned for odd b
+                            uint32_t a0, a1, a2, a3;
+                            if (b & 1) {
+                                a0 = lds32(rowA + 34 * b + 2 + 4 * t); a2 = lds32(rowA + 34 * b + 18 + 4 * t);
+                                a1 = lds32(rowB + 34 * b + 2 + 4 * t); a3 = lds32(rowB + 34 * b + 18 + 4 * t);
+                            } else {
+                                a0 = __funnelshift_r(lds32(rowA + 34 * b + 4 * t), lds32(rowA + 34 * b + 4 + 4 * t), 16);
+                                a2 = __funnelshift_r(lds32(rowA + 34 * b + 16 + 4 * t), lds32(rowA + 34 * b + 20 + 4 * t), 16);
+                                a1 = __funnelshift_r(lds32(rowB + 34 * b + 4 * t), lds32(rowB + 34 * b + 4 + 4 * t), 16);
+                                a3 = __funnelshift_r(lds32(rowB + 34 * b + 16 + 4 * t), lds32(rowB + 34 * b + 20 + 4 * t), 16);
+                            }
+                            const float dA = __half2float(*reinterpret_cast<const __half*>(rowA + 34 * b));
+                            const float dB = __half2float(*reinterpret_cast<const __half*>(rowB + 34 * b));
+#pragma unroll
+                            for (int pr = 0; pr < NPAIR; pr++) {
+                                int c[4];
+                                mma_s8s8(c, a0, a1, a2, a3, bf[pr][b][0], bf[pr][b][1]);
+                                const float v0 = (float)c[0], v1 = (float)c[1], v2 = (float)c[2], v3 = (float)c[3];
+#pragma unroll
+                                for (int which = 0; which < 2; which++) {
+                                    const int tok = 2 * pr + which;
+                                    if (tok >= M) continue;
+                                    const float c0 = which ? cB0 : cA0, c1 = which ? cB1 : cA1;
+                                    yacc[rg][0][tok] = fmaf(dA * isv[tok], c0 * v0 + c1 * v1, yacc[rg][0][tok]);
+                                    yacc[rg][1][tok] = fmaf(dB * isv[tok], c0 * v2 + c1 * v3, yacc[rg][1][tok]);
+                                }
+                            }
+                        }
+                    }
+                } else if constexpr (TYPE == LC_TYPE_Q4_0) {
 #pragma unroll
                     for (int rg = 0; rg < RG; rg++) {
                         const unsigned char* rowA = tilep + (rg * 16 + g) * UB;
@@ -631,9 +676,9 @@ void dump_mring() {
 }  // namespace
 
 template <int M, int WARPS, int STAGES>
-static size_t mma_smem_bytes(int k, bool grouped = false) {
+static size_t mma_smem_bytes(int k, bool grouped = false, int unit_bytes = 144) {
     int nunits = grouped ? 0 : k / kUnitElems;
-    size_t b = (size_t)WARPS * STAGES * 144 * kTileRows;
+    size_t b = (size_t)WARPS * STAGES * unit_bytes * kTileRows;
     b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * M * 8 * 4 + (size_t)nunits * M * 4;
     b += (size_t)2 * WARPS * M * 32 * 4 + (size_t)M * 32 * 4 + (size_t)(32 + M) * 4;
     b = (b + 7) & ~(size_t)7;
@@ -644,7 +689,7 @@ static size_t mma_smem_bytes(int k, bool grouped = false) {
 template <int M, int WARPS, int STAGES, bool GROUPED = false, uint32_t TYPE = LC_TYPE_Q4_K>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, GROUPED, TYPE>;
-    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k, GROUPED);
+    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k, GROUPED, TYPE == LC_TYPE_Q8_0 ? 272 : 144);
     LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
@@ -684,10 +729,11 @@ template <int M, uint32_t TYPE = LC_TYPE_Q4_K>
 static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = true;
     int k = a.w->k;
+    constexpr int ub = TYPE == LC_TYPE_Q8_0 ? 272 : 144;
     if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
-        if (mma_smem_bytes<M, 16, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 16, 2, false, TYPE>(a, s);
+        if (mma_smem_bytes<M, 16, 2>(k, false, ub) <= kMaxSmem) return launch_mma_cfg<M, 16, 2, false, TYPE>(a, s);
     }
-    if (mma_smem_bytes<M, 8, 2>(k) <= kMaxSmem) return launch_mma_cfg<M, 8, 2, false, TYPE>(a, s);
+    if (mma_smem_bytes<M, 8, 2>(k, false, ub) <= kMaxSmem) return launch_mma_cfg<M, 8, 2, false, TYPE>(a, s);
     *launched = false;
     return LC_OK;
 }
@@ -726,6 +772,12 @@ int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) 
         if (a.m <= 2) return launch_mma_m<2, LC_TYPE_Q4_0>(a, s, launched);
         if (a.m <= 4) return launch_mma_m<4, LC_TYPE_Q4_0>(a, s, launched);
         return LC_OK;  // wider token tiles of this type stay with the f32 kernel
+    }
+    if (a.w->typ == LC_TYPE_Q8_0) {
+        if (a.m <= 1) return launch_mma_m<1, LC_TYPE_Q8_0>(a, s, launched);
+        if (a.m <= 2) return launch_mma_m<2, LC_TYPE_Q8_0>(a, s, launched);
+        if (a.m <= 4) return launch_mma_m<4, LC_TYPE_Q8_0>(a, s, launched);
+        return LC_OK;
     }
     if (a.m <= 1) return launch_mma_m<1>(a, s, launched);
     if (a.m <= 2) return launch_mma_m<2>(a, s, launched);
