@@ -2,6 +2,7 @@
 // load-time weight sanity scan and the embedding row gather.
 #include "lc_kernels.h"
 #include "lc_quant.cuh"
+#include "lc_tma.cuh"
 
 namespace lc {
 
@@ -23,8 +24,10 @@ __global__ void sanity_kernel(uint32_t typ, const uint8_t* __restrict__ w, size_
     if ((threadIdx.x & 31) == 0 && bad) atomicAdd(count, (unsigned long long)bad);
 }
 
-__global__ void embed_kernel(uint32_t typ, const uint8_t* __restrict__ w, size_t rows, size_t cols,
-                             const int64_t* __restrict__ ids, float* __restrict__ out) {
+__global__ void __launch_bounds__(1024) embed_kernel(uint32_t typ, const uint8_t* __restrict__ w, size_t rows, size_t cols,
+                                                     const int64_t* __restrict__ ids, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();  // the token ids may come from the kernel ahead (a decode step's advance), and `out` may still be read by it
     int t = blockIdx.x;
     int64_t id = ids[t];
     bool ok = id >= 0 && (size_t)id < rows;
@@ -59,8 +62,8 @@ int32_t launch_sanity_scan(uint32_t typ, const void* w, size_t n, unsigned long 
 int32_t launch_embed(uint32_t typ, const void* w, size_t rows, size_t cols, const int64_t* ids, int n, float* out,
                      cudaStream_t s) {
     if (n <= 0) return LC_OK;
-    embed_kernel<<<n, 256, 0, s>>>(typ, (const uint8_t*)w, rows, cols, ids, out);
-    LC_CUDA(cudaGetLastError());
+    // a row is a few thousand elements, each decoded on its own: many threads, a few elements each
+    LC_CUDA(launch_pdl(embed_kernel, dim3((unsigned)n), dim3(cols >= 2048 ? 1024 : 256), 0, s, typ, (const uint8_t*)w, rows, cols, ids, out));
     return LC_OK;
 }
 

@@ -1264,6 +1264,11 @@ static int32_t run_decode_steps(lc_model* m, int n_seqs, int steps) {
             cfg.gridDim = dim3(1);
             cfg.blockDim = dim3(std::max(32, (n_seqs + 31) / 32 * 32));
             cfg.stream = r->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
             LC_CUDA(cudaLaunchKernelEx(&cfg, advance_kernel, (const int64_t*)r->d_next, r->d_tokens, r->d_tok_pos, r->d_tok_rope, (int)n_seqs,
                                        (int)r->cfg.rope_mode, r->d_out_tokens, r->d_step_ctr));
             r->launches_in_call += 1;

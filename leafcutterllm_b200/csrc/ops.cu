@@ -5,6 +5,7 @@
 #include <algorithm>
 #include "lc_kernels.h"
 #include "lc_quant.cuh"
+#include "lc_tma.cuh"
 
 namespace lc {
 
@@ -152,8 +153,10 @@ __device__ __forceinline__ int32_t total_key(float f) {
 // sampler.rs:6-10: max_by keeps the last of equal maxima -> compare (key, index) pairs.
 // The same pick kept as its key, with the index offset by index_base: the maximum of such keys over vocabulary slices is
 // the pick over the whole vocabulary, equal maxima still going to the higher index.
-__global__ void argmax_key_kernel(const float* __restrict__ v, size_t n, int index_base, long long* out) {
+__global__ void __launch_bounds__(1024) argmax_key_kernel(const float* __restrict__ v, size_t n, int index_base, long long* out) {
     __shared__ long long shk[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = v + (size_t)blockIdx.x * n;
     long long best = LLONG_MIN;
     for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -177,17 +180,29 @@ __global__ void argmax_key_kernel(const float* __restrict__ v, size_t n, int ind
     }
 }
 __global__ void key_to_token_kernel(const long long* __restrict__ keys, size_t rows, int64_t* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < rows) out[i] = (int64_t)(uint32_t)(keys[i] & 0xffffffffll);
 }
 
-__global__ void argmax_kernel(const float* __restrict__ v, size_t n, int64_t* out) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ v, size_t n, int64_t* out) {
     __shared__ long long shk[32];
+    pdl_launch_dependents();
+    pdl_wait();  // the logits come from the kernel ahead
     const float* row = v + (size_t)blockIdx.x * n;
     long long best = LLONG_MIN;
-    for (size_t i = threadIdx.x; i < n; i += blockDim.x) {
-        long long key = ((long long)total_key(row[i]) << 32) | (long long)(uint32_t)i;
+    auto take = [&](float x, size_t i) {
+        const long long key = ((long long)total_key(x) << 32) | (long long)(uint32_t)i;
         best = key > best ? key : best;
+    };
+    if ((n & 3) == 0 && ((uintptr_t)row & 15) == 0) {
+        for (size_t i = (size_t)threadIdx.x * 4; i < n; i += (size_t)blockDim.x * 4) {
+            const float4 q = *reinterpret_cast<const float4*>(row + i);
+            take(q.x, i); take(q.y, i + 1); take(q.z, i + 2); take(q.w, i + 3);
+        }
+    } else {
+        for (size_t i = threadIdx.x; i < n; i += blockDim.x) take(row[i], i);
     }
     for (int o = 16; o > 0; o >>= 1) {
         long long other = __shfl_xor_sync(0xffffffffu, best, o);
@@ -270,20 +285,17 @@ int32_t launch_rope(float* x, size_t seq, size_t heads, size_t hd, float theta, 
 }
 int32_t launch_argmax(const float* v, size_t n, size_t rows, int64_t* out, cudaStream_t s) {
     if (rows == 0 || n == 0) return LC_OK;
-    argmax_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, out);
-    LC_CUDA(cudaGetLastError());
+    LC_CUDA(launch_pdl(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, s, v, n, out));
     return LC_OK;
 }
 int32_t launch_argmax_key(const float* v, size_t n, size_t rows, int index_base, long long* out_keys, cudaStream_t s) {
     if (rows == 0 || n == 0) return LC_OK;
-    argmax_key_kernel<<<(unsigned)rows, 1024, 0, s>>>(v, n, index_base, out_keys);
-    LC_CUDA(cudaGetLastError());
+    LC_CUDA(launch_pdl(argmax_key_kernel, dim3((unsigned)rows), dim3(1024), 0, s, v, n, index_base, out_keys));
     return LC_OK;
 }
 int32_t launch_key_to_token(const long long* keys, size_t rows, int64_t* out_tokens, cudaStream_t s) {
     if (rows == 0) return LC_OK;
-    key_to_token_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, s>>>(keys, rows, out_tokens);
-    LC_CUDA(cudaGetLastError());
+    LC_CUDA(launch_pdl(key_to_token_kernel, dim3((unsigned)((rows + 127) / 128)), dim3(128), 0, s, keys, rows, out_tokens));
     return LC_OK;
 }
 
