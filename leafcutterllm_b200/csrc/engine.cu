@@ -419,7 +419,10 @@ int32_t moe_block(lc_model* m, int l, const float* x, const float* norm_w, int T
     MoeRouteArgs r;
     r.x = x; r.norm_w = norm_w; r.eps = m->cfg.rms_eps; r.H = m->H; r.T = T; r.w_router = w.router; r.n_experts = E; r.top_k = K;
     r.sel = m->d_moe_sel; r.wsel = m->d_moe_w;
-    if (grouped) { r.counts = m->d_moe_cnt; r.lists = m->d_moe_lists; r.list_stride = kMoeGroupedTokens; r.touched = m->d_moe_touched; }
+    if (grouped) {
+        r.counts = m->d_moe_cnt; r.lists = m->d_moe_lists; r.list_stride = kMoeGroupedTokens; r.touched = m->d_moe_touched;
+        r.ticket = reinterpret_cast<unsigned*>(m->d_moe_cnt + E);  // one word behind the counts
+    }
     r.local_first = e0; r.local_count = El;
     LC_TRY(launch_moe_route(r, m->stream));
     m->launches_in_call += 1;
@@ -988,7 +991,8 @@ int32_t lc_model_finalize(lc_model* m) {
     if (m->cfg.n_experts > 0) {
         const int E = m->cfg.n_experts, K = m->cfg.top_k;
         LC_TRY(dalloc(&m->d_moe_sel, (size_t)T * K)); LC_TRY(dalloc(&m->d_moe_w, (size_t)T * K));
-        LC_TRY(dalloc(&m->d_moe_cnt, (size_t)E)); LC_TRY(dalloc(&m->d_moe_lists, (size_t)E * kMoeGroupedTokens));
+        LC_TRY(dalloc(&m->d_moe_cnt, (size_t)E + 1)); LC_TRY(dalloc(&m->d_moe_lists, (size_t)E * kMoeGroupedTokens));
+        LC_CUDA(cudaMemsetAsync(m->d_moe_cnt, 0, ((size_t)E + 1) * sizeof(int32_t), m->stream));  // the word behind the counts is the router's ticket
         LC_TRY(dalloc(&m->d_moe_h, (size_t)kMoeGroupedTokens * K * F)); LC_TRY(dalloc(&m->d_moe_y, (size_t)kMoeGroupedTokens * K * H));
         LC_TRY(dalloc(&m->d_moe_yall, (size_t)E * T * H));
         auto planes_alloc = [&](GemvPlanes* pl, size_t rows, int k) -> int32_t {

@@ -209,6 +209,7 @@ struct MoeRouteArgs {
     int list_stride = 0;
     unsigned long long* touched = nullptr;
     int local_first = 0, local_count = 0;  // experts this rank holds (0 count = all): only those are counted in `touched`
+    unsigned* ticket = nullptr;            // with `lists`: a device word, zero between launches (the CTA that finishes last builds the lists)
 };
 int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s);
 // out[t] = residual[t] + sum_j wsel[t][j] * y[row(t, j)] in ascending expert order; mode 0: row = t * top_k + j,

@@ -7,9 +7,9 @@
 //   gate weights = softmax over the selected logits;
 //   output = residual + sum over the selected experts, in ascending expert index, of weight * expert_ffn(rms_norm(x)).
 //
-// moe_route_kernel   one CTA per block of 64 tokens: RMS scale per token, one warp per (token, expert) dot product,
-//                    one thread per token picks and weighs, and -- when the whole call fits one block -- expert e's
-//                    thread lists the (token, choice) slots it received, in token order, for the grouped expert product.
+// moe_route_kernel   one CTA per token: RMS scale, one warp per (token, expert) dot product, one thread picks and weighs, and
+//                    -- for calls of up to 64 tokens -- the CTA that finishes last lists, per expert and in token order, the
+//                    (token, choice) slots it received, for the grouped expert product.
 // moe_combine_kernel out[t] = residual[t] + sum_j w[t][j] * y[row(t, j)], j in ascending expert order.
 #include "lc_kernels.h"
 
@@ -17,50 +17,51 @@ namespace lc {
 
 namespace {
 
-constexpr int kRouteTokens = 64;   // tokens per CTA of the router
-constexpr int kRouteThreads = 1024;
+constexpr int kRouteTokens = 64;   // most tokens of a call whose slot lists are built (the grouped expert product's limit)
+constexpr int kRouteThreads = 256;
 
 __device__ __forceinline__ int32_t total_key_f(float f) {  // orders f32 bit patterns like Rust's f32::total_cmp
     int32_t b = __float_as_int(f);
     return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1);
 }
 
+// One CTA per token.  The arithmetic per token is that of a single warp per sum (lane-strided fused multiply-adds, then the
+// warp tree), whatever the grid: warp 0 forms the RMS scale, the warps share the experts' dot products, thread 0 picks and
+// weighs.  When the call wants slot lists (`lists`), the CTA that finishes last (a ticket) reads every token's choices back
+// and lists, per expert and in token order, the (token, choice) slots it received.
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int H, int T, const float* __restrict__ w_router,
                  int E, int K, int32_t* __restrict__ sel, float* __restrict__ wsel, int32_t* __restrict__ cnt, int32_t* __restrict__ lists,
-                 int list_stride, unsigned long long* __restrict__ touched, int local_first, int local_count) {
-    __shared__ float scale_s[kRouteTokens];
-    __shared__ float logit_s[kRouteTokens * kMaxExperts];
-    __shared__ int sel_s[kRouteTokens * kMaxTopK];
+                 int list_stride, unsigned long long* __restrict__ touched, int local_first, int local_count, unsigned* __restrict__ ticket) {
+    __shared__ float scale_s;
+    __shared__ float logit_s[kMaxExperts];
+    __shared__ int last_s;
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const int t0 = blockIdx.x * kRouteTokens, nt = min(kRouteTokens, T - t0);
-    for (int t = warp; t < nt; t += nwarps) {  // cpu.rs:49-60: 1 / sqrt(mean(x^2) + eps)
-        const float* xr = x + (size_t)(t0 + t) * H;
+    const int t = blockIdx.x;
+    const float* xr = x + (size_t)t * H;
+    if (warp == 0) {  // cpu.rs:49-60: 1 / sqrt(mean(x^2) + eps)
         float ss = 0.f;
         for (int i = lane; i < H; i += 32) ss = fmaf(xr[i], xr[i], ss);
         ss = warp_sum(ss);
-        if (lane == 0) scale_s[t] = norm_w ? 1.0f / sqrtf(ss / (float)H + eps) : 1.0f;
+        if (lane == 0) scale_s = norm_w ? 1.0f / sqrtf(ss / (float)H + eps) : 1.0f;
     }
     __syncthreads();
-    for (int pe = warp; pe < nt * E; pe += nwarps) {
-        const int t = pe / E, e = pe - t * E;
-        const float* xr = x + (size_t)(t0 + t) * H;
+    const float sc = scale_s;
+    for (int e = warp; e < E; e += nwarps) {
         const float* wr = w_router + (size_t)e * H;
-        const float sc = scale_s[t];
         float acc = 0.f;
         for (int i = lane; i < H; i += 32) {
             const float xn = norm_w ? (xr[i] * sc) * norm_w[i] : xr[i];
             acc = fmaf(xn, wr[i], acc);
         }
         acc = warp_sum(acc);
-        if (lane == 0) logit_s[t * kMaxExperts + e] = acc;
+        if (lane == 0) logit_s[e] = acc;
     }
     __syncthreads();
-    if ((int)threadIdx.x < nt) {
-        const int t = threadIdx.x;
-        const float* lg = logit_s + t * kMaxExperts;
+    if (threadIdx.x == 0) {
+        const float* lg = logit_s;
         unsigned long long used = 0ull;
         for (int kk = 0; kk < K; kk++) {
             int best = -1;
@@ -77,23 +78,29 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, 
         int j = 0;
         for (int e = 0; e < E; e++) {
             if (!((used >> e) & 1ull)) continue;
-            sel[(size_t)(t0 + t) * K + j] = e;                       // ascending expert index
-            wsel[(size_t)(t0 + t) * K + j] = expf(lg[e] - mx) / sum;
-            sel_s[t * kMaxTopK + j] = e;
+            sel[(size_t)t * K + j] = e;                       // ascending expert index
+            wsel[(size_t)t * K + j] = expf(lg[e] - mx) / sum;
             j++;
         }
     }
     if (lists == nullptr) return;   // many-token calls run every expert on every token and only need sel / wsel
+    if (threadIdx.x == 0) {
+        __threadfence();  // this token's choices are in global memory before the ticket is
+        last_s = atomicAdd(ticket, 1u) == (unsigned)(T - 1) ? 1 : 0;
+    }
     __syncthreads();
+    if (!last_s) return;
+    __threadfence();
     if ((int)threadIdx.x < E) {
         const int e = threadIdx.x;
         int n = 0;
-        for (int t = 0; t < nt; t++)
+        for (int tt = 0; tt < T; tt++)
             for (int j = 0; j < K; j++)
-                if (sel_s[t * kMaxTopK + j] == e) lists[(size_t)e * list_stride + n++] = (t0 + t) * K + j;
+                if (__ldcg(sel + (size_t)tt * K + j) == e) lists[(size_t)e * list_stride + n++] = tt * K + j;
         cnt[e] = n;
         if (touched && n > 0 && e >= local_first && e < local_first + local_count) atomicAdd(touched, 1ull);
     }
+    if (threadIdx.x == 0) *ticket = 0;  // every CTA has taken its ticket: ready for the next launch
 }
 
 // mode 0: row(t, j) = t * K + j (one row per slot); mode 1: row(t, j) = (sel[t][j] - local_first) * T_stride + t (a plane per
@@ -144,9 +151,9 @@ int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s) {
              "moe route: %d experts / top %d outside 1..%d / 1..%d", a.n_experts, a.top_k, kMaxExperts, kMaxTopK);
     const bool want_lists = a.lists != nullptr;
     if (want_lists) LC_CHECK(a.T <= kRouteTokens && a.counts && a.list_stride >= a.T, LC_ERR_INVALID, "moe route: slot lists need a call of at most %d tokens", kRouteTokens);
-    const unsigned grid = (unsigned)((a.T + kRouteTokens - 1) / kRouteTokens);
-    LC_CUDA(launch_dep(moe_route_kernel, dim3(grid), dim3(kRouteThreads), s, a.x, a.norm_w, a.eps, a.H, a.T, a.w_router, a.n_experts, a.top_k, a.sel,
-                       a.wsel, a.counts, a.lists, a.list_stride, a.touched, a.local_first, a.local_count > 0 ? a.local_count : a.n_experts));
+    if (want_lists) LC_CHECK(a.ticket != nullptr, LC_ERR_INVALID, "moe route: slot lists need the ticket word");
+    LC_CUDA(launch_dep(moe_route_kernel, dim3((unsigned)a.T), dim3(kRouteThreads), s, a.x, a.norm_w, a.eps, a.H, a.T, a.w_router, a.n_experts, a.top_k, a.sel,
+                       a.wsel, a.counts, a.lists, a.list_stride, a.touched, a.local_first, a.local_count > 0 ? a.local_count : a.n_experts, a.ticket));
     return LC_OK;
 }
 
