@@ -48,6 +48,7 @@ struct StreamParams {
                                 // ticket merge: the same room as f32 [q head][contributor][2 + kHD], then one ticket word per kv head
     int max_contrib;
     int ticket_merge;           // see the merge at the end of the kernel
+    int head_cap;               // most CTAs that share one kv head's pages (0: no limit)
     int nstages;
     unsigned long long* ring;  // diagnostics (LC_ATTN_RING): [launch slot][8] wall-clock stamps, or null
     int ring_slot;
@@ -103,7 +104,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
     const int T = kv.n_kv * np;
     // CTAs that take part: about four items each where a head has that many pages (fewer, larger shares to add up).  The
     // share per CTA never exceeds one head's pages (T / min(4, np) >= n_kv CTAs), so a run touches at most two kv heads.
-    const int G = min((int)gridDim.x, max(1, T / max(1, min(4, np))));
+    const int min_items = max(max(1, min(4, np)), P.head_cap > 0 ? (np + P.head_cap - 1) / P.head_cap : 0);
+    const int G = min((int)gridDim.x, max(1, T / min_items));
     const bool active = (int)blockIdx.x < G;
     const int i_begin = active ? (int)((long long)blockIdx.x * T / G) : 0;
     const int i_end = active ? (int)((long long)(blockIdx.x + 1) * T / G) : 0;
@@ -525,21 +527,40 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap ktm, const __grid_co
                 asm volatile("bar.sync 1, %0;" ::"r"(kCThreads) : "memory");
                 if (*s_last) {
                     __threadfence();
+                    // The shares' maxima and sums first, a warp per query head with its lanes over the contributors: the scale of
+                    // every share and the scaled sums go to shared memory (the warps' states there are no longer needed), one
+                    // lane adds the sums in CTA order.  Then every output reads its nc weighted values with independent loads.
+                    // (With each thread walking maxima, sums and values of all contributors by itself the merge of 16 shares of
+                    // eight heads took 14 us.)
+                    float* esc = st_s;                              // [GSZ][nc]
+                    float* lsc = esc + (size_t)GSZ * P.max_contrib;  // [GSZ][nc]
+                    float* lsum = lsc + (size_t)GSZ * P.max_contrib; // [GSZ]
+                    for (int g = warp; g < GSZ; g += kCWarps) {
+                        const float* base = part + (size_t)(seg * GSZ + g) * P.max_contrib * (2 + kHD);
+                        float M = -INFINITY;
+                        for (int c = lane; c < nc; c += 32) M = fmaxf(M, __ldcg(base + (size_t)c * (2 + kHD)));
+                        M = warp_max(M);
+                        for (int c = lane; c < nc; c += 32) {
+                            const float* q = base + (size_t)c * (2 + kHD);
+                            const float e = expf(__ldcg(q) - M);  // exp(-inf) = 0 for a share without keys
+                            esc[g * nc + c] = e;
+                            lsc[g * nc + c] = __ldcg(q + 1) * e;
+                        }
+                        __syncwarp();
+                        if (lane == 0) {
+                            float L = 0.f;
+                            for (int c = 0; c < nc; c++) L += lsc[g * nc + c];  // CTA order
+                            lsum[g] = L;
+                        }
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"r"(kCThreads) : "memory");
                     for (int w = tid; w < GSZ * kHD; w += kCThreads) {
                         const int g = w / kHD, dx = w - g * kHD, head = seg * GSZ + g;
-                        const float* base = part + (size_t)head * P.max_contrib * (2 + kHD);
-                        float M = -INFINITY;
-                        for (int c = 0; c < nc; c++) M = fmaxf(M, __ldcg(base + (size_t)c * (2 + kHD)));
-                        float L = 0.f, A = 0.f;
-    #pragma unroll 4
-                        for (int c = 0; c < nc; c++) {  // CTA order
-                            const float* q = base + (size_t)c * (2 + kHD);
-                            const float Mc = __ldcg(q), Lc = __ldcg(q + 1), Ac = __ldcg(q + 2 + dx);
-                            const float e = expf(Mc - M);  // exp(-inf) = 0 for a share without keys
-                            L += Lc * e;
-                            A += Ac * e;
-                        }
-                        p.out[(size_t)head * kHD + dx] = A / L;
+                        const float* base = part + (size_t)head * P.max_contrib * (2 + kHD) + 2 + dx;
+                        float A = 0.f;
+    #pragma unroll 8
+                        for (int c = 0; c < nc; c++) A += __ldcg(base + (size_t)c * (2 + kHD)) * esc[g * nc + c];  // CTA order
+                        p.out[(size_t)head * kHD + dx] = A / lsum[g];
                     }
                     if (tid == 0) tickets[seg] = 0;  // every CTA of the head has taken its ticket: ready for the next launch
                 }
@@ -583,6 +604,10 @@ int32_t launch_stream(const AttnParams& a, unsigned long long* slots, cudaStream
     P.a = a;
     P.max_contrib = stream_max_contrib(a.kv.n_kv);
     P.ticket_merge = P.max_contrib > 12 ? 1 : 0;  // by geometry only, so that a model never changes the slots' format
+    // One kv head on this GPU (a cut model): a page costs a CTA about as much as a share costs the merge, so at most 32 CTAs share a head
+    // (70B shape over 8 GPUs at 4096 keys, 16 rank-layers per step on one GPU: 1.32 ms without a limit, 1.25 / 1.24 ms with 16 / 32).
+    static const int cap_env = getenv("LC_ATTN_HEAD_CAP") ? atoi(getenv("LC_ATTN_HEAD_CAP")) : 32;
+    P.head_cap = cap_env;
     P.slots = slots;
     if (!g_aring && getenv("LC_ATTN_RING")) {  // diagnostics: wall-clock stamps per launch, printed at exit
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
