@@ -152,9 +152,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         for (int j = 0; j < STAGES && j < njobs; j++) issue_next();  // weights do not depend on the previous kernel
     }
-    // One token whose k fits one unit per warp: each warp reads its own 256 elements ONCE, for the sum of squares and for
-    // the planes, and the gains (weights: no dependency on the kernel ahead) are already in registers by then.
-    const bool one_pass = !GROUPED && (M == 1) && p.norm_w != nullptr && nunits <= WARPS;
+    // One token whose k fits one or two units per warp: each warp reads its own elements ONCE, for the sum of squares and for
+    // the planes, and the gains of its first unit (weights: no dependency on the kernel ahead) are already in registers by then.
+    const bool one_pass = !GROUPED && (M == 1) && p.norm_w != nullptr && nunits <= 2 * WARPS;
     float nw0[8];
     if (one_pass && warp < nunits) {
         const float4* np = reinterpret_cast<const float4*>(p.norm_w + warp * kUnitElems + 8 * lane);
@@ -170,7 +170,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
     const unsigned push_e = p.push.world > 0 ? *p.push.epoch + 1u : 0u;
 
     // ---- RMS-norm scale per token (cpu.rs:49-60) when fused ----
-    float v0[8];
+    float v0[8], v1[8];
     float rms0 = 1.f;
     if (one_pass) {
         float ss = 0.f;
@@ -181,6 +181,14 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             v0[0] = u0.x; v0[1] = u0.y; v0[2] = u0.z; v0[3] = u0.w; v0[4] = u1.x; v0[5] = u1.y; v0[6] = u1.z; v0[7] = u1.w;
 #pragma unroll
             for (int j = 0; j < 8; j++) ss = fmaf(v0[j], v0[j], ss);
+        }
+        if (warp + WARPS < nunits) {  // the warp's second unit
+            const int e0 = (warp + WARPS) * kUnitElems + 8 * lane;
+            const float4* xp = reinterpret_cast<const float4*>(xrow(0) + e0);
+            const float4 u0 = xp[0], u1 = xp[1];
+            v1[0] = u0.x; v1[1] = u0.y; v1[2] = u0.z; v1[3] = u0.w; v1[4] = u1.x; v1[5] = u1.y; v1[6] = u1.z; v1[7] = u1.w;
+#pragma unroll
+            for (int j = 0; j < 8; j++) ss = fmaf(v1[j], v1[j], ss);
         }
         ss = warp_sum(ss);
         if (lane == 0) scratch[warp] = ss;
@@ -217,8 +225,16 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             float v[8];
             const int e0 = unit * kUnitElems + 8 * lane;
             if (one_pass) {
+                if (ui == 0) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) v[j] = (v0[j] * rms0) * nw0[j];
+                    for (int j = 0; j < 8; j++) v[j] = (v0[j] * rms0) * nw0[j];
+                } else {
+                    const float4* np = reinterpret_cast<const float4*>(p.norm_w + e0);
+                    const float4 n0 = np[0], n1 = np[1];
+                    const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = (v1[j] * rms0) * nw[j];
+                }
             } else if (tk < m_act) {
                 const float4* xp = reinterpret_cast<const float4*>(xrow(tk) + e0);
                 float4 u0 = xp[0], u1 = xp[1];
