@@ -87,6 +87,8 @@ QM_CASES = [
     (12, 9, 1024, 64), (12, 2, 11008, 128),
     (2, 1, 2048, 2048), (2, 1, 5632, 2048), (2, 4, 256, 100), (2, 1, 96, 64),
     (8, 1, 2048, 3200), (8, 5, 512, 70), (8, 1, 64, 48),
+    # Q4_0 / Q8_0 on the int8 tensor-core kernel: two to four tokens, rows of one to 43 units, row counts off the 32-row tile
+    (2, 2, 1024, 77), (2, 3, 2304, 40), (2, 4, 11008, 33), (8, 2, 1024, 50), (8, 3, 768, 100), (8, 4, 4096, 33), (8, 1, 11008, 65),
     (13, 1, 512, 40), (14, 2, 512, 40), (20, 1, 128, 40), (0, 2, 100, 24), (1, 1, 100, 24),
     (13, 1, 4096, 300), (13, 5, 2816, 64), (13, 8, 256, 19), (14, 1, 4096, 300), (14, 3, 11008, 40), (14, 8, 768, 21),
     (20, 1, 4096, 300), (20, 2, 2816, 33), (0, 3, 512, 40), (1, 1, 4096, 300), (1, 8, 256, 19), (1, 2, 11008, 33),
