@@ -25,15 +25,16 @@ __device__ __forceinline__ int32_t total_key_f(float f) {  // orders f32 bit pat
     return b ^ (int32_t)(((uint32_t)(b >> 31)) >> 1);
 }
 
-// One CTA per token.  The arithmetic per token is that of a single warp per sum (lane-strided fused multiply-adds, then the
-// warp tree), whatever the grid: warp 0 forms the RMS scale, the warps share the experts' dot products, thread 0 picks and
-// weighs.  When the call wants slot lists (`lists`), the CTA that finishes last (a ticket) reads every token's choices back
+// One CTA per token: the row comes into shared memory once (float4 reads; the sum of squares on the way), is normalised there,
+// the warps share the experts' dot products (float4 pieces per lane in order, then the warp tree), thread 0 picks and weighs.
+// The order of every sum is fixed by the block shape alone, so every rank of a cut model and every call computes the same bits.  When the call wants slot lists (`lists`), the CTA that finishes last (a ticket) reads every token's choices back
 // and lists, per expert and in token order, the (token, choice) slots it received.
 __global__ void __launch_bounds__(kRouteThreads)
 moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int H, int T, const float* __restrict__ w_router,
                  int E, int K, int32_t* __restrict__ sel, float* __restrict__ wsel, int32_t* __restrict__ cnt, int32_t* __restrict__ lists,
                  int list_stride, unsigned long long* __restrict__ touched, int local_first, int local_count, unsigned* __restrict__ ticket) {
-    __shared__ float scale_s;
+    extern __shared__ float xs[];  // the token's row, then its normalised form
+    __shared__ float part_s[kRouteThreads / 32];
     __shared__ float logit_s[kMaxExperts];
     __shared__ int last_s;
     pdl_launch_dependents();
@@ -41,20 +42,36 @@ moe_route_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int t = blockIdx.x;
     const float* xr = x + (size_t)t * H;
-    if (warp == 0) {  // cpu.rs:49-60: 1 / sqrt(mean(x^2) + eps)
-        float ss = 0.f;
-        for (int i = lane; i < H; i += 32) ss = fmaf(xr[i], xr[i], ss);
-        ss = warp_sum(ss);
-        if (lane == 0) scale_s = norm_w ? 1.0f / sqrtf(ss / (float)H + eps) : 1.0f;
+    // cpu.rs:49-60: 1 / sqrt(mean(x^2) + eps).  Every thread sums its own float4 pieces in order, the warps' sums are added in warp order.
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(xr + i);
+        *reinterpret_cast<float4*>(xs + i) = v;
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) part_s[warp] = ss;
+    __syncthreads();
+    float sc = 1.0f;
+    if (norm_w) {
+        float tot = 0.f;
+        for (int w = 0; w < nwarps; w++) tot += part_s[w];
+        sc = 1.0f / sqrtf(tot / (float)H + eps);
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {  // each thread its own pieces: no barrier needed before
+            float4 v = *reinterpret_cast<float4*>(xs + i);
+            const float4 g = *reinterpret_cast<const float4*>(norm_w + i);
+            v.x = (v.x * sc) * g.x; v.y = (v.y * sc) * g.y; v.z = (v.z * sc) * g.z; v.w = (v.w * sc) * g.w;
+            *reinterpret_cast<float4*>(xs + i) = v;
+        }
     }
     __syncthreads();
-    const float sc = scale_s;
-    for (int e = warp; e < E; e += nwarps) {
+    for (int e = warp; e < E; e += nwarps) {  // one warp per expert: lane l takes float4 pieces l, l + 32, ... in order
         const float* wr = w_router + (size_t)e * H;
         float acc = 0.f;
-        for (int i = lane; i < H; i += 32) {
-            const float xn = norm_w ? (xr[i] * sc) * norm_w[i] : xr[i];
-            acc = fmaf(xn, wr[i], acc);
+        for (int i = lane * 4; i < H; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(xs + i);
+            const float4 w4 = __ldg(reinterpret_cast<const float4*>(wr + i));
+            acc = fmaf(v.x, w4.x, acc); acc = fmaf(v.y, w4.y, acc); acc = fmaf(v.z, w4.z, acc); acc = fmaf(v.w, w4.w, acc);
         }
         acc = warp_sum(acc);
         if (lane == 0) logit_s[e] = acc;
@@ -130,6 +147,24 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int32_t* _
 }
 
 template <typename... KArgs, typename... Args>
+cudaError_t launch_dep_smem(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = ensure_smem_limit((const void*)kern, smem);
+        if (e != cudaSuccess) return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
 cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -152,7 +187,10 @@ int32_t launch_moe_route(const MoeRouteArgs& a, cudaStream_t s) {
     const bool want_lists = a.lists != nullptr;
     if (want_lists) LC_CHECK(a.T <= kRouteTokens && a.counts && a.list_stride >= a.T, LC_ERR_INVALID, "moe route: slot lists need a call of at most %d tokens", kRouteTokens);
     if (want_lists) LC_CHECK(a.ticket != nullptr, LC_ERR_INVALID, "moe route: slot lists need the ticket word");
-    LC_CUDA(launch_dep(moe_route_kernel, dim3((unsigned)a.T), dim3(kRouteThreads), s, a.x, a.norm_w, a.eps, a.H, a.T, a.w_router, a.n_experts, a.top_k, a.sel,
+    LC_CHECK(a.H % 4 == 0 && ((uintptr_t)a.x % 16) == 0 && ((uintptr_t)a.w_router % 16) == 0 && (!a.norm_w || ((uintptr_t)a.norm_w % 16) == 0) &&
+                 (size_t)a.H * sizeof(float) <= 160 * 1024,
+             LC_ERR_INVALID, "moe route: rows must be 16-byte aligned multiples of four elements");
+    LC_CUDA(launch_dep_smem(moe_route_kernel, dim3((unsigned)a.T), dim3(kRouteThreads), (size_t)a.H * sizeof(float), s, a.x, a.norm_w, a.eps, a.H, a.T, a.w_router, a.n_experts, a.top_k, a.sel,
                        a.wsel, a.counts, a.lists, a.list_stride, a.touched, a.local_first, a.local_count > 0 ? a.local_count : a.n_experts, a.ticket));
     return LC_OK;
 }
