@@ -555,7 +555,7 @@ def cut_model_legs(lc, synth, ranks, rank: int, world: int, local: int) -> dict:
     try:
         sums = {"32 KiB (one token of hidden 8192)": round(ranks.barrier_max(lcd.time_allreduce(8192, 100)), 2),
                 "1 MiB (32 tokens)": round(ranks.barrier_max(lcd.time_allreduce(262144, 50)), 2)}
-        out["rank_sums"] = {"us_per_sum": sums, "path_up_to_128KiB": "peer memory: tagged words written into every rank's buffer over NVLink, summed in rank order"
+        out["rank_sums"] = {"us_per_sum": sums, "path_up_to_256KiB": "peer memory: tagged words written into every rank's buffer over NVLink, summed in rank order"
                             if lcd.info()["peer_memory"] else "NCCL all-reduce", "larger": "NCCL all-reduce"}
 
         def decode_leg(eng, spec, n_seqs, prompt_len, steps, warm, seed0):

@@ -29,7 +29,20 @@ namespace lc {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr int kLLWords = 32768;              // values per rank and sum on the peer-memory path (128 KiB of f32); larger sums use NCCL
+// Values per rank and sum on the peer-memory path (LC_DIST_LL_WORDS, a multiple of 1024); larger sums use NCCL.  Default 256 KiB of
+// f32: there the tagged words still win (2 GPUs 9.2 against 10.7 us, 8 GPUs 20.1 against 27.4 us); at 512 KiB NCCL is ahead
+// (12.6 against 11.7 us, 35.5 against 27.7 us): every rank writes its whole row, twice as wide, into every peer.
+static int ll_words() {
+    static const int v = [] {
+        const char* e = getenv("LC_DIST_LL_WORDS");
+        int w = e ? atoi(e) : 65536;
+        if (w < 1024) w = 1024;
+        if (w > (1 << 20)) w = 1 << 20;
+        return w / 1024 * 1024;
+    }();
+    return v;
+}
+#define kLLWords (ll_words())
 
 // ---- NCCL through dlopen ----
 typedef struct { char internal[128]; } NcclId;
@@ -105,6 +118,7 @@ struct LLParams {
     unsigned* debug;                       // 8 words written by the first wait that runs out: what it was waiting for
     unsigned long long timeout_ns;
     int rank, world;
+    int row_words;                         // values per source rank in a slot
 };
 
 __device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
@@ -131,7 +145,7 @@ __global__ void __launch_bounds__(256) peer_ll_kernel(LLParams P, const void* __
     // kernel that skipped the wait would read the count before the previous sum's kernel has moved it.)
     pdl_wait();
     const unsigned e = *P.epoch + 1; // stable for the whole kernel: only this kernel's last CTA moves it, after everyone read it
-    const size_t row = (size_t)kLLWords, slot = (size_t)(e & 1u) * P.world * row;
+    const size_t row = (size_t)P.row_words, slot = (size_t)(e & 1u) * P.world * row;
     const size_t words = KEYS ? 2 * count : count;
     const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
     if (push) {
@@ -219,6 +233,7 @@ LLParams ll_params() {
     static const unsigned long long ms = getenv("LC_DIST_TIMEOUT_MS") ? strtoull(getenv("LC_DIST_TIMEOUT_MS"), nullptr, 10) : 10000ull;
     P.timeout_ns = ms * 1000000ull;
     P.rank = g_dist.rank; P.world = g_dist.world;
+    P.row_words = kLLWords;
     return P;
 }
 
