@@ -608,6 +608,24 @@ def cut_model_legs(lc, synth, ranks, rank: int, world: int, local: int) -> dict:
     return out
 
 
+def tp_ranks_one_gpu(lc, synth, tp: int, layers: int, ctx: int, steps: int) -> dict:
+    """The ranks of the Llama-3-70B shape cut over `tp` GPUs, all in this process on ONE GPU (an in-process group: the same
+    kernels with the same per-rank shapes, the sums over the ranks by a local kernel instead of over NVLink).  A profiling
+    case: a launch list of this run shows what each rank executes; the time printed is all ranks' kernels one after the other."""
+    from leafcutterllm_b200.engine import Engine
+    lc._capi.check(lc.load().lc_set_device(0))
+    spec = synth.LLAMA70B.with_layers(layers)
+    engs = [synth.build_engine(spec, ctx + 64, on_device=True, device=0, tp_size=tp, tp_rank=r) for r in range(tp)]
+    lead = Engine.group(engs)
+    _, nxt = lead.forward_batch([0], [synth.prompt_tokens(ctx, spec.vocab_size, 5)], want_logits=False)
+    toks, _ = lead.decode_loop([0], [int(nxt[0])], 3)
+    toks, ms = lead.decode_loop([0], toks[-1].tolist(), steps)
+    for e in engs:
+        e.close()
+    return {"workload": f"Llama-3-70B shape, {layers} layers, cut over {tp} ranks that all run on one GPU, batch 1, context {ctx}",
+            "ms_per_step_all_ranks_in_turn": round(ms / steps, 4), "steps": steps, "not_the_metric": "profiling case"}
+
+
 def run_ours(args):
     rank, world, local = dist_env()
     import leafcutterllm_b200 as lc
@@ -742,7 +760,10 @@ def main():
     ap.add_argument("--no-bs64", action="store_true", help="skip the 64-sequence continuous-batching leg (configs[2])")
     ap.add_argument("--no-extra", action="store_true", help="skip the legs after the metric: configs[0], configs[3] (one GPU), the cut 70B / mixture models (several GPUs)")
     ap.add_argument("--ref-context", type=int, default=64, help="--impl reference: context of the sampled CPU run (the oracle's prefill is slow)")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64", "moe", "tiny"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64", "moe", "tiny", "tp-ranks"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count; tp-ranks: the ranks of a cut 70B-shape model as one in-process group on one GPU (what each rank's kernels cost)")
+    ap.add_argument("--gemm-shapes", default="", help="--only gemm: k x n pairs instead of the 7B layer shapes, e.g. 1024x12288,8192x12288")
+    ap.add_argument("--gemm-tokens", default="", help="--only gemm: token counts instead of 64,512")
+    ap.add_argument("--tp", type=int, default=8, help="--only tp-ranks: ranks the model is cut over")
     ap.add_argument("--profile-range", action="store_true", help="bracket the timed decode loop with cudaProfilerStart/Stop")
     ap.add_argument("--layers", type=int, default=0, help="profiling only: keep this many of the 32 layers (the printed number is then not the metric)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="context prefilled before decoding (default: the 2048 of the workload)")
@@ -771,7 +792,14 @@ def main():
         print(json.dumps(moe_decode(lc, synth, 0, steps=min(args.steps, 64), layers=args.layers) if args.only == "moe" else tiny_decode(lc, synth, 0)))
     elif args.only in ("gemm", "gemm-small"):
         import leafcutterllm_b200 as lc
-        print(json.dumps(gemm_microbench(lc, tokens=(64,) if args.only == "gemm-small" else (64, 512), small=args.only == "gemm-small")))
+        shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.gemm_shapes.split(",")] if args.gemm_shapes else None
+        tokens = tuple(int(v) for v in args.gemm_tokens.split(",")) if args.gemm_tokens else ((64,) if args.only == "gemm-small" else (64, 512))
+        print(json.dumps(gemm_microbench(lc, tokens=tokens, small=args.only == "gemm-small", shapes=shapes)))
+    elif args.only == "tp-ranks":
+        import leafcutterllm_b200 as lc
+        from leafcutterllm_b200 import synth
+        print(json.dumps(tp_ranks_one_gpu(lc, synth, args.tp, args.layers if args.layers > 0 else 2, args.prompt_len if args.prompt_len != PROMPT_LEN else 4096,
+                                          min(args.steps, 16))))
     elif args.only == "gemv":
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth
