@@ -760,7 +760,7 @@ def main():
     ap.add_argument("--no-bs64", action="store_true", help="skip the 64-sequence continuous-batching leg (configs[2])")
     ap.add_argument("--no-extra", action="store_true", help="skip the legs after the metric: configs[0], configs[3] (one GPU), the cut 70B / mixture models (several GPUs)")
     ap.add_argument("--ref-context", type=int, default=64, help="--impl reference: context of the sampled CPU run (the oracle's prefill is slow)")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64", "moe", "tiny", "tp-ranks"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count; tp-ranks: the ranks of a cut 70B-shape model as one in-process group on one GPU (what each rank's kernels cost)")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64", "moe", "tiny", "tp-ranks", "tcgen05-probe"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count; tp-ranks: the ranks of a cut 70B-shape model as one in-process group on one GPU (what each rank's kernels cost)")
     ap.add_argument("--gemm-shapes", default="", help="--only gemm: k x n pairs instead of the 7B layer shapes, e.g. 1024x12288,8192x12288")
     ap.add_argument("--gemm-tokens", default="", help="--only gemm: token counts instead of 64,512")
     ap.add_argument("--tp", type=int, default=8, help="--only tp-ranks: ranks the model is cut over")
@@ -795,6 +795,15 @@ def main():
         shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.gemm_shapes.split(",")] if args.gemm_shapes else None
         tokens = tuple(int(v) for v in args.gemm_tokens.split(",")) if args.gemm_tokens else ((64,) if args.only == "gemm-small" else (64, 512))
         print(json.dumps(gemm_microbench(lc, tokens=tokens, small=args.only == "gemm-small", shapes=shapes)))
+    elif args.only == "tcgen05-probe":
+        import ctypes as C
+        import leafcutterllm_b200 as lc
+        out = (C.c_double * 16)()
+        lc._capi.check(lc.load().lc_tcgen05_probe(out))
+        names = ["mma_n128_one_issuer", "mma_n256_one_issuer", "mma_n128_two_issuers_each", "commit", "st16_wait", "st16_wait_fence_arrive128",
+                 "ld16_wait", "fence_before", "fence_after", "barrier_probe_vote", "arrive_to_waiter_returns", "unpack_chunk_4_warps",
+                 "unpack_chunk_8_warps", "unpack_chunk_16_warps"]
+        print(json.dumps({"unit": "SM cycles per operation", **{n: round(out[i], 1) for i, n in enumerate(names)}}))
     elif args.only == "tp-ranks":
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth

@@ -217,6 +217,13 @@ int32_t lc_dist_debug(uint32_t* out8);
 /* Microseconds per sum of `count` floats over the ranks, averaged over `iters` back-to-back sums on the library's stream
  * (CUDA events; a measurement helper for the all-reduce that sits between a layer's products). */
 int32_t lc_dist_time_allreduce(size_t count, int32_t iters, float* out_us);
+
+/* Diagnostic, no counterpart in the reference: SM cycles per operation of the building blocks of the many-token product on
+ * this GPU (one CTA, no memory traffic): out16[0..13] = tcgen05.mma M128 K16 issued by one thread at N = 128 and N = 256,
+ * by two threads at once, tcgen05.commit, tcgen05.st + wait, the same + fence + barrier arrival of 128 threads,
+ * tcgen05.ld + wait, the two tcgen05 fences, a barrier probe + warp vote, arrival -> a waiting thread returns, and the
+ * unpacking of one 64-element Q4_K chunk of 32 rows with 4 / 8 / 16 warps at it.  Every wait inside is bounded. */
+int32_t lc_tcgen05_probe(double* out16);
 int32_t lc_model_group(lc_model** handles, int32_t n);
 /* Which part of a tensor a rank keeps: kind 0 = all of it, 1 = rows [first, first + count) (dims[1] index; for stacked expert
  * tensors rows of the flattened [dims[2] * dims[1]] matrix), 2 = columns [first, first + count) of every row (dims[0] index),

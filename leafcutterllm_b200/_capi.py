@@ -131,6 +131,7 @@ SIGNATURES = {
     "lc_dist_debug": (_i32, [_vp]),
     "lc_dist_info": (_i32, [C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_i32)]),
     "lc_dist_time_allreduce": (_i32, [_sz, _i32, C.POINTER(C.c_float)]),
+    "lc_tcgen05_probe": (_i32, [C.POINTER(C.c_double)]),
     "lc_model_group": (_i32, [C.POINTER(_vp), _i32]),
     "lc_shard_plan": (_i32, [C.POINTER(ModelConfig), C.c_char_p, _vp, _i32, C.POINTER(_i32), C.POINTER(_u64), C.POINTER(_u64)]),
 }

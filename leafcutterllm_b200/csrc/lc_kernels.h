@@ -130,6 +130,7 @@ struct GemmWorkspace {
     mutable const float* prep_norm = nullptr;
     mutable int prep_k = 0, prep_t = 0;
 };
+int32_t run_tcgen05_probe(double* out16_host, cudaStream_t s);
 int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max);
 void qgemm_workspace_free(GemmWorkspace* ws);
 // true when launch_qgemm implements these arguments for T tokens (Q4_K weights, T at least LC_GEMM_MIN_TOKENS, default 5: up to four tokens the

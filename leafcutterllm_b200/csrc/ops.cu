@@ -487,6 +487,12 @@ int32_t lc_qmatmul_dev(uint32_t typ, const float* a_dev, const void* w_dev, size
     return qmatmul_rows(w, a_dev, m, c_dev);
 }
 
+int32_t lc_tcgen05_probe(double* out16) {
+    if (!have_device()) return LC_ERR_CUDA;
+    LC_CHECK(out16 != nullptr, LC_ERR_INVALID, "lc_tcgen05_probe: null pointer");
+    return run_tcgen05_probe(out16, stream());
+}
+
 int32_t lc_q8_0_matmul_shard(const float* a, const float* scales, const int8_t* qs, size_t m, size_t k, size_t n, float* c) {
     LC_CHECK(a && scales && qs && c, LC_ERR_INVALID, "lc_q8_0_matmul_shard: null pointer");
     LC_CHECK(n % 32 == 0, LC_ERR_INVALID, "lc_q8_0_matmul_shard: n=%zu must be a multiple of 32", n);

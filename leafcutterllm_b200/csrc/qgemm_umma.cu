@@ -674,6 +674,169 @@ qgemm_reduce_prep_kernel(const float* __restrict__ partial, int slices, int T, i
     xprep_row(row, acc, next_norm_w, next_eps, n, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
 }
 
+// ---- diagnostic: what the building blocks of the kernel above cost on this GPU ----------------------------------------
+// One CTA, no global-memory traffic in the timed parts; every wait bounded.  out[] (SM cycles per operation):
+//   0  tcgen05.mma M128 N128 K16, A in tensor memory, one issuing thread, a commit after every four
+//   1  the same with N = 256
+//   2  the same (N = 128) issued by two threads at once, own accumulators each: cycles per instruction of one thread
+//   3  tcgen05.commit
+//   4  tcgen05.st x16 + wait::st                  5  ... + fence + arrival of 128 threads on one barrier
+//   6  tcgen05.ld x16 + wait::ld                  7  tcgen05.fence::before_thread_sync     8  ...::after_thread_sync
+//   9  barrier probe of a completed phase + warp vote
+//   10 arrival by one thread -> a waiting thread returns (mean of eight)
+//   11 / 12 / 13  unpacking one 64-element chunk of 32 rows, per warp, with 4 / 8 / 16 warps at it
+__global__ void __launch_bounds__(512, 1) tcgen05_probe_kernel(double* out) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 96 * 1024);  // [0..7] and [16..23] count 1, [8..15] count 128
+    uint32_t* slot = reinterpret_cast<uint32_t*>(bars + 24);
+    long long* stamp = reinterpret_cast<long long*>(slot + 4);     // [16] hop stamps
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < 96 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(sm)[i] = 0x11111111u * (uint32_t)(i % 7) + (uint32_t)i;
+    if (tid == 0) {
+        for (int i = 0; i < 24; i++) mbar_init(&bars[i], (i >= 8 && i < 16) ? 128 : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *slot;
+    bool ok = true;
+    constexpr int R = 64;
+    if (tid == 0) {  // 0, 1, 3: one issuer
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(sm));
+        int ph = 0;
+        for (int ni = 0; ni < 2; ni++) {
+            const uint32_t id = idesc_f16(ni ? 256 : 128);
+            const long long t0 = clock64();
+            for (int r = 0; r < R; r++) {
+                umma_f16_ts(tmem, tmem + 384 + (r & 3) * 8, bdesc + (uint64_t)((r & 3) * 2), id, 1u);
+                if ((r & 3) == 3) umma_commit(&bars[1 + ((r >> 2) & 3)]);
+            }
+            const long long t1 = clock64();
+            umma_commit(&bars[0]);
+            const long long t2 = clock64();
+            ok = mbar_wait(&bars[0], (uint32_t)ph) && ok;
+            ph ^= 1;
+            out[ni] = (double)(t1 - t0) / R;
+            if (ni == 0) out[3] = (double)(t2 - t1);
+        }
+    }
+    __syncthreads();
+    if ((warp == 4 || warp == 5) && lane == 0) {  // 2: two issuers at once
+        const int g = warp - 4;
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(sm + g * 32768));
+        const uint32_t id = idesc_f16(128);
+        const long long t0 = clock64();
+        for (int r = 0; r < R; r++) {
+            umma_f16_ts(tmem + g * 128, tmem + 384 + g * 64 + (r & 3) * 8, bdesc + (uint64_t)((r & 3) * 2), id, 1u);
+            if ((r & 3) == 3) umma_commit(&bars[5 + g]);
+        }
+        const long long t1 = clock64();
+        umma_commit(&bars[16 + g]);  // every product of this thread has completed before tensor memory is written below
+        ok = mbar_wait(&bars[16 + g], 0u) && ok;
+        if (g == 0) out[2] = (double)(t1 - t0) / R;
+    }
+    __syncthreads();
+    if (warp < 4) {  // 4 .. 9
+        uint32_t v[16];
+        for (int i = 0; i < 16; i++) v[i] = (uint32_t)(lane + i);
+        const uint32_t base = tmem + ((uint32_t)(warp * 32) << 16);
+        long long t0 = clock64();
+        for (int r = 0; r < 32; r++) { tmem_st16(base + 448 + (r & 1) * 16, v); asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+        long long t1 = clock64();
+        for (int r = 0; r < 32; r++) {
+            tmem_st16(base + 448 + (r & 1) * 16, v);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(&bars[8 + (r & 7)]);
+        }
+        long long t2 = clock64();
+        uint32_t acc = 0;
+        for (int r = 0; r < 32; r++) { tmem_ld16(base + 256 + (r & 3) * 16, v); asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); acc += v[3]; }
+        long long t3 = clock64();
+        for (int r = 0; r < 32; r++) tc_fence_before();
+        long long t4 = clock64();
+        for (int r = 0; r < 32; r++) tc_fence_after();
+        long long t5 = clock64();
+        for (int r = 0; r < 32; r++) acc += __all_sync(0xffffffffu, mbar_test(&bars[0], 1u)) ? 1u : 0u;  // phase 1 of barrier 0 completed above
+        long long t6 = clock64();
+        if (tid == 0) {
+            out[4] = (t1 - t0) / 32.0; out[5] = (t2 - t1) / 32.0; out[6] = (t3 - t2) / 32.0; out[7] = (t4 - t3) / 32.0; out[8] = (t5 - t4) / 32.0;
+            out[9] = (t6 - t5) / 32.0;
+        }
+        if (acc == 0x9e3779b9u) stamp[15] = 1;  // keeps the loads' results alive
+    }
+    __syncthreads();
+    if (warp == 2 && lane == 0) {  // 10: the arriving side
+        for (int r = 0; r < 8; r++) {
+            const long long t = clock64();
+            while (clock64() - t < 3000) {}
+            stamp[r] = clock64();
+            mbar_arrive(&bars[18]);
+        }
+    }
+    if (warp == 3 && lane == 0) {  // 10: the waiting side
+        for (int r = 0; r < 8; r++) { ok = mbar_wait(&bars[18], (uint32_t)(r & 1)) && ok; stamp[8 + r] = clock64(); }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        double h = 0;
+        for (int r = 0; r < 8; r++) h += (double)(stamp[8 + r] - stamp[r]);
+        out[10] = h / 8;
+    }
+    for (int nw = 4, k = 0; nw <= 16; nw *= 2, k++) {  // 11 .. 13
+        __syncthreads();
+        if (warp < nw) {
+            const unsigned char* rp = sm + ((warp & 3) * 32 + lane) * kUnitBytes;
+            uint32_t acc = 0;
+            const long long t0 = clock64();
+            for (int it = 0; it < 32; it++) {
+                HdrQ4K hdr;
+                load_hdr(rp, hdr);
+                for (int c = 0; c < 4; c++) {
+                    uint32_t col[32];
+                    unpack_chunk(rp, hdr, c, col);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) acc ^= col[i];
+                    asm volatile("" ::: "memory");
+                }
+            }
+            const long long t1 = clock64();
+            if (tid == 0) out[11 + k] = (double)(t1 - t0) / 128.0;
+            if (acc == 0x9e3779b9u) stamp[15] = 1;  // keeps the unpacked values alive
+        }
+    }
+    if (!ok && tid == 0) out[15] = -1.0;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+int32_t run_tcgen05_probe(double* out16_host, cudaStream_t s) {
+    double* d = nullptr;
+    LC_CUDA(cudaMalloc((void**)&d, 16 * sizeof(double)));
+    LC_CUDA(cudaMemsetAsync(d, 0, 16 * sizeof(double), s));
+    const size_t smem = 96 * 1024 + 1024 + 1024;
+    LC_CUDA(ensure_smem_limit((const void*)tcgen05_probe_kernel, smem));
+    tcgen05_probe_kernel<<<1, 512, smem, s>>>(d);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out16_host, d, 16 * sizeof(double), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(d);
+    LC_CUDA(e);
+    LC_CHECK(out16_host[15] == 0.0, LC_ERR_CUDA, "tcgen05 probe: a bounded wait ran out");
+    return LC_OK;
+}
+
 // ---- host side --------------------------------------------------------------------------------------------------------
 int32_t qgemm_workspace_alloc(GemmWorkspace* ws, int t_cap, int k_max) {
     LC_CHECK(ws && t_cap > 0 && k_max > 0, LC_ERR_INVALID, "qgemm workspace: bad size");
