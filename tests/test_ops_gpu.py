@@ -198,3 +198,14 @@ def test_rope_and_argmax(gpu, oracle):
     assert gpu.sample_top_p(v, 0.0, 1.0) == 31000 == oracle.argmax(v)  # last of equal maxima
     v = r.standard_normal(128256).astype(np.float32)
     assert gpu.sample_top_p(v, 0.0, 1.0) == oracle.argmax(v)
+
+
+def test_tcgen05_probe_runs(gpu):
+    """The diagnostic that times the building blocks of the many-token product: it must come back (every wait inside is
+    bounded) with a positive cycle count for each of its fourteen measurements."""
+    import ctypes as C
+    out = (C.c_double * 16)()
+    gpu._capi.check(gpu.load().lc_tcgen05_probe(out))
+    vals = [out[i] for i in range(14)]
+    assert all(v > 0 for v in vals), vals
+    assert out[15] == 0.0
