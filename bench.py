@@ -666,14 +666,25 @@ def run_ours(args):
     nxt = toks[-1]
     ctx_mid = plen + max(args.warmup, 3) + args.steps // 2
 
-    # end to end: host token in (pinned staging), logits + pick out, every step, through lc_forward_batch
+    # end to end: host token in (pinned staging inside the library), logits + pick out, every step, through the C ABI's
+    # lc_forward_batch with host buffers that live across the steps (what a binding of the reference's Engine::forward would hold)
+    import ctypes as C
+    import numpy as np
+    e_seq = np.zeros(1, np.int32); e_cnt = np.ones(1, np.int32)
+    e_tok = np.array([int(nxt[0])], np.int64); e_next = np.zeros(1, np.int64)
+    e_logits = np.empty((1, spec.vocab_size), np.float32)
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    def e2e_step():
+        lc._capi.check(lib.lc_forward_batch(eng._h, 1, vp(e_seq), vp(e_tok), vp(e_cnt), vp(e_logits), vp(e_next)))
+        e_tok[0] = e_next[0]
     for _ in range(3):
-        _, nxt = eng.forward_batch([0], [[int(nxt[0])]], want_logits=True)
+        e2e_step()
     barrier_max(0.0)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        _, nxt = eng.forward_batch([0], [[int(nxt[0])]], want_logits=True)
+        e2e_step()
     e2e_s = barrier_max(time.perf_counter() - t0)
+    assert int(np.argmax(e_logits[0][::-1])) == spec.vocab_size - 1 - int(e_next[0]), "the pick is not the last maximum of the logits that came back"
     h2d = 8
     d2h = spec.vocab_size * 4 + 8
 

@@ -622,6 +622,26 @@ void finish_call(lc_model* m) {
 }  // namespace
 
 // A bounded wait inside a kernel ran out (TMA transaction or grid barrier): report instead of returning wrong tokens.
+// The device error flag travels with a call's other results (queued before the call's synchronisation) instead of in a
+// round trip of its own; flag_result() looks at what arrived.
+static int32_t queue_flag_read(lc_model* m) {
+    int* f = gemv_error_flag_dev();
+    int* dst = reinterpret_cast<int*>(m->pin_next + m->max_seqs);
+    *dst = 0;
+    if (f) LC_CUDA(cudaMemcpyAsync(dst, f, sizeof(int), cudaMemcpyDeviceToHost, m->stream));
+    return LC_OK;
+}
+static int32_t flag_result(lc_model* m) {
+    const int v = *reinterpret_cast<const int*>(m->pin_next + m->max_seqs);
+    if (v != 0) {
+        cudaMemsetAsync(gemv_error_flag_dev(), 0, sizeof(int), m->stream);
+        set_error("a device-side check failed (code %d: %s); the results of this call are not valid", v,
+                  v >= 20 ? "an index outside its range" : "a bounded wait ran out");
+        return LC_ERR_CUDA;
+    }
+    return LC_OK;
+}
+
 static int32_t check_device_flag(lc_model* m) {
     int* f = gemv_error_flag_dev();
     if (!f) return LC_OK;
@@ -1026,7 +1046,7 @@ int32_t lc_model_finalize(lc_model* m) {
     LC_TRY(dalloc(&m->d_attn_counters, (size_t)T * m->nh));
     LC_CUDA(cudaMemsetAsync(m->d_attn_counters, 0, (size_t)T * m->nh * sizeof(int), m->stream));
     LC_CUDA(cudaHostAlloc((void**)&m->pin_tokens, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
-    LC_CUDA(cudaHostAlloc((void**)&m->pin_next, (size_t)m->max_seqs * 8, cudaHostAllocDefault));
+    LC_CUDA(cudaHostAlloc((void**)&m->pin_next, ((size_t)m->max_seqs + 1) * 8, cudaHostAllocDefault));  // + one word: the device error flag of a call
     LC_CUDA(cudaHostAlloc((void**)&m->pin_logits, (size_t)m->max_seqs * m->cfg.vocab_size * 4, cudaHostAllocDefault));
     LC_TRY(reserve_out_tokens(m, (size_t)1024 * m->max_seqs));
     LC_CUDA(cudaEventCreate(&m->ev0));
@@ -1192,11 +1212,12 @@ int32_t lc_forward_batch(lc_model* lead, int32_t n_seqs, const int32_t* seq_ids,
         }
         LC_TRY(run_decode_steps(lead, n_seqs, 1));
         if (next_out) LC_CUDA(cudaMemcpyAsync(lead->pin_next, lead->d_next, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, lead->stream));
+        LC_TRY(queue_flag_read(lead));
         if (logits_out) LC_TRY(fetch_logits(lead, n_seqs, logits_out));
         LC_CUDA(cudaStreamSynchronize(lead->stream));
         if (next_out) memcpy(next_out, lead->pin_next, (size_t)n_seqs * 8);
         for (lc_model* m : R) { after_decode_steps(m, n_seqs, seq_ids, 1); finish_call(m); }
-        return check_device_flag(lead);
+        return flag_result(lead);
     }
     for (lc_model* m : R) m->meta_valid = false;
     // Rotary index = position inside the CALL (reference mode, attention.rs:13-21) or the cache position.
