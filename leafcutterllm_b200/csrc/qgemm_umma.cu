@@ -283,19 +283,21 @@ xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, floa
 
 // grid = (row tiles x matrices, token tiles, shares of k).  tmw0 / tmw1: raw blocks of the matrix (and of `up` for
 // EPI_SILU_MUL: CTAs past the first matrix's tiles work on the second), box = one unit x 128 rows.  tmx: the prepared
-// activations [2 halves][t_cap rows][k] f16, box = 64 elements x N rows x both halves, 128-byte swizzle; tms: the
-// sub-block sums [2][t_cap rows][k / 16], same box.
+// activations [2 halves][t_cap rows][k] f16 seen in four dimensions (element, row, half, 64-element chunk), box = 64 elements
+// x N rows x both halves x two chunks, 128-byte swizzle; tms: the sub-block sums [2][t_cap rows][k / 16], box = 64 x N x both halves.
 //
 // Roles (16 warps): warp 0 requests the activation tiles, warp 3 the raw boxes; the units of k are dealt in turn to two
 // pipelines g = 0, 1, each made of an unpack group of four warps (4 + 4g ..), an issuing thread (warp 1 + g) and its own
-// accumulators in tensor memory: one thread issues a tcgen05.mma of this shape every ~80 cycles at best, two together reach
-// the tensor pipe's rate (~67 cycles per M128 N128 K16).  Warps 12-15 only drain: thread r owns row r's f32 results for
-// the whole kernel, reads a finished unit's sums with tcgen05.ld while both pipelines already work on the next units, and
-// writes the tile at the end.  The unpack threads never wait for a product, the drain never unpacks.
+// accumulators in tensor memory: one thread issues a tcgen05.mma of this shape every ~70 cycles at best, two together reach
+// the tensor pipe's rate (~62 cycles per M128 N128 K16; lc_tcgen05_probe measures both).  Chunk c of every unit goes through
+// tensor-memory stage c, so a group unpacks a whole unit ahead of the products.  Warps 12-15 only drain: thread r owns row
+// r's f32 results for the whole kernel, reads a finished unit's sums with tcgen05.ld while both pipelines already work on
+// the next units, and writes the tile at the end.  The unpack threads never wait for a product, the drain never unpacks.
 //
 // The offset term -dmin * m needs no drain per unit: dmin * m (11 x 6 bits) is split exactly into two f16 (high part and
 // remainder), the sixteen values of a unit form one K = 16 operand against the sub-block sums stored twice, and the
-// products of all units accumulate in one set of columns per pipeline, read once at the end.
+// products of all units accumulate in ONE set of columns, read once at the end; the two issuers take turns on it (each
+// waits for the completion of the other's unit before), so the additions happen in k order.
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_constant__ CUtensorMap tmw1,
                       const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tms, GemmParams p) {
