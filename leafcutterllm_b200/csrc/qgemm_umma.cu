@@ -53,7 +53,9 @@ constexpr int kChunkK = 64;    // k per pipeline step: one 128-byte swizzled row
 constexpr int kMaxTok = 64;    // tokens per CTA (a multiple of 16)
 constexpr int kMaxRaw = 4;     // raw unit boxes in flight
 constexpr int kMaxB = 4;       // activation stages of two chunks each: two units in flight, and a stage always serves the same pipeline
-constexpr int kThreads = 512;  // warps 0 and 3 producers, warps 1-2 the two issuers, warps 4..7 and 8..11 the two unpack groups, 12..15 the drain
+constexpr int kUnpackGroups = 3;  // groups of four warps that take the units of k in turn
+constexpr int kDrainGroups = 2;   // groups of four warps that each drain half of the tokens
+constexpr int kThreads = 32 * (4 + 4 * kUnpackGroups + 4 * kDrainGroups);  // warps 0 and 3 producers, 1-2 the two issuers, then the unpack groups, then the drain
 constexpr int kDRing = 8;      // units whose per-row d travel from the unpack threads to the drain at a time
 constexpr int kUnitBytes = 144;
 // tensor-memory columns
@@ -61,8 +63,7 @@ constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kC
 constexpr uint32_t kColsPerPipe = 128;
 constexpr uint32_t kColDmin = 256;       // [0, N): -sum dmin m sx of all units
 constexpr uint32_t kColA = 320;          // four A stages of 32 columns: chunk c (64 k) of every unit goes through stage c
-constexpr uint32_t kColAmin = 448;       // four stages of 8 columns for the offset operand: two per pipeline, so that the operand of a unit
-                                         // can be written while the pipeline's unit before is still being multiplied
+constexpr uint32_t kColAmin = 448;       // a stage of 8 columns per unpack group for the offset operand of the unit it works on
 
 struct GemmParams {
     float* out;             // [T, n]
@@ -286,13 +287,15 @@ xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, floa
 // activations [2 halves][t_cap rows][k] f16 seen in four dimensions (element, row, half, 64-element chunk), box = 64 elements
 // x N rows x both halves x two chunks, 128-byte swizzle; tms: the sub-block sums [2][t_cap rows][k / 16], box = 64 x N x both halves.
 //
-// Roles (16 warps): warp 0 requests the activation tiles, warp 3 the raw boxes; the units of k are dealt in turn to two
-// pipelines g = 0, 1, each made of an unpack group of four warps (4 + 4g ..), an issuing thread (warp 1 + g) and its own
-// accumulators in tensor memory: one thread issues a tcgen05.mma of this shape every ~70 cycles at best, two together reach
-// the tensor pipe's rate (~62 cycles per M128 N128 K16; lc_tcgen05_probe measures both).  Chunk c of every unit goes through
-// tensor-memory stage c, so a group unpacks a whole unit ahead of the products.  Warps 12-15 only drain: thread r owns row
-// r's f32 results for the whole kernel, reads a finished unit's sums with tcgen05.ld while both pipelines already work on
-// the next units, and writes the tile at the end.  The unpack threads never wait for a product, the drain never unpacks.
+// Roles (24 warps): warp 0 requests the activation tiles, warp 3 the raw boxes.  The units of k are multiplied by two
+// pipelines in turn (unit s by pipeline s & 1: the issuing thread of warp 1 + (s & 1) and its own accumulators in tensor
+// memory): one thread issues a tcgen05.mma of this shape every ~70 cycles at best, two together reach the tensor pipe's
+// rate (~62 cycles per M128 N128 K16; lc_tcgen05_probe measures both).  They are unpacked by THREE groups of four warps in
+// turn (unit s by group s % 3: unpacking a unit takes a group about as long as three units take the pipelines); chunk c
+// of every unit goes through tensor-memory stage c, so a group works a whole unit ahead of the products.  Two groups of
+// four warps only drain, half of the tokens each: thread r owns row r's f32 results of its tokens for the whole kernel,
+// reads a finished unit's sums with tcgen05.ld while both pipelines already work on the next units, and writes the tile at
+// the end.  The unpack threads never wait for a product, the drain never unpacks.
 //
 // The offset term -dmin * m needs no drain per unit: dmin * m (11 x 6 bits) is split exactly into two f16 (high part and
 // remainder), the sixteen values of a unit form one K = 16 operand against the sub-block sums stored twice, and the
@@ -328,11 +331,13 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     uint64_t* b_empty = b_full + kMaxB;        // [kMaxB]   multiply (commit) -> producer
     uint64_t* s_full = b_empty + kMaxB;        // [2]       sub-block sums of four units: producer -> multiply
     uint64_t* s_empty = s_full + 2;            // [2]       multiply (the commit behind the last offset product that used them) -> producer
-    uint64_t* a_full = s_empty + 2;            // [2][4]    unpack group g filled stage c (128 arrivals) -> issuer g
-    uint64_t* a_empty = a_full + 8;            // [2][4]    issuer g's products of stage c are complete (commit) -> the other group
-    uint64_t* am_full = a_empty + 8;           // [2][2]    the offset operand of pipeline g, stage j & 1 (128 arrivals)
-    uint64_t* am_empty = am_full + 4;          // [2][2]    its product is complete (commit)
-    uint64_t* d_full = am_empty + 4;           // [2]       all products of a unit of pipeline g are complete (commit): the drain may read its sums,
+    // A barrier's waiter must see every phase of it: where two issuers or three unpack groups take turns, every (waiter, resource)
+    // pair has a barrier of its own, so nobody ever waits for a phase two or more ahead of the last one it saw.
+    uint64_t* a_full = s_empty + 2;            // [2][4]    stage c holds a chunk of a unit of pipeline g (128 arrivals) -> issuer g
+    uint64_t* a_empty = a_full + 8;            // [groups][4] the products of stage c are complete (commit): the barrier of the group that fills it next
+    uint64_t* am_full = a_empty + 4 * kUnpackGroups;  // [groups] the offset operand of the group's unit (128 arrivals); one stage per group
+    uint64_t* am_empty = am_full + kUnpackGroups;     // [groups] its product is complete (commit)
+    uint64_t* d_full = am_empty + kUnpackGroups;           // [2]       all products of a unit of pipeline g are complete (commit): the drain may read its sums,
                                                //           and the other issuer may add the next unit's offset product
     uint64_t* d_empty = d_full + 2;            // [2]       the drain has read them (128 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 2);
@@ -342,10 +347,11 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
         for (int i = 0; i < kMaxRaw; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 128); }
         for (int i = 0; i < kMaxB; i++) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
         for (int i = 0; i < 2; i++) {
-            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 1); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128);
+            mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 1); mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 128 * kDrainGroups);
         }
-        for (int i = 0; i < 4; i++) { mbar_init(&am_full[i], 128); mbar_init(&am_empty[i], 1); }
-        for (int i = 0; i < 8; i++) { mbar_init(&a_full[i], 128); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < kUnpackGroups; i++) { mbar_init(&am_full[i], 128); mbar_init(&am_empty[i], 1); }
+        for (int i = 0; i < 8; i++) mbar_init(&a_full[i], 128);
+        for (int i = 0; i < 4 * kUnpackGroups; i++) mbar_init(&a_empty[i], 1);
         *raw_issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -441,17 +447,19 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++)
                         umma_f16_ts(d_main, a_t + ks * 8, bdesc + (uint64_t)(ks * 2), idesc_main, (uint32_t)((c | ks) != 0));
-                    umma_commit(&a_empty[g * 4 + c]);
+                    umma_commit(&a_empty[((s + 1) % kUnpackGroups) * 4 + c]);  // the group of the unit behind this one fills the stage next
                     if (c & 1) umma_commit(&b_empty[sb]);
                 }
                 if (!ok) break;
                 {   // the offset term: A = the unit's sixteen halves of -dmin * m, B = this unit's 16 columns of the sums tile.
                     // One set of columns accumulates all units; the two issuers take turns, each waiting for the other's
                     // product of the unit before, so the additions happen in k order.
-                    const int q = s >> 2, ss = q & 1, am = g * 2 + (j & 1);
+                    const int q = s >> 2, ss = q & 1, am = s % kUnpackGroups;
                     if (!twait(&s_full[ss], (q >> 1) & 1, 3)) { ok = false; break; }
-                    if (!twait(&am_full[am], (j >> 1) & 1, 4)) { ok = false; break; }
+                    // first the other issuer's unit: with it every earlier unit is complete, so the operand barrier below (which
+                    // the two issuers see in turn) is in this unit's phase
                     if (s > 0 && !twait(&d_full[1 - g], ((s - 1) >> 1) & 1, 5)) { ok = false; break; }
+                    if (!twait(&am_full[am], (s / kUnpackGroups) & 1, 4)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t sdesc = umma_desc_sw128(smem_u32(st + (size_t)ss * b_bytes)) + (uint64_t)((s & 3) * 2);
                     umma_f16_ts(d_min, tmem + kColAmin + am * 8, sdesc, idesc_min, (uint32_t)(s > 0));
@@ -463,15 +471,15 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             }
             trace_out(2 + g);
         }
-    } else if (warp < 12) {
-        // ---------------------------------------------------------------- unpack
-        const int g = (warp - 4) >> 2;                // pipeline
+    } else if (warp < 4 + 4 * kUnpackGroups) {
+        // ---------------------------------------------------------------- unpack: group ug takes units ug, ug + kUnpackGroups, ...
+        const int ug = (warp - 4) >> 2;
         const int quarter = warp & 3;                 // the tensor-memory lanes this warp may touch
         const int row = quarter * 32 + lane;          // row of the tile owned by this thread
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const bool tr = quarter == 0 && lane == 0;
-        int j = 0;
-        for (int s = g; s < nseq && ok; s += 2, j++) {
+        for (int s = ug; s < nseq && ok; s += kUnpackGroups) {
+            const int g = s & 1;  // the unit's pipeline
             const int sr = s % RS;
             {   // the request for this unit's box has been made (see the producer)
                 const unsigned t0 = (unsigned)clock64();
@@ -494,16 +502,16 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 // unit before has read it, which ended long ago
                 uint32_t mc[8];
                 unpack_mins(hdr, mc);
-                ok = wait_all(&am_empty[g * 2 + (j & 1)], ((j >> 1) & 1) ^ 1, 2);
+                ok = wait_all(&am_empty[ug], ((s / kUnpackGroups) & 1) ^ 1, 2);
                 if (!ok) break;
                 tc_fence_after();
-                tmem_st8(tmem + lane_base + kColAmin + (g * 2 + (j & 1)) * 8, mc);
+                tmem_st8(tmem + lane_base + kColAmin + ug * 8, mc);
             }
             for (int c = 0; c < 4 && ok; c++) {
                 // stage c still holds the unit before this one (the other group's) until that unit's products have read it; ask
                 // now, look at the answer after the unpacking
-                const uint32_t par = (uint32_t)(((s - 1) >> 1) & 1);
-                bool free_now = s == 0 || mbar_test(&a_empty[(1 - g) * 4 + c], par);
+                const uint32_t par = (uint32_t)(((s - 1) / kUnpackGroups) & 1);  // this group's barrier: one commit per unit it fills after the first
+                bool free_now = s == 0 || mbar_test(&a_empty[ug * 4 + c], par);
                 uint32_t col[32];
                 unsigned tq0 = 0;
                 if (tracing) tq0 = (unsigned)clock64();
@@ -514,9 +522,9 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[5] += t1 - tq0; tq0 = t1; }
                 tc_fence_before();
-                mbar_arrive(c > 0 ? &a_full[g * 4 + c - 1] : &am_full[g * 2 + (j & 1)]);
+                mbar_arrive(c > 0 ? &a_full[g * 4 + c - 1] : &am_full[ug]);
                 if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[6] += t1 - tq0; tq0 = t1; }
-                if (!free_now) free_now = mbar_wait(&a_empty[(1 - g) * 4 + c], par);
+                if (!free_now) free_now = mbar_wait(&a_empty[ug * 4 + c], par);
                 ok = __all_sync(0xffffffffu, free_now);
                 if (!ok) break;
                 tc_fence_after();
@@ -531,15 +539,17 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             tc_fence_before();
             mbar_arrive(&a_full[g * 4 + 3]);
         }
-        if (tr) trace_out(4 + g);
+        if (tr && ug < 2) trace_out(4 + ug);
     } else {
         // ---------------------------------------------------------------- drain, then epilogue
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        float y[kMaxTok];
+        constexpr int kTokD = kMaxTok / kDrainGroups;                     // tokens per drain group
+        const int tbase = ((warp - 4 - 4 * kUnpackGroups) >> 2) * kTokD;  // this group's first token of the tile
+        float y[kTokD];
 #pragma unroll
-        for (int t = 0; t < kMaxTok; t++) y[t] = 0.f;
+        for (int t = 0; t < kTokD; t++) y[t] = 0.f;
         pdl_wait();
         for (int s = 0; s < nseq && ok; s++) {
             const int g = s & 1, j = s >> 1;
@@ -549,11 +559,11 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             tc_fence_after();
             const float d = dd[(s & (kDRing - 1)) * kRows + row];
 #pragma unroll
-            for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
-                if (t0 < N) {
+            for (int t0 = 0; t0 < kTokD; t0 += 16) {
+                if (tbase + t0 < N) {
                     uint32_t a[16], b[16];
-                    tmem_ld16(d_main + t0, a);
-                    if (two) tmem_ld16(d_main + N + t0, b);
+                    tmem_ld16(d_main + tbase + t0, a);
+                    if (two) tmem_ld16(d_main + N + tbase + t0, b);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
@@ -566,15 +576,15 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             tc_fence_before();
             mbar_arrive(&d_empty[g]);
         }
-        if (quarter == 0 && lane == 0) trace_out(6);
+        if (quarter == 0 && lane == 0 && tbase == 0) trace_out(6);
         // the offset sums (complete: every unit's d_full followed its offset product)
         if (ok && nseq > 0) {
             const uint32_t d_min = tmem + lane_base + kColDmin;
 #pragma unroll
-            for (int t0 = 0; t0 < kMaxTok; t0 += 16) {
-                if (t0 < N) {
+            for (int t0 = 0; t0 < kTokD; t0 += 16) {
+                if (tbase + t0 < N) {
                     uint32_t m[16];
-                    tmem_ld16(d_min + t0, m);
+                    tmem_ld16(d_min + tbase + t0, m);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int i = 0; i < 16; i++) y[t0 + i] += __uint_as_float(m[i]);
@@ -587,15 +597,15 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 // a share of k, or one of the two matrices of gate/up: the sums (scaled back per token) go to the summing kernel
                 float* dst = p.partial + ((size_t)(blockIdx.z * p.nmat + mat) * p.T) * p.n;
 #pragma unroll
-                for (int t = 0; t < kMaxTok; t++) {
-                    const int tok = tok0 + t;
-                    if (t < N && tok < p.T) dst[(size_t)tok * p.n + grow] = y[t] * __ldg(p.tok_scale + tok);
+                for (int t = 0; t < kTokD; t++) {
+                    const int tok = tok0 + tbase + t;
+                    if (tbase + t < N && tok < p.T) dst[(size_t)tok * p.n + grow] = y[t] * __ldg(p.tok_scale + tok);
                 }
             } else {
 #pragma unroll
-                for (int t = 0; t < kMaxTok; t++) {
-                    const int tok = tok0 + t;
-                    if (t < N && tok < p.T) {
+                for (int t = 0; t < kTokD; t++) {
+                    const int tok = tok0 + tbase + t;
+                    if (tbase + t < N && tok < p.T) {
                         const size_t o = (size_t)tok * p.n + grow;
                         float v = y[t] * __ldg(p.tok_scale + tok);
                         if (p.epi == EPI_ADD_RESIDUAL) v = __fadd_rn(p.residual[o], v);
