@@ -49,7 +49,6 @@ namespace lc {
 namespace {
 
 constexpr int kRows = 128;     // weight rows per CTA = MMA M
-constexpr int kChunkK = 64;    // k per pipeline step: one 128-byte swizzled row of f16
 constexpr int kMaxTok = 64;    // tokens per CTA (a multiple of 16)
 constexpr int kMaxRaw = 4;     // raw unit boxes in flight
 constexpr int kMaxB = 4;       // activation stages of two chunks each: two units in flight, and a stage always serves the same pipeline
