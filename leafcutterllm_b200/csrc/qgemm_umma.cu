@@ -199,28 +199,28 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 // One token per CTA: optional RMS norm, power-of-two scale, hi/lo split to f16, sub-block sums.
 // xh: [hi rows | lo rows at lo_offset] of K f16; sx: the same for the sums, rows of K/16 f16 -- per 256-element unit the
 // eight sub-block sums, twice.
-// The passes of the preparation over a token's row held in shared memory; `acc` = this thread's part of the sum of
-// squares, accumulated over elements 4 * tid + 4 * blockDim * j in that order.
-__device__ __forceinline__ void xprep_row(float* row, float acc, const float* __restrict__ norm_w, float eps, int K, int t,
+// The preparation of a token's row held in shared memory.  `acc` = this thread's part of the sum of squares, accumulated
+// over elements 4 * tid + 4 * blockDim * j in that order; `amax` = this thread's largest |x g| (|x| without a norm).  One
+// block-wide reduction gives both the RMS scale and the row's largest magnitude (scale * max |x g|: it only picks the
+// power of two that brings the row below 1, so its last-bit difference from max |(x scale) g| does not matter).
+__device__ __forceinline__ void xprep_row(float* row, float acc, float amax, const float* __restrict__ norm_w, float eps, int K, int t,
                                           __half* __restrict__ xh, size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset,
                                           float* __restrict__ tok_scale, float* sh) {
-    float mx = 0.f;
     float scale = 1.f;
-    if (norm_w) {
-        const float ss = block_sum(acc, sh);
-        scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));  // cpu.rs:52-55
+    float mx;
+    {   // sh: [0, 32) the warps' sums, [32, 64) their maxima
+        const float ws = warp_sum(acc), wm = warp_max(amax);
+        const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+        if (lane == 0) { sh[w] = ws; sh[32 + w] = wm; }
+        __syncthreads();  // also: the whole row is in shared memory
+        float r = (threadIdx.x < nw) ? sh[threadIdx.x] : 0.0f, rm = (threadIdx.x < nw) ? sh[32 + threadIdx.x] : 0.0f;
+        if (w == 0) { r = warp_sum(r); rm = warp_max(rm); }
+        __syncthreads();
+        if (threadIdx.x == 0) { sh[0] = r; sh[32] = rm; }
+        __syncthreads();
+        if (norm_w) scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sh[0], (float)K), eps)));  // cpu.rs:52-55
+        mx = sh[32] * scale;
     }
-    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
-        float4 v = *reinterpret_cast<float4*>(row + i);
-        if (norm_w) {
-            const float4 g = *reinterpret_cast<const float4*>(norm_w + i);
-            v.x = __fmul_rn(__fmul_rn(v.x, scale), g.x); v.y = __fmul_rn(__fmul_rn(v.y, scale), g.y);
-            v.z = __fmul_rn(__fmul_rn(v.z, scale), g.z); v.w = __fmul_rn(__fmul_rn(v.w, scale), g.w);
-            *reinterpret_cast<float4*>(row + i) = v;
-        }
-        mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));  // NaN does not raise the maximum
-    }
-    mx = block_max(mx, sh);
     int e = 0;
     if (mx > 0.f && mx < INFINITY) (void)frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1)
     const float down = ldexpf(1.0f, -e);
@@ -235,7 +235,12 @@ __device__ __forceinline__ void xprep_row(float* row, float acc, const float* __
         const int i = i0 + threadIdx.x * 4;
         float part = 0.f;
         if (i < K) {
-            const float4 v = *reinterpret_cast<float4*>(row + i);
+            float4 v = *reinterpret_cast<float4*>(row + i);
+            if (norm_w) {
+                const float4 g = *reinterpret_cast<const float4*>(norm_w + i);
+                v.x = __fmul_rn(__fmul_rn(v.x, scale), g.x); v.y = __fmul_rn(__fmul_rn(v.y, scale), g.y);
+                v.z = __fmul_rn(__fmul_rn(v.z, scale), g.z); v.w = __fmul_rn(__fmul_rn(v.w, scale), g.w);
+            }
             const float a = v.x * down, b = v.y * down, c = v.z * down, d = v.w * down;
             const __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(c, d);
             const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
@@ -267,18 +272,21 @@ __global__ void __launch_bounds__(1024)
 xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int K, __half* __restrict__ xh,
              size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
     extern __shared__ float row[];
-    __shared__ float sh[32];
+    __shared__ float sh[64];
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const float* xr = x + (size_t)t * K;
-    float acc = 0.f;
+    float acc = 0.f, amax = 0.f;
     for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
         const float4 v = *reinterpret_cast<const float4*>(xr + i);
         *reinterpret_cast<float4*>(row + i) = v;
         acc = fmaf(v.x, v.x, acc); acc = fmaf(v.y, v.y, acc); acc = fmaf(v.z, v.z, acc); acc = fmaf(v.w, v.w, acc);
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (norm_w) g = *reinterpret_cast<const float4*>(norm_w + i);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x * g.x), fabsf(v.y * g.y)), fmaxf(fabsf(v.z * g.z), fabsf(v.w * g.w))));  // NaN does not raise the maximum
     }
-    xprep_row(row, acc, norm_w, eps, K, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
+    xprep_row(row, acc, amax, norm_w, eps, K, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
 }
 
 // grid = (row tiles x matrices, token tiles, shares of k).  tmw0 / tmw1: raw blocks of the matrix (and of `up` for
@@ -657,12 +665,12 @@ qgemm_reduce_prep_kernel(const float* __restrict__ partial, int slices, int T, i
                          float* __restrict__ out, const float* __restrict__ next_norm_w, float next_eps, __half* __restrict__ xh,
                          size_t lo_offset, __half* __restrict__ sx, size_t sx_lo_offset, float* __restrict__ tok_scale) {
     extern __shared__ float row[];
-    __shared__ float sh[32];
+    __shared__ float sh[64];
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const size_t plane = (size_t)T * n;
-    float acc = 0.f;
+    float acc = 0.f, amax = 0.f;
     for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
         const size_t idx = (size_t)t * n + i;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
@@ -681,8 +689,11 @@ qgemm_reduce_prep_kernel(const float* __restrict__ partial, int slices, int T, i
         *reinterpret_cast<float4*>(out + idx) = a;
         *reinterpret_cast<float4*>(row + i) = a;
         acc = fmaf(a.x, a.x, acc); acc = fmaf(a.y, a.y, acc); acc = fmaf(a.z, a.z, acc); acc = fmaf(a.w, a.w, acc);
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (next_norm_w) g = *reinterpret_cast<const float4*>(next_norm_w + i);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x * g.x), fabsf(a.y * g.y)), fmaxf(fabsf(a.z * g.z), fabsf(a.w * g.w))));
     }
-    xprep_row(row, acc, next_norm_w, next_eps, n, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
+    xprep_row(row, acc, amax, next_norm_w, next_eps, n, t, xh, lo_offset, sx, sx_lo_offset, tok_scale, sh);
 }
 
 // ---- diagnostic: what the building blocks of the kernel above cost on this GPU ----------------------------------------
