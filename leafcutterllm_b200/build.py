@@ -16,8 +16,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libleafcutter_b200.so")
-SOURCES = ["common.cu", "dequant.cu", "scan.cu", "sampler.cu", "synth.cu", "ops.cu", "qgemv.cu", "qgemv_mma.cu", "qgemv_kq.cu", "qgemm_umma.cu", "moe.cu", "dist.cu", "attention.cu", "attention_stream.cu", "attention_prefill.cu", "engine.cu", "gguf.cu", "shard_engine.cu"]
-HEADERS = ["lc_common.cuh", "lc_quant.cuh", "lc_kernels.h", "lc_synth.h", "lc_tma.cuh", "lc_attn.cuh", os.path.join("..", "..", "include", "leafcutter_b200.h")]
+SOURCES = ["common.cu", "dequant.cu", "scan.cu", "sampler.cu", "synth.cu", "ops.cu", "qgemv.cu", "qgemv_mma.cu", "qgemv_mma_q6k.cu", "qgemv_kq.cu", "qgemm_umma.cu", "moe.cu", "dist.cu", "attention.cu", "attention_stream.cu", "attention_prefill.cu", "engine.cu", "gguf.cu", "shard_engine.cu"]
+HEADERS = ["lc_common.cuh", "lc_quant.cuh", "lc_kernels.h", "lc_synth.h", "lc_tma.cuh", "lc_planes.cuh", "lc_attn.cuh", os.path.join("..", "..", "include", "leafcutter_b200.h")]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [

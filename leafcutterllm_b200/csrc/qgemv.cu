@@ -629,6 +629,11 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
             return launch_qgemv(hi, s);
         }
     }
+    if (a.w->typ == LC_TYPE_Q6_K) {
+        bool launched = false;
+        LC_TRY(launch_qgemv_mma_q6k(a, s, &launched));
+        if (launched) return LC_OK;
+    }
     {
         bool launched = false;
         LC_TRY(launch_qgemv_kq(a, s, &launched));  // Q5_K / Q6_K with whole 256-element blocks, F16 / F32 rows

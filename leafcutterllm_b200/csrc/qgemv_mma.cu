@@ -20,6 +20,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include "lc_kernels.h"
+#include "lc_planes.cuh"
 #include "lc_quant.cuh"
 #include "lc_tma.cuh"
 
@@ -596,7 +597,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 __global__ void __launch_bounds__(256) gemv_planes_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, float eps, int k,
                                                           unsigned char* __restrict__ planes, float* __restrict__ sxf, float* __restrict__ inv2s) {
     __shared__ float s_part[8];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = lane & 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nunits = k / kUnitElems;
     const size_t row = blockIdx.x;
     const float* xr = x + row * (size_t)k;
@@ -626,40 +627,8 @@ __global__ void __launch_bounds__(256) gemv_planes_kernel(const float* __restric
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = (v[j] * rms) * nw[j];
         }
-        float amax = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
-        amax = warp_max(amax);
-        const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
-        const int s = max(-100, min(100, 22 - ex));
-        const float up = __uint_as_float((uint32_t)(127 + s) << 23), dn = __uint_as_float((uint32_t)(127 - s) << 23);
-        uint32_t pw[3][2];
-        int xsum = 0;
-        int d0[8], d1[8], d2[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            float sv = v[j] * up;
-            sv = fminf(fmaxf(sv, -4194304.f), 4194304.f);
-            const int X = __float2int_rn(sv);
-            xsum += X;
-            d0[j] = X;
-            d1[j] = (X - (int)(signed char)X) >> 8;
-            d2[j] = (d1[j] - (int)(signed char)d1[j]) >> 8;
-        }
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            pw[0][h] = __byte_perm(__byte_perm(d0[4 * h], d0[4 * h + 1], 0x0040), __byte_perm(d0[4 * h + 2], d0[4 * h + 3], 0x0040), 0x5410);
-            pw[1][h] = __byte_perm(__byte_perm(d1[4 * h], d1[4 * h + 1], 0x0040), __byte_perm(d1[4 * h + 2], d1[4 * h + 3], 0x0040), 0x5410);
-            pw[2][h] = __byte_perm(__byte_perm(d2[4 * h], d2[4 * h + 1], 0x0040), __byte_perm(d2[4 * h + 2], d2[4 * h + 3], 0x0040), 0x5410);
-        }
-        const int sb = lane >> 2, inner = (8 * lane) & 31;
         const size_t at = row * nunits + unit;
-#pragma unroll
-        for (int pl = 0; pl < 3; pl++) *reinterpret_cast<uint2*>(planes + at * 768 + sb * 96 + pl * 32 + inner) = make_uint2(pw[pl][0], pw[pl][1]);
-        xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
-        xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
-        if (t == 0) sxf[at * 8 + sb] = (float)xsum * dn;
-        if (lane == 0) inv2s[at] = dn;
+        unit_planes(v, lane, planes + at * 768, 96, sxf + at * 8, inv2s + at);
     }
 }
 

@@ -191,9 +191,12 @@ def test_a_second_model_does_not_disturb_a_captured_decode_step(gpu, oracle):
     eng.close()
 
 
-def test_mixed_quant_types_like_q4_k_m(gpu, oracle):
+@pytest.mark.parametrize("other", [12, 14])
+def test_mixed_quant_types_like_q4_k_m(gpu, oracle, other):
     """A "Q4_K_M" file keeps attn_v and ffn_down in Q6_K while q, k, o, gate and up are Q4_K: the three projections of a
-    layer then cannot be one matrix (three products per layer) and the Q6_K matrices run through the K-quant kernel.
+    layer then cannot be one matrix (three products per layer); the Q6_K matrices run through the int8 tensor-core kernel
+    for one to four tokens (fused norm, residual epilogue) and the plain-load kernel for the 8-token tiles of the prefill.
+    other = 14: every matrix is Q6_K (one fused q/k/v matrix, SiLU(gate) * up epilogue on Q6_K).
     Prefill (17 tokens: the unfused parts are interleaved into the q/k/v rows), decode and greedy tokens against the oracle."""
     from leafcutterllm_b200 import Engine, synth
     H, Fd, V, nh, nkv, L = 256, 512, 384, 2, 1, 2
@@ -213,9 +216,9 @@ def test_mixed_quant_types_like_q4_k_m(gpu, oracle):
     tensors = [("token_embd.weight", 12, (H, V)), ("output_norm.weight", 0, (H,)), ("output.weight", 14, (H, V))]
     for l in range(L):
         p = f"blk.{l}."
-        tensors += [(p + "attn_norm.weight", 0, (H,)), (p + "attn_q.weight", 12, (H, nh * hd)), (p + "attn_k.weight", 12, (H, nkv * hd)),
-                    (p + "attn_v.weight", 14, (H, nkv * hd)), (p + "attn_output.weight", 12, (nh * hd, H)), (p + "ffn_norm.weight", 0, (H,)),
-                    (p + "ffn_gate.weight", 12, (H, Fd)), (p + "ffn_up.weight", 12, (H, Fd)), (p + "ffn_down.weight", 14, (Fd, H))]
+        tensors += [(p + "attn_norm.weight", 0, (H,)), (p + "attn_q.weight", other, (H, nh * hd)), (p + "attn_k.weight", other, (H, nkv * hd)),
+                    (p + "attn_v.weight", 14, (H, nkv * hd)), (p + "attn_output.weight", other, (nh * hd, H)), (p + "ffn_norm.weight", 0, (H,)),
+                    (p + "ffn_gate.weight", other, (H, Fd)), (p + "ffn_up.weight", other, (H, Fd)), (p + "ffn_down.weight", 14, (Fd, H))]
     for name, typ, dims in tensors:
         n = int(np.prod(dims))
         data = np.ones(n, np.float32).view(np.uint8) if typ == 0 else (q6k(dims[1], dims[0]) if typ == 14 else synth.host_tensor(typ, 21, name, n))

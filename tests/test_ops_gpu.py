@@ -92,6 +92,10 @@ QM_CASES = [
     (13, 1, 512, 40), (14, 2, 512, 40), (20, 1, 128, 40), (0, 2, 100, 24), (1, 1, 100, 24),
     (13, 1, 4096, 300), (13, 5, 2816, 64), (13, 8, 256, 19), (14, 1, 4096, 300), (14, 3, 11008, 40), (14, 8, 768, 21),
     (20, 1, 4096, 300), (20, 2, 2816, 33), (0, 3, 512, 40), (1, 1, 4096, 300), (1, 8, 256, 19), (1, 2, 11008, 33),
+    # Q6_K on the int8 tensor-core kernel (a multiple of 16 rows, one to four tokens): one unit, an odd number of units (every
+    # other row's blocks then start two bytes off a word), more units than warps, several tiles per CTA
+    (14, 1, 256, 16), (14, 1, 4096, 4096), (14, 1, 11008, 4096), (14, 2, 2816, 64), (14, 3, 11008, 48), (14, 4, 768, 160), (14, 4, 8192, 32),
+    (14, 1, 4096, 32000),
 ]
 
 
