@@ -52,6 +52,7 @@ static inline int unit_bytes_of(uint32_t typ) {
         case LC_TYPE_Q4_K: return 144;
         case LC_TYPE_Q4_0: return 144;  // 8 blocks of 18 B
         case LC_TYPE_Q8_0: return 272;  // 8 blocks of 34 B
+        case LC_TYPE_Q5_K: return 176;
         default: return 0;
     }
 }
@@ -595,13 +596,16 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
     if (a.epi == EPI_ADD_RESIDUAL) LC_CHECK(a.residual, LC_ERR_INVALID, "qgemv: residual missing");
     bool tma_ok = a.w->has_tmap && (a.epi != EPI_SILU_MUL || a.w2->has_tmap);
     static const bool force_fp32 = getenv("LC_GEMV_FP32") != nullptr;
-    if (tma_ok && (a.w->typ == LC_TYPE_Q4_K || ((a.w->typ == LC_TYPE_Q4_0 || a.w->typ == LC_TYPE_Q8_0) && a.w->k % kUnitElems == 0)) && !force_fp32) {
+    static const bool q5k_plain = getenv("LC_GEMV_Q5K_PLAIN") != nullptr;
+    const bool f32_types = a.w->typ == LC_TYPE_Q4_K || a.w->typ == LC_TYPE_Q4_0 || a.w->typ == LC_TYPE_Q8_0;  // types qgemv_tma_kernel knows
+    if (tma_ok && (a.w->typ == LC_TYPE_Q4_K || (a.w->typ == LC_TYPE_Q5_K && !q5k_plain) ||
+                   ((a.w->typ == LC_TYPE_Q4_0 || a.w->typ == LC_TYPE_Q8_0) && a.w->k % kUnitElems == 0)) && !force_fp32) {
         bool launched = false;
         LC_TRY(launch_qgemv_mma_q4k(a, s, &launched));
         if (launched) return LC_OK;
     }
     LC_CHECK(a.push == nullptr, LC_ERR_STATE, "qgemv: rows cannot leave as tagged words from this kernel (qgemv_push_supported was not asked)");
-    if (tma_ok) {
+    if (tma_ok && f32_types) {
         for (int mt = round_m(a.m); mt >= 1; mt >>= 1) {
             // the kernel handles mt tokens per pass; when shared memory cannot hold round_m(m) token
             // vectors the caller's m is split further below

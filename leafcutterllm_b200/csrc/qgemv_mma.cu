@@ -40,6 +40,9 @@ __device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
+// bytes of a row's 256 weights
+__host__ __device__ constexpr int mma_unit_bytes(uint32_t typ) { return typ == LC_TYPE_Q8_0 ? 272 : (typ == LC_TYPE_Q5_K ? 176 : 144); }
+
 __device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *reinterpret_cast<const uint32_t*>(p); }
 __device__ __forceinline__ int byte_of(uint32_t w, int j) { return (int)((w >> (8 * j)) & 0xFFu); }
 
@@ -64,10 +67,12 @@ __device__ __forceinline__ int plane_off(int unit, int sb, int tok, int plane) {
 // offset -8 d sum(x) is shared out over the four threads of a row like the min term of Q4_K.
 // TYPE = LC_TYPE_Q8_0: eight 34-byte blocks = 272 bytes per 256 weights; a block is one s8 x s8 MMA (the weights are the
 // signed bytes themselves, mod.rs:47-49), no offset.
+// TYPE = LC_TYPE_Q5_K: a Q4_K block with the elements' fifth bits between the header and the nibbles (176 bytes; bit s of
+// qh[l] belongs to element l of sub-block s, mod.rs:101-143): the A bytes are nibble | bit << 4, high nibbles moved down.
 template <int M, int WARPS, int STAGES, bool GROUPED = false, uint32_t TYPE = LC_TYPE_Q4_K>
 __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 8 && M <= 2) ? 2 : 1)
 qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1, GemvParams p, GemvGroupParams gp) {
-    constexpr int UB = TYPE == LC_TYPE_Q8_0 ? 272 : 144;  // bytes of a row's 256 weights
+    constexpr int UB = mma_unit_bytes(TYPE);  // bytes of a row's 256 weights
     const CUtensorMap* t0p = &tm0;
     const CUtensorMap* t1p = &tm1;
     int m_act = p.m;
@@ -475,7 +480,15 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                     unpack_scales_k4(hA.y, hA.z, hA.w, &scA[0], &scA[1], &mnA[0], &mnA[1]);
                     unpack_scales_k4(hB.y, hB.z, hB.w, &scB[0], &scB[1], &mnB[0], &mnB[1]);
                     // one int32 accumulator per C element: low-nibble products are scaled by 16*sc, high-nibble
-                    // products (which carry a factor 16 because the nibble stays in place) by sc
+                    // products (which carry a factor 16 because the nibble stays in place) by sc; Q5_K moves the high
+                    // nibbles down to make room for the fifth bit, and both kinds are scaled by sc
+                    constexpr bool Q5 = TYPE == LC_TYPE_Q5_K;
+                    constexpr int QS = Q5 ? 48 : 16;  // where the nibbles start
+                    uint32_t qhA0 = 0, qhA1 = 0, qhB0 = 0, qhB1 = 0;  // fifth bits of elements 4t .. 4t + 3 and 16 + 4t .. of every sub-block
+                    if constexpr (Q5) {
+                        qhA0 = lds32(rowA + 16 + 4 * t); qhA1 = lds32(rowA + 32 + 4 * t);
+                        qhB0 = lds32(rowB + 16 + 4 * t); qhB1 = lds32(rowB + 32 + 4 * t);
+                    }
                     int acc[NPAIR][4];
 #pragma unroll
                     for (int pr = 0; pr < NPAIR; pr++)
@@ -483,14 +496,29 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
                         for (int j = 0; j < 4; j++) acc[pr][j] = 0;
 #pragma unroll
                     for (int grp = 0; grp < 4; grp++) {
-                        const uint32_t wA0 = lds32(rowA + 16 + 32 * grp + 4 * t), wA1 = lds32(rowA + 32 + 32 * grp + 4 * t);
-                        const uint32_t wB0 = lds32(rowB + 16 + 32 * grp + 4 * t), wB1 = lds32(rowB + 32 + 32 * grp + 4 * t);
+                        const uint32_t wA0 = lds32(rowA + QS + 32 * grp + 4 * t), wA1 = lds32(rowA + QS + 16 + 32 * grp + 4 * t);
+                        const uint32_t wB0 = lds32(rowB + QS + 32 * grp + 4 * t), wB1 = lds32(rowB + QS + 16 + 32 * grp + 4 * t);
                         const uint32_t swA = scA[grp >> 1], swB = scB[grp >> 1];
                         const int jl = (2 * grp) & 3;  // byte of the even sub-block in the packed scale word (0 or 2)
-                        const int sAl = (int)((jl ? (swA >> 12) : (swA << 4)) & 0xFF0u), sAh = (int)__byte_perm(swA, 0, 0x4440 + jl + 1);
-                        const int sBl = (int)((jl ? (swB >> 12) : (swB << 4)) & 0xFF0u), sBh = (int)__byte_perm(swB, 0, 0x4440 + jl + 1);
-                        const uint32_t a0 = wA0 & 0x0F0F0F0Fu, a1 = wB0 & 0x0F0F0F0Fu, a2 = wA1 & 0x0F0F0F0Fu, a3 = wB1 & 0x0F0F0F0Fu;
-                        const uint32_t h0 = wA0 & 0xF0F0F0F0u, h1 = wB0 & 0xF0F0F0F0u, h2 = wA1 & 0xF0F0F0F0u, h3 = wB1 & 0xF0F0F0F0u;
+                        const int sAh = (int)__byte_perm(swA, 0, 0x4440 + jl + 1), sBh = (int)__byte_perm(swB, 0, 0x4440 + jl + 1);
+                        int sAl, sBl;
+                        uint32_t a0, a1, a2, a3, h0, h1, h2, h3;
+                        if constexpr (Q5) {
+                            sAl = (int)__byte_perm(swA, 0, 0x4440 + jl);
+                            sBl = (int)__byte_perm(swB, 0, 0x4440 + jl);
+                            // bit 2 grp (low nibbles' sub-block) and bit 2 grp + 1 (high nibbles') of every qh byte, moved to bit 4
+                            auto lo5 = [&](uint32_t q) { return (grp < 2 ? (q << (4 - 2 * grp)) : (q >> (2 * grp - 4))) & 0x10101010u; };
+                            auto hi5 = [&](uint32_t q) { return (grp < 2 ? (q << (3 - 2 * grp)) : (q >> (2 * grp - 3))) & 0x10101010u; };
+                            a0 = (wA0 & 0x0F0F0F0Fu) | lo5(qhA0); a1 = (wB0 & 0x0F0F0F0Fu) | lo5(qhB0);
+                            a2 = (wA1 & 0x0F0F0F0Fu) | lo5(qhA1); a3 = (wB1 & 0x0F0F0F0Fu) | lo5(qhB1);
+                            h0 = ((wA0 >> 4) & 0x0F0F0F0Fu) | hi5(qhA0); h1 = ((wB0 >> 4) & 0x0F0F0F0Fu) | hi5(qhB0);
+                            h2 = ((wA1 >> 4) & 0x0F0F0F0Fu) | hi5(qhA1); h3 = ((wB1 >> 4) & 0x0F0F0F0Fu) | hi5(qhB1);
+                        } else {
+                            sAl = (int)((jl ? (swA >> 12) : (swA << 4)) & 0xFF0u);
+                            sBl = (int)((jl ? (swB >> 12) : (swB << 4)) & 0xFF0u);
+                            a0 = wA0 & 0x0F0F0F0Fu; a1 = wB0 & 0x0F0F0F0Fu; a2 = wA1 & 0x0F0F0F0Fu; a3 = wB1 & 0x0F0F0F0Fu;
+                            h0 = wA0 & 0xF0F0F0F0u; h1 = wB0 & 0xF0F0F0F0u; h2 = wA1 & 0xF0F0F0F0u; h3 = wB1 & 0xF0F0F0F0u;
+                        }
 #pragma unroll
                         for (int pr = 0; pr < NPAIR; pr++) {
                             int c[4];
@@ -674,7 +702,7 @@ static size_t mma_smem_bytes(int k, bool grouped = false, int unit_bytes = 144) 
 template <int M, int WARPS, int STAGES, bool GROUPED = false, uint32_t TYPE = LC_TYPE_Q4_K>
 static int32_t launch_mma_cfg(const GemvArgs& a, cudaStream_t s) {
     auto kern = qgemv_mma_q4k_kernel<M, WARPS, STAGES, GROUPED, TYPE>;
-    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k, GROUPED, TYPE == LC_TYPE_Q8_0 ? 272 : 144);
+    size_t smem = mma_smem_bytes<M, WARPS, STAGES>(a.w->k, GROUPED, mma_unit_bytes(TYPE));
     LC_CUDA(ensure_smem_limit((const void*)kern, kMaxSmem));
     GemvParams p;
     p.x = a.x; p.out = a.out; p.residual = a.residual; p.norm_w = a.norm_w; p.eps = a.eps;
@@ -714,7 +742,7 @@ template <int M, uint32_t TYPE = LC_TYPE_Q4_K>
 static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = true;
     int k = a.w->k;
-    constexpr int ub = TYPE == LC_TYPE_Q8_0 ? 272 : 144;
+    constexpr int ub = mma_unit_bytes(TYPE);
     if constexpr (M <= 4) {  // wider token tiles need more than 128 registers per thread: 8 warps
         if (mma_smem_bytes<M, 16, 2>(k, false, ub) <= kMaxSmem) return launch_mma_cfg<M, 16, 2, false, TYPE>(a, s);
     }
@@ -763,6 +791,12 @@ int32_t launch_qgemv_mma_q4k(const GemvArgs& a, cudaStream_t s, bool* launched) 
         if (a.m <= 2) return launch_mma_m<2, LC_TYPE_Q8_0>(a, s, launched);
         if (a.m <= 4) return launch_mma_m<4, LC_TYPE_Q8_0>(a, s, launched);
         return LC_OK;
+    }
+    if (a.w->typ == LC_TYPE_Q5_K) {
+        if (a.m <= 1) return launch_mma_m<1, LC_TYPE_Q5_K>(a, s, launched);
+        if (a.m <= 2) return launch_mma_m<2, LC_TYPE_Q5_K>(a, s, launched);
+        if (a.m <= 4) return launch_mma_m<4, LC_TYPE_Q5_K>(a, s, launched);
+        return LC_OK;  // wider token tiles stay with the plain-load kernel
     }
     if (a.m <= 1) return launch_mma_m<1>(a, s, launched);
     if (a.m <= 2) return launch_mma_m<2>(a, s, launched);

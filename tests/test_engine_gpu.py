@@ -191,12 +191,13 @@ def test_a_second_model_does_not_disturb_a_captured_decode_step(gpu, oracle):
     eng.close()
 
 
-@pytest.mark.parametrize("other", [12, 14])
+@pytest.mark.parametrize("other", [12, 13, 14])
 def test_mixed_quant_types_like_q4_k_m(gpu, oracle, other):
     """A "Q4_K_M" file keeps attn_v and ffn_down in Q6_K while q, k, o, gate and up are Q4_K: the three projections of a
     layer then cannot be one matrix (three products per layer); the Q6_K matrices run through the int8 tensor-core kernel
     for one to four tokens (fused norm, residual epilogue) and the plain-load kernel for the 8-token tiles of the prefill.
-    other = 14: every matrix is Q6_K (one fused q/k/v matrix, SiLU(gate) * up epilogue on Q6_K).
+    other = 14: every matrix is Q6_K (one fused q/k/v matrix, SiLU(gate) * up epilogue on Q6_K); other = 13: the Q5_K + Q6_K
+    mix of a "Q5_K_M" file (Q5_K through the Q4_K kernel's fifth-bit variant).
     Prefill (17 tokens: the unfused parts are interleaved into the q/k/v rows), decode and greedy tokens against the oracle."""
     from leafcutterllm_b200 import Engine, synth
     H, Fd, V, nh, nkv, L = 256, 512, 384, 2, 1, 2
@@ -210,6 +211,14 @@ def test_mixed_quant_types_like_q4_k_m(gpu, oracle, other):
         raw[:, 209] = d >> 8
         return raw.ravel()
 
+    def q5k(rows, cols):  # random blocks: 6-bit scales and mins as they come, small d and dmin
+        raw = r.integers(0, 256, (rows * cols // 256, 176), dtype=np.uint8)
+        for at in (0, 2):
+            d = np.float16(r.uniform(2e-5, 2e-4, raw.shape[0])).view(np.uint16)
+            raw[:, at] = d & 0xFF
+            raw[:, at + 1] = d >> 8
+        return raw.ravel()
+
     eng = Engine(H, L, nh, nkv, Fd, V, max_seq_len=64)
     om = oracle.OracleModel(H, L, nh, nkv, Fd, V, max_seq_len=64)
     hd = H // nh
@@ -221,7 +230,7 @@ def test_mixed_quant_types_like_q4_k_m(gpu, oracle, other):
                     (p + "ffn_gate.weight", other, (H, Fd)), (p + "ffn_up.weight", other, (H, Fd)), (p + "ffn_down.weight", 14, (Fd, H))]
     for name, typ, dims in tensors:
         n = int(np.prod(dims))
-        data = np.ones(n, np.float32).view(np.uint8) if typ == 0 else (q6k(dims[1], dims[0]) if typ == 14 else synth.host_tensor(typ, 21, name, n))
+        data = np.ones(n, np.float32).view(np.uint8) if typ == 0 else (q6k(dims[1], dims[0]) if typ == 14 else (q5k(dims[1], dims[0]) if typ == 13 else synth.host_tensor(typ, 21, name, n)))
         eng.set_tensor(name, typ, dims, data)
         om.set_tensor(name, typ, list(dims), data)
     eng.finalize()

@@ -96,6 +96,8 @@ QM_CASES = [
     # other row's blocks then start two bytes off a word), more units than warps, several tiles per CTA
     (14, 1, 256, 16), (14, 1, 4096, 4096), (14, 1, 11008, 4096), (14, 2, 2816, 64), (14, 3, 11008, 48), (14, 4, 768, 160), (14, 4, 8192, 32),
     (14, 1, 4096, 32000),
+    # Q5_K on the Q4_K kernel's fifth-bit variant (one to four tokens)
+    (13, 1, 11008, 4096), (13, 2, 2816, 77), (13, 3, 11008, 40), (13, 4, 4096, 33), (13, 1, 256, 8),
 ]
 
 
