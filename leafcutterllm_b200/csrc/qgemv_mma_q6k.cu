@@ -3,9 +3,12 @@
 //   y[t, r] = sum_k x[t, k] * w[r, k],   w = d * sc[k / 16] * (q - 32)      (rust/src/kernels/mod.rs:145-180)
 //
 // The arithmetic of the Q4_K kernel: the activations of a 256-element unit become 24-bit fixed point in three balanced
-// byte planes, the 6-bit weights minus 32 are signed bytes, and a 16-element sub-block (one int8 scale) is one
-// mma.sync m16n8k16 s8 x s8 -> s32 with 16 weight rows as A and the planes of up to two tokens as the B columns.  The
-// int8 scales multiply the int32 sums as integers; d and 2^-s are applied once per unit in f32.
+// byte planes, the 6-bit weights are unsigned bytes, and a 16-element sub-block (one int8 scale) is one
+// mma.sync m16n8k16 u8 x s8 -> s32 with 16 weight rows as A and the planes of up to two tokens as the B columns.  The
+// int8 scales multiply the int32 sums as integers; d and 2^-s are applied once per unit in f32.  The offset,
+//   sum_sub sc[sub] * sum_k (q - 32) P[k] = sum_sub sc[sub] * (sum_k q P[k])  -  32 * sum_sub sc[sub] * S[sub],   S = sum of P over the sub-block,
+// is a product of its own: the sixteen scales of a row are the A bytes of one more MMA against the sub-block sums of
+// every plane (|S| <= 2048: two balanced byte digits, two MMAs per unit), written once per unit beside the planes.
 //
 // Data path.  A Q6_K block has 210 bytes, so nothing of a row is 16-byte aligned and no tensor-map box describes a
 // [unit x rows] tile.  A warp owns a unit of k; per 16-row tile it copies, for every row, the fourteen 16-byte pieces that
@@ -30,11 +33,15 @@ constexpr int kRows = 16;                       // rows per tile: one MMA row gr
 constexpr int kPieces = 14;                     // 16-byte pieces per row and unit: the block plus its offset from a 16-byte boundary (<= 14)
 constexpr int kPitch = 240;                     // bytes between the rows of a stage (60 words: eight rows start in eight different banks)
 constexpr int kStageBytes = kRows * kPitch;
-constexpr int kCopies = kRows * kPieces / 32;   // pieces per lane and tile
-static_assert(kRows * kPieces % 32 == 0, "a tile's pieces are dealt evenly to the lanes");
+static_assert(2 * kPieces <= 32 && kRows % 2 == 0, "a warp instruction copies the pieces of two rows");
 
 __device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
                  : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                  : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
 }
@@ -50,7 +57,13 @@ __device__ __forceinline__ uint32_t lds32(const unsigned char* p) { return *rein
 __device__ __forceinline__ uint32_t block_word(const unsigned char* base, int sh, int o) {
     return __funnelshift_r(lds32(base + o), lds32(base + o + 4), sh);
 }
-__device__ __forceinline__ int sbyte(uint32_t w, int b) { return ((int)(w << (24 - 8 * b))) >> 24; }
+// byte b of w, sign extended: a byte permute whose selector asks for the byte's sign in the three upper positions
+__device__ __forceinline__ int sbyte(uint32_t w, int b) {
+    uint32_t r;
+    const uint32_t sel = ((8u | b) << 12) | ((8u | b) << 8) | ((8u | b) << 4) | (uint32_t)b;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0), "r"(sel));
+    return (int)r;
+}
 
 // planes of one unit: [sub-block 8][token M][plane 3][32 bytes]
 template <int M>
@@ -77,6 +90,8 @@ qgemv_mma_q6k_kernel(const unsigned char* __restrict__ w0, const unsigned char* 
     size_t off = (size_t)WARPS * STAGES * kStageBytes;
     unsigned char* planes = smem + off;                       // [nunits][8][M][3][32] int8
     off += (size_t)nunits * 8 * M * 96;
+    unsigned char* ssum = smem + off;                         // [nunits][token pair][digit 2][column 8][sub-block 16] int8
+    off += (size_t)nunits * NPAIR * 256;
     float* inv2s = reinterpret_cast<float*>(smem + off);      // [nunits][M]: 2^-s
     off += (size_t)nunits * M * 4;
     float* red = reinterpret_cast<float*>(smem + off);        // [2][WARPS][M][16]
@@ -96,16 +111,20 @@ qgemv_mma_q6k_kernel(const unsigned char* __restrict__ w0, const unsigned char* 
     // producer cursor: the next job to request (all lanes; every call commits one group, an empty one past the last job,
     // so that "all but the newest STAGES - 1 groups" always means "the job about to be read")
     int pj = 0, p_ti = 0, p_mat = 0, p_ui = 0, p_st = 0;
+    const int c_row = lane >= kPieces ? 1 : 0, c_piece = lane - kPieces * c_row;
     auto issue_next = [&]() {
         if (pj < njobs) {
             const unsigned char* wm = p_mat ? w1 : w0;
             const size_t b0 = job_start(p_ti, p_ui);
-            const uint32_t dst0 = smem_u32(stage_base + (size_t)p_st * kStageBytes);
+            // two rows per instruction: lanes 0-13 the pieces of an even row, lanes 14-27 those of the next
+            if (lane < 2 * kPieces) {
+                const uint32_t dst0 = smem_u32(stage_base + (size_t)p_st * kStageBytes) + (uint32_t)(c_row * kPitch + 16 * c_piece);
+                size_t at = b0 + (size_t)c_row * row_bytes;
 #pragma unroll
-            for (int i = 0; i < kCopies; i++) {
-                const int id = i * 32 + lane, rr = id / kPieces, c = id - rr * kPieces;
-                const size_t src = ((b0 + (size_t)rr * row_bytes) & ~(size_t)15) + (size_t)(16 * c);
-                if (src < total) cp_async16(dst0 + (uint32_t)(rr * kPitch + 16 * c), wm + src);
+                for (int i = 0; i < kRows / 2; i++, at += 2 * row_bytes) {
+                    const size_t src = (at & ~(size_t)15) + (size_t)(16 * c_piece);
+                    if (src < total) cp_async16(dst0 + (uint32_t)(2 * i * kPitch), wm + src);
+                }
             }
             pj++;
             if (++p_st == STAGES) p_st = 0;
@@ -165,6 +184,20 @@ qgemv_mma_q6k_kernel(const unsigned char* __restrict__ w0, const unsigned char* 
             }
             unit_planes(v, lane, planes + plane_off<M>(unit, 0, tk, 0), M * 96, nullptr, inv2s + unit * M + tk);
         }
+        __syncwarp();
+        // the sums of every plane over the sixteen 16-element sub-blocks, as two balanced byte digits: column 3 (tk & 1) + plane
+        // of pair tk / 2; columns 6 and 7 stay unread
+        for (int i = lane; i < M * 3 * 16; i += 32) {
+            const int tk = i / 48, pl = (i >> 4) % 3, is = i & 15;
+            const uint32_t* pp = reinterpret_cast<const uint32_t*>(planes + plane_off<M>(unit, is >> 1, tk, pl) + 16 * (is & 1));
+            int sum = 0;
+#pragma unroll
+            for (int q = 0; q < 4; q++) sum = __dp4a((int)pp[q], 0x01010101, sum);
+            const int lo = (int)(signed char)sum, hi = (sum - lo) >> 8;
+            unsigned char* sp = ssum + (size_t)(unit * NPAIR + (tk >> 1)) * 256 + (3 * (tk & 1) + pl) * 16 + is;
+            sp[0] = (unsigned char)lo;
+            sp[128] = (unsigned char)hi;
+        }
     }
     __syncwarp();
 
@@ -176,7 +209,7 @@ qgemv_mma_q6k_kernel(const unsigned char* __restrict__ w0, const unsigned char* 
     const int bcol_tok = (g >= 3) ? 1 : 0, bcol_pl = (g >= 3) ? g - 3 : g;
 
     // B fragments of a unit: per 32-element sub-block the plane bytes of elements 4t .. 4t + 3 and 16 + 4t ..
-    uint32_t bf[NPAIR][8][2];
+    uint32_t bf[NPAIR][8][2], bs[NPAIR][2];  // bs: the two digits of the sums of sub-blocks 4t .. 4t + 3 in this thread's column
     float isv[M];
     auto load_unit_consts = [&](int unit) {
 #pragma unroll
@@ -190,6 +223,10 @@ qgemv_mma_q6k_kernel(const unsigned char* __restrict__ w0, const unsigned char* 
                 bf[pr][sb][0] = colv ? v0 : 0u;
                 bf[pr][sb][1] = colv ? v1 : 0u;
             }
+            const unsigned char* sp = ssum + (size_t)(unit * NPAIR + pr) * 256 + (colv ? g : 0) * 16 + 4 * t;
+            const uint32_t s0 = lds32(sp), s1 = lds32(sp + 128);
+            bs[pr][0] = colv ? s0 : 0u;
+            bs[pr][1] = colv ? s1 : 0u;
         }
 #pragma unroll
         for (int tk = 0; tk < M; tk++) isv[tk] = inv2s[unit * M + tk];
@@ -242,19 +279,28 @@ qgemv_mma_q6k_kernel(const unsigned char* __restrict__ w0, const unsigned char* 
                             const uint32_t loA = (qlA[c] >> (4 * (j >> 1))) & 0x0F0F0F0Fu, loB = (qlB[c] >> (4 * (j >> 1))) & 0x0F0F0F0Fu;
                             const uint32_t hiA = (j < 2 ? (qhA[h] << (4 - 2 * j)) : (qhA[h] >> (2 * j - 4))) & 0x30303030u;
                             const uint32_t hiB = (j < 2 ? (qhB[h] << (4 - 2 * j)) : (qhB[h] >> (2 * j - 4))) & 0x30303030u;
-                            // q - 32 as a signed byte: q + 96 stays below 256 (no carry between bytes), and flipping bit 7 subtracts 128 mod 256
-                            const uint32_t a0 = ((loA | hiA) + 0x60606060u) ^ 0x80808080u;
-                            const uint32_t a1 = ((loB | hiB) + 0x60606060u) ^ 0x80808080u;
+                            const uint32_t a0 = loA | hiA, a1 = loB | hiB;  // q, 0 .. 63
                             const int is = 8 * n + 2 * j + h;
                             const int sA = sbyte(scA[is >> 2], is & 3), sB = sbyte(scB[is >> 2], is & 3);
 #pragma unroll
                             for (int pr = 0; pr < NPAIR; pr++) {
                                 int cc[4];
-                                mma_s8s8_k16(cc, a0, a1, bf[pr][4 * n + j][h]);
+                                mma_u8s8_k16(cc, a0, a1, bf[pr][4 * n + j][h]);
                                 acc[pr][0] += sA * cc[0]; acc[pr][1] += sA * cc[1]; acc[pr][2] += sB * cc[2]; acc[pr][3] += sB * cc[3];
                             }
                         }
                     }
+                }
+                // ---- the offset: -32 sum_sub sc[sub] S[sub]; this thread's A bytes are the scales of sub-blocks 4t .. 4t + 3 ----
+                const uint32_t sa = t == 0 ? scA[0] : (t == 1 ? scA[1] : (t == 2 ? scA[2] : scA[3]));
+                const uint32_t sb_ = t == 0 ? scB[0] : (t == 1 ? scB[1] : (t == 2 ? scB[2] : scB[3]));
+#pragma unroll
+                for (int pr = 0; pr < NPAIR; pr++) {
+                    int c0[4], c1[4];
+                    mma_s8s8_k16(c0, sa, sb_, bs[pr][0]);
+                    mma_s8s8_k16(c1, sa, sb_, bs[pr][1]);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[pr][j] -= 32 * (c0[j] + 256 * c1[j]);
                 }
                 // ---- fold planes and scales into this thread's f32 partial row sums ----
 #pragma unroll
@@ -322,7 +368,7 @@ template <int M, int WARPS, int STAGES>
 size_t q6k_smem_bytes(int k) {
     const int nunits = k / kUnitElems;
     size_t b = (size_t)WARPS * STAGES * kStageBytes;
-    b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * M * 4;
+    b += (size_t)nunits * 8 * M * 96 + (size_t)nunits * ((M + 1) / 2) * 256 + (size_t)nunits * M * 4;
     b += (size_t)2 * WARPS * M * kRows * 4 + (size_t)M * kRows * 4 + (size_t)(32 + M) * 4;
     return b;
 }
