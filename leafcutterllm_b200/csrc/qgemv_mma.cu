@@ -198,11 +198,9 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
         }
         ss = warp_sum(ss);
         if (lane == 0) scratch[warp] = ss;
-        __syncthreads();
-        float r = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; w++) r += scratch[w];  // every thread, same order
-        rms0 = 1.0f / sqrtf(r / (float)p.k + p.eps);
+        // No barrier here: the planes are those of x * gain, and the RMS factor -- one scalar for the whole row -- multiplies
+        // the finished row sums behind the barrier of the cross-warp reduction, where every warp's part of the sum of
+        // squares is visible.  A unit's power-of-two scale follows its own largest magnitude, so it does not care.
     } else if (!GROUPED && p.norm_w) {
         for (int tk = 0; tk < M; tk++) {
             float ss = 0.f;
@@ -583,9 +581,13 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
             __syncthreads();
             if (warp < M) {
                 const int tk = warp;
-                float y = 0.f;
+                float y = 0.f, ssq = 0.f;
 #pragma unroll 4
-                for (int w = 0; w < WARPS; w++) y += rb[(w * M + tk) * 32 + lane];
+                for (int w = 0; w < WARPS; w++) {
+                    y += rb[(w * M + tk) * 32 + lane];
+                    if (one_pass) ssq += scratch[w];  // same order in every thread and CTA
+                }
+                if (one_pass) y *= 1.0f / sqrtf(ssq / (float)p.k + p.eps);  // cpu.rs:52-55
                 const int row = lane < TR ? tile * TR + lane : p.n;  // lanes past the tile's rows hold nothing
                 bool have = false;
                 if (p.epi == EPI_SILU_MUL) {
