@@ -19,26 +19,24 @@ __device__ __forceinline__ void unit_planes(const float (&v)[8], int lane, unsig
     const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
     const int s = max(-100, min(100, 22 - ex));  // |x| * 2^s < 2^22
     const float up = __uint_as_float((uint32_t)(127 + s) << 23), dn = __uint_as_float((uint32_t)(127 - s) << 23);
-    // a digit is the sign-extended low byte of what is left, so the byte to store is simply that low byte
+    // The digits are the bytes of X + 0x808080 with their top bits flipped: that sum is b0 + 256 b1 + 65536 b2 with unsigned
+    // bytes, so X = (b0 - 128) + 256 (b1 - 128) + 65536 (b2 - 128), and b - 128 as a signed byte is b ^ 0x80.
     uint32_t pw[3][2];
     int xsum = 0;
-    int d0[8], d1[8], d2[8];
+    uint32_t y[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         float sv = v[j] * up;
         sv = fminf(fmaxf(sv, -4194304.f), 4194304.f);
         const int X = __float2int_rn(sv);
         xsum += X;
-        d0[j] = X;
-        d1[j] = (X - (int)(signed char)X) >> 8;
-        d2[j] = (d1[j] - (int)(signed char)d1[j]) >> 8;
+        y[j] = (uint32_t)(X + 0x808080) ^ 0x808080u;
     }
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        pw[0][h] = __byte_perm(__byte_perm(d0[4 * h], d0[4 * h + 1], 0x0040), __byte_perm(d0[4 * h + 2], d0[4 * h + 3], 0x0040), 0x5410);
-        pw[1][h] = __byte_perm(__byte_perm(d1[4 * h], d1[4 * h + 1], 0x0040), __byte_perm(d1[4 * h + 2], d1[4 * h + 3], 0x0040), 0x5410);
-        pw[2][h] = __byte_perm(__byte_perm(d2[4 * h], d2[4 * h + 1], 0x0040), __byte_perm(d2[4 * h + 2], d2[4 * h + 3], 0x0040), 0x5410);
-    }
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+        for (int pl = 0; pl < 3; pl++)  // byte pl of four consecutive elements
+            pw[pl][h] = __byte_perm(__byte_perm(y[4 * h], y[4 * h + 1], 0x0040 + 0x11 * pl), __byte_perm(y[4 * h + 2], y[4 * h + 3], 0x0040 + 0x11 * pl), 0x5410);
     const int sb = lane >> 2, inner = (8 * lane) & 31;
 #pragma unroll
     for (int pl = 0; pl < 3; pl++) *reinterpret_cast<uint2*>(dst + sb * sb_stride + pl * 32 + inner) = make_uint2(pw[pl][0], pw[pl][1]);

@@ -255,43 +255,7 @@ qgemv_mma_q4k_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 8; j++) v[j] = 0.f;
             }
-            float amax = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
-            amax = warp_max(amax);
-            // amax = f * 2^ex with f in [0.5, 1): ex from the exponent field (zero, denormal and non-finite inputs fall into the clamp)
-            const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
-            const int s = max(-100, min(100, 22 - ex));                   // |x| * 2^s < 2^22
-            const float up = __uint_as_float((uint32_t)(127 + s) << 23), dn = __uint_as_float((uint32_t)(127 - s) << 23);
-            // balanced base-256 digits X = P0 + 256 P1 + 65536 P2, each in [-128, 127]: a digit is the sign-extended low byte
-            // of what is left, so the byte to store is simply that low byte; four of them are gathered with byte permutes
-            uint32_t pw[3][2];
-            int xsum = 0;
-            int d0[8], d1[8], d2[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-                float sv = v[j] * up;
-                sv = fminf(fmaxf(sv, -4194304.f), 4194304.f);             // NaN / Inf inputs do not reach here as finite work
-                const int X = __float2int_rn(sv);
-                xsum += X;
-                d0[j] = X;
-                d1[j] = (X - (int)(signed char)X) >> 8;
-                d2[j] = (d1[j] - (int)(signed char)d1[j]) >> 8;
-            }
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                pw[0][h] = __byte_perm(__byte_perm(d0[4 * h], d0[4 * h + 1], 0x0040), __byte_perm(d0[4 * h + 2], d0[4 * h + 3], 0x0040), 0x5410);
-                pw[1][h] = __byte_perm(__byte_perm(d1[4 * h], d1[4 * h + 1], 0x0040), __byte_perm(d1[4 * h + 2], d1[4 * h + 3], 0x0040), 0x5410);
-                pw[2][h] = __byte_perm(__byte_perm(d2[4 * h], d2[4 * h + 1], 0x0040), __byte_perm(d2[4 * h + 2], d2[4 * h + 3], 0x0040), 0x5410);
-            }
-            const int sb = lane >> 2, inner = (8 * lane) & 31;
-#pragma unroll
-            for (int pl = 0; pl < 3; pl++)
-                *reinterpret_cast<uint2*>(planes + plane_off<M>(unit, sb, tk, pl) + inner) = make_uint2(pw[pl][0], pw[pl][1]);
-            xsum += __shfl_xor_sync(0xffffffffu, xsum, 1);
-            xsum += __shfl_xor_sync(0xffffffffu, xsum, 2);
-            if (t == 0) sxf[(unit * M + tk) * 8 + sb] = (float)xsum * dn;
-            if (lane == 0) inv2s[unit * M + tk] = dn;
+            unit_planes(v, lane, planes + plane_off<M>(unit, 0, tk, 0), M * 96, sxf + (unit * M + tk) * 8, inv2s + unit * M + tk);
         }
     }
     __syncwarp();
