@@ -236,6 +236,32 @@ def tiny_decode(lc, synth, local: int, steps: int = 128, warm: int = 3) -> dict:
             "frac": round(algo / (per_step * 1e-3) / 1e9 / peak, 4), "peak_source": which, "gpu_launches": int(ctr["kernel_launches"])}
 
 
+def q4km_decode(lc, synth, local: int, prompt_len: int = PROMPT_LEN, steps: int = 64, warm: int = 3, layers: int = 0) -> dict:
+    """The bench workload with the type mix of a "Q4_K_M" file instead of Q4_K throughout: Q6_K head, Q6_K attn_v and ffn_down
+    in 16 of the 32 layers (synth.ModelSpec.mixed_type), so q/k/v run as three products in those layers.  Batch 1,
+    2048-token seeded prompt, greedy decode steps (CUDA events around the graph replays)."""
+    spec = synth.LLAMA7B_Q4KM if layers <= 0 else synth.LLAMA7B_Q4KM.with_layers(layers)
+    eng = synth.build_engine(spec, prompt_len + warm + steps + 16, on_device=True, device=local)
+    prompt = synth.prompt_tokens(prompt_len, spec.vocab_size, 0)
+    t0 = time.perf_counter()
+    _, nxt = eng.forward_batch([0], [prompt.tolist()], want_logits=False)
+    t_prefill = time.perf_counter() - t0
+    toks, _ = eng.decode_loop([0], nxt, warm)
+    eng.reset_counters()
+    toks, ms = eng.decode_loop([0], toks[-1].tolist(), steps)
+    ctr = eng.counters()
+    eng.close()
+    peak, which = measured_peaks()
+    algo = ctr["algo_bytes_last_step"]
+    per_step = ms / steps
+    n_q6 = sum(1 for l in range(spec.num_layers) if spec.mixed_type(l, "down") == 14)
+    return {"workload": f"Llama-2-7B shape with the Q4_K_M type mix (Q6_K head, Q6_K attn_v and ffn_down in {n_q6} of {spec.num_layers} layers, Q4_K "
+                        f"elsewhere), batch 1, {prompt_len}-token seeded prompt, greedy decode",
+            "value": round(steps / (ms * 1e-3), 1), "unit": "tok/s", "ms_per_step": round(per_step, 4), "steps": steps, "prefill_s": round(t_prefill, 3),
+            "algorithmic_bytes_per_step": int(algo), "achieved_gbs": round(algo / (per_step * 1e-3) / 1e9, 1), "peak_gbs": peak,
+            "frac": round(algo / (per_step * 1e-3) / 1e9 / peak, 4), "peak_source": which, "gpu_launches": int(ctr["kernel_launches"])}
+
+
 def moe_decode(lc, synth, local: int, n_seqs: int = 16, prompt_len: int = 1024, steps: int = 64, warm: int = 3, layers: int = 0) -> dict:
     """BASELINE.json configs[3] on ONE GPU: Mixtral-8x7B shape (32 layers, hidden 4096, 32 q / 8 kv heads, 8 experts of FFN 14336,
     two per token, vocabulary 32000), experts and attention Q4_K, f32 router; 16 sequences with 1024-token seeded prompts, then
@@ -722,6 +748,7 @@ def run_ours(args):
             if not args.no_cpu:
                 line["tiny"]["cpu_baseline"] = tiny_cpu()
             line["moe"] = moe_decode(lc, synth, local)
+            line["q4km"] = q4km_decode(lc, synth, local)
         if world > 1 and not args.no_extra and args.layers <= 0:
             extra = cut_model_legs(lc, synth, ranks, rank, world, local)
             if rank == 0:
@@ -771,7 +798,7 @@ def main():
     ap.add_argument("--no-bs64", action="store_true", help="skip the 64-sequence continuous-batching leg (configs[2])")
     ap.add_argument("--no-extra", action="store_true", help="skip the legs after the metric: configs[0], configs[3] (one GPU), the cut 70B / mixture models (several GPUs)")
     ap.add_argument("--ref-context", type=int, default=64, help="--impl reference: context of the sampled CPU run (the oracle's prefill is slow)")
-    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64", "moe", "tiny", "tp-ranks", "tcgen05-probe"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count; tp-ranks: the ranks of a cut 70B-shape model as one in-process group on one GPU (what each rank's kernels cost)")
+    ap.add_argument("--only", default="", choices=["", "gemv", "attn", "gemv-sweep", "gemv-types", "gemm", "gemm-small", "bs64", "moe", "tiny", "q4km", "tp-ranks", "tcgen05-probe"], help="gemv / attn: run just the isolated GEMV or decode-attention loop (small cases for profilers); gemv-sweep: GEMV time against row count; tp-ranks: the ranks of a cut 70B-shape model as one in-process group on one GPU (what each rank's kernels cost)")
     ap.add_argument("--gemm-shapes", default="", help="--only gemm: k x n pairs instead of the 7B layer shapes, e.g. 1024x12288,8192x12288")
     ap.add_argument("--gemm-tokens", default="", help="--only gemm: token counts instead of 64,512")
     ap.add_argument("--tp", type=int, default=8, help="--only tp-ranks: ranks the model is cut over")
@@ -796,6 +823,11 @@ def main():
         if args.layers > 0:
             out["not_the_metric"] = f"profiling case: {args.layers} of 32 layers"
         print(json.dumps(out))
+    elif args.only == "q4km":
+        import leafcutterllm_b200 as lc
+        from leafcutterllm_b200 import synth
+        lc._capi.check(lc.load().lc_set_device(0))
+        print(json.dumps(q4km_decode(lc, synth, 0, prompt_len=args.prompt_len, steps=min(args.steps, 64), layers=args.layers)))
     elif args.only in ("moe", "tiny"):
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth

@@ -1,5 +1,5 @@
 // Deterministic synthetic weights: a counter-based N(0, sigma) generator and
-// GGUF-order Q4_0 / Q8_0 / Q4_K quantisers, written so that the host build and
+// GGUF-order Q4_0 / Q8_0 / Q4_K / Q5_K / Q6_K quantisers, written so that the host build and
 // the device build of this one file produce IDENTICAL bytes.
 //
 // How bit-equality across CPU and GPU is kept: only IEEE-exact operations are
@@ -13,7 +13,9 @@
 // absmax recipes of rust/src/kernels/q4_0.rs:98-137 and q8_0.rs:90-122 with
 // the element order of the GGUF dequantisers (rust/src/kernels/mod.rs:16-51).
 // The Q4_K rule (per-32 min/max -> 6-bit scale/min against per-256 d, dmin) is
-// this project's own and is inverted exactly by rust/src/kernels/mod.rs:54-98.
+// this project's own and is inverted exactly by rust/src/kernels/mod.rs:54-98;
+// Q5_K is the same rule with 32 levels (mod.rs:101-143), Q6_K a per-16 absmax
+// against an int8 scale and a per-256 d (mod.rs:145-180).
 #pragma once
 #include <stdint.h>
 
@@ -279,12 +281,93 @@ LCS_HD void lcs_quantize_q4_k_block(const float* x, uint8_t* out) {
     }
 }
 
+// Q5_K, 176 bytes per 256 elements: the Q4_K header, 32 bytes of fifth bits (bit s of byte l = element l of sub-block s),
+// 128 nibble bytes.
+LCS_HD void lcs_quantize_q5_k_block(const float* x, uint8_t* out) {
+    float scale[8], mn[8];
+    float max_scale = 0.0f, max_min = 0.0f;
+    for (int j = 0; j < 8; j++) {
+        float lo = 0.0f, hi = 0.0f;
+        for (int i = 0; i < 32; i++) { float v = x[j * 32 + i]; if (v < lo) lo = v; if (v > hi) hi = v; }
+        scale[j] = LCS_FDIV(LCS_FSUB(hi, lo), 31.0f);
+        mn[j] = -lo;
+        if (scale[j] > max_scale) max_scale = scale[j];
+        if (mn[j] > max_min) max_min = mn[j];
+    }
+    uint16_t hd = lcs_f32_to_f16(LCS_FDIV(max_scale, 63.0f));
+    uint16_t hm = lcs_f32_to_f16(LCS_FDIV(max_min, 63.0f));
+    float d = lcs_f16_to_f32(hd), dmin = lcs_f16_to_f32(hm);
+    out[0] = (uint8_t)(hd & 0xFF); out[1] = (uint8_t)(hd >> 8);
+    out[2] = (uint8_t)(hm & 0xFF); out[3] = (uint8_t)(hm >> 8);
+    uint8_t sc[8], mm[8];
+    for (int j = 0; j < 8; j++) {
+        sc[j] = d > 0.0f ? (uint8_t)lcs_clamp(lcs_round(LCS_FDIV(scale[j], d)), 0.0f, 63.0f) : 0;
+        mm[j] = dmin > 0.0f ? (uint8_t)lcs_clamp(lcs_round(LCS_FDIV(mn[j], dmin)), 0.0f, 63.0f) : 0;
+    }
+    uint8_t* s = out + 4;
+    for (int j = 0; j < 4; j++) {
+        s[j] = (uint8_t)((sc[j] & 63) | ((sc[j + 4] >> 4) << 6));
+        s[j + 4] = (uint8_t)((mm[j] & 63) | ((mm[j + 4] >> 4) << 6));
+        s[j + 8] = (uint8_t)((sc[j + 4] & 0x0F) | ((mm[j + 4] & 0x0F) << 4));
+    }
+    uint8_t* qh = out + 16;
+    uint8_t* qs = out + 48;
+    for (int l = 0; l < 32; l++) qh[l] = 0;
+    for (int g = 0; g < 4; g++) {
+        float dl1 = LCS_FMUL(d, (float)sc[2 * g]), ml1 = LCS_FMUL(dmin, (float)mm[2 * g]);
+        float dl2 = LCS_FMUL(d, (float)sc[2 * g + 1]), ml2 = LCS_FMUL(dmin, (float)mm[2 * g + 1]);
+        for (int l = 0; l < 32; l++) {
+            int q1 = 0, q2 = 0;
+            if (dl1 > 0.0f) q1 = (int)lcs_clamp(lcs_round(LCS_FDIV(LCS_FADD(x[64 * g + l], ml1), dl1)), 0.0f, 31.0f);
+            if (dl2 > 0.0f) q2 = (int)lcs_clamp(lcs_round(LCS_FDIV(LCS_FADD(x[64 * g + 32 + l], ml2), dl2)), 0.0f, 31.0f);
+            qs[32 * g + l] = (uint8_t)((q1 & 15) | ((q2 & 15) << 4));
+            qh[l] = (uint8_t)(qh[l] | ((q1 >> 4) << (2 * g)) | ((q2 >> 4) << (2 * g + 1)));
+        }
+    }
+}
+
+// Q6_K, 210 bytes per 256 elements: 128 bytes of low nibbles, 64 bytes of high bit pairs, 16 int8 scales (one per 16
+// elements), f16 d.  Element 128 n + 32 j + l: nibble j / 2 of ql[64 n + 32 (j & 1) + l], bits 2 j of qh[32 n + l].
+LCS_HD void lcs_quantize_q6_k_block(const float* x, uint8_t* out) {
+    float scale[16];
+    float max_scale = 0.0f;
+    for (int j = 0; j < 16; j++) {
+        float amax = 0.0f;
+        for (int i = 0; i < 16; i++) { float a = x[j * 16 + i] < 0.0f ? -x[j * 16 + i] : x[j * 16 + i]; if (a > amax) amax = a; }
+        scale[j] = LCS_FDIV(amax, 31.0f);
+        if (scale[j] > max_scale) max_scale = scale[j];
+    }
+    uint16_t hd = lcs_f32_to_f16(LCS_FDIV(max_scale, 127.0f));
+    float d = lcs_f16_to_f32(hd);
+    out[208] = (uint8_t)(hd & 0xFF); out[209] = (uint8_t)(hd >> 8);
+    int sc[16];
+    for (int j = 0; j < 16; j++) {
+        sc[j] = d > 0.0f ? (int)lcs_clamp(lcs_round(LCS_FDIV(scale[j], d)), 0.0f, 127.0f) : 0;
+        out[192 + j] = (uint8_t)(int8_t)sc[j];
+    }
+    for (int i = 0; i < 192; i++) out[i] = 0;
+    for (int n = 0; n < 2; n++)
+        for (int j = 0; j < 4; j++)
+            for (int l = 0; l < 32; l++) {
+                int e = 128 * n + 32 * j + l;
+                float dl = LCS_FMUL(d, (float)sc[e / 16]);
+                int q = 32;
+                if (dl > 0.0f) q = (int)lcs_clamp(LCS_FADD(lcs_round(LCS_FDIV(x[e], dl)), 32.0f), 0.0f, 63.0f);
+                uint8_t* ql = out + 64 * n + 32 * (j & 1) + l;
+                uint8_t* qh = out + 128 + 32 * n + l;
+                *ql = (uint8_t)(*ql | ((q & 15) << (4 * (j >> 1))));
+                *qh = (uint8_t)(*qh | ((q >> 4) << (2 * j)));
+            }
+}
+
 // ggml type codes used here (rust/src/model/quant.rs:45-76).
 #define LCS_TYPE_F32 0
 #define LCS_TYPE_F16 1
 #define LCS_TYPE_Q4_0 2
 #define LCS_TYPE_Q8_0 8
 #define LCS_TYPE_Q4_K 12
+#define LCS_TYPE_Q5_K 13
+#define LCS_TYPE_Q6_K 14
 
 // Writes the quantised bytes of block `blk` (block index over the flattened
 // row-major tensor) of the synthetic tensor into `out`.
@@ -293,6 +376,11 @@ LCS_HD void lcs_synth_block(uint32_t typ, uint64_t seed, uint64_t name_hash, flo
         float x[256];
         for (int i = 0; i < 256; i++) x[i] = lcs_normal(seed, name_hash, blk * 256 + i, sigma);
         lcs_quantize_q4_k_block(x, out);
+    } else if (typ == LCS_TYPE_Q5_K || typ == LCS_TYPE_Q6_K) {
+        float x[256];
+        for (int i = 0; i < 256; i++) x[i] = lcs_normal(seed, name_hash, blk * 256 + i, sigma);
+        if (typ == LCS_TYPE_Q5_K) lcs_quantize_q5_k_block(x, out);
+        else lcs_quantize_q6_k_block(x, out);
     } else if (typ == LCS_TYPE_Q4_0) {
         float x[32];
         for (int i = 0; i < 32; i++) x[i] = lcs_normal(seed, name_hash, blk * 32 + i, sigma);

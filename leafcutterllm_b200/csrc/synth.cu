@@ -7,6 +7,11 @@
 
 namespace lc {
 
+static bool synth_has_quantiser(uint32_t typ) {
+    return typ == LC_TYPE_F32 || typ == LC_TYPE_F16 || typ == LC_TYPE_Q4_0 || typ == LC_TYPE_Q8_0 || typ == LC_TYPE_Q4_K || typ == LC_TYPE_Q5_K ||
+           typ == LC_TYPE_Q6_K;
+}
+
 __global__ void synth_kernel(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigma, size_t n_blocks,
                              uint32_t block_bytes, uint8_t* out) {
     size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -29,7 +34,7 @@ int32_t launch_synth_part(uint32_t typ, uint64_t seed, uint64_t name_hash, float
                           size_t blk0, size_t blks, void* out_dev, cudaStream_t s) {
     QuantGeom g;
     LC_CHECK(quant_geom(typ, &g), LC_ERR_UNSUPPORTED, "synth: unsupported ggml type %u", typ);
-    LC_CHECK(typ == LC_TYPE_F32 || typ == LC_TYPE_F16 || typ == LC_TYPE_Q4_0 || typ == LC_TYPE_Q8_0 || typ == LC_TYPE_Q4_K,
+    LC_CHECK(synth_has_quantiser(typ),
              LC_ERR_UNSUPPORTED, "synth: no quantiser for ggml type %u", typ);
     LC_CHECK(blk0 + blks <= row_blocks, LC_ERR_INVALID, "synth: blocks %zu..%zu outside a row of %zu", blk0, blk0 + blks, row_blocks);
     const size_t total = rows * blks;
@@ -46,7 +51,7 @@ int32_t launch_synth(uint32_t typ, uint64_t seed, uint64_t name_hash, float sigm
                      cudaStream_t s) {
     QuantGeom g;
     LC_CHECK(quant_geom(typ, &g), LC_ERR_UNSUPPORTED, "synth: unsupported ggml type %u", typ);
-    LC_CHECK(typ == LC_TYPE_F32 || typ == LC_TYPE_F16 || typ == LC_TYPE_Q4_0 || typ == LC_TYPE_Q8_0 || typ == LC_TYPE_Q4_K,
+    LC_CHECK(synth_has_quantiser(typ),
              LC_ERR_UNSUPPORTED, "synth: no quantiser for ggml type %u", typ);
     LC_CHECK(n_elems % g.block_elems == 0, LC_ERR_INVALID, "synth: %zu elements is not a whole number of blocks", n_elems);
     size_t nb = n_elems / g.block_elems;
@@ -69,7 +74,7 @@ int32_t lc_synth_tensor_host(uint32_t typ, uint64_t seed, const char* name, floa
     QuantGeom g;
     LC_CHECK(name && out_bytes, LC_ERR_INVALID, "lc_synth_tensor_host: null argument");
     LC_CHECK(quant_geom(typ, &g), LC_ERR_UNSUPPORTED, "synth: unsupported ggml type %u", typ);
-    LC_CHECK(typ == LC_TYPE_F32 || typ == LC_TYPE_F16 || typ == LC_TYPE_Q4_0 || typ == LC_TYPE_Q8_0 || typ == LC_TYPE_Q4_K,
+    LC_CHECK(synth_has_quantiser(typ),
              LC_ERR_UNSUPPORTED, "synth: no quantiser for ggml type %u", typ);
     LC_CHECK(n_elems % g.block_elems == 0, LC_ERR_INVALID, "synth: %zu elements is not a whole number of blocks", n_elems);
     size_t nb = n_elems / g.block_elems;

@@ -13,7 +13,7 @@ from typing import Iterator, Tuple
 
 import numpy as np
 
-from ._capi import TYPE_F32, TYPE_Q4_0, TYPE_Q4_K, TYPE_Q8_0, check, load
+from ._capi import TYPE_F32, TYPE_Q4_0, TYPE_Q4_K, TYPE_Q6_K, TYPE_Q8_0, check, load
 
 SIGMA = 0.02
 WEIGHT_SEED = 1234
@@ -34,12 +34,25 @@ class ModelSpec:
     embed_type: int = TYPE_Q4_K
     head_type: int = TYPE_Q4_K
     tied_head: bool = False
+    mix: str = ""        # "q4_k_m": the type mix of such a file (see mixed_type) instead of layer_type / head_type throughout
     n_experts: int = 0   # > 0: a mixture-of-experts FFN in every layer (f32 router + n_experts SwiGLU experts, top_k of them per token)
     top_k: int = 0
 
     @property
     def head_dim(self) -> int:
         return self.hidden_size // self.num_heads
+
+    def mixed_type(self, layer: int, which: str) -> int:
+        """The type of attn_v / ffn_down of a layer (which = "v" | "down") and of the head (layer = -1).  With mix = "q4_k_m":
+        Q6_K for the head and, for attn_v and ffn_down, in the first and last eighth of the layers and every third layer
+        between; Q4_K elsewhere -- the placement the usual quantisation tool gives its "Q4_K_M" files."""
+        if self.mix != "q4_k_m":
+            return self.head_type if layer < 0 else self.layer_type
+        if layer < 0:
+            return TYPE_Q6_K
+        n = self.num_layers
+        more = layer < n // 8 or layer >= 7 * n // 8 or (layer - n // 8) % 3 == 2
+        return TYPE_Q6_K if more else TYPE_Q4_K
 
     def tensors(self) -> Iterator[Tuple[str, int, Tuple[int, ...], str]]:
         """(gguf name, ggml type, dims fastest-first, 'normal' | 'ones')"""
@@ -48,13 +61,13 @@ class ModelSpec:
         yield "token_embd.weight", self.embed_type, (H, V), "normal"
         yield "output_norm.weight", TYPE_F32, (H,), "ones"
         if not self.tied_head:
-            yield "output.weight", self.head_type, (H, V), "normal"
+            yield "output.weight", self.mixed_type(-1, "head"), (H, V), "normal"
         for l in range(self.num_layers):
             p = f"blk.{l}."
             yield p + "attn_norm.weight", TYPE_F32, (H,), "ones"
             yield p + "attn_q.weight", self.layer_type, (H, nq), "normal"
             yield p + "attn_k.weight", self.layer_type, (H, nkv), "normal"
-            yield p + "attn_v.weight", self.layer_type, (H, nkv), "normal"
+            yield p + "attn_v.weight", self.mixed_type(l, "v"), (H, nkv), "normal"
             yield p + "attn_output.weight", self.layer_type, (nq, H), "normal"
             yield p + "ffn_norm.weight", TYPE_F32, (H,), "ones"
             if self.n_experts > 0:
@@ -67,7 +80,7 @@ class ModelSpec:
                 continue
             yield p + "ffn_gate.weight", self.layer_type, (H, F), "normal"
             yield p + "ffn_up.weight", self.layer_type, (H, F), "normal"
-            yield p + "ffn_down.weight", self.layer_type, (F, H), "normal"
+            yield p + "ffn_down.weight", self.mixed_type(l, "down"), (F, H), "normal"
 
     def with_layers(self, n: int) -> "ModelSpec":
         import dataclasses
@@ -78,6 +91,8 @@ class ModelSpec:
 TINY = ModelSpec("tinyllama-1.1b-shape-q4_0", 22, 2048, 32, 4, 5632, 32000, 10000.0, TYPE_Q4_0, TYPE_Q8_0, TYPE_Q8_0)
 # Llama-2-7B shape, Q4_K throughout.
 LLAMA7B = ModelSpec("llama2-7b-shape-q4_k", 32, 4096, 32, 32, 11008, 32000, 10000.0, TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K)
+# Llama-2-7B shape with the type mix of a "Q4_K_M" file: Q6_K head, Q6_K attn_v and ffn_down in about half of the layers.
+LLAMA7B_Q4KM = ModelSpec("llama2-7b-shape-q4_k_m", 32, 4096, 32, 32, 11008, 32000, 10000.0, TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K, mix="q4_k_m")
 # Mixtral-8x7B shape: 8 experts of FFN 14336, two per token, 32 q / 8 kv heads, Q4_K (router f32).
 MIXTRAL = ModelSpec("mixtral-8x7b-shape-q4_k", 32, 4096, 32, 8, 14336, 32000, 10000.0, TYPE_Q4_K, TYPE_Q4_K, TYPE_Q4_K, n_experts=8, top_k=2)
 # Llama-3-70B shape, Q4_K.

@@ -1028,6 +1028,8 @@ int orc_synth_tensor(uint32_t typ, uint64_t seed, const char* name, float sigma,
         case 2: be = 32; bb = 18; break;
         case 8: be = 32; bb = 34; break;
         case 12: be = 256; bb = 144; break;
+        case 13: be = 256; bb = 176; break;
+        case 14: be = 256; bb = 210; break;
         default: return -1;
     }
     if (!name || !out_bytes || n_elems % be) return -1;

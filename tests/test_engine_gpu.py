@@ -37,6 +37,26 @@ def test_forward_and_generate_small(gpu, oracle, types):
     eng.close()
 
 
+@pytest.mark.parametrize("on_device", [False, True])
+def test_q4_k_m_mix_with_generated_weights(gpu, oracle, on_device):
+    """Eight layers with the type mix of a "Q4_K_M" file (Q6_K head; Q6_K attn_v and ffn_down in layers 0, 3, 6, 7), weights
+    from the generator's own Q4_K and Q6_K quantisers on the host and on the device: prefill logits, a decode step and
+    greedy tokens against the oracle."""
+    from leafcutterllm_b200 import synth
+    from leafcutterllm_b200.synth import ModelSpec
+    spec = ModelSpec("small-q4_k_m", 8, 256, 8, 2, 768, 1008, 10000.0, 12, 12, 12, mix="q4_k_m")
+    assert [l for l in range(8) if spec.mixed_type(l, "down") == 14] == [0, 3, 6, 7]
+    eng, om = make_pair(gpu, oracle, spec, max_seq_len=96, on_device=on_device)
+    prompt = synth.prompt_tokens(21, spec.vocab_size, 5)
+    want = om.forward(prompt)
+    assert_close(eng.forward(prompt), want, LOGIT_ABS, LOGIT_REL, "prefill logits")
+    nxt = int(np.argmax(want))
+    assert_close(eng.forward([nxt]), om.forward([nxt]), LOGIT_ABS, LOGIT_REL, "decode logits")
+    ref, margins = om.generate(prompt, 20, stop_on_eos=False, want_margins=True)
+    assert eng.generate(prompt, 20, stop_on_eos=False) == ref, margins
+    eng.close()
+
+
 def test_layer_probes(gpu, oracle):
     spec = small_spec(12, 12, 12, layers=1, hidden=512, heads=8, kv=4, ffn=768)
     eng, om = make_pair(gpu, oracle, spec, max_seq_len=64)

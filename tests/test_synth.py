@@ -23,7 +23,8 @@ def test_host_generator_is_normal_0_02(lc):
     assert np.abs(z).max() < 6.5
 
 
-@pytest.mark.parametrize("typ,tol", [(8, 0.02 * 4.5 / 127 * 0.51), (2, 0.02 * 4.5 / 8 * 1.01), (12, 0.02 * 9 / 15 * 0.6)])
+@pytest.mark.parametrize("typ,tol", [(8, 0.02 * 4.5 / 127 * 0.51), (2, 0.02 * 4.5 / 8 * 1.01), (12, 0.02 * 9 / 15 * 0.6),
+                                     (13, 0.02 * 9 / 31 * 0.6), (14, 0.02 * 4.5 / 31 * 0.6)])
 def test_quantisers_round_trip_through_the_reference_dequantisers(lc, oracle, typ, tol):
     from leafcutterllm_b200 import synth
     n = 256 * 64
@@ -55,7 +56,7 @@ def test_prompt_tokens_are_uniform_and_seeded(lc):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("typ", [0, 1, 2, 8, 12])
+@pytest.mark.parametrize("typ", [0, 1, 2, 8, 12, 13, 14])
 def test_device_generator_matches_host_bytes(gpu, typ):
     import ctypes as C
     from leafcutterllm_b200 import synth
@@ -76,8 +77,22 @@ def test_oracle_side_generator_makes_the_same_bytes(lc, oracle):
     its generator must make the bytes the CUDA library's host generator makes."""
     import numpy as np
     from leafcutterllm_b200 import synth
-    for typ, n in [(12, 256 * 40), (2, 32 * 70), (8, 32 * 70), (0, 1000), (1, 1000)]:
+    for typ, n in [(12, 256 * 40), (13, 256 * 40), (14, 256 * 40), (2, 32 * 70), (8, 32 * 70), (0, 1000), (1, 1000)]:
         a = synth.host_tensor(typ, 1234, "blk.3.ffn_up.weight", n)
         b = oracle.synth_tensor(typ, 1234, "blk.3.ffn_up.weight", synth.SIGMA, n)
         assert np.array_equal(a, b), typ
     assert np.array_equal(synth.prompt_tokens(50, 32000, 3), oracle.synth_tokens(synth.PROMPT_SEED + 3, 50, 32000))
+
+
+def test_q4_k_m_type_mix(lc):
+    """The "Q4_K_M" spec keeps q, k, o, gate, up and the embedding in Q4_K, and puts the head and -- in the first and last
+    eighth of the layers and every third layer between -- attn_v and ffn_down in Q6_K."""
+    from leafcutterllm_b200 import synth
+    spec = synth.LLAMA7B_Q4KM
+    types = {name: typ for name, typ, _, _ in spec.tensors()}
+    assert types["output.weight"] == 14 and types["token_embd.weight"] == 12
+    q6_layers = [l for l in range(32) if types[f"blk.{l}.ffn_down.weight"] == 14]
+    assert q6_layers == [0, 1, 2, 3, 6, 9, 12, 15, 18, 21, 24, 27, 28, 29, 30, 31]
+    assert all(types[f"blk.{l}.attn_v.weight"] == types[f"blk.{l}.ffn_down.weight"] for l in range(32))
+    assert all(types[f"blk.{l}.{t}.weight"] == 12 for l in range(32) for t in ("attn_q", "attn_k", "attn_output", "ffn_gate", "ffn_up"))
+    assert all(typ == 12 for name, typ, _, _ in synth.LLAMA7B.tensors() if not name.endswith("norm.weight"))
