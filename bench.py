@@ -819,7 +819,7 @@ def main():
         import leafcutterllm_b200 as lc
         from leafcutterllm_b200 import synth
         spec = synth.LLAMA7B if args.layers <= 0 else synth.LLAMA7B.with_layers(args.layers)
-        out = batched_decode(lc, synth, spec, 0, steps=min(args.steps, 32), profile_range=args.profile_range)
+        out = batched_decode(lc, synth, spec, 0, steps=min(args.steps, 128), profile_range=args.profile_range)
         if args.layers > 0:
             out["not_the_metric"] = f"profiling case: {args.layers} of 32 layers"
         print(json.dumps(out))
