@@ -430,7 +430,7 @@ int32_t lc_dequantize_dev(uint32_t typ, const void* bytes_dev, size_t n_elems, f
 }
 
 // Rows of `a` against a quantised matrix: token tiles of at most 8 rows per pass of the matrix-vector kernels, or -- for
-// five rows and more of Q4_K -- chunks of up to 512 rows through the tensor-core product (qgemm_umma.cu).
+// five rows and more of Q4_K or Q5_K -- chunks of up to 512 rows through the tensor-core product (qgemm_umma.cu).
 static int32_t qmatmul_rows(const QWeight& w, const float* a_dev, size_t m, float* c_dev) {
     static GemmWorkspace ws;  // callers are serialised (L1 mutex / single library stream)
     GemvArgs probe;
@@ -438,7 +438,7 @@ static int32_t qmatmul_rows(const QWeight& w, const float* a_dev, size_t m, floa
     probe.x = a_dev;
     probe.out = c_dev;
     const int chunk = 512;
-    if (w.typ == LC_TYPE_Q4_K && w.has_tmap && m >= 5) {
+    if ((w.typ == LC_TYPE_Q4_K || w.typ == LC_TYPE_Q5_K) && w.has_tmap && m >= 5) {
         if (!ws.xh || ws.k_max < w.k) {
             qgemm_workspace_free(&ws);
             LC_TRY(qgemm_workspace_alloc(&ws, chunk, w.k));

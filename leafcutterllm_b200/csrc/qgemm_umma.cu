@@ -1,4 +1,4 @@
-// Q4_K weights times MANY tokens (prefill chunks, batched decode steps of five or more sequences) on the
+// Q4_K (and Q5_K: the kernel's UB = 176 form) weights times MANY tokens (prefill chunks, batched decode steps of five or more sequences) on the
 // 5th-generation tensor cores: the dense contraction of the path (Tensor::matmul with m > 1, rust/src/tensor.rs:107-135,
 // over weights that the reference dequantises per call, rust/src/model/loader.rs:213-224).
 //
@@ -56,7 +56,7 @@ constexpr int kUnpackGroups = 3;  // groups of four warps that take the units of
 constexpr int kDrainGroups = 2;   // groups of four warps that each drain half of the tokens
 constexpr int kThreads = 32 * (4 + 4 * kUnpackGroups + 4 * kDrainGroups);  // warps 0 and 3 producers, 1-2 the two issuers, then the unpack groups, then the drain
 constexpr int kDRing = 8;      // units whose per-row d travel from the unpack threads to the drain at a time
-constexpr int kUnitBytes = 144;
+constexpr int kUnitBytes = 144;  // Q4_K; a Q5_K unit has 176 (the kernel's UB)
 // tensor-memory columns
 constexpr uint32_t kColD = 0;            // accumulators of pipeline g at g * kColsPerPipe: [0, 2N) sum (sc q) x_hi | sum (sc q) x_lo of its unit in progress
 constexpr uint32_t kColsPerPipe = 128;
@@ -148,19 +148,31 @@ __device__ __forceinline__ uint32_t h2_pair(float v) {  // (v, v) as f16x2; v is
 // Chunk c of a unit = group c of mod.rs:77-96: 32 bytes whose low nibbles are elements 0..31 under sc[2c] and whose high
 // nibbles are elements 32..63 under sc[2c + 1].  Column j of `col` holds (sc q) of elements 2j, 2j + 1, exact in f16:
 // (1024 + q) * sc - 1024 * sc is one fused multiply-add whose exact result, at most 945, needs no rounding.
+// UB = 176: a Q5_K unit (mod.rs:101-143) -- the same header, then 32 bytes whose bit s is the fifth bit of element l of
+// sub-block s, then the nibbles: q < 32, (sc q) at most 1953, still exact.
+template <int UB>
 __device__ __forceinline__ void unpack_chunk(const unsigned char* rp, const HdrQ4K& h, int c, uint32_t (&col)[32]) {
     const uint32_t scw = c < 2 ? h.sc_lo : h.sc_hi;
     const int sh = (c & 1) * 16;
     const float fa = (float)((scw >> sh) & 0xFFu), fb = (float)((scw >> (sh + 8)) & 0xFFu);
     const uint32_t sa = h2_pair(fa), sb = h2_pair(fb), ka = h2_pair(-1024.0f * fa), kb = h2_pair(-1024.0f * fb);
-    const uint4* q = reinterpret_cast<const uint4*>(rp + 16 + 32 * c);
+    const uint4* q = reinterpret_cast<const uint4*>(rp + (UB == 176 ? 48 : 16) + 32 * c);
 #pragma unroll
     for (int half = 0; half < 2; half++) {
         const uint4 v = q[half];
         const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+        uint32_t hb[4] = {0u, 0u, 0u, 0u};
+        if constexpr (UB == 176) {
+            const uint4 hq = *reinterpret_cast<const uint4*>(rp + 16 + 16 * half);
+            hb[0] = hq.x; hb[1] = hq.y; hb[2] = hq.z; hb[3] = hq.w;
+        }
 #pragma unroll
         for (int wi = 0; wi < 4; wi++) {
-            const uint32_t lo4 = vv[wi] & 0x0F0F0F0Fu, hi4 = (vv[wi] >> 4) & 0x0F0F0F0Fu;
+            uint32_t lo4 = vv[wi] & 0x0F0F0F0Fu, hi4 = (vv[wi] >> 4) & 0x0F0F0F0Fu;
+            if constexpr (UB == 176) {
+                lo4 |= ((hb[wi] >> (2 * c)) & 0x01010101u) << 4;
+                hi4 |= ((hb[wi] >> (2 * c + 1)) & 0x01010101u) << 4;
+            }
             const int j = half * 8 + wi * 2;
             col[j] = h2_fma(bias_pair(lo4, 0), sa, ka);
             col[j + 1] = h2_fma(bias_pair(lo4, 1), sa, ka);
@@ -308,6 +320,7 @@ xprep_kernel(const float* __restrict__ x, const float* __restrict__ norm_w, floa
 // remainder), the sixteen values of a unit form one K = 16 operand against the sub-block sums stored twice, and the
 // products of all units accumulate in ONE set of columns, read once at the end; the two issuers take turns on it (each
 // waits for the completion of the other's unit before), so the additions happen in k order.
+template <int UB>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_constant__ CUtensorMap tmw1,
                       const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tms, GemmParams p) {
@@ -324,7 +337,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
     const int RS = p.raw_stages;
     constexpr int BS = kMaxB;
     const bool two = p.terms == 3;
-    constexpr uint32_t raw_bytes = kUnitBytes * kRows;
+    constexpr uint32_t raw_bytes = UB * kRows;
     const uint32_t b_half = (uint32_t)N * 128u, b_bytes = 2u * b_half;
 
     unsigned char* bt = smem;                              // [BS][2 chunks][hi N x 128 B | lo N x 128 B], 1024-byte aligned
@@ -425,7 +438,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 const int sr = s % RS;
                 if (!twait(&raw_empty[sr], ((s / RS) & 1) ^ 1, 0)) { ok = false; break; }
                 mbar_expect_tx(&raw_full[sr], raw_bytes);
-                tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + s) * (kUnitBytes / 4), tile * kRows, &raw_full[sr]);
+                tma_load_2d(raw + (size_t)sr * raw_bytes, mat ? &tmw1 : &tmw0, (u_begin + s) * (UB / 4), tile * kRows, &raw_full[sr]);
                 // with an odd number of stages a stage serves the two unpack groups in turn, and a group that waited for unit
                 // s before unit s - RS had landed would read that phase's parity as its own: it first waits for this count
                 asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(raw_issued)), "r"((uint32_t)(s + 1)) : "memory");
@@ -499,7 +512,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
             }
             ok = wait_all(&raw_full[sr], (s / RS) & 1, 1);
             if (!ok) break;
-            const unsigned char* rp = raw + (size_t)sr * raw_bytes + (size_t)row * kUnitBytes;
+            const unsigned char* rp = raw + (size_t)sr * raw_bytes + (size_t)row * UB;
             HdrQ4K hdr;
             load_hdr(rp, hdr);
             // the ring is deep enough: unit s + kDRing cannot be unpacked before unit s has been drained (its chunks need the
@@ -522,7 +535,7 @@ qgemm_umma_q4k_kernel(const __grid_constant__ CUtensorMap tmw0, const __grid_con
                 uint32_t col[32];
                 unsigned tq0 = 0;
                 if (tracing) tq0 = (unsigned)clock64();
-                unpack_chunk(rp, hdr, c, col);
+                unpack_chunk<UB>(rp, hdr, c, col);
                 if (tracing) { const unsigned t1 = (unsigned)clock64(); wacc[4] += t1 - tq0; tq0 = t1; }
                 // the chunk before this one (the offset operand ahead of the first) has had the time of this unpacking to reach
                 // tensor memory
@@ -823,7 +836,7 @@ __global__ void __launch_bounds__(512, 1) tcgen05_probe_kernel(double* out) {
                 load_hdr(rp, hdr);
                 for (int c = 0; c < 4; c++) {
                     uint32_t col[32];
-                    unpack_chunk(rp, hdr, c, col);
+                    unpack_chunk<kUnitBytes>(rp, hdr, c, col);
 #pragma unroll
                     for (int i = 0; i < 32; i++) acc ^= col[i];
                     asm volatile("" ::: "memory");
@@ -893,7 +906,7 @@ static int gemm_min_tokens() {
 }
 bool qgemm_applies(const GemvArgs& a, int T, const GemmWorkspace& ws) {
     if (!a.w || !ws.xh) return false;
-    if (a.w->typ != LC_TYPE_Q4_K || !a.w->has_tmap || a.w->k % kUnitElems != 0) return false;
+    if ((a.w->typ != LC_TYPE_Q4_K && a.w->typ != LC_TYPE_Q5_K) || !a.w->has_tmap || a.w->k % kUnitElems != 0) return false;
     if (a.epi == EPI_SILU_MUL && (!a.w2 || a.w2->typ != a.w->typ || !a.w2->has_tmap)) return false;
     if (T < gemm_min_tokens() || T > ws.t_cap || a.w->k > ws.k_max) return false;
     if (((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return false;
@@ -929,7 +942,9 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     // eight activation stages (two units: a stage always serves the same pipeline); the raw boxes take what is left
     const size_t b_bytes = (size_t)2 * N * 128;
     const size_t fixed = 1024 + (size_t)(2 * kMaxB + 2) * b_bytes + (size_t)kDRing * kRows * sizeof(float) + 512;
-    p.raw_stages = std::min(kMaxRaw, (int)((kMaxSmem - fixed) / ((size_t)kUnitBytes * kRows)));
+    const bool q5 = a.w->typ == LC_TYPE_Q5_K;
+    const size_t unit_bytes = q5 ? 176 : kUnitBytes;
+    p.raw_stages = std::min(kMaxRaw, (int)((kMaxSmem - fixed) / (unit_bytes * kRows)));
     if (getenv("LC_GEMM_RAWSTAGES")) p.raw_stages = std::max(2, std::min(p.raw_stages, atoi(getenv("LC_GEMM_RAWSTAGES"))));
     LC_CHECK(p.raw_stages >= 2, LC_ERR_UNSUPPORTED, "qgemm: shared memory too small");
     p.b_stages = kMaxB;
@@ -942,8 +957,9 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
         LC_CUDA(cudaMemsetAsync(d_trace, 0, 56 * sizeof(unsigned), s));
         p.trace = d_trace;
     }
-    const size_t smem = fixed + (size_t)p.raw_stages * kUnitBytes * kRows;
-    LC_CUDA(ensure_smem_limit((const void*)qgemm_umma_q4k_kernel, smem));
+    const size_t smem = fixed + (size_t)p.raw_stages * unit_bytes * kRows;
+    auto kern = q5 ? qgemm_umma_q4k_kernel<176> : qgemm_umma_q4k_kernel<kUnitBytes>;
+    LC_CUDA(ensure_smem_limit((const void*)kern, smem));
     const CUtensorMap* t0 = (const CUtensorMap*)a.w->tmap_wide;
     const CUtensorMap* t1 = a.w2 ? (const CUtensorMap*)a.w2->tmap_wide : t0;
     // Few tiles (a batched decode step on the square matrices): split k over several CTAs so that all SMs work; the
@@ -977,7 +993,7 @@ int32_t launch_qgemm(const GemvArgs& a, const GemmWorkspace& ws, cudaStream_t s,
     p.tiles = tiles; p.nmat = nmat;
     p.partial = summed ? ws.partial : nullptr;
     dim3 grid((unsigned)(tiles * nmat), (unsigned)ttiles, (unsigned)ks);
-    LC_CUDA(launch_pdl(qgemm_umma_q4k_kernel, grid, dim3(kThreads), smem, s, *t0, *t1, tmx, tms, p));
+    LC_CUDA(launch_pdl(kern, grid, dim3(kThreads), smem, s, *t0, *t1, tmx, tms, p));
     if (summed) {
         const size_t plane = (size_t)T * n;
         if (a.prep_next && n % kUnitElems == 0 && n <= ws.k_max) {

@@ -126,22 +126,23 @@ def test_qmatmul_vs_oracle(gpu, oracle, typ, m, k, n):
     assert_close(got, want, 2e-5 * scale, 1e-4, f"qmatmul typ={typ} {m}x{k}x{n}")
 
 
+@pytest.mark.parametrize("typ", [12, 13])
 @pytest.mark.parametrize("m,k,n", [(9, 256, 128), (16, 512, 128), (64, 4096, 512), (40, 2816, 300), (130, 1024, 256), (200, 11008, 128)])
-def test_qmatmul_q4k_many_tokens_tensor_core_gemm(gpu, oracle, monkeypatch, m, k, n):
-    """Nine tokens and more go through the tcgen05 product (weights dequantised into tensor memory as f16 high/low halves,
+def test_qmatmul_q4k_many_tokens_tensor_core_gemm(gpu, oracle, monkeypatch, typ, m, k, n):
+    """Q4_K and Q5_K (the same unit with a fifth bit per element).  Nine tokens and more go through the tcgen05 product (weights dequantised into tensor memory as f16 high/low halves,
     activations as swizzled f16 high/low tiles): one k unit, token counts that are not a multiple of 16 or of the
     64-token tile, rows that are not a multiple of 128, a long k.  Activations carry a wide dynamic range so that the
     per-token power-of-two scale matters."""
     from leafcutterllm_b200 import synth
-    w = synth.host_tensor(12, 43, f"gemm_{k}_{n}", n * k)
+    w = synth.host_tensor(typ, 43, f"gemm_{k}_{n}", n * k)
     r = rng(k + n + m)
     a = (r.standard_normal((m, k)) * np.exp(r.uniform(-6, 6, (m, 1)))).astype(np.float32).ravel()
-    got = gpu.qmatmul(12, a, w, m, k, n).reshape(m, n)
-    want = oracle.qmatmul(12, a, w, m, k, n).reshape(m, n)
+    got = gpu.qmatmul(typ, a, w, m, k, n).reshape(m, n)
+    want = oracle.qmatmul(typ, a, w, m, k, n).reshape(m, n)
     for t in range(m):  # per token: its own scale
         assert_close(got[t], want[t], 2e-5 * np.abs(want[t]).max(), 1e-4, f"gemm {m}x{k}x{n} token {t}")
     monkeypatch.setenv("LC_GEMM_TERMS", "1")  # plain f16 operands: 2^-11 per factor
-    fast = gpu.qmatmul(12, a, w, m, k, n).reshape(m, n)
+    fast = gpu.qmatmul(typ, a, w, m, k, n).reshape(m, n)
     for t in range(m):
         assert_close(fast[t], want[t], 4e-3 * np.abs(want[t]).max(), 0, f"one-term gemm token {t}")
 
