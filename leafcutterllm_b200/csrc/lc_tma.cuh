@@ -116,6 +116,9 @@ int32_t launch_qgemv_mma_q4k_grouped(const GemvArgs& a, cudaStream_t s, bool* la
 bool qgemv_mma_supports(int k);
 // qgemv_mma_q6k.cu: Q6_K through int8 tensor-core MMAs, up to four tokens; *launched = false when the shape does not fit.
 int32_t launch_qgemv_mma_q6k(const GemvArgs& a, cudaStream_t s, bool* launched);
+bool qgemv_mma_q6k_supports(const GemvArgs& a, int m);
+// true when the Q5_K form of the tensor-core matrix-vector kernel fits shared memory for four tokens of k elements
+bool qgemv_mma_q5k_supports4(int k);
 // qgemv_kq.cu: Q5_K, Q6_K, F16 and F32, up to eight tokens, plain loads; *launched = false for other types or shapes.
 int32_t launch_qgemv_kq(const GemvArgs& a, cudaStream_t s, bool* launched);
 

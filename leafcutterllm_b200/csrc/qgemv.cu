@@ -638,6 +638,22 @@ int32_t launch_qgemv(const GemvArgs& a, cudaStream_t s) {
         LC_TRY(launch_qgemv_mma_q6k(a, s, &launched));
         if (launched) return LC_OK;
     }
+    // Five to eight tokens of Q5_K / Q6_K (the token tiles of a prefill): two passes of the tensor-core kernels over the
+    // weights are several times faster than one of the plain-load kernel, whose every row pair re-reads all tokens' activations.
+    if (a.m > 4 && !a.push &&
+        ((a.w->typ == LC_TYPE_Q6_K && qgemv_mma_q6k_supports(a, 4)) ||
+         (a.w->typ == LC_TYPE_Q5_K && tma_ok && !q5k_plain && !force_fp32 && qgemv_mma_q5k_supports4(a.w->k) && ((uintptr_t)a.x % 16) == 0 &&
+          (!a.norm_w || ((uintptr_t)a.norm_w % 16) == 0)))) {
+        const int half = a.m / 2;
+        GemvArgs lo = a, hi = a;
+        lo.m = half;
+        hi.m = a.m - half;
+        hi.x = a.x + (size_t)half * a.w->k;
+        hi.out = a.out + (size_t)half * a.w->n;
+        if (a.residual) hi.residual = a.residual + (size_t)half * a.w->n;
+        LC_TRY(launch_qgemv(lo, s));
+        return launch_qgemv(hi, s);
+    }
     {
         bool launched = false;
         LC_TRY(launch_qgemv_kq(a, s, &launched));  // Q5_K / Q6_K with whole 256-element blocks, F16 / F32 rows

@@ -717,6 +717,10 @@ static int32_t launch_mma_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
     return LC_OK;
 }
 
+bool qgemv_mma_q5k_supports4(int k) {
+    return k > 0 && k % kUnitElems == 0 && (mma_smem_bytes<4, 16, 2>(k, false, 176) <= kMaxSmem || mma_smem_bytes<4, 8, 2>(k, false, 176) <= kMaxSmem);
+}
+
 bool qgemv_mma_supports(int k) {
     return k > 0 && k % kUnitElems == 0 && (mma_smem_bytes<1, 16, 2>(k) <= kMaxSmem || mma_smem_bytes<1, 8, 2>(k) <= kMaxSmem);
 }

@@ -405,16 +405,24 @@ int32_t launch_m(const GemvArgs& a, cudaStream_t s, bool* launched) {
 
 }  // namespace
 
+// true when launch_qgemv_mma_q6k would run these arguments with m tokens
+bool qgemv_mma_q6k_supports(const GemvArgs& a, int m) {
+    static const bool plain = getenv("LC_GEMV_Q6K_PLAIN") != nullptr;
+    const QWeight* w = a.w;
+    if (plain || !w || w->typ != LC_TYPE_Q6_K || a.group || a.push || m < 1 || m > 4) return false;
+    if (w->k <= 0 || w->k % kUnitElems != 0 || w->n <= 0 || w->n % kRows != 0) return false;
+    if (((uintptr_t)w->data % 16) != 0 || ((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return false;
+    if (a.epi == EPI_SILU_MUL && (!a.w2 || ((uintptr_t)a.w2->data % 16) != 0)) return false;
+    if (m <= 1) return q6k_smem_bytes<1, 8, 2>(w->k) <= kMaxSmem;
+    if (m <= 2) return q6k_smem_bytes<2, 8, 2>(w->k) <= kMaxSmem;
+    return q6k_smem_bytes<4, 8, 2>(w->k) <= kMaxSmem;
+}
+
 // Q6_K rows of whole 256-element blocks, a multiple of 16 rows, up to four tokens; *launched = false otherwise (the plain-load
 // kernel takes those) and when LC_GEMV_Q6K_PLAIN is set.
 int32_t launch_qgemv_mma_q6k(const GemvArgs& a, cudaStream_t s, bool* launched) {
     *launched = false;
-    static const bool plain = getenv("LC_GEMV_Q6K_PLAIN") != nullptr;
-    const QWeight* w = a.w;
-    if (plain || !w || w->typ != LC_TYPE_Q6_K || a.group || a.push || a.m < 1 || a.m > 4) return LC_OK;
-    if (w->k <= 0 || w->k % kUnitElems != 0 || w->n <= 0 || w->n % kRows != 0) return LC_OK;
-    if (((uintptr_t)w->data % 16) != 0 || ((uintptr_t)a.x % 16) != 0 || (a.norm_w && ((uintptr_t)a.norm_w % 16) != 0)) return LC_OK;
-    if (a.epi == EPI_SILU_MUL && (!a.w2 || ((uintptr_t)a.w2->data % 16) != 0)) return LC_OK;
+    if (!qgemv_mma_q6k_supports(a, a.m)) return LC_OK;
     if (a.m <= 1) return launch_m<1>(a, s, launched);
     if (a.m <= 2) return launch_m<2>(a, s, launched);
     return launch_m<4>(a, s, launched);

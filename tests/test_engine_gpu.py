@@ -215,7 +215,7 @@ def test_a_second_model_does_not_disturb_a_captured_decode_step(gpu, oracle):
 def test_mixed_quant_types_like_q4_k_m(gpu, oracle, other):
     """A "Q4_K_M" file keeps attn_v and ffn_down in Q6_K while q, k, o, gate and up are Q4_K: the three projections of a
     layer then cannot be one matrix (three products per layer); the Q6_K matrices run through the int8 tensor-core kernel
-    for one to four tokens (fused norm, residual epilogue) and the plain-load kernel for the 8-token tiles of the prefill.
+    (fused norm, residual epilogue), the 8-token tiles of the prefill as two passes of it.
     other = 14: every matrix is Q6_K (one fused q/k/v matrix, SiLU(gate) * up epilogue on Q6_K); other = 13: the Q5_K + Q6_K
     mix of a "Q5_K_M" file (Q5_K through the Q4_K kernel's fifth-bit variant).
     Prefill (17 tokens: the unfused parts are interleaved into the q/k/v rows), decode and greedy tokens against the oracle."""

@@ -98,6 +98,8 @@ QM_CASES = [
     (14, 1, 4096, 32000),
     # Q5_K on the Q4_K kernel's fifth-bit variant (one to four tokens)
     (13, 1, 11008, 4096), (13, 2, 2816, 77), (13, 3, 11008, 40), (13, 4, 4096, 33), (13, 1, 256, 8),
+    # five to eight tokens of these types: two passes of the tensor-core kernels
+    (14, 8, 4096, 64), (14, 6, 11008, 32), (14, 5, 512, 48), (13, 7, 11008, 40), (13, 8, 4096, 96),
 ]
 
 
