@@ -144,7 +144,8 @@ int32_t lc_flush_l2(void);
 
 /* Deterministic synthetic tensors (test and benchmark input; no counterpart in the reference).
  * Element i of tensor (seed, name) is N(0, sigma) from a counter-based generator, quantised to
- * `typ` in GGUF block order.  The host and the device generator produce identical bytes. */
+ * `typ` (F32, F16, Q4_0, Q8_0, Q4_K, Q5_K or Q6_K; LC_ERR_UNSUPPORTED otherwise) in GGUF block order.  The host and the
+ * device generator produce identical bytes. */
 int32_t lc_synth_tensor_host(uint32_t typ, uint64_t seed, const char* name, float sigma, size_t n_elems, void* out_bytes);
 int32_t lc_synth_tensor_dev(uint32_t typ, uint64_t seed, const char* name, float sigma, size_t n_elems, void* out_dev);
 int32_t lc_synth_tokens(uint64_t seed, size_t n, int64_t vocab, int64_t* out);
